@@ -1,0 +1,155 @@
+/*
+ * b200norm — C ABI of the sm_100a row-wise normalization / softmax kernels.
+ *
+ * Every entry point enqueues work on the CUDA stream the caller passes (a cudaStream_t cast to
+ * void*; NULL = the legacy default stream) and returns without synchronising the host.  The
+ * library allocates nothing unless an entry point's comment says otherwise: every input, output
+ * and workspace is a device pointer owned by the caller and borrowed only for the duration of the
+ * enqueued work.  All tensors are row-major contiguous.  Return value: B2N_OK (0) or a negative
+ * b2n_status.  Nothing here throws, aborts or traps.
+ *
+ * Each entry point replaces one launcher of intel/torch-xpu-ops; the citation next to it gives the
+ * reference declaration (path within that project) whose role it takes.
+ */
+#ifndef B200NORM_H_
+#define B200NORM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2N_ABI_VERSION 1
+
+/* element types; values are part of the ABI */
+typedef enum b2n_dtype {
+  B2N_F32 = 0,
+  B2N_F16 = 1,
+  B2N_BF16 = 2,
+  B2N_F64 = 3
+} b2n_dtype;
+
+typedef enum b2n_status {
+  B2N_OK = 0,
+  B2N_ERR_BAD_ARG = -1,           /* null pointer, negative size, bad enum */
+  B2N_ERR_UNSUPPORTED_DTYPE = -2, /* dtype combination has no kernel */
+  B2N_ERR_WORKSPACE = -3,         /* workspace missing or too small */
+  B2N_ERR_CUDA = -4,              /* a CUDA runtime call failed; see b2n_last_cuda_error */
+  B2N_ERR_TIMEOUT = -5,           /* a bounded device-side wait gave up (read via b2n_device_status) */
+  B2N_ERR_TARGET_RANGE = -6,      /* nll_loss: a target outside [0, C) that is not ignore_index */
+  B2N_ERR_TOO_LARGE = -7          /* size beyond what the entry point accepts */
+} b2n_status;
+
+/* reduction modes of nll_loss; same numbering as at::Reduction */
+typedef enum b2n_reduction { B2N_REDUCE_NONE = 0, B2N_REDUCE_MEAN = 1, B2N_REDUCE_SUM = 2 } b2n_reduction;
+
+/* kernel family selection, for tests and profiling; B2N_PATH_AUTO is what production uses */
+typedef enum b2n_path {
+  B2N_PATH_AUTO = 0,
+  B2N_PATH_GENERIC = 1, /* global-memory multi-pass kernels: any alignment, any N */
+  B2N_PATH_RING = 2,    /* persistent CTAs, bulk-async (TMA) shared-memory ring, register-resident rows */
+  B2N_PATH_CLUSTER = 3  /* long rows split over a thread-block cluster (distributed shared memory) */
+} b2n_path;
+
+int b2n_abi_version(void);
+const char* b2n_strerror(int status);
+/* cudaError_t of the most recent failing CUDA call made by this thread inside the library */
+int b2n_last_cuda_error(void);
+/* Force a kernel family for subsequent calls from this thread (b2n_path); returns the previous
+ * value.  A forced family that cannot take a given shape makes the call return
+ * B2N_ERR_BAD_ARG instead of silently using another one. */
+int b2n_set_path(int path);
+/* Name of the kernel family the most recent launch from this thread used ("generic", "ring", ...). */
+const char* b2n_last_path(void);
+/* Reads and clears the device-side status word of the current device (synchronises `stream`).
+ * 0, or the b2n_status recorded by a kernel (B2N_ERR_TIMEOUT, B2N_ERR_TARGET_RANGE). */
+int b2n_device_status(void* stream);
+
+/* ---- layer norm / RMS norm ------------------------------------------------------------------
+ * x, y: [M, N] of x_dtype.  gamma, beta: [N] of w_dtype or NULL (w_dtype == x_dtype or B2N_F32).
+ * mean, rstd: [M] of the accumulate type (float; double when x_dtype == B2N_F64).
+ *
+ * Replaces at::native::xpu::layer_norm_kernel (src/ATen/native/xpu/sycl/LayerNormKernels.h:19-28)
+ * behind layer_norm_xpu (src/ATen/native/xpu/LayerNorm.cpp:35). */
+int b2n_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, void* mean,
+                       void* rstd, int64_t M, int64_t N, double eps, int x_dtype, int w_dtype,
+                       void* stream);
+
+/* Replaces at::native::xpu::rms_norm_kernel (sycl/LayerNormKernels.h:42-49) behind
+ * _fused_rms_norm_xpu (LayerNorm.cpp:203).  y = gamma * (x * rstd), rstd = 1/sqrt(mean(x^2)+eps). */
+int b2n_rms_norm_fwd(const void* x, const void* gamma, void* y, void* rstd, int64_t M, int64_t N,
+                     double eps, int x_dtype, int w_dtype, void* stream);
+
+/* Bytes of scratch the two backward entry points need for the weight-gradient partial sums
+ * (0 when neither dgamma nor dbeta is requested). */
+size_t b2n_norm_bwd_workspace_bytes(int64_t M, int64_t N, int x_dtype, int w_dtype, int want_wgrad);
+
+/* dx (x_dtype, [M,N]), dgamma / dbeta (w_dtype, [N]); any of the three may be NULL (masked off).
+ * workspace: >= b2n_norm_bwd_workspace_bytes(...) bytes, 256-byte aligned, contents ignored.
+ * The weight gradients are summed in a fixed order: bit-reproducible from run to run.
+ *
+ * Replaces at::native::xpu::layer_norm_backward_kernel (sycl/LayerNormKernels.h:30-40) behind
+ * layer_norm_backward_xpu (LayerNorm.cpp:99). */
+int b2n_layer_norm_bwd(const void* dy, const void* x, const void* mean, const void* rstd,
+                       const void* gamma, void* dx, void* dgamma, void* dbeta, void* workspace,
+                       size_t workspace_bytes, int64_t M, int64_t N, int x_dtype, int w_dtype,
+                       void* stream);
+
+/* Replaces at::native::xpu::rms_norm_backward_kernel (sycl/LayerNormKernels.h:51-58) behind
+ * _fused_rms_norm_backward_xpu (LayerNorm.cpp:255). */
+int b2n_rms_norm_bwd(const void* dy, const void* x, const void* rstd, const void* gamma, void* dx,
+                     void* dgamma, void* workspace, size_t workspace_bytes, int64_t M, int64_t N,
+                     int x_dtype, int w_dtype, void* stream);
+
+/* ---- softmax / log-softmax --------------------------------------------------------------------
+ * The tensor is viewed as [outer, N, inner]; the reduction runs over N (inner == 1 for the last
+ * dim).  out_dtype == in_dtype, or B2N_F32 with a 16-bit input ("half_to_float").
+ *
+ * Replaces at::native::xpu::_softmax_kernel / _log_softmax_kernel
+ * (src/ATen/native/xpu/sycl/SoftMaxKernels.h:19-29) behind softmax_xpu_out / log_softmax_xpu_out
+ * (src/ATen/native/xpu/SoftMax.cpp:22, :94). */
+int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t inner, int in_dtype,
+                    int out_dtype, int is_log, void* stream);
+
+/* dy: grad_dtype; y (forward output): grad_dtype; dx: dx_dtype (== grad_dtype, or a 16-bit type
+ * with grad_dtype == B2N_F32 for the half_to_float backward).
+ * softmax: dx = y*(dy - sum(y*dy)); log-softmax: dx = dy - exp(y)*sum(dy).
+ *
+ * Replaces _softmax_backward_kernel / _log_softmax_backward_kernel (sycl/SoftMaxKernels.h:31-43)
+ * behind softmax_backward_xpu_out / log_softmax_backward_xpu_out (SoftMax.cpp:30, :61). */
+int b2n_softmax_bwd(const void* dy, const void* y, void* dx, int64_t outer, int64_t N,
+                    int64_t inner, int grad_dtype, int dx_dtype, int is_log, void* stream);
+
+/* ---- nll_loss ---------------------------------------------------------------------------------
+ * logp: [M, C] of dtype; target: [M] int64 (target_is_u8 == 0) or uint8; weight: [C] of dtype or
+ * NULL.  reduction none: out[M]; mean/sum: out[1].  total_weight[1] of dtype.
+ * sums_f32: optional device float[2] that receives {sum_i -w[t_i]*logp[i,t_i], sum_i w[t_i]} before
+ * the mean division (what a row-sharded caller all-reduces); may be NULL.
+ * workspace: >= b2n_nll_loss_workspace_bytes(M) bytes.
+ * A target outside [0, C) other than ignore_index contributes nothing and records
+ * B2N_ERR_TARGET_RANGE in the device status word (the reference asserts on the device instead).
+ *
+ * Replaces at::native::xpu::nll_loss_forward_kernel (src/ATen/native/xpu/sycl/LossNLLKernel.h)
+ * behind nll_loss_forward_out_xpu (src/ATen/native/xpu/LossNLL.cpp:22). */
+size_t b2n_nll_loss_workspace_bytes(int64_t M);
+int b2n_nll_loss_fwd(const void* logp, const void* target, const void* weight, void* out,
+                     void* total_weight, float* sums_f32, void* workspace, size_t workspace_bytes,
+                     int64_t M, int64_t C, int reduction, int64_t ignore_index, int dtype,
+                     int target_is_u8, void* stream);
+
+/* grad_input [M, C] is zero-filled, then grad_input[i, t_i] = -w[t_i] * g (/ total_weight for
+ * mean), g = grad_out[i] (none) or grad_out[0].
+ *
+ * Replaces at::native::xpu::nll_loss_backward_kernel (sycl/LossNLLKernel.h) behind
+ * nll_loss_backward_out_xpu (LossNLL.cpp:35), including its grad_input.zero_(). */
+int b2n_nll_loss_bwd(const void* grad_out, const void* target, const void* weight,
+                     const void* total_weight, void* grad_input, int64_t M, int64_t C,
+                     int reduction, int64_t ignore_index, int dtype, int target_is_u8,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200NORM_H_ */

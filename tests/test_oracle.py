@@ -1,0 +1,158 @@
+"""Pins the oracle: the C restatement of the reference's algorithms against PyTorch CPU ATen, both
+against the committed golden vectors, and the known-answer properties the reference's own tests
+assert for this path."""
+import math
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import aten_oracle as ao
+from oracle import restate
+
+GOLDEN = torch.load(Path(__file__).parent / "golden" / "golden_v1.pt")
+
+
+def close32(a, b, tol=1.0):
+    return ao.fp32_err(a, b) <= tol
+
+
+@pytest.mark.parametrize("name", ["ln_f32", "ln_bf16_w32", "ln_f16", "ln_f32_n5"])
+def test_golden_layer_norm_matches_aten_and_restatement(name):
+    c = GOLDEN[name]
+    n = c["x"].shape[-1]
+    y, mean, rstd = ao.layer_norm_fwd(c["x"], [n], c["gamma"], c["beta"], c["eps"])
+    assert torch.equal(y, c["y"]) and torch.equal(mean, c["mean"]) and torch.equal(rstd, c["rstd"])
+    # restatement (Welford, 1 lane and a 32-lane split as the reference's work-group does)
+    for lanes in (1, 32):
+        ry, rmean, rrstd = restate.norm_fwd(c["x"], c["gamma"], c["beta"], c["eps"], rms=False, lanes=lanes)
+        assert close32(rmean, c["mean"].reshape(-1)) and close32(rrstd, c["rstd"].reshape(-1))
+        if c["x"].dtype == torch.float32:
+            assert close32(ry, c["y"])
+        else:
+            assert ao.ulp_distance(ry.to(c["x"].dtype), c["y"]) <= 1
+    rdx, rdg, rdb = restate.norm_bwd(c["dy"], c["x"], c["mean"], c["rstd"], c["gamma"], rms=False)
+    if c["x"].dtype == torch.float32:
+        assert close32(rdx, c["dx"], tol=4.0)
+    else:
+        assert ao.ulp_distance(rdx.to(c["x"].dtype), c["dx"]) <= 1
+    assert torch.allclose(rdg.float(), c["dgamma"].float(), rtol=1e-4, atol=1e-4)
+    assert torch.allclose(rdb.float(), c["dbeta"].float(), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["rms_f32", "rms_bf16_w32"])
+def test_golden_rms_norm(name):
+    c = GOLDEN[name]
+    n = c["x"].shape[-1]
+    y, rstd = ao.rms_norm_fwd(c["x"], [n], c["weight"], c["eps"])
+    assert torch.equal(y, c["y"]) and torch.equal(rstd, c["rstd"])
+    ry, _, rrstd = restate.norm_fwd(c["x"], c["weight"], None, c["eps"], rms=True)
+    assert close32(rrstd, c["rstd"].reshape(-1))
+    # the backward has no CPU ATen kernel: autograd through the composite (golden) vs the restated
+    # closed form of the reference (rms branch of its backward functor)
+    rdx, rdw, _ = restate.norm_bwd(c["dy"], c["x"], None, c["rstd"], c["weight"], rms=True)
+    if c["x"].dtype == torch.float32:
+        assert close32(ry, c["y"]) and close32(rdx, c["dx"], tol=4.0)
+    else:
+        assert ao.ulp_distance(ry.to(c["x"].dtype), c["y"]) <= 1
+        assert ao.ulp_distance(rdx.to(c["x"].dtype), c["dx"]) <= 1
+    assert torch.allclose(rdw.float(), c["dweight"].float(), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["sm_f32_last", "sm_bf16_last", "sm_f32_dim0", "sm_f32_dim1"])
+def test_golden_softmax(name):
+    c = GOLDEN[name]
+    dt = c["x"].dtype
+    for is_log, tag in ((False, "softmax"), (True, "log_softmax")):
+        y = ao.softmax_fwd(c["x"], c["dim"], is_log)
+        assert torch.equal(y, c[tag])
+        ry = restate.softmax_fwd(c["x"], c["dim"], is_log)
+        rdx = restate.softmax_bwd(c["dy"], c[tag], c["dim"], is_log)
+        if dt == torch.float32:
+            assert close32(ry, c[tag], tol=2.0) and close32(rdx, c[tag + "_bwd"], tol=4.0)
+        else:
+            assert ao.ulp_distance(ry.to(dt), c[tag]) <= 1
+            assert ao.ulp_distance(rdx.to(dt), c[tag + "_bwd"]) <= 1
+
+
+def test_golden_nll():
+    c = GOLDEN["nll_f32"]
+    for red in (0, 1, 2):
+        for w, tag in ((None, "now"), (c["weight"], "w")):
+            out, tw = ao.nll_fwd(c["logp"], c["target"], w, red, c["ignore_index"])
+            assert torch.equal(out, c[f"out_{red}_{tag}"]) and torch.equal(tw, c[f"tw_{red}_{tag}"])
+            if red:
+                rout, rtw = restate.nll_fwd(c["logp"], c["target"], w, red == 1, c["ignore_index"])
+                assert math.isclose(float(rout), float(out), rel_tol=1e-5) and math.isclose(float(rtw), float(tw), rel_tol=1e-6)
+
+
+# ---- known-answer properties taken from the reference's tests --------------------------------------
+def test_layer_norm_large_offset_stays_finite():
+    # test/regressions/test_layer_norm.py:19-28 — a row of 1e15 + {0..4} must not produce NaN
+    x = torch.tensor([[1e15 + i for i in range(5)]], dtype=torch.float32)
+    y, mean, rstd = restate.norm_fwd(x, None, None, 1e-5, rms=False)
+    ry, _, _ = ao.layer_norm_fwd(x, [5], None, None, 1e-5)
+    assert torch.isfinite(y).all() and torch.isfinite(ry).all()
+
+
+def test_rms_dbeta_free_and_dgamma_formula():
+    # test/regressions/test_rms_norm.py:76-79 — dgamma == sum_i dy * x * rstd
+    x = ao.randn((33, 48), 5)
+    dy = ao.randn((33, 48), 6)
+    w = ao.randn((48,), 7, mean=1.0, std=0.02)
+    _, rstd = ao.rms_norm_fwd(x, [48], w, 1e-6)
+    _, dw = ao.rms_norm_bwd(dy, x, [48], w, 1e-6)
+    expect = (dy.double() * x.double() * rstd.double()).sum(0)
+    assert torch.allclose(dw.double(), expect, rtol=1e-5, atol=1e-5)
+    _, rdw, _ = restate.norm_bwd(dy, x, None, rstd, w, rms=True)
+    assert torch.allclose(rdw, expect, rtol=1e-6, atol=1e-6)
+
+
+def test_log_softmax_shift_invariance_and_unit_mass():
+    # test/xpu/test_nn_xpu.py:14177-14190, :14141-14147
+    x = ao.randn((5, 300), 8)
+    a = restate.softmax_fwd(x, -1, True)
+    b = restate.softmax_fwd(x + 100.0, -1, True)
+    assert torch.allclose(a, b, atol=1e-4)
+    assert torch.allclose(a.exp().sum(-1), torch.ones(5), atol=1e-5)
+
+
+def test_log_softmax_of_ones_gives_log_vocab():
+    # test/xpu/test_nn_xpu.py:17902-17911 — nll of a constant row over V classes is log V
+    V = 5000
+    logp = restate.softmax_fwd(torch.ones(3, V), -1, True)
+    out, tw = restate.nll_fwd(logp, torch.tensor([0, 7, V - 1]), None, True, -100)
+    assert math.isclose(float(out), math.log(V), rel_tol=1e-5) and float(tw) == 3.0
+
+
+def test_nll_all_ignored_is_nan_for_mean_and_zero_for_sum():
+    # test/xpu/test_nn_xpu.py:16003-16045
+    logp = torch.log_softmax(ao.randn((4, 6), 9), -1)
+    t = torch.full((4,), -100)
+    out, tw = ao.nll_fwd(logp, t, None, 1, -100)
+    assert math.isnan(float(out)) and float(tw) == 0.0
+    out, _ = ao.nll_fwd(logp, t, None, 2, -100)
+    assert float(out) == 0.0
+    rout, rtw = restate.nll_fwd(logp, t, None, True, -100)
+    assert math.isnan(float(rout)) and float(rtw) == 0.0
+
+
+def test_all_masked_row_is_nan_on_cpu_aten():
+    # the semantics the kernels must reproduce: an all -inf row gives NaN, single -inf entries 0 / -inf
+    x = torch.tensor([[float("-inf")] * 4, [0.0, float("-inf"), 1.0, 2.0]])
+    y = ao.softmax_fwd(x, -1, False)
+    assert torch.isnan(y[0]).all() and y[1, 1] == 0
+    ly = ao.softmax_fwd(x, -1, True)
+    assert torch.isnan(ly[0]).all() and ly[1, 1] == float("-inf")
+
+
+def test_comparators():
+    a = torch.tensor([1.0, 2.0, -3.0], dtype=torch.bfloat16)
+    b = a.clone()
+    assert ao.ulp_distance(a, b) == 0
+    b[0] = torch.nextafter(torch.tensor(1.0), torch.tensor(2.0)).to(torch.bfloat16)  # rounds back to 1.0
+    assert ao.ulp_distance(a, b) == 0
+    c = (a.view(torch.int16) + 1).view(torch.bfloat16)
+    assert ao.ulp_distance(a, c) == 1
+    assert ao.fp32_err(torch.tensor([1.0, 0.0]), torch.tensor([1.0 + 5e-6, 1e-7])) <= 1.0
+    assert ao.fp32_err(torch.tensor([1.0]), torch.tensor([1.001])) > 1.0

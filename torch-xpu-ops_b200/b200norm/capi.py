@@ -1,0 +1,356 @@
+"""ctypes wrappers over the C ABI, with the reference's operator names and argument meaning.
+
+Each function mirrors the ATen operator that intel/torch-xpu-ops implements for this path
+(src/ATen/native/xpu/LayerNorm.cpp, SoftMax.cpp, LossNLL.cpp): same arguments, same outputs, same
+error behaviour for bad shapes.  torch is used for device memory and streams only — every result
+is produced by a kernel of libb200norm.so, called with raw pointers and sizes.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import (BF16, F16, F32, F64, OK, REDUCE_MEAN, REDUCE_NONE, REDUCE_SUM, B200NormError,
+               load_library)
+
+_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float64: F64}
+
+
+def _dt(t: torch.dtype) -> int:
+    try:
+        return _DTYPES[t]
+    except KeyError:
+        raise TypeError(f"b200norm: unsupported dtype {t}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check(status: int, what: str) -> None:
+    if status != OK:
+        raise B200NormError(status, what)
+
+
+def _require_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("b200norm: expected CUDA tensors (there is no CPU path)")
+
+
+def _norm_dims(x: torch.Tensor, normalized_shape: Sequence[int], weight, bias) -> Tuple[int, int]:
+    """M, N with the checks of at::native::_check_layer_norm_inputs."""
+    ns = tuple(int(s) for s in normalized_shape)
+    if len(ns) < 1:
+        raise RuntimeError("Expected normalized_shape to be at least 1-dimensional")
+    for name, w in (("weight", weight), ("bias", bias)):
+        if w is not None and tuple(w.shape) != ns:
+            raise RuntimeError(f"Expected {name} to be of same shape as normalized_shape, but got {name} of shape "
+                               f"{tuple(w.shape)} and normalized_shape = {ns}")
+    if x.dim() < len(ns) or tuple(x.shape[x.dim() - len(ns):]) != ns:
+        raise RuntimeError(f"Given normalized_shape={list(ns)}, expected input with shape [*, "
+                           f"{', '.join(map(str, ns))}], but got input of size {list(x.shape)}")
+    n = math.prod(ns)
+    m = math.prod(x.shape[: x.dim() - len(ns)])
+    return m, n
+
+
+def _stat_shape(x: torch.Tensor, normalized_ndim: int):
+    axis = x.dim() - normalized_ndim
+    return list(x.shape[:axis]) + [1] * normalized_ndim
+
+
+def _acc_dtype(t: torch.dtype) -> torch.dtype:
+    return torch.float64 if t == torch.float64 else torch.float32
+
+
+def _weight_dtype(x, weight, bias) -> int:
+    w = weight if weight is not None else bias
+    if w is None:
+        return _dt(x.dtype)
+    if weight is not None and bias is not None and weight.dtype != bias.dtype:
+        raise RuntimeError("weight and bias must have the same dtype")
+    if w.dtype != x.dtype and w.dtype != torch.float32:
+        raise RuntimeError(f"weight dtype must equal the input dtype or be float32, got {w.dtype} for {x.dtype}")
+    return _dt(w.dtype)
+
+
+def set_path(path: int) -> int:
+    """Force a kernel family (b200norm.PATH_*) for this thread; returns the previous setting."""
+    return load_library().b2n_set_path(path)
+
+
+def last_path() -> str:
+    return load_library().b2n_last_path().decode()
+
+
+def device_status(device=None) -> int:
+    """Read-and-clear the device status word (synchronises the current stream)."""
+    with torch.cuda.device(device):
+        return load_library().b2n_device_status(torch.cuda.current_stream().cuda_stream)
+
+
+# ---- layer norm / RMS norm -------------------------------------------------------------------------
+def native_layer_norm(input, normalized_shape, weight=None, bias=None, eps=1e-5, out=None):
+    """aten::native_layer_norm -> (Y, mean, rstd); mean/rstd in the accumulate dtype.
+
+    out: optional preallocated (Y, mean[M], rstd[M]) to write into (no allocation on the call path).
+    """
+    _require_cuda(input, weight, bias)
+    lib = load_library()
+    M, N = _norm_dims(input, normalized_shape, weight, bias)
+    x = input.contiguous()
+    g = weight.contiguous() if weight is not None else None
+    b = bias.contiguous() if bias is not None else None
+    acc = _acc_dtype(x.dtype)
+    if out is not None:
+        y, mean, rstd = out
+        mean, rstd = mean.view(-1), rstd.view(-1)
+    else:
+        y = torch.empty_like(x, memory_format=torch.contiguous_format)
+        mean = torch.empty(M, dtype=acc, device=x.device)
+        rstd = torch.empty(M, dtype=acc, device=x.device)
+    if M > 0:
+        with torch.cuda.device(x.device):
+            _check(lib.b2n_layer_norm_fwd(_ptr(x), _ptr(g), _ptr(b), _ptr(y), _ptr(mean), _ptr(rstd), M, N,
+                                          float(eps), _dt(x.dtype), _weight_dtype(x, g, b), _stream(x)),
+                   "b2n_layer_norm_fwd")
+    shape = _stat_shape(input, len(normalized_shape))
+    return y, mean.view(shape), rstd.view(shape)
+
+
+def native_layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight=None, bias=None,
+                               output_mask=(True, True, True), out=None, workspace=None):
+    """aten::native_layer_norm_backward -> (dX?, dgamma?, dbeta?); masked-off outputs are None.
+
+    out: optional preallocated (dX, dgamma, dbeta) (entries may be None to allocate);
+    workspace: optional preallocated uint8 scratch of b2n_norm_bwd_workspace_bytes(...) bytes.
+    """
+    _require_cuda(grad_out, input, mean, rstd, weight, bias)
+    lib = load_library()
+    M, N = _norm_dims(input, normalized_shape, weight, bias)
+    x = input.contiguous()
+    dy = grad_out.contiguous()
+    if dy.dtype != x.dtype:
+        raise RuntimeError(f"grad_out dtype {dy.dtype} does not match input dtype {x.dtype}")
+    g = weight.contiguous() if weight is not None else None
+    acc = _acc_dtype(x.dtype)
+    mean_c = mean.to(acc).contiguous().view(-1)
+    rstd_c = rstd.to(acc).contiguous().view(-1)
+    o_dx, o_dg, o_db = out if out is not None else (None, None, None)
+    mk = (torch.empty_like if M > 0 else torch.zeros_like)
+    dx = (o_dx if o_dx is not None else torch.empty_like(x)) if output_mask[0] else None
+    dgamma = ((o_dg if o_dg is not None else mk(weight.contiguous()))
+              if (output_mask[1] and weight is not None) else None)
+    dbeta = ((o_db if o_db is not None else mk(bias.contiguous()))
+             if (output_mask[2] and bias is not None) else None)
+    if M > 0 and N > 0:
+        xdt, wdt = _dt(x.dtype), _weight_dtype(x, weight, bias)
+        want_w = dgamma is not None or dbeta is not None
+        with torch.cuda.device(x.device):
+            nbytes = lib.b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, int(want_w))
+            ws = workspace if workspace is not None else torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+            if ws.numel() < nbytes:
+                raise ValueError(f"workspace too small: {ws.numel()} < {nbytes}")
+            _check(lib.b2n_layer_norm_bwd(_ptr(dy), _ptr(x), _ptr(mean_c), _ptr(rstd_c), _ptr(g), _ptr(dx),
+                                          _ptr(dgamma), _ptr(dbeta), _ptr(ws) if nbytes else None, nbytes, M, N,
+                                          xdt, wdt, _stream(x)),
+                   "b2n_layer_norm_bwd")
+    return dx, dgamma, dbeta
+
+
+def _fused_rms_norm(input, normalized_shape, weight=None, eps=None, out=None):
+    """aten::_fused_rms_norm -> (Y, rstd).  eps=None means the accumulate type's machine epsilon.
+
+    out: optional preallocated (Y, rstd[M]).
+    """
+    _require_cuda(input, weight)
+    lib = load_library()
+    M, N = _norm_dims(input, normalized_shape, weight, weight)
+    x = input.contiguous()
+    g = weight.contiguous() if weight is not None else None
+    acc = _acc_dtype(x.dtype)
+    if eps is None:
+        eps = torch.finfo(acc).eps
+    if out is not None:
+        y, rstd = out
+        rstd = rstd.view(-1)
+    else:
+        y = torch.empty_like(x, memory_format=torch.contiguous_format)
+        rstd = torch.empty(M, dtype=acc, device=x.device)
+    if M > 0:
+        with torch.cuda.device(x.device):
+            _check(lib.b2n_rms_norm_fwd(_ptr(x), _ptr(g), _ptr(y), _ptr(rstd), M, N, float(eps), _dt(x.dtype),
+                                        _weight_dtype(x, g, None), _stream(x)),
+                   "b2n_rms_norm_fwd")
+    return y, rstd.view(_stat_shape(input, len(normalized_shape)))
+
+
+def _fused_rms_norm_backward(grad_out, input, normalized_shape, rstd, weight=None, output_mask=(True, True),
+                             out=None, workspace=None):
+    """aten::_fused_rms_norm_backward -> (dX?, dW?).  out / workspace: optional preallocated buffers."""
+    _require_cuda(grad_out, input, rstd, weight)
+    lib = load_library()
+    M, N = _norm_dims(input, normalized_shape, weight, weight)
+    x = input.contiguous()
+    dy = grad_out.contiguous()
+    if dy.dtype != x.dtype:
+        raise RuntimeError(f"grad_out dtype {dy.dtype} does not match input dtype {x.dtype}")
+    g = weight.contiguous() if weight is not None else None
+    rstd_c = rstd.to(_acc_dtype(x.dtype)).contiguous().view(-1)
+    o_dx, o_dg = out if out is not None else (None, None)
+    mk = (torch.empty_like if M > 0 else torch.zeros_like)
+    dx = (o_dx if o_dx is not None else torch.empty_like(x)) if output_mask[0] else None
+    dgamma = (o_dg if o_dg is not None else mk(g)) if (output_mask[1] and g is not None) else None
+    if M > 0 and N > 0:
+        xdt, wdt = _dt(x.dtype), _weight_dtype(x, weight, None)
+        with torch.cuda.device(x.device):
+            nbytes = lib.b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, int(dgamma is not None))
+            ws = workspace if workspace is not None else torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+            if ws.numel() < nbytes:
+                raise ValueError(f"workspace too small: {ws.numel()} < {nbytes}")
+            _check(lib.b2n_rms_norm_bwd(_ptr(dy), _ptr(x), _ptr(rstd_c), _ptr(g), _ptr(dx), _ptr(dgamma),
+                                        _ptr(ws) if nbytes else None, nbytes, M, N, xdt, wdt, _stream(x)),
+                   "b2n_rms_norm_bwd")
+    return dx, dgamma
+
+
+# ---- softmax family ----------------------------------------------------------------------------------
+def _softmax_dims(t: torch.Tensor, dim: int):
+    if t.dim() == 0:
+        if dim not in (0, -1):
+            raise IndexError(f"Dimension out of range (expected to be in range of [-1, 0], but got {dim})")
+        return 1, 1, 1
+    if not -t.dim() <= dim < t.dim():
+        raise IndexError(f"Dimension out of range (expected to be in range of [{-t.dim()}, {t.dim() - 1}], "
+                         f"but got {dim})")
+    dim %= t.dim()
+    return math.prod(t.shape[:dim]), t.shape[dim], math.prod(t.shape[dim + 1:])
+
+
+def _softmax_fwd(input, dim, half_to_float, is_log, name, out=None):
+    _require_cuda(input)
+    lib = load_library()
+    if half_to_float and input.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("conversion is supported for Half and BFloat16 type only")
+    outer, n, inner = _softmax_dims(input, dim)
+    x = input.contiguous()
+    y = out if out is not None else torch.empty_like(x, dtype=torch.float32 if half_to_float else x.dtype)
+    if x.numel() > 0:
+        with torch.cuda.device(x.device):
+            _check(lib.b2n_softmax_fwd(_ptr(x), _ptr(y), outer, n, inner, _dt(x.dtype), _dt(y.dtype), int(is_log),
+                                       _stream(x)), name)
+    return y
+
+
+def _softmax(input, dim, half_to_float=False, out=None):
+    """aten::_softmax (out: optional preallocated contiguous result)"""
+    return _softmax_fwd(input, dim, half_to_float, False, "b2n_softmax_fwd", out)
+
+
+def _log_softmax(input, dim, half_to_float=False, out=None):
+    """aten::_log_softmax (out: optional preallocated contiguous result)"""
+    return _softmax_fwd(input, dim, half_to_float, True, "b2n_softmax_fwd(log)", out)
+
+
+def _softmax_bwd(grad_output, output, dim, input_dtype, is_log, name, out=None):
+    _require_cuda(grad_output, output)
+    lib = load_library()
+    if grad_output.dtype != input_dtype and not (
+            grad_output.dtype == torch.float32 and input_dtype in (torch.float16, torch.bfloat16)):
+        raise RuntimeError("expected input and grad types to match, or input to be at::Half and grad to be at::Float")
+    if grad_output.shape != output.shape:
+        raise RuntimeError("grad_output and output sizes differ")
+    outer, n, inner = _softmax_dims(grad_output, dim)
+    g = grad_output.contiguous()
+    y = output.to(g.dtype).contiguous()
+    dx = out if out is not None else torch.empty_like(g, dtype=input_dtype)
+    if g.numel() > 0:
+        with torch.cuda.device(g.device):
+            _check(lib.b2n_softmax_bwd(_ptr(g), _ptr(y), _ptr(dx), outer, n, inner, _dt(g.dtype), _dt(dx.dtype),
+                                       int(is_log), _stream(g)), name)
+    return dx
+
+
+def _softmax_backward_data(grad_output, output, dim, input_dtype, out=None):
+    """aten::_softmax_backward_data"""
+    return _softmax_bwd(grad_output, output, dim, input_dtype, False, "b2n_softmax_bwd", out)
+
+
+def _log_softmax_backward_data(grad_output, output, dim, input_dtype, out=None):
+    """aten::_log_softmax_backward_data"""
+    return _softmax_bwd(grad_output, output, dim, input_dtype, True, "b2n_softmax_bwd(log)", out)
+
+
+# ---- nll_loss --------------------------------------------------------------------------------------------
+def _nll_check(self, target, weight):
+    if not 0 < self.dim() <= 2:
+        raise RuntimeError("input tensor should be 1D or 2D")
+    if target.dim() > 1:
+        raise RuntimeError("0D or 1D target tensor expected, multi-target not supported")
+    if not (self.dim() == 1 and target.dim() == 0) and self.shape[0] != target.shape[0]:
+        raise RuntimeError(f"size mismatch (got input: {list(self.shape)}, target: {list(target.shape)})")
+    if weight is not None and (weight.dim() != 1 or weight.numel() != self.shape[-1]):
+        raise RuntimeError("weight tensor should be defined either for all classes or no classes")
+    if target.dtype not in (torch.int64, torch.uint8):
+        raise RuntimeError(f"expected target dtype Long or Byte but got {target.dtype}")
+
+
+def nll_loss_forward(self, target, weight=None, reduction=REDUCE_MEAN, ignore_index=-100, return_sums=False):
+    """aten::nll_loss_forward -> (output, total_weight).
+
+    return_sums=True additionally returns a float32[2] device tensor {sum -w*x, sum w} taken before
+    the mean division: what a row-sharded caller all-reduces.
+    """
+    _require_cuda(self, target, weight)
+    lib = load_library()
+    _nll_check(self, target, weight)
+    C = self.shape[-1]
+    M = 1 if self.dim() == 1 else self.shape[0]
+    x = self.contiguous()
+    t = target.contiguous()
+    w = weight.to(x.dtype).contiguous() if weight is not None else None
+    if reduction == REDUCE_NONE and self.dim() == 2:
+        out = torch.empty(M, dtype=x.dtype, device=x.device)
+    else:
+        out = torch.empty((), dtype=x.dtype, device=x.device)
+    total_weight = torch.zeros((), dtype=x.dtype, device=x.device)
+    sums = torch.zeros(2, dtype=torch.float32, device=x.device) if return_sums else None
+    with torch.cuda.device(x.device):
+        nbytes = lib.b2n_nll_loss_workspace_bytes(M)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        _check(lib.b2n_nll_loss_fwd(_ptr(x), _ptr(t), _ptr(w), _ptr(out), _ptr(total_weight), _ptr(sums), _ptr(ws),
+                                    nbytes, M, C, int(reduction), int(ignore_index), _dt(x.dtype),
+                                    int(t.dtype == torch.uint8), _stream(x)), "b2n_nll_loss_fwd")
+    if return_sums:
+        return out, total_weight, sums
+    return out, total_weight
+
+
+def nll_loss_backward(grad_output, self, target, weight=None, reduction=REDUCE_MEAN, ignore_index=-100,
+                      total_weight=None, out=None):
+    """aten::nll_loss_backward -> grad_input (zero-filled, one value scattered per row)."""
+    _require_cuda(grad_output, self, target, weight, total_weight)
+    lib = load_library()
+    _nll_check(self, target, weight)
+    C = self.shape[-1]
+    M = 1 if self.dim() == 1 else self.shape[0]
+    g = grad_output.to(self.dtype).contiguous()
+    t = target.contiguous()
+    w = weight.to(self.dtype).contiguous() if weight is not None else None
+    tw = total_weight.to(self.dtype).contiguous() if total_weight is not None else None
+    red = int(reduction)
+    if self.dim() == 1 and red == REDUCE_NONE:
+        red = REDUCE_SUM  # a single row: the scalar grad_output applies as is
+    grad_input = out if out is not None else torch.empty_like(self, memory_format=torch.contiguous_format)
+    with torch.cuda.device(self.device):
+        _check(lib.b2n_nll_loss_bwd(_ptr(g), _ptr(t), _ptr(w), _ptr(tw), _ptr(grad_input), M, C, red,
+                                    int(ignore_index), _dt(self.dtype), int(t.dtype == torch.uint8), _stream(self)),
+               "b2n_nll_loss_bwd")
+    return grad_input

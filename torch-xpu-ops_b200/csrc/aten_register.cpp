@@ -1,0 +1,478 @@
+// ATen dispatcher registration: the CUDA-key kernels of the row-wise normalization / softmax
+// operator family, re-implemented on top of the b200norm C ABI.  This file plays the role of
+// intel/torch-xpu-ops' host wrappers (src/ATen/native/xpu/LayerNorm.cpp, SoftMax.cpp, LossNLL.cpp):
+// argument checks, contiguity, output allocation, stat reshaping — no device code.  Loading the
+// shared object replaces PyTorch's own CUDA kernels for exactly these operators; the ATen schemas
+// are untouched, so autograd formulas and every caller keep working.
+//
+// There is no fallback: a non-zero status from the C ABI becomes a c10::Error.
+#include <ATen/ATen.h>
+#include <ATen/AccumulateType.h>
+#include <ATen/ExpandUtils.h>
+#include <ATen/WrapDimUtils.h>
+#include <ATen/native/Resize.h>
+#include <ATen/native/layer_norm.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include <array>
+#include <tuple>
+#include <vector>
+
+#include "b200norm.h"
+
+namespace b200norm {
+
+using at::Tensor;
+
+static int to_b2n_dtype(at::ScalarType t, const char* what) {
+  switch (t) {
+    case at::kFloat: return B2N_F32;
+    case at::kHalf: return B2N_F16;
+    case at::kBFloat16: return B2N_BF16;
+    case at::kDouble: return B2N_F64;
+    default: TORCH_CHECK(false, "b200norm: ", what, ": unsupported dtype ", t);
+  }
+}
+
+static void check_status(int st, const char* op) {
+  TORCH_CHECK(st == B2N_OK, "b200norm::", op, " failed: ", b2n_strerror(st),
+              st == B2N_ERR_CUDA ? " (cudaError " : "", st == B2N_ERR_CUDA ? std::to_string(b2n_last_cuda_error()) : "",
+              st == B2N_ERR_CUDA ? ")" : "");
+}
+
+static void* cur_stream() { return static_cast<void*>(c10::cuda::getCurrentCUDAStream().stream()); }
+
+static at::ScalarType acc_type_of(at::ScalarType t) { return t == at::kDouble ? at::kDouble : at::kFloat; }
+
+static std::vector<int64_t> stat_shape_of(const Tensor& input, size_t normalized_ndim) {
+  // input.shape[:axis] + [1] * normalized_ndim  (LayerNorm.cpp:82-94 of the reference)
+  const size_t axis = input.dim() - normalized_ndim;
+  std::vector<int64_t> shape;
+  for (size_t i = 0; i < axis; ++i) shape.push_back(input.size(i));
+  for (size_t i = axis; i < static_cast<size_t>(input.dim()); ++i) shape.push_back(1);
+  return shape;
+}
+
+static int weight_dtype(const Tensor& input, const Tensor& weight, const Tensor& bias, const char* op) {
+  if (weight.defined() && bias.defined()) {
+    TORCH_CHECK(weight.scalar_type() == bias.scalar_type(), op, ": weight and bias must have the same dtype");
+  }
+  const Tensor& w = weight.defined() ? weight : bias;
+  if (!w.defined()) return to_b2n_dtype(input.scalar_type(), op);
+  TORCH_CHECK(w.scalar_type() == input.scalar_type() || w.scalar_type() == at::kFloat, op,
+              ": weight dtype must equal the input dtype or be float32, got ", w.scalar_type(), " for input ",
+              input.scalar_type());
+  return to_b2n_dtype(w.scalar_type(), op);
+}
+
+// ---- native_layer_norm ---------------------------------------------------------------------------
+std::tuple<Tensor, Tensor, Tensor> native_layer_norm(const Tensor& input, at::IntArrayRef normalized_shape,
+                                                     const std::optional<Tensor>& weight_opt,
+                                                     const std::optional<Tensor>& bias_opt, double eps) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  c10::MaybeOwned<Tensor> bias_mo = at::borrow_from_optional_tensor(bias_opt);
+  const Tensor& weight = *weight_mo;
+  const Tensor& bias = *bias_mo;
+  TORCH_CHECK(input.is_cuda(), "native_layer_norm: expected a CUDA tensor");
+  TORCH_CHECK(!weight.defined() || weight.device() == input.device(), "native_layer_norm: weight on another device");
+  TORCH_CHECK(!bias.defined() || bias.device() == input.device(), "native_layer_norm: bias on another device");
+  const c10::cuda::CUDAGuard guard(input.device());
+
+  auto M_N = at::native::_check_layer_norm_inputs(input, normalized_shape, weight, bias);
+  const int64_t M = M_N.first, N = M_N.second;
+  auto X = input.expect_contiguous();
+  auto gamma = weight.expect_contiguous();
+  auto beta = bias.expect_contiguous();
+
+  Tensor Y = at::empty_like(*X, at::MemoryFormat::Contiguous);
+  const auto acc = acc_type_of(input.scalar_type());
+  Tensor mean = at::empty({M}, X->options().dtype(acc));
+  Tensor rstd = at::empty({M}, X->options().dtype(acc));
+  if (M > 0) {
+    const int xdt = to_b2n_dtype(input.scalar_type(), "native_layer_norm");
+    const int wdt = weight_dtype(input, weight, bias, "native_layer_norm");
+    check_status(b2n_layer_norm_fwd(X->const_data_ptr(), gamma->defined() ? gamma->const_data_ptr() : nullptr,
+                                    beta->defined() ? beta->const_data_ptr() : nullptr, Y.mutable_data_ptr(),
+                                    mean.mutable_data_ptr(), rstd.mutable_data_ptr(), M, N, eps, xdt, wdt,
+                                    cur_stream()),
+                 "layer_norm_fwd");
+  }
+  const auto stat_shape = stat_shape_of(input, normalized_shape.size());
+  return std::make_tuple(std::move(Y), mean.view(stat_shape), rstd.view(stat_shape));
+}
+
+std::tuple<Tensor, Tensor, Tensor> native_layer_norm_backward(
+    const Tensor& grad_out, const Tensor& input, at::IntArrayRef normalized_shape, const Tensor& mean,
+    const Tensor& rstd, const std::optional<Tensor>& weight_opt, const std::optional<Tensor>& bias_opt,
+    std::array<bool, 3> mask) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  c10::MaybeOwned<Tensor> bias_mo = at::borrow_from_optional_tensor(bias_opt);
+  const Tensor& weight = *weight_mo;
+  const Tensor& bias = *bias_mo;
+  TORCH_CHECK(input.is_cuda() && grad_out.is_cuda(), "native_layer_norm_backward: expected CUDA tensors");
+  const c10::cuda::CUDAGuard guard(input.device());
+
+  auto M_N = at::native::_check_layer_norm_inputs(input, normalized_shape, weight, bias);
+  const int64_t M = M_N.first, N = M_N.second;
+  auto X = input.expect_contiguous();
+  auto gamma = weight.expect_contiguous();
+  auto beta = bias.expect_contiguous();
+  Tensor dY = grad_out.contiguous();
+  TORCH_CHECK(dY.scalar_type() == X->scalar_type(), "native_layer_norm_backward: grad_out dtype ", dY.scalar_type(),
+              " does not match input dtype ", X->scalar_type());
+  const auto acc = acc_type_of(input.scalar_type());
+  Tensor mean_c = mean.to(acc).contiguous();
+  Tensor rstd_c = rstd.to(acc).contiguous();
+
+  Tensor dX, dgamma, dbeta;
+  if (mask[0]) dX = at::empty_like(*X, at::MemoryFormat::Contiguous);
+  // a gradient for an absent weight/bias is returned as an undefined tensor when it is not asked
+  // for, and with the weight's shape (zeros when M == 0) when it is — LayerNorm.cpp:150-181
+  if (mask[1] && gamma->defined()) dgamma = M > 0 ? at::empty_like(*gamma, at::MemoryFormat::Contiguous)
+                              : at::zeros_like(*gamma, at::MemoryFormat::Contiguous);
+  if (mask[2] && beta->defined()) dbeta = M > 0 ? at::empty_like(*beta, at::MemoryFormat::Contiguous)
+                             : at::zeros_like(*beta, at::MemoryFormat::Contiguous);
+  if (M > 0 && N > 0) {
+    const int xdt = to_b2n_dtype(input.scalar_type(), "native_layer_norm_backward");
+    const int wdt = weight_dtype(input, weight, bias, "native_layer_norm_backward");
+    const bool want_w = dgamma.defined() || dbeta.defined();
+    const size_t ws_bytes = b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, want_w);
+    Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, X->options().dtype(at::kByte));
+    check_status(b2n_layer_norm_bwd(dY.const_data_ptr(), X->const_data_ptr(), mean_c.const_data_ptr(),
+                                    rstd_c.const_data_ptr(), gamma->defined() ? gamma->const_data_ptr() : nullptr,
+                                    dX.defined() ? dX.mutable_data_ptr() : nullptr,
+                                    dgamma.defined() ? dgamma.mutable_data_ptr() : nullptr,
+                                    dbeta.defined() ? dbeta.mutable_data_ptr() : nullptr,
+                                    ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, M, N, xdt, wdt, cur_stream()),
+                 "layer_norm_bwd");
+  }
+  return std::make_tuple(std::move(dX), std::move(dgamma), std::move(dbeta));
+}
+
+// ---- _fused_rms_norm -----------------------------------------------------------------------------
+std::tuple<Tensor, Tensor> fused_rms_norm(const Tensor& input, at::IntArrayRef normalized_shape,
+                                          const std::optional<Tensor>& weight_opt, std::optional<double> eps_opt) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  const Tensor& weight = *weight_mo;
+  TORCH_CHECK(input.is_cuda(), "_fused_rms_norm: expected a CUDA tensor");
+  const c10::cuda::CUDAGuard guard(input.device());
+  auto M_N = at::native::_check_layer_norm_inputs(input, normalized_shape, weight, weight);
+  const int64_t M = M_N.first, N = M_N.second;
+  auto X = input.expect_contiguous();
+  auto gamma = weight.expect_contiguous();
+  const auto acc = acc_type_of(input.scalar_type());
+  // default eps = machine epsilon of the accumulate type (LayerNorm.cpp:218-224)
+  const double eps = eps_opt.value_or(acc == at::kFloat ? static_cast<double>(std::numeric_limits<float>::epsilon())
+                                                        : std::numeric_limits<double>::epsilon());
+  Tensor Y = at::empty_like(*X, at::MemoryFormat::Contiguous);
+  Tensor rstd = at::empty({M}, X->options().dtype(acc));
+  if (M > 0) {
+    const int xdt = to_b2n_dtype(input.scalar_type(), "_fused_rms_norm");
+    const int wdt = weight_dtype(input, weight, Tensor(), "_fused_rms_norm");
+    check_status(b2n_rms_norm_fwd(X->const_data_ptr(), gamma->defined() ? gamma->const_data_ptr() : nullptr,
+                                  Y.mutable_data_ptr(), rstd.mutable_data_ptr(), M, N, eps, xdt, wdt, cur_stream()),
+                 "rms_norm_fwd");
+  }
+  return std::make_tuple(std::move(Y), rstd.view(stat_shape_of(input, normalized_shape.size())));
+}
+
+std::tuple<Tensor, Tensor> fused_rms_norm_backward(const Tensor& grad_out, const Tensor& input,
+                                                   at::IntArrayRef normalized_shape, const Tensor& rstd,
+                                                   const std::optional<Tensor>& weight_opt, std::array<bool, 2> mask) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  const Tensor& weight = *weight_mo;
+  TORCH_CHECK(input.is_cuda() && grad_out.is_cuda(), "_fused_rms_norm_backward: expected CUDA tensors");
+  const c10::cuda::CUDAGuard guard(input.device());
+  auto M_N = at::native::_check_layer_norm_inputs(input, normalized_shape, weight, weight);
+  const int64_t M = M_N.first, N = M_N.second;
+  auto X = input.expect_contiguous();
+  auto gamma = weight.expect_contiguous();
+  Tensor dY = grad_out.contiguous();
+  TORCH_CHECK(dY.scalar_type() == X->scalar_type(), "_fused_rms_norm_backward: grad_out dtype ", dY.scalar_type(),
+              " does not match input dtype ", X->scalar_type());
+  Tensor rstd_c = rstd.to(acc_type_of(input.scalar_type())).contiguous();
+  Tensor dX, dgamma;
+  if (mask[0]) dX = at::empty_like(*X, at::MemoryFormat::Contiguous);
+  if (mask[1] && gamma->defined()) dgamma = M > 0 ? at::empty_like(*gamma, at::MemoryFormat::Contiguous)
+                              : at::zeros_like(*gamma, at::MemoryFormat::Contiguous);
+  if (M > 0 && N > 0) {
+    const int xdt = to_b2n_dtype(input.scalar_type(), "_fused_rms_norm_backward");
+    const int wdt = weight_dtype(input, weight, Tensor(), "_fused_rms_norm_backward");
+    const size_t ws_bytes = b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, dgamma.defined());
+    Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, X->options().dtype(at::kByte));
+    check_status(b2n_rms_norm_bwd(dY.const_data_ptr(), X->const_data_ptr(), rstd_c.const_data_ptr(),
+                                  gamma->defined() ? gamma->const_data_ptr() : nullptr,
+                                  dX.defined() ? dX.mutable_data_ptr() : nullptr,
+                                  dgamma.defined() ? dgamma.mutable_data_ptr() : nullptr,
+                                  ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, M, N, xdt, wdt, cur_stream()),
+                 "rms_norm_bwd");
+  }
+  return std::make_tuple(std::move(dX), std::move(dgamma));
+}
+
+// ---- softmax family ------------------------------------------------------------------------------
+struct SoftmaxDims { int64_t outer, n, inner; };
+static SoftmaxDims softmax_dims(const Tensor& t, int64_t dim) {
+  // a 0-dim tensor is treated as one element (SoftMaxKernels.cpp:2143-2148 of the reference)
+  if (t.dim() == 0) return {1, 1, 1};
+  SoftmaxDims d{1, t.size(dim), 1};
+  for (int64_t i = 0; i < dim; ++i) d.outer *= t.size(i);
+  for (int64_t i = dim + 1; i < t.dim(); ++i) d.inner *= t.size(i);
+  return d;
+}
+
+static void softmax_forward_into(const Tensor& input, int64_t dim_, bool half_to_float, bool is_log, const Tensor& out,
+                                 const char* op) {
+  const c10::cuda::CUDAGuard guard(input.device());
+  if (half_to_float) {
+    TORCH_CHECK(input.scalar_type() == at::kHalf || input.scalar_type() == at::kBFloat16, op,
+                ": conversion is supported for Half and BFloat16 type only");
+  }
+  const int64_t dim = at::maybe_wrap_dim(dim_, input.dim());
+  TORCH_CHECK(dim >= 0 && dim < std::max<int64_t>(input.dim(), 1), op, ": dim must be non-negative and less than input dimensions");
+  TORCH_CHECK(out.is_contiguous(), op, ": output must be contiguous");
+  if (input.numel() == 0) return;
+  Tensor x = input.contiguous();
+  const SoftmaxDims d = softmax_dims(x, dim);
+  check_status(b2n_softmax_fwd(x.const_data_ptr(), out.mutable_data_ptr(), d.outer, d.n, d.inner,
+                               to_b2n_dtype(x.scalar_type(), op), to_b2n_dtype(out.scalar_type(), op), is_log ? 1 : 0,
+                               cur_stream()),
+               op);
+}
+
+static Tensor softmax_forward(const Tensor& input, int64_t dim, bool half_to_float, bool is_log, const char* op) {
+  TORCH_CHECK(input.is_cuda(), op, ": expected a CUDA tensor");
+  const c10::cuda::CUDAGuard guard(input.device());
+  Tensor out = at::empty_like(input, input.options().dtype(half_to_float ? at::kFloat : input.scalar_type()),
+                              at::MemoryFormat::Contiguous);
+  softmax_forward_into(input, dim, half_to_float, is_log, out, op);
+  return out;
+}
+
+static Tensor& softmax_forward_out(const Tensor& input, int64_t dim, bool half_to_float, bool is_log, Tensor& out,
+                                   const char* op) {
+  TORCH_CHECK(input.is_cuda() && out.is_cuda(), op, ": expected CUDA tensors");
+  const auto want = half_to_float ? at::kFloat : input.scalar_type();
+  TORCH_CHECK(out.scalar_type() == want, op, ": expected out dtype ", want, " but got ", out.scalar_type());
+  at::native::resize_output(out, input.sizes());
+  if (out.is_contiguous()) {
+    softmax_forward_into(input, dim, half_to_float, is_log, out, op);
+  } else {
+    Tensor tmp = at::empty_like(input, input.options().dtype(want), at::MemoryFormat::Contiguous);
+    softmax_forward_into(input, dim, half_to_float, is_log, tmp, op);
+    out.copy_(tmp);
+  }
+  return out;
+}
+
+static void softmax_backward_into(const Tensor& grad, const Tensor& output, int64_t dim_, at::ScalarType input_dtype,
+                                  bool is_log, const Tensor& grad_input, const char* op) {
+  const c10::cuda::CUDAGuard guard(grad.device());
+  const bool half_to_float = grad.scalar_type() != input_dtype;
+  if (half_to_float) {
+    TORCH_CHECK(grad.scalar_type() == at::kFloat && (input_dtype == at::kHalf || input_dtype == at::kBFloat16), op,
+                ": expected input and grad types to match, or input to be at::Half/BFloat16 and grad to be at::Float");
+  }
+  TORCH_CHECK(grad.sizes() == output.sizes(), op, ": grad and output sizes differ");
+  const int64_t dim = at::maybe_wrap_dim(dim_, grad.dim());
+  TORCH_CHECK(dim >= 0 && dim < std::max<int64_t>(grad.dim(), 1), op, ": dim must be non-negative and less than input dimensions");
+  if (grad.numel() == 0) return;
+  Tensor g = grad.contiguous();
+  Tensor y = output.to(g.scalar_type()).contiguous();
+  const SoftmaxDims d = softmax_dims(g, dim);
+  check_status(b2n_softmax_bwd(g.const_data_ptr(), y.const_data_ptr(), grad_input.mutable_data_ptr(), d.outer, d.n,
+                               d.inner, to_b2n_dtype(g.scalar_type(), op), to_b2n_dtype(grad_input.scalar_type(), op),
+                               is_log ? 1 : 0, cur_stream()),
+               op);
+}
+
+static Tensor softmax_backward(const Tensor& grad, const Tensor& output, int64_t dim, at::ScalarType input_dtype,
+                               bool is_log, const char* op) {
+  TORCH_CHECK(grad.is_cuda() && output.is_cuda(), op, ": expected CUDA tensors");
+  const c10::cuda::CUDAGuard guard(grad.device());
+  Tensor gi = at::empty_like(grad, grad.options().dtype(input_dtype), at::MemoryFormat::Contiguous);
+  softmax_backward_into(grad, output, dim, input_dtype, is_log, gi, op);
+  return gi;
+}
+
+static Tensor& softmax_backward_out(const Tensor& grad, const Tensor& output, int64_t dim, at::ScalarType input_dtype,
+                                    bool is_log, Tensor& grad_input, const char* op) {
+  TORCH_CHECK(grad.is_cuda() && output.is_cuda() && grad_input.is_cuda(), op, ": expected CUDA tensors");
+  TORCH_CHECK(grad_input.scalar_type() == input_dtype, op, ": expected grad_input dtype ", input_dtype, " but got ",
+              grad_input.scalar_type());
+  at::native::resize_output(grad_input, grad.sizes());
+  if (grad_input.is_contiguous()) {
+    softmax_backward_into(grad, output, dim, input_dtype, is_log, grad_input, op);
+  } else {
+    Tensor tmp = at::empty_like(grad, grad.options().dtype(input_dtype), at::MemoryFormat::Contiguous);
+    softmax_backward_into(grad, output, dim, input_dtype, is_log, tmp, op);
+    grad_input.copy_(tmp);
+  }
+  return grad_input;
+}
+
+Tensor softmax(const Tensor& self, int64_t dim, bool h2f) { return softmax_forward(self, dim, h2f, false, "_softmax"); }
+Tensor& softmax_out(const Tensor& self, int64_t dim, bool h2f, Tensor& out) {
+  return softmax_forward_out(self, dim, h2f, false, out, "_softmax.out");
+}
+Tensor log_softmax(const Tensor& self, int64_t dim, bool h2f) { return softmax_forward(self, dim, h2f, true, "_log_softmax"); }
+Tensor& log_softmax_out(const Tensor& self, int64_t dim, bool h2f, Tensor& out) {
+  return softmax_forward_out(self, dim, h2f, true, out, "_log_softmax.out");
+}
+Tensor softmax_backward_data(const Tensor& grad, const Tensor& output, int64_t dim, at::ScalarType input_dtype) {
+  return softmax_backward(grad, output, dim, input_dtype, false, "_softmax_backward_data");
+}
+Tensor& softmax_backward_data_out(const Tensor& grad, const Tensor& output, int64_t dim, at::ScalarType input_dtype,
+                                  Tensor& grad_input) {
+  return softmax_backward_out(grad, output, dim, input_dtype, false, grad_input, "_softmax_backward_data.out");
+}
+Tensor log_softmax_backward_data(const Tensor& grad, const Tensor& output, int64_t dim, at::ScalarType input_dtype) {
+  return softmax_backward(grad, output, dim, input_dtype, true, "_log_softmax_backward_data");
+}
+Tensor& log_softmax_backward_data_out(const Tensor& grad, const Tensor& output, int64_t dim,
+                                      at::ScalarType input_dtype, Tensor& grad_input) {
+  return softmax_backward_out(grad, output, dim, input_dtype, true, grad_input, "_log_softmax_backward_data.out");
+}
+
+// ---- nll_loss ------------------------------------------------------------------------------------
+// Shape rules of the upstream meta function for nll_loss_forward.
+static void nll_check(const Tensor& self, const Tensor& target, const Tensor& weight) {
+  TORCH_CHECK(self.dim() > 0 && self.dim() <= 2, "input tensor should be 1D or 2D");
+  TORCH_CHECK(target.dim() <= 1, "0D or 1D target tensor expected, multi-target not supported");
+  const bool no_batch = self.dim() == 1 && target.dim() == 0;
+  TORCH_CHECK(no_batch || (self.size(0) == target.size(0)), "size mismatch (got input: ", self.sizes(),
+              ", target: ", target.sizes(), ")");
+  const int64_t C = self.size(-1);
+  TORCH_CHECK(!weight.defined() || (weight.dim() == 1 && weight.numel() == C),
+              "weight tensor should be defined either for all ", C, " classes or no classes but got weight tensor of shape: ",
+              weight.sizes());
+  TORCH_CHECK(target.scalar_type() == at::kLong || target.scalar_type() == at::kByte,
+              "expected target dtype Long or Byte but got ", target.scalar_type());
+}
+
+static void nll_forward_into(const Tensor& self, const Tensor& target, const Tensor& weight, int64_t reduction,
+                             int64_t ignore_index, const Tensor& output, const Tensor& total_weight) {
+  const c10::cuda::CUDAGuard guard(self.device());
+  const int64_t C = self.size(-1);
+  const int64_t M = self.dim() == 1 ? 1 : self.size(0);
+  Tensor x = self.contiguous();
+  Tensor t = target.contiguous();
+  Tensor w = weight.defined() ? weight.to(self.scalar_type()).contiguous() : Tensor();
+  const size_t ws_bytes = b2n_nll_loss_workspace_bytes(M);
+  Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, self.options().dtype(at::kByte));
+  if (reduction == at::Reduction::None) total_weight.zero_();
+  check_status(b2n_nll_loss_fwd(x.const_data_ptr(), t.const_data_ptr(), w.defined() ? w.const_data_ptr() : nullptr,
+                                output.mutable_data_ptr(), total_weight.mutable_data_ptr(), nullptr,
+                                ws.mutable_data_ptr(), ws_bytes, M, C, static_cast<int>(reduction), ignore_index,
+                                to_b2n_dtype(self.scalar_type(), "nll_loss_forward"),
+                                t.scalar_type() == at::kByte ? 1 : 0, cur_stream()),
+               "nll_loss_fwd");
+}
+
+std::tuple<Tensor, Tensor> nll_loss_forward(const Tensor& self, const Tensor& target,
+                                            const std::optional<Tensor>& weight_opt, int64_t reduction,
+                                            int64_t ignore_index) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  const Tensor& weight = *weight_mo;
+  TORCH_CHECK(self.is_cuda() && target.is_cuda(), "nll_loss_forward: expected CUDA tensors");
+  nll_check(self, target, weight);
+  const c10::cuda::CUDAGuard guard(self.device());
+  const bool batched_none = reduction == at::Reduction::None && self.dim() == 2;
+  Tensor output = batched_none ? at::empty({self.size(0)}, self.options()) : at::empty({}, self.options());
+  Tensor total_weight = at::empty({}, self.options());
+  nll_forward_into(self, target, weight, reduction, ignore_index, output, total_weight);
+  return std::make_tuple(std::move(output), std::move(total_weight));
+}
+
+std::tuple<Tensor&, Tensor&> nll_loss_forward_out(const Tensor& self, const Tensor& target,
+                                                  const std::optional<Tensor>& weight_opt, int64_t reduction,
+                                                  int64_t ignore_index, Tensor& output, Tensor& total_weight) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  const Tensor& weight = *weight_mo;
+  TORCH_CHECK(self.is_cuda() && target.is_cuda(), "nll_loss_forward: expected CUDA tensors");
+  nll_check(self, target, weight);
+  const bool batched_none = reduction == at::Reduction::None && self.dim() == 2;
+  at::native::resize_output(output, batched_none ? at::IntArrayRef({self.size(0)}) : at::IntArrayRef({}));
+  at::native::resize_output(total_weight, {});
+  TORCH_CHECK(output.scalar_type() == self.scalar_type() && total_weight.scalar_type() == self.scalar_type(),
+              "nll_loss_forward.output: out tensors must have the input dtype");
+  TORCH_CHECK(output.is_contiguous(), "nll_loss_forward.output: output must be contiguous");
+  nll_forward_into(self, target, weight, reduction, ignore_index, output, total_weight);
+  return std::forward_as_tuple(output, total_weight);
+}
+
+static void nll_backward_into(const Tensor& grad_output, const Tensor& self, const Tensor& target,
+                              const Tensor& weight, int64_t reduction, int64_t ignore_index,
+                              const Tensor& total_weight, const Tensor& grad_input) {
+  const c10::cuda::CUDAGuard guard(self.device());
+  const int64_t C = self.size(-1);
+  const int64_t M = self.dim() == 1 ? 1 : self.size(0);
+  Tensor g = grad_output.to(self.scalar_type()).contiguous();
+  Tensor t = target.contiguous();
+  Tensor w = weight.defined() ? weight.to(self.scalar_type()).contiguous() : Tensor();
+  Tensor tw = total_weight.to(self.scalar_type()).contiguous();
+  if (reduction == at::Reduction::None && self.dim() == 2) {
+    TORCH_CHECK(g.dim() == 1 && g.size(0) == M, "Expected a tensor of dimension 1 and tensor.size[0] == ", M,
+                " but got: dimension ", g.dim(), " and tensor.size[0] == ", g.dim() ? g.size(0) : 0);
+  } else {
+    TORCH_CHECK(g.numel() == 1, "Expected a single element grad_output tensor, but got: ", g.sizes());
+  }
+  check_status(b2n_nll_loss_bwd(g.const_data_ptr(), t.const_data_ptr(), w.defined() ? w.const_data_ptr() : nullptr,
+                                tw.const_data_ptr(), grad_input.mutable_data_ptr(), M, C,
+                                static_cast<int>(self.dim() == 1 && reduction == at::Reduction::None ? at::Reduction::Sum
+                                                                                                    : reduction),
+                                ignore_index, to_b2n_dtype(self.scalar_type(), "nll_loss_backward"),
+                                t.scalar_type() == at::kByte ? 1 : 0, cur_stream()),
+               "nll_loss_bwd");
+}
+
+Tensor nll_loss_backward(const Tensor& grad_output, const Tensor& self, const Tensor& target,
+                         const std::optional<Tensor>& weight_opt, int64_t reduction, int64_t ignore_index,
+                         const Tensor& total_weight) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  const Tensor& weight = *weight_mo;
+  TORCH_CHECK(self.is_cuda() && target.is_cuda() && grad_output.is_cuda(), "nll_loss_backward: expected CUDA tensors");
+  nll_check(self, target, weight);
+  const c10::cuda::CUDAGuard guard(self.device());
+  Tensor grad_input = at::empty_like(self, at::MemoryFormat::Contiguous);
+  nll_backward_into(grad_output, self, target, weight, reduction, ignore_index, total_weight, grad_input);
+  return grad_input;
+}
+
+Tensor& nll_loss_backward_out(const Tensor& grad_output, const Tensor& self, const Tensor& target,
+                              const std::optional<Tensor>& weight_opt, int64_t reduction, int64_t ignore_index,
+                              const Tensor& total_weight, Tensor& grad_input) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  const Tensor& weight = *weight_mo;
+  TORCH_CHECK(self.is_cuda() && target.is_cuda() && grad_output.is_cuda(), "nll_loss_backward: expected CUDA tensors");
+  nll_check(self, target, weight);
+  at::native::resize_output(grad_input, self.sizes());
+  TORCH_CHECK(grad_input.scalar_type() == self.scalar_type() && grad_input.is_contiguous(),
+              "nll_loss_backward.grad_input: grad_input must be contiguous and have the input dtype");
+  nll_backward_into(grad_output, self, target, weight, reduction, ignore_index, total_weight, grad_input);
+  return grad_input;
+}
+
+}  // namespace b200norm
+
+TORCH_LIBRARY_IMPL(aten, CUDA, m) {
+  using namespace b200norm;
+  m.impl("native_layer_norm", TORCH_FN(native_layer_norm));
+  m.impl("native_layer_norm_backward", TORCH_FN(native_layer_norm_backward));
+  m.impl("_fused_rms_norm", TORCH_FN(fused_rms_norm));
+  m.impl("_fused_rms_norm_backward", TORCH_FN(fused_rms_norm_backward));
+  m.impl("_softmax", TORCH_FN(softmax));
+  m.impl("_softmax.out", TORCH_FN(softmax_out));
+  m.impl("_log_softmax", TORCH_FN(log_softmax));
+  m.impl("_log_softmax.out", TORCH_FN(log_softmax_out));
+  m.impl("_softmax_backward_data", TORCH_FN(softmax_backward_data));
+  m.impl("_softmax_backward_data.out", TORCH_FN(softmax_backward_data_out));
+  m.impl("_log_softmax_backward_data", TORCH_FN(log_softmax_backward_data));
+  m.impl("_log_softmax_backward_data.out", TORCH_FN(log_softmax_backward_data_out));
+  m.impl("nll_loss_forward", TORCH_FN(nll_loss_forward));
+  m.impl("nll_loss_forward.output", TORCH_FN(nll_loss_forward_out));
+  m.impl("nll_loss_backward", TORCH_FN(nll_loss_backward));
+  m.impl("nll_loss_backward.grad_input", TORCH_FN(nll_loss_backward_out));
+}

@@ -1,0 +1,188 @@
+// The C ABI declared in include/b200norm.h: argument validation, then the typed launchers.
+#include <mutex>
+
+#include "common.cuh"
+#include "launchers.h"
+
+namespace b2n {
+
+namespace {
+constexpr int kMaxDevices = 64;
+__device__ int g_status_word = 0;  // one per device (each device that loads the module has its own)
+
+thread_local int tl_last_cuda_error = 0;
+thread_local int tl_forced_path = B2N_PATH_AUTO;
+thread_local const char* tl_last_path = "none";
+
+struct PerDevice {
+  std::once_flag once;
+  DeviceInfo info{};
+  int* status_ptr = nullptr;
+};
+PerDevice g_devices[kMaxDevices];
+
+PerDevice& current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  PerDevice& pd = g_devices[dev % kMaxDevices];
+  std::call_once(pd.once, [&pd, dev]() {
+    cudaDeviceGetAttribute(&pd.info.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&pd.info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) == cudaSuccess) pd.status_ptr = static_cast<int*>(p);
+  });
+  return pd;
+}
+}  // namespace
+
+const DeviceInfo& device_info() { return current_device().info; }
+int* device_status_ptr() { return current_device().status_ptr; }
+int check_cuda(cudaError_t e) {
+  if (e == cudaSuccess) return B2N_OK;
+  tl_last_cuda_error = static_cast<int>(e);
+  return B2N_ERR_CUDA;
+}
+int forced_path() { return tl_forced_path; }
+void note_path(const char* name) { tl_last_path = name; }
+
+static bool valid_dtype(int dt) { return dt >= B2N_F32 && dt <= B2N_F64; }
+
+}  // namespace b2n
+
+using namespace b2n;
+
+extern "C" {
+
+int b2n_abi_version(void) { return B2N_ABI_VERSION; }
+
+const char* b2n_strerror(int status) {
+  switch (status) {
+    case B2N_OK: return "ok";
+    case B2N_ERR_BAD_ARG: return "bad argument";
+    case B2N_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype combination";
+    case B2N_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case B2N_ERR_CUDA: return "CUDA runtime error";
+    case B2N_ERR_TIMEOUT: return "bounded device-side wait gave up";
+    case B2N_ERR_TARGET_RANGE: return "nll_loss target out of range";
+    case B2N_ERR_TOO_LARGE: return "size beyond the entry point's limit";
+    default: return "unknown status";
+  }
+}
+
+int b2n_last_cuda_error(void) { return tl_last_cuda_error; }
+
+int b2n_set_path(int path) {
+  const int prev = tl_forced_path;
+  if (path >= B2N_PATH_AUTO && path <= B2N_PATH_CLUSTER) tl_forced_path = path;
+  return prev;
+}
+
+const char* b2n_last_path(void) { return tl_last_path; }
+
+int b2n_device_status(void* stream) {
+  int* p = device_status_ptr();
+  if (p == nullptr) return B2N_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  if (check_cuda(cudaMemcpyAsync(&v, p, sizeof(int), cudaMemcpyDeviceToHost, st))) return B2N_ERR_CUDA;
+  if (check_cuda(cudaStreamSynchronize(st))) return B2N_ERR_CUDA;
+  if (v != 0) {
+    if (check_cuda(cudaMemsetAsync(p, 0, sizeof(int), st))) return B2N_ERR_CUDA;
+    if (check_cuda(cudaStreamSynchronize(st))) return B2N_ERR_CUDA;
+  }
+  return v;
+}
+
+int b2n_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, void* mean, void* rstd,
+                       int64_t M, int64_t N, double eps, int x_dtype, int w_dtype, void* stream) {
+  if (M < 0 || N < 0 || !valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return B2N_ERR_BAD_ARG;
+  if (M == 0) return B2N_OK;
+  if (!x || !y || !mean || !rstd) return B2N_ERR_BAD_ARG;
+  if (gamma == nullptr && beta == nullptr) w_dtype = x_dtype;
+  return launch_norm_fwd(false, x, gamma, beta, y, mean, rstd, M, N, eps, x_dtype, w_dtype,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int b2n_rms_norm_fwd(const void* x, const void* gamma, void* y, void* rstd, int64_t M, int64_t N, double eps,
+                     int x_dtype, int w_dtype, void* stream) {
+  if (M < 0 || N < 0 || !valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return B2N_ERR_BAD_ARG;
+  if (M == 0) return B2N_OK;
+  if (!x || !y || !rstd) return B2N_ERR_BAD_ARG;
+  if (gamma == nullptr) w_dtype = x_dtype;
+  return launch_norm_fwd(true, x, gamma, nullptr, y, nullptr, rstd, M, N, eps, x_dtype, w_dtype,
+                         static_cast<cudaStream_t>(stream));
+}
+
+size_t b2n_norm_bwd_workspace_bytes(int64_t M, int64_t N, int x_dtype, int w_dtype, int want_wgrad) {
+  if (!valid_dtype(x_dtype)) return 0;
+  return norm_bwd_workspace_bytes(M, N, x_dtype, w_dtype, want_wgrad);
+}
+
+int b2n_layer_norm_bwd(const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma,
+                       void* dx, void* dgamma, void* dbeta, void* workspace, size_t workspace_bytes, int64_t M,
+                       int64_t N, int x_dtype, int w_dtype, void* stream) {
+  if (M < 0 || N < 0 || !valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return B2N_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return B2N_OK;
+  if (!dy || !x || !mean || !rstd) return B2N_ERR_BAD_ARG;
+  if (!dx && !dgamma && !dbeta) return B2N_OK;
+  if (gamma == nullptr && dgamma == nullptr && dbeta == nullptr) w_dtype = x_dtype;
+  return launch_norm_bwd(false, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, workspace, workspace_bytes, M, N,
+                         x_dtype, w_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int b2n_rms_norm_bwd(const void* dy, const void* x, const void* rstd, const void* gamma, void* dx, void* dgamma,
+                     void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int x_dtype, int w_dtype,
+                     void* stream) {
+  if (M < 0 || N < 0 || !valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return B2N_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return B2N_OK;
+  if (!dy || !x || !rstd) return B2N_ERR_BAD_ARG;
+  if (!dx && !dgamma) return B2N_OK;
+  if (gamma == nullptr && dgamma == nullptr) w_dtype = x_dtype;
+  return launch_norm_bwd(true, dy, x, nullptr, rstd, gamma, dx, dgamma, nullptr, workspace, workspace_bytes, M, N,
+                         x_dtype, w_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t inner, int in_dtype, int out_dtype,
+                    int is_log, void* stream) {
+  if (outer < 0 || N < 0 || inner < 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return B2N_ERR_BAD_ARG;
+  if (outer == 0 || N == 0 || inner == 0) return B2N_OK;
+  if (!x || !y) return B2N_ERR_BAD_ARG;
+  return launch_softmax_fwd(x, y, outer, N, inner, in_dtype, out_dtype, is_log != 0,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int b2n_softmax_bwd(const void* dy, const void* y, void* dx, int64_t outer, int64_t N, int64_t inner,
+                    int grad_dtype, int dx_dtype, int is_log, void* stream) {
+  if (outer < 0 || N < 0 || inner < 0 || !valid_dtype(grad_dtype) || !valid_dtype(dx_dtype)) return B2N_ERR_BAD_ARG;
+  if (outer == 0 || N == 0 || inner == 0) return B2N_OK;
+  if (!dy || !y || !dx) return B2N_ERR_BAD_ARG;
+  return launch_softmax_bwd(dy, y, dx, outer, N, inner, grad_dtype, dx_dtype, is_log != 0,
+                            static_cast<cudaStream_t>(stream));
+}
+
+size_t b2n_nll_loss_workspace_bytes(int64_t M) { return nll_loss_workspace_bytes(M); }
+
+int b2n_nll_loss_fwd(const void* logp, const void* target, const void* weight, void* out, void* total_weight,
+                     float* sums_f32, void* workspace, size_t workspace_bytes, int64_t M, int64_t C,
+                     int reduction, int64_t ignore_index, int dtype, int target_is_u8, void* stream) {
+  if (M < 0 || C < 0 || !valid_dtype(dtype) || reduction < B2N_REDUCE_NONE || reduction > B2N_REDUCE_SUM)
+    return B2N_ERR_BAD_ARG;
+  if (M > 0 && (!logp || !target)) return B2N_ERR_BAD_ARG;
+  if (!out) return B2N_ERR_BAD_ARG;
+  return launch_nll_loss_fwd(logp, target, weight, out, total_weight, sums_f32, workspace, workspace_bytes, M, C,
+                             reduction, ignore_index, dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
+}
+
+int b2n_nll_loss_bwd(const void* grad_out, const void* target, const void* weight, const void* total_weight,
+                     void* grad_input, int64_t M, int64_t C, int reduction, int64_t ignore_index, int dtype,
+                     int target_is_u8, void* stream) {
+  if (M < 0 || C < 0 || !valid_dtype(dtype) || reduction < B2N_REDUCE_NONE || reduction > B2N_REDUCE_SUM)
+    return B2N_ERR_BAD_ARG;
+  if (M == 0 || C == 0) return B2N_OK;
+  if (!grad_out || !target || !grad_input) return B2N_ERR_BAD_ARG;
+  if (reduction == B2N_REDUCE_MEAN && !total_weight) return B2N_ERR_BAD_ARG;
+  return launch_nll_loss_bwd(grad_out, target, weight, total_weight, grad_input, M, C, reduction, ignore_index,
+                             dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

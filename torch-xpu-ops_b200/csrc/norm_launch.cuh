@@ -1,0 +1,250 @@
+// Typed host launchers for layer norm / RMS norm.  Instantiated per (T, WT) pair in the norm_*.cu
+// files so the instantiations compile in parallel.
+#pragma once
+#include <atomic>
+#include <type_traits>
+
+#include "launchers.h"
+#include "norm_generic.cuh"
+#include "norm_ring.cuh"
+#include "plan.h"
+
+namespace b2n {
+
+// Elements per thread in the ring kernels: forward keeps x, gamma, beta in registers; backward
+// keeps gamma, dgamma, dbeta and two working arrays, so it gets half as many elements.
+constexpr int kNormFwdEpt = 32;
+constexpr int kNormBwdEpt = 16;
+
+// Opt the kernel into its dynamic shared memory, once per device.
+template <typename K> int set_smem_once(K kernel, size_t bytes, std::atomic<uint64_t>& mask) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError());
+  const uint64_t bit = 1ull << (dev & 63);
+  if (mask.load(std::memory_order_acquire) & bit) return B2N_OK;
+  (void)bytes;
+  const int st = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 device_info().max_smem_optin));
+  if (st == B2N_OK) mask.fetch_or(bit, std::memory_order_release);
+  return st;
+}
+
+inline int generic_grid(int64_t rows, int rows_per_block) {
+  const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
+  const int64_t cap = static_cast<int64_t>(device_info().sm_count) * 16;
+  return static_cast<int>(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+template <typename T, typename WT>
+bool norm_vectorizable(int64_t N, const void* a, const void* b, const void* c) {
+  constexpr int V = 16 / sizeof(T);
+  return N % V == 0 && is_aligned(a, 16) && (b == nullptr || is_aligned(b, 16)) &&
+         (c == nullptr || is_aligned(c, 16));
+}
+
+// ---- forward ------------------------------------------------------------------------------------
+template <typename T, typename WT, bool RMS, int GROUP>
+int norm_fwd_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, float* mean,
+                         float* rstd, int64_t M, int64_t N, double eps, cudaStream_t st) {
+  constexpr int VPT = kNormFwdEpt / Pack16<T>::VEC;
+  auto kernel = norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT>;
+  static std::atomic<uint64_t> mask{0};
+  if (int e = set_smem_once(kernel, p.smem, mask)) return e;
+  kernel<<<p.grid, kRingThreads, p.smem, st>>>(x, gamma, beta, y, mean, rstd, M, static_cast<int>(N),
+                                               static_cast<float>(eps), p.stages, p.rpg, device_status_ptr());
+  return check_cuda(cudaGetLastError());
+}
+
+template <typename T, typename WT, bool RMS>
+int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* y_, void* mean_, void* rstd_,
+                   int64_t M, int64_t N, double eps, cudaStream_t st) {
+  using A = acc_t<T>;
+  const T* x = static_cast<const T*>(x_);
+  const WT* gamma = static_cast<const WT*>(gamma_);
+  const WT* beta = static_cast<const WT*>(beta_);
+  T* y = static_cast<T*>(y_);
+  A* mean = static_cast<A*>(mean_);
+  A* rstd = static_cast<A*>(rstd_);
+  const int forced = forced_path();
+
+  if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
+    if (forced != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
+      const DeviceInfo& di = device_info();
+      const RingPlan p = plan_ring(M, N, sizeof(T), 1, kNormFwdEpt, di.sm_count, di.max_smem_optin);
+      if (p.ok) {
+        note_path("ring");
+        switch (p.group) {
+          case 32: return norm_fwd_ring_launch<T, WT, RMS, 32>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+          case 64: return norm_fwd_ring_launch<T, WT, RMS, 64>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+          case 128: return norm_fwd_ring_launch<T, WT, RMS, 128>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+          case 256: return norm_fwd_ring_launch<T, WT, RMS, 256>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+          default: return norm_fwd_ring_launch<T, WT, RMS, 512>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+        }
+      }
+    }
+  }
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+
+  note_path("generic");
+  constexpr int V = 16 / sizeof(T);
+  const bool vec = norm_vectorizable<T, WT>(N, x, y, nullptr);
+  const A eps_a = static_cast<A>(eps);
+  if (N <= 1024) {
+    const int grid = generic_grid(M, 8);
+    if (vec) norm_fwd_generic_kernel<T, WT, RMS, 32, V><<<grid, 256, 0, st>>>(x, gamma, beta, y, mean, rstd, M, N, eps_a);
+    else norm_fwd_generic_kernel<T, WT, RMS, 32, 1><<<grid, 256, 0, st>>>(x, gamma, beta, y, mean, rstd, M, N, eps_a);
+  } else {
+    const int grid = generic_grid(M, 1);
+    const int threads = N <= 8192 ? 256 : 1024;
+    if (vec) norm_fwd_generic_kernel<T, WT, RMS, 0, V><<<grid, threads, 0, st>>>(x, gamma, beta, y, mean, rstd, M, N, eps_a);
+    else norm_fwd_generic_kernel<T, WT, RMS, 0, 1><<<grid, threads, 0, st>>>(x, gamma, beta, y, mean, rstd, M, N, eps_a);
+  }
+  return check_cuda(cudaGetLastError());
+}
+
+// ---- backward -----------------------------------------------------------------------------------
+// Number of partial rows ([2][N] accumulate-type values each) the weight-gradient reduction writes.
+inline int64_t wgrad_generic_chunks(int64_t M) {
+  int64_t c = (M + 63) / 64;
+  return c < 1 ? 1 : (c > 256 ? 256 : c);
+}
+template <typename T> int64_t wgrad_partial_rows(int64_t M, int64_t N) {
+  int64_t rows = wgrad_generic_chunks(M);
+  if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
+    const DeviceInfo& di = device_info();
+    const RingPlan p = plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, di.sm_count, di.max_smem_optin);
+    if (p.ok && static_cast<int64_t>(p.grid) * p.ng > rows) rows = static_cast<int64_t>(p.grid) * p.ng;
+  }
+  return rows;
+}
+template <typename T> size_t norm_bwd_ws_bytes_typed(int64_t M, int64_t N) {
+  return static_cast<size_t>(wgrad_partial_rows<T>(M, N)) * 2 * static_cast<size_t>(N) * sizeof(acc_t<T>);
+}
+
+template <typename T, typename WT, bool RMS, int GROUP>
+int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x, const float* mean,
+                         const float* rstd, const WT* gamma, T* dx, float* ws, int64_t M, int64_t N,
+                         cudaStream_t st) {
+  constexpr int VPT = kNormBwdEpt / Pack16<T>::VEC;
+  static std::atomic<uint64_t> mask_w{0}, mask_n{0};
+  if (wgrad) {
+    auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true>;
+    if (int e = set_smem_once(kernel, p.smem, mask_w)) return e;
+    kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
+                                                 p.stages, p.rpg, device_status_ptr());
+  } else {
+    auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false>;
+    if (int e = set_smem_once(kernel, p.smem, mask_n)) return e;
+    kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
+                                                 p.stages, p.rpg, device_status_ptr());
+  }
+  return check_cuda(cudaGetLastError());
+}
+
+template <typename T, typename WT, bool RMS>
+int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const void* rstd_, const void* gamma_,
+                   void* dx_, void* dgamma_, void* dbeta_, void* workspace, size_t workspace_bytes, int64_t M,
+                   int64_t N, cudaStream_t st) {
+  using A = acc_t<T>;
+  const T* dy = static_cast<const T*>(dy_);
+  const T* x = static_cast<const T*>(x_);
+  const A* mean = static_cast<const A*>(mean_);
+  const A* rstd = static_cast<const A*>(rstd_);
+  const WT* gamma = static_cast<const WT*>(gamma_);
+  T* dx = static_cast<T*>(dx_);
+  WT* dgamma = static_cast<WT*>(dgamma_);
+  WT* dbeta = RMS ? nullptr : static_cast<WT*>(dbeta_);
+  const bool wgrad = dgamma != nullptr || dbeta != nullptr;
+  const int forced = forced_path();
+  if (wgrad) {
+    if (workspace == nullptr || !is_aligned(workspace, 16) || workspace_bytes < norm_bwd_ws_bytes_typed<T>(M, N))
+      return B2N_ERR_WORKSPACE;
+  }
+  A* ws = static_cast<A*>(workspace);
+  const dim3 fold_block(32, 8);
+  const dim3 fold_grid(static_cast<unsigned>((N + 31) / 32), 2);
+
+  if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
+    if (forced != B2N_PATH_GENERIC && dx != nullptr && is_aligned(dy, 16) && is_aligned(x, 16) &&
+        is_aligned(dx, 16) && N <= (1 << 20)) {
+      const DeviceInfo& di = device_info();
+      const RingPlan p = plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, di.sm_count, di.max_smem_optin);
+      if (p.ok) {
+        note_path("ring");
+        int e;
+        switch (p.group) {
+          case 32: e = norm_bwd_ring_launch<T, WT, RMS, 32>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          case 64: e = norm_bwd_ring_launch<T, WT, RMS, 64>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          case 128: e = norm_bwd_ring_launch<T, WT, RMS, 128>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          case 256: e = norm_bwd_ring_launch<T, WT, RMS, 256>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          default: e = norm_bwd_ring_launch<T, WT, RMS, 512>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+        }
+        if (e != B2N_OK || !wgrad) return e;
+        norm_bwd_wgrad_fold_kernel<float, WT><<<fold_grid, fold_block, 0, st>>>(
+            ws, dgamma, dbeta, static_cast<int64_t>(p.grid) * p.ng, N);
+        return check_cuda(cudaGetLastError());
+      }
+    }
+  }
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+
+  note_path("generic");
+  if (dx != nullptr) {
+    constexpr int V = 16 / sizeof(T);
+    const bool vec = norm_vectorizable<T, WT>(N, dy, x, dx);
+    if (N <= 1024) {
+      const int grid = generic_grid(M, 8);
+      if (vec) norm_bwd_dx_generic_kernel<T, WT, RMS, 32, V><<<grid, 256, 0, st>>>(dy, x, mean, rstd, gamma, dx, M, N);
+      else norm_bwd_dx_generic_kernel<T, WT, RMS, 32, 1><<<grid, 256, 0, st>>>(dy, x, mean, rstd, gamma, dx, M, N);
+    } else {
+      const int grid = generic_grid(M, 1);
+      const int threads = N <= 8192 ? 256 : 1024;
+      if (vec) norm_bwd_dx_generic_kernel<T, WT, RMS, 0, V><<<grid, threads, 0, st>>>(dy, x, mean, rstd, gamma, dx, M, N);
+      else norm_bwd_dx_generic_kernel<T, WT, RMS, 0, 1><<<grid, threads, 0, st>>>(dy, x, mean, rstd, gamma, dx, M, N);
+    }
+    if (int e = check_cuda(cudaGetLastError())) return e;
+  }
+  if (wgrad) {
+    const int64_t chunks = wgrad_generic_chunks(M);
+    const int64_t rpc = (M + chunks - 1) / chunks;
+    const dim3 block(32, 8);
+    const dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>(chunks));
+    norm_bwd_wgrad_partial_kernel<T, RMS><<<grid, block, 0, st>>>(dy, x, mean, rstd, ws, M, N, rpc);
+    if (int e = check_cuda(cudaGetLastError())) return e;
+    norm_bwd_wgrad_fold_kernel<A, WT><<<fold_grid, fold_block, 0, st>>>(ws, dgamma, dbeta, chunks, N);
+    if (int e = check_cuda(cudaGetLastError())) return e;
+  }
+  return B2N_OK;
+}
+
+// Declares/defines the per-type entry points that norm_dispatch.cu switches over.
+#define B2N_NORM_TYPED_DECL(NAME)                                                                               \
+  int norm_fwd_##NAME(bool rms, const void* x, const void* gamma, const void* beta, void* y, void* mean,       \
+                      void* rstd, int64_t M, int64_t N, double eps, cudaStream_t st);                           \
+  int norm_bwd_##NAME(bool rms, const void* dy, const void* x, const void* mean, const void* rstd,              \
+                      const void* gamma, void* dx, void* dgamma, void* dbeta, void* ws, size_t ws_bytes,        \
+                      int64_t M, int64_t N, cudaStream_t st);                                                   \
+  size_t norm_bwd_ws_##NAME(int64_t M, int64_t N);
+
+#define B2N_NORM_TYPED_DEFINE(NAME, T, WT)                                                                      \
+  int norm_fwd_##NAME(bool rms, const void* x, const void* gamma, const void* beta, void* y, void* mean,       \
+                      void* rstd, int64_t M, int64_t N, double eps, cudaStream_t st) {                          \
+    return rms ? norm_fwd_typed<T, WT, true>(x, gamma, beta, y, mean, rstd, M, N, eps, st)                      \
+               : norm_fwd_typed<T, WT, false>(x, gamma, beta, y, mean, rstd, M, N, eps, st);                    \
+  }                                                                                                             \
+  int norm_bwd_##NAME(bool rms, const void* dy, const void* x, const void* mean, const void* rstd,              \
+                      const void* gamma, void* dx, void* dgamma, void* dbeta, void* ws, size_t ws_bytes,        \
+                      int64_t M, int64_t N, cudaStream_t st) {                                                  \
+    return rms ? norm_bwd_typed<T, WT, true>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st) \
+               : norm_bwd_typed<T, WT, false>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st); \
+  }                                                                                                             \
+  size_t norm_bwd_ws_##NAME(int64_t M, int64_t N) { return norm_bwd_ws_bytes_typed<T>(M, N); }
+
+B2N_NORM_TYPED_DECL(f32)
+B2N_NORM_TYPED_DECL(f16)
+B2N_NORM_TYPED_DECL(f16_w32)
+B2N_NORM_TYPED_DECL(bf16)
+B2N_NORM_TYPED_DECL(bf16_w32)
+B2N_NORM_TYPED_DECL(f64)
+
+}  // namespace b2n

@@ -1,0 +1,52 @@
+// Host-side launch planning for the ring kernels.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include "ring.cuh"
+
+namespace b2n {
+
+struct RingPlan {
+  bool ok = false;
+  int group = 0;   // threads per row: 32, 64, 128, 256 or 512
+  int ng = 0;      // row groups per CTA = 512 / group
+  int rpg = 1;     // rows per group per tile
+  int stages = 0;  // ring depth
+  int grid = 0;    // persistent CTAs
+  size_t smem = 0; // dynamic shared memory per CTA
+};
+
+// N elements of `esize` bytes per row, `nin` tensors staged per tile, `ept` elements per thread.
+// Not ok when the row is not a multiple of 16 bytes, does not fit 512 threads x ept elements, or
+// fewer than two stages fit in shared memory.
+inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int sm_count, int max_smem) {
+  RingPlan p;
+  const int vec = 16 / esize;
+  if (M <= 0 || N <= 0 || N % vec != 0) return p;
+  const int64_t nvec = N / vec;
+  const int vpt = ept / vec;
+  int group = 32;
+  while (group <= kRingConsumerThreads && static_cast<int64_t>(group) * vpt < nvec) group *= 2;
+  if (group > kRingConsumerThreads) return p;
+  p.group = group;
+  p.ng = kRingConsumerThreads / group;
+  const int64_t row_bytes = N * esize;
+  const int64_t target = nin == 1 ? 32768 : 16384;  // bytes per tensor per tile
+  int64_t rpg = target / (p.ng * row_bytes);
+  // keep at least ~4 tiles per CTA when there are few rows
+  while (rpg > 1 && (M + p.ng * rpg - 1) / (p.ng * rpg) < 4LL * sm_count) --rpg;
+  p.rpg = static_cast<int>(rpg < 1 ? 1 : (rpg > 4 ? 4 : rpg));
+  const int64_t stage = static_cast<int64_t>(nin) * p.ng * p.rpg * row_bytes;
+  int64_t s = (static_cast<int64_t>(max_smem) - kRingHeaderBytes) / stage;
+  if (s > kMaxStages) s = kMaxStages;
+  if (s < 2) return p;
+  p.stages = static_cast<int>(s);
+  p.smem = static_cast<size_t>(kRingHeaderBytes + s * stage);
+  const int64_t ntiles = (M + p.ng * p.rpg - 1) / (p.ng * p.rpg);
+  p.grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);
+  p.ok = true;
+  return p;
+}
+
+}  // namespace b2n

@@ -1,0 +1,207 @@
+// Generic softmax / log-softmax kernels: any N, any alignment, any softmax dim, fp32 / fp16 / bf16 /
+// fp64, optional 16-bit -> fp32 output ("half_to_float").
+//
+// Semantics follow at::native::xpu::host_softmax / host_softmax_backward
+// (src/ATen/native/xpu/sycl/SoftMaxKernels.cpp:2125-2240) and the CPU ATen kernels they are tested
+// against: -inf entries give exactly 0 (softmax) / -inf (log-softmax); a row that is all -inf, or
+// that holds +inf or NaN, comes out as NaN.
+#pragma once
+#include "common.cuh"
+
+namespace b2n {
+
+template <typename A> __device__ __forceinline__ A acc_nan();
+template <> __device__ __forceinline__ float acc_nan<float>() { return __int_as_float(0x7fc00000); }
+template <> __device__ __forceinline__ double acc_nan<double>() { return __longlong_as_double(0x7ff8000000000000LL); }
+
+// running (max, sum of exp(x - max)) pair
+template <typename A> struct MaxSum {
+  A m, s;
+  __device__ __forceinline__ void init() { m = acc_neg_inf<A>(); s = 0; }
+  __device__ __forceinline__ void add(A x) {
+    if (x > m) {
+      s = s * acc_exp(m - x) + A(1);  // m == -inf: exp(-inf) == 0 and s == 0
+      m = x;
+    } else if (!(x == acc_neg_inf<A>())) {
+      s += acc_exp(x - m);  // NaN propagates through here
+    }
+  }
+  __device__ __forceinline__ void merge(const MaxSum& o) {
+    const A nm = acc_max(m, o.m);
+    const A a = (m == acc_neg_inf<A>()) ? A(0) : s * acc_exp(m - nm);
+    const A b = (o.m == acc_neg_inf<A>()) ? A(0) : o.s * acc_exp(o.m - nm);
+    // NaN sums must survive a -inf max on the same side
+    s = ((m == acc_neg_inf<A>() && s != s) || (o.m == acc_neg_inf<A>() && o.s != o.s)) ? acc_nan<A>() : a + b;
+    m = nm;
+  }
+};
+
+template <typename A> __device__ __forceinline__ MaxSum<A> warp_merge(MaxSum<A> v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum<A> t;
+    t.m = __shfl_xor_sync(0xffffffffu, v.m, o);
+    t.s = __shfl_xor_sync(0xffffffffu, v.s, o);
+    v.merge(t);
+  }
+  return v;
+}
+
+template <int TPR, typename A> __device__ __forceinline__ MaxSum<A> row_merge(MaxSum<A> v, A* scratch /*64*/) {
+  v = warp_merge(v);
+  if constexpr (TPR == 32) {
+    return v;
+  } else {
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (l == 0) { scratch[2 * w] = v.m; scratch[2 * w + 1] = v.s; }
+    __syncthreads();
+    MaxSum<A> r;
+    r.m = scratch[0]; r.s = scratch[1];
+    for (int i = 1; i < nw; ++i) {
+      MaxSum<A> t;
+      t.m = scratch[2 * i]; t.s = scratch[2 * i + 1];
+      r.merge(t);
+    }
+    return r;
+  }
+}
+
+// Softmax over the last dim.  Pass 1 streams the row once keeping a running (max, sum); pass 2
+// re-reads it (L1/L2) and writes the result: two reads and one write per element.
+template <typename TI, typename TO, bool LOG, int TPR, int V>
+__global__ void softmax_fwd_generic_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t M, int64_t N) {
+  using A = acc_t<TI>;
+  __shared__ A scratch[64];
+  const int tpr = TPR == 32 ? 32 : static_cast<int>(blockDim.x);
+  const int rpb = TPR == 32 ? static_cast<int>(blockDim.x) / 32 : 1;
+  const int sub = TPR == 32 ? static_cast<int>(threadIdx.x) / 32 : 0;
+  const int lane = TPR == 32 ? static_cast<int>(threadIdx.x) % 32 : static_cast<int>(threadIdx.x);
+  const int64_t nv = N / V;
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * rpb; row0 < M; row0 += static_cast<int64_t>(gridDim.x) * rpb) {
+    const int64_t row = row0 + sub;
+    if (row >= M) continue;
+    const TI* xr = x + row * N;
+    TO* yr = y + row * N;
+    MaxSum<A> ms;
+    ms.init();
+    for (int64_t v = lane; v < nv; v += tpr) {
+      const Vec<TI, V> p = ld_vec<TI, V>(xr + v * V);
+#pragma unroll
+      for (int e = 0; e < V; ++e) ms.add(to_acc<A>(p.v[e]));
+    }
+    ms = row_merge<TPR>(ms, scratch);
+    if (ms.m == -acc_neg_inf<A>()) ms.s = acc_nan<A>();  // +inf in the row: exp(inf - inf)
+    const A mx = ms.m;
+    const A lg = LOG ? acc_log(ms.s) : A(0);
+    for (int64_t v = lane; v < nv; v += tpr) {
+      const Vec<TI, V> p = ld_vec<TI, V>(xr + v * V);
+      Vec<TO, V> o;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const A d = to_acc<A>(p.v[e]) - mx;
+        o.v[e] = from_acc<TO>(LOG ? d - lg : acc_exp(d) / ms.s);
+      }
+      st_vec<TO, V>(yr + v * V, o);
+    }
+  }
+}
+
+// softmax: dx = y*(dy - sum(y*dy)); log-softmax: dx = dy - exp(y)*sum(dy).
+// TG: type of dy and y; TO: type of dx.
+template <typename TG, typename TO, bool LOG, int TPR, int V>
+__global__ void softmax_bwd_generic_kernel(const TG* __restrict__ dy, const TG* __restrict__ y,
+                                           TO* __restrict__ dx, int64_t M, int64_t N) {
+  using A = acc_t<TG>;
+  __shared__ A scratch[32];
+  const int tpr = TPR == 32 ? 32 : static_cast<int>(blockDim.x);
+  const int rpb = TPR == 32 ? static_cast<int>(blockDim.x) / 32 : 1;
+  const int sub = TPR == 32 ? static_cast<int>(threadIdx.x) / 32 : 0;
+  const int lane = TPR == 32 ? static_cast<int>(threadIdx.x) % 32 : static_cast<int>(threadIdx.x);
+  const int64_t nv = N / V;
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * rpb; row0 < M; row0 += static_cast<int64_t>(gridDim.x) * rpb) {
+    const int64_t row = row0 + sub;
+    if (row >= M) continue;
+    const TG* dyr = dy + row * N;
+    const TG* yr = y + row * N;
+    TO* dxr = dx + row * N;
+    A s = 0;
+    for (int64_t v = lane; v < nv; v += tpr) {
+      const Vec<TG, V> pd = ld_vec<TG, V>(dyr + v * V);
+      if constexpr (LOG) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) s += to_acc<A>(pd.v[e]);
+      } else {
+        const Vec<TG, V> py = ld_vec<TG, V>(yr + v * V);
+#pragma unroll
+        for (int e = 0; e < V; ++e) s += to_acc<A>(pd.v[e]) * to_acc<A>(py.v[e]);
+      }
+    }
+    s = row_reduce<TPR>(s, scratch, SumOp());
+    for (int64_t v = lane; v < nv; v += tpr) {
+      const Vec<TG, V> pd = ld_vec<TG, V>(dyr + v * V);
+      const Vec<TG, V> py = ld_vec<TG, V>(yr + v * V);
+      Vec<TO, V> o;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const A d = to_acc<A>(pd.v[e]), yy = to_acc<A>(py.v[e]);
+        o.v[e] = from_acc<TO>(LOG ? d - acc_exp(yy) * s : yy * (d - s));
+      }
+      st_vec<TO, V>(dxr + v * V, o);
+    }
+  }
+}
+
+// Softmax along a dim that is not the last: the tensor is [outer, N, inner] and one thread walks
+// one (outer, inner) line with stride `inner`, so neighbouring threads touch neighbouring
+// addresses.  Three passes (max, sum, write).
+template <typename TI, typename TO, bool LOG>
+__global__ void softmax_fwd_spatial_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t outer,
+                                           int64_t N, int64_t inner) {
+  using A = acc_t<TI>;
+  const int64_t total = outer * inner;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t o = idx / inner, in = idx % inner;
+    const TI* xp = x + o * N * inner + in;
+    TO* yp = y + o * N * inner + in;
+    A mx = acc_neg_inf<A>();
+    bool has_nan = false;
+    for (int64_t j = 0; j < N; ++j) {
+      const A v = to_acc<A>(xp[j * inner]);
+      has_nan |= (v != v);
+      mx = acc_max(mx, v);
+    }
+    A s = 0;
+    for (int64_t j = 0; j < N; ++j) s += acc_exp(to_acc<A>(xp[j * inner]) - mx);
+    if (has_nan) s = acc_nan<A>();
+    const A lg = LOG ? acc_log(s) : A(0);
+    for (int64_t j = 0; j < N; ++j) {
+      const A d = to_acc<A>(xp[j * inner]) - mx;
+      yp[j * inner] = from_acc<TO>(LOG ? d - lg : acc_exp(d) / s);
+    }
+  }
+}
+
+template <typename TG, typename TO, bool LOG>
+__global__ void softmax_bwd_spatial_kernel(const TG* __restrict__ dy, const TG* __restrict__ y,
+                                           TO* __restrict__ dx, int64_t outer, int64_t N, int64_t inner) {
+  using A = acc_t<TG>;
+  const int64_t total = outer * inner;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t o = idx / inner, in = idx % inner;
+    const int64_t base = o * N * inner + in;
+    A s = 0;
+    for (int64_t j = 0; j < N; ++j) {
+      const A d = to_acc<A>(dy[base + j * inner]);
+      s += LOG ? d : d * to_acc<A>(y[base + j * inner]);
+    }
+    for (int64_t j = 0; j < N; ++j) {
+      const A d = to_acc<A>(dy[base + j * inner]), yy = to_acc<A>(y[base + j * inner]);
+      dx[base + j * inner] = from_acc<TO>(LOG ? d - acc_exp(yy) * s : yy * (d - s));
+    }
+  }
+}
+
+}  // namespace b2n

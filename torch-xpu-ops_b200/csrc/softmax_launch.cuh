@@ -1,0 +1,176 @@
+// Typed host launchers for softmax / log-softmax.  Instantiated per type pair in softmax_*.cu.
+#pragma once
+#include <atomic>
+#include <type_traits>
+
+#include "launchers.h"
+#include "plan.h"
+#include "softmax_generic.cuh"
+#include "softmax_ring.cuh"
+
+namespace b2n {
+
+constexpr int kSoftmaxEpt = 32;  // elements per thread in the ring kernels
+
+template <typename K> int set_smem_once_sm(K kernel, std::atomic<uint64_t>& mask) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError());
+  const uint64_t bit = 1ull << (dev & 63);
+  if (mask.load(std::memory_order_acquire) & bit) return B2N_OK;
+  const int st = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 device_info().max_smem_optin));
+  if (st == B2N_OK) mask.fetch_or(bit, std::memory_order_release);
+  return st;
+}
+
+inline int softmax_generic_grid(int64_t rows, int rows_per_block) {
+  const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
+  const int64_t cap = static_cast<int64_t>(device_info().sm_count) * 16;
+  return static_cast<int>(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+template <typename T, bool LOG, int GROUP>
+int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int64_t N, cudaStream_t st) {
+  constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
+  auto kernel = softmax_fwd_ring_kernel<T, LOG, GROUP, VPT>;
+  static std::atomic<uint64_t> mask{0};
+  if (int e = set_smem_once_sm(kernel, mask)) return e;
+  kernel<<<p.grid, kRingThreads, p.smem, st>>>(x, y, M, static_cast<int>(N), p.stages, p.rpg, device_status_ptr());
+  return check_cuda(cudaGetLastError());
+}
+
+template <typename T, bool LOG, int GROUP>
+int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, int64_t M, int64_t N,
+                            cudaStream_t st) {
+  constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
+  auto kernel = softmax_bwd_ring_kernel<T, LOG, GROUP, VPT>;
+  static std::atomic<uint64_t> mask{0};
+  if (int e = set_smem_once_sm(kernel, mask)) return e;
+  kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, y, dx, M, static_cast<int>(N), p.stages, p.rpg,
+                                               device_status_ptr());
+  return check_cuda(cudaGetLastError());
+}
+
+template <typename TI, typename TO, bool LOG>
+int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_t inner, cudaStream_t st) {
+  const TI* x = static_cast<const TI*>(x_);
+  TO* y = static_cast<TO*>(y_);
+  const int forced = forced_path();
+  if (inner == 1) {
+    const int64_t M = outer;
+    if constexpr (std::is_same<TI, TO>::value && sizeof(TI) <= 4 && !std::is_same<TI, double>::value) {
+      if (forced != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
+        const DeviceInfo& di = device_info();
+        const RingPlan p = plan_ring(M, N, sizeof(TI), 1, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
+        if (p.ok) {
+          note_path("ring");
+          switch (p.group) {
+            case 32: return softmax_fwd_ring_launch<TI, LOG, 32>(p, x, y, M, N, st);
+            case 64: return softmax_fwd_ring_launch<TI, LOG, 64>(p, x, y, M, N, st);
+            case 128: return softmax_fwd_ring_launch<TI, LOG, 128>(p, x, y, M, N, st);
+            case 256: return softmax_fwd_ring_launch<TI, LOG, 256>(p, x, y, M, N, st);
+            default: return softmax_fwd_ring_launch<TI, LOG, 512>(p, x, y, M, N, st);
+          }
+        }
+      }
+    }
+    if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+    note_path("generic");
+    constexpr int V = 16 / sizeof(TI);  // vector width in elements, by the input type
+    const bool vec = N % V == 0 && is_aligned(x, 16) && is_aligned(y, V * sizeof(TO));
+    if (N <= 1024) {
+      const int grid = softmax_generic_grid(M, 8);
+      if (vec) softmax_fwd_generic_kernel<TI, TO, LOG, 32, V><<<grid, 256, 0, st>>>(x, y, M, N);
+      else softmax_fwd_generic_kernel<TI, TO, LOG, 32, 1><<<grid, 256, 0, st>>>(x, y, M, N);
+    } else {
+      const int grid = softmax_generic_grid(M, 1);
+      const int threads = N <= 8192 ? 256 : 1024;
+      if (vec) softmax_fwd_generic_kernel<TI, TO, LOG, 0, V><<<grid, threads, 0, st>>>(x, y, M, N);
+      else softmax_fwd_generic_kernel<TI, TO, LOG, 0, 1><<<grid, threads, 0, st>>>(x, y, M, N);
+    }
+    return check_cuda(cudaGetLastError());
+  }
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+  note_path("generic");
+  const int grid = softmax_generic_grid(outer * inner, 256);
+  softmax_fwd_spatial_kernel<TI, TO, LOG><<<grid, 256, 0, st>>>(x, y, outer, N, inner);
+  return check_cuda(cudaGetLastError());
+}
+
+template <typename TG, typename TO, bool LOG>
+int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer, int64_t N, int64_t inner,
+                      cudaStream_t st) {
+  const TG* dy = static_cast<const TG*>(dy_);
+  const TG* y = static_cast<const TG*>(y_);
+  TO* dx = static_cast<TO*>(dx_);
+  const int forced = forced_path();
+  if (inner == 1) {
+    const int64_t M = outer;
+    if constexpr (std::is_same<TG, TO>::value && sizeof(TG) <= 4 && !std::is_same<TG, double>::value) {
+      if (forced != B2N_PATH_GENERIC && is_aligned(dy, 16) && is_aligned(y, 16) && is_aligned(dx, 16) &&
+          N <= (1 << 20)) {
+        const DeviceInfo& di = device_info();
+        const RingPlan p = plan_ring(M, N, sizeof(TG), 2, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
+        if (p.ok) {
+          note_path("ring");
+          switch (p.group) {
+            case 32: return softmax_bwd_ring_launch<TG, LOG, 32>(p, dy, y, dx, M, N, st);
+            case 64: return softmax_bwd_ring_launch<TG, LOG, 64>(p, dy, y, dx, M, N, st);
+            case 128: return softmax_bwd_ring_launch<TG, LOG, 128>(p, dy, y, dx, M, N, st);
+            case 256: return softmax_bwd_ring_launch<TG, LOG, 256>(p, dy, y, dx, M, N, st);
+            default: return softmax_bwd_ring_launch<TG, LOG, 512>(p, dy, y, dx, M, N, st);
+          }
+        }
+      }
+    }
+    if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+    note_path("generic");
+    constexpr int V = (16 / sizeof(TG)) < (16 / sizeof(TO)) ? (16 / sizeof(TG)) : (16 / sizeof(TO));
+    const bool vec = N % V == 0 && is_aligned(dy, V * sizeof(TG)) && is_aligned(y, V * sizeof(TG)) &&
+                     is_aligned(dx, V * sizeof(TO));
+    if (N <= 1024) {
+      const int grid = softmax_generic_grid(M, 8);
+      if (vec) softmax_bwd_generic_kernel<TG, TO, LOG, 32, V><<<grid, 256, 0, st>>>(dy, y, dx, M, N);
+      else softmax_bwd_generic_kernel<TG, TO, LOG, 32, 1><<<grid, 256, 0, st>>>(dy, y, dx, M, N);
+    } else {
+      const int grid = softmax_generic_grid(M, 1);
+      const int threads = N <= 8192 ? 256 : 1024;
+      if (vec) softmax_bwd_generic_kernel<TG, TO, LOG, 0, V><<<grid, threads, 0, st>>>(dy, y, dx, M, N);
+      else softmax_bwd_generic_kernel<TG, TO, LOG, 0, 1><<<grid, threads, 0, st>>>(dy, y, dx, M, N);
+    }
+    return check_cuda(cudaGetLastError());
+  }
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+  note_path("generic");
+  const int grid = softmax_generic_grid(outer * inner, 256);
+  softmax_bwd_spatial_kernel<TG, TO, LOG><<<grid, 256, 0, st>>>(dy, y, dx, outer, N, inner);
+  return check_cuda(cudaGetLastError());
+}
+
+#define B2N_SOFTMAX_TYPED_DECL(NAME)                                                                         \
+  int softmax_fwd_##NAME(bool is_log, const void* x, void* y, int64_t outer, int64_t N, int64_t inner,       \
+                         cudaStream_t st);                                                                   \
+  int softmax_bwd_##NAME(bool is_log, const void* dy, const void* y, void* dx, int64_t outer, int64_t N,     \
+                         int64_t inner, cudaStream_t st);
+
+// fwd: TI -> TO.  bwd: (dy, y) of type BG -> dx of type BO.
+#define B2N_SOFTMAX_TYPED_DEFINE(NAME, TI, TO, BG, BO)                                                       \
+  int softmax_fwd_##NAME(bool is_log, const void* x, void* y, int64_t outer, int64_t N, int64_t inner,       \
+                         cudaStream_t st) {                                                                  \
+    return is_log ? softmax_fwd_typed<TI, TO, true>(x, y, outer, N, inner, st)                               \
+                  : softmax_fwd_typed<TI, TO, false>(x, y, outer, N, inner, st);                             \
+  }                                                                                                          \
+  int softmax_bwd_##NAME(bool is_log, const void* dy, const void* y, void* dx, int64_t outer, int64_t N,     \
+                         int64_t inner, cudaStream_t st) {                                                   \
+    return is_log ? softmax_bwd_typed<BG, BO, true>(dy, y, dx, outer, N, inner, st)                          \
+                  : softmax_bwd_typed<BG, BO, false>(dy, y, dx, outer, N, inner, st);                        \
+  }
+
+B2N_SOFTMAX_TYPED_DECL(f32)
+B2N_SOFTMAX_TYPED_DECL(f16)
+B2N_SOFTMAX_TYPED_DECL(bf16)
+B2N_SOFTMAX_TYPED_DECL(f64)
+B2N_SOFTMAX_TYPED_DECL(f16_f32)   // half_to_float: fwd f16 -> f32, bwd f32 grads -> f16 dx
+B2N_SOFTMAX_TYPED_DECL(bf16_f32)  // same with bf16
+
+}  // namespace b2n
