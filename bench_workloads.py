@@ -1,0 +1,265 @@
+"""The other BASELINE workloads for bench.py (--workload cfg1|cfg2|cfg3|cfg5).  Same conventions as
+bench.Cfg4LayerNorm: seeded synthetic inputs, preallocated outputs, algorithmic bytes = every tensor
+of the operators' signatures read or written once."""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+
+class _Simple:
+    """Shared plumbing: un-chunked end-to-end step (copy in, ATen ops, copy out)."""
+    e2e_chunks = 1
+    launches_per_step = 2
+
+    def make_e2e_state(self, rows, dev):
+        cpu = self.make_cpu_state(rows)
+        host_in = {k: cpu[k].pin_memory() for k in self.e2e_inputs}
+        return {"in": host_in, "out": None, "dev": dev}
+
+    def e2e_step(self, st, e2e, world):
+        dev_in = {k: v.to(e2e["dev"], non_blocking=True) for k, v in e2e["in"].items()}
+        outs = self.aten_step({**st, **dev_in}, world)
+        if e2e["out"] is None:
+            e2e["out"] = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for h, o in zip(e2e["out"], outs):
+            h.copy_(o, non_blocking=True)
+        return outs
+
+    def e2e_bytes(self, rows):
+        cpu_in = sum(self._nbytes(rows, k) for k in self.e2e_inputs)
+        return cpu_in, self._out_bytes(rows)
+
+
+class Cfg1LayerNormFwd(_Simple):
+    name, rows, N, cpu_sample_rows = "cfg1", 4096, 1024, 4096
+    e2e_inputs = ("x",)
+    launches_per_step = 1
+
+    def describe(self):
+        return "native_layer_norm fwd, fp32 [4096, 1024], eps 1e-5 (launch-bound: 33.6 MB)"
+
+    def bytes_per_rows(self, rows):
+        n = self.N
+        fwd = 2 * rows * n * 4 + 2 * n * 4 + 2 * rows * 4
+        return {"total": fwd, "layer_norm_fwd_ring": fwd}
+
+    def make_cpu_state(self, rows):
+        g = torch.Generator().manual_seed(1001)
+        n = self.N
+        return {"x": torch.randn((rows, n), generator=g), "gamma": torch.randn(n, generator=g) * 0.02 + 1.0,
+                "beta": torch.randn(n, generator=g) * 0.02}
+
+    def make_device_state(self, rows, dev, seed):
+        # 16 rotating input/output sets (0.5 GB) so back-to-back launches never find their rows in L2
+        st = {k: v.to(dev) for k, v in self.make_cpu_state(rows).items()}
+        st["xs"] = [st["x"].clone() for _ in range(16)]
+        st["ys"] = [torch.empty_like(st["x"]) for _ in range(16)]
+        st["mean"] = torch.empty(rows, device=dev)
+        st["rstd"] = torch.empty(rows, device=dev)
+        st["i"] = 0
+        return st
+
+    def step(self, capi, st, world):
+        i = st["i"] = (st["i"] + 1) % 16
+        capi.native_layer_norm(st["xs"][i], [self.N], st["gamma"], st["beta"], 1e-5, out=(st["ys"][i], st["mean"], st["rstd"]))
+
+    def cpu_step(self, cpu):
+        return torch.ops.aten.native_layer_norm(cpu["x"], [self.N], cpu["gamma"], cpu["beta"], 1e-5)
+
+    def aten_step(self, st, world):
+        return torch.ops.aten.native_layer_norm(st["x"], [self.N], st["gamma"], st["beta"], 1e-5)
+
+    def _nbytes(self, rows, k):
+        return rows * self.N * 4
+
+    def _out_bytes(self, rows):
+        return rows * self.N * 4 + 2 * rows * 4
+
+
+class Cfg2RmsNorm(_Simple):
+    name, rows, N, cpu_sample_rows = "cfg2", 8192, 4096, 8192
+    e2e_inputs = ("x", "dy")
+    launches_per_step = 3
+
+    def describe(self):
+        return "_fused_rms_norm fwd + _fused_rms_norm_backward (dx, dweight), bf16 [8192, 4096], fp32 weight, eps 1e-6"
+
+    def bytes_per_rows(self, rows):
+        n = self.N
+        fwd = 2 * rows * n * 2 + n * 4 + rows * 4
+        bwd = 3 * rows * n * 2 + rows * 4 + 2 * n * 4
+        return {"total": fwd + bwd, "rms_norm_fwd_ring": fwd, "rms_norm_bwd_ring": bwd}
+
+    def make_cpu_state(self, rows):
+        g = torch.Generator().manual_seed(2001)
+        n = self.N
+        return {"x": torch.randn((rows, n), generator=g).to(torch.bfloat16),
+                "dy": torch.randn((rows, n), generator=g).to(torch.bfloat16),
+                "weight": torch.randn(n, generator=g) * 0.02 + 1.0}
+
+    def make_device_state(self, rows, dev, seed):
+        from b200norm import BF16, F32, load_library
+        st = {k: v.to(dev) for k, v in self.make_cpu_state(rows).items()}
+        # 4 rotating sets: 4 x 4 x 64 MiB = 1 GiB working set, far beyond L2
+        st["sets"] = [{"x": st["x"].clone(), "dy": st["dy"].clone(), "y": torch.empty_like(st["x"]),
+                       "dx": torch.empty_like(st["x"])} for _ in range(4)]
+        st["rstd"] = torch.empty(rows, device=dev)
+        st["wgrad"] = torch.zeros((2, self.N), device=dev)
+        nbytes = load_library().b2n_norm_bwd_workspace_bytes(rows, self.N, BF16, F32, 1)
+        st["ws"] = torch.empty(max(nbytes, 1), device=dev, dtype=torch.uint8)
+        st["i"] = 0
+        return st
+
+    def step(self, capi, st, world):
+        i = st["i"] = (st["i"] + 1) % 4
+        s, n = st["sets"][i], self.N
+        capi._fused_rms_norm(s["x"], [n], st["weight"], 1e-6, out=(s["y"], st["rstd"]))
+        capi._fused_rms_norm_backward(s["dy"], s["x"], [n], st["rstd"], st["weight"], (True, True),
+                                      out=(s["dx"], st["wgrad"][0]), workspace=st["ws"])
+        if world > 1:
+            dist.all_reduce(st["wgrad"])
+
+    def cpu_step(self, cpu):
+        # no CPU kernel exists for _fused_rms_norm(_backward): autograd through the CPU composite
+        x = cpu["x"].float().requires_grad_(True)
+        w = cpu["weight"].clone().requires_grad_(True)
+        y = torch.nn.functional.rms_norm(x, [self.N], w, 1e-6)
+        return torch.autograd.grad(y, [x, w], cpu["dy"].float())
+
+    def aten_step(self, st, world):
+        n = self.N
+        y, rstd = torch.ops.aten._fused_rms_norm(st["x"], [n], st["weight"], 1e-6)
+        dx, dw = torch.ops.aten._fused_rms_norm_backward(st["dy"], st["x"], [n], rstd, st["weight"], [True, True])
+        if world > 1:
+            dist.all_reduce(dw)
+        return y, dx, dw
+
+    def _nbytes(self, rows, k):
+        return rows * self.N * 2
+
+    def _out_bytes(self, rows):
+        return 2 * rows * self.N * 2 + self.N * 4
+
+
+class Cfg3Softmax(_Simple):
+    name, T, cpu_sample_rows = "cfg3", 2048, 8192
+    rows = 8 * 32 * 2048
+    e2e_inputs = ("s", "g")
+
+    def describe(self):
+        return ("_softmax + _softmax_backward_data over the last dim, bf16 [8, 32, 2048, 2048] causal scores "
+                "(strict upper triangle -inf, applied before the op)")
+
+    def bytes_per_rows(self, rows):
+        t = self.T
+        return {"total": 5 * rows * t * 2, "softmax_fwd_ring": 2 * rows * t * 2, "softmax_bwd_ring": 3 * rows * t * 2}
+
+    def _make(self, rows, dev, gen):
+        t = self.T
+        s = torch.randn((rows, t), generator=gen, device=dev) / math.sqrt(128)
+        r = torch.arange(rows, device=dev).remainder(t).view(-1, 1)
+        s.masked_fill_(torch.arange(t, device=dev).view(1, -1) > r, float("-inf"))
+        g = torch.randn((rows, t), generator=gen, device=dev).to(torch.bfloat16)
+        return s.to(torch.bfloat16), g
+
+    def make_cpu_state(self, rows):
+        s, g = self._make(rows, torch.device("cpu"), torch.Generator().manual_seed(3001))
+        return {"s": s, "g": g}
+
+    def make_device_state(self, rows, dev, seed):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        st = {}
+        parts = [self._make(min(65536, rows - r), dev, gen) for r in range(0, rows, 65536)]
+        st["s"] = torch.cat([p[0] for p in parts])
+        st["g"] = torch.cat([p[1] for p in parts])
+        del parts
+        st["p"] = torch.empty_like(st["s"])
+        st["dx"] = torch.empty_like(st["s"])
+        return st
+
+    def step(self, capi, st, world):
+        capi._softmax(st["s"], -1, False, out=st["p"])
+        capi._softmax_backward_data(st["g"], st["p"], -1, torch.bfloat16, out=st["dx"])
+
+    def cpu_step(self, cpu):
+        p = torch.ops.aten._softmax(cpu["s"], -1, False)
+        return torch.ops.aten._softmax_backward_data(cpu["g"], p, -1, torch.bfloat16)
+
+    def aten_step(self, st, world):
+        p = torch.ops.aten._softmax(st["s"], -1, False)
+        return p, torch.ops.aten._softmax_backward_data(st["g"], p, -1, torch.bfloat16)
+
+    def _nbytes(self, rows, k):
+        return rows * self.T * 2
+
+    def _out_bytes(self, rows):
+        return 2 * rows * self.T * 2
+
+
+class Cfg5CrossEntropy(_Simple):
+    name, rows, V, cpu_sample_rows = "cfg5", 16384, 128256, 1024
+    e2e_inputs = ("logits", "target")
+    launches_per_step = 6
+
+    def describe(self):
+        return ("_log_softmax + nll_loss_forward(mean) + nll_loss_backward + _log_softmax_backward_data, "
+                "bf16 logits [16384, 128256] ~N(0,2), int64 targets; loss sum/count all-reduced")
+
+    def bytes_per_rows(self, rows):
+        v = self.V
+        fwd, bwd = 2 * rows * v * 2, 3 * rows * v * 2
+        return {"total": fwd + bwd + rows * 40, "log_softmax_fwd_ring": fwd, "log_softmax_bwd_ring": bwd,
+                "log_softmax_fwd_generic": fwd, "log_softmax_bwd_generic": bwd,
+                "log_softmax_fwd_cluster": fwd, "log_softmax_bwd_cluster": bwd}
+
+    def make_cpu_state(self, rows):
+        g = torch.Generator().manual_seed(5001)
+        return {"logits": (torch.randn((rows, self.V), generator=g) * 2.0).to(torch.bfloat16),
+                "target": torch.randint(0, self.V, (rows,), generator=g)}
+
+    def make_device_state(self, rows, dev, seed):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        st = {"logits": torch.empty((rows, self.V), device=dev, dtype=torch.bfloat16)}
+        for r in range(0, rows, 2048):
+            k = min(2048, rows - r)
+            st["logits"][r:r + k] = (torch.randn((k, self.V), generator=gen, device=dev) * 2.0).to(torch.bfloat16)
+        st["target"] = torch.randint(0, self.V, (rows,), generator=gen, device=dev)
+        st["logp"] = torch.empty_like(st["logits"])
+        st["grad_logp"] = torch.empty_like(st["logits"])
+        st["dlogits"] = torch.empty_like(st["logits"])
+        st["one"] = torch.ones((), device=dev, dtype=torch.bfloat16)
+        return st
+
+    def step(self, capi, st, world):
+        logp = capi._log_softmax(st["logits"], -1, False, out=st["logp"])
+        _, _, sums = capi.nll_loss_forward(logp, st["target"], None, 2, -100, return_sums=True)
+        if world > 1:
+            dist.all_reduce(sums)
+        st["loss"] = sums[0] / sums[1]
+        tw = sums[1].to(torch.bfloat16)
+        capi.nll_loss_backward(st["one"], logp, st["target"], None, 1, -100, tw, out=st["grad_logp"])
+        capi._log_softmax_backward_data(st["grad_logp"], logp, -1, torch.bfloat16, out=st["dlogits"])
+
+    def cpu_step(self, cpu):
+        logp = torch.ops.aten._log_softmax(cpu["logits"], -1, False)
+        out, tw = torch.ops.aten.nll_loss_forward(logp, cpu["target"], None, 1, -100)
+        g = torch.ops.aten.nll_loss_backward(torch.ones((), dtype=torch.bfloat16), logp, cpu["target"], None, 1, -100, tw)
+        return torch.ops.aten._log_softmax_backward_data(g, logp, -1, torch.bfloat16)
+
+    def aten_step(self, st, world):
+        logp = torch.ops.aten._log_softmax(st["logits"], -1, False)
+        out, tw = torch.ops.aten.nll_loss_forward(logp, st["target"], None, 1, -100)
+        g = torch.ops.aten.nll_loss_backward(torch.ones_like(out), logp, st["target"], None, 1, -100, tw)
+        return out, torch.ops.aten._log_softmax_backward_data(g, logp, -1, torch.bfloat16)
+
+    def _nbytes(self, rows, k):
+        return rows * self.V * 2 if k == "logits" else rows * 8
+
+    def _out_bytes(self, rows):
+        return rows * self.V * 2 + 2
+
+
+EXTRA = {"cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg5": Cfg5CrossEntropy}

@@ -67,6 +67,15 @@ const char* b2n_last_path(void);
  * 0, or the b2n_status recorded by a kernel (B2N_ERR_TIMEOUT, B2N_ERR_TARGET_RANGE). */
 int b2n_device_status(void* stream);
 
+/* Number of kernels this thread has launched through the library since it was loaded. */
+unsigned long long b2n_launch_count(void);
+/* Measurement aid.  Between b2n_profile_begin() and b2n_profile_end() every main kernel launched
+ * from this thread (not the small fold / scatter kernels) is bracketed by a pair of CUDA events on
+ * its stream.  b2n_profile_end synchronises on them and writes one line per kernel name,
+ * "name launches total_milliseconds\n", into report (NUL-terminated, truncated to cap). */
+int b2n_profile_begin(void);
+int b2n_profile_end(char* report, size_t cap);
+
 /* ---- layer norm / RMS norm ------------------------------------------------------------------
  * x, y: [M, N] of x_dtype.  gamma, beta: [N] of w_dtype or NULL (w_dtype == x_dtype or B2N_F32).
  * mean, rstd: [M] of the accumulate type (float; double when x_dtype == B2N_F64).

@@ -18,11 +18,15 @@ RESTATE_SO = OUT_DIR / "librestate.so"
 def build_restate(force: bool = False) -> Path:
     src = HERE / "restate.c"
     OUT_DIR.mkdir(exist_ok=True)
-    if force or not RESTATE_SO.exists() or RESTATE_SO.stat().st_mtime < src.stat().st_mtime:
+    import hashlib
+    stamp = OUT_DIR / "librestate.stamp"
+    digest = hashlib.sha256(src.read_bytes()).hexdigest()
+    if force or not RESTATE_SO.exists() or not stamp.exists() or stamp.read_text().strip() != digest:
         cmd = ["gcc", "-O2", "-fPIC", "-shared", "-ffp-contract=off", "-std=c11", str(src), "-o", str(RESTATE_SO), "-lm"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError("oracle build failed:\n" + proc.stdout + proc.stderr)
+        stamp.write_text(digest)
     return RESTATE_SO
 
 

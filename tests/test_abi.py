@@ -1,0 +1,76 @@
+"""The C ABI: the library loads without a GPU, exports every symbol the header declares, and its
+argument validation answers without touching a device."""
+import ctypes
+import re
+from pathlib import Path
+
+import b200norm
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "b200norm.h"
+
+
+def declared_functions():
+    text = HEADER.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b2n_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for required in ("b2n_layer_norm_fwd", "b2n_layer_norm_bwd", "b2n_rms_norm_fwd", "b2n_rms_norm_bwd",
+                     "b2n_softmax_fwd", "b2n_softmax_bwd", "b2n_nll_loss_fwd", "b2n_nll_loss_bwd",
+                     "b2n_norm_bwd_workspace_bytes", "b2n_strerror", "b2n_abi_version"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(str(b200norm.LIB_PATH))
+    missing = [n for n in declared_functions() if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_abi_version_and_strerror():
+    lib = b200norm.load_library()
+    assert lib.b2n_abi_version() == b200norm.ABI_VERSION
+    assert lib.b2n_strerror(0) == b"ok"
+    for code in range(-7, 0):
+        assert lib.b2n_strerror(code) not in (b"ok", b"unknown status")
+    assert lib.b2n_strerror(-99) == b"unknown status"
+
+
+def test_argument_validation_needs_no_device():
+    lib = b200norm.load_library()
+    # negative sizes and bad enums are rejected before any CUDA call
+    assert lib.b2n_layer_norm_fwd(None, None, None, None, None, None, -1, 8, 1e-5, 0, 0, None) == b200norm.ERR_BAD_ARG
+    assert lib.b2n_layer_norm_fwd(None, None, None, None, None, None, 4, 8, 1e-5, 9, 0, None) == b200norm.ERR_BAD_ARG
+    assert lib.b2n_softmax_fwd(None, None, 4, 8, 1, 0, 0, 0, None) == b200norm.ERR_BAD_ARG  # null pointers
+    # empty problems are a successful no-op
+    assert lib.b2n_layer_norm_fwd(None, None, None, None, None, None, 0, 8, 1e-5, 0, 0, None) == b200norm.OK
+    assert lib.b2n_softmax_fwd(None, None, 0, 8, 1, 0, 0, 0, None) == b200norm.OK
+    assert lib.b2n_nll_loss_fwd(None, None, None, None, None, None, None, 0, 4, 8, 5, -100, 0, 0, None) == b200norm.ERR_BAD_ARG
+
+
+def test_path_forcing_round_trips():
+    lib = b200norm.load_library()
+    prev = lib.b2n_set_path(b200norm.PATH_RING)
+    assert lib.b2n_set_path(prev) == b200norm.PATH_RING
+    assert lib.b2n_set_path(77) == prev  # out-of-range values are ignored
+    assert lib.b2n_set_path(prev) == prev
+
+
+def test_aten_registration_is_built():
+    assert b200norm.ATEN_LIB_PATH.exists()
+
+
+def test_product_does_not_import_the_oracle():
+    # the oracle is test infrastructure; nothing under the package or csrc may reference it
+    pkg = ROOT / "torch-xpu-ops_b200"
+    offenders = []
+    for path in list(pkg.rglob("*.py")) + list(pkg.rglob("*.cu")) + list(pkg.rglob("*.cuh")) + list(pkg.rglob("*.cpp")) + list(pkg.rglob("*.h")):
+        if "build" in path.parts:
+            continue
+        text = path.read_text()
+        if re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M) or "oracle/" in text:
+            offenders.append(str(path))
+    assert not offenders, offenders

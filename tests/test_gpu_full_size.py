@@ -1,0 +1,149 @@
+"""The five workloads at their full sizes.  A CPU oracle over gigabytes would take minutes, so each
+case checks (a) sampled rows bit-for-bit (<= 1 ulp / 1e-5) against the oracle and (b) properties that
+hold for every row: softmax rows sum to one and masked entries are exactly zero, log-softmax rows have
+zero log-sum-exp, weight gradients are additive over row blocks (what row sharding relies on), the
+loss equals the mean of the gathered log-probabilities."""
+import math
+
+import pytest
+import torch
+
+import b200norm
+from b200norm import capi
+from oracle import aten_oracle as ao
+
+from gpu_util import DEV
+
+pytestmark = pytest.mark.gpu
+
+
+def sample_rows(m, k=48, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.randperm(m, generator=g)[:k].sort().values
+    idx[0], idx[-1] = 0, m - 1
+    return idx
+
+
+def test_config1_layer_norm_fp32_4096x1024_full_compare():
+    M, N = 4096, 1024
+    x = ao.randn((M, N), 1001)
+    g, b = ao.randn((N,), 1002, mean=1.0, std=0.02), ao.randn((N,), 1003, std=0.02)
+    y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5)
+    assert capi.last_path() == "ring"
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+    assert ao.fp32_err(y, ry) <= 1.0
+    assert float((mean.cpu() - rmean).abs().max()) <= 1e-6
+    assert float(((rstd.cpu() - rrstd) / rrstd).abs().max()) <= 1e-5
+
+
+def test_config2_rms_norm_bf16_8192x4096_full_compare():
+    M, N = 8192, 4096
+    x, dy = ao.randn((M, N), 2001, torch.bfloat16), ao.randn((M, N), 2004, torch.bfloat16)
+    w = ao.randn((N,), 2002, mean=1.0, std=0.02)
+    y, rstd = capi._fused_rms_norm(x.to(DEV), [N], w.to(DEV), 1e-6)
+    assert capi.last_path() == "ring"
+    dx, dw = capi._fused_rms_norm_backward(dy.to(DEV), x.to(DEV), [N], rstd, w.to(DEV))
+    assert capi.last_path() == "ring"
+    ry, rrstd = ao.rms_norm_fwd(x, [N], w, 1e-6)
+    rdx, rdw = ao.rms_norm_bwd(dy, x, [N], w, 1e-6)
+    assert ao.ulp_distance(y.cpu(), ry) <= 1 and ao.ulp_distance(dx.cpu(), rdx) <= 1
+    terms = dy.double() * x.double() * rrstd.double()
+    err = ((dw.cpu().double() - terms.sum(0)).abs() / terms.abs().sum(0)).max()
+    assert float(err) <= 1e-6, float(err)
+    assert torch.allclose(dw.cpu(), rdw, rtol=1e-4, atol=1e-3)
+
+
+def test_config3_causal_softmax_bf16_8x32x2048x2048():
+    B, H, T = 8, 32, 2048
+    gen = torch.Generator(device=DEV).manual_seed(3001)
+    s = (torch.randn((B, H, T, T), generator=gen, device=DEV, dtype=torch.float32) / math.sqrt(128)).to(torch.bfloat16)
+    mask = torch.ones(T, T, dtype=torch.bool, device=DEV).triu(1)
+    s.masked_fill_(mask, float("-inf"))
+    p = capi._softmax(s, -1, False)
+    assert capi.last_path() == "ring"
+    flat_s, flat_p = s.view(-1, T), p.view(-1, T)
+    # every row: masked entries exactly zero, the rest sums to one within the bf16 rounding of T terms
+    assert float(p.masked_select(mask.expand_as(p)).abs().max()) == 0.0
+    sums = flat_p.float().sum(-1)
+    assert float((sums - 1).abs().max()) <= 4e-3
+    idx = sample_rows(flat_s.shape[0])
+    assert ao.ulp_distance(flat_p[idx.to(DEV)].cpu(), ao.softmax_fwd(flat_s[idx.to(DEV)].cpu(), -1, False)) <= 1
+    g = torch.randn((B, H, T, T), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    dx = capi._softmax_backward_data(g, p, -1, torch.bfloat16)
+    assert capi.last_path() == "ring"
+    flat_g, flat_dx = g.view(-1, T), dx.view(-1, T)
+    ref = ao.softmax_bwd(flat_g[idx.to(DEV)].cpu(), flat_p[idx.to(DEV)].cpu(), -1, False, torch.bfloat16)
+    assert ao.ulp_distance(flat_dx[idx.to(DEV)].cpu(), ref) <= 1
+    # softmax gradients sum to ~0 along the row, and are exactly zero where p is zero
+    assert float(dx.masked_select(mask.expand_as(dx)).abs().max()) == 0.0
+    assert float(flat_dx.float().sum(-1).abs().max()) <= 5e-2
+    assert capi.device_status() == 0
+
+
+def test_config4_layer_norm_bf16_65536x8192():
+    M, N = 65536, 8192
+    gen = torch.Generator(device=DEV).manual_seed(4001)
+    x = torch.randn((M, N), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    dy = torch.randn((M, N), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    g, b = ao.randn((N,), 4002, mean=1.0, std=0.02).to(DEV), ao.randn((N,), 4003, std=0.02).to(DEV)
+    y, mean, rstd = capi.native_layer_norm(x, [N], g, b, 1e-5)
+    assert capi.last_path() == "ring"
+    dx, dg, db = capi.native_layer_norm_backward(dy, x, [N], mean, rstd, g, b)
+    assert capi.last_path() == "ring"
+    idx = sample_rows(M).to(DEV)
+    ry, rmean, rrstd = ao.layer_norm_fwd(x[idx].cpu(), [N], g.cpu(), b.cpu(), 1e-5)
+    assert ao.ulp_distance(y[idx].cpu(), ry) <= 1
+    assert float((mean[idx].cpu() - rmean).abs().max()) <= 1e-6
+    assert float(((rstd[idx].cpu() - rrstd) / rrstd).abs().max()) <= 1e-5
+    rdx, _, _ = ao.layer_norm_bwd(dy[idx].cpu(), x[idx].cpu(), [N], rmean, rrstd, g.cpu(), b.cpu())
+    assert ao.ulp_distance(dx[idx].cpu(), rdx) <= 1
+    # every row: the normalised output before the affine map has zero mean and unit variance
+    z = (y[:4096].float() - b) / g
+    assert float(z.mean(-1).abs().max()) <= 2e-3 and float((z.var(-1, unbiased=False) - 1).abs().max()) <= 1e-2
+    # weight gradients: additive over row blocks (what row sharding relies on) ...
+    parts = []
+    for k in range(4):
+        sl = slice(k * M // 4, (k + 1) * M // 4)
+        _, pg, pb = capi.native_layer_norm_backward(dy[sl], x[sl], [N], mean[sl], rstd[sl], g, b, (False, True, True))
+        parts.append(torch.stack([pg, pb]).double())
+    total = sum(parts)
+    l1 = (dy[:, :64].double().abs()).sum(0)  # L1 scale of the dbeta terms on a column sample
+    assert float(((total[1, :64] - db[:64].double()).abs() / l1).max()) <= 1e-6
+    assert torch.allclose(total[0].float(), dg, rtol=1e-3, atol=0.5)
+    # ... and dbeta equals an fp64 column sum of dy on a column sample
+    ref_db = dy[:, :64].double().sum(0)
+    assert float(((db[:64].double() - ref_db).abs() / l1).max()) <= 1e-6
+    xh = (x[:, :64].double() - mean.double()) * rstd.double()
+    terms = dy[:, :64].double() * xh
+    assert float(((dg[:64].double() - terms.sum(0)).abs() / terms.abs().sum(0)).max()) <= 1e-6
+    assert capi.device_status() == 0
+
+
+def test_config5_log_softmax_nll_bf16_16384x128256():
+    M, V = 16384, 128256
+    gen = torch.Generator(device=DEV).manual_seed(5001)
+    logits = torch.empty((M, V), device=DEV, dtype=torch.bfloat16)
+    for k in range(0, M, 2048):  # fp32 normal draws in slabs keep the transient under 1.1 GB
+        logits[k:k + 2048] = (torch.randn((2048, V), generator=gen, device=DEV) * 2.0).to(torch.bfloat16)
+    t = ao.randint(V, (M,), 5002).to(DEV)
+    logp = capi._log_softmax(logits, -1, False)
+    idx = sample_rows(M, 24).to(DEV)
+    assert ao.ulp_distance(logp[idx].cpu(), ao.softmax_fwd(logits[idx].cpu(), -1, True)) <= 1
+    # every row: log-sum-exp of the output is zero up to the bf16 rounding of the entries
+    lse = torch.cat([torch.logsumexp(logp[k:k + 1024].float(), -1) for k in range(0, M, 1024)])
+    assert float(lse.abs().max()) <= 2e-2
+    out, tw, sums = capi.nll_loss_forward(logp, t, None, 1, -100, return_sums=True)
+    picked = logp.gather(1, t.view(-1, 1)).double().cpu()
+    assert float(tw) == M
+    assert math.isclose(float(sums[0]), float(-picked.sum()), rel_tol=1e-6)
+    assert ao.ulp_distance(out.cpu().reshape(1), torch.tensor([-picked.mean()]).to(torch.bfloat16)) <= 1
+    del logits
+    grad_logp = capi.nll_loss_backward(torch.ones((), device=DEV, dtype=torch.bfloat16), logp, t, None, 1, -100, tw)
+    assert float(grad_logp.gather(1, t.view(-1, 1)).float().mean()) == pytest.approx(-1.0 / M, rel=1e-2)
+    dlogits = capi._log_softmax_backward_data(grad_logp, logp, -1, torch.bfloat16)
+    ref = ao.softmax_bwd(grad_logp[idx].cpu(), logp[idx].cpu(), -1, True, torch.bfloat16)
+    assert ao.ulp_distance(dlogits[idx].cpu(), ref) <= 1
+    # rows of the cross-entropy gradient sum to ~0
+    rs = torch.cat([dlogits[k:k + 1024].float().sum(-1) for k in range(0, M, 1024)])
+    assert float(rs.abs().max()) <= 1e-5
+    assert capi.device_status() == 0

@@ -1,0 +1,271 @@
+"""Layer norm / RMS norm parity: CUDA kernels through the C ABI vs the CPU oracle.
+
+Tolerances (stated by the task): fp32 outputs |a-b| <= 1e-5*|b| + 1e-6*max(1, rms(b)); 16-bit outputs
+within 1 ulp of the fp32-accumulated reference (CPU ATen on fp32 upcasts, rounded once); mean/rstd
+relative 1e-5; fp32 weight-gradient sums within 1e-6 of the L1 norm of their terms from an fp64 sum.
+"""
+import math
+
+import pytest
+import torch
+
+import b200norm
+from b200norm import capi
+from oracle import aten_oracle as ao
+from oracle import restate
+
+from gpu_util import DEV, forced_path, guarded_empty, misaligned, ring_eligible
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 1), (3, 5), (7, 128), (33, 130), (257, 1024), (64, 4096), (19, 8192), (5, 16384), (3, 40000)]
+DTYPES = [(torch.float32, torch.float32), (torch.bfloat16, torch.float32), (torch.bfloat16, torch.bfloat16),
+          (torch.float16, torch.float16), (torch.float16, torch.float32)]
+PATHS = [b200norm.PATH_AUTO, b200norm.PATH_GENERIC]
+
+
+def check_out(a, ref, what):
+    if ref.dtype in (torch.bfloat16, torch.float16):
+        d = ao.ulp_distance(a.cpu(), ref)
+        assert d <= 1, f"{what}: {d} ulp"
+    else:
+        e = ao.fp32_err(a, ref)
+        assert e <= 1.0, f"{what}: error {e:.3f} x tolerance"
+
+
+def check_stat(a, ref, what):
+    a, ref = a.cpu().double().reshape(-1), ref.double().reshape(-1)
+    err = ((a - ref).abs() / (1e-5 * ref.abs() + 1e-6)).max()
+    assert err <= 1.0, f"{what}: {float(err):.3f} x tolerance"
+
+
+def check_wgrad(a, terms, what):
+    """a: kernel result [N]; terms: fp64 [M, N] summands.  Error relative to the L1 norm of the terms."""
+    ref = terms.sum(0)
+    l1 = terms.abs().sum(0).clamp_min(1e-30)
+    if a.dtype in (torch.bfloat16, torch.float16):
+        assert ao.ulp_distance(a.cpu(), ref.to(a.dtype)) <= 1 or torch.allclose(a.cpu().double(), ref, rtol=2e-2, atol=1e-3), what
+    else:
+        err = ((a.cpu().double() - ref).abs() / l1).max()
+        assert err <= 1e-6, f"{what}: {float(err):.3e} of L1"
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("dt,wdt", DTYPES)
+@pytest.mark.parametrize("M,N", SHAPES)
+def test_layer_norm_fwd_bwd(M, N, dt, wdt, path):
+    x = ao.randn((M, N), 100 + N, dt)
+    g = ao.randn((N,), 101, wdt, 1.0, 0.02)
+    b = ao.randn((N,), 102, wdt, 0.0, 0.02)
+    dy = ao.randn((M, N), 103, dt)
+    with forced_path(path):
+        y_buf, y_chk = guarded_empty((M, N), dt)
+        mean_buf, mean_chk = guarded_empty((M,), torch.float32)
+        rstd_buf, rstd_chk = guarded_empty((M,), torch.float32)
+        y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5, out=(y_buf, mean_buf, rstd_buf))
+        used = capi.last_path()
+        dx_buf, dx_chk = guarded_empty((M, N), dt)
+        dg_buf, dg_chk = guarded_empty((N,), wdt)
+        db_buf, db_chk = guarded_empty((N,), wdt)
+        dx, dg, db = capi.native_layer_norm_backward(dy.to(DEV), x.to(DEV), [N], mean, rstd, g.to(DEV), b.to(DEV),
+                                                     out=(dx_buf, dg_buf, db_buf))
+    torch.cuda.synchronize()
+    for chk in (y_chk, mean_chk, rstd_chk, dx_chk, dg_chk, db_chk):
+        chk()
+    if path == b200norm.PATH_AUTO and ring_eligible(N, dt, 32):
+        assert used == "ring"
+    if path == b200norm.PATH_GENERIC:
+        assert used == "generic"
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+    check_out(y, ry, "y")
+    check_stat(mean, rmean, "mean")
+    check_stat(rstd, rrstd, "rstd")
+    # backward against the oracle evaluated at OUR mean/rstd inputs == the oracle's (they agree to 1e-5)
+    rdx, _, _ = ao.layer_norm_bwd(dy, x, [N], rmean, rrstd, g, b)
+    check_out(dx, rdx, "dx")
+    xh = (x.double() - rmean.double().reshape(-1, 1)) * rrstd.double().reshape(-1, 1)
+    check_wgrad(dg, dy.double() * xh, "dgamma")
+    check_wgrad(db, dy.double(), "dbeta")
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("dt,wdt", DTYPES)
+@pytest.mark.parametrize("M,N", SHAPES)
+def test_rms_norm_fwd_bwd(M, N, dt, wdt, path):
+    x = ao.randn((M, N), 200 + N, dt)
+    w = ao.randn((N,), 201, wdt, 1.0, 0.02)
+    dy = ao.randn((M, N), 202, dt)
+    with forced_path(path):
+        y, rstd = capi._fused_rms_norm(x.to(DEV), [N], w.to(DEV), 1e-6)
+        dx_buf, dx_chk = guarded_empty((M, N), dt)
+        dw_buf, dw_chk = guarded_empty((N,), wdt)
+        dx, dw = capi._fused_rms_norm_backward(dy.to(DEV), x.to(DEV), [N], rstd, w.to(DEV), out=(dx_buf, dw_buf))
+    torch.cuda.synchronize()
+    dx_chk(); dw_chk()
+    ry, rrstd = ao.rms_norm_fwd(x, [N], w, 1e-6)
+    check_out(y, ry, "y")
+    check_stat(rstd, rrstd, "rstd")
+    rdx, rdw = ao.rms_norm_bwd(dy, x, [N], w, 1e-6)
+    check_out(dx, rdx, "dx")
+    check_wgrad(dw, dy.double() * x.double() * rrstd.double().reshape(-1, 1), "dweight")
+    # the restated closed form of the reference's rms backward agrees too (no CPU ATen kernel exists)
+    cdx, cdw, _ = restate.norm_bwd(dy, x, None, rrstd, w, rms=True)
+    if dt == torch.float32:
+        assert ao.fp32_err(dx, cdx) <= 4.0
+    else:
+        assert ao.ulp_distance(dx.cpu(), cdx.to(dt)) <= 1
+
+
+@pytest.mark.parametrize("has_w,has_b", [(False, False), (True, False), (False, True)])
+@pytest.mark.parametrize("N", [5, 128, 2048])
+def test_layer_norm_optional_affine(N, has_w, has_b):
+    M = 21
+    x = ao.randn((M, N), 300, torch.float32)
+    g = ao.randn((N,), 301, torch.float32, 1.0, 0.1) if has_w else None
+    b = ao.randn((N,), 302, torch.float32) if has_b else None
+    dy = ao.randn((M, N), 303, torch.float32)
+    dev = lambda t: None if t is None else t.to(DEV)
+    y, mean, rstd = capi.native_layer_norm(dev(x), [N], dev(g), dev(b), 1e-5)
+    dx, dg, db = capi.native_layer_norm_backward(dev(dy), dev(x), [N], mean, rstd, dev(g), dev(b))
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+    rdx, rdg, rdb = ao.layer_norm_bwd(dy, x, [N], rmean, rrstd, g, b)
+    check_out(y, ry, "y"); check_out(dx, rdx, "dx")
+    assert (dg is None) == (g is None) and (db is None) == (b is None)
+    if g is not None:
+        assert torch.allclose(dg.cpu(), rdg, rtol=1e-4, atol=1e-5)
+    if b is not None:
+        assert torch.allclose(db.cpu(), rdb, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("mask", [(True, False, False), (False, True, True), (True, True, False), (False, False, True)])
+def test_layer_norm_backward_masks(mask):
+    M, N = 40, 1024
+    x, dy = ao.randn((M, N), 310, torch.bfloat16), ao.randn((M, N), 311, torch.bfloat16)
+    g, b = ao.randn((N,), 312, torch.float32, 1.0, 0.02), ao.randn((N,), 313, torch.float32)
+    y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5)
+    dx, dg, db = capi.native_layer_norm_backward(dy.to(DEV), x.to(DEV), [N], mean, rstd, g.to(DEV), b.to(DEV), mask)
+    rdx, rdg, rdb = ao.layer_norm_bwd(dy, x, [N], mean.cpu(), rstd.cpu(), g, b)
+    assert (dx is not None) == mask[0] and (dg is not None) == mask[1] and (db is not None) == mask[2]
+    if dx is not None:
+        assert ao.ulp_distance(dx.cpu(), rdx) <= 1
+    if dg is not None:
+        assert torch.allclose(dg.cpu(), rdg, rtol=1e-4, atol=1e-4)
+    if db is not None:
+        assert torch.allclose(db.cpu(), rdb, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [128, 1000])
+def test_unaligned_pointers_take_the_generic_kernels(N, dt):
+    M = 17
+    x, dy = ao.randn((M, N), 320, dt), ao.randn((M, N), 321, dt)
+    g, b = ao.randn((N,), 322, dt, 1.0, 0.02), ao.randn((N,), 323, dt)
+    xd, dyd = misaligned(x.to(DEV)), misaligned(dy.to(DEV))
+    assert xd.data_ptr() % 16 != 0
+    y, mean, rstd = capi.native_layer_norm(xd, [N], g.to(DEV), b.to(DEV), 1e-5)
+    assert capi.last_path() == "generic"
+    dx, dg, db = capi.native_layer_norm_backward(dyd, xd, [N], mean, rstd, g.to(DEV), b.to(DEV))
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+    rdx, _, _ = ao.layer_norm_bwd(dy, x, [N], rmean, rrstd, g, b)
+    check_out(y, ry, "y"); check_out(dx, rdx, "dx")
+
+
+def test_float64_goes_through_the_generic_kernels():
+    M, N = 9, 77
+    x, dy = ao.randn((M, N), 330).double(), ao.randn((M, N), 331).double()
+    g, b = ao.randn((N,), 332).double(), ao.randn((N,), 333).double()
+    y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5)
+    assert mean.dtype == torch.float64
+    dx, dg, db = capi.native_layer_norm_backward(dy.to(DEV), x.to(DEV), [N], mean, rstd, g.to(DEV), b.to(DEV))
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+    rdx, rdg, rdb = ao.layer_norm_bwd(dy, x, [N], rmean, rrstd, g, b)
+    for a, r in ((y, ry), (dx, rdx), (dg, rdg), (db, rdb)):
+        assert torch.allclose(a.cpu(), r, rtol=1e-10, atol=1e-10)
+
+
+def test_large_offset_row_is_finite_and_matches():
+    # the reference's regression case: 1e15 + {0..4} must not turn into NaN
+    x = torch.tensor([[1e15 + i for i in range(5)]] * 3, dtype=torch.float32)
+    y, mean, rstd = capi.native_layer_norm(x.to(DEV), [5], None, None, 1e-5)
+    ry, _, _ = ao.layer_norm_fwd(x, [5], None, None, 1e-5)
+    assert torch.isfinite(y).all()
+    assert torch.allclose(y.cpu(), ry, atol=1e-5)
+    # the vector / ring path too: a constant huge row must come out as exactly zero
+    x = torch.full((4, 64), 1e15)
+    y, mean, _ = capi.native_layer_norm(x.to(DEV), [64], None, None, 1e-5)
+    assert capi.last_path() == "ring"
+    assert float(y.abs().max()) == 0.0 and torch.equal(mean.cpu().reshape(-1), x[:, 0])
+
+
+def test_rms_default_eps_is_accumulate_type_epsilon():
+    x = ao.randn((8, 256), 340, torch.bfloat16)
+    w = ao.randn((256,), 341, torch.bfloat16, 1.0, 0.02)
+    y, rstd = capi._fused_rms_norm(x.to(DEV), [256], w.to(DEV), None)
+    ry, rrstd = ao.rms_norm_fwd(x, [256], w, torch.finfo(torch.float32).eps)
+    check_out(y, ry, "y"); check_stat(rstd, rrstd, "rstd")
+
+
+def test_rms_dweight_equals_row_count_terms():
+    # reference regression: with dy == 1 and x == 1, dweight_j = M * rstd (rstd ~ 1)
+    M, N = 3000, 512
+    x = torch.ones(M, N, dtype=torch.bfloat16)
+    w = torch.ones(N, dtype=torch.float32)
+    y, rstd = capi._fused_rms_norm(x.to(DEV), [N], w.to(DEV), 1e-6)
+    dx, dw = capi._fused_rms_norm_backward(x.to(DEV), x.to(DEV), [N], rstd, w.to(DEV))
+    assert torch.allclose(dw.cpu(), torch.full((N,), float(M)), rtol=1e-5)
+
+
+def test_multi_dim_normalized_shape_and_stat_shapes():
+    x = ao.randn((2, 3, 4, 8), 350, torch.float32)
+    g, b = ao.randn((4, 8), 351), ao.randn((4, 8), 352)
+    y, mean, rstd = capi.native_layer_norm(x.to(DEV), [4, 8], g.to(DEV), b.to(DEV), 1e-5)
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [4, 8], g, b, 1e-5)
+    assert list(mean.shape) == [2, 3, 1, 1] == list(rmean.shape)
+    check_out(y, ry, "y")
+
+
+def test_empty_batch_and_bad_shapes():
+    x = torch.empty(0, 16, device=DEV)
+    g = torch.ones(16, device=DEV)
+    y, mean, rstd = capi.native_layer_norm(x, [16], g, g, 1e-5)
+    assert y.shape == (0, 16) and mean.shape == (0, 1)
+    dx, dg, db = capi.native_layer_norm_backward(x, x, [16], mean, rstd, g, g)
+    assert float(dg.abs().sum()) == 0 and float(db.abs().sum()) == 0
+    with pytest.raises(RuntimeError):
+        capi.native_layer_norm(torch.ones(4, 8, device=DEV), [16], None, None, 1e-5)
+    with pytest.raises(RuntimeError):
+        capi.native_layer_norm(torch.ones(4, 16, device=DEV), [16], torch.ones(8, device=DEV), None, 1e-5)
+    with pytest.raises(ValueError):
+        capi.native_layer_norm(torch.ones(4, 16), [16], None, None, 1e-5)  # CPU tensor: no CPU path
+
+
+def test_weight_gradients_are_bit_reproducible():
+    M, N = 5000, 4096
+    x, dy = ao.randn((M, N), 360, torch.bfloat16).to(DEV), ao.randn((M, N), 361, torch.bfloat16).to(DEV)
+    g, b = ao.randn((N,), 362).to(DEV), ao.randn((N,), 363).to(DEV)
+    y, mean, rstd = capi.native_layer_norm(x, [N], g, b, 1e-5)
+    runs = [capi.native_layer_norm_backward(dy, x, [N], mean, rstd, g, b) for _ in range(3)]
+    for dx, dg, db in runs[1:]:
+        assert torch.equal(dg, runs[0][1]) and torch.equal(db, runs[0][2]) and torch.equal(dx, runs[0][0])
+
+
+def test_workspace_too_small_is_rejected():
+    lib = b200norm.load_library()
+    M, N = 64, 1024
+    x = torch.zeros(M, N, device=DEV)
+    st = torch.zeros(M, device=DEV)
+    g = torch.ones(N, device=DEV)
+    need = lib.b2n_norm_bwd_workspace_bytes(M, N, b200norm.F32, b200norm.F32, 1)
+    assert need > 0
+    ws = torch.empty(need // 2, dtype=torch.uint8, device=DEV)
+    rc = lib.b2n_layer_norm_bwd(x.data_ptr(), x.data_ptr(), st.data_ptr(), st.data_ptr(), g.data_ptr(), x.data_ptr(),
+                                g.data_ptr(), g.data_ptr(), ws.data_ptr(), need // 2, M, N, 0, 0, None)
+    assert rc == b200norm.ERR_WORKSPACE
+    rc = lib.b2n_layer_norm_fwd(x.data_ptr(), None, None, x.data_ptr(), st.data_ptr(), st.data_ptr(), M, N, 1e-5,
+                                b200norm.F32, b200norm.F16, None)
+    assert rc == b200norm.OK  # weight dtype is irrelevant when there are no weights
+    rc = lib.b2n_layer_norm_fwd(x.data_ptr(), g.data_ptr(), None, x.data_ptr(), st.data_ptr(), st.data_ptr(), M, N, 1e-5,
+                                b200norm.F32, b200norm.F16, None)
+    assert rc == b200norm.ERR_UNSUPPORTED_DTYPE
+    torch.cuda.synchronize()

@@ -1,0 +1,180 @@
+"""softmax / log-softmax parity: CUDA kernels through the C ABI vs the CPU oracle (tolerances as in
+test_gpu_norm.py: fp32 1e-5 relative with an absolute floor, 16-bit within 1 ulp of the
+fp32-accumulated reference)."""
+import math
+
+import pytest
+import torch
+
+import b200norm
+from b200norm import capi
+from oracle import aten_oracle as ao
+
+from gpu_util import DEV, forced_path, guarded_empty, misaligned
+
+pytestmark = pytest.mark.gpu
+
+ROW_SHAPES = [(1, 1), (3, 5), (7, 128), (33, 130), (129, 1000), (64, 2048), (40, 4096), (9, 8192), (4, 16384),
+              (3, 40000), (2, 128256)]
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+PATHS = [b200norm.PATH_AUTO, b200norm.PATH_GENERIC]
+
+
+def check_out(a, ref, what, tol=1.0):
+    if ref.dtype in (torch.bfloat16, torch.float16):
+        d = ao.ulp_distance(a.cpu(), ref)
+        assert d <= 1, f"{what}: {d} ulp"
+    else:
+        e = ao.fp32_err(a, ref)
+        assert e <= tol, f"{what}: error {e:.3f} x tolerance"
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("is_log", [False, True])
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("M,N", ROW_SHAPES)
+def test_last_dim_fwd_bwd(M, N, dt, is_log, path):
+    x = ao.randn((M, N), 400 + N, dt, 0.0, 2.0)
+    dy = ao.randn((M, N), 401, dt)
+    fwd = capi._log_softmax if is_log else capi._softmax
+    bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+    with forced_path(path):
+        y_buf, y_chk = guarded_empty((M, N), dt)
+        y = fwd(x.to(DEV), -1, False, out=y_buf)
+        used = capi.last_path()
+        dx_buf, dx_chk = guarded_empty((M, N), dt)
+        dx = bwd(dy.to(DEV), y, -1, dt, out=dx_buf)
+    torch.cuda.synchronize()
+    y_chk(); dx_chk()
+    if path == b200norm.PATH_GENERIC:
+        assert used == "generic"
+    ry = ao.softmax_fwd(x, -1, is_log)
+    check_out(y, ry, "y")
+    # backward on the kernel's own forward output, as autograd would
+    rdx = ao.softmax_bwd(dy, y.cpu(), -1, is_log, dt)
+    check_out(dx, rdx, "dx", tol=2.0)
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("is_log", [False, True])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,dim", [((6, 5, 3), 0), ((2, 7, 4), 1), ((4, 33, 65), 1), ((128, 16), 0), ((3, 4, 5, 6), 2),
+                                       ((2, 3, 4), -1), ((5,), 0)])
+def test_any_dim(shape, dim, dt, is_log):
+    x = ao.randn(shape, 410, dt, 0.0, 2.0)
+    dy = ao.randn(shape, 411, dt)
+    fwd = capi._log_softmax if is_log else capi._softmax
+    bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+    y = fwd(x.to(DEV), dim, False)
+    dx = bwd(dy.to(DEV), y, dim, dt)
+    check_out(y, ao.softmax_fwd(x, dim, is_log), "y")
+    check_out(dx, ao.softmax_bwd(dy, y.cpu(), dim, is_log, dt), "dx", tol=2.0)
+
+
+def test_zero_dim_tensor():
+    x = torch.tensor(3.0, device=DEV)
+    assert float(capi._softmax(x, 0, False)) == 1.0
+    assert float(capi._log_softmax(x, -1, False)) == 0.0
+    with pytest.raises(IndexError):
+        capi._softmax(x, 1, False)
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [64, 2048, 5000])
+def test_masked_and_degenerate_rows(N, dt, path):
+    # row 0: causal-style -inf tail; row 1: all -inf (NaN on CPU ATen and in the reference); row 2: one +inf;
+    # row 3: one NaN; row 4: ordinary
+    x = ao.randn((5, N), 420, torch.float32)
+    x[0, N // 3:] = float("-inf")
+    x[1, :] = float("-inf")
+    x[2, 7] = float("inf")
+    x[3, 9] = float("nan")
+    x = x.to(dt)
+    with forced_path(path):
+        for is_log in (False, True):
+            fwd = capi._log_softmax if is_log else capi._softmax
+            y = fwd(x.to(DEV), -1, False).cpu()
+            ry = ao.softmax_fwd(x, -1, is_log)
+            assert torch.equal(torch.isnan(y), torch.isnan(ry)), "NaN pattern"
+            assert torch.isnan(y[1]).all() and torch.isnan(y[2]).all() and torch.isnan(y[3]).all()
+            if is_log:
+                assert (y[0, N // 3:] == float("-inf")).all()
+            else:
+                assert (y[0, N // 3:] == 0).all()
+            check_out(y[0:1], ry[0:1], "masked row")
+            check_out(y[4:5], ry[4:5], "plain row")
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape,dim", [((9, 64), -1), ((3, 1000), 1), ((4, 6, 10), 1), ((2, 2048), -1)])
+def test_half_to_float(shape, dim, dt):
+    # the reference's regression (fp16 -> fp32 output for every dim); CPU has no such kernel: oracle = op(x.float())
+    x = ao.randn(shape, 430, dt, 0.0, 2.0)
+    dy = ao.randn(shape, 431, torch.float32)
+    for is_log in (False, True):
+        fwd = capi._log_softmax if is_log else capi._softmax
+        bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+        y = fwd(x.to(DEV), dim, True)
+        assert y.dtype == torch.float32
+        ry = ao.softmax_fwd(x, dim, is_log, out_dtype=torch.float32)
+        assert ao.fp32_err(y, ry) <= 1.0
+        dx = bwd(dy.to(DEV), y, dim, dt)
+        assert dx.dtype == dt
+        rdx = ao.softmax_bwd(dy, y.cpu(), dim, is_log, dt)
+        assert ao.ulp_distance(dx.cpu(), rdx) <= 1
+    with pytest.raises(RuntimeError):
+        capi._softmax(torch.ones(4, 4, device=DEV), -1, True)  # only 16-bit inputs convert
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [33, 128, 1001])
+@pytest.mark.parametrize("shift", [1, 3])
+def test_alignment_shifts(N, dt, shift):
+    # the reference's test_softmax_results matrix: odd sizes and 1-element shifts that break alignment
+    x = ao.randn((11, N), 440, dt, 0.0, 2.0)
+    dy = ao.randn((11, N), 441, dt)
+    xd, dyd = misaligned(x.to(DEV), shift), misaligned(dy.to(DEV), shift)
+    for is_log in (False, True):
+        fwd = capi._log_softmax if is_log else capi._softmax
+        bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+        y = fwd(xd, -1, False)
+        assert capi.last_path() == "generic"
+        check_out(y, ao.softmax_fwd(x, -1, is_log), "y")
+        dx = bwd(dyd, y, -1, dt)
+        check_out(dx, ao.softmax_bwd(dy, y.cpu(), -1, is_log, dt), "dx", tol=2.0)
+
+
+def test_known_answers():
+    # log_softmax is shift invariant; exp(log_softmax) sums to one (reference test_log_softmax_big / _double)
+    x = ao.randn((8, 4096), 450).to(DEV)
+    a = capi._log_softmax(x, -1, False)
+    b = capi._log_softmax(x + 1000.0, -1, False)
+    assert torch.allclose(a, b, atol=2e-4)
+    assert torch.allclose(a.exp().sum(-1), torch.ones(8, device=DEV), atol=1e-5)
+    # _softmax_backward_data(x, x) with x == 1/numel gives out[0] == 1/numel (reference :17914-17920)
+    n = 1 << 16
+    v = torch.full((1, n), 1.0 / n, device=DEV)
+    out = capi._softmax_backward_data(v, v, -1, torch.float32)
+    assert math.isclose(float(out[0, 0]), (1.0 / n) * (1.0 / n - 1.0 / n), abs_tol=1e-9)
+
+
+def test_float64():
+    x = ao.randn((5, 333), 460).double()
+    dy = ao.randn((5, 333), 461).double()
+    for is_log in (False, True):
+        fwd = capi._log_softmax if is_log else capi._softmax
+        bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+        y = fwd(x.to(DEV), -1, False)
+        assert torch.allclose(y.cpu(), ao.softmax_fwd(x, -1, is_log), rtol=1e-12, atol=1e-12)
+        dx = bwd(dy.to(DEV), y, -1, torch.float64)
+        assert torch.allclose(dx.cpu(), ao.softmax_bwd(dy, y.cpu(), -1, is_log, torch.float64), rtol=1e-12, atol=1e-12)
+
+
+def test_ring_is_used_for_aligned_rows_and_refuses_others_when_forced():
+    x = ao.randn((64, 2048), 470, torch.bfloat16).to(DEV)
+    capi._softmax(x, -1, False)
+    assert capi.last_path() == "ring"
+    with forced_path(b200norm.PATH_RING):
+        with pytest.raises(b200norm.B200NormError):
+            capi._softmax(ao.randn((4, 33), 471).to(DEV), -1, False)  # 33 floats: not a multiple of 16 bytes

@@ -60,6 +60,9 @@ def load_library() -> ctypes.CDLL:
         "b2n_set_path": (i32, [i32]),
         "b2n_last_path": (c.c_char_p, []),
         "b2n_device_status": (i32, [vp]),
+        "b2n_launch_count": (c.c_ulonglong, []),
+        "b2n_profile_begin": (i32, []),
+        "b2n_profile_end": (i32, [c.c_char_p, sz]),
         "b2n_layer_norm_fwd": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, dbl, i32, i32, vp]),
         "b2n_rms_norm_fwd": (i32, [vp, vp, vp, vp, i64, i64, dbl, i32, i32, vp]),
         "b2n_norm_bwd_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),

@@ -37,6 +37,20 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found: the CUDA extension cannot be built")
 
 
+def _digest(paths, extra: str = "") -> str:
+    """Content hash of the given files: the up-to-date test that survives a copy of the tree (mtimes do not)."""
+    import hashlib
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _stamp_ok(stamp: Path, digest: str, product: Path) -> bool:
+    return product.exists() and stamp.exists() and stamp.read_text().strip() == digest
+
+
 def _newest(paths) -> float:
     return max(p.stat().st_mtime for p in paths)
 
@@ -52,6 +66,10 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.glob("*.h"))
     hdr_time = _newest(headers)
     sources = sorted(CSRC.glob("*.cu"))
+    stamp = PKG_DIR / ".libb200norm.stamp"
+    digest = _digest(headers + sources, " ".join(NVCC_FLAGS))
+    if not force and _stamp_ok(stamp, digest, LIB):
+        return LIB
     nvcc = _nvcc()
     jobs = []
     objects = []
@@ -67,6 +85,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
             list(pool.map(_run, jobs))
     if jobs or force or not LIB.exists() or LIB.stat().st_mtime < _newest(objects):
         _run([nvcc, "-shared", "-o", str(LIB), *map(str, objects), "-cudart", "shared"])
+    stamp.write_text(digest)
     return LIB
 
 
@@ -76,7 +95,9 @@ def build_aten(force: bool = False, verbose: bool = False) -> Path:
 
     src = CSRC / "aten_register.cpp"
     deps = [src, INCLUDE / "b200norm.h"]
-    if not force and ATEN_LIB.exists() and ATEN_LIB.stat().st_mtime >= max(_newest(deps), LIB.stat().st_mtime):
+    stamp = PKG_DIR / "._b200norm_aten.stamp"
+    digest = _digest(deps, torch.__version__)
+    if not force and _stamp_ok(stamp, digest, ATEN_LIB):
         return ATEN_LIB
     if verbose:
         print("[b200norm] compiling the ATen registration", file=sys.stderr)
@@ -90,6 +111,7 @@ def build_aten(force: bool = False, verbose: bool = False) -> Path:
         "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}", "-Wl,--no-as-needed",
     ]
     _run(cmd)
+    stamp.write_text(digest)
     return ATEN_LIB
 
 

@@ -96,6 +96,28 @@ def device_status(device=None) -> int:
         return load_library().b2n_device_status(torch.cuda.current_stream().cuda_stream)
 
 
+def launch_count() -> int:
+    """Kernels launched through the library by this thread so far."""
+    return int(load_library().b2n_launch_count())
+
+
+def profile_begin() -> None:
+    """Start bracketing every main kernel launch of this thread with CUDA events."""
+    _check(load_library().b2n_profile_begin(), "b2n_profile_begin")
+
+
+def profile_end() -> dict:
+    """Stop, synchronise, and return {kernel name: (launches, total milliseconds)}."""
+    import ctypes
+    buf = ctypes.create_string_buffer(8192)
+    _check(load_library().b2n_profile_end(buf, len(buf)), "b2n_profile_end")
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.split()
+        out[name] = (int(n), float(ms))
+    return out
+
+
 # ---- layer norm / RMS norm -------------------------------------------------------------------------
 def native_layer_norm(input, normalized_shape, weight=None, bias=None, eps=1e-5, out=None):
     """aten::native_layer_norm -> (Y, mean, rstd); mean/rstd in the accumulate dtype.

@@ -1,5 +1,7 @@
 // The C ABI declared in include/b200norm.h: argument validation, then the typed launchers.
 #include <mutex>
+#include <string>
+#include <vector>
 
 #include "common.cuh"
 #include "launchers.h"
@@ -13,6 +15,12 @@ __device__ int g_status_word = 0;  // one per device (each device that loads the
 thread_local int tl_last_cuda_error = 0;
 thread_local int tl_forced_path = B2N_PATH_AUTO;
 thread_local const char* tl_last_path = "none";
+thread_local unsigned long long tl_launches = 0;
+
+struct ProfileRecord { const char* name; cudaEvent_t start, stop; };
+thread_local bool tl_profiling = false;
+thread_local std::vector<ProfileRecord> tl_records;
+constexpr size_t kMaxProfileRecords = 1 << 16;
 
 struct PerDevice {
   std::once_flag once;
@@ -42,6 +50,24 @@ int check_cuda(cudaError_t e) {
   tl_last_cuda_error = static_cast<int>(e);
   return B2N_ERR_CUDA;
 }
+int launched() {
+  ++tl_launches;
+  return check_cuda(cudaGetLastError());
+}
+
+ProfileScope::ProfileScope(const char* kernel_name, cudaStream_t st) : slot(-1), stream(st) {
+  if (!tl_profiling || tl_records.size() >= kMaxProfileRecords) return;
+  ProfileRecord r{kernel_name, nullptr, nullptr};
+  if (cudaEventCreate(&r.start) != cudaSuccess) return;
+  if (cudaEventCreate(&r.stop) != cudaSuccess) { cudaEventDestroy(r.start); return; }
+  cudaEventRecord(r.start, st);
+  slot = static_cast<int>(tl_records.size());
+  tl_records.push_back(r);
+}
+ProfileScope::~ProfileScope() {
+  if (slot >= 0) cudaEventRecord(tl_records[slot].stop, stream);
+}
+
 int forced_path() { return tl_forced_path; }
 void note_path(const char* name) { tl_last_path = name; }
 
@@ -78,6 +104,43 @@ int b2n_set_path(int path) {
 }
 
 const char* b2n_last_path(void) { return tl_last_path; }
+
+unsigned long long b2n_launch_count(void) { return tl_launches; }
+
+int b2n_profile_begin(void) {
+  for (auto& r : tl_records) { cudaEventDestroy(r.start); cudaEventDestroy(r.stop); }
+  tl_records.clear();
+  tl_profiling = true;
+  return B2N_OK;
+}
+
+int b2n_profile_end(char* report, size_t cap) {
+  tl_profiling = false;
+  struct Agg { const char* name; int launches; double ms; };
+  std::vector<Agg> aggs;
+  int rc = B2N_OK;
+  for (auto& r : tl_records) {
+    float ms = 0.0f;
+    if (check_cuda(cudaEventSynchronize(r.stop)) || check_cuda(cudaEventElapsedTime(&ms, r.start, r.stop))) rc = B2N_ERR_CUDA;
+    size_t k = 0;
+    for (; k < aggs.size(); ++k)
+      if (std::string(aggs[k].name) == r.name) break;
+    if (k == aggs.size()) aggs.push_back({r.name, 0, 0.0});
+    aggs[k].launches += 1;
+    aggs[k].ms += ms;
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
+  tl_records.clear();
+  std::string out;
+  for (auto& a : aggs) out += std::string(a.name) + " " + std::to_string(a.launches) + " " + std::to_string(a.ms) + "\n";
+  if (report != nullptr && cap > 0) {
+    const size_t n = out.size() < cap - 1 ? out.size() : cap - 1;
+    out.copy(report, n);
+    report[n] = 0;
+  }
+  return rc;
+}
 
 int b2n_device_status(void* stream) {
   int* p = device_status_ptr();

@@ -266,5 +266,15 @@ int check_cuda(cudaError_t e);            // records e for b2n_last_cuda_error; 
 int forced_path();                        // b2n_set_path value of this thread
 void note_path(const char* name);         // records the family used by the last launch
 int* device_status_ptr();                 // device address of the status word of the current device
+int launched();                           // counts one kernel launch; returns check_cuda(cudaGetLastError())
+
+// Brackets one main-kernel launch with a pair of CUDA events on its stream while this thread has
+// profiling switched on (b2n_profile_begin); otherwise does nothing.
+struct ProfileScope {
+  ProfileScope(const char* kernel_name, cudaStream_t st);
+  ~ProfileScope();
+  int slot;
+  cudaStream_t stream;
+};
 
 }  // namespace b2n

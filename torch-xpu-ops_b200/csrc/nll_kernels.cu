@@ -134,7 +134,7 @@ int nll_fwd_typed(const void* logp, const void* target, const void* weight, void
     nll_fwd_none_kernel<T, IdxT><<<grid, kNllThreads, 0, st>>>(static_cast<const T*>(logp), target,
                                                                static_cast<const T*>(weight),
                                                                static_cast<T*>(out), M, C, ignore_index, status);
-    return check_cuda(cudaGetLastError());
+    return launched();
   }
   int64_t blocks = (M + kNllThreads - 1) / kNllThreads;
   if (blocks < 1) blocks = 1;
@@ -143,10 +143,10 @@ int nll_fwd_typed(const void* logp, const void* target, const void* weight, void
                                                                 static_cast<const T*>(weight),
                                                                 static_cast<A*>(workspace), M, C, ignore_index,
                                                                 status);
-  if (int e = check_cuda(cudaGetLastError())) return e;
+  if (int e = launched()) return e;
   nll_fwd_fold_kernel<T><<<1, kNllThreads, 0, st>>>(static_cast<const A*>(workspace), grid, static_cast<T*>(out),
                                                     static_cast<T*>(total_weight), sums_f32, reduction, M);
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 template <typename T, typename IdxT>
@@ -159,7 +159,7 @@ int nll_bwd_typed(const void* grad_out, const void* target, const void* weight, 
   nll_bwd_kernel<T, IdxT><<<grid, kNllThreads, 0, st>>>(
       static_cast<const T*>(grad_out), target, static_cast<const T*>(weight), static_cast<const T*>(total_weight),
       static_cast<T*>(grad_input), M, C, reduction, ignore_index, device_status_ptr());
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 }  // namespace

@@ -4,8 +4,9 @@
 //
 // Arithmetic follows at::native::xpu::layer_norm_kernel_impl and layer_norm_backward_kernel_impl
 // (src/ATen/native/xpu/sycl/LayerNormKernels.cpp:648-699, :1117-1416) with two deliberate
-// differences: the variance is an exact two-pass sum of (x-mean)^2 in the accumulate type, and no
-// intermediate product is rounded to the storage type.
+// differences: the variance is a two-pass sum of (x-mean)^2 in the accumulate type (taken relative
+// to the row's first element) instead of Welford updates, and no intermediate product is rounded
+// to the storage type.
 #pragma once
 #include "common.cuh"
 
@@ -30,27 +31,31 @@ __global__ void norm_fwd_generic_kernel(const T* __restrict__ x, const WT* __res
     if (row >= M) continue;  // only possible with TPR == 32 (no CTA-wide barrier below in that case)
     const T* xr = x + row * N;
     T* yr = y + row * N;
+    // Layer norm sums are taken relative to the row's first element: a large common offset
+    // (say 1e15 + small) then cancels exactly instead of being rounded away in the row sum.
+    const A shift = RMS ? A(0) : to_acc<A>(xr[0]);
     A s = 0;
     for (int64_t v = lane; v < nv; v += tpr) {
       const Vec<T, V> p = ld_vec<T, V>(xr + v * V);
 #pragma unroll
       for (int e = 0; e < V; ++e) {
-        const A a = to_acc<A>(p.v[e]);
+        const A a = to_acc<A>(p.v[e]) - shift;
         s += RMS ? a * a : a;
       }
     }
     s = row_reduce<TPR>(s, scratch, SumOp());
-    A mu = 0, rs;
+    A mu = 0, mu_d = 0, rs;
     if constexpr (RMS) {
       rs = acc_rsqrt(s / static_cast<A>(N) + eps);
     } else {
-      mu = s / static_cast<A>(N);
+      mu_d = s / static_cast<A>(N);  // mean of (x - shift)
+      mu = shift + mu_d;
       A q = 0;
       for (int64_t v = lane; v < nv; v += tpr) {
         const Vec<T, V> p = ld_vec<T, V>(xr + v * V);
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          const A d = to_acc<A>(p.v[e]) - mu;
+          const A d = (to_acc<A>(p.v[e]) - shift) - mu_d;
           q += d * d;
         }
       }
@@ -63,7 +68,7 @@ __global__ void norm_fwd_generic_kernel(const T* __restrict__ x, const WT* __res
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         const int64_t j = v * V + e;
-        A t = (to_acc<A>(p.v[e]) - mu) * rs;
+        A t = ((to_acc<A>(p.v[e]) - shift) - mu_d) * rs;
         if (gamma) t *= to_acc<A>(gamma[j]);
         if (!RMS && beta) t += to_acc<A>(beta[j]);
         o.v[e] = from_acc<T>(t);

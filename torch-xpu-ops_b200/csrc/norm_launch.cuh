@@ -50,9 +50,10 @@ int norm_fwd_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const W
   auto kernel = norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once(kernel, p.smem, mask)) return e;
+  ProfileScope prof(RMS ? "rms_norm_fwd_ring" : "layer_norm_fwd_ring", st);
   kernel<<<p.grid, kRingThreads, p.smem, st>>>(x, gamma, beta, y, mean, rstd, M, static_cast<int>(N),
                                                static_cast<float>(eps), p.stages, p.rpg, device_status_ptr());
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 template <typename T, typename WT, bool RMS>
@@ -86,6 +87,7 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
 
   note_path("generic");
+  ProfileScope prof(RMS ? "rms_norm_fwd_generic" : "layer_norm_fwd_generic", st);
   constexpr int V = 16 / sizeof(T);
   const bool vec = norm_vectorizable<T, WT>(N, x, y, nullptr);
   const A eps_a = static_cast<A>(eps);
@@ -99,7 +101,7 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
     if (vec) norm_fwd_generic_kernel<T, WT, RMS, 0, V><<<grid, threads, 0, st>>>(x, gamma, beta, y, mean, rstd, M, N, eps_a);
     else norm_fwd_generic_kernel<T, WT, RMS, 0, 1><<<grid, threads, 0, st>>>(x, gamma, beta, y, mean, rstd, M, N, eps_a);
   }
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 // ---- backward -----------------------------------------------------------------------------------
@@ -127,6 +129,7 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
                          cudaStream_t st) {
   constexpr int VPT = kNormBwdEpt / Pack16<T>::VEC;
   static std::atomic<uint64_t> mask_w{0}, mask_n{0};
+  ProfileScope prof(RMS ? "rms_norm_bwd_ring" : "layer_norm_bwd_ring", st);
   if (wgrad) {
     auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true>;
     if (int e = set_smem_once(kernel, p.smem, mask_w)) return e;
@@ -138,7 +141,7 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
     kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
                                                  p.stages, p.rpg, device_status_ptr());
   }
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 template <typename T, typename WT, bool RMS>
@@ -182,7 +185,7 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
         if (e != B2N_OK || !wgrad) return e;
         norm_bwd_wgrad_fold_kernel<float, WT><<<fold_grid, fold_block, 0, st>>>(
             ws, dgamma, dbeta, static_cast<int64_t>(p.grid) * p.ng, N);
-        return check_cuda(cudaGetLastError());
+        return launched();
       }
     }
   }
@@ -190,6 +193,7 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
 
   note_path("generic");
   if (dx != nullptr) {
+    ProfileScope prof(RMS ? "rms_norm_bwd_dx_generic" : "layer_norm_bwd_dx_generic", st);
     constexpr int V = 16 / sizeof(T);
     const bool vec = norm_vectorizable<T, WT>(N, dy, x, dx);
     if (N <= 1024) {
@@ -202,17 +206,20 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
       if (vec) norm_bwd_dx_generic_kernel<T, WT, RMS, 0, V><<<grid, threads, 0, st>>>(dy, x, mean, rstd, gamma, dx, M, N);
       else norm_bwd_dx_generic_kernel<T, WT, RMS, 0, 1><<<grid, threads, 0, st>>>(dy, x, mean, rstd, gamma, dx, M, N);
     }
-    if (int e = check_cuda(cudaGetLastError())) return e;
+    if (int e = launched()) return e;
   }
   if (wgrad) {
     const int64_t chunks = wgrad_generic_chunks(M);
     const int64_t rpc = (M + chunks - 1) / chunks;
     const dim3 block(32, 8);
     const dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>(chunks));
-    norm_bwd_wgrad_partial_kernel<T, RMS><<<grid, block, 0, st>>>(dy, x, mean, rstd, ws, M, N, rpc);
-    if (int e = check_cuda(cudaGetLastError())) return e;
+    {
+      ProfileScope prof("norm_bwd_wgrad_generic", st);
+      norm_bwd_wgrad_partial_kernel<T, RMS><<<grid, block, 0, st>>>(dy, x, mean, rstd, ws, M, N, rpc);
+      if (int e = launched()) return e;
+    }
     norm_bwd_wgrad_fold_kernel<A, WT><<<fold_grid, fold_block, 0, st>>>(ws, dgamma, dbeta, chunks, N);
-    if (int e = check_cuda(cudaGetLastError())) return e;
+    if (int e = launched()) return e;
   }
   return B2N_OK;
 }

@@ -68,6 +68,15 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
       const int64_t row = row0 + lr;
       if (row >= M) break;  // uniform over the group
       const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
+      // Layer norm works on d = x - shift, shift = the row's first element (a shared-memory
+      // broadcast read): a large common offset then cancels exactly instead of being rounded away
+      // in the row sum.  RMS norm needs the raw values (shift = 0).
+      float shift = 0.0f;
+      if constexpr (!RMS) {
+        float first[VEC];
+        P::unpack(lds128(rbase), first);
+        shift = first[0];
+      }
       float xv[EPT];
       float red1[1] = {0.0f};
 #pragma unroll
@@ -76,25 +85,32 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         if (v < nvec) {
           P::unpack(lds128(rbase + v * 16), &xv[k * VEC]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) red1[0] += RMS ? xv[k * VEC + e] * xv[k * VEC + e] : xv[k * VEC + e];
+          for (int e = 0; e < VEC; ++e) {
+            if constexpr (RMS) {
+              red1[0] += xv[k * VEC + e] * xv[k * VEC + e];
+            } else {
+              xv[k * VEC + e] -= shift;
+              red1[0] += xv[k * VEC + e];
+            }
+          }
         } else {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) xv[k * VEC + e] = 0.0f;
         }
       }
       group_reduce<GROUP, 1>(red1, rs->red, grp, tg, phase, SumOp());
-      float mu = 0.0f, rsd;
+      float mu_d = 0.0f, rsd;  // mu_d: mean of (x - shift)
       if constexpr (RMS) {
         rsd = acc_rsqrt(red1[0] * inv_n + eps);
       } else {
-        mu = red1[0] * inv_n;
+        mu_d = red1[0] * inv_n;
         float red2[1] = {0.0f};
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           if (tg + k * GROUP < nvec) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-              const float d = xv[k * VEC + e] - mu;
+              const float d = xv[k * VEC + e] - mu_d;
               red2[0] += d * d;
             }
           }
@@ -102,6 +118,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         group_reduce<GROUP, 1>(red2, rs->red, grp, tg, phase, SumOp());
         rsd = acc_rsqrt(red2[0] * inv_n + eps);
       }
+      const float mu = shift + mu_d;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
@@ -109,7 +126,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           float o[VEC];
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            const float t = (xv[k * VEC + e] - mu) * rsd * gw[k * VEC + e];
+            const float t = (xv[k * VEC + e] - mu_d) * rsd * gw[k * VEC + e];
             o[e] = RMS ? t : t + gb[k * VEC + e];
           }
           sts128(rbase + v * 16, P::pack(o));

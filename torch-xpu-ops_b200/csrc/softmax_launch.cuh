@@ -35,8 +35,9 @@ int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int6
   auto kernel = softmax_fwd_ring_kernel<T, LOG, GROUP, VPT>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
+  ProfileScope prof(LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring", st);
   kernel<<<p.grid, kRingThreads, p.smem, st>>>(x, y, M, static_cast<int>(N), p.stages, p.rpg, device_status_ptr());
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 template <typename T, bool LOG, int GROUP>
@@ -46,9 +47,10 @@ int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, i
   auto kernel = softmax_bwd_ring_kernel<T, LOG, GROUP, VPT>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
+  ProfileScope prof(LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring", st);
   kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, y, dx, M, static_cast<int>(N), p.stages, p.rpg,
                                                device_status_ptr());
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 template <typename TI, typename TO, bool LOG>
@@ -76,6 +78,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
     }
     if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
     note_path("generic");
+    ProfileScope prof(LOG ? "log_softmax_fwd_generic" : "softmax_fwd_generic", st);
     constexpr int V = 16 / sizeof(TI);  // vector width in elements, by the input type
     const bool vec = N % V == 0 && is_aligned(x, 16) && is_aligned(y, V * sizeof(TO));
     if (N <= 1024) {
@@ -88,13 +91,13 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
       if (vec) softmax_fwd_generic_kernel<TI, TO, LOG, 0, V><<<grid, threads, 0, st>>>(x, y, M, N);
       else softmax_fwd_generic_kernel<TI, TO, LOG, 0, 1><<<grid, threads, 0, st>>>(x, y, M, N);
     }
-    return check_cuda(cudaGetLastError());
+    return launched();
   }
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
   note_path("generic");
   const int grid = softmax_generic_grid(outer * inner, 256);
   softmax_fwd_spatial_kernel<TI, TO, LOG><<<grid, 256, 0, st>>>(x, y, outer, N, inner);
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 template <typename TG, typename TO, bool LOG>
@@ -125,6 +128,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
     }
     if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
     note_path("generic");
+    ProfileScope prof(LOG ? "log_softmax_bwd_generic" : "softmax_bwd_generic", st);
     constexpr int V = (16 / sizeof(TG)) < (16 / sizeof(TO)) ? (16 / sizeof(TG)) : (16 / sizeof(TO));
     const bool vec = N % V == 0 && is_aligned(dy, V * sizeof(TG)) && is_aligned(y, V * sizeof(TG)) &&
                      is_aligned(dx, V * sizeof(TO));
@@ -138,13 +142,13 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
       if (vec) softmax_bwd_generic_kernel<TG, TO, LOG, 0, V><<<grid, threads, 0, st>>>(dy, y, dx, M, N);
       else softmax_bwd_generic_kernel<TG, TO, LOG, 0, 1><<<grid, threads, 0, st>>>(dy, y, dx, M, N);
     }
-    return check_cuda(cudaGetLastError());
+    return launched();
   }
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
   note_path("generic");
   const int grid = softmax_generic_grid(outer * inner, 256);
   softmax_bwd_spatial_kernel<TG, TO, LOG><<<grid, 256, 0, st>>>(dy, y, dx, outer, N, inner);
-  return check_cuda(cudaGetLastError());
+  return launched();
 }
 
 #define B2N_SOFTMAX_TYPED_DECL(NAME)                                                                         \
