@@ -57,6 +57,32 @@ def ulp_distance(a: torch.Tensor, b: torch.Tensor) -> int:
     return int(d.max())
 
 
+def lowp_mismatch(a: torch.Tensor, ref: torch.Tensor, floor_scale: float = 1e-6):
+    """Gate for bf16/fp16 outputs: an element passes when it is within 1 ulp of the reference OR within the
+    absolute floor floor_scale * max(1, rms(ref)) — the same floor the fp32 gate uses.  The floor only matters
+    for outputs near zero, where one 16-bit ulp is smaller than the fp32 rounding error of the reference itself
+    (a difference of terms of size ~1).  Returns (number of failing elements, worst ulp distance among them)."""
+    assert a.dtype == ref.dtype and a.dtype in (torch.bfloat16, torch.float16), (a.dtype, ref.dtype)
+    assert a.shape == ref.shape, (a.shape, ref.shape)
+    if a.numel() == 0:
+        return 0, 0
+    a, ref = a.detach().cpu(), ref.detach().cpu()
+    na, nb = torch.isnan(a), torch.isnan(ref)
+    if not torch.equal(na, nb):
+        return int((na != nb).sum()), 1 << 30
+    d = (_ordered_int(a) - _ordered_int(ref)).abs()
+    d = torch.where(na, torch.zeros_like(d), d)
+    af, rf = a.double(), ref.double()
+    finite = torch.isfinite(rf)
+    rms = float(rf[finite].pow(2).mean().sqrt()) if finite.any() else 0.0
+    floor = floor_scale * max(1.0, rms)
+    absdiff = torch.where(finite & torch.isfinite(af), (af - rf).abs(), torch.full_like(rf, float("inf")))
+    absdiff = torch.where(af == rf, torch.zeros_like(absdiff), absdiff)  # equal infinities
+    bad = (d > 1) & (absdiff > floor)
+    n_bad = int(bad.sum())
+    return n_bad, (int(d[bad].max()) if n_bad else 0)
+
+
 def fp32_err(a: torch.Tensor, b: torch.Tensor) -> float:
     """max |a-b| / (1e-5*|b| + 1e-6*max(1, rms(b))): <= 1 means "fp32 relative error <= 1e-5" with the
     absolute floor that outputs near zero need (element-wise relative error is unbounded there)."""

@@ -51,7 +51,7 @@ def test_layer_norm_autograd(shape, ns, dt, wdt):
     if dt == torch.float32:
         assert ao.fp32_err(y, ry) <= 1 and ao.fp32_err(xd.grad, rdx) <= 2
     else:
-        assert ao.ulp_distance(y.detach().cpu(), ry) <= 1 and ao.ulp_distance(xd.grad.cpu(), rdx) <= 1
+        assert ao.lowp_mismatch(y.detach(), ry)[0] == 0 and ao.lowp_mismatch(xd.grad, rdx)[0] == 0
     assert gd.grad.dtype == wdt and bd.grad.dtype == wdt
     tol = dict(rtol=1e-4, atol=1e-4) if wdt == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     assert torch.allclose(gd.grad.cpu().float(), rdg.float(), **tol)
@@ -74,7 +74,7 @@ def test_rms_norm_ops_directly():
     ry, rrstd = ao.rms_norm_fwd(x, [4096], w, 1e-6)
     rdx, rdw = ao.rms_norm_bwd(dy, x, [4096], w, 1e-6)
     assert rstd.shape == (32, 1) and dw.dtype == torch.float32
-    assert ao.ulp_distance(y.cpu(), ry) <= 1 and ao.ulp_distance(dx.cpu(), rdx) <= 1
+    assert ao.lowp_mismatch(y, ry)[0] == 0 and ao.lowp_mismatch(dx, rdx)[0] == 0
     assert torch.allclose(dw.cpu(), rdw, rtol=1e-4, atol=1e-4)
     # same-dtype weights go through F.rms_norm's fused dispatch and autograd
     xd = ao.randn((8, 256), 623).to(DEV).requires_grad_(True)
@@ -101,7 +101,7 @@ def test_softmax_autograd_every_dim(shape, dt):
             if dt == torch.float32:
                 assert ao.fp32_err(y, ry) <= 1 and ao.fp32_err(xd.grad, rdx) <= 2
             else:
-                assert ao.ulp_distance(y.detach().cpu(), ry) <= 1 and ao.ulp_distance(xd.grad.cpu(), rdx) <= 1
+                assert ao.lowp_mismatch(y.detach(), ry)[0] == 0 and ao.lowp_mismatch(xd.grad, rdx)[0] == 0
 
 
 def test_softmax_out_variants_and_dtype_argument():
@@ -150,24 +150,35 @@ def test_cross_entropy_end_to_end(dt):
         assert torch.allclose(a.cpu(), b, rtol=1e-5, atol=1e-5)
 
 
-def test_opinfo_samples_native_layer_norm_and_nll():
-    # the reference runs upstream's OpInfo samples for these ops against CPU (test_compare_cpu)
-    from torch.testing._internal.common_methods_invocations import op_db
-    wanted = {"native_layer_norm", "nn.functional.layer_norm", "nn.functional.rms_norm", "_softmax_backward_data",
-              "_log_softmax_backward_data", "softmax", "log_softmax", "nn.functional.nll_loss"}
-    seen = set()
-    for op in op_db:
-        if op.name not in wanted or op.variant_test_name not in ("", "with_dtype"):
-            continue
-        seen.add(op.name)
-        for sample in op.sample_inputs("cuda", torch.float32, requires_grad=False):
-            cpu = sample.transform(lambda t: t.cpu() if isinstance(t, torch.Tensor) else t)
-            got = op(sample.input, *sample.args, **sample.kwargs)
-            exp = op(cpu.input, *cpu.args, **cpu.kwargs)
-            got = got if isinstance(got, (tuple, list)) else (got,)
-            exp = exp if isinstance(exp, (tuple, list)) else (exp,)
-            for a, e in zip(got, exp):
-                if isinstance(a, torch.Tensor):
-                    assert a.shape == e.shape, (op.name, a.shape, e.shape)
-                    torch.testing.assert_close(a.cpu(), e, rtol=1e-4, atol=1e-5, equal_nan=True, msg=lambda m: f"{op.name}: {m}")
-    assert {"native_layer_norm", "softmax", "log_softmax", "nn.functional.nll_loss"} <= seen
+@pytest.mark.parametrize("shape,ns,has_w,has_b", [((1, 2, 3), [1, 2, 3], True, True), ((2, 2, 3), [2, 3], True, False),
+                                                  ((1,), [1], False, False), ((1, 2), [2], True, True),
+                                                  ((0, 1), [1], True, True), ((2, 0, 4), [4], True, True),
+                                                  ((3, 5, 7), [5, 7], False, True)])
+def test_layer_norm_sample_matrix(shape, ns, has_w, has_b):
+    # the shape / optional-argument matrix of upstream's sample_inputs_native_layer_norm, compared with CPU
+    x = ao.randn(shape, 660)
+    g = ao.randn(ns, 661) if has_w else None
+    b = ao.randn(ns, 662) if has_b else None
+    dev = lambda t: None if t is None else t.to(DEV)
+    got = torch.ops.aten.native_layer_norm(dev(x), ns, dev(g), dev(b), 0.5)
+    exp = torch.ops.aten.native_layer_norm(x, ns, g, b, 0.5)
+    for a, e in zip(got, exp):
+        assert a.shape == e.shape
+        torch.testing.assert_close(a.cpu(), e, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("shape", [(5, 3), (3,), (0, 4), (2, 3, 4, 5)])
+@pytest.mark.parametrize("red", ["none", "mean", "sum"])
+def test_nll_loss_sample_matrix(shape, red):
+    # batch / no-batch / empty-batch / spatial inputs through F.nll_loss, weights and ignore_index included
+    c = shape[1] if len(shape) > 1 else shape[0]
+    logp = torch.log_softmax(ao.randn(shape, 670), 1 if len(shape) > 1 else 0)
+    tshape = (shape[0],) + tuple(shape[2:]) if len(shape) > 1 else ()
+    t = ao.randint(c, tshape, 671)
+    w = ao.randn((c,), 672).abs() + 0.1
+    for weight in (None, w):
+        for ign in (-100, 1):
+            a = F.nll_loss(logp.to(DEV), t.to(DEV), None if weight is None else weight.to(DEV), ignore_index=ign, reduction=red)
+            e = F.nll_loss(logp, t, weight, ignore_index=ign, reduction=red)
+            assert a.shape == e.shape
+            torch.testing.assert_close(a.cpu(), e, rtol=1e-5, atol=1e-6, equal_nan=True)

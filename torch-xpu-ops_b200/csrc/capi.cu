@@ -231,7 +231,7 @@ int b2n_nll_loss_fwd(const void* logp, const void* target, const void* weight, v
   if (M < 0 || C < 0 || !valid_dtype(dtype) || reduction < B2N_REDUCE_NONE || reduction > B2N_REDUCE_SUM)
     return B2N_ERR_BAD_ARG;
   if (M > 0 && (!logp || !target)) return B2N_ERR_BAD_ARG;
-  if (!out) return B2N_ERR_BAD_ARG;
+  if (!out && !(reduction == B2N_REDUCE_NONE && M == 0)) return B2N_ERR_BAD_ARG;
   return launch_nll_loss_fwd(logp, target, weight, out, total_weight, sums_f32, workspace, workspace_bytes, M, C,
                              reduction, ignore_index, dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
 }

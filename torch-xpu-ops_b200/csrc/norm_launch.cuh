@@ -11,9 +11,10 @@
 
 namespace b2n {
 
-// Elements per thread in the ring kernels: forward keeps x, gamma, beta in registers; backward
-// keeps gamma, dgamma, dbeta and two working arrays, so it gets half as many elements.
-constexpr int kNormFwdEpt = 32;
+// Elements per thread in the ring kernels.  The forward keeps x, gamma and beta in registers
+// (with 32 elements the compiler re-loads the weights from global memory every row instead of
+// holding 96 values); the backward keeps gamma, dgamma, dbeta and two working arrays.
+constexpr int kNormFwdEpt = 16;
 constexpr int kNormBwdEpt = 16;
 
 // Opt the kernel into its dynamic shared memory, once per device.

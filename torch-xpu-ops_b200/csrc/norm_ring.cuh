@@ -2,6 +2,11 @@
 // Rows are 16-byte aligned multiples of 16 bytes; a row is shared by GROUP threads, each holding
 // VPT 16-byte vectors of it in registers, so every element is read from HBM once and written once.
 // Accumulation is fp32; mean/rstd are fp32.
+//
+// Instruction budget: at HBM speed an SM has roughly 20 thread-instructions per element, of which
+// per-row overhead (barrier waits, the cross-thread reductions) takes a large share when a thread
+// holds only 16 elements of a row.  Hence: independent partial accumulators (no 16-long dependent
+// add chains), FMA forms for the output expressions, and no integer division in the row loop.
 #pragma once
 #include "ring.cuh"
 
@@ -28,20 +33,14 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
                      T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t M,
                      int N, float eps, int S, int RPG, int* status) {
   using P = Pack16<T>;
-  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingConsumerThreads / GROUP;
+  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   RingShared* rs = reinterpret_cast<RingShared*>(smem_raw);
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.M = M;
-  g.row_bytes = static_cast<uint32_t>(N) * sizeof(T);
-  g.TR = NG * RPG;
-  g.S = S;
-  g.stage_bytes = static_cast<uint32_t>(g.TR) * g.row_bytes;
-  g.ntiles = (M + g.TR - 1) / g.TR;
-
-  ring_init(rs, S, kRingConsumerThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S, 1);
+  ring_init(rs, S, kRingThreads / 32);
   const int tid = threadIdx.x;
   RingProducer<1> prod(rs, stages, g, status);
   prod.in[0] = reinterpret_cast<const unsigned char*>(x);
@@ -55,17 +54,18 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   float gw[EPT], gb[EPT];
   load_weights<WT, GROUP, VPT, VEC>(gamma, 1.0f, nvec, tg, gw);
   if constexpr (!RMS) load_weights<WT, GROUP, VPT, VEC>(beta, 0.0f, nvec, tg, gb);
-  int phase = 0;
+  int red_phase = 0;
+  const uint32_t stages_u32 = smem_u32(stages);
 
-  const int64_t n = g.my_tiles();
+  RingCursor cur;
+  cur.start(g);
   int64_t i = 0;
-  for (; i < n; ++i) {
-    if (!ring_consumer_wait(rs, g, i, status)) break;
-    const int64_t row0 = g.tile_row0(i);
-    const uint32_t sbase = smem_u32(stages + static_cast<size_t>(i % S) * g.stage_bytes);
+  for (; i < g.my_tiles; ++i, cur.advance(g)) {
+    if (!ring_consumer_wait(rs, cur, status)) break;
+    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
-      const int64_t row = row0 + lr;
+      const int64_t row = cur.row0 + lr;
       if (row >= M) break;  // uniform over the group
       const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       // Layer norm works on d = x - shift, shift = the row's first element (a shared-memory
@@ -78,7 +78,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         shift = first[0];
       }
       float xv[EPT];
-      float red1[1] = {0.0f};
+      float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
@@ -86,11 +86,12 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           P::unpack(lds128(rbase + v * 16), &xv[k * VEC]);
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
+            const int j = k * VEC + e;
             if constexpr (RMS) {
-              red1[0] += xv[k * VEC + e] * xv[k * VEC + e];
+              part[j & 3] = fmaf(xv[j], xv[j], part[j & 3]);
             } else {
-              xv[k * VEC + e] -= shift;
-              red1[0] += xv[k * VEC + e];
+              xv[j] -= shift;
+              part[j & 3] += xv[j];
             }
           }
         } else {
@@ -98,27 +99,31 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           for (int e = 0; e < VEC; ++e) xv[k * VEC + e] = 0.0f;
         }
       }
-      group_reduce<GROUP, 1>(red1, rs->red, grp, tg, phase, SumOp());
+      float red1[1] = {(part[0] + part[1]) + (part[2] + part[3])};
+      group_reduce<GROUP, 1>(red1, rs->red, grp, tg, red_phase, SumOp());
       float mu_d = 0.0f, rsd;  // mu_d: mean of (x - shift)
       if constexpr (RMS) {
         rsd = acc_rsqrt(red1[0] * inv_n + eps);
       } else {
         mu_d = red1[0] * inv_n;
-        float red2[1] = {0.0f};
+        float q[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           if (tg + k * GROUP < nvec) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-              const float d = xv[k * VEC + e] - mu_d;
-              red2[0] += d * d;
+              const int j = k * VEC + e;
+              const float d = xv[j] - mu_d;
+              q[j & 3] = fmaf(d, d, q[j & 3]);
             }
           }
         }
-        group_reduce<GROUP, 1>(red2, rs->red, grp, tg, phase, SumOp());
+        float red2[1] = {(q[0] + q[1]) + (q[2] + q[3])};
+        group_reduce<GROUP, 1>(red2, rs->red, grp, tg, red_phase, SumOp());
         rsd = acc_rsqrt(red2[0] * inv_n + eps);
       }
-      const float mu = shift + mu_d;
+      // y = ((d - mu_d) * rstd) * gamma + beta as two FMAs: fma(fma(d, rstd, -mu_d*rstd), gamma, beta)
+      const float c = -mu_d * rsd;
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
@@ -126,48 +131,45 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           float o[VEC];
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            const float t = (xv[k * VEC + e] - mu_d) * rsd * gw[k * VEC + e];
-            o[e] = RMS ? t : t + gb[k * VEC + e];
+            const int j = k * VEC + e;
+            if constexpr (RMS) o[e] = (xv[j] * rsd) * gw[j];
+            else o[e] = fmaf(fmaf(xv[j], rsd, c), gw[j], gb[j]);
           }
           sts128(rbase + v * 16, P::pack(o));
         }
       }
       if (tg == 0) {
-        if (!RMS && mean) mean[row] = mu;
+        if (!RMS && mean) mean[row] = shift + mu_d;
         if (rstd) rstd[row] = rsd;
       }
     }
-    ring_consumer_release(rs, g, i);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(i);
+    ring_consumer_release(rs, cur);
+    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(i);
+  if (tid == 0) prod.epilogue(cur, i);
 }
 
 // Backward: stage = [dy tile | x tile]; dx overwrites the dy tile.  Every thread also accumulates
 // dgamma/dbeta for its own columns over all rows its group sees and writes them, at the end, as
 // partial row (blockIdx.x * NG + group) of ws ([P][2][N] fp32).  WGRAD = false skips that.
 // dx must not be null (a backward without dx goes through the generic weight-gradient kernels).
+//
+// Per row: s1 = sum(gamma*dy), s2 = sum(gamma*dy*xhat), xhat = (x - mean) * rstd,
+// dx = rstd * (gamma*dy - (xhat*s2 + s1)/N)   (RMS: mean = 0, s1 = 0).
 template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD>
 __global__ void __launch_bounds__(kRingThreads, 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx,
                      float* __restrict__ ws, int64_t M, int N, int S, int RPG, int* status) {
   using P = Pack16<T>;
-  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingConsumerThreads / GROUP;
+  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   RingShared* rs = reinterpret_cast<RingShared*>(smem_raw);
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.M = M;
-  g.row_bytes = static_cast<uint32_t>(N) * sizeof(T);
-  g.TR = NG * RPG;
-  g.S = S;
-  g.stage_bytes = 2u * static_cast<uint32_t>(g.TR) * g.row_bytes;
-  g.ntiles = (M + g.TR - 1) / g.TR;
-  const uint32_t slot = static_cast<uint32_t>(g.TR) * g.row_bytes;
-
-  ring_init(rs, S, kRingConsumerThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S, 2);
+  ring_init(rs, S, kRingThreads / 32);
   const int tid = threadIdx.x;
   RingProducer<2> prod(rs, stages, g, status);
   prod.in[0] = reinterpret_cast<const unsigned char*>(dy);
@@ -183,34 +185,36 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   load_weights<WT, GROUP, VPT, VEC>(gamma, 1.0f, nvec, tg, gw);
 #pragma unroll
   for (int e = 0; e < EPT; ++e) { dg[e] = 0.0f; db[e] = 0.0f; }
-  int phase = 0;
+  int red_phase = 0;
+  const uint32_t stages_u32 = smem_u32(stages);
 
-  const int64_t n = g.my_tiles();
+  RingCursor cur;
+  cur.start(g);
   int64_t i = 0;
-  for (; i < n; ++i) {
-    const int64_t row0 = g.tile_row0(i);
-    // row statistics of this tile: issued before the wait so their latency hides behind it
-    float mu_r[4], rs_r[4];  // RPG <= 4
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int64_t row = row0 + grp * RPG + r;
-      const bool ok = r < RPG && row < M;
-      mu_r[r] = (!RMS && ok) ? __ldg(mean + row) : 0.0f;
-      rs_r[r] = ok ? __ldg(rstd + row) : 0.0f;
+  for (; i < g.my_tiles; ++i, cur.advance(g)) {
+    // statistics of this group's first row in the tile: issued before the wait, so the global-load
+    // latency hides behind it (later rows of a multi-row tile load theirs in place)
+    const int64_t row_first = cur.row0 + grp * RPG;
+    float mu_p = 0.0f, rs_p = 0.0f;
+    if (row_first < M) {
+      if (!RMS) mu_p = __ldg(mean + row_first);
+      rs_p = __ldg(rstd + row_first);
     }
-    if (!ring_consumer_wait(rs, g, i, status)) break;
-    const uint32_t sbase = smem_u32(stages + static_cast<size_t>(i % S) * g.stage_bytes);
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      if (r >= RPG) break;
+    if (!ring_consumer_wait(rs, cur, status)) break;
+    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
+    for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
-      const int64_t row = row0 + lr;
+      const int64_t row = row_first + r;
       if (row >= M) break;  // uniform over the group
       const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
-      const uint32_t xbase = dbase + slot;
-      const float mu = mu_r[r], rsd = rs_r[r];
+      const uint32_t xbase = dbase + g.slot_bytes;
+      float mu = mu_p, rsd = rs_p;
+      if (r > 0) {
+        if (!RMS) mu = __ldg(mean + row);
+        rsd = __ldg(rstd + row);
+      }
       float gv[EPT], xh[EPT];  // gamma*dy and xhat
-      float red[2] = {0.0f, 0.0f};
+      float p2[2] = {0.0f, 0.0f}, p1[2] = {0.0f, 0.0f};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
@@ -223,10 +227,10 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
             const int j = k * VEC + e;
             xh[j] = (xh[j] - mu) * rsd;
             gv[j] = dv[e] * gw[j];
-            red[0] += gv[j] * xh[j];
-            if (!RMS) red[1] += gv[j];
+            p2[j & 1] = fmaf(gv[j], xh[j], p2[j & 1]);
+            if (!RMS) p1[j & 1] += gv[j];
             if (WGRAD) {
-              dg[j] += dv[e] * xh[j];
+              dg[j] = fmaf(dv[e], xh[j], dg[j]);
               if (!RMS) db[j] += dv[e];
             }
           }
@@ -235,23 +239,37 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
           for (int e = 0; e < VEC; ++e) { gv[k * VEC + e] = 0.0f; xh[k * VEC + e] = 0.0f; }
         }
       }
-      group_reduce<GROUP, 2>(red, rs->red, grp, tg, phase, SumOp());
-      const float a = red[0] * inv_n, b = RMS ? 0.0f : red[1] * inv_n;
+      float ar, br;
+      if constexpr (RMS) {
+        float red[1] = {p2[0] + p2[1]};
+        group_reduce<GROUP, 1>(red, rs->red, grp, tg, red_phase, SumOp());
+        ar = red[0] * inv_n * rsd;
+        br = 0.0f;
+      } else {
+        float red[2] = {p2[0] + p2[1], p1[0] + p1[1]};
+        group_reduce<GROUP, 2>(red, rs->red, grp, tg, red_phase, SumOp());
+        ar = red[0] * inv_n * rsd;
+        br = red[1] * inv_n * rsd;
+      }
+      // dx = rstd*gv - (xhat*(s2/N)*rstd + (s1/N)*rstd): two FMAs per element
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
           float o[VEC];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) o[e] = rsd * (gv[k * VEC + e] - (xh[k * VEC + e] * a + b));
+          for (int e = 0; e < VEC; ++e) {
+            const int j = k * VEC + e;
+            o[e] = fmaf(gv[j], rsd, -fmaf(xh[j], ar, br));
+          }
           sts128(dbase + v * 16, P::pack(o));
         }
       }
     }
-    ring_consumer_release(rs, g, i);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(i);
+    ring_consumer_release(rs, cur);
+    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(i);
+  if (tid == 0) prod.epilogue(cur, i);
 
   if (WGRAD) {
     const int64_t prow = static_cast<int64_t>(blockIdx.x) * NG + grp;

@@ -27,12 +27,12 @@ inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int
   const int64_t nvec = N / vec;
   const int vpt = ept / vec;
   int group = 32;
-  while (group <= kRingConsumerThreads && static_cast<int64_t>(group) * vpt < nvec) group *= 2;
-  if (group > kRingConsumerThreads) return p;
+  while (group <= kRingThreads && static_cast<int64_t>(group) * vpt < nvec) group *= 2;
+  if (group > kRingThreads) return p;
   p.group = group;
-  p.ng = kRingConsumerThreads / group;
+  p.ng = kRingThreads / group;
   const int64_t row_bytes = N * esize;
-  const int64_t target = nin == 1 ? 32768 : 16384;  // bytes per tensor per tile
+  const int64_t target = 32768;  // bytes per tensor per tile
   int64_t rpg = target / (p.ng * row_bytes);
   // keep at least ~4 tiles per CTA when there are few rows
   while (rpg > 1 && (M + p.ng * rpg - 1) / (p.ng * rpg) < 4LL * sm_count) --rpg;

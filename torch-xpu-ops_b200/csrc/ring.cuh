@@ -10,37 +10,50 @@
 //
 // Stage layout: NIN input tiles back to back (tile k at k * TR * row_bytes); the result overwrites
 // input tile 0.  Tile i of a CTA is global tile blockIdx.x + i * gridDim.x.
+//
+// All per-tile bookkeeping (stage index, barrier phase, first row) is carried incrementally in a
+// RingCursor: with one or two rows per tile, a 64-bit division per tile would cost more
+// instructions than the arithmetic on the row.
 #pragma once
 #include "common.cuh"
 
 namespace b2n {
 
 constexpr int kMaxStages = 16;
-constexpr int kRingHeaderBytes = 1024;            // barriers + flags + reduction scratch
-constexpr int kRingRedFloats = 128;               // reduction scratch inside the header
-constexpr int kRingConsumerThreads = 512;
-constexpr int kRingThreads = kRingConsumerThreads;  // thread 0 doubles as the producer
+constexpr int kRingHeaderBytes = 1024;  // barriers + reduction scratch
+constexpr int kRingRedFloats = 160;     // reduction scratch inside the header
+constexpr int kRingThreads = 512;       // 16 warps; thread 0 doubles as the producer
 
 struct RingShared {
   uint64_t full[kMaxStages];  // tile landed in the stage (bulk-copy bytes counted)
-  uint64_t done[kMaxStages];  // every consumer warp finished writing the stage's result
+  uint64_t done[kMaxStages];  // every warp finished writing the stage's result
   int pad[4];
   float red[kRingRedFloats];  // per-group reduction scratch, double-buffered
 };
 static_assert(sizeof(RingShared) <= kRingHeaderBytes, "ring header too large");
 
 struct RingGeom {
-  int64_t M;           // rows
-  uint32_t row_bytes;  // bytes per row of one tensor (multiple of 16)
-  int TR;              // rows per tile
-  int S;               // stages
+  int64_t M;            // rows
+  int64_t tile_stride;  // rows between consecutive tiles of this CTA = gridDim.x * TR
+  int64_t my_tiles;     // tiles this CTA processes
+  int64_t first_row;    // first row of this CTA's tile 0
+  uint32_t row_bytes;   // bytes per row of one tensor (multiple of 16)
+  uint32_t slot_bytes;  // TR * row_bytes: one tensor's share of a stage
   uint32_t stage_bytes;
-  int64_t ntiles;
-  __device__ __forceinline__ int64_t my_tiles() const {
-    return ntiles > blockIdx.x ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  }
-  __device__ __forceinline__ int64_t tile_row0(int64_t i) const {
-    return (static_cast<int64_t>(blockIdx.x) + i * gridDim.x) * TR;
+  int TR;               // rows per tile
+  int S;                // stages
+
+  __device__ __forceinline__ void init(int64_t M_, int N, int esize, int TR_, int S_, int nin) {
+    M = M_;
+    TR = TR_;
+    S = S_;
+    row_bytes = static_cast<uint32_t>(N) * esize;
+    slot_bytes = static_cast<uint32_t>(TR_) * row_bytes;
+    stage_bytes = slot_bytes * nin;
+    tile_stride = static_cast<int64_t>(gridDim.x) * TR_;
+    first_row = static_cast<int64_t>(blockIdx.x) * TR_;
+    const int64_t ntiles = (M_ + TR_ - 1) / TR_;
+    my_tiles = ntiles > blockIdx.x ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   }
   __device__ __forceinline__ uint32_t tile_bytes(int64_t row0) const {
     const int64_t rows = (M - row0 < TR) ? (M - row0) : TR;
@@ -48,11 +61,23 @@ struct RingGeom {
   }
 };
 
-__device__ __forceinline__ void ring_init(RingShared* rs, int S, int consumer_warps) {
+// Where one tile lives: its stage, the parity of that stage's barriers for this use, its first row.
+struct RingCursor {
+  int64_t row0;
+  int s;
+  uint32_t phase;
+  __device__ __forceinline__ void start(const RingGeom& g) { row0 = g.first_row; s = 0; phase = 0; }
+  __device__ __forceinline__ void advance(const RingGeom& g) {
+    row0 += g.tile_stride;
+    if (++s == g.S) { s = 0; phase ^= 1u; }
+  }
+};
+
+__device__ __forceinline__ void ring_init(RingShared* rs, int S, int warps) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&rs->full[s], 1);
-      mbar_init(&rs->done[s], consumer_warps);
+      mbar_init(&rs->done[s], warps);
     }
     mbar_init_fence();
   }
@@ -70,87 +95,105 @@ template <int NIN> struct RingProducer {
   const unsigned char* in[NIN];
   unsigned char* out;
   int* status;
-  int64_t n;             // tiles of this CTA
-  int64_t loads_issued;  // tiles whose loads have been issued
+  int64_t loads_left;  // tiles whose loads have not been issued yet
+  RingCursor next;     // the next tile to load
+  bool have_prev;      // a store has been issued before (its stage is the next to refill)
 
   __device__ __forceinline__ RingProducer(RingShared* rs_, unsigned char* stages_, const RingGeom& g_, int* status_)
-      : rs(rs_), stages(stages_), g(g_), out(nullptr), status(status_), n(g_.my_tiles()), loads_issued(0) {}
-
-  __device__ __forceinline__ void issue_load(int64_t i) {
-    const int s = static_cast<int>(i % g.S);
-    const int64_t row0 = g.tile_row0(i);
-    const uint32_t bytes = g.tile_bytes(row0);
-    const uint32_t slot = static_cast<uint32_t>(g.TR) * g.row_bytes;
-    unsigned char* dst = stages + static_cast<size_t>(s) * g.stage_bytes;
-    mbar_arrive_expect_tx(&rs->full[s], bytes * NIN);
+      : rs(rs_), stages(stages_), g(g_), out(nullptr), status(status_), loads_left(g_.my_tiles), have_prev(false) {
+    next.start(g_);
+  }
+  __device__ __forceinline__ void issue_next_load() {
+    const uint32_t bytes = g.tile_bytes(next.row0);
+    unsigned char* dst = stages + static_cast<size_t>(next.s) * g.stage_bytes;
+    const size_t goff = static_cast<size_t>(next.row0) * g.row_bytes;
+    mbar_arrive_expect_tx(&rs->full[next.s], bytes * NIN);
 #pragma unroll
-    for (int k = 0; k < NIN; ++k) bulk_g2s(dst + k * slot, in[k] + row0 * g.row_bytes, bytes, &rs->full[s]);
+    for (int k = 0; k < NIN; ++k) bulk_g2s(dst + k * g.slot_bytes, in[k] + goff, bytes, &rs->full[next.s]);
+    next.advance(g);
+    --loads_left;
   }
   // Before the first tile: fill the ring.
   __device__ __forceinline__ void prologue() {
-    const int64_t pre = n < g.S ? n : g.S;
-    for (int64_t i = 0; i < pre; ++i) issue_load(i);
-    loads_issued = pre;
+    for (int k = 0; k < g.S && loads_left > 0; ++k) issue_next_load();
   }
-  // After this thread's own work on tile i: send the tile out once every warp has finished it, then
-  // refill the stage of tile i-1, whose store (now the second newest group) has read its source.
-  __device__ __forceinline__ bool after_tile(int64_t i) {
-    const int s = static_cast<int>(i % g.S);
-    if (!mbar_wait(&rs->done[s], static_cast<uint32_t>((i / g.S) & 1), status)) return false;
-    const int64_t row0 = g.tile_row0(i);
-    bulk_s2g(out + row0 * g.row_bytes, stages + static_cast<size_t>(s) * g.stage_bytes, g.tile_bytes(row0));
+  // After this thread's own work on the tile at `cur`: send the tile out once every warp has
+  // finished it, then refill the stage of the tile before it, whose store (now the second newest
+  // bulk group) has finished reading shared memory.  With S stages in rotation that stage is
+  // exactly where the next tile to load belongs.
+  __device__ __forceinline__ bool after_tile(const RingCursor& cur) {
+    if (!mbar_wait(&rs->done[cur.s], cur.phase, status)) return false;
+    bulk_s2g(out + static_cast<size_t>(cur.row0) * g.row_bytes, stages + static_cast<size_t>(cur.s) * g.stage_bytes,
+             g.tile_bytes(cur.row0));
     bulk_commit();
-    if (i >= 1 && loads_issued < n) {
+    if (have_prev && loads_left > 0) {
       bulk_wait_read<1>();
-      issue_load(loads_issued);  // == i - 1 + S
-      ++loads_issued;
+      issue_next_load();
     }
+    have_prev = true;
     return true;
   }
-  // After the last tile, or after a wait gave up at tile `reached`: nothing of this CTA may still be
-  // in flight when its shared memory goes away.
-  __device__ __forceinline__ void epilogue(int64_t reached) {
-    for (int64_t j = reached; j < loads_issued; ++j)
-      mbar_wait(&rs->full[j % g.S], static_cast<uint32_t>((j / g.S) & 1), status);
+  // After the last tile, or after a wait gave up with loaded tiles not yet consumed starting at
+  // `cur`: nothing of this CTA may still be in flight when its shared memory goes away.
+  __device__ __forceinline__ void epilogue(RingCursor cur, int64_t tiles_done) {
+    const int64_t issued = g.my_tiles - loads_left;
+    for (int64_t j = tiles_done; j < issued; ++j) {
+      mbar_wait(&rs->full[cur.s], cur.phase, status);
+      cur.advance(g);
+    }
     bulk_wait_all<0>();
   }
 };
 
 // Consumer side of one tile: wait for it, and (after the caller's arithmetic) hand it back.
-__device__ __forceinline__ bool ring_consumer_wait(RingShared* rs, const RingGeom& g, int64_t i, int* status) {
-  return mbar_wait(&rs->full[i % g.S], static_cast<uint32_t>((i / g.S) & 1), status);
+__device__ __forceinline__ bool ring_consumer_wait(RingShared* rs, const RingCursor& cur, int* status) {
+  return mbar_wait(&rs->full[cur.s], cur.phase, status);
 }
-__device__ __forceinline__ void ring_consumer_release(RingShared* rs, const RingGeom& g, int64_t i) {
+__device__ __forceinline__ void ring_consumer_release(RingShared* rs, const RingCursor& cur) {
   fence_async_smem();
   __syncwarp();
-  if ((threadIdx.x & 31) == 0) mbar_arrive(&rs->done[i % g.S]);
+  if ((threadIdx.x & 31) == 0) mbar_arrive(&rs->done[cur.s]);
 }
 
 // ---- reductions over the GROUP threads that share a row ----------------------------------------
 // GROUP == 32: shuffles only.  GROUP > 32: per-warp partials through the header scratch and a
 // named barrier private to the group (id 1 + group).  `phase` alternates the scratch half so one
-// barrier per reduction is enough.  K values are reduced together.
+// barrier per reduction is enough.  K values (K <= 4) are reduced together; scratch layout
+// [group][phase][K][W] so a thread reads one value's W partials with 16-byte loads.
 template <int GROUP, int K, typename Op>
 __device__ __forceinline__ void group_reduce(float (&v)[K], float* red, int group, int tg, int& phase, Op op) {
 #pragma unroll
   for (int k = 0; k < K; ++k) v[k] = warp_reduce(v[k], op);
   if constexpr (GROUP > 32) {
     constexpr int W = GROUP / 32;
-    static_assert((kRingConsumerThreads / 32) * 2 * 2 <= kRingRedFloats, "scratch too small");
-    static_assert(K <= 2, "scratch sized for two values");
-    float* buf = red + ((group * 2 + phase) * W) * 2;
+    static_assert(K <= 4, "scratch sized for four values");
+    static_assert((kRingThreads / 32) * 2 * 4 <= kRingRedFloats, "scratch too small");
+    float* buf = red + (group * 2 + phase) * (4 * W);
     phase ^= 1;
     if ((tg & 31) == 0) {
 #pragma unroll
-      for (int k = 0; k < K; ++k) buf[(tg >> 5) * 2 + k] = v[k];
+      for (int k = 0; k < K; ++k) buf[k * W + (tg >> 5)] = v[k];
     }
     named_bar_sync(1 + group, GROUP);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      float r = buf[k];
+      float p[W];
+      if constexpr (W % 4 == 0) {
 #pragma unroll
-      for (int w = 1; w < W; ++w) r = op(r, buf[w * 2 + k]);
-      v[k] = r;
+        for (int w = 0; w < W; w += 4) {
+          const float4 q = *reinterpret_cast<const float4*>(buf + k * W + w);
+          p[w] = q.x; p[w + 1] = q.y; p[w + 2] = q.z; p[w + 3] = q.w;
+        }
+      } else {
+#pragma unroll
+        for (int w = 0; w < W; ++w) p[w] = buf[k * W + w];
+      }
+      // fixed pairwise order: identical in every thread, short dependency chain
+#pragma unroll
+      for (int stride = 1; stride < W; stride *= 2)
+#pragma unroll
+        for (int w = 0; w + stride < W; w += 2 * stride) p[w] = op(p[w], p[w + stride]);
+      v[k] = p[0];
     }
   }
 }

@@ -30,20 +30,14 @@ __global__ void __launch_bounds__(kRingThreads, 1)
 softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S, int RPG,
                         int* status) {
   using P = Pack16<T>;
-  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingConsumerThreads / GROUP;
+  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   RingShared* rs = reinterpret_cast<RingShared*>(smem_raw);
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.M = M;
-  g.row_bytes = static_cast<uint32_t>(N) * sizeof(T);
-  g.TR = NG * RPG;
-  g.S = S;
-  g.stage_bytes = static_cast<uint32_t>(g.TR) * g.row_bytes;
-  g.ntiles = (M + g.TR - 1) / g.TR;
-
-  ring_init(rs, S, kRingConsumerThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S, 1);
+  ring_init(rs, S, kRingThreads / 32);
   const int tid = threadIdx.x;
   RingProducer<1> prod(rs, stages, g, status);
   prod.in[0] = reinterpret_cast<const unsigned char*>(x);
@@ -53,49 +47,53 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
-  int phase = 0;
+  int red_phase = 0;
   const float ninf = acc_neg_inf<float>();
+  const uint32_t stages_u32 = smem_u32(stages);
 
-  const int64_t n = g.my_tiles();
+  RingCursor cur;
+  cur.start(g);
   int64_t i = 0;
-  for (; i < n; ++i) {
-    if (!ring_consumer_wait(rs, g, i, status)) break;
-    const int64_t row0 = g.tile_row0(i);
-    const uint32_t sbase = smem_u32(stages + static_cast<size_t>(i % S) * g.stage_bytes);
+  for (; i < g.my_tiles; ++i, cur.advance(g)) {
+    if (!ring_consumer_wait(rs, cur, status)) break;
+    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
-      if (row0 + lr >= M) break;  // uniform over the group
+      if (cur.row0 + lr >= M) break;  // uniform over the group
       const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       float xv[EPT];
-      float mx[1] = {ninf};
+      float pm[4] = {ninf, ninf, ninf, ninf};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
           P::unpack(lds128(rbase + v * 16), &xv[k * VEC]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) mx[0] = fmaxf(mx[0], xv[k * VEC + e]);
+          for (int e = 0; e < VEC; ++e) pm[e & 3] = fmaxf(pm[e & 3], xv[k * VEC + e]);
         } else {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) xv[k * VEC + e] = ninf;
         }
       }
-      group_reduce<GROUP, 1>(mx, rs->red, grp, tg, phase, MaxOp());
+      float mx[1] = {fmaxf(fmaxf(pm[0], pm[1]), fmaxf(pm[2], pm[3]))};
+      group_reduce<GROUP, 1>(mx, rs->red, grp, tg, red_phase, MaxOp());
       const RowExp<T> rexp(mx[0]);
-      float sum[1] = {0.0f};
+      float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         if (tg + k * GROUP < nvec) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
             const float ex = rexp(xv[k * VEC + e]);
-            sum[0] += ex;
+            ps[e & 3] += ex;
             if (!LOG) xv[k * VEC + e] = ex;
           }
         }
       }
-      group_reduce<GROUP, 1>(sum, rs->red, grp, tg, phase, SumOp());
+      float sum[1] = {(ps[0] + ps[1]) + (ps[2] + ps[3])};
+      group_reduce<GROUP, 1>(sum, rs->red, grp, tg, red_phase, SumOp());
       const float lg = LOG ? logf(sum[0]) : 0.0f;
+      const float off = mx[0] + lg;  // 16-bit log-softmax: x - (max + log sum) in one subtraction
       const float inv = LOG ? 0.0f : 1.0f / sum[0];
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
@@ -104,41 +102,36 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
           float o[VEC];
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            if constexpr (LOG) o[e] = (xv[k * VEC + e] - mx[0]) - lg;
-            else if constexpr (sizeof(T) == 4) o[e] = xv[k * VEC + e] / sum[0];
-            else o[e] = xv[k * VEC + e] * inv;
+            const float t = xv[k * VEC + e];
+            if constexpr (LOG) o[e] = sizeof(T) == 4 ? (t - mx[0]) - lg : t - off;
+            else if constexpr (sizeof(T) == 4) o[e] = t / sum[0];
+            else o[e] = t * inv;
           }
           sts128(rbase + v * 16, P::pack(o));
         }
       }
     }
-    ring_consumer_release(rs, g, i);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(i);
+    ring_consumer_release(rs, cur);
+    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(i);
+  if (tid == 0) prod.epilogue(cur, i);
 }
 
 // stage = [dy tile | y tile]; dx overwrites the dy tile.
+// softmax: dx = y*(dy - sum(y*dy)); log-softmax: dx = dy - exp(y)*sum(dy).
 template <typename T, bool LOG, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingThreads, 1)
 softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t M,
                         int N, int S, int RPG, int* status) {
   using P = Pack16<T>;
-  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingConsumerThreads / GROUP;
+  constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   RingShared* rs = reinterpret_cast<RingShared*>(smem_raw);
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.M = M;
-  g.row_bytes = static_cast<uint32_t>(N) * sizeof(T);
-  g.TR = NG * RPG;
-  g.S = S;
-  g.stage_bytes = 2u * static_cast<uint32_t>(g.TR) * g.row_bytes;
-  g.ntiles = (M + g.TR - 1) / g.TR;
-  const uint32_t slot = static_cast<uint32_t>(g.TR) * g.row_bytes;
-
-  ring_init(rs, S, kRingConsumerThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S, 2);
+  ring_init(rs, S, kRingThreads / 32);
   const int tid = threadIdx.x;
   RingProducer<2> prod(rs, stages, g, status);
   prod.in[0] = reinterpret_cast<const unsigned char*>(dy);
@@ -149,21 +142,22 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
 
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
-  int phase = 0;
+  int red_phase = 0;
+  const uint32_t stages_u32 = smem_u32(stages);
 
-  const int64_t n = g.my_tiles();
+  RingCursor cur;
+  cur.start(g);
   int64_t i = 0;
-  for (; i < n; ++i) {
-    if (!ring_consumer_wait(rs, g, i, status)) break;
-    const int64_t row0 = g.tile_row0(i);
-    const uint32_t sbase = smem_u32(stages + static_cast<size_t>(i % S) * g.stage_bytes);
+  for (; i < g.my_tiles; ++i, cur.advance(g)) {
+    if (!ring_consumer_wait(rs, cur, status)) break;
+    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
-      if (row0 + lr >= M) break;  // uniform over the group
+      if (cur.row0 + lr >= M) break;  // uniform over the group
       const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
-      const uint32_t ybase = dbase + slot;
+      const uint32_t ybase = dbase + g.slot_bytes;
       float dv[EPT], yv[EPT];
-      float sum[1] = {0.0f};
+      float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
@@ -171,13 +165,18 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
           P::unpack(lds128(dbase + v * 16), &dv[k * VEC]);
           P::unpack(lds128(ybase + v * 16), &yv[k * VEC]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) sum[0] += LOG ? dv[k * VEC + e] : dv[k * VEC + e] * yv[k * VEC + e];
+          for (int e = 0; e < VEC; ++e) {
+            const int j = k * VEC + e;
+            if constexpr (LOG) ps[e & 3] += dv[j];
+            else ps[e & 3] = fmaf(dv[j], yv[j], ps[e & 3]);
+          }
         } else {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) { dv[k * VEC + e] = 0.0f; yv[k * VEC + e] = 0.0f; }
         }
       }
-      group_reduce<GROUP, 1>(sum, rs->red, grp, tg, phase, SumOp());
+      float sum[1] = {(ps[0] + ps[1]) + (ps[2] + ps[3])};
+      group_reduce<GROUP, 1>(sum, rs->red, grp, tg, red_phase, SumOp());
       const float s = sum[0];
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
@@ -189,7 +188,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
             const float d = dv[k * VEC + e], yy = yv[k * VEC + e];
             if constexpr (LOG) {
               const float ey = sizeof(T) == 4 ? expf(yy) : ex2_approx(yy * kLog2e);
-              o[e] = d - ey * s;
+              o[e] = fmaf(-ey, s, d);
             } else {
               o[e] = yy * (d - s);
             }
@@ -198,10 +197,10 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
         }
       }
     }
-    ring_consumer_release(rs, g, i);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(i);
+    ring_consumer_release(rs, cur);
+    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(i);
+  if (tid == 0) prod.epilogue(cur, i);
 }
 
 }  // namespace b2n
