@@ -202,6 +202,15 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
                : "memory");
 }
 
+// Packed fp32 arithmetic (sm_100: one instruction works on two fp32 lanes, each rounded exactly as
+// its scalar counterpart).  The row kernels are bound by instruction issue, not by the FMA pipe,
+// so halving the instruction count of the element-wise math is a direct win.
+__device__ __forceinline__ float2 bcast2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float hsum2(float2 a) { return a.x + a.y; }
+
 // 16 bytes <-> VEC floats for each storage type (VEC = 16 / sizeof(T))
 template <typename T> struct Pack16;
 template <> struct Pack16<float> {
@@ -211,6 +220,13 @@ template <> struct Pack16<float> {
   }
   static __device__ __forceinline__ uint4 pack(const float* f) {
     return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+  static __device__ __forceinline__ void unpack2(const uint4& p, float2* f) {
+    f[0] = make_float2(__uint_as_float(p.x), __uint_as_float(p.y));
+    f[1] = make_float2(__uint_as_float(p.z), __uint_as_float(p.w));
+  }
+  static __device__ __forceinline__ uint4 pack2(const float2* f) {
+    return make_uint4(__float_as_uint(f[0].x), __float_as_uint(f[0].y), __float_as_uint(f[1].x), __float_as_uint(f[1].y));
   }
 };
 template <> struct Pack16<bf16> {
@@ -232,6 +248,20 @@ template <> struct Pack16<bf16> {
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
   }
+  static __device__ __forceinline__ void unpack2(const uint4& p, float2* f) {
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  }
+  static __device__ __forceinline__ uint4 pack2(const float2* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __float22bfloat162_rn(f[i]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
 };
 template <> struct Pack16<f16> {
   static constexpr int VEC = 8;
@@ -248,6 +278,20 @@ template <> struct Pack16<f16> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  static __device__ __forceinline__ void unpack2(const uint4& p, float2* f) {
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+  }
+  static __device__ __forceinline__ uint4 pack2(const float2* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __float22half2_rn(f[i]);
       w[i] = *reinterpret_cast<uint32_t*>(&h);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);

@@ -15,15 +15,20 @@ namespace b2n {
 // thread tg of a group owns vectors tg + k*GROUP (k < VPT) of every row its group processes, so its
 // gamma/beta values — and, in the backward, its dgamma/dbeta accumulators — stay in registers for
 // the whole launch.
+// Values are kept as float2 pairs of neighbouring columns: the element-wise math runs on the
+// packed fp32 instructions of sm_100 (fma2 / add2 / mul2 in common.cuh).
 template <typename WT, int GROUP, int VPT, int VEC>
 __device__ __forceinline__ void load_weights(const WT* __restrict__ w, float fill, int nvec, int tg,
-                                             float (&out)[VPT * VEC]) {
+                                             float2 (&out)[VPT * VEC / 2]) {
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = tg + k * GROUP;
 #pragma unroll
-    for (int e = 0; e < VEC; ++e)
-      out[k * VEC + e] = (w != nullptr && v < nvec) ? to_acc<float>(w[v * VEC + e]) : fill;
+    for (int e = 0; e < VEC; e += 2) {
+      const bool ok = w != nullptr && v < nvec;
+      out[(k * VEC + e) / 2] = make_float2(ok ? to_acc<float>(w[v * VEC + e]) : fill,
+                                           ok ? to_acc<float>(w[v * VEC + e + 1]) : fill);
+    }
   }
 }
 
@@ -34,6 +39,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
                      int N, float eps, int S, int RPG, int* status) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
+  constexpr int RB = 2;  // rows a group works on at once
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   RingShared* rs = reinterpret_cast<RingShared*>(smem_raw);
   unsigned char* stages = smem_raw + kRingHeaderBytes;
@@ -51,7 +57,8 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
   const float inv_n = 1.0f / static_cast<float>(N);
-  float gw[EPT], gb[EPT];
+  constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
+  float2 gw[HP], gb[HP];
   load_weights<WT, GROUP, VPT, VEC>(gamma, 1.0f, nvec, tg, gw);
   if constexpr (!RMS) load_weights<WT, GROUP, VPT, VEC>(beta, 0.0f, nvec, tg, gb);
   int red_phase = 0;
@@ -63,84 +70,111 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   for (; i < g.my_tiles; ++i, cur.advance(g)) {
     if (!ring_consumer_wait(rs, cur, status)) break;
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
-    for (int r = 0; r < RPG; ++r) {
-      const int lr = grp * RPG + r;
-      const int64_t row = cur.row0 + lr;
-      if (row >= M) break;  // uniform over the group
-      const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
-      // Layer norm works on d = x - shift, shift = the row's first element (a shared-memory
-      // broadcast read): a large common offset then cancels exactly instead of being rounded away
-      // in the row sum.  RMS norm needs the raw values (shift = 0).
-      float shift = 0.0f;
-      if constexpr (!RMS) {
-        float first[VEC];
-        P::unpack(lds128(rbase), first);
-        shift = first[0];
-      }
-      float xv[EPT];
-      float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // A group takes its rows of the tile RB at a time: the partial sums of RB rows go through ONE
+    // group reduction (one barrier, RB values), which halves the time the group's warps spend
+    // waiting on each other when a single group spans the whole CTA.
+    for (int r = 0; r < RPG; r += RB) {
+      const int lr0 = grp * RPG + r;
+      const int64_t row_a = cur.row0 + lr0;
+      if (row_a >= M) break;  // uniform over the group
+      bool valid[RB];
+      uint32_t rbase[RB];
+      float shift[RB];
+      float2 xv[RB][HP];
+      float red1[RB];
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        const int v = tg + k * GROUP;
-        if (v < nvec) {
-          P::unpack(lds128(rbase + v * 16), &xv[k * VEC]);
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const int j = k * VEC + e;
-            if constexpr (RMS) {
-              part[j & 3] = fmaf(xv[j], xv[j], part[j & 3]);
-            } else {
-              xv[j] -= shift;
-              part[j & 3] += xv[j];
-            }
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < VEC; ++e) xv[k * VEC + e] = 0.0f;
+      for (int b = 0; b < RB; ++b) {
+        valid[b] = (r + b < RPG) && (row_a + b < M);
+        rbase[b] = sbase + static_cast<uint32_t>(lr0 + b) * g.row_bytes;
+        // Layer norm works on d = x - shift, shift = the row's first element (a shared-memory
+        // broadcast read): a large common offset then cancels exactly instead of being rounded
+        // away in the row sum.  RMS norm needs the raw values (shift = 0).
+        shift[b] = 0.0f;
+        if (!RMS && valid[b]) {
+          float2 first[VH];
+          P::unpack2(lds128(rbase[b]), first);
+          shift[b] = first[0].x;
         }
-      }
-      float red1[1] = {(part[0] + part[1]) + (part[2] + part[3])};
-      group_reduce<GROUP, 1>(red1, rs->red, grp, tg, red_phase, SumOp());
-      float mu_d = 0.0f, rsd;  // mu_d: mean of (x - shift)
-      if constexpr (RMS) {
-        rsd = acc_rsqrt(red1[0] * inv_n + eps);
-      } else {
-        mu_d = red1[0] * inv_n;
-        float q[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float2 nshift = bcast2(-shift[b]);
+        float2 part[2] = {bcast2(0.0f), bcast2(0.0f)};
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
-          if (tg + k * GROUP < nvec) {
+          const int v = tg + k * GROUP;
+          if (valid[b] && v < nvec) {
+            P::unpack2(lds128(rbase[b] + v * 16), &xv[b][k * VH]);
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-              const int j = k * VEC + e;
-              const float d = xv[j] - mu_d;
-              q[j & 3] = fmaf(d, d, q[j & 3]);
+            for (int e = 0; e < VH; ++e) {
+              const int j = k * VH + e;
+              if constexpr (RMS) {
+                part[j & 1] = fma2(xv[b][j], xv[b][j], part[j & 1]);
+              } else {
+                xv[b][j] = add2(xv[b][j], nshift);
+                part[j & 1] = add2(part[j & 1], xv[b][j]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < VH; ++e) xv[b][k * VH + e] = bcast2(0.0f);
+          }
+        }
+        red1[b] = hsum2(add2(part[0], part[1]));
+      }
+      group_reduce<GROUP, RB>(red1, rs->red, grp, tg, red_phase, SumOp());
+      float mu_d[RB], rsd[RB];  // mu_d: mean of (x - shift)
+      if constexpr (RMS) {
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+          mu_d[b] = 0.0f;
+          rsd[b] = acc_rsqrt(red1[b] * inv_n + eps);
+        }
+      } else {
+        float red2[RB];
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+          mu_d[b] = red1[b] * inv_n;
+          const float2 nmu = bcast2(-mu_d[b]);
+          float2 q[2] = {bcast2(0.0f), bcast2(0.0f)};
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) {
+            if (tg + k * GROUP < nvec) {
+#pragma unroll
+              for (int e = 0; e < VH; ++e) {
+                const int j = k * VH + e;
+                const float2 d = add2(xv[b][j], nmu);
+                q[j & 1] = fma2(d, d, q[j & 1]);
+              }
             }
           }
+          red2[b] = hsum2(add2(q[0], q[1]));
         }
-        float red2[1] = {(q[0] + q[1]) + (q[2] + q[3])};
-        group_reduce<GROUP, 1>(red2, rs->red, grp, tg, red_phase, SumOp());
-        rsd = acc_rsqrt(red2[0] * inv_n + eps);
+        group_reduce<GROUP, RB>(red2, rs->red, grp, tg, red_phase, SumOp());
+#pragma unroll
+        for (int b = 0; b < RB; ++b) rsd[b] = acc_rsqrt(red2[b] * inv_n + eps);
       }
-      // y = ((d - mu_d) * rstd) * gamma + beta as two FMAs: fma(fma(d, rstd, -mu_d*rstd), gamma, beta)
-      const float c = -mu_d * rsd;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        const int v = tg + k * GROUP;
-        if (v < nvec) {
-          float o[VEC];
+      for (int b = 0; b < RB; ++b) {
+        if (!valid[b]) continue;
+        // y = ((d - mu_d) * rstd) * gamma + beta as two FMAs: fma(fma(d, rstd, -mu_d*rstd), gamma, beta)
+        const float2 rs2 = bcast2(rsd[b]);
+        const float2 c2 = bcast2(-mu_d[b] * rsd[b]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const int j = k * VEC + e;
-            if constexpr (RMS) o[e] = (xv[j] * rsd) * gw[j];
-            else o[e] = fmaf(fmaf(xv[j], rsd, c), gw[j], gb[j]);
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tg + k * GROUP;
+          if (v < nvec) {
+            float2 o[VH];
+#pragma unroll
+            for (int e = 0; e < VH; ++e) {
+              const int j = k * VH + e;
+              if constexpr (RMS) o[e] = mul2(mul2(xv[b][j], rs2), gw[j]);
+              else o[e] = fma2(fma2(xv[b][j], rs2, c2), gw[j], gb[j]);
+            }
+            sts128(rbase[b] + v * 16, P::pack2(o));
           }
-          sts128(rbase + v * 16, P::pack(o));
         }
-      }
-      if (tg == 0) {
-        if (!RMS && mean) mean[row] = shift + mu_d;
-        if (rstd) rstd[row] = rsd;
+        if (tg == 0) {
+          if (!RMS && mean) mean[row_a + b] = shift[b] + mu_d[b];
+          if (rstd) rstd[row_a + b] = rsd[b];
+        }
       }
     }
     ring_consumer_release(rs, cur);
@@ -181,10 +215,11 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
   const float inv_n = 1.0f / static_cast<float>(N);
-  float gw[EPT], dg[EPT], db[EPT];
+  constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
+  float2 gw[HP], dg[HP], db[HP];
   load_weights<WT, GROUP, VPT, VEC>(gamma, 1.0f, nvec, tg, gw);
 #pragma unroll
-  for (int e = 0; e < EPT; ++e) { dg[e] = 0.0f; db[e] = 0.0f; }
+  for (int e = 0; e < HP; ++e) { dg[e] = bcast2(0.0f); db[e] = bcast2(0.0f); }
   int red_phase = 0;
   const uint32_t stages_u32 = smem_u32(stages);
 
@@ -213,56 +248,57 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
         if (!RMS) mu = __ldg(mean + row);
         rsd = __ldg(rstd + row);
       }
-      float gv[EPT], xh[EPT];  // gamma*dy and xhat
-      float p2[2] = {0.0f, 0.0f}, p1[2] = {0.0f, 0.0f};
+      const float2 nmu = bcast2(-mu), rs2 = bcast2(rsd);
+      float2 gv[HP], xh[HP];  // gamma*dy and xhat
+      float2 p2 = bcast2(0.0f), p1 = bcast2(0.0f);
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
-          float dv[VEC];
-          P::unpack(lds128(dbase + v * 16), dv);
-          P::unpack(lds128(xbase + v * 16), &xh[k * VEC]);
+          float2 dv[VH];
+          P::unpack2(lds128(dbase + v * 16), dv);
+          P::unpack2(lds128(xbase + v * 16), &xh[k * VH]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const int j = k * VEC + e;
-            xh[j] = (xh[j] - mu) * rsd;
-            gv[j] = dv[e] * gw[j];
-            p2[j & 1] = fmaf(gv[j], xh[j], p2[j & 1]);
-            if (!RMS) p1[j & 1] += gv[j];
+          for (int e = 0; e < VH; ++e) {
+            const int j = k * VH + e;
+            xh[j] = mul2(add2(xh[j], nmu), rs2);
+            gv[j] = mul2(dv[e], gw[j]);
+            p2 = fma2(gv[j], xh[j], p2);
+            if (!RMS) p1 = add2(p1, gv[j]);
             if (WGRAD) {
-              dg[j] = fmaf(dv[e], xh[j], dg[j]);
-              if (!RMS) db[j] += dv[e];
+              dg[j] = fma2(dv[e], xh[j], dg[j]);
+              if (!RMS) db[j] = add2(db[j], dv[e]);
             }
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) { gv[k * VEC + e] = 0.0f; xh[k * VEC + e] = 0.0f; }
+          for (int e = 0; e < VH; ++e) { gv[k * VH + e] = bcast2(0.0f); xh[k * VH + e] = bcast2(0.0f); }
         }
       }
-      float ar, br;
+      float2 nar, nbr;  // -(s2/N)*rstd and -(s1/N)*rstd
       if constexpr (RMS) {
-        float red[1] = {p2[0] + p2[1]};
+        float red[1] = {hsum2(p2)};
         group_reduce<GROUP, 1>(red, rs->red, grp, tg, red_phase, SumOp());
-        ar = red[0] * inv_n * rsd;
-        br = 0.0f;
+        nar = bcast2(-(red[0] * inv_n * rsd));
+        nbr = bcast2(0.0f);
       } else {
-        float red[2] = {p2[0] + p2[1], p1[0] + p1[1]};
+        float red[2] = {hsum2(p2), hsum2(p1)};
         group_reduce<GROUP, 2>(red, rs->red, grp, tg, red_phase, SumOp());
-        ar = red[0] * inv_n * rsd;
-        br = red[1] * inv_n * rsd;
+        nar = bcast2(-(red[0] * inv_n * rsd));
+        nbr = bcast2(-(red[1] * inv_n * rsd));
       }
-      // dx = rstd*gv - (xhat*(s2/N)*rstd + (s1/N)*rstd): two FMAs per element
+      // dx = rstd*gv - (xhat*(s2/N)*rstd + (s1/N)*rstd): two packed FMAs per pair
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
-          float o[VEC];
+          float2 o[VH];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const int j = k * VEC + e;
-            o[e] = fmaf(gv[j], rsd, -fmaf(xh[j], ar, br));
+          for (int e = 0; e < VH; ++e) {
+            const int j = k * VH + e;
+            o[e] = fma2(gv[j], rs2, fma2(xh[j], nar, nbr));
           }
-          sts128(dbase + v * 16, P::pack(o));
+          sts128(dbase + v * 16, P::pack2(o));
         }
       }
     }
@@ -281,10 +317,10 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       if (v < nvec) {
 #pragma unroll
         for (int q = 0; q < VEC / 4; ++q) {
-          const int j = k * VEC + q * 4;
-          *reinterpret_cast<float4*>(wg + v * VEC + q * 4) = make_float4(dg[j], dg[j + 1], dg[j + 2], dg[j + 3]);
+          const int j = (k * VEC + q * 4) / 2;
+          *reinterpret_cast<float4*>(wg + v * VEC + q * 4) = make_float4(dg[j].x, dg[j].y, dg[j + 1].x, dg[j + 1].y);
           if (!RMS)
-            *reinterpret_cast<float4*>(wb + v * VEC + q * 4) = make_float4(db[j], db[j + 1], db[j + 2], db[j + 3]);
+            *reinterpret_cast<float4*>(wb + v * VEC + q * 4) = make_float4(db[j].x, db[j].y, db[j + 1].x, db[j + 1].y);
         }
       }
     }

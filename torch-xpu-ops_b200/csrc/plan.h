@@ -37,6 +37,7 @@ inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int
   // keep at least ~4 tiles per CTA when there are few rows
   while (rpg > 1 && (M + p.ng * rpg - 1) / (p.ng * rpg) < 4LL * sm_count) --rpg;
   p.rpg = static_cast<int>(rpg < 1 ? 1 : (rpg > 4 ? 4 : rpg));
+  if (p.rpg == 3) p.rpg = 2;  // the kernels take a group's rows two at a time
   const int64_t stage = static_cast<int64_t>(nin) * p.ng * p.rpg * row_bytes;
   int64_t s = (static_cast<int64_t>(max_smem) - kRingHeaderBytes) / stage;
   if (s > kMaxStages) s = kMaxStages;

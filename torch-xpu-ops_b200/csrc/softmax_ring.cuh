@@ -61,53 +61,71 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       const int lr = grp * RPG + r;
       if (cur.row0 + lr >= M) break;  // uniform over the group
       const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
-      float xv[EPT];
+      constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
+      float2 xv[HP];
       float pm[4] = {ninf, ninf, ninf, ninf};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
-          P::unpack(lds128(rbase + v * 16), &xv[k * VEC]);
+          P::unpack2(lds128(rbase + v * 16), &xv[k * VH]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) pm[e & 3] = fmaxf(pm[e & 3], xv[k * VEC + e]);
+          for (int e = 0; e < VH; ++e) {
+            pm[(2 * e) & 3] = fmaxf(pm[(2 * e) & 3], xv[k * VH + e].x);
+            pm[(2 * e + 1) & 3] = fmaxf(pm[(2 * e + 1) & 3], xv[k * VH + e].y);
+          }
         } else {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) xv[k * VEC + e] = ninf;
+          for (int e = 0; e < VH; ++e) xv[k * VH + e] = bcast2(ninf);
         }
       }
       float mx[1] = {fmaxf(fmaxf(pm[0], pm[1]), fmaxf(pm[2], pm[3]))};
       group_reduce<GROUP, 1>(mx, rs->red, grp, tg, red_phase, MaxOp());
-      const RowExp<T> rexp(mx[0]);
-      float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      // exp(x - max): 16-bit storage uses 2^(x*log2e - max*log2e) (one packed FMA + the hardware
+      // 2^x per element); fp32 storage uses expf
+      const float2 l2e = bcast2(kLog2e), c2 = bcast2(-mx[0] * kLog2e);
+      float2 ps[2] = {bcast2(0.0f), bcast2(0.0f)};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         if (tg + k * GROUP < nvec) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const float ex = rexp(xv[k * VEC + e]);
-            ps[e & 3] += ex;
-            if (!LOG) xv[k * VEC + e] = ex;
+          for (int e = 0; e < VH; ++e) {
+            const int j = k * VH + e;
+            float2 ex;
+            if constexpr (sizeof(T) == 4) {
+              ex = make_float2(expf(xv[j].x - mx[0]), expf(xv[j].y - mx[0]));
+            } else {
+              const float2 t = fma2(xv[j], l2e, c2);
+              ex = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+            }
+            ps[j & 1] = add2(ps[j & 1], ex);
+            if (!LOG) xv[j] = ex;
           }
         }
       }
-      float sum[1] = {(ps[0] + ps[1]) + (ps[2] + ps[3])};
+      float sum[1] = {hsum2(add2(ps[0], ps[1]))};
       group_reduce<GROUP, 1>(sum, rs->red, grp, tg, red_phase, SumOp());
       const float lg = LOG ? logf(sum[0]) : 0.0f;
-      const float off = mx[0] + lg;  // 16-bit log-softmax: x - (max + log sum) in one subtraction
-      const float inv = LOG ? 0.0f : 1.0f / sum[0];
+      const float2 noff = bcast2(-(mx[0] + lg));  // 16-bit log-softmax: x - (max + log sum) in one add
+      const float2 inv = bcast2(LOG ? 0.0f : 1.0f / sum[0]);
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
-          float o[VEC];
+          float2 o[VH];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const float t = xv[k * VEC + e];
-            if constexpr (LOG) o[e] = sizeof(T) == 4 ? (t - mx[0]) - lg : t - off;
-            else if constexpr (sizeof(T) == 4) o[e] = t / sum[0];
-            else o[e] = t * inv;
+          for (int e = 0; e < VH; ++e) {
+            const float2 t = xv[k * VH + e];
+            if constexpr (LOG) {
+              if constexpr (sizeof(T) == 4) o[e] = make_float2((t.x - mx[0]) - lg, (t.y - mx[0]) - lg);
+              else o[e] = add2(t, noff);
+            } else if constexpr (sizeof(T) == 4) {
+              o[e] = make_float2(t.x / sum[0], t.y / sum[0]);
+            } else {
+              o[e] = mul2(t, inv);
+            }
           }
-          sts128(rbase + v * 16, P::pack(o));
+          sts128(rbase + v * 16, P::pack2(o));
         }
       }
     }
@@ -156,44 +174,51 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
       if (cur.row0 + lr >= M) break;  // uniform over the group
       const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       const uint32_t ybase = dbase + g.slot_bytes;
-      float dv[EPT], yv[EPT];
-      float ps[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
+      float2 dv[HP], yv[HP];
+      float2 ps[2] = {bcast2(0.0f), bcast2(0.0f)};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
-          P::unpack(lds128(dbase + v * 16), &dv[k * VEC]);
-          P::unpack(lds128(ybase + v * 16), &yv[k * VEC]);
+          P::unpack2(lds128(dbase + v * 16), &dv[k * VH]);
+          P::unpack2(lds128(ybase + v * 16), &yv[k * VH]);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const int j = k * VEC + e;
-            if constexpr (LOG) ps[e & 3] += dv[j];
-            else ps[e & 3] = fmaf(dv[j], yv[j], ps[e & 3]);
+          for (int e = 0; e < VH; ++e) {
+            const int j = k * VH + e;
+            if constexpr (LOG) ps[j & 1] = add2(ps[j & 1], dv[j]);
+            else ps[j & 1] = fma2(dv[j], yv[j], ps[j & 1]);
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) { dv[k * VEC + e] = 0.0f; yv[k * VEC + e] = 0.0f; }
+          for (int e = 0; e < VH; ++e) { dv[k * VH + e] = bcast2(0.0f); yv[k * VH + e] = bcast2(0.0f); }
         }
       }
-      float sum[1] = {(ps[0] + ps[1]) + (ps[2] + ps[3])};
+      float sum[1] = {hsum2(add2(ps[0], ps[1]))};
       group_reduce<GROUP, 1>(sum, rs->red, grp, tg, red_phase, SumOp());
-      const float s = sum[0];
+      const float2 ns = bcast2(-sum[0]), l2e = bcast2(kLog2e);
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (v < nvec) {
-          float o[VEC];
+          float2 o[VH];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            const float d = dv[k * VEC + e], yy = yv[k * VEC + e];
+          for (int e = 0; e < VH; ++e) {
+            const float2 d = dv[k * VH + e], yy = yv[k * VH + e];
             if constexpr (LOG) {
-              const float ey = sizeof(T) == 4 ? expf(yy) : ex2_approx(yy * kLog2e);
-              o[e] = fmaf(-ey, s, d);
+              float2 ey;
+              if constexpr (sizeof(T) == 4) {
+                ey = make_float2(expf(yy.x), expf(yy.y));
+              } else {
+                const float2 t = mul2(yy, l2e);
+                ey = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+              }
+              o[e] = fma2(ey, ns, d);   // dy - exp(y)*sum
             } else {
-              o[e] = yy * (d - s);
+              o[e] = mul2(yy, add2(d, ns));  // y*(dy - sum)
             }
           }
-          sts128(dbase + v * 16, P::pack(o));
+          sts128(dbase + v * 16, P::pack2(o));
         }
       }
     }
