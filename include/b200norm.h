@@ -61,6 +61,14 @@ int b2n_last_cuda_error(void);
  * value.  A forced family that cannot take a given shape makes the call return
  * B2N_ERR_BAD_ARG instead of silently using another one. */
 int b2n_set_path(int path);
+/* Tuning aid for sweeps: override one launch parameter of the ring kernels for this thread
+ * (0 restores the automatic choice).  Values that do not fit a shape are clamped. */
+typedef enum b2n_tuning_knob {
+  B2N_TUNE_ROWS_PER_GROUP = 0, /* rows of a tile each row group works through (1..4) */
+  B2N_TUNE_STAGES = 1,         /* upper bound on the ring depth */
+  B2N_TUNE_STORE_LAG = 2       /* bulk stores left in flight before a stage is refilled (1..3) */
+} b2n_tuning_knob;
+int b2n_set_tuning(int knob, int value);
 /* Name of the kernel family the most recent launch from this thread used ("generic", "ring", ...). */
 const char* b2n_last_path(void);
 /* Reads and clears the device-side status word of the current device (synchronises `stream`).

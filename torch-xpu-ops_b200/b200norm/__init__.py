@@ -27,6 +27,7 @@ ERR_BAD_ARG, ERR_UNSUPPORTED_DTYPE, ERR_WORKSPACE, ERR_CUDA = -1, -2, -3, -4
 ERR_TIMEOUT, ERR_TARGET_RANGE, ERR_TOO_LARGE = -5, -6, -7
 PATH_AUTO, PATH_GENERIC, PATH_RING, PATH_CLUSTER = 0, 1, 2, 3
 REDUCE_NONE, REDUCE_MEAN, REDUCE_SUM = 0, 1, 2
+TUNE_ROWS_PER_GROUP, TUNE_STAGES, TUNE_STORE_LAG = 0, 1, 2
 
 
 class B200NormError(RuntimeError):
@@ -59,6 +60,7 @@ def load_library() -> ctypes.CDLL:
         "b2n_last_cuda_error": (i32, []),
         "b2n_set_path": (i32, [i32]),
         "b2n_last_path": (c.c_char_p, []),
+        "b2n_set_tuning": (i32, [i32, i32]),
         "b2n_device_status": (i32, [vp]),
         "b2n_launch_count": (c.c_ulonglong, []),
         "b2n_profile_begin": (i32, []),

@@ -86,6 +86,11 @@ def set_path(path: int) -> int:
     return load_library().b2n_set_path(path)
 
 
+def set_tuning(knob: int, value: int) -> None:
+    """Override a ring-kernel launch parameter for this thread (b200norm.TUNE_*; 0 = automatic)."""
+    _check(load_library().b2n_set_tuning(knob, value), "b2n_set_tuning")
+
+
 def last_path() -> str:
     return load_library().b2n_last_path().decode()
 

@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "launchers.h"
+#include "plan.h"
 
 namespace b2n {
 
@@ -68,6 +69,11 @@ ProfileScope::~ProfileScope() {
   if (slot >= 0) cudaEventRecord(tl_records[slot].stop, stream);
 }
 
+RingTuning& ring_tuning() {
+  thread_local RingTuning t;
+  return t;
+}
+
 int forced_path() { return tl_forced_path; }
 void note_path(const char* name) { tl_last_path = name; }
 
@@ -104,6 +110,17 @@ int b2n_set_path(int path) {
 }
 
 const char* b2n_last_path(void) { return tl_last_path; }
+
+int b2n_set_tuning(int knob, int value) {
+  RingTuning& t = ring_tuning();
+  if (value < 0) return B2N_ERR_BAD_ARG;
+  switch (knob) {
+    case B2N_TUNE_ROWS_PER_GROUP: t.rpg = value; return B2N_OK;
+    case B2N_TUNE_STAGES: t.stages = value; return B2N_OK;
+    case B2N_TUNE_STORE_LAG: t.lag = value; return B2N_OK;
+    default: return B2N_ERR_BAD_ARG;
+  }
+}
 
 unsigned long long b2n_launch_count(void) { return tl_launches; }
 

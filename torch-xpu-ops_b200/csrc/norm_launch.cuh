@@ -52,8 +52,8 @@ int norm_fwd_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const W
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once(kernel, p.smem, mask)) return e;
   ProfileScope prof(RMS ? "rms_norm_fwd_ring" : "layer_norm_fwd_ring", st);
-  kernel<<<p.grid, kRingThreads, p.smem, st>>>(x, gamma, beta, y, mean, rstd, M, static_cast<int>(N),
-                                               static_cast<float>(eps), p.stages, p.rpg, device_status_ptr());
+  kernel<<<p.grid, kRingBlock, p.smem, st>>>(x, gamma, beta, y, mean, rstd, M, static_cast<int>(N),
+                                               static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg, device_status_ptr());
   return launched();
 }
 
@@ -134,13 +134,13 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
   if (wgrad) {
     auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true>;
     if (int e = set_smem_once(kernel, p.smem, mask_w)) return e;
-    kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
-                                                 p.stages, p.rpg, device_status_ptr());
+    kernel<<<p.grid, kRingBlock, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
+                                                 p.stages | (p.lag << 8), p.rpg, device_status_ptr());
   } else {
     auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false>;
     if (int e = set_smem_once(kernel, p.smem, mask_n)) return e;
-    kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
-                                                 p.stages, p.rpg, device_status_ptr());
+    kernel<<<p.grid, kRingBlock, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
+                                                 p.stages | (p.lag << 8), p.rpg, device_status_ptr());
   }
   return launched();
 }

@@ -33,10 +33,10 @@ __device__ __forceinline__ void load_weights(const WT* __restrict__ w, float fil
 }
 
 template <typename T, typename WT, bool RMS, int GROUP, int VPT>
-__global__ void __launch_bounds__(kRingThreads, 1)
+__global__ void __launch_bounds__(kRingBlock, 1)
 norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta,
                      T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t M,
-                     int N, float eps, int S, int RPG, int* status) {
+                     int N, float eps, int S_lag, int RPG, int* status) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   constexpr int RB = 2;  // rows a group works on at once
@@ -45,14 +45,20 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S, 1);
-  ring_init(rs, S, kRingThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1);
+  ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
-  RingProducer<1> prod(rs, stages, g, status);
-  prod.in[0] = reinterpret_cast<const unsigned char*>(x);
-  prod.out = reinterpret_cast<unsigned char*>(y);
-  if (tid == 0) prod.prologue();
-  bool prod_ok = true;  // thread 0: a failed wait ends its producer duties, not its consumer loop
+  if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
+    ring_producer_regs();
+    if (tid == kRingThreads) {
+      RingProducer<1> prod(rs, stages, g, status);
+      prod.in[0] = reinterpret_cast<const unsigned char*>(x);
+      prod.out = reinterpret_cast<unsigned char*>(y);
+      prod.run();
+    }
+    return;
+  }
+  ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
@@ -178,9 +184,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
       }
     }
     ring_consumer_release(rs, cur);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(cur, i);
 }
 
 // Backward: stage = [dy tile | x tile]; dx overwrites the dy tile.  Every thread also accumulates
@@ -191,10 +195,10 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 // Per row: s1 = sum(gamma*dy), s2 = sum(gamma*dy*xhat), xhat = (x - mean) * rstd,
 // dx = rstd * (gamma*dy - (xhat*s2 + s1)/N)   (RMS: mean = 0, s1 = 0).
 template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD>
-__global__ void __launch_bounds__(kRingThreads, 1)
+__global__ void __launch_bounds__(kRingBlock, 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx,
-                     float* __restrict__ ws, int64_t M, int N, int S, int RPG, int* status) {
+                     float* __restrict__ ws, int64_t M, int N, int S_lag, int RPG, int* status) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -202,15 +206,21 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S, 2);
-  ring_init(rs, S, kRingThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 2);
+  ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
-  RingProducer<2> prod(rs, stages, g, status);
-  prod.in[0] = reinterpret_cast<const unsigned char*>(dy);
-  prod.in[1] = reinterpret_cast<const unsigned char*>(x);
-  prod.out = reinterpret_cast<unsigned char*>(dx);
-  if (tid == 0) prod.prologue();
-  bool prod_ok = true;  // thread 0: a failed wait ends its producer duties, not its consumer loop
+  if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
+    ring_producer_regs();
+    if (tid == kRingThreads) {
+      RingProducer<2> prod(rs, stages, g, status);
+      prod.in[0] = reinterpret_cast<const unsigned char*>(dy);
+      prod.in[1] = reinterpret_cast<const unsigned char*>(x);
+      prod.out = reinterpret_cast<unsigned char*>(dx);
+      prod.run();
+    }
+    return;
+  }
+  ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
@@ -303,9 +313,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       }
     }
     ring_consumer_release(rs, cur);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(cur, i);
 
   if (WGRAD) {
     const int64_t prow = static_cast<int64_t>(blockIdx.x) * NG + grp;

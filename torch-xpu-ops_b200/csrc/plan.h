@@ -13,9 +13,14 @@ struct RingPlan {
   int ng = 0;      // row groups per CTA = 512 / group
   int rpg = 1;     // rows per group per tile
   int stages = 0;  // ring depth
+  int lag = 1;     // stores left in flight before a stage is refilled (see RingProducer::after_tile)
   int grid = 0;    // persistent CTAs
   size_t smem = 0; // dynamic shared memory per CTA
 };
+
+// Per-thread overrides for tuning sweeps (0 = automatic); set through b2n_set_tuning.
+struct RingTuning { int rpg = 0; int stages = 0; int lag = 0; };
+RingTuning& ring_tuning();
 
 // N elements of `esize` bytes per row, `nin` tensors staged per tile, `ept` elements per thread.
 // Not ok when the row is not a multiple of 16 bytes, does not fit 512 threads x ept elements, or
@@ -38,11 +43,19 @@ inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int
   while (rpg > 1 && (M + p.ng * rpg - 1) / (p.ng * rpg) < 4LL * sm_count) --rpg;
   p.rpg = static_cast<int>(rpg < 1 ? 1 : (rpg > 4 ? 4 : rpg));
   if (p.rpg == 3) p.rpg = 2;  // the kernels take a group's rows two at a time
+  const RingTuning& tune = ring_tuning();
+  if (tune.rpg > 0) p.rpg = tune.rpg > 4 ? 4 : tune.rpg;
   const int64_t stage = static_cast<int64_t>(nin) * p.ng * p.rpg * row_bytes;
   int64_t s = (static_cast<int64_t>(max_smem) - kRingHeaderBytes) / stage;
   if (s > kMaxStages) s = kMaxStages;
+  if (tune.stages > 0 && tune.stages < s) s = tune.stages;
   if (s < 2) return p;
   p.stages = static_cast<int>(s);
+  p.lag = 1;
+  if (tune.lag > 0) p.lag = tune.lag;
+  if (p.lag > s - 2) p.lag = static_cast<int>(s) - 2;
+  if (p.lag < 1) p.lag = 1;
+  if (p.lag > 3) p.lag = 3;
   p.smem = static_cast<size_t>(kRingHeaderBytes + s * stage);
   const int64_t ntiles = (M + p.ng * p.rpg - 1) / (p.ng * p.rpg);
   p.grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);

@@ -8,6 +8,14 @@
 // next tiles and the store of the previous one overlap the arithmetic, and the bytes in flight per
 // SM do not depend on occupancy or register count.
 //
+// Roles: 16 consumer warps (512 threads) and one producer warpgroup (4 warps, of which one thread
+// works).  The producer's bulk-copy instructions and its wait for a store to drain block for about
+// as long as HBM takes to move a tile, so they must not sit in a warp that also has a consumer's
+// share of every row.  A 17th..20th warp would normally cap every thread at 96 registers; the
+// producer warpgroup therefore gives its registers back (setmaxnreg.dec) and the consumers grow to
+// 112 (setmaxnreg.inc; the CTA cannot hold more than its launch allocation of 640 x 96, and asking
+// for more would wait forever), the warp-specialisation pattern of sm_90+.
+//
 // Stage layout: NIN input tiles back to back (tile k at k * TR * row_bytes); the result overwrites
 // input tile 0.  Tile i of a CTA is global tile blockIdx.x + i * gridDim.x.
 //
@@ -22,7 +30,12 @@ namespace b2n {
 constexpr int kMaxStages = 16;
 constexpr int kRingHeaderBytes = 1024;  // barriers + reduction scratch
 constexpr int kRingRedFloats = 160;     // reduction scratch inside the header
-constexpr int kRingThreads = 512;       // 16 warps; thread 0 doubles as the producer
+constexpr int kRingThreads = 512;       // consumer threads (16 warps)
+constexpr int kRingBlock = 640;         // + one producer warpgroup
+constexpr int kConsumerRegs = 112;      // the CTA keeps its launch allocation (640 x 96): 512 x 112 + 128 x 24 <= 61440
+
+__device__ __forceinline__ void ring_producer_regs() { asm volatile("setmaxnreg.dec.sync.aligned.u32 24;"); }
+__device__ __forceinline__ void ring_consumer_regs() { asm volatile("setmaxnreg.inc.sync.aligned.u32 112;"); }
 
 struct RingShared {
   uint64_t full[kMaxStages];  // tile landed in the stage (bulk-copy bytes counted)
@@ -42,11 +55,14 @@ struct RingGeom {
   uint32_t stage_bytes;
   int TR;               // rows per tile
   int S;                // stages
+  int lag;              // bulk stores the producer leaves in flight before it refills a stage (1..3)
 
-  __device__ __forceinline__ void init(int64_t M_, int N, int esize, int TR_, int S_, int nin) {
+  // S_lag packs the two launch parameters: stages in the low 8 bits, lag above them.
+  __device__ __forceinline__ void init(int64_t M_, int N, int esize, int TR_, int S_lag, int nin) {
     M = M_;
     TR = TR_;
-    S = S_;
+    S = S_lag & 0xff;
+    lag = S_lag >> 8;
     row_bytes = static_cast<uint32_t>(N) * esize;
     slot_bytes = static_cast<uint32_t>(TR_) * row_bytes;
     stage_bytes = slot_bytes * nin;
@@ -84,9 +100,7 @@ __device__ __forceinline__ void ring_init(RingShared* rs, int S, int warps) {
   __syncthreads();
 }
 
-// Producer duties, carried by thread 0 of the CTA between its own consumer work (a 17th warp would
-// cap every thread at 96 registers, because a fifth warp on one SM sub-partition shrinks the
-// per-thread share of its register file; 16 warps leave 128).
+// The producer loop, run by ONE thread of the producer warpgroup.
 // in[k]: base of input tensor k; out: base of the result tensor.
 template <int NIN> struct RingProducer {
   RingShared* rs;
@@ -97,10 +111,9 @@ template <int NIN> struct RingProducer {
   int* status;
   int64_t loads_left;  // tiles whose loads have not been issued yet
   RingCursor next;     // the next tile to load
-  bool have_prev;      // a store has been issued before (its stage is the next to refill)
 
   __device__ __forceinline__ RingProducer(RingShared* rs_, unsigned char* stages_, const RingGeom& g_, int* status_)
-      : rs(rs_), stages(stages_), g(g_), out(nullptr), status(status_), loads_left(g_.my_tiles), have_prev(false) {
+      : rs(rs_), stages(stages_), g(g_), out(nullptr), status(status_), loads_left(g_.my_tiles) {
     next.start(g_);
   }
   __device__ __forceinline__ void issue_next_load() {
@@ -113,31 +126,33 @@ template <int NIN> struct RingProducer {
     next.advance(g);
     --loads_left;
   }
-  // Before the first tile: fill the ring.
-  __device__ __forceinline__ void prologue() {
-    for (int k = 0; k < g.S && loads_left > 0; ++k) issue_next_load();
-  }
-  // After this thread's own work on the tile at `cur`: send the tile out once every warp has
-  // finished it, then refill the stage of the tile before it, whose store (now the second newest
-  // bulk group) has finished reading shared memory.  With S stages in rotation that stage is
+  // Fill the ring; then, tile by tile: wait until every consumer warp has finished the tile, send
+  // it out, and refill the stage of the tile `lag` tiles back, whose store (now the lag-th newest
+  // bulk group) has finished reading shared memory — with S stages in rotation that stage is
   // exactly where the next tile to load belongs.
-  __device__ __forceinline__ bool after_tile(const RingCursor& cur) {
-    if (!mbar_wait(&rs->done[cur.s], cur.phase, status)) return false;
-    bulk_s2g(out + static_cast<size_t>(cur.row0) * g.row_bytes, stages + static_cast<size_t>(cur.s) * g.stage_bytes,
-             g.tile_bytes(cur.row0));
-    bulk_commit();
-    if (have_prev && loads_left > 0) {
-      bulk_wait_read<1>();
-      issue_next_load();
+  __device__ __forceinline__ void run() {
+    for (int k = 0; k < g.S && loads_left > 0; ++k) issue_next_load();
+    RingCursor cur;
+    cur.start(g);
+    int stores = 0;
+    int64_t i = 0;
+    for (; i < g.my_tiles; ++i, cur.advance(g)) {
+      if (!mbar_wait(&rs->done[cur.s], cur.phase, status)) break;
+      bulk_s2g(out + static_cast<size_t>(cur.row0) * g.row_bytes,
+               stages + static_cast<size_t>(cur.s) * g.stage_bytes, g.tile_bytes(cur.row0));
+      bulk_commit();
+      if (stores < 4) ++stores;
+      if (stores > g.lag && loads_left > 0) {
+        if (g.lag == 1) bulk_wait_read<1>();
+        else if (g.lag == 2) bulk_wait_read<2>();
+        else bulk_wait_read<3>();
+        issue_next_load();
+      }
     }
-    have_prev = true;
-    return true;
-  }
-  // After the last tile, or after a wait gave up with loaded tiles not yet consumed starting at
-  // `cur`: nothing of this CTA may still be in flight when its shared memory goes away.
-  __device__ __forceinline__ void epilogue(RingCursor cur, int64_t tiles_done) {
+    // Nothing of this CTA may still be in flight when its shared memory goes away: if a wait gave
+    // up, let the loads that were issued but never consumed land first.
     const int64_t issued = g.my_tiles - loads_left;
-    for (int64_t j = tiles_done; j < issued; ++j) {
+    for (int64_t j = i; j < issued; ++j) {
       mbar_wait(&rs->full[cur.s], cur.phase, status);
       cur.advance(g);
     }

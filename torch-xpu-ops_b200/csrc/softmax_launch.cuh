@@ -36,7 +36,7 @@ int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int6
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
   ProfileScope prof(LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring", st);
-  kernel<<<p.grid, kRingThreads, p.smem, st>>>(x, y, M, static_cast<int>(N), p.stages, p.rpg, device_status_ptr());
+  kernel<<<p.grid, kRingBlock, p.smem, st>>>(x, y, M, static_cast<int>(N), p.stages | (p.lag << 8), p.rpg, device_status_ptr());
   return launched();
 }
 
@@ -48,7 +48,7 @@ int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, i
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
   ProfileScope prof(LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring", st);
-  kernel<<<p.grid, kRingThreads, p.smem, st>>>(dy, y, dx, M, static_cast<int>(N), p.stages, p.rpg,
+  kernel<<<p.grid, kRingBlock, p.smem, st>>>(dy, y, dx, M, static_cast<int>(N), p.stages | (p.lag << 8), p.rpg,
                                                device_status_ptr());
   return launched();
 }

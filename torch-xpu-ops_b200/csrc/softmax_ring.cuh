@@ -26,8 +26,8 @@ template <typename T> struct RowExp {
 };
 
 template <typename T, bool LOG, int GROUP, int VPT>
-__global__ void __launch_bounds__(kRingThreads, 1)
-softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S, int RPG,
+__global__ void __launch_bounds__(kRingBlock, 1)
+softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S_lag, int RPG,
                         int* status) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
@@ -36,14 +36,20 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S, 1);
-  ring_init(rs, S, kRingThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1);
+  ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
-  RingProducer<1> prod(rs, stages, g, status);
-  prod.in[0] = reinterpret_cast<const unsigned char*>(x);
-  prod.out = reinterpret_cast<unsigned char*>(y);
-  if (tid == 0) prod.prologue();
-  bool prod_ok = true;  // thread 0: a failed wait ends its producer duties, not its consumer loop
+  if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
+    ring_producer_regs();
+    if (tid == kRingThreads) {
+      RingProducer<1> prod(rs, stages, g, status);
+      prod.in[0] = reinterpret_cast<const unsigned char*>(x);
+      prod.out = reinterpret_cast<unsigned char*>(y);
+      prod.run();
+    }
+    return;
+  }
+  ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
@@ -130,17 +136,15 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       }
     }
     ring_consumer_release(rs, cur);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(cur, i);
 }
 
 // stage = [dy tile | y tile]; dx overwrites the dy tile.
 // softmax: dx = y*(dy - sum(y*dy)); log-softmax: dx = dy - exp(y)*sum(dy).
 template <typename T, bool LOG, int GROUP, int VPT>
-__global__ void __launch_bounds__(kRingThreads, 1)
+__global__ void __launch_bounds__(kRingBlock, 1)
 softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t M,
-                        int N, int S, int RPG, int* status) {
+                        int N, int S_lag, int RPG, int* status) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -148,15 +152,21 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S, 2);
-  ring_init(rs, S, kRingThreads / 32);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 2);
+  ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
-  RingProducer<2> prod(rs, stages, g, status);
-  prod.in[0] = reinterpret_cast<const unsigned char*>(dy);
-  prod.in[1] = reinterpret_cast<const unsigned char*>(y);
-  prod.out = reinterpret_cast<unsigned char*>(dx);
-  if (tid == 0) prod.prologue();
-  bool prod_ok = true;  // thread 0: a failed wait ends its producer duties, not its consumer loop
+  if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
+    ring_producer_regs();
+    if (tid == kRingThreads) {
+      RingProducer<2> prod(rs, stages, g, status);
+      prod.in[0] = reinterpret_cast<const unsigned char*>(dy);
+      prod.in[1] = reinterpret_cast<const unsigned char*>(y);
+      prod.out = reinterpret_cast<unsigned char*>(dx);
+      prod.run();
+    }
+    return;
+  }
+  ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
   const int nvec = N / VEC;
@@ -223,9 +233,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
       }
     }
     ring_consumer_release(rs, cur);
-    if (tid == 0 && prod_ok) prod_ok = prod.after_tile(cur);
   }
-  if (tid == 0) prod.epilogue(cur, i);
 }
 
 }  // namespace b2n
