@@ -69,6 +69,14 @@ typedef enum b2n_tuning_knob {
   B2N_TUNE_STORE_LAG = 2       /* bulk stores left in flight before a stage is refilled (1..3) */
 } b2n_tuning_knob;
 int b2n_set_tuning(int knob, int value);
+/* Diagnostic: while a buffer is set (this thread), CTA 0 of the layer-norm / RMS-norm forward ring
+ * kernel appends event records to it.  Layout (64-bit words, zero the buffer first): word 0 / 1 =
+ * record counts of the two writers (consumer thread 0, producer thread); then cap records per
+ * writer, cap = (bytes - 16) / 32, each {event << 48 | tile index, %globaltimer ns}.
+ * Events: 1/2 consumer wait begin/end, 3 consumer released the tile, 4 producer saw the tile done,
+ * 5 store issued, 6 waited for an older store to drain, 7 next load issued, 8+k points inside the
+ * consumer's arithmetic.  NULL switches it off. */
+int b2n_set_trace_buffer(void* device_buffer, size_t bytes);
 /* Name of the kernel family the most recent launch from this thread used ("generic", "ring", ...). */
 const char* b2n_last_path(void);
 /* Reads and clears the device-side status word of the current device (synchronises `stream`).

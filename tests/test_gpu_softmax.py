@@ -178,3 +178,34 @@ def test_ring_is_used_for_aligned_rows_and_refuses_others_when_forced():
     with forced_path(b200norm.PATH_RING):
         with pytest.raises(b200norm.B200NormError):
             capi._softmax(ao.randn((4, 33), 471).to(DEV), -1, False)  # 33 floats: not a multiple of 16 bytes
+
+
+@pytest.mark.parametrize("is_log", [False, True])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("M,N", [(5, 16384), (3, 40000), (7, 65544), (2, 128256), (300, 20008)])
+def test_cluster_kernels_for_long_rows(M, N, dt, is_log):
+    # rows split over a thread-block cluster (ragged last slice included: 65544 and 20008 vectors do not
+    # divide evenly); degenerate rows keep the CPU semantics
+    x = ao.randn((M, N), 480 + N % 97, torch.float32, 0.0, 2.0)
+    x[0, N // 2:] = float("-inf")
+    if M > 2:
+        x[1, :] = float("-inf")
+        x[2, 11] = float("nan")
+    x = x.to(dt)
+    dy = ao.randn((M, N), 481, dt)
+    fwd = capi._log_softmax if is_log else capi._softmax
+    bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+    with forced_path(b200norm.PATH_CLUSTER):
+        y_buf, y_chk = guarded_empty((M, N), dt)
+        y = fwd(x.to(DEV), -1, False, out=y_buf)
+        assert capi.last_path() == "cluster"
+        dx_buf, dx_chk = guarded_empty((M, N), dt)
+        dx = bwd(dy.to(DEV), y, -1, dt, out=dx_buf)
+        assert capi.last_path() == "cluster"
+    torch.cuda.synchronize()
+    y_chk(); dx_chk()
+    ry = ao.softmax_fwd(x, -1, is_log)
+    assert torch.equal(torch.isnan(y.cpu()), torch.isnan(ry))
+    check_out(y, ry, "y")
+    check_out(dx, ao.softmax_bwd(dy, y.cpu(), -1, is_log, dt), "dx", tol=2.0)
+    assert capi.device_status() == 0

@@ -111,6 +111,18 @@ int b2n_set_path(int path) {
 
 const char* b2n_last_path(void) { return tl_last_path; }
 
+int b2n_set_trace_buffer(void* device_buffer, size_t bytes) {
+  RingTuning& t = ring_tuning();
+  if (device_buffer == nullptr || bytes < 80) {
+    t.trace_buf = nullptr;
+    t.trace_cap = 0;
+    return B2N_OK;
+  }
+  t.trace_buf = static_cast<unsigned long long*>(device_buffer);
+  t.trace_cap = static_cast<unsigned>((bytes - 16) / 32);  // two writers, 16 bytes per record
+  return B2N_OK;
+}
+
 int b2n_set_tuning(int knob, int value) {
   RingTuning& t = ring_tuning();
   if (value < 0) return B2N_ERR_BAD_ARG;

@@ -50,6 +50,12 @@ __device__ __forceinline__ float acc_log(float v) { return logf(v); }
 __device__ __forceinline__ double acc_log(double v) { return log(v); }
 __device__ __forceinline__ float acc_rsqrt(float v) { return 1.0f / sqrtf(v); }
 __device__ __forceinline__ double acc_rsqrt(double v) { return 1.0 / sqrt(v); }
+// 1/sqrt(v) to within 1 ulp: hardware estimate (2 ulp) plus one Newton step, five instructions
+// instead of the ~30 of an IEEE sqrt followed by an IEEE division
+__device__ __forceinline__ float rsqrt_nr(float v) {
+  const float r = rsqrtf(v);
+  return r * fmaf(-0.5f * v * r, r, 1.5f);
+}
 __device__ __forceinline__ float acc_max(float a, float b) { return fmaxf(a, b); }
 __device__ __forceinline__ double acc_max(double a, double b) { return fmax(a, b); }
 template <typename A> __device__ __forceinline__ A acc_neg_inf();

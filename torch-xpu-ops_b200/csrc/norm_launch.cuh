@@ -53,7 +53,8 @@ int norm_fwd_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const W
   if (int e = set_smem_once(kernel, p.smem, mask)) return e;
   ProfileScope prof(RMS ? "rms_norm_fwd_ring" : "layer_norm_fwd_ring", st);
   kernel<<<p.grid, kRingBlock, p.smem, st>>>(x, gamma, beta, y, mean, rstd, M, static_cast<int>(N),
-                                               static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg, device_status_ptr());
+                                               static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg, device_status_ptr(),
+                                               ring_tuning().trace_buf, ring_tuning().trace_cap);
   return launched();
 }
 

@@ -36,7 +36,8 @@ template <typename T, typename WT, bool RMS, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta,
                      T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t M,
-                     int N, float eps, int S_lag, int RPG, int* status) {
+                     int N, float eps, int S_lag, int RPG, int* status, unsigned long long* trace_buf,
+                     unsigned trace_cap) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   constexpr int RB = 2;  // rows a group works on at once
@@ -45,7 +46,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1, trace_buf, trace_cap);
   ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
   if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
@@ -72,9 +73,12 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 
   RingCursor cur;
   cur.start(g);
+  unsigned tk = 0;  // trace record counter (diagnostic)
   int64_t i = 0;
   for (; i < g.my_tiles; ++i, cur.advance(g)) {
+    if (tid == 0) g.trace.put(0, tk, EV_C_WAIT_BEGIN, i);
     if (!ring_consumer_wait(rs, cur, status)) break;
+    if (tid == 0) g.trace.put(0, tk, EV_C_WAIT_END, i);
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     // A group takes its rows of the tile RB at a time: the partial sums of RB rows go through ONE
     // group reduction (one barrier, RB values), which halves the time the group's warps spend
@@ -125,13 +129,15 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         }
         red1[b] = hsum2(add2(part[0], part[1]));
       }
+      if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 0, i);
       group_reduce<GROUP, RB>(red1, rs->red, grp, tg, red_phase, SumOp());
+      if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 1, i);
       float mu_d[RB], rsd[RB];  // mu_d: mean of (x - shift)
       if constexpr (RMS) {
 #pragma unroll
         for (int b = 0; b < RB; ++b) {
           mu_d[b] = 0.0f;
-          rsd[b] = acc_rsqrt(red1[b] * inv_n + eps);
+          rsd[b] = rsqrt_nr(red1[b] * inv_n + eps);
         }
       } else {
         float red2[RB];
@@ -153,9 +159,11 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           }
           red2[b] = hsum2(add2(q[0], q[1]));
         }
+        if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 2, i);
         group_reduce<GROUP, RB>(red2, rs->red, grp, tg, red_phase, SumOp());
+        if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 3, i);
 #pragma unroll
-        for (int b = 0; b < RB; ++b) rsd[b] = acc_rsqrt(red2[b] * inv_n + eps);
+        for (int b = 0; b < RB; ++b) rsd[b] = rsqrt_nr(red2[b] * inv_n + eps);
       }
 #pragma unroll
       for (int b = 0; b < RB; ++b) {
@@ -183,7 +191,9 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         }
       }
     }
+    if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 4, i);
     ring_consumer_release(rs, cur);
+    if (tid == 0) g.trace.put(0, tk, EV_C_RELEASED, i);
   }
 }
 

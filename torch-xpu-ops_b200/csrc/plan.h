@@ -19,7 +19,11 @@ struct RingPlan {
 };
 
 // Per-thread overrides for tuning sweeps (0 = automatic); set through b2n_set_tuning.
-struct RingTuning { int rpg = 0; int stages = 0; int lag = 0; };
+struct RingTuning {
+  int rpg = 0, stages = 0, lag = 0;
+  unsigned long long* trace_buf = nullptr;  // device buffer for the event trace (diagnostic), or null
+  unsigned trace_cap = 0;                   // records it can hold
+};
 RingTuning& ring_tuning();
 
 // N elements of `esize` bytes per row, `nin` tensors staged per tile, `ept` elements per thread.

@@ -45,7 +45,29 @@ struct RingShared {
 };
 static_assert(sizeof(RingShared) <= kRingHeaderBytes, "ring header too large");
 
+// Optional event trace (a diagnostic: see b2n_set_trace_buffer).  CTA 0 appends (event, tile,
+// %globaltimer) records; buf[0] is the record count, records follow as pairs of 64-bit words.
+enum RingEvent : unsigned {
+  EV_C_WAIT_BEGIN = 1, EV_C_WAIT_END = 2, EV_C_RELEASED = 3,
+  EV_P_DONE_SEEN = 4, EV_P_STORE_ISSUED = 5, EV_P_READ_WAITED = 6, EV_P_LOAD_ISSUED = 7,
+  EV_C_STEP = 8  // + step number: points inside the consumer's arithmetic
+};
+struct RingTrace {
+  unsigned long long* buf;
+  unsigned cap;  // records per writer (two writers: consumer thread 0 and the producer thread)
+  // Each writer appends to its own half with a private counter (no atomics: the stores are fire
+  // and forget, so tracing barely perturbs the timing).  word 0 / word 1 = the writers' counts.
+  __device__ __forceinline__ void put(unsigned writer, unsigned& k, unsigned ev, int64_t tile) const {
+    if (buf == nullptr || blockIdx.x != 0 || k >= cap) return;
+    unsigned long long* p = buf + 2 + 2 * (static_cast<size_t>(writer) * cap + k);
+    p[0] = (static_cast<unsigned long long>(ev) << 48) | static_cast<unsigned long long>(tile);
+    p[1] = globaltimer_ns();
+    buf[writer] = ++k;
+  }
+};
+
 struct RingGeom {
+  RingTrace trace;
   int64_t M;            // rows
   int64_t tile_stride;  // rows between consecutive tiles of this CTA = gridDim.x * TR
   int64_t my_tiles;     // tiles this CTA processes
@@ -58,7 +80,10 @@ struct RingGeom {
   int lag;              // bulk stores the producer leaves in flight before it refills a stage (1..3)
 
   // S_lag packs the two launch parameters: stages in the low 8 bits, lag above them.
-  __device__ __forceinline__ void init(int64_t M_, int N, int esize, int TR_, int S_lag, int nin) {
+  __device__ __forceinline__ void init(int64_t M_, int N, int esize, int TR_, int S_lag, int nin,
+                                       unsigned long long* trace_buf = nullptr, unsigned trace_cap = 0) {
+    trace.buf = trace_buf;
+    trace.cap = trace_cap;
     M = M_;
     TR = TR_;
     S = S_lag & 0xff;
@@ -135,18 +160,23 @@ template <int NIN> struct RingProducer {
     RingCursor cur;
     cur.start(g);
     int stores = 0;
+    unsigned tk = 0;
     int64_t i = 0;
     for (; i < g.my_tiles; ++i, cur.advance(g)) {
       if (!mbar_wait(&rs->done[cur.s], cur.phase, status)) break;
+      g.trace.put(1, tk, EV_P_DONE_SEEN, i);
       bulk_s2g(out + static_cast<size_t>(cur.row0) * g.row_bytes,
                stages + static_cast<size_t>(cur.s) * g.stage_bytes, g.tile_bytes(cur.row0));
       bulk_commit();
+      g.trace.put(1, tk, EV_P_STORE_ISSUED, i);
       if (stores < 4) ++stores;
       if (stores > g.lag && loads_left > 0) {
         if (g.lag == 1) bulk_wait_read<1>();
         else if (g.lag == 2) bulk_wait_read<2>();
         else bulk_wait_read<3>();
+        g.trace.put(1, tk, EV_P_READ_WAITED, i);
         issue_next_load();
+        g.trace.put(1, tk, EV_P_LOAD_ISSUED, i);
       }
     }
     // Nothing of this CTA may still be in flight when its shared memory goes away: if a wait gave
@@ -171,45 +201,46 @@ __device__ __forceinline__ void ring_consumer_release(RingShared* rs, const Ring
 }
 
 // ---- reductions over the GROUP threads that share a row ----------------------------------------
-// GROUP == 32: shuffles only.  GROUP > 32: per-warp partials through the header scratch and a
-// named barrier private to the group (id 1 + group).  `phase` alternates the scratch half so one
-// barrier per reduction is enough.  K values (K <= 4) are reduced together; scratch layout
-// [group][phase][K][W] so a thread reads one value's W partials with 16-byte loads.
+// K values (K <= 2) are reduced together, in a fixed order (bit-reproducible).
+//
+// Within a warp, two values share one butterfly: the first exchange (lane ^ 16) leaves value 0 in
+// lanes 0-15 and value 1 in lanes 16-31, so the remaining four levels serve both at once.
+// Across the W = GROUP/32 warps of a group: lane 0 / lane 16 of each warp write the warp's totals
+// to the header scratch ([group][phase][K][W], double-buffered by `phase` so one named barrier per
+// reduction is enough); after the barrier, lane (k*W + w) of EVERY warp reads partial (k, w) and a
+// log2(W)-level butterfly inside each W-lane segment finishes the job — one shared-memory load and
+// at most four shuffles per thread instead of W loads and W adds.
 template <int GROUP, int K, typename Op>
 __device__ __forceinline__ void group_reduce(float (&v)[K], float* red, int group, int tg, int& phase, Op op) {
+  static_assert(K == 1 || K == 2, "one or two values");
+  const int lane = tg & 31;
+  float x;
+  if constexpr (K == 1) {
+    x = warp_reduce(v[0], op);
+  } else {
+    const bool hi = (lane & 16) != 0;
+    const float keep = hi ? v[1] : v[0];
+    const float send = hi ? v[0] : v[1];
+    x = op(keep, __shfl_xor_sync(0xffffffffu, send, 16));
 #pragma unroll
-  for (int k = 0; k < K; ++k) v[k] = warp_reduce(v[k], op);
-  if constexpr (GROUP > 32) {
+    for (int o = 8; o > 0; o >>= 1) x = op(x, __shfl_xor_sync(0xffffffffu, x, o));
+  }
+  if constexpr (GROUP == 32) {
+    v[0] = __shfl_sync(0xffffffffu, x, 0);
+    if constexpr (K == 2) v[1] = __shfl_sync(0xffffffffu, x, 16);
+  } else {
     constexpr int W = GROUP / 32;
-    static_assert(K <= 4, "scratch sized for four values");
-    static_assert((kRingThreads / 32) * 2 * 4 <= kRingRedFloats, "scratch too small");
-    float* buf = red + (group * 2 + phase) * (4 * W);
+    static_assert(W * K <= 32, "partials of one reduction fit a warp");
+    static_assert((kRingThreads / 32) * 2 * 2 <= kRingRedFloats, "scratch too small");
+    float* buf = red + (group * 2 + phase) * (2 * W);
     phase ^= 1;
-    if ((tg & 31) == 0) {
-#pragma unroll
-      for (int k = 0; k < K; ++k) buf[k * W + (tg >> 5)] = v[k];
-    }
+    if ((lane & 15) == 0 && (K == 2 || lane == 0)) buf[(lane >> 4) * W + (tg >> 5)] = x;
     named_bar_sync(1 + group, GROUP);
+    float y = buf[lane < W * K ? lane : 0];
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      float p[W];
-      if constexpr (W % 4 == 0) {
-#pragma unroll
-        for (int w = 0; w < W; w += 4) {
-          const float4 q = *reinterpret_cast<const float4*>(buf + k * W + w);
-          p[w] = q.x; p[w + 1] = q.y; p[w + 2] = q.z; p[w + 3] = q.w;
-        }
-      } else {
-#pragma unroll
-        for (int w = 0; w < W; ++w) p[w] = buf[k * W + w];
-      }
-      // fixed pairwise order: identical in every thread, short dependency chain
-#pragma unroll
-      for (int stride = 1; stride < W; stride *= 2)
-#pragma unroll
-        for (int w = 0; w + stride < W; w += 2 * stride) p[w] = op(p[w], p[w + stride]);
-      v[k] = p[0];
-    }
+    for (int o = W / 2; o > 0; o >>= 1) y = op(y, __shfl_xor_sync(0xffffffffu, y, o));
+    v[0] = __shfl_sync(0xffffffffu, y, 0);
+    if constexpr (K == 2) v[1] = __shfl_sync(0xffffffffu, y, W);
   }
 }
 

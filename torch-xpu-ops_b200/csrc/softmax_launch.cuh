@@ -7,6 +7,7 @@
 #include "plan.h"
 #include "softmax_generic.cuh"
 #include "softmax_ring.cuh"
+#include "softmax_cluster.cuh"
 
 namespace b2n {
 
@@ -53,6 +54,65 @@ int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, i
   return launched();
 }
 
+// Rows too long for the ring: split a row over a cluster of C CTAs (C = 2, 4 or 8), slice in shared
+// memory.  Returns B2N_ERR_BAD_ARG when the row does not fit even 8 CTAs (the caller then falls
+// back to the generic kernels).
+struct ClusterPlan { bool ok = false; int c = 0; int slice_vecs = 0; size_t smem = 0; };
+inline ClusterPlan plan_cluster(int64_t N, int esize, int nin, int max_smem) {
+  ClusterPlan p;
+  const int vec = 16 / esize;
+  if (N % vec != 0) return p;
+  const int64_t nvec = N / vec;
+  const int64_t third = (static_cast<int64_t>(max_smem) / 3 - kClusterHeaderBytes - 1024) / 16 * 16;  // three CTAs per SM
+  const int64_t whole = (static_cast<int64_t>(max_smem) - kClusterHeaderBytes) / 16 * 16;
+  for (int pass = 0; pass < 2 && !p.ok; ++pass) {
+    const int64_t budget = pass == 0 ? third : whole;
+    for (int c = 2; c <= 8; c *= 2) {
+      const int64_t sv = (nvec + c - 1) / c;
+      if (sv * 16 * nin <= budget) {
+        p.ok = true;
+        p.c = c;
+        p.slice_vecs = static_cast<int>(sv);
+        p.smem = static_cast<size_t>(kClusterHeaderBytes + sv * 16 * nin);
+        break;
+      }
+    }
+  }
+  return p;
+}
+
+template <typename T, bool LOG, bool BWD>
+int softmax_cluster_launch(const ClusterPlan& p, const T* in0, const T* in1, T* out, int64_t M, int64_t N,
+                           cudaStream_t st) {
+  auto kernel = softmax_cluster_kernel<T, LOG, BWD>;
+  static std::atomic<uint64_t> mask{0};
+  if (int e = set_smem_once_sm(kernel, mask)) return e;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.c;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.blockDim = dim3(kClusterThreads);
+  cfg.dynamicSmemBytes = p.smem;
+  cfg.stream = st;
+  // persistent clusters: as many as the device holds at once
+  cfg.gridDim = dim3(static_cast<unsigned>(p.c) * device_info().sm_count);
+  int max_clusters = 0;
+  if (int e = check_cuda(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg))) return e;
+  if (max_clusters < 1) return B2N_ERR_BAD_ARG;
+  const int64_t nclusters = M < max_clusters ? M : max_clusters;
+  cfg.gridDim = dim3(static_cast<unsigned>(nclusters * p.c));
+  ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_cluster" : "softmax_bwd_cluster")
+                        : (LOG ? "log_softmax_fwd_cluster" : "softmax_fwd_cluster"), st);
+  int* status = device_status_ptr();
+  const int slice_vecs = p.slice_vecs;
+  if (int e = check_cuda(cudaLaunchKernelEx(&cfg, kernel, in0, in1, out, M, N, slice_vecs, status))) return e;
+  return launched();
+}
+
 template <typename TI, typename TO, bool LOG>
 int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_t inner, cudaStream_t st) {
   const TI* x = static_cast<const TI*>(x_);
@@ -64,7 +124,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
       if (forced != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
         const DeviceInfo& di = device_info();
         const RingPlan p = plan_ring(M, N, sizeof(TI), 1, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
-        if (p.ok) {
+        if (p.ok && forced != B2N_PATH_CLUSTER) {
           note_path("ring");
           switch (p.group) {
             case 32: return softmax_fwd_ring_launch<TI, LOG, 32>(p, x, y, M, N, st);
@@ -72,6 +132,13 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
             case 128: return softmax_fwd_ring_launch<TI, LOG, 128>(p, x, y, M, N, st);
             case 256: return softmax_fwd_ring_launch<TI, LOG, 256>(p, x, y, M, N, st);
             default: return softmax_fwd_ring_launch<TI, LOG, 512>(p, x, y, M, N, st);
+          }
+        }
+        if (forced != B2N_PATH_RING && (forced == B2N_PATH_CLUSTER || N * sizeof(TI) >= 32768)) {
+          const ClusterPlan cp = plan_cluster(N, sizeof(TI), 1, di.max_smem_optin);
+          if (cp.ok) {
+            note_path("cluster");
+            return softmax_cluster_launch<TI, LOG, false>(cp, x, static_cast<const TI*>(nullptr), y, M, N, st);
           }
         }
       }
@@ -114,7 +181,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
           N <= (1 << 20)) {
         const DeviceInfo& di = device_info();
         const RingPlan p = plan_ring(M, N, sizeof(TG), 2, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
-        if (p.ok) {
+        if (p.ok && forced != B2N_PATH_CLUSTER) {
           note_path("ring");
           switch (p.group) {
             case 32: return softmax_bwd_ring_launch<TG, LOG, 32>(p, dy, y, dx, M, N, st);
@@ -122,6 +189,13 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
             case 128: return softmax_bwd_ring_launch<TG, LOG, 128>(p, dy, y, dx, M, N, st);
             case 256: return softmax_bwd_ring_launch<TG, LOG, 256>(p, dy, y, dx, M, N, st);
             default: return softmax_bwd_ring_launch<TG, LOG, 512>(p, dy, y, dx, M, N, st);
+          }
+        }
+        if (forced != B2N_PATH_RING && (forced == B2N_PATH_CLUSTER || N * sizeof(TG) >= 32768)) {
+          const ClusterPlan cp = plan_cluster(N, sizeof(TG), 2, di.max_smem_optin);
+          if (cp.ok) {
+            note_path("cluster");
+            return softmax_cluster_launch<TG, LOG, true>(cp, dy, y, dx, M, N, st);
           }
         }
       }
