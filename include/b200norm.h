@@ -66,7 +66,8 @@ int b2n_set_path(int path);
 typedef enum b2n_tuning_knob {
   B2N_TUNE_ROWS_PER_GROUP = 0, /* rows of a tile each row group works through (1..4) */
   B2N_TUNE_STAGES = 1,         /* upper bound on the ring depth */
-  B2N_TUNE_STORE_LAG = 2       /* bulk stores left in flight before a stage is refilled (1..3) */
+  B2N_TUNE_STORE_LAG = 2,      /* bulk stores left in flight before a stage is refilled (1..3) */
+  B2N_TUNE_CLUSTER_SIZE = 3    /* CTAs per row in the cluster kernels (2, 4 or 8) */
 } b2n_tuning_knob;
 int b2n_set_tuning(int knob, int value);
 /* Diagnostic: while a buffer is set (this thread), CTA 0 of the layer-norm / RMS-norm forward ring

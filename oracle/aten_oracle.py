@@ -185,6 +185,14 @@ def softmax_bwd(dy, y, dim, is_log: bool, input_dtype, exact: bool = True):
     return op(_cpu(dy), _cpu(y), dim, input_dtype)
 
 
+def softmax_bwd_fp64(dy, y, dim, is_log: bool, out_dtype):
+    """The backward evaluated in float64 on the same inputs, rounded once.  Over rows of tens of thousands of
+    elements the fp32 CPU kernel's own row sum carries ~1e-4 of absolute error, which the kernel under test
+    does not share; this is the reference to use where that matters."""
+    op = aten._log_softmax_backward_data if is_log else aten._softmax_backward_data
+    return op(dy.detach().cpu().double(), y.detach().cpu().double(), dim, torch.float64).to(out_dtype)
+
+
 def nll_fwd(logp, target, weight, reduction: int, ignore_index: int, exact: bool = True):
     """(output, total_weight); exact: fp32 upcast, rounded once."""
     if exact and logp.dtype != torch.float64:

@@ -207,5 +207,10 @@ def test_cluster_kernels_for_long_rows(M, N, dt, is_log):
     ry = ao.softmax_fwd(x, -1, is_log)
     assert torch.equal(torch.isnan(y.cpu()), torch.isnan(ry))
     check_out(y, ry, "y")
-    check_out(dx, ao.softmax_bwd(dy, y.cpu(), -1, is_log, dt), "dx", tol=2.0)
+    if dt == torch.float32:
+        # judged against the fp64 evaluation: the fp32 CPU kernel's own sum over a row this long is the
+        # larger error (see oracle.aten_oracle.softmax_bwd_fp64)
+        check_out(dx, ao.softmax_bwd_fp64(dy, y.cpu(), -1, is_log, dt), "dx", tol=2.0)
+    else:
+        check_out(dx, ao.softmax_bwd(dy, y.cpu(), -1, is_log, dt), "dx", tol=2.0)
     assert capi.device_status() == 0

@@ -1,6 +1,8 @@
 // Typed host launchers for softmax / log-softmax.  Instantiated per type pair in softmax_*.cu.
 #pragma once
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 #include <type_traits>
 
 #include "launchers.h"
@@ -65,9 +67,11 @@ inline ClusterPlan plan_cluster(int64_t N, int esize, int nin, int max_smem) {
   const int64_t nvec = N / vec;
   const int64_t third = (static_cast<int64_t>(max_smem) / 3 - kClusterHeaderBytes - 1024) / 16 * 16;  // three CTAs per SM
   const int64_t whole = (static_cast<int64_t>(max_smem) - kClusterHeaderBytes) / 16 * 16;
+  const int forced_c = ring_tuning().cluster;
   for (int pass = 0; pass < 2 && !p.ok; ++pass) {
     const int64_t budget = pass == 0 ? third : whole;
     for (int c = 2; c <= 8; c *= 2) {
+      if (forced_c >= 2 && c != forced_c) continue;
       const int64_t sv = (nvec + c - 1) / c;
       if (sv * 16 * nin <= budget) {
         p.ok = true;
@@ -104,6 +108,9 @@ int softmax_cluster_launch(const ClusterPlan& p, const T* in0, const T* in1, T* 
   if (int e = check_cuda(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg))) return e;
   if (max_clusters < 1) return B2N_ERR_BAD_ARG;
   const int64_t nclusters = M < max_clusters ? M : max_clusters;
+  if (getenv("B2N_DEBUG") != nullptr)
+    fprintf(stderr, "[b200norm] cluster launch: C=%d slice_vecs=%d smem=%zu max_clusters=%d clusters=%lld\n", p.c,
+            p.slice_vecs, p.smem, max_clusters, static_cast<long long>(nclusters));
   cfg.gridDim = dim3(static_cast<unsigned>(nclusters * p.c));
   ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_cluster" : "softmax_bwd_cluster")
                         : (LOG ? "log_softmax_fwd_cluster" : "softmax_fwd_cluster"), st);
