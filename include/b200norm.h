@@ -123,6 +123,21 @@ int b2n_layer_norm_bwd(const void* dy, const void* x, const void* mean, const vo
                        size_t workspace_bytes, int64_t M, int64_t N, int x_dtype, int w_dtype,
                        void* stream);
 
+/* No counterpart in the reference: the same backward for callers that cannot allocate — an
+ * inference engine's plug-in enqueue callback, a serving loop with a frozen memory pool, a
+ * process whose device memory already belongs to another allocator — and so have no workspace
+ * to pass.  The weight-gradient partial sums live in a fixed device array inside the library
+ * (b2n_noalloc_scratch_bytes() = 16 MiB, held by every GPU that loads the library until the
+ * process exits); nothing is allocated on the call path.  Problems that need more scratch than
+ * that (b2n_norm_bwd_workspace_bytes(...) > 16 MiB) return B2N_ERR_TOO_LARGE.  All calls on a
+ * device share the array, so calls that overlap on the GPU race: serialise them.  The first call
+ * on a device looks up the array's address; make it before any stream capture begins.  Results
+ * equal b2n_layer_norm_bwd's. */
+size_t b2n_noalloc_scratch_bytes(void);
+int b2n_layer_norm_bwd_noalloc(const void* dy, const void* x, const void* mean, const void* rstd,
+                               const void* gamma, void* dx, void* dgamma, void* dbeta, int64_t M,
+                               int64_t N, int x_dtype, int w_dtype, void* stream);
+
 /* Replaces at::native::xpu::rms_norm_backward_kernel (sycl/LayerNormKernels.h:51-58) behind
  * _fused_rms_norm_backward_xpu (LayerNorm.cpp:255). */
 int b2n_rms_norm_bwd(const void* dy, const void* x, const void* rstd, const void* gamma, void* dx,
