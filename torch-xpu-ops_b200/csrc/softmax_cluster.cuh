@@ -22,7 +22,7 @@ namespace b2n {
 
 namespace cg = cooperative_groups;
 
-constexpr int kClusterThreads = 512;
+constexpr int kClusterThreads = 256;
 constexpr int kClusterHeaderBytes = 256;
 
 // exp for a value already reduced by the row maximum: expf for fp32 storage, the hardware 2^x for
