@@ -331,6 +331,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--rows", type=int, default=0, help="override the workload's global row count (small cases for ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -340,6 +341,9 @@ def main():
     if args.workload != "cfg4":
         _load_more_workloads()
     wl = WORKLOADS[args.workload]()
+    if args.rows > 0:
+        wl.rows = args.rows
+        wl.cpu_sample_rows = min(wl.cpu_sample_rows, args.rows)
 
     if args.impl == "reference":
         run_reference(args, wl, rank)

@@ -213,7 +213,8 @@ class Cfg5CrossEntropy(_Simple):
         fwd, bwd = 2 * rows * v * 2, 3 * rows * v * 2
         return {"total": fwd + bwd + rows * 40, "log_softmax_fwd_ring": fwd, "log_softmax_bwd_ring": bwd,
                 "log_softmax_fwd_generic": fwd, "log_softmax_bwd_generic": bwd,
-                "log_softmax_fwd_cluster": fwd, "log_softmax_bwd_cluster": bwd}
+                "log_softmax_fwd_cluster": fwd, "log_softmax_bwd_cluster": bwd,
+                "log_softmax_fwd_twopass": fwd, "log_softmax_bwd_twopass": bwd}
 
     def make_cpu_state(self, rows):
         g = torch.Generator().manual_seed(5001)

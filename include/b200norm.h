@@ -50,7 +50,8 @@ typedef enum b2n_path {
   B2N_PATH_AUTO = 0,
   B2N_PATH_GENERIC = 1, /* global-memory multi-pass kernels: any alignment, any N */
   B2N_PATH_RING = 2,    /* persistent CTAs, bulk-async (TMA) shared-memory ring, register-resident rows */
-  B2N_PATH_CLUSTER = 3  /* long rows split over a thread-block cluster (distributed shared memory) */
+  B2N_PATH_CLUSTER = 3, /* long rows split over a thread-block cluster, slices resident in shared memory */
+  B2N_PATH_TWOPASS = 4  /* long rows streamed through the ring twice, second pass served from L2 */
 } b2n_path;
 
 int b2n_abi_version(void);

@@ -127,7 +127,7 @@ def test_config5_log_softmax_nll_bf16_16384x128256():
         logits[k:k + 2048] = (torch.randn((2048, V), generator=gen, device=DEV) * 2.0).to(torch.bfloat16)
     t = ao.randint(V, (M,), 5002).to(DEV)
     logp = capi._log_softmax(logits, -1, False)
-    assert capi.last_path() == "cluster"
+    assert capi.last_path() in ("cluster", "twopass")
     idx = sample_rows(M, 24).to(DEV)
     assert ao.lowp_mismatch(logp[idx], ao.softmax_fwd(logits[idx].cpu(), -1, True))[0] == 0
     # every row: log-sum-exp of the output is zero up to the bf16 rounding of the entries
@@ -142,7 +142,7 @@ def test_config5_log_softmax_nll_bf16_16384x128256():
     grad_logp = capi.nll_loss_backward(torch.ones((), device=DEV, dtype=torch.bfloat16), logp, t, None, 1, -100, tw)
     assert float(grad_logp.gather(1, t.view(-1, 1)).float().mean()) == pytest.approx(-1.0 / M, rel=1e-2)
     dlogits = capi._log_softmax_backward_data(grad_logp, logp, -1, torch.bfloat16)
-    assert capi.last_path() == "cluster"
+    assert capi.last_path() in ("cluster", "twopass")
     ref = ao.softmax_bwd(grad_logp[idx].cpu(), logp[idx].cpu(), -1, True, torch.bfloat16)
     assert ao.lowp_mismatch(dlogits[idx], ref)[0] == 0
     # rows of the cross-entropy gradient sum to ~0

@@ -180,12 +180,14 @@ def test_ring_is_used_for_aligned_rows_and_refuses_others_when_forced():
             capi._softmax(ao.randn((4, 33), 471).to(DEV), -1, False)  # 33 floats: not a multiple of 16 bytes
 
 
+@pytest.mark.parametrize("path,name", [(b200norm.PATH_CLUSTER, "cluster"), (b200norm.PATH_TWOPASS, "twopass")])
 @pytest.mark.parametrize("is_log", [False, True])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.float16])
 @pytest.mark.parametrize("M,N", [(5, 16384), (3, 40000), (7, 65544), (2, 128256), (300, 20008)])
-def test_cluster_kernels_for_long_rows(M, N, dt, is_log):
-    # rows split over a thread-block cluster (ragged last slice included: 65544 and 20008 vectors do not
-    # divide evenly); degenerate rows keep the CPU semantics
+def test_long_row_kernels(M, N, dt, is_log, path, name):
+    # the two kernel families for rows beyond the ring: slices resident in the shared memory of a cluster, and
+    # two passes through the ring (ragged last slice / chunk included: 65544 and 20008 elements do not divide
+    # evenly); degenerate rows keep the CPU semantics
     x = ao.randn((M, N), 480 + N % 97, torch.float32, 0.0, 2.0)
     x[0, N // 2:] = float("-inf")
     if M > 2:
@@ -195,13 +197,13 @@ def test_cluster_kernels_for_long_rows(M, N, dt, is_log):
     dy = ao.randn((M, N), 481, dt)
     fwd = capi._log_softmax if is_log else capi._softmax
     bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
-    with forced_path(b200norm.PATH_CLUSTER):
+    with forced_path(path):
         y_buf, y_chk = guarded_empty((M, N), dt)
         y = fwd(x.to(DEV), -1, False, out=y_buf)
-        assert capi.last_path() == "cluster"
+        assert capi.last_path() == name
         dx_buf, dx_chk = guarded_empty((M, N), dt)
         dx = bwd(dy.to(DEV), y, -1, dt, out=dx_buf)
-        assert capi.last_path() == "cluster"
+        assert capi.last_path() == name
     torch.cuda.synchronize()
     y_chk(); dx_chk()
     ry = ao.softmax_fwd(x, -1, is_log)

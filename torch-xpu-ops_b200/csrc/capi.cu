@@ -105,7 +105,7 @@ int b2n_last_cuda_error(void) { return tl_last_cuda_error; }
 
 int b2n_set_path(int path) {
   const int prev = tl_forced_path;
-  if (path >= B2N_PATH_AUTO && path <= B2N_PATH_CLUSTER) tl_forced_path = path;
+  if (path >= B2N_PATH_AUTO && path <= B2N_PATH_TWOPASS) tl_forced_path = path;
   return prev;
 }
 

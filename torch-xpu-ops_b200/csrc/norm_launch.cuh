@@ -86,7 +86,7 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
       }
     }
   }
-  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
 
   note_path("generic");
   ProfileScope prof(RMS ? "rms_norm_fwd_generic" : "layer_norm_fwd_generic", st);
@@ -191,7 +191,7 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
       }
     }
   }
-  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
 
   note_path("generic");
   if (dx != nullptr) {

@@ -21,7 +21,7 @@ struct RingPlan {
 // Per-thread overrides for tuning sweeps (0 = automatic); set through b2n_set_tuning.
 struct RingTuning {
   int rpg = 0, stages = 0, lag = 0;
-  int cluster = 0;  // CTAs per row in the cluster kernels (2, 4 or 8)
+  int cluster = 0;  // CTAs per row in the cluster kernels (1, 2, 4 or 8)
   unsigned long long* trace_buf = nullptr;  // device buffer for the event trace (diagnostic), or null
   unsigned trace_cap = 0;                   // records it can hold
 };

@@ -10,6 +10,7 @@
 #include "softmax_generic.cuh"
 #include "softmax_ring.cuh"
 #include "softmax_cluster.cuh"
+#include "softmax_twopass.cuh"
 
 namespace b2n {
 
@@ -56,30 +57,26 @@ int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, i
   return launched();
 }
 
-// Rows too long for the ring: split a row over a cluster of C CTAs (C = 2, 4 or 8), slice in shared
-// memory.  Returns B2N_ERR_BAD_ARG when the row does not fit even 8 CTAs (the caller then falls
-// back to the generic kernels).
+// Rows too long for the ring: a row is split over a cluster of C CTAs (C = 1, 2, 4 or 8, one CTA per
+// SM), each keeping its slice resident in shared memory.  Not ok when the row does not fit even 8
+// CTAs (the caller then falls back to the generic kernels).
 struct ClusterPlan { bool ok = false; int c = 0; int slice_vecs = 0; size_t smem = 0; };
 inline ClusterPlan plan_cluster(int64_t N, int esize, int nin, int max_smem) {
   ClusterPlan p;
   const int vec = 16 / esize;
   if (N % vec != 0) return p;
   const int64_t nvec = N / vec;
-  const int64_t third = (static_cast<int64_t>(max_smem) / 3 - kClusterHeaderBytes - 1024) / 16 * 16;  // three CTAs per SM
-  const int64_t whole = (static_cast<int64_t>(max_smem) - kClusterHeaderBytes) / 16 * 16;
+  const int64_t budget = (static_cast<int64_t>(max_smem) - kSlabHeaderBytes) / 16 * 16;
   const int forced_c = ring_tuning().cluster;
-  for (int pass = 0; pass < 2 && !p.ok; ++pass) {
-    const int64_t budget = pass == 0 ? third : whole;
-    for (int c = 2; c <= 8; c *= 2) {
-      if (forced_c >= 2 && c != forced_c) continue;
-      const int64_t sv = (nvec + c - 1) / c;
-      if (sv * 16 * nin <= budget) {
-        p.ok = true;
-        p.c = c;
-        p.slice_vecs = static_cast<int>(sv);
-        p.smem = static_cast<size_t>(kClusterHeaderBytes + sv * 16 * nin);
-        break;
-      }
+  for (int c = 1; c <= kSlabMaxCluster; c *= 2) {
+    if (forced_c >= 1 && c != forced_c) continue;
+    const int64_t sv = (nvec + c - 1) / c;
+    if (sv * 16 * nin <= budget && sv <= static_cast<int64_t>(kSlabChunkVecs) * kSlabMaxChunks) {
+      p.ok = true;
+      p.c = c;
+      p.slice_vecs = static_cast<int>(sv);
+      p.smem = static_cast<size_t>(kSlabHeaderBytes + sv * 16 * nin);
+      break;
     }
   }
   return p;
@@ -88,7 +85,7 @@ inline ClusterPlan plan_cluster(int64_t N, int esize, int nin, int max_smem) {
 template <typename T, bool LOG, bool BWD>
 int softmax_cluster_launch(const ClusterPlan& p, const T* in0, const T* in1, T* out, int64_t M, int64_t N,
                            cudaStream_t st) {
-  auto kernel = softmax_cluster_kernel<T, LOG, BWD>;
+  auto kernel = softmax_slab_kernel<T, LOG, BWD>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
   cudaLaunchConfig_t cfg = {};
@@ -99,7 +96,7 @@ int softmax_cluster_launch(const ClusterPlan& p, const T* in0, const T* in1, T* 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cfg.blockDim = dim3(kClusterThreads);
+  cfg.blockDim = dim3(kSlabThreads);
   cfg.dynamicSmemBytes = p.smem;
   cfg.stream = st;
   // persistent clusters: as many as the device holds at once
@@ -120,6 +117,27 @@ int softmax_cluster_launch(const ClusterPlan& p, const T* in0, const T* in1, T* 
   return launched();
 }
 
+// Rows of any length: two passes through the ring per row, the second served from L2.
+template <typename T, bool LOG, bool BWD>
+int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_t N, cudaStream_t st) {
+  auto kernel = softmax_twopass_kernel<T, LOG, BWD>;
+  static std::atomic<uint64_t> mask{0};
+  if (int e = set_smem_once_sm(kernel, mask)) return e;
+  const DeviceInfo& di = device_info();
+  const int64_t stage = static_cast<int64_t>(kTwoPassChunkVecs) * 16 * (BWD ? 2 : 1);
+  int64_t stages = (static_cast<int64_t>(di.max_smem_optin) - kRingHeaderBytes) / stage;
+  if (stages > kMaxStages) stages = kMaxStages;
+  const int tuned = ring_tuning().stages;
+  if (tuned > 0 && tuned < stages) stages = tuned;
+  if (stages < 3) return B2N_ERR_BAD_ARG;
+  const size_t smem = static_cast<size_t>(kRingHeaderBytes + stages * stage);
+  const int grid = static_cast<int>(M < di.sm_count ? M : di.sm_count);
+  ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_twopass" : "softmax_bwd_twopass")
+                        : (LOG ? "log_softmax_fwd_twopass" : "softmax_fwd_twopass"), st);
+  kernel<<<grid, kRingBlock, smem, st>>>(in0, in1, out, M, N, static_cast<int>(stages), device_status_ptr());
+  return launched();
+}
+
 template <typename TI, typename TO, bool LOG>
 int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_t inner, cudaStream_t st) {
   const TI* x = static_cast<const TI*>(x_);
@@ -131,7 +149,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
       if (forced != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
         const DeviceInfo& di = device_info();
         const RingPlan p = plan_ring(M, N, sizeof(TI), 1, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
-        if (p.ok && forced != B2N_PATH_CLUSTER) {
+        if (p.ok && forced != B2N_PATH_CLUSTER && forced != B2N_PATH_TWOPASS) {
           note_path("ring");
           switch (p.group) {
             case 32: return softmax_fwd_ring_launch<TI, LOG, 32>(p, x, y, M, N, st);
@@ -141,16 +159,19 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
             default: return softmax_fwd_ring_launch<TI, LOG, 512>(p, x, y, M, N, st);
           }
         }
-        if (forced != B2N_PATH_RING && (forced == B2N_PATH_CLUSTER || N * sizeof(TI) >= 32768)) {
+        if (forced == B2N_PATH_CLUSTER) {
           const ClusterPlan cp = plan_cluster(N, sizeof(TI), 1, di.max_smem_optin);
           if (cp.ok) {
             note_path("cluster");
             return softmax_cluster_launch<TI, LOG, false>(cp, x, static_cast<const TI*>(nullptr), y, M, N, st);
           }
+        } else if (forced == B2N_PATH_TWOPASS || (forced == B2N_PATH_AUTO && N * sizeof(TI) >= 32768)) {
+          note_path("twopass");
+          return softmax_twopass_launch<TI, LOG, false>(x, static_cast<const TI*>(nullptr), y, M, N, st);
         }
       }
     }
-    if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+    if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
     note_path("generic");
     ProfileScope prof(LOG ? "log_softmax_fwd_generic" : "softmax_fwd_generic", st);
     constexpr int V = 16 / sizeof(TI);  // vector width in elements, by the input type
@@ -167,7 +188,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
     }
     return launched();
   }
-  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
   const int grid = softmax_generic_grid(outer * inner, 256);
   softmax_fwd_spatial_kernel<TI, TO, LOG><<<grid, 256, 0, st>>>(x, y, outer, N, inner);
@@ -188,7 +209,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
           N <= (1 << 20)) {
         const DeviceInfo& di = device_info();
         const RingPlan p = plan_ring(M, N, sizeof(TG), 2, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
-        if (p.ok && forced != B2N_PATH_CLUSTER) {
+        if (p.ok && forced != B2N_PATH_CLUSTER && forced != B2N_PATH_TWOPASS) {
           note_path("ring");
           switch (p.group) {
             case 32: return softmax_bwd_ring_launch<TG, LOG, 32>(p, dy, y, dx, M, N, st);
@@ -198,16 +219,19 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
             default: return softmax_bwd_ring_launch<TG, LOG, 512>(p, dy, y, dx, M, N, st);
           }
         }
-        if (forced != B2N_PATH_RING && (forced == B2N_PATH_CLUSTER || N * sizeof(TG) >= 32768)) {
+        if (forced == B2N_PATH_CLUSTER) {
           const ClusterPlan cp = plan_cluster(N, sizeof(TG), 2, di.max_smem_optin);
           if (cp.ok) {
             note_path("cluster");
             return softmax_cluster_launch<TG, LOG, true>(cp, dy, y, dx, M, N, st);
           }
+        } else if (forced == B2N_PATH_TWOPASS || (forced == B2N_PATH_AUTO && N * sizeof(TG) >= 32768)) {
+          note_path("twopass");
+          return softmax_twopass_launch<TG, LOG, true>(dy, y, dx, M, N, st);
         }
       }
     }
-    if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+    if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
     note_path("generic");
     ProfileScope prof(LOG ? "log_softmax_bwd_generic" : "softmax_bwd_generic", st);
     constexpr int V = (16 / sizeof(TG)) < (16 / sizeof(TO)) ? (16 / sizeof(TG)) : (16 / sizeof(TO));
@@ -225,7 +249,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
     }
     return launched();
   }
-  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER) return B2N_ERR_BAD_ARG;
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
   const int grid = softmax_generic_grid(outer * inner, 256);
   softmax_bwd_spatial_kernel<TG, TO, LOG><<<grid, 256, 0, st>>>(dy, y, dx, outer, N, inner);
