@@ -81,6 +81,7 @@ class Cfg1LayerNormFwd(_Simple):
 
 class Cfg2RmsNorm(_Simple):
     name, rows, N, cpu_sample_rows = "cfg2", 8192, 4096, 8192
+    collective = "all_reduce(fp32[2,N]) per step"
     e2e_inputs = ("x", "dy")
     launches_per_step = 3
 
@@ -146,6 +147,7 @@ class Cfg2RmsNorm(_Simple):
 
 class Cfg3Softmax(_Simple):
     name, T, cpu_sample_rows = "cfg3", 2048, 8192
+    collective = "none (rows are independent)"
     rows = 8 * 32 * 2048
     e2e_inputs = ("s", "g")
 
@@ -201,6 +203,7 @@ class Cfg3Softmax(_Simple):
 
 class Cfg5CrossEntropy(_Simple):
     name, rows, V, cpu_sample_rows = "cfg5", 16384, 128256, 1024
+    collective = "all_reduce(fp32[2]: loss sum, weight sum) per step"
     e2e_inputs = ("logits", "target")
     launches_per_step = 6
 

@@ -32,6 +32,8 @@ __device__ __forceinline__ void load_weights(const WT* __restrict__ w, float fil
   }
 }
 
+constexpr int kTraceTid = 160;  // the consumer thread that writes trace records (lane 0 of warp 5)
+
 template <typename T, typename WT, bool RMS, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta,
@@ -76,9 +78,9 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   unsigned tk = 0;  // trace record counter (diagnostic)
   int64_t i = 0;
   for (; i < g.my_tiles; ++i, cur.advance(g)) {
-    if (tid == 0) g.trace.put(0, tk, EV_C_WAIT_BEGIN, i);
+    if (tid == kTraceTid) g.trace.put(0, tk, EV_C_WAIT_BEGIN, i);
     if (!ring_consumer_wait(rs, cur, status)) break;
-    if (tid == 0) g.trace.put(0, tk, EV_C_WAIT_END, i);
+    if (tid == kTraceTid) g.trace.put(0, tk, EV_C_WAIT_END, i);
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     // A group takes its rows of the tile RB at a time: the partial sums of RB rows go through ONE
     // group reduction (one barrier, RB values), which halves the time the group's warps spend
@@ -129,9 +131,9 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         }
         red1[b] = hsum2(add2(part[0], part[1]));
       }
-      if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 0, i);
+      if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 0, i);
       group_reduce<GROUP, RB>(red1, rs->red, grp, tg, red_phase, SumOp());
-      if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 1, i);
+      if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 1, i);
       float mu_d[RB], rsd[RB];  // mu_d: mean of (x - shift)
       if constexpr (RMS) {
 #pragma unroll
@@ -159,12 +161,13 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           }
           red2[b] = hsum2(add2(q[0], q[1]));
         }
-        if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 2, i);
+        if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 2, i);
         group_reduce<GROUP, RB>(red2, rs->red, grp, tg, red_phase, SumOp());
-        if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 3, i);
+        if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 3, i);
 #pragma unroll
         for (int b = 0; b < RB; ++b) rsd[b] = rsqrt_nr(red2[b] * inv_n + eps);
       }
+      if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 5, i);
 #pragma unroll
       for (int b = 0; b < RB; ++b) {
         if (!valid[b]) continue;
@@ -185,15 +188,16 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
             sts128(rbase[b] + v * 16, P::pack2(o));
           }
         }
+        if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 6 + b, i);
         if (tg == 0) {
           if (!RMS && mean) mean[row_a + b] = shift[b] + mu_d[b];
           if (rstd) rstd[row_a + b] = rsd[b];
         }
       }
     }
-    if (tid == 0) g.trace.put(0, tk, EV_C_STEP + 4, i);
+    if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 4, i);
     ring_consumer_release(rs, cur);
-    if (tid == 0) g.trace.put(0, tk, EV_C_RELEASED, i);
+    if (tid == kTraceTid) g.trace.put(0, tk, EV_C_RELEASED, i);
   }
 }
 

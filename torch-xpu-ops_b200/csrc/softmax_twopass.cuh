@@ -160,13 +160,20 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
             const float nm = fmaxf(pm, vm);
             const float scale = (pm == ninf) ? 0.0f : row_exp2p<T>(pm - nm);
             const float base = (nm == ninf) ? 0.0f : nm;  // all -inf so far: exp(-inf - 0) = 0; NaN stays NaN
-            float a0 = 0.0f, a1 = 0.0f;
+            float2 a = bcast2(0.0f);
+            if constexpr (sizeof(T) == 4) {
 #pragma unroll
-            for (int e = 0; e < VH; ++e) {
-              a0 += row_exp2p<T>(f[e].x - base);
-              a1 += row_exp2p<T>(f[e].y - base);
+              for (int e = 0; e < VH; ++e) a = add2(a, make_float2(expf(f[e].x - base), expf(f[e].y - base)));
+            } else {
+              // 2^(x*log2e - base*log2e): one packed FMA per pair, then the hardware 2^x
+              const float2 l2e = bcast2(kLog2e), nb = bcast2(-base * kLog2e);
+#pragma unroll
+              for (int e = 0; e < VH; ++e) {
+                const float2 tt = fma2(f[e], l2e, nb);
+                a = add2(a, make_float2(ex2_approx(tt.x), ex2_approx(tt.y)));
+              }
             }
-            ps = fmaf(ps, scale, a0 + a1);
+            ps = fmaf(ps, scale, hsum2(a));
             pm = nm;
           } else if constexpr (LOG) {
 #pragma unroll
