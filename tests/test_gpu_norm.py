@@ -207,6 +207,48 @@ def test_large_offset_row_is_finite_and_matches():
     assert float(y.abs().max()) == 0.0 and torch.equal(mean.cpu().reshape(-1), x[:, 0])
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [256, 4096, 8192])
+def test_rows_whose_first_element_is_far_from_the_mean(N, dt):
+    # The ring forward shifts a row by its first element and takes both moments in one reduction unless that
+    # element lies far from the row mean, in which case it recomputes the variance about the mean.  Rows of
+    # every kind, interleaved so that both kinds meet in one tile: ordinary, first element an outlier by
+    # 3..1000 standard deviations, large common offset with small spread, constant.
+    M = 64
+    x = ao.randn((M, N), 350 + N, torch.float32)
+    for r in range(M):
+        kind = r % 8
+        if kind in (1, 2, 3):
+            x[r, 0] += (3.0, 30.0, 1000.0)[kind - 1]
+        elif kind == 4:
+            x[r] = 300.0 + 0.25 * x[r]
+        elif kind == 5:
+            x[r] = -7.5
+        elif kind == 6:
+            x[r] = 1e4 + x[r]
+            x[r, 0] = 0.0
+    x = x.to(dt)
+    g = ao.randn((N,), 351, torch.float32, 1.0, 0.02)
+    b = ao.randn((N,), 352, torch.float32, 0.0, 0.02)
+    y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5)
+    assert capi.last_path() == "ring"
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+    # statistics against fp64
+    xd = x.double()
+    mu = xd.mean(1)
+    rs = 1.0 / torch.sqrt(xd.var(1, unbiased=False) + 1e-5)
+    check_stat(mean, mu, "mean")
+    check_stat(rstd, rs, "rstd")
+    if dt == torch.float32:
+        # CPU ATen's own fp32 statistics carry a few 1e-6 of error on the offset rows; judge y by fp64
+        ref = ((xd - mu[:, None]) * rs[:, None] * g.double() + b.double())
+        err = ((y.cpu().double() - ref).abs() / (1e-5 * ref.abs() + 1e-6 * max(1.0, float(ref.pow(2).mean().sqrt())))).max()
+        assert float(err) <= 1.0, f"y: {float(err):.3f} x tolerance"
+    else:
+        check_out(y, ry, "y")
+    assert capi.device_status() == 0
+
+
 def test_rms_default_eps_is_accumulate_type_epsilon():
     x = ao.randn((8, 256), 340, torch.bfloat16)
     w = ao.randn((256,), 341, torch.bfloat16, 1.0, 0.02)

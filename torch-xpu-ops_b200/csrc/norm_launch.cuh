@@ -73,7 +73,8 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
   if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
     if (forced != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
       const DeviceInfo& di = device_info();
-      const RingPlan p = plan_ring(M, N, sizeof(T), 1, kNormFwdEpt, di.sm_count, di.max_smem_optin);
+      // one tensor per stage: 64 KB tiles (half as many tile hand-overs) still leave three stages in rotation
+      const RingPlan p = plan_ring(M, N, sizeof(T), 1, kNormFwdEpt, di.sm_count, di.max_smem_optin, 65536);
       if (p.ok) {
         note_path("ring");
         switch (p.group) {
@@ -107,6 +108,9 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
 }
 
 // ---- backward -----------------------------------------------------------------------------------
+template <typename T> RingPlan plan_norm_bwd(int64_t M, int64_t N, const DeviceInfo& di) {
+  return plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, di.sm_count, di.max_smem_optin);
+}
 // Number of partial rows ([2][N] accumulate-type values each) the weight-gradient reduction writes.
 inline int64_t wgrad_generic_chunks(int64_t M) {
   int64_t c = (M + 63) / 64;
@@ -116,7 +120,7 @@ template <typename T> int64_t wgrad_partial_rows(int64_t M, int64_t N) {
   int64_t rows = wgrad_generic_chunks(M);
   if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
     const DeviceInfo& di = device_info();
-    const RingPlan p = plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, di.sm_count, di.max_smem_optin);
+    const RingPlan p = plan_norm_bwd<T>(M, N, di);
     if (p.ok && static_cast<int64_t>(p.grid) * p.ng > rows) rows = static_cast<int64_t>(p.grid) * p.ng;
   }
   return rows;
@@ -173,7 +177,7 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
     if (forced != B2N_PATH_GENERIC && dx != nullptr && is_aligned(dy, 16) && is_aligned(x, 16) &&
         is_aligned(dx, 16) && N <= (1 << 20)) {
       const DeviceInfo& di = device_info();
-      const RingPlan p = plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, di.sm_count, di.max_smem_optin);
+      const RingPlan p = plan_norm_bwd<T>(M, N, di);
       if (p.ok) {
         note_path("ring");
         int e;

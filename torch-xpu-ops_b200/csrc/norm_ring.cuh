@@ -93,14 +93,14 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
       uint32_t rbase[RB];
       float shift[RB];
       float2 xv[RB][HP];
-      float red1[RB];
+      float red1[RB * (RMS ? 1 : 2)];  // RMS: sum x^2;  layer norm: sum d and sum d^2 per row
 #pragma unroll
       for (int b = 0; b < RB; ++b) {
         valid[b] = (r + b < RPG) && (row_a + b < M);
         rbase[b] = sbase + static_cast<uint32_t>(lr0 + b) * g.row_bytes;
         // Layer norm works on d = x - shift, shift = the row's first element (a shared-memory
         // broadcast read): a large common offset then cancels exactly instead of being rounded
-        // away in the row sum.  RMS norm needs the raw values (shift = 0).
+        // away in the row sums.  RMS norm needs the raw values (shift = 0).
         shift[b] = 0.0f;
         if (!RMS && valid[b]) {
           float2 first[VH];
@@ -108,7 +108,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           shift[b] = first[0].x;
         }
         const float2 nshift = bcast2(-shift[b]);
-        float2 part[2] = {bcast2(0.0f), bcast2(0.0f)};
+        float2 ps[2] = {bcast2(0.0f), bcast2(0.0f)}, pq[2] = {bcast2(0.0f), bcast2(0.0f)};
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
@@ -117,22 +117,26 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
               const int j = k * VH + e;
-              if constexpr (RMS) {
-                part[j & 1] = fma2(xv[b][j], xv[b][j], part[j & 1]);
-              } else {
+              if constexpr (!RMS) {
                 xv[b][j] = add2(xv[b][j], nshift);
-                part[j & 1] = add2(part[j & 1], xv[b][j]);
+                ps[j & 1] = add2(ps[j & 1], xv[b][j]);
               }
+              pq[j & 1] = fma2(xv[b][j], xv[b][j], pq[j & 1]);
             }
           } else {
 #pragma unroll
             for (int e = 0; e < VH; ++e) xv[b][k * VH + e] = bcast2(0.0f);
           }
         }
-        red1[b] = hsum2(add2(part[0], part[1]));
+        if constexpr (RMS) {
+          red1[b] = hsum2(add2(pq[0], pq[1]));
+        } else {
+          red1[2 * b] = hsum2(add2(ps[0], ps[1]));
+          red1[2 * b + 1] = hsum2(add2(pq[0], pq[1]));
+        }
       }
       if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 0, i);
-      group_reduce<GROUP, RB>(red1, rs->red, grp, tg, red_phase, SumOp());
+      group_reduce<GROUP, RB * (RMS ? 1 : 2)>(red1, rs->red, grp, tg, red_phase, SumOp());
       if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 1, i);
       float mu_d[RB], rsd[RB];  // mu_d: mean of (x - shift)
       if constexpr (RMS) {
@@ -142,30 +146,58 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
           rsd[b] = rsqrt_nr(red1[b] * inv_n + eps);
         }
       } else {
-        float red2[RB];
+        // One reduction gives both moments of d.  var = E[d^2] - E[d]^2 loses (1 + 3 E[d]^2/var)
+        // ulps to cancellation, which is harmless while the row's first element lies within a few
+        // standard deviations of its mean (the usual case: |z| < 2.8 for 99.5 % of Gaussian rows).
+        // Otherwise — decided on the reduced values, so identically by every thread of the group —
+        // the variance is taken again about the mean with a second pass over the registers.
+        float var[RB];
+        bool exact = true;
 #pragma unroll
         for (int b = 0; b < RB; ++b) {
-          mu_d[b] = red1[b] * inv_n;
-          const float2 nmu = bcast2(-mu_d[b]);
-          float2 q[2] = {bcast2(0.0f), bcast2(0.0f)};
+          mu_d[b] = red1[2 * b] * inv_n;
+          const float m2 = mu_d[b] * mu_d[b];
+          var[b] = fmaf(red1[2 * b + 1], inv_n, -m2);
+          exact = exact && (m2 <= 8.0f * var[b]);  // false for NaN and for a variance that cancelled below zero
+        }
+        if (!exact) {
+          // Second pass, from the tile still in shared memory, with the mean just found as the new
+          // shift (an outlying first element also costs every d the low bits of x, so the registers
+          // are rebuilt, not reused): c = sum d and q = sum d^2 about a shift that is now within
+          // rounding of the mean give mean = shift + c/N and var = (q - c^2/N)/N without cancellation.
+          float red2[2 * RB];
 #pragma unroll
-          for (int k = 0; k < VPT; ++k) {
-            if (tg + k * GROUP < nvec) {
+          for (int b = 0; b < RB; ++b) {
+            shift[b] += mu_d[b];
+            const float2 nshift = bcast2(-shift[b]);
+            float2 q[2] = {bcast2(0.0f), bcast2(0.0f)}, c[2] = {bcast2(0.0f), bcast2(0.0f)};
 #pragma unroll
-              for (int e = 0; e < VH; ++e) {
-                const int j = k * VH + e;
-                const float2 d = add2(xv[b][j], nmu);
-                q[j & 1] = fma2(d, d, q[j & 1]);
+            for (int k = 0; k < VPT; ++k) {
+              const int v = tg + k * GROUP;
+              if (valid[b] && v < nvec) {
+                P::unpack2(lds128(rbase[b] + v * 16), &xv[b][k * VH]);
+#pragma unroll
+                for (int e = 0; e < VH; ++e) {
+                  const int j = k * VH + e;
+                  xv[b][j] = add2(xv[b][j], nshift);
+                  c[j & 1] = add2(c[j & 1], xv[b][j]);
+                  q[j & 1] = fma2(xv[b][j], xv[b][j], q[j & 1]);
+                }
               }
             }
+            red2[2 * b] = hsum2(add2(c[0], c[1]));
+            red2[2 * b + 1] = hsum2(add2(q[0], q[1]));
           }
-          red2[b] = hsum2(add2(q[0], q[1]));
-        }
-        if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 2, i);
-        group_reduce<GROUP, RB>(red2, rs->red, grp, tg, red_phase, SumOp());
-        if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 3, i);
+          group_reduce<GROUP, 2 * RB>(red2, rs->red, grp, tg, red_phase, SumOp());
 #pragma unroll
-        for (int b = 0; b < RB; ++b) rsd[b] = rsqrt_nr(red2[b] * inv_n + eps);
+          for (int b = 0; b < RB; ++b) {
+            mu_d[b] = red2[2 * b] * inv_n;
+            const float vq = fmaf(-mu_d[b], red2[2 * b], red2[2 * b + 1]) * inv_n;
+            var[b] = vq < 0.0f ? 0.0f : vq;  // keeps NaN
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < RB; ++b) rsd[b] = rsqrt_nr(var[b] + eps);
       }
       if (tid == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 5, i);
 #pragma unroll

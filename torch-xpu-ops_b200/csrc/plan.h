@@ -28,9 +28,12 @@ struct RingTuning {
 RingTuning& ring_tuning();
 
 // N elements of `esize` bytes per row, `nin` tensors staged per tile, `ept` elements per thread.
+// `target`: bytes per tensor per tile to aim for; `default_lag`: see RingPlan::lag; `reserve`: bytes of
+// shared memory the kernel keeps between the ring header and the stages.
 // Not ok when the row is not a multiple of 16 bytes, does not fit 512 threads x ept elements, or
 // fewer than two stages fit in shared memory.
-inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int sm_count, int max_smem) {
+inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int sm_count, int max_smem,
+                          int64_t target = 32768, int default_lag = 1, int64_t reserve = 0) {
   RingPlan p;
   const int vec = 16 / esize;
   if (M <= 0 || N <= 0 || N % vec != 0) return p;
@@ -42,7 +45,6 @@ inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int
   p.group = group;
   p.ng = kRingThreads / group;
   const int64_t row_bytes = N * esize;
-  const int64_t target = 32768;  // bytes per tensor per tile
   int64_t rpg = target / (p.ng * row_bytes);
   // keep at least ~4 tiles per CTA when there are few rows
   while (rpg > 1 && (M + p.ng * rpg - 1) / (p.ng * rpg) < 4LL * sm_count) --rpg;
@@ -51,17 +53,17 @@ inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int
   const RingTuning& tune = ring_tuning();
   if (tune.rpg > 0) p.rpg = tune.rpg > 4 ? 4 : tune.rpg;
   const int64_t stage = static_cast<int64_t>(nin) * p.ng * p.rpg * row_bytes;
-  int64_t s = (static_cast<int64_t>(max_smem) - kRingHeaderBytes) / stage;
+  int64_t s = (static_cast<int64_t>(max_smem) - kRingHeaderBytes - reserve) / stage;
   if (s > kMaxStages) s = kMaxStages;
   if (tune.stages > 0 && tune.stages < s) s = tune.stages;
   if (s < 2) return p;
   p.stages = static_cast<int>(s);
-  p.lag = 1;
+  p.lag = default_lag;
   if (tune.lag > 0) p.lag = tune.lag;
   if (p.lag > s - 2) p.lag = static_cast<int>(s) - 2;
   if (p.lag < 1) p.lag = 1;
   if (p.lag > 3) p.lag = 3;
-  p.smem = static_cast<size_t>(kRingHeaderBytes + s * stage);
+  p.smem = static_cast<size_t>(kRingHeaderBytes + reserve + s * stage);
   const int64_t ntiles = (M + p.ng * p.rpg - 1) / (p.ng * p.rpg);
   p.grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);
   p.ok = true;

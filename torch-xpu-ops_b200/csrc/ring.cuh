@@ -201,46 +201,71 @@ __device__ __forceinline__ void ring_consumer_release(RingShared* rs, const Ring
 }
 
 // ---- reductions over the GROUP threads that share a row ----------------------------------------
-// K values (K <= 2) are reduced together, in a fixed order (bit-reproducible).
+// K values (K = 1, 2 or 4) are reduced together, in a fixed order (bit-reproducible).
 //
-// Within a warp, two values share one butterfly: the first exchange (lane ^ 16) leaves value 0 in
-// lanes 0-15 and value 1 in lanes 16-31, so the remaining four levels serve both at once.
-// Across the W = GROUP/32 warps of a group: lane 0 / lane 16 of each warp write the warp's totals
-// to the header scratch ([group][phase][K][W], double-buffered by `phase` so one named barrier per
-// reduction is enough); after the barrier, lane (k*W + w) of EVERY warp reads partial (k, w) and a
-// log2(W)-level butterfly inside each W-lane segment finishes the job — one shared-memory load and
-// at most four shuffles per thread instead of W loads and W adds.
+// Within a warp the K values share one butterfly: each of the first log2(K) exchanges halves the
+// number of values a lane carries (lane ^ 16 leaves values {0,1} in lanes 0-15 and {2,3} in lanes
+// 16-31; lane ^ 8 splits those again), so value k ends up, fully summed, in the lanes of segment k
+// of the warp (32/K lanes each) after 2 + 1 + 3 shuffles for four values instead of 4 x 5.
+// Across the W = GROUP/32 warps of a group: the first lane of each segment writes the warp's total
+// of its value to the header scratch ([group][phase][K][W], double-buffered by `phase` so one named
+// barrier per reduction is enough); after the barrier every warp reads the K*W partials one (or,
+// for K*W = 64, two) per lane and finishes with a log2(W)-level butterfly inside W-lane segments —
+// one shared-memory load and at most four shuffles per thread instead of W loads and W adds.
 template <int GROUP, int K, typename Op>
 __device__ __forceinline__ void group_reduce(float (&v)[K], float* red, int group, int tg, int& phase, Op op) {
-  static_assert(K == 1 || K == 2, "one or two values");
+  static_assert(K == 1 || K == 2 || K == 4, "one, two or four values");
+  constexpr unsigned kFull = 0xffffffffu;
   const int lane = tg & 31;
   float x;
   if constexpr (K == 1) {
     x = warp_reduce(v[0], op);
-  } else {
+  } else if constexpr (K == 2) {
     const bool hi = (lane & 16) != 0;
     const float keep = hi ? v[1] : v[0];
     const float send = hi ? v[0] : v[1];
-    x = op(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+    x = op(keep, __shfl_xor_sync(kFull, send, 16));
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) x = op(x, __shfl_xor_sync(0xffffffffu, x, o));
+    for (int o = 8; o > 0; o >>= 1) x = op(x, __shfl_xor_sync(kFull, x, o));
+  } else {
+    const bool hi = (lane & 16) != 0, hi8 = (lane & 8) != 0;
+    const float a0 = op(hi ? v[2] : v[0], __shfl_xor_sync(kFull, hi ? v[0] : v[2], 16));
+    const float a1 = op(hi ? v[3] : v[1], __shfl_xor_sync(kFull, hi ? v[1] : v[3], 16));
+    x = op(hi8 ? a1 : a0, __shfl_xor_sync(kFull, hi8 ? a0 : a1, 8));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) x = op(x, __shfl_xor_sync(kFull, x, o));
   }
+  constexpr int SEG = 32 / K;  // value k sits in lanes [k*SEG, (k+1)*SEG) of every warp
   if constexpr (GROUP == 32) {
-    v[0] = __shfl_sync(0xffffffffu, x, 0);
-    if constexpr (K == 2) v[1] = __shfl_sync(0xffffffffu, x, 16);
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = __shfl_sync(kFull, x, k * SEG);
   } else {
     constexpr int W = GROUP / 32;
-    static_assert(W * K <= 32, "partials of one reduction fit a warp");
-    static_assert((kRingThreads / 32) * 2 * 2 <= kRingRedFloats, "scratch too small");
-    float* buf = red + (group * 2 + phase) * (2 * W);
+    static_assert((kRingThreads / 32) * 2 * 4 <= kRingRedFloats, "scratch too small");
+    float* buf = red + (group * 2 + phase) * (4 * W);  // fixed stride: reductions of different K may alternate
     phase ^= 1;
-    if ((lane & 15) == 0 && (K == 2 || lane == 0)) buf[(lane >> 4) * W + (tg >> 5)] = x;
+    if ((lane & (SEG - 1)) == 0) buf[(lane / SEG) * W + (tg >> 5)] = x;
     named_bar_sync(1 + group, GROUP);
-    float y = buf[lane < W * K ? lane : 0];
+    if constexpr (W * K <= 32) {
+      float y = buf[lane < W * K ? lane : 0];
 #pragma unroll
-    for (int o = W / 2; o > 0; o >>= 1) y = op(y, __shfl_xor_sync(0xffffffffu, y, o));
-    v[0] = __shfl_sync(0xffffffffu, y, 0);
-    if constexpr (K == 2) v[1] = __shfl_sync(0xffffffffu, y, W);
+      for (int o = W / 2; o > 0; o >>= 1) y = op(y, __shfl_xor_sync(kFull, y, o));
+#pragma unroll
+      for (int k = 0; k < K; ++k) v[k] = __shfl_sync(kFull, y, k * W);
+    } else {
+      // 64 partials (four values x 16 warps): lane l holds (value l/16, warp l%16) and
+      // (value 2 + l/16, warp l%16); the first exchange folds the two into one
+      static_assert(W == 16 && K == 4, "two partials per lane");
+      const float y0 = buf[lane], y1 = buf[lane + 32];
+      const bool hi8 = (lane & 8) != 0;
+      float y = op(hi8 ? y1 : y0, __shfl_xor_sync(kFull, hi8 ? y0 : y1, 8));
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) y = op(y, __shfl_xor_sync(kFull, y, o));
+      v[0] = __shfl_sync(kFull, y, 0);
+      v[1] = __shfl_sync(kFull, y, 16);
+      v[2] = __shfl_sync(kFull, y, 8);
+      v[3] = __shfl_sync(kFull, y, 24);
+    }
   }
 }
 
