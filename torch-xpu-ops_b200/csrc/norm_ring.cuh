@@ -49,6 +49,8 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 
   RingGeom g;
   g.init(M, N, sizeof(T), NG * RPG, S_lag, 1, trace_buf, trace_cap);
+  unsigned tk = 0;  // trace record counter (diagnostic)
+  if (threadIdx.x == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 8, 0);  // kernel entry
   ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
   if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
@@ -75,7 +77,6 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 
   RingCursor cur;
   cur.start(g);
-  unsigned tk = 0;  // trace record counter (diagnostic)
   int64_t i = 0;
   for (; i < g.my_tiles; ++i, cur.advance(g)) {
     if (tid == kTraceTid) g.trace.put(0, tk, EV_C_WAIT_BEGIN, i);
