@@ -282,16 +282,23 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
 
   RingCursor cur;
   cur.start(g);
+  // mean/rstd of the group's first two rows of a tile are fetched one whole tile ahead: a global
+  // load issued where the value is needed would add its full latency to every row (rows 2 and 3 of
+  // a four-row tile — short rows, several groups per CTA to hide it — load theirs in place)
+  // lane b (b < 2) of every warp holds the statistics of row b: two registers per tile instead of four
+  float mu_c = 0.0f, rs_c = 0.0f;
+  auto load_stats = [&](int64_t row0, float& mu, float& rsd) {
+    const int b = threadIdx.x & 31;
+    const bool ok = b < 2 && b < RPG && row0 + b < M;
+    mu = (!RMS && ok) ? __ldg(mean + row0 + b) : 0.0f;
+    rsd = ok ? __ldg(rstd + row0 + b) : 0.0f;
+  };
+  if (g.my_tiles > 0) load_stats(cur.row0 + grp * RPG, mu_c, rs_c);
   int64_t i = 0;
   for (; i < g.my_tiles; ++i, cur.advance(g)) {
-    // statistics of this group's first row in the tile: issued before the wait, so the global-load
-    // latency hides behind it (later rows of a multi-row tile load theirs in place)
     const int64_t row_first = cur.row0 + grp * RPG;
-    float mu_p = 0.0f, rs_p = 0.0f;
-    if (row_first < M) {
-      if (!RMS) mu_p = __ldg(mean + row_first);
-      rs_p = __ldg(rstd + row_first);
-    }
+    float mu_n = 0.0f, rs_n = 0.0f;
+    if (i + 1 < g.my_tiles) load_stats(row_first + g.tile_stride, mu_n, rs_n);
     if (!ring_consumer_wait(rs, cur, status)) break;
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     for (int r = 0; r < RPG; ++r) {
@@ -300,9 +307,12 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       if (row >= M) break;  // uniform over the group
       const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       const uint32_t xbase = dbase + g.slot_bytes;
-      float mu = mu_p, rsd = rs_p;
-      if (r > 0) {
-        if (!RMS) mu = __ldg(mean + row);
+      float mu, rsd;
+      if (r < 2) {
+        mu = __shfl_sync(0xffffffffu, mu_c, r);
+        rsd = __shfl_sync(0xffffffffu, rs_c, r);
+      } else {
+        mu = RMS ? 0.0f : __ldg(mean + row);
         rsd = __ldg(rstd + row);
       }
       const float2 nmu = bcast2(-mu), rs2 = bcast2(rsd);
@@ -360,6 +370,8 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       }
     }
     ring_consumer_release(rs, cur);
+    mu_c = mu_n;
+    rs_c = rs_n;
   }
 
   if (WGRAD) {
