@@ -7,7 +7,8 @@ One "step" is one pass of the workload's operators over one batch of seeded synt
 default workload is BASELINE config 4: native_layer_norm forward + backward (dx, dgamma, dbeta) on
 bf16 [65536, 8192] with fp32 gamma/beta, rows sharded evenly over the N ranks (strong scaling), the
 fused fp32 [2, 8192] dgamma|dbeta buffer all-reduced over NCCL each step.  Other workloads
-(--workload cfg1|cfg2|cfg3|cfg5) run the other BASELINE configs the same way.
+(--workload cfg1|cfg2|cfg3|cfg5) run the other BASELINE configs the same way; cfg5f is config 5 with the fused
+cross-entropy backward.
 
 Prints ONE JSON line (rank 0).  `value` is algorithmic bytes (every tensor of the operators'
 signatures read or written once) of all ranks / device time, inputs resident in HBM; `e2e` is the

@@ -266,4 +266,44 @@ class Cfg5CrossEntropy(_Simple):
         return rows * self.V * 2 + 2
 
 
-EXTRA = {"cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg5": Cfg5CrossEntropy}
+class Cfg5FusedTail(Cfg5CrossEntropy):
+    """Config 5 with the two backward operators replaced by the fused kernel (b2n_cross_entropy_bwd): the same
+    inputs and the same dlogits, without the dense gradient of the log-probabilities.  Not a BASELINE config:
+    its bytes are those the fused formulation needs (log-softmax 2 passes + backward 2 passes over the logits)."""
+    name = "cfg5f"
+    launches_per_step = 4
+
+    def describe(self):
+        return ("_log_softmax + nll_loss_forward(mean) + fused cross-entropy backward (nll_loss_backward and "
+                "_log_softmax_backward_data in one pass), bf16 logits [16384, 128256] ~N(0,2), int64 targets")
+
+    def bytes_per_rows(self, rows):
+        v = self.V
+        fwd, bwd = 2 * rows * v * 2, 2 * rows * v * 2
+        return {"total": fwd + bwd + rows * 40, "log_softmax_fwd_twopass": fwd, "log_softmax_fwd_generic": fwd,
+                "cross_entropy_bwd_ring": bwd, "cross_entropy_bwd_generic": bwd}
+
+    def make_device_state(self, rows, dev, seed):
+        st = super().make_device_state(rows, dev, seed)
+        del st["grad_logp"]
+        return st
+
+    def step(self, capi, st, world):
+        logp = capi._log_softmax(st["logits"], -1, False, out=st["logp"])
+        _, _, sums = capi.nll_loss_forward(logp, st["target"], None, 2, -100, return_sums=True)
+        if world > 1:
+            dist.all_reduce(sums)
+        st["loss"] = sums[0] / sums[1]
+        tw = sums[1].to(torch.bfloat16)
+        capi.cross_entropy_backward(st["one"], logp, st["target"], None, 1, -100, tw, out=st["dlogits"])
+
+    def aten_step(self, st, world):
+        from b200norm import capi
+        x = st["logits"].detach().requires_grad_(True)
+        loss = capi.cross_entropy(x, st["target"])
+        loss.backward()
+        return loss.detach(), x.grad
+
+
+EXTRA = {"cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg5": Cfg5CrossEntropy,
+         "cfg5f": Cfg5FusedTail}

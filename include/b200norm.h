@@ -191,6 +191,24 @@ int b2n_nll_loss_bwd(const void* grad_out, const void* target, const void* weigh
                      int reduction, int64_t ignore_index, int dtype, int target_is_u8,
                      void* stream);
 
+/* ---- fused cross-entropy tail -------------------------------------------------------------------
+ * b2n_nll_loss_bwd followed by b2n_softmax_bwd(is_log = 1) in one pass, without the dense [M, C]
+ * gradient between them:
+ *   dx[i, j] = s_i * (exp(logp[i, j]) - [j == target_i]),
+ *   s_i = w[t_i] * g (/ total_weight for mean), g = grad_out[i] (none) or grad_out[0];
+ * rows whose target is ignore_index are zero.  logp is the output of b2n_softmax_fwd(is_log = 1);
+ * dx may alias logp.  One read and one write per element instead of the pair's write + two reads +
+ * write.  Out-of-range targets are treated like b2n_nll_loss_fwd treats them.
+ *
+ * The reference has no single entry point for this: it is the composition its callers reach
+ * through autograd, nll_loss_backward_out_xpu (src/ATen/native/xpu/LossNLL.cpp:35-56, kernel
+ * sycl/LossNLLKernel.cpp:325-380) then log_softmax_backward_xpu_out (SoftMax.cpp:61-92); results
+ * equal that composition evaluated in fp32. */
+int b2n_cross_entropy_bwd(const void* logp, const void* target, const void* weight,
+                          const void* grad_out, const void* total_weight, void* dx, int64_t M,
+                          int64_t C, int reduction, int64_t ignore_index, int dtype,
+                          int target_is_u8, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

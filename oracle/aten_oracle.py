@@ -204,3 +204,14 @@ def nll_fwd(logp, target, weight, reduction: int, ignore_index: int, exact: bool
 def nll_bwd(grad_out, logp, target, weight, reduction: int, ignore_index: int, total_weight):
     return aten.nll_loss_backward(_cpu(grad_out), _cpu(logp), _cpu(target), _cpu(weight), reduction, ignore_index,
                                   _cpu(total_weight))
+
+
+def cross_entropy_bwd(grad_out, logp, target, weight, reduction: int, ignore_index: int, total_weight):
+    """nll_loss_backward followed by _log_softmax_backward_data(dim=-1), both on fp32 upcasts (fp64 stays
+    fp64), rounded once to logp's dtype: the composition a fused cross-entropy backward must equal."""
+    wide = torch.float64 if logp.dtype == torch.float64 else torch.float32
+    up = lambda t: None if t is None else t.detach().cpu().to(wide)
+    y = up(logp)
+    grad = aten.nll_loss_backward(up(grad_out), y, _cpu(target), up(weight), reduction, ignore_index,
+                                  up(total_weight))
+    return aten._log_softmax_backward_data(grad, y, -1, wide).to(logp.dtype)

@@ -381,3 +381,57 @@ def nll_loss_backward(grad_output, self, target, weight=None, reduction=REDUCE_M
                                     int(ignore_index), _dt(self.dtype), int(t.dtype == torch.uint8), _stream(self)),
                "b2n_nll_loss_bwd")
     return grad_input
+
+
+# ---- fused cross-entropy tail ----------------------------------------------------------------------------
+def cross_entropy_backward(grad_output, log_probs, target, weight=None, reduction=REDUCE_MEAN, ignore_index=-100,
+                           total_weight=None, out=None):
+    """nll_loss_backward followed by _log_softmax_backward_data(dim=-1) as one kernel:
+    grad_input[i, j] = s_i * (exp(log_probs[i, j]) - [j == target_i]).  `out` may be `log_probs` itself."""
+    _require_cuda(grad_output, log_probs, target, weight, total_weight)
+    lib = load_library()
+    _nll_check(log_probs, target, weight)
+    C = log_probs.shape[-1]
+    M = 1 if log_probs.dim() == 1 else log_probs.shape[0]
+    y = log_probs.contiguous()
+    g = grad_output.to(y.dtype).contiguous()
+    t = target.contiguous()
+    w = weight.to(y.dtype).contiguous() if weight is not None else None
+    tw = total_weight.to(y.dtype).contiguous() if total_weight is not None else None
+    red = int(reduction)
+    if log_probs.dim() == 1 and red == REDUCE_NONE:
+        red = REDUCE_SUM  # a single row: the scalar grad_output applies as is
+    dx = out if out is not None else torch.empty_like(y)
+    with torch.cuda.device(y.device):
+        _check(lib.b2n_cross_entropy_bwd(_ptr(y), _ptr(t), _ptr(w), _ptr(g), _ptr(tw), _ptr(dx), M, C, red,
+                                         int(ignore_index), _dt(y.dtype), int(t.dtype == torch.uint8), _stream(y)),
+               "b2n_cross_entropy_bwd")
+    return dx
+
+
+class _CrossEntropy(torch.autograd.Function):
+    """log_softmax + nll_loss forward on the library's kernels; the fused kernel backward."""
+
+    @staticmethod
+    def forward(ctx, logits, target, weight, reduction, ignore_index):
+        logp = _log_softmax(logits, -1, False)
+        loss, total_weight = nll_loss_forward(logp, target, weight, reduction, ignore_index)
+        ctx.save_for_backward(logp, target, weight if weight is not None else logp.new_empty(0), total_weight)
+        ctx.has_weight = weight is not None
+        ctx.reduction = reduction
+        ctx.ignore_index = ignore_index
+        return loss
+
+    @staticmethod
+    def backward(ctx, grad_loss):
+        logp, target, weight, total_weight = ctx.saved_tensors
+        dx = cross_entropy_backward(grad_loss, logp, target, weight if ctx.has_weight else None, ctx.reduction,
+                                    ctx.ignore_index, total_weight)
+        return dx, None, None, None, None
+
+
+def cross_entropy(logits, target, weight=None, reduction="mean", ignore_index=-100):
+    """torch.nn.functional.cross_entropy for class-index targets over the last dim of a 1-D or 2-D input
+    (no label smoothing), with the backward fused into one pass over the log-probabilities."""
+    red = {"none": REDUCE_NONE, "mean": REDUCE_MEAN, "sum": REDUCE_SUM}[reduction]
+    return _CrossEntropy.apply(logits, target, weight, red, ignore_index)

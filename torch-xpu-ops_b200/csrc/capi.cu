@@ -278,4 +278,16 @@ int b2n_nll_loss_bwd(const void* grad_out, const void* target, const void* weigh
                              dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
 }
 
+int b2n_cross_entropy_bwd(const void* logp, const void* target, const void* weight, const void* grad_out,
+                          const void* total_weight, void* dx, int64_t M, int64_t C, int reduction,
+                          int64_t ignore_index, int dtype, int target_is_u8, void* stream) {
+  if (M < 0 || C < 0 || !valid_dtype(dtype) || reduction < B2N_REDUCE_NONE || reduction > B2N_REDUCE_SUM)
+    return B2N_ERR_BAD_ARG;
+  if (M == 0 || C == 0) return B2N_OK;
+  if (!logp || !grad_out || !target || !dx) return B2N_ERR_BAD_ARG;
+  if (reduction == B2N_REDUCE_MEAN && !total_weight) return B2N_ERR_BAD_ARG;
+  return launch_cross_entropy_bwd(logp, target, weight, grad_out, total_weight, dx, M, C, reduction, ignore_index,
+                                  dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"
