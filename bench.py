@@ -102,10 +102,13 @@ class Cfg4LayerNorm(Workload):
         capi.native_layer_norm(st["x"], [n], st["gamma"], st["beta"], 1e-5, out=(st["y"], st["mean"], st["rstd"]))
         capi.native_layer_norm_backward(st["dy"], st["x"], [n], st["mean"], st["rstd"], st["gamma"], st["beta"],
                                         (True, True, True), out=(st["dx"], wg[0], wg[1]), workspace=st["ws"])
-        if world > 1:
+        if world > 1 and COLLECTIVE_MODE != "none":
             # one all-reduce(SUM) of the fused [dgamma | dbeta] buffer the fold kernel just wrote; asynchronous,
             # so it overlaps the next step's forward (nothing reads the reduced gradients inside the step)
-            st["works"][k] = dist.all_reduce(wg, async_op=True)
+            if COLLECTIVE_MODE == "async":
+                st["works"][k] = dist.all_reduce(wg, async_op=True)
+            else:
+                dist.all_reduce(wg)
 
     def finish(self, st):
         for w in st["works"]:
@@ -197,6 +200,7 @@ class Cfg4LayerNorm(Workload):
         return 2 * rows * n * 2, 2 * rows * n * 2 + 2 * n * 4
 
 
+COLLECTIVE_MODE = "async"  # --collective: async (default) | sync | none (diagnostic: no gradient exchange)
 WORKLOADS = {"cfg4": Cfg4LayerNorm}
 
 
@@ -343,12 +347,18 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg4")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"])
+    ap.add_argument("--collective", default="async", choices=["async", "sync", "none"],
+                    help="cfg4 gradient all-reduce: overlapped with the next step, in-stream, or (diagnostic) skipped")
+    ap.add_argument("--sm-margin", type=int, default=-1,
+                    help="SMs the persistent kernels leave free for a collective kernel running beside them (default 0)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--rows", type=int, default=0, help="override the workload's global row count (small cases for ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    global COLLECTIVE_MODE
+    COLLECTIVE_MODE = args.collective
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -372,6 +382,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     import b200norm
     from b200norm import capi, shard
+    sm_margin = max(args.sm_margin, 0)
+    capi.set_tuning(b200norm.TUNE_SM_MARGIN, sm_margin)
 
     b200norm.load_library()
     if args.scaling == "strong":
@@ -479,8 +491,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16 storage, f32 accumulate", "data": "synthetic",
             "config": {"workload": f"{wl.name}: {wl.describe()}", "global_rows": global_rows, "rows_per_gpu": rows,
-                       "parallelism": f"row-sharded dp{world}", "l2": "inputs larger than L2 (no flush needed)",
-                       "collective": getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, overlapped with the next step") if world > 1 else "none"},
+                       "sm_margin": sm_margin, "parallelism": f"row-sharded dp{world}", "l2": "inputs larger than L2 (no flush needed)",
+                       "collective": (getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, " + {"async": "overlapped with the next step", "sync": "in stream", "none": "SKIPPED (diagnostic run)"}[COLLECTIVE_MODE]) if world > 1 else "none")},
             "pct_of_peak_measured": round(100 * value / world / peak, 2),
             "pct_of_peak_nominal": round(100 * value / world / NOMINAL_HBM_GBS, 2),
             "rows_per_s": round(global_rows * args.steps / (ms * 1e-3), 1),

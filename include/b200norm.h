@@ -62,13 +62,16 @@ int b2n_last_cuda_error(void);
  * value.  A forced family that cannot take a given shape makes the call return
  * B2N_ERR_BAD_ARG instead of silently using another one. */
 int b2n_set_path(int path);
-/* Tuning aid for sweeps: override one launch parameter of the ring kernels for this thread
- * (0 restores the automatic choice).  Values that do not fit a shape are clamped. */
+/* Launch parameters of the ring kernels, per calling thread (0 restores the automatic choice).
+ * Values that do not fit a shape are clamped.  Knobs 0-3 are tuning aids for sweeps; the SM margin
+ * is for production use. */
 typedef enum b2n_tuning_knob {
   B2N_TUNE_ROWS_PER_GROUP = 0, /* rows of a tile each row group works through (1..4) */
   B2N_TUNE_STAGES = 1,         /* upper bound on the ring depth */
   B2N_TUNE_STORE_LAG = 2,      /* bulk stores left in flight before a stage is refilled (1..3) */
-  B2N_TUNE_CLUSTER_SIZE = 3    /* CTAs per row in the cluster kernels (2, 4 or 8) */
+  B2N_TUNE_CLUSTER_SIZE = 3,   /* CTAs per row in the cluster kernels (2, 4 or 8) */
+  B2N_TUNE_SM_MARGIN = 4       /* SMs the persistent kernels leave free, e.g. for the kernel of a collective that
+                                  runs beside them on another stream (it cannot share an SM with a ring CTA) */
 } b2n_tuning_knob;
 int b2n_set_tuning(int knob, int value);
 /* Diagnostic: while a buffer is set (this thread), CTA 0 of the layer-norm / RMS-norm forward ring

@@ -1,4 +1,5 @@
 // The C ABI declared in include/b200norm.h: argument validation, then the typed launchers.
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -12,6 +13,12 @@ namespace b2n {
 namespace {
 constexpr int kMaxDevices = 64;
 __device__ int g_status_word = 0;  // one per device (each device that loads the module has its own)
+// Tile-counter slots of the ring kernels: {next tile, CTAs finished} pairs, all zero between
+// launches (the last CTA of a launch zeroes its pair).  Launches take slots in rotation, so two
+// launches share a pair only if kTileCounterSlots launches were in flight at once.
+constexpr unsigned kTileCounterSlots = 4096;
+__device__ unsigned g_tile_counters[2 * kTileCounterSlots];
+std::atomic<unsigned> g_next_counter_slot{0};
 
 thread_local int tl_last_cuda_error = 0;
 thread_local int tl_forced_path = B2N_PATH_AUTO;
@@ -27,6 +34,7 @@ struct PerDevice {
   std::once_flag once;
   DeviceInfo info{};
   int* status_ptr = nullptr;
+  unsigned* counters = nullptr;
 };
 PerDevice g_devices[kMaxDevices];
 
@@ -39,6 +47,7 @@ PerDevice& current_device() {
     cudaDeviceGetAttribute(&pd.info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_status_word) == cudaSuccess) pd.status_ptr = static_cast<int*>(p);
+    if (cudaGetSymbolAddress(&p, g_tile_counters) == cudaSuccess) pd.counters = static_cast<unsigned*>(p);
   });
   return pd;
 }
@@ -46,6 +55,11 @@ PerDevice& current_device() {
 
 const DeviceInfo& device_info() { return current_device().info; }
 int* device_status_ptr() { return current_device().status_ptr; }
+unsigned* next_tile_counter() {
+  unsigned* base = current_device().counters;
+  if (base == nullptr) return nullptr;
+  return base + 2 * (g_next_counter_slot.fetch_add(1, std::memory_order_relaxed) % kTileCounterSlots);
+}
 int check_cuda(cudaError_t e) {
   if (e == cudaSuccess) return B2N_OK;
   tl_last_cuda_error = static_cast<int>(e);
@@ -131,6 +145,7 @@ int b2n_set_tuning(int knob, int value) {
     case B2N_TUNE_STAGES: t.stages = value; return B2N_OK;
     case B2N_TUNE_STORE_LAG: t.lag = value; return B2N_OK;
     case B2N_TUNE_CLUSTER_SIZE: t.cluster = value; return B2N_OK;
+    case B2N_TUNE_SM_MARGIN: t.sm_margin = value; return B2N_OK;
     default: return B2N_ERR_BAD_ARG;
   }
 }

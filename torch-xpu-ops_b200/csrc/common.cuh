@@ -116,6 +116,16 @@ template <int TPR, typename A, typename Op> __device__ __forceinline__ A row_red
 // (one int per device, passed to the kernels as an argument: see device_status_ptr below)
 __device__ __forceinline__ void record_status(int* status, int code) { atomicCAS(status, 0, code); }
 
+// Programmatic dependent launch (sm_90+).  A kernel launched with launch_pdl() below may become
+// resident while the kernel before it in the stream is still running: pdl_wait() holds it until
+// that kernel has completed and its writes are visible, so everything before the call (barrier
+// setup, register reallocation) overlaps the predecessor's tail and the launch latency disappears.
+// No global memory may be touched before pdl_wait().  pdl_launch_dependents() tells the scheduler
+// that the NEXT kernel in the stream may be made resident as soon as SMs free up.  Both are no-ops
+// in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
 // ---------------------------------------------------------------------------------------------
 // sm_100a PTX: mbarrier + bulk-async (TMA) copies between global and shared memory.
 // No cluster multicast is used anywhere.
@@ -316,7 +326,27 @@ int check_cuda(cudaError_t e);            // records e for b2n_last_cuda_error; 
 int forced_path();                        // b2n_set_path value of this thread
 void note_path(const char* name);         // records the family used by the last launch
 int* device_status_ptr();                 // device address of the status word of the current device
+unsigned* next_tile_counter();            // a zeroed {next tile, CTAs finished} pair for one ring-kernel launch
 int launched();                           // counts one kernel launch; returns check_cuda(cudaGetLastError())
+
+// Launch with the programmatic-stream-serialization attribute (see pdl_wait above).  The kernel
+// must call pdl_wait() before its first global-memory access.
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return check_cuda(e);
+  return launched();
+}
 
 // Brackets one main-kernel launch with a pair of CUDA events on its stream while this thread has
 // profiling switched on (b2n_profile_begin); otherwise does nothing.

@@ -255,11 +255,11 @@ int ce_bwd_typed(const void* logp_, const void* target, const void* weight_, con
       if (stages >= 3) {
         note_path("ring");
         const size_t smem = static_cast<size_t>(kRingHeaderBytes + stages * stage);
-        const int grid = static_cast<int>(M < di.sm_count ? M : di.sm_count);
+        const int ctas = persistent_ctas(di.sm_count);
+        const int grid = static_cast<int>(M < ctas ? M : ctas);
         ProfileScope prof("cross_entropy_bwd_ring", st);
-        kernel<<<grid, kRingBlock, smem, st>>>(logp, target, weight, grad_out, total_weight, dx, M, N, reduction,
-                                               ignore_index, static_cast<int>(stages), device_status_ptr());
-        return launched();
+        return launch_pdl(kernel, dim3(grid), dim3(kRingBlock), smem, st, logp, target, weight, grad_out, total_weight,
+                          dx, M, N, reduction, ignore_index, static_cast<int>(stages), device_status_ptr());
       }
     }
   }

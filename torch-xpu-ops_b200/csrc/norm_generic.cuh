@@ -181,6 +181,8 @@ template <typename A, typename WT>
 __global__ void norm_bwd_wgrad_fold_kernel(const A* __restrict__ ws, WT* __restrict__ dgamma,
                                            WT* __restrict__ dbeta, int64_t P, int64_t N) {
   __shared__ A sm[8][33];
+  pdl_launch_dependents();  // see common.cuh: no-ops unless launched with launch_pdl
+  pdl_wait();
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int plane = blockIdx.y;
   WT* out = plane == 0 ? dgamma : dbeta;

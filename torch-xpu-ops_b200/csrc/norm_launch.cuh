@@ -52,10 +52,9 @@ int norm_fwd_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const W
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once(kernel, p.smem, mask)) return e;
   ProfileScope prof(RMS ? "rms_norm_fwd_ring" : "layer_norm_fwd_ring", st);
-  kernel<<<p.grid, kRingBlock, p.smem, st>>>(x, gamma, beta, y, mean, rstd, M, static_cast<int>(N),
-                                               static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg, device_status_ptr(),
-                                               ring_tuning().trace_buf, ring_tuning().trace_cap);
-  return launched();
+  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, gamma, beta, y, mean, rstd, M,
+                    static_cast<int>(N), static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg, device_status_ptr(),
+                    next_tile_counter(), ring_tuning().trace_buf, ring_tuning().trace_cap);
 }
 
 template <typename T, typename WT, bool RMS>
@@ -74,7 +73,7 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
     if (forced != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
       const DeviceInfo& di = device_info();
       // one tensor per stage: 64 KB tiles (half as many tile hand-overs) still leave three stages in rotation
-      const RingPlan p = plan_ring(M, N, sizeof(T), 1, kNormFwdEpt, di.sm_count, di.max_smem_optin, 65536);
+      const RingPlan p = plan_ring(M, N, sizeof(T), 1, kNormFwdEpt, persistent_ctas(di.sm_count), di.max_smem_optin, 65536);
       if (p.ok) {
         note_path("ring");
         switch (p.group) {
@@ -108,8 +107,10 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
 }
 
 // ---- backward -----------------------------------------------------------------------------------
-template <typename T> RingPlan plan_norm_bwd(int64_t M, int64_t N, const DeviceInfo& di) {
-  return plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, di.sm_count, di.max_smem_optin);
+// full = true plans for every SM whatever margin is set: what the workspace must be large enough for.
+template <typename T> RingPlan plan_norm_bwd(int64_t M, int64_t N, const DeviceInfo& di, bool full = false) {
+  return plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, full ? di.sm_count : persistent_ctas(di.sm_count),
+                   di.max_smem_optin);
 }
 // Number of partial rows ([2][N] accumulate-type values each) the weight-gradient reduction writes.
 inline int64_t wgrad_generic_chunks(int64_t M) {
@@ -120,7 +121,7 @@ template <typename T> int64_t wgrad_partial_rows(int64_t M, int64_t N) {
   int64_t rows = wgrad_generic_chunks(M);
   if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
     const DeviceInfo& di = device_info();
-    const RingPlan p = plan_norm_bwd<T>(M, N, di);
+    const RingPlan p = plan_norm_bwd<T>(M, N, di, true);
     if (p.ok && static_cast<int64_t>(p.grid) * p.ng > rows) rows = static_cast<int64_t>(p.grid) * p.ng;
   }
   return rows;
@@ -139,15 +140,17 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
   if (wgrad) {
     auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true>;
     if (int e = set_smem_once(kernel, p.smem, mask_w)) return e;
-    kernel<<<p.grid, kRingBlock, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
-                                                 p.stages | (p.lag << 8), p.rpg, device_status_ptr());
+    // fixed tile assignment (no counter): the partial sums a CTA forms, and with them dgamma/dbeta, are then
+    // the same bits on every run
+    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, M,
+                      static_cast<int>(N), p.stages | (p.lag << 8), p.rpg, device_status_ptr(),
+                      static_cast<unsigned*>(nullptr));
   } else {
     auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false>;
     if (int e = set_smem_once(kernel, p.smem, mask_n)) return e;
-    kernel<<<p.grid, kRingBlock, p.smem, st>>>(dy, x, mean, rstd, gamma, dx, ws, M, static_cast<int>(N),
-                                                 p.stages | (p.lag << 8), p.rpg, device_status_ptr());
+    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, M,
+                      static_cast<int>(N), p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter());
   }
-  return launched();
 }
 
 template <typename T, typename WT, bool RMS>
@@ -189,9 +192,8 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
           default: e = norm_bwd_ring_launch<T, WT, RMS, 512>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
         }
         if (e != B2N_OK || !wgrad) return e;
-        norm_bwd_wgrad_fold_kernel<float, WT><<<fold_grid, fold_block, 0, st>>>(
-            ws, dgamma, dbeta, static_cast<int64_t>(p.grid) * p.ng, N);
-        return launched();
+        return launch_pdl(norm_bwd_wgrad_fold_kernel<float, WT>, fold_grid, fold_block, 0, st,
+                          static_cast<const float*>(ws), dgamma, dbeta, static_cast<int64_t>(p.grid) * p.ng, N);
       }
     }
   }

@@ -38,8 +38,8 @@ template <typename T, typename WT, bool RMS, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta,
                      T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t M,
-                     int N, float eps, int S_lag, int RPG, int* status, unsigned long long* trace_buf,
-                     unsigned trace_cap) {
+                     int N, float eps, int S_lag, int RPG, int* status, unsigned* tile_ctr,
+                     unsigned long long* trace_buf, unsigned trace_cap) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   constexpr int RB = 2;  // rows a group works on at once
@@ -48,7 +48,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1, trace_buf, trace_cap);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1, tile_ctr, trace_buf, trace_cap);
   unsigned tk = 0;  // trace record counter (diagnostic)
   if (threadIdx.x == kTraceTid) g.trace.put(0, tk, EV_C_STEP + 8, 0);  // kernel entry
   ring_init(rs, g.S, kRingThreads / 32);
@@ -76,11 +76,12 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   const uint32_t stages_u32 = smem_u32(stages);
 
   RingCursor cur;
-  cur.start(g);
-  int64_t i = 0;
-  for (; i < g.my_tiles; ++i, cur.advance(g)) {
-    if (tid == kTraceTid) g.trace.put(0, tk, EV_C_WAIT_BEGIN, i);
-    if (!ring_consumer_wait(rs, cur, status)) break;
+  cur.start();
+  for (;; cur.advance(g)) {
+    if (tid == kTraceTid) g.trace.put(0, tk, EV_C_WAIT_BEGIN, 0);
+    int i;  // the tile in this stage
+    if (!ring_consumer_wait(rs, cur, status, i) || i < 0) break;
+    const int64_t tile_row0 = g.first_row(i);
     if (tid == kTraceTid) g.trace.put(0, tk, EV_C_WAIT_END, i);
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     // A group takes its rows of the tile RB at a time: the partial sums of RB rows go through ONE
@@ -88,7 +89,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
     // waiting on each other when a single group spans the whole CTA.
     for (int r = 0; r < RPG; r += RB) {
       const int lr0 = grp * RPG + r;
-      const int64_t row_a = cur.row0 + lr0;
+      const int64_t row_a = tile_row0 + lr0;
       if (row_a >= M) break;  // uniform over the group
       bool valid[RB];
       uint32_t rbase[RB];
@@ -245,7 +246,8 @@ template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx,
-                     float* __restrict__ ws, int64_t M, int N, int S_lag, int RPG, int* status) {
+                     float* __restrict__ ws, int64_t M, int N, int S_lag, int RPG, int* status,
+                     unsigned* tile_ctr) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -253,7 +255,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S_lag, 2);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 2, tile_ctr);
   ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
   if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
@@ -281,25 +283,36 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   const uint32_t stages_u32 = smem_u32(stages);
 
   RingCursor cur;
-  cur.start(g);
+  cur.start();
   // mean/rstd of the group's first two rows of a tile are fetched one whole tile ahead: a global
   // load issued where the value is needed would add its full latency to every row (rows 2 and 3 of
-  // a four-row tile — short rows, several groups per CTA to hide it — load theirs in place)
+  // a four-row tile — short rows, several groups per CTA to hide it — load theirs in place).
+  // Which tile the next stage holds is read from its tile_id slot before that stage has been
+  // waited for — a hint (the producer has normally written it long before); the id seen after the
+  // wait decides, and a wrong guess reloads in place.
   // lane b (b < 2) of every warp holds the statistics of row b: two registers per tile instead of four
   float mu_c = 0.0f, rs_c = 0.0f;
+  int id_c = -1;  // the tile mu_c / rs_c were loaded for
   auto load_stats = [&](int64_t row0, float& mu, float& rsd) {
     const int b = threadIdx.x & 31;
     const bool ok = b < 2 && b < RPG && row0 + b < M;
     mu = (!RMS && ok) ? __ldg(mean + row0 + b) : 0.0f;
     rsd = ok ? __ldg(rstd + row0 + b) : 0.0f;
   };
-  if (g.my_tiles > 0) load_stats(cur.row0 + grp * RPG, mu_c, rs_c);
-  int64_t i = 0;
-  for (; i < g.my_tiles; ++i, cur.advance(g)) {
-    const int64_t row_first = cur.row0 + grp * RPG;
+  const bool fixed = tile_ctr == nullptr;  // fixed assignment: this CTA's k-th tile is blockIdx.x + k * gridDim.x
+  unsigned k_tile = 0;
+  for (;; cur.advance(g), ++k_tile) {
     float mu_n = 0.0f, rs_n = 0.0f;
-    if (i + 1 < g.my_tiles) load_stats(row_first + g.tile_stride, mu_n, rs_n);
-    if (!ring_consumer_wait(rs, cur, status)) break;
+    int id_n = -1;
+    if (fixed) {  // the next tile is known: fetch its statistics a whole tile ahead
+      const unsigned t = blockIdx.x + (k_tile + 1) * gridDim.x;
+      id_n = t < g.ntiles ? static_cast<int>(t) : -1;
+      if (id_n >= 0) load_stats(g.first_row(id_n) + grp * RPG, mu_n, rs_n);
+    }
+    int i;  // the tile in this stage
+    if (!ring_consumer_wait(rs, cur, status, i) || i < 0) break;
+    const int64_t row_first = g.first_row(i) + grp * RPG;
+    if (i != id_c) load_stats(row_first, mu_c, rs_c);  // first tile, or the hint was stale (uniform over a warp)
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
@@ -368,10 +381,15 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
           sts128(dbase + v * 16, P::pack2(o));
         }
       }
+      if (!fixed && r == 0) {  // by now the producer has normally named the next stage's tile
+        id_n = ring_peek_tile(rs, cur.next_stage(g));
+        if (id_n >= 0) load_stats(g.first_row(id_n) + grp * RPG, mu_n, rs_n);
+      }
     }
     ring_consumer_release(rs, cur);
     mu_c = mu_n;
     rs_c = rs_n;
+    id_c = id_n;
   }
 
   if (WGRAD) {

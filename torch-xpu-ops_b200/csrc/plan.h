@@ -22,10 +22,17 @@ struct RingPlan {
 struct RingTuning {
   int rpg = 0, stages = 0, lag = 0;
   int cluster = 0;  // CTAs per row in the cluster kernels (1, 2, 4 or 8)
+  int sm_margin = 0;  // SMs the persistent kernels leave free (for a collective's kernel running beside them)
   unsigned long long* trace_buf = nullptr;  // device buffer for the event trace (diagnostic), or null
   unsigned trace_cap = 0;                   // records it can hold
 };
 RingTuning& ring_tuning();
+
+// CTAs of a persistent kernel on a device with sm_count SMs: one per SM, less the margin the caller asked for.
+inline int persistent_ctas(int sm_count) {
+  const int n = sm_count - ring_tuning().sm_margin;
+  return n < 1 ? 1 : n;
+}
 
 // N elements of `esize` bytes per row, `nin` tensors staged per tile, `ept` elements per thread.
 // `target`: bytes per tensor per tile to aim for; `default_lag`: see RingPlan::lag; `reserve`: bytes of
@@ -65,6 +72,7 @@ inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int
   if (p.lag > 3) p.lag = 3;
   p.smem = static_cast<size_t>(kRingHeaderBytes + reserve + s * stage);
   const int64_t ntiles = (M + p.ng * p.rpg - 1) / (p.ng * p.rpg);
+  if (ntiles > 0x7fff0000LL) return p;  // tile indices are handed out through a 32-bit counter
   p.grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);
   p.ok = true;
   return p;

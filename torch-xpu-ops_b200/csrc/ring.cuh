@@ -17,11 +17,18 @@
 // for more would wait forever), the warp-specialisation pattern of sm_90+.
 //
 // Stage layout: NIN input tiles back to back (tile k at k * TR * row_bytes); the result overwrites
-// input tile 0.  Tile i of a CTA is global tile blockIdx.x + i * gridDim.x.
+// input tile 0.
 //
-// All per-tile bookkeeping (stage index, barrier phase, first row) is carried incrementally in a
-// RingCursor: with one or two rows per tile, a 64-bit division per tile would cost more
-// instructions than the arithmetic on the row.
+// Tiles are handed out dynamically: the producer thread takes the next tile index from a global
+// counter (one atomicAdd per tile, fetched one tile ahead so its latency never shows) and leaves
+// it in the stage's tile_id slot for the consumers.  A CTA that starts late — because another
+// kernel, say a collective on a second stream, still holds its SM — then simply takes fewer
+// tiles, instead of making the whole launch wait for a fixed share it began late.  The counter
+// lives in a library-owned slot {next tile, CTAs finished}; the last CTA to finish zeroes it.
+// (The norm backward with weight gradients keeps a fixed assignment: see RingProducer::fetch.)
+//
+// Stage index and barrier phase are carried incrementally in a RingCursor; no division in the
+// tile loop.
 #pragma once
 #include "common.cuh"
 
@@ -29,17 +36,18 @@ namespace b2n {
 
 constexpr int kMaxStages = 16;
 constexpr int kRingHeaderBytes = 1024;  // barriers + reduction scratch
-constexpr int kRingRedFloats = 160;     // reduction scratch inside the header
+constexpr int kRingRedFloats = 128;     // reduction scratch inside the header
 constexpr int kRingThreads = 512;       // consumer threads (16 warps)
 constexpr int kRingBlock = 640;         // + one producer warpgroup
-constexpr int kConsumerRegs = 112;      // the CTA keeps its launch allocation (640 x 96): 512 x 112 + 128 x 24 <= 61440
+constexpr int kConsumerRegs = 112;      // the CTA keeps its launch allocation (640 x 96): 512 x 112 + 128 x 32 == 61440
 
-__device__ __forceinline__ void ring_producer_regs() { asm volatile("setmaxnreg.dec.sync.aligned.u32 24;"); }
+__device__ __forceinline__ void ring_producer_regs() { asm volatile("setmaxnreg.dec.sync.aligned.u32 32;"); }
 __device__ __forceinline__ void ring_consumer_regs() { asm volatile("setmaxnreg.inc.sync.aligned.u32 112;"); }
 
 struct RingShared {
   uint64_t full[kMaxStages];  // tile landed in the stage (bulk-copy bytes counted)
   uint64_t done[kMaxStages];  // every warp finished writing the stage's result
+  int tile_id[kMaxStages];    // which tile the stage holds; -1: no tiles are left (written by the producer)
   int pad[4];
   float red[kRingRedFloats];  // per-group reduction scratch, double-buffered
 };
@@ -69,49 +77,49 @@ struct RingTrace {
 struct RingGeom {
   RingTrace trace;
   int64_t M;            // rows
-  int64_t tile_stride;  // rows between consecutive tiles of this CTA = gridDim.x * TR
-  int64_t my_tiles;     // tiles this CTA processes
-  int64_t first_row;    // first row of this CTA's tile 0
+  unsigned* ctr;        // global {next tile, CTAs finished} pair of this launch
+  uint32_t ntiles;      // tiles in the launch
   uint32_t row_bytes;   // bytes per row of one tensor (multiple of 16)
   uint32_t slot_bytes;  // TR * row_bytes: one tensor's share of a stage
   uint32_t stage_bytes;
+  uint32_t last_bytes;  // bytes per tensor of the last tile (fewer rows when TR does not divide M)
   int TR;               // rows per tile
   int S;                // stages
   int lag;              // bulk stores the producer leaves in flight before it refills a stage (1..3)
 
   // S_lag packs the two launch parameters: stages in the low 8 bits, lag above them.
-  __device__ __forceinline__ void init(int64_t M_, int N, int esize, int TR_, int S_lag, int nin,
+  __device__ __forceinline__ void init(int64_t M_, int N, int esize, int TR_, int S_lag, int nin, unsigned* ctr_,
                                        unsigned long long* trace_buf = nullptr, unsigned trace_cap = 0) {
     trace.buf = trace_buf;
     trace.cap = trace_cap;
     M = M_;
+    ctr = ctr_;
     TR = TR_;
     S = S_lag & 0xff;
     lag = S_lag >> 8;
     row_bytes = static_cast<uint32_t>(N) * esize;
     slot_bytes = static_cast<uint32_t>(TR_) * row_bytes;
     stage_bytes = slot_bytes * nin;
-    tile_stride = static_cast<int64_t>(gridDim.x) * TR_;
-    first_row = static_cast<int64_t>(blockIdx.x) * TR_;
-    const int64_t ntiles = (M_ + TR_ - 1) / TR_;
-    my_tiles = ntiles > blockIdx.x ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    ntiles = static_cast<uint32_t>((M_ + TR_ - 1) / TR_);
+    last_bytes = static_cast<uint32_t>(M_ - static_cast<int64_t>(ntiles - 1) * TR_) * row_bytes;
   }
-  __device__ __forceinline__ uint32_t tile_bytes(int64_t row0) const {
-    const int64_t rows = (M - row0 < TR) ? (M - row0) : TR;
-    return static_cast<uint32_t>(rows) * row_bytes;
+  __device__ __forceinline__ int64_t first_row(int tile) const { return static_cast<int64_t>(tile) * TR; }
+  // per tensor: where a tile starts and how many bytes it has
+  __device__ __forceinline__ size_t tile_offset(int tile) const { return static_cast<size_t>(tile) * slot_bytes; }
+  __device__ __forceinline__ uint32_t tile_bytes(int tile) const {
+    return static_cast<uint32_t>(tile) + 1u == ntiles ? last_bytes : slot_bytes;
   }
 };
 
-// Where one tile lives: its stage, the parity of that stage's barriers for this use, its first row.
+// Where the next tile of a CTA lives: its stage and the parity of that stage's barriers for this use.
 struct RingCursor {
-  int64_t row0;
   int s;
   uint32_t phase;
-  __device__ __forceinline__ void start(const RingGeom& g) { row0 = g.first_row; s = 0; phase = 0; }
+  __device__ __forceinline__ void start() { s = 0; phase = 0; }
   __device__ __forceinline__ void advance(const RingGeom& g) {
-    row0 += g.tile_stride;
     if (++s == g.S) { s = 0; phase ^= 1u; }
   }
+  __device__ __forceinline__ int next_stage(const RingGeom& g) const { return s + 1 == g.S ? 0 : s + 1; }
 };
 
 __device__ __forceinline__ void ring_init(RingShared* rs, int S, int warps) {
@@ -120,9 +128,14 @@ __device__ __forceinline__ void ring_init(RingShared* rs, int S, int warps) {
       mbar_init(&rs->full[s], 1);
       mbar_init(&rs->done[s], warps);
     }
+    for (int s = 0; s < kMaxStages; ++s) rs->tile_id[s] = -1;
     mbar_init_fence();
   }
   __syncthreads();
+  // Up to here nothing outside the CTA has been touched.  Let the next kernel of the stream become
+  // resident as SMs free up, and wait for the previous one to finish before the first global access.
+  pdl_launch_dependents();
+  pdl_wait();
 }
 
 // The producer loop, run by ONE thread of the producer warpgroup.
@@ -134,65 +147,108 @@ template <int NIN> struct RingProducer {
   const unsigned char* in[NIN];
   unsigned char* out;
   int* status;
-  int64_t loads_left;  // tiles whose loads have not been issued yet
-  RingCursor next;     // the next tile to load
+  int next_id;     // the tile the next load will fetch, taken from the counter one tile ahead; -1: none left
+  unsigned issued; // tiles whose loads have been issued
+  bool ended;      // the end marker has been placed: nothing more to load
+  RingCursor next; // where the next load goes
+  unsigned fetched;  // tile indices taken so far
+  unsigned retired;  // how many CTAs had finished taking tiles before this one
 
   __device__ __forceinline__ RingProducer(RingShared* rs_, unsigned char* stages_, const RingGeom& g_, int* status_)
-      : rs(rs_), stages(stages_), g(g_), out(nullptr), status(status_), loads_left(g_.my_tiles) {
-    next.start(g_);
+      : rs(rs_), stages(stages_), g(g_), out(nullptr), status(status_), next_id(-1), issued(0), ended(false), fetched(0), retired(0) {
+    next.start();
   }
+  // A CTA's first S tiles are blockIdx.x + k * gridDim.x (no atomic in front of the loads that fill
+  // the ring); tiles from S * gridDim.x on come from the counter.  Without a counter
+  // (g.ctr == nullptr) the fixed pattern continues: the assignment a kernel asks for when what it
+  // accumulates across tiles (the norm backward's weight gradients) must not depend on which CTA
+  // happened to be early.
+  __device__ __forceinline__ int fetch() {
+    unsigned t;
+    if (g.ctr == nullptr || fetched < static_cast<unsigned>(g.S)) t = blockIdx.x + fetched * gridDim.x;
+    else t = static_cast<unsigned>(g.S) * gridDim.x + atomicAdd(g.ctr, 1u);
+    ++fetched;
+    return t < g.ntiles ? static_cast<int>(t) : -1;
+  }
+  // Loads the next tile into the next stage, or — when the tiles have run out — marks that stage
+  // as the end: its `full` barrier completes without a copy and the consumers leave when they
+  // reach it.  The tile_id store is ordered before the barrier operation that follows it.
   __device__ __forceinline__ void issue_next_load() {
-    const uint32_t bytes = g.tile_bytes(next.row0);
-    unsigned char* dst = stages + static_cast<size_t>(next.s) * g.stage_bytes;
-    const size_t goff = static_cast<size_t>(next.row0) * g.row_bytes;
-    mbar_arrive_expect_tx(&rs->full[next.s], bytes * NIN);
+    const int id = next_id;
+    rs->tile_id[next.s] = id;
+    if (id < 0) {
+      mbar_arrive(&rs->full[next.s]);
+      ended = true;
+      // this CTA takes no more tiles: say so now, look at the answer when everything else is done
+      if (g.ctr != nullptr) retired = atomicAdd(g.ctr + 1, 1u);
+    } else {
+      unsigned char* dst = stages + static_cast<size_t>(next.s) * g.stage_bytes;
+      const size_t goff = g.tile_offset(id);
+      const uint32_t bytes = g.tile_bytes(id);
+      mbar_arrive_expect_tx(&rs->full[next.s], bytes * NIN);
 #pragma unroll
-    for (int k = 0; k < NIN; ++k) bulk_g2s(dst + k * g.slot_bytes, in[k] + goff, bytes, &rs->full[next.s]);
+      for (int k = 0; k < NIN; ++k) bulk_g2s(dst + k * g.slot_bytes, in[k] + goff, bytes, &rs->full[next.s]);
+      ++issued;
+      next_id = fetch();
+    }
     next.advance(g);
-    --loads_left;
   }
   // Fill the ring; then, tile by tile: wait until every consumer warp has finished the tile, send
   // it out, and refill the stage of the tile `lag` tiles back, whose store (now the lag-th newest
   // bulk group) has finished reading shared memory — with S stages in rotation that stage is
-  // exactly where the next tile to load belongs.
+  // exactly where the next load belongs.
   __device__ __forceinline__ void run() {
-    for (int k = 0; k < g.S && loads_left > 0; ++k) issue_next_load();
+    next_id = fetch();
+    for (int k = 0; k < g.S && !ended; ++k) issue_next_load();
     RingCursor cur;
-    cur.start(g);
+    cur.start();
     int stores = 0;
-    unsigned tk = 0;
-    int64_t i = 0;
-    for (; i < g.my_tiles; ++i, cur.advance(g)) {
+    unsigned done = 0;
+    for (; done < issued; ++done, cur.advance(g)) {
+      // what the store will need, worked out before the wait (the id is this thread's own earlier store)
+      const int id = rs->tile_id[cur.s];
+      unsigned char* gdst = out + g.tile_offset(id);
+      const unsigned char* ssrc = stages + static_cast<size_t>(cur.s) * g.stage_bytes;
+      const uint32_t bytes = g.tile_bytes(id);
       if (!mbar_wait(&rs->done[cur.s], cur.phase, status)) break;
-      g.trace.put(1, tk, EV_P_DONE_SEEN, i);
-      bulk_s2g(out + static_cast<size_t>(cur.row0) * g.row_bytes,
-               stages + static_cast<size_t>(cur.s) * g.stage_bytes, g.tile_bytes(cur.row0));
+      bulk_s2g(gdst, ssrc, bytes);
       bulk_commit();
-      g.trace.put(1, tk, EV_P_STORE_ISSUED, i);
       if (stores < 4) ++stores;
-      if (stores > g.lag && loads_left > 0) {
+      if (stores > g.lag && !ended) {
         if (g.lag == 1) bulk_wait_read<1>();
         else if (g.lag == 2) bulk_wait_read<2>();
         else bulk_wait_read<3>();
-        g.trace.put(1, tk, EV_P_READ_WAITED, i);
         issue_next_load();
-        g.trace.put(1, tk, EV_P_LOAD_ISSUED, i);
       }
     }
     // Nothing of this CTA may still be in flight when its shared memory goes away: if a wait gave
     // up, let the loads that were issued but never consumed land first.
-    const int64_t issued = g.my_tiles - loads_left;
-    for (int64_t j = i; j < issued; ++j) {
+    for (unsigned j = done; j < issued; ++j) {
       mbar_wait(&rs->full[cur.s], cur.phase, status);
       cur.advance(g);
     }
     bulk_wait_all<0>();
+    // The last CTA to finish taking tiles zeroes the counter pair for the slot's next launch (every
+    // CTA's last fetch completed before it said so: its result is what ended the CTA's loads).
+    if (g.ctr != nullptr && !ended) retired = atomicAdd(g.ctr + 1, 1u);  // a wait gave up before the end marker
+    if (g.ctr != nullptr && retired == gridDim.x - 1) {
+      g.ctr[0] = 0;
+      g.ctr[1] = 0;
+    }
   }
 };
 
-// Consumer side of one tile: wait for it, and (after the caller's arithmetic) hand it back.
-__device__ __forceinline__ bool ring_consumer_wait(RingShared* rs, const RingCursor& cur, int* status) {
-  return mbar_wait(&rs->full[cur.s], cur.phase, status);
+// Consumer side of one tile: wait for the stage, learn which tile it holds (tile < 0: none left;
+// false: the wait gave up), and — after the caller's arithmetic — hand it back.
+__device__ __forceinline__ bool ring_consumer_wait(RingShared* rs, const RingCursor& cur, int* status, int& tile) {
+  if (!mbar_wait(&rs->full[cur.s], cur.phase, status)) return false;
+  tile = rs->tile_id[cur.s];
+  return true;
+}
+// The tile id the producer has left — or is yet to leave — in a stage the consumers have not waited
+// for: a hint to prefetch by, to be checked against the real id after the wait.
+__device__ __forceinline__ int ring_peek_tile(RingShared* rs, int stage) {
+  return *reinterpret_cast<volatile int*>(&rs->tile_id[stage]);
 }
 __device__ __forceinline__ void ring_consumer_release(RingShared* rs, const RingCursor& cur) {
   fence_async_smem();

@@ -40,8 +40,8 @@ int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int6
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
   ProfileScope prof(LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring", st);
-  kernel<<<p.grid, kRingBlock, p.smem, st>>>(x, y, M, static_cast<int>(N), p.stages | (p.lag << 8), p.rpg, device_status_ptr());
-  return launched();
+  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
+                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter());
 }
 
 template <typename T, bool LOG, int GROUP>
@@ -52,9 +52,8 @@ int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, i
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
   ProfileScope prof(LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring", st);
-  kernel<<<p.grid, kRingBlock, p.smem, st>>>(dy, y, dx, M, static_cast<int>(N), p.stages | (p.lag << 8), p.rpg,
-                                               device_status_ptr());
-  return launched();
+  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, y, dx, M, static_cast<int>(N),
+                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter());
 }
 
 // Rows too long for the ring: a row is split over a cluster of C CTAs (C = 1, 2, 4 or 8, one CTA per
@@ -131,11 +130,12 @@ int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_
   if (tuned > 0 && tuned < stages) stages = tuned;
   if (stages < 3) return B2N_ERR_BAD_ARG;
   const size_t smem = static_cast<size_t>(kRingHeaderBytes + stages * stage);
-  const int grid = static_cast<int>(M < di.sm_count ? M : di.sm_count);
+  const int ctas = persistent_ctas(di.sm_count);
+  const int grid = static_cast<int>(M < ctas ? M : ctas);
   ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_twopass" : "softmax_bwd_twopass")
                         : (LOG ? "log_softmax_fwd_twopass" : "softmax_fwd_twopass"), st);
-  kernel<<<grid, kRingBlock, smem, st>>>(in0, in1, out, M, N, static_cast<int>(stages), device_status_ptr());
-  return launched();
+  return launch_pdl(kernel, dim3(grid), dim3(kRingBlock), smem, st, in0, in1, out, M, N, static_cast<int>(stages),
+                    device_status_ptr());
 }
 
 template <typename TI, typename TO, bool LOG>
@@ -148,7 +148,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
     if constexpr (std::is_same<TI, TO>::value && sizeof(TI) <= 4 && !std::is_same<TI, double>::value) {
       if (forced != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
         const DeviceInfo& di = device_info();
-        const RingPlan p = plan_ring(M, N, sizeof(TI), 1, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
+        const RingPlan p = plan_ring(M, N, sizeof(TI), 1, kSoftmaxEpt, persistent_ctas(di.sm_count), di.max_smem_optin);
         if (p.ok && forced != B2N_PATH_CLUSTER && forced != B2N_PATH_TWOPASS) {
           note_path("ring");
           switch (p.group) {
@@ -208,7 +208,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
       if (forced != B2N_PATH_GENERIC && is_aligned(dy, 16) && is_aligned(y, 16) && is_aligned(dx, 16) &&
           N <= (1 << 20)) {
         const DeviceInfo& di = device_info();
-        const RingPlan p = plan_ring(M, N, sizeof(TG), 2, kSoftmaxEpt, di.sm_count, di.max_smem_optin);
+        const RingPlan p = plan_ring(M, N, sizeof(TG), 2, kSoftmaxEpt, persistent_ctas(di.sm_count), di.max_smem_optin);
         if (p.ok && forced != B2N_PATH_CLUSTER && forced != B2N_PATH_TWOPASS) {
           note_path("ring");
           switch (p.group) {

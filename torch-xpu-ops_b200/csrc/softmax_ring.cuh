@@ -28,7 +28,7 @@ template <typename T> struct RowExp {
 template <typename T, bool LOG, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S_lag, int RPG,
-                        int* status) {
+                        int* status, unsigned* tile_ctr) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -36,7 +36,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 1, tile_ctr);
   ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
   if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
@@ -58,14 +58,15 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
   const uint32_t stages_u32 = smem_u32(stages);
 
   RingCursor cur;
-  cur.start(g);
-  int64_t i = 0;
-  for (; i < g.my_tiles; ++i, cur.advance(g)) {
-    if (!ring_consumer_wait(rs, cur, status)) break;
+  cur.start();
+  for (;; cur.advance(g)) {
+    int tile;
+    if (!ring_consumer_wait(rs, cur, status, tile) || tile < 0) break;
+    const int64_t tile_row0 = g.first_row(tile);
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
-      if (cur.row0 + lr >= M) break;  // uniform over the group
+      if (tile_row0 + lr >= M) break;  // uniform over the group
       const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
       float2 xv[HP];
@@ -144,7 +145,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 template <typename T, bool LOG, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t M,
-                        int N, int S_lag, int RPG, int* status) {
+                        int N, int S_lag, int RPG, int* status, unsigned* tile_ctr) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -152,7 +153,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
   unsigned char* stages = smem_raw + kRingHeaderBytes;
 
   RingGeom g;
-  g.init(M, N, sizeof(T), NG * RPG, S_lag, 2);
+  g.init(M, N, sizeof(T), NG * RPG, S_lag, 2, tile_ctr);
   ring_init(rs, g.S, kRingThreads / 32);
   const int tid = threadIdx.x;
   if (tid >= kRingThreads) {  // producer warpgroup: one thread moves the tiles, all four warps shed registers
@@ -174,14 +175,15 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
   const uint32_t stages_u32 = smem_u32(stages);
 
   RingCursor cur;
-  cur.start(g);
-  int64_t i = 0;
-  for (; i < g.my_tiles; ++i, cur.advance(g)) {
-    if (!ring_consumer_wait(rs, cur, status)) break;
+  cur.start();
+  for (;; cur.advance(g)) {
+    int tile;
+    if (!ring_consumer_wait(rs, cur, status, tile) || tile < 0) break;
+    const int64_t tile_row0 = g.first_row(tile);
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
-      if (cur.row0 + lr >= M) break;  // uniform over the group
+      if (tile_row0 + lr >= M) break;  // uniform over the group
       const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       const uint32_t ybase = dbase + g.slot_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
