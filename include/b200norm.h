@@ -74,13 +74,12 @@ typedef enum b2n_tuning_knob {
                                   runs beside them on another stream (it cannot share an SM with a ring CTA) */
 } b2n_tuning_knob;
 int b2n_set_tuning(int knob, int value);
-/* Diagnostic: while a buffer is set (this thread), CTA 0 of the layer-norm / RMS-norm forward ring
- * kernel appends event records to it.  Layout (64-bit words, zero the buffer first): word 0 / 1 =
- * record counts of the two writers (consumer thread 0, producer thread); then cap records per
- * writer, cap = (bytes - 16) / 32, each {event << 48 | tile index, %globaltimer ns}.
- * Events: 1/2 consumer wait begin/end, 3 consumer released the tile, 4 producer saw the tile done,
- * 5 store issued, 6 waited for an older store to drain, 7 next load issued, 8+k points inside the
- * consumer's arithmetic.  NULL switches it off. */
+/* Diagnostic: while a buffer is set (this thread), one consumer thread of CTA 0 of the layer-norm /
+ * RMS-norm forward ring kernel appends event records to it.  Layout (64-bit words, zero the buffer
+ * first): word 0 = record count (word 1 belongs to a second writer slot that is unused); then the
+ * records, at most cap = (bytes - 16) / 32 of them, each {event << 48 | tile index, %globaltimer
+ * ns}.  Events: 1/2 consumer wait begin/end, 3 consumer released the tile, 8+k points inside the
+ * consumer's arithmetic (16: kernel entry).  NULL switches it off. */
 int b2n_set_trace_buffer(void* device_buffer, size_t bytes);
 /* Name of the kernel family the most recent launch from this thread used ("generic", "ring", ...). */
 const char* b2n_last_path(void);

@@ -57,12 +57,11 @@ static_assert(sizeof(RingShared) <= kRingHeaderBytes, "ring header too large");
 // %globaltimer) records; buf[0] is the record count, records follow as pairs of 64-bit words.
 enum RingEvent : unsigned {
   EV_C_WAIT_BEGIN = 1, EV_C_WAIT_END = 2, EV_C_RELEASED = 3,
-  EV_P_DONE_SEEN = 4, EV_P_STORE_ISSUED = 5, EV_P_READ_WAITED = 6, EV_P_LOAD_ISSUED = 7,
   EV_C_STEP = 8  // + step number: points inside the consumer's arithmetic
 };
 struct RingTrace {
   unsigned long long* buf;
-  unsigned cap;  // records per writer (two writers: consumer thread 0 and the producer thread)
+  unsigned cap;  // records per writer slot (slot 0: one consumer thread; slot 1 is free)
   // Each writer appends to its own half with a private counter (no atomics: the stores are fire
   // and forget, so tracing barely perturbs the timing).  word 0 / word 1 = the writers' counts.
   __device__ __forceinline__ void put(unsigned writer, unsigned& k, unsigned ev, int64_t tile) const {
