@@ -13,8 +13,8 @@
 // per element instead of 8 (zero-fill + dense gradient read) on top of them.
 //
 // Kernel: the same shared-memory ring as the other row kernels (ring.cuh), one pass, chunks of
-// 32 KB of a row per stage; a persistent CTA owns whole rows so the per-row scalars (target, scale)
-// are fetched once per row, one row ahead.  dx may alias logp.
+// 32 KB of a row per stage; a persistent CTA takes whole rows (handed out dynamically) so the
+// per-row scalars (target, scale) are fetched once per row.  dx may alias logp.
 #include <atomic>
 
 #include "launchers.h"
@@ -55,7 +55,8 @@ template <typename T, typename IdxT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 ce_bwd_ring_kernel(const T* __restrict__ logp, const void* __restrict__ target, const T* __restrict__ weight,
                    const T* __restrict__ grad_out, const T* __restrict__ total_weight, T* __restrict__ dx,
-                   int64_t M, int64_t N, int reduction, int64_t ignore_index, int S, int* status) {
+                   int64_t M, int64_t N, int reduction, int64_t ignore_index, int S, int* status,
+                   unsigned* tile_ctr) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, VH = VEC / 2;
   constexpr int VPT = kCeChunkVecs / kRingThreads;
@@ -67,8 +68,6 @@ ce_bwd_ring_kernel(const T* __restrict__ logp, const void* __restrict__ target, 
   const int tid = threadIdx.x;
   const int64_t nvec = N / VEC;
   const int nch = static_cast<int>((nvec + kCeChunkVecs - 1) / kCeChunkVecs);
-  const int64_t my_rows = M > blockIdx.x ? (M - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int64_t my_tiles = my_rows * nch;
   auto chunk_vecs = [&](int c) {
     const int64_t left = nvec - static_cast<int64_t>(c) * kCeChunkVecs;
     return static_cast<int>(left < kCeChunkVecs ? left : kCeChunkVecs);
@@ -80,48 +79,75 @@ ce_bwd_ring_kernel(const T* __restrict__ logp, const void* __restrict__ target, 
     // ---------------- producer ----------------
     ring_producer_regs();
     if (tid == kRingThreads) {
-      int64_t l_row = blockIdx.x;  // cursor of the next tile to load
-      int l_chunk = 0, l_stage = 0;
-      int64_t loads_issued = 0;
+      // Rows are handed out dynamically: the CTA's first row is blockIdx.x, later ones come from the
+      // global counter, fetched one row ahead.  The row of every tile is left in the stage's tile_id
+      // slot — for the consumers (which row's target and scale apply), for this thread's own store
+      // later, and as the end marker (-1).
+      auto fetch_row = [&]() {
+        const unsigned r = gridDim.x + atomicAdd(tile_ctr, 1u);
+        return r < static_cast<unsigned>(M) ? static_cast<int>(r) : -1;
+      };
+      int next_row = static_cast<int>(blockIdx.x);
+      int l_row = -1, l_chunk = 0, l_stage = 0;  // cursor of the next tile to load
+      unsigned loads_issued = 0, retired = 0;
+      bool ended = false;
       auto issue_next_load = [&]() {
+        if (l_chunk == 0) {  // a new row
+          l_row = next_row;
+          if (l_row < 0) {
+            rs->tile_id[l_stage] = -1;
+            mbar_arrive(&rs->full[l_stage]);
+            ended = true;
+            retired = atomicAdd(tile_ctr + 1, 1u);
+            return;
+          }
+          next_row = fetch_row();
+        }
         const uint32_t bytes = static_cast<uint32_t>(chunk_vecs(l_chunk)) * 16u;
         const size_t goff = (static_cast<size_t>(l_row) * static_cast<size_t>(nvec) +
                              static_cast<size_t>(l_chunk) * kCeChunkVecs) * 16;
+        rs->tile_id[l_stage] = l_row;
         mbar_arrive_expect_tx(&rs->full[l_stage], bytes);
         bulk_g2s(stages + static_cast<size_t>(l_stage) * kStageBytes,
                  reinterpret_cast<const unsigned char*>(logp) + goff, bytes, &rs->full[l_stage]);
         ++loads_issued;
-        if (++l_chunk == nch) { l_chunk = 0; l_row += gridDim.x; }
+        if (++l_chunk == nch) l_chunk = 0;
         if (++l_stage == S) l_stage = 0;
       };
-      for (int k = 0; k < S && loads_issued < my_tiles; ++k) issue_next_load();
+      for (int k = 0; k < S && !ended; ++k) issue_next_load();
 
-      int64_t row = blockIdx.x;  // cursor of the tile whose completion is awaited
-      int chunk = 0, stage = 0;
+      int chunk = 0, stage = 0;  // cursor of the tile whose completion is awaited
       uint32_t phase = 0;
-      int64_t t = 0;
-      for (; t < my_tiles; ++t) {
-        if (!mbar_wait(&rs->done[stage], phase, status)) break;
+      unsigned t = 0;
+      for (; t < loads_issued; ++t) {
+        const int row = rs->tile_id[stage];  // this thread's own earlier store
         const size_t goff = (static_cast<size_t>(row) * static_cast<size_t>(nvec) +
                              static_cast<size_t>(chunk) * kCeChunkVecs) * 16;
+        if (!mbar_wait(&rs->done[stage], phase, status)) break;
         bulk_s2g(reinterpret_cast<unsigned char*>(dx) + goff, stages + static_cast<size_t>(stage) * kStageBytes,
                  static_cast<uint32_t>(chunk_vecs(chunk)) * 16u);
         bulk_commit();
         // the store of tile t-1 has read its stage once at most one group is pending; that stage is
         // where load number t-1+S belongs
-        if (t > 0 && loads_issued < my_tiles) {
+        if (t > 0 && !ended) {
           bulk_wait_read<1>();
           issue_next_load();
         }
-        if (++chunk == nch) { chunk = 0; row += gridDim.x; }
+        if (++chunk == nch) chunk = 0;
         if (++stage == S) { stage = 0; phase ^= 1u; }
       }
       // if a wait gave up, let the loads already issued land before the CTA's shared memory goes away
-      for (int64_t j = t; j < loads_issued; ++j) {
+      for (unsigned j = t; j < loads_issued; ++j) {
         mbar_wait(&rs->full[stage], phase, status);
         if (++stage == S) { stage = 0; phase ^= 1u; }
       }
       bulk_wait_all<0>();
+      // the last CTA to stop taking rows zeroes the counter pair for the slot's next launch
+      if (!ended) retired = atomicAdd(tile_ctr + 1, 1u);
+      if (retired == gridDim.x - 1) {
+        tile_ctr[0] = 0;
+        tile_ctr[1] = 0;
+      }
     }
     return;
   }
@@ -131,23 +157,21 @@ ce_bwd_ring_kernel(const T* __restrict__ logp, const void* __restrict__ target, 
   const uint32_t stages_u32 = smem_u32(stages);
   int stage = 0;
   uint32_t phase = 0;
-  float s_next = 0.0f;
-  int64_t t_next = -1;
-  if (my_rows > 0)
-    ce_row_params<T, IdxT>(blockIdx.x, target, weight, grad_out, total_weight, N, reduction, ignore_index, status,
-                           s_next, t_next);
-  for (int64_t r = 0; r < my_rows; ++r) {
-    const float s = s_next;
-    const int64_t t = t_next;
-    if (r + 1 < my_rows)  // the next row's scalars: their load latency hides behind this row's chunks
-      ce_row_params<T, IdxT>(blockIdx.x + (r + 1) * static_cast<int64_t>(gridDim.x), target, weight, grad_out,
-                             total_weight, N, reduction, ignore_index, status, s_next, t_next);
+  for (;;) {  // one iteration per row, until the producer's end marker
+    // the row's first chunk names the row; its target and scale are fetched then (the stages already
+    // filled behind it keep the memory pipe busy meanwhile)
+    bool ok = mbar_wait(&rs->full[stage], phase, status);
+    if (!ok) break;
+    const int row = rs->tile_id[stage];
+    if (row < 0) break;  // uniform: every consumer reads the same slot
+    float s;
+    int64_t t;
+    ce_row_params<T, IdxT>(row, target, weight, grad_out, total_weight, N, reduction, ignore_index, status, s, t);
     const int64_t tv = t >= 0 ? t / VEC : -1;  // the vector and the lane of the target column
     const int te = t >= 0 ? static_cast<int>(t % VEC) : 0;
     const float2 s2 = bcast2(s), l2e = bcast2(kLog2e);
-    bool ok = true;
     for (int c = 0; c < nch; ++c) {
-      ok = mbar_wait(&rs->full[stage], phase, status);
+      if (c > 0) ok = mbar_wait(&rs->full[stage], phase, status);
       if (!ok) break;
       const int cv = chunk_vecs(c);
       const uint32_t s0 = stages_u32 + static_cast<uint32_t>(stage) * kStageBytes;
@@ -259,7 +283,7 @@ int ce_bwd_typed(const void* logp_, const void* target, const void* weight_, con
         const int grid = static_cast<int>(M < ctas ? M : ctas);
         ProfileScope prof("cross_entropy_bwd_ring", st);
         return launch_pdl(kernel, dim3(grid), dim3(kRingBlock), smem, st, logp, target, weight, grad_out, total_weight,
-                          dx, M, N, reduction, ignore_index, static_cast<int>(stages), device_status_ptr());
+                          dx, M, N, reduction, ignore_index, static_cast<int>(stages), device_status_ptr(), next_tile_counter());
       }
     }
   }

@@ -135,7 +135,7 @@ int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_
   ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_twopass" : "softmax_bwd_twopass")
                         : (LOG ? "log_softmax_fwd_twopass" : "softmax_fwd_twopass"), st);
   return launch_pdl(kernel, dim3(grid), dim3(kRingBlock), smem, st, in0, in1, out, M, N, static_cast<int>(stages),
-                    device_status_ptr());
+                    device_status_ptr(), next_tile_counter());
 }
 
 template <typename TI, typename TO, bool LOG>

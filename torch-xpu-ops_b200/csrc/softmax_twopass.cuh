@@ -32,7 +32,7 @@ template <typename T> __device__ __forceinline__ float row_exp2p(float d) {
 template <typename T, bool LOG, bool BWD>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* __restrict__ out, int64_t M,
-                       int64_t N, int S, int* status) {
+                       int64_t N, int S, int* status, unsigned* tile_ctr) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, VH = VEC / 2;
   constexpr int NIN2 = BWD ? 2 : 1;                 // tensors staged per chunk in pass 2
@@ -47,8 +47,6 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
   const int tid = threadIdx.x;
   const int64_t nvec = N / VEC;
   const int nch = static_cast<int>((nvec + kTwoPassChunkVecs - 1) / kTwoPassChunkVecs);
-  const int64_t my_rows = M > blockIdx.x ? (M - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int64_t my_tiles = my_rows * 2 * nch;
   auto chunk_vecs = [&](int c) {
     const int64_t left = nvec - static_cast<int64_t>(c) * kTwoPassChunkVecs;
     return static_cast<int>(left < kTwoPassChunkVecs ? left : kTwoPassChunkVecs);
@@ -60,37 +58,56 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
     // ---------------- producer ----------------
     ring_producer_regs();
     if (tid == kRingThreads) {
-      // cursor of the next tile to load
-      int64_t l_row = blockIdx.x;
-      int l_pass = 0, l_chunk = 0, l_stage = 0;
-      uint32_t l_phase = 0;
-      int64_t loads_issued = 0;
+      // Rows are handed out dynamically (as the ring kernels hand out tiles): the CTA's first row is
+      // blockIdx.x, later ones come from the global counter, fetched one row ahead.  The row of
+      // every tile is left in the stage's tile_id slot — for this thread's own store later, and as
+      // the end marker (-1) the consumers look for at the start of a row.
+      auto fetch_row = [&]() {
+        const unsigned r = gridDim.x + atomicAdd(tile_ctr, 1u);
+        return r < static_cast<unsigned>(M) ? static_cast<int>(r) : -1;
+      };
+      int next_row = static_cast<int>(blockIdx.x);
+      int l_row = -1, l_pass = 0, l_chunk = 0, l_stage = 0;  // cursor of the next tile to load
+      unsigned loads_issued = 0, retired = 0;
+      bool ended = false;
       auto issue_next_load = [&]() {
+        if (l_pass == 0 && l_chunk == 0) {  // a new row
+          l_row = next_row;
+          if (l_row < 0) {
+            rs->tile_id[l_stage] = -1;
+            mbar_arrive(&rs->full[l_stage]);
+            ended = true;
+            retired = atomicAdd(tile_ctr + 1, 1u);
+            return;
+          }
+          next_row = fetch_row();
+        }
         const uint32_t bytes = static_cast<uint32_t>(chunk_vecs(l_chunk)) * 16u;
         const size_t goff = (static_cast<size_t>(l_row) * static_cast<size_t>(nvec) +
                              static_cast<size_t>(l_chunk) * kTwoPassChunkVecs) * 16;
         unsigned char* dst = stages + static_cast<size_t>(l_stage) * kStageBytes;
         const int nin = l_pass == 0 ? NIN1 : NIN2;
+        rs->tile_id[l_stage] = l_row;
         mbar_arrive_expect_tx(&rs->full[l_stage], bytes * nin);
         bulk_g2s(dst, reinterpret_cast<const unsigned char*>(in0) + goff, bytes, &rs->full[l_stage]);
         if (nin == 2) bulk_g2s(dst + kChunkBytes, reinterpret_cast<const unsigned char*>(in1) + goff, bytes, &rs->full[l_stage]);
         ++loads_issued;
         if (++l_chunk == nch) {
           l_chunk = 0;
-          if (++l_pass == 2) { l_pass = 0; l_row += gridDim.x; }
+          if (++l_pass == 2) l_pass = 0;
         }
-        if (++l_stage == S) { l_stage = 0; l_phase ^= 1u; }
+        if (++l_stage == S) l_stage = 0;
       };
-      for (int k = 0; k < S && loads_issued < my_tiles; ++k) issue_next_load();
+      for (int k = 0; k < S && !ended; ++k) issue_next_load();
 
       // cursor of the tile whose completion is awaited
-      int64_t row = blockIdx.x;
       int pass = 0, chunk = 0, stage = 0;
       uint32_t phase = 0;
-      int pending = 0;          // bulk stores issued and not yet known to have drained (0..2)
-      int64_t free_upto = -1;   // every tile <= free_upto has released its stage
-      int64_t t = 0;
-      for (; t < my_tiles; ++t) {
+      int pending = 0;                // bulk stores issued and not yet known to have drained (0..2)
+      int64_t free_upto = -1;         // every tile <= free_upto has released its stage
+      unsigned t = 0;
+      for (; t < loads_issued; ++t) {
+        const int row = rs->tile_id[stage];  // this thread's own earlier store
         if (!mbar_wait(&rs->done[stage], phase, status)) break;
         if (pass == 0) {
           // nothing to store; stages are recycled in tile order, so older stores must have drained
@@ -103,21 +120,27 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
                    static_cast<uint32_t>(chunk_vecs(chunk)) * 16u);
           bulk_commit();
           if (++pending > 1) { bulk_wait_read<1>(); pending = 1; }
-          free_upto = t - pending;
+          free_upto = static_cast<int64_t>(t) - pending;
         }
-        while (loads_issued < my_tiles && loads_issued - S <= free_upto) issue_next_load();
+        while (!ended && static_cast<int64_t>(loads_issued) - S <= free_upto) issue_next_load();
         if (++chunk == nch) {
           chunk = 0;
-          if (++pass == 2) { pass = 0; row += gridDim.x; }
+          if (++pass == 2) pass = 0;
         }
         if (++stage == S) { stage = 0; phase ^= 1u; }
       }
       // if a wait gave up, let the loads already issued land before the CTA's shared memory goes away
-      for (int64_t j = t; j < loads_issued; ++j) {
+      for (unsigned j = t; j < loads_issued; ++j) {
         mbar_wait(&rs->full[stage], phase, status);
         if (++stage == S) { stage = 0; phase ^= 1u; }
       }
       bulk_wait_all<0>();
+      // the last CTA to stop taking rows zeroes the counter pair for the slot's next launch
+      if (!ended) retired = atomicAdd(tile_ctr + 1, 1u);
+      if (retired == gridDim.x - 1) {
+        tile_ctr[0] = 0;
+        tile_ctr[1] = 0;
+      }
     }
     return;
   }
@@ -136,13 +159,14 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
     if ((tid & 31) == 0) mbar_arrive(&rs->done[stage]);
   };
 
-  for (int64_t r = 0; r < my_rows; ++r) {
+  for (;;) {  // one iteration per row, until the producer's end marker
     // ---- pass 1: running statistics over the row's chunks ------------------------------------------
     float pm = ninf, ps = 0.0f;          // forward: per-thread running max and sum of exp(x - pm)
     float2 acc2[2] = {bcast2(0.0f), bcast2(0.0f)};  // backward: sum dy or sum y*dy
     bool ok = true;
     for (int c = 0; c < nch; ++c) {
       ok = mbar_wait(&rs->full[stage], phase, status);
+      if (ok && c == 0 && rs->tile_id[stage] < 0) ok = false;  // no rows left (uniform: every consumer reads the same slot)
       if (!ok) break;
       const int cv = chunk_vecs(c);
       const uint32_t s0 = stages_u32 + static_cast<uint32_t>(stage) * kStageBytes, s1 = s0 + kChunkBytes;
