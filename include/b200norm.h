@@ -150,10 +150,14 @@ int b2n_rms_norm_bwd(const void* dy, const void* x, const void* rstd, const void
 /* ---- softmax / log-softmax --------------------------------------------------------------------
  * The tensor is viewed as [outer, N, inner]; the reduction runs over N (inner == 1 for the last
  * dim).  out_dtype == in_dtype, or B2N_F32 with a 16-bit input ("half_to_float").
+ * is_log: 0 softmax, 1 log-softmax, 2 "safe" softmax — a row whose every element is -inf gives
+ * zeros instead of NaN (a row that also holds a NaN still gives NaN).
  *
  * Replaces at::native::xpu::_softmax_kernel / _log_softmax_kernel
  * (src/ATen/native/xpu/sycl/SoftMaxKernels.h:19-29) behind softmax_xpu_out / log_softmax_xpu_out
- * (src/ATen/native/xpu/SoftMax.cpp:22, :94). */
+ * (src/ATen/native/xpu/SoftMax.cpp:22, :94); mode 2 replaces _safe_softmax_kernel
+ * (SoftMaxKernels.h, host_softmax<false, true> in SoftMaxKernels.cpp:2125-2178) behind
+ * _safe_softmax_xpu (SoftMax.cpp:102-126). */
 int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t inner, int in_dtype,
                     int out_dtype, int is_log, void* stream);
 

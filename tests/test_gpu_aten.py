@@ -182,3 +182,25 @@ def test_nll_loss_sample_matrix(shape, red):
             e = F.nll_loss(logp, t, weight, ignore_index=ign, reduction=red)
             assert a.shape == e.shape
             torch.testing.assert_close(a.cpu(), e, rtol=1e-5, atol=1e-6, equal_nan=True)
+
+
+def test_safe_softmax_through_the_dispatcher_with_autograd():
+    x = torch.randn(6, 2048)
+    x[2] = float("-inf")
+    x[x > 1.5] = float("-inf")
+    xd = x.to(DEV).requires_grad_(True)
+    with forced_path(b200norm.PATH_RING):  # a kernel of PyTorch's own would not fail here for a ring-ineligible shape
+        with pytest.raises(RuntimeError, match="b200norm"):
+            torch._safe_softmax(torch.randn(4, 33, device=DEV), -1)
+    y = torch._safe_softmax(xd, -1)
+    assert capi.last_path() == "ring"
+    g = torch.randn(6, 2048)
+    y.backward(g.to(DEV))
+    xr = x.clone().requires_grad_(True)
+    yr = torch._safe_softmax(xr, -1)
+    yr.backward(g)
+    assert float(y[2].abs().max()) == 0.0 and not bool(torch.isnan(y).any())
+    assert torch.allclose(y.detach().cpu(), yr.detach(), rtol=1e-5, atol=1e-7)
+    assert torch.allclose(xd.grad.cpu(), xr.grad, rtol=1e-4, atol=1e-6)
+    y16 = torch._safe_softmax(x.to(DEV).half(), -1, torch.float32)
+    assert y16.dtype == torch.float32 and float(y16[2].abs().max()) == 0.0

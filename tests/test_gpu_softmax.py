@@ -216,3 +216,64 @@ def test_long_row_kernels(M, N, dt, is_log, path, name):
     else:
         check_out(dx, ao.softmax_bwd(dy, y.cpu(), -1, is_log, dt), "dx", tol=2.0)
     assert capi.device_status() == 0
+
+
+# ---- _safe_softmax: rows of all -inf give zeros (SoftMaxKernels.cpp:327-330 of the reference, test/regressions/
+# test_safe_softmax.py) ----------------------------------------------------------------------------------------
+def _safe_case(M, N, dt, seed=900):
+    x = ao.randn((M, N), seed, torch.float32)
+    x[x > 1.0] = float("-inf")          # scattered masked entries
+    for r in range(0, M, 3):
+        x[r] = float("-inf")            # fully masked rows
+    if M > 4:
+        x[4] = float("-inf")
+        x[4, N // 2] = float("nan")     # masked but for a NaN: must stay NaN
+        x[1, 0] = float("inf")          # +inf in an ordinary row: NaN as in the plain softmax
+    return x.to(dt)
+
+
+def _safe_ref(x, dim, out_dtype):
+    ref = torch.ops.aten._safe_softmax(x.float(), dim)
+    return ref.to(out_dtype)
+
+
+@pytest.mark.parametrize("path,N", [(b200norm.PATH_AUTO, 64), (b200norm.PATH_AUTO, 2048), (b200norm.PATH_GENERIC, 2048),
+                                    (b200norm.PATH_GENERIC, 333), (b200norm.PATH_AUTO, 20008),
+                                    (b200norm.PATH_TWOPASS, 16384), (b200norm.PATH_AUTO, 40000)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+def test_safe_softmax_last_dim(N, dt, path):
+    M = 11
+    x = _safe_case(M, N, dt)
+    with forced_path(path):
+        y = capi._safe_softmax(x.to(DEV), -1)
+    ref = _safe_ref(x, -1, dt)
+    got = y.cpu()
+    assert torch.equal(torch.isnan(got), torch.isnan(ref)), "NaN pattern"
+    for r in range(0, M, 3):
+        assert float(got[r].abs().max()) == 0.0, "a fully masked row must be exactly zero"
+    assert bool(torch.isnan(got[4]).all()) and bool(torch.isnan(got[1]).all())
+    ok = ~torch.isnan(ref)
+    if dt == torch.float32:
+        assert torch.allclose(got[ok], ref[ok], rtol=1e-5, atol=1e-7)
+    else:
+        n_bad, worst = ao.lowp_mismatch(got[ok], ref[ok])
+        assert n_bad == 0, (n_bad, worst)
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_safe_softmax_other_dims_and_half_to_float(dt):
+    x = _safe_case(12, 40, dt).reshape(3, 4, 40).clone()
+    x[:, 2, 7] = float("-inf")  # a fully masked line along dim 0
+    y = capi._safe_softmax(x.to(DEV), 0).cpu()
+    ref = _safe_ref(x, 0, dt)
+    assert torch.equal(torch.isnan(y), torch.isnan(ref))
+    assert float(y[:, 2, 7].abs().max()) == 0.0
+    ok = ~torch.isnan(ref)
+    assert torch.allclose(y[ok].float(), ref[ok].float(), rtol=1e-2 if dt != torch.float32 else 1e-5, atol=1e-6)
+    if dt != torch.float32:
+        y32 = capi._safe_softmax(x.to(DEV), -1, torch.float32).cpu()
+        assert y32.dtype == torch.float32
+        r32 = torch.ops.aten._safe_softmax(x.float(), -1)
+        ok = ~torch.isnan(r32)
+        assert torch.equal(torch.isnan(y32), torch.isnan(r32)) and torch.allclose(y32[ok], r32[ok], rtol=1e-5, atol=1e-7)

@@ -281,6 +281,14 @@ def _softmax(input, dim, half_to_float=False, out=None):
     return _softmax_fwd(input, dim, half_to_float, False, "b2n_softmax_fwd", out)
 
 
+def _safe_softmax(input, dim, dtype=None, out=None):
+    """aten::_safe_softmax: softmax in which a row of all -inf gives zeros instead of NaN."""
+    if input.dtype in (torch.float16, torch.bfloat16) and dtype == torch.float32:
+        return _softmax_fwd(input, dim, True, 2, "b2n_softmax_fwd(safe)", out)
+    x = input.to(dtype) if dtype is not None else input
+    return _softmax_fwd(x, dim, False, 2, "b2n_softmax_fwd(safe)", out)
+
+
 def _log_softmax(input, dim, half_to_float=False, out=None):
     """aten::_log_softmax (out: optional preallocated contiguous result)"""
     return _softmax_fwd(input, dim, half_to_float, True, "b2n_softmax_fwd(log)", out)

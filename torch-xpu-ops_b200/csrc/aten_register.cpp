@@ -223,7 +223,7 @@ static SoftmaxDims softmax_dims(const Tensor& t, int64_t dim) {
   return d;
 }
 
-static void softmax_forward_into(const Tensor& input, int64_t dim_, bool half_to_float, bool is_log, const Tensor& out,
+static void softmax_forward_into(const Tensor& input, int64_t dim_, bool half_to_float, int mode, const Tensor& out,
                                  const char* op) {
   const c10::cuda::CUDAGuard guard(input.device());
   if (half_to_float) {
@@ -237,31 +237,31 @@ static void softmax_forward_into(const Tensor& input, int64_t dim_, bool half_to
   Tensor x = input.contiguous();
   const SoftmaxDims d = softmax_dims(x, dim);
   check_status(b2n_softmax_fwd(x.const_data_ptr(), out.mutable_data_ptr(), d.outer, d.n, d.inner,
-                               to_b2n_dtype(x.scalar_type(), op), to_b2n_dtype(out.scalar_type(), op), is_log ? 1 : 0,
+                               to_b2n_dtype(x.scalar_type(), op), to_b2n_dtype(out.scalar_type(), op), mode,
                                cur_stream()),
                op);
 }
 
-static Tensor softmax_forward(const Tensor& input, int64_t dim, bool half_to_float, bool is_log, const char* op) {
+static Tensor softmax_forward(const Tensor& input, int64_t dim, bool half_to_float, int mode, const char* op) {
   TORCH_CHECK(input.is_cuda(), op, ": expected a CUDA tensor");
   const c10::cuda::CUDAGuard guard(input.device());
   Tensor out = at::empty_like(input, input.options().dtype(half_to_float ? at::kFloat : input.scalar_type()),
                               at::MemoryFormat::Contiguous);
-  softmax_forward_into(input, dim, half_to_float, is_log, out, op);
+  softmax_forward_into(input, dim, half_to_float, mode, out, op);
   return out;
 }
 
-static Tensor& softmax_forward_out(const Tensor& input, int64_t dim, bool half_to_float, bool is_log, Tensor& out,
+static Tensor& softmax_forward_out(const Tensor& input, int64_t dim, bool half_to_float, int mode, Tensor& out,
                                    const char* op) {
   TORCH_CHECK(input.is_cuda() && out.is_cuda(), op, ": expected CUDA tensors");
   const auto want = half_to_float ? at::kFloat : input.scalar_type();
   TORCH_CHECK(out.scalar_type() == want, op, ": expected out dtype ", want, " but got ", out.scalar_type());
   at::native::resize_output(out, input.sizes());
   if (out.is_contiguous()) {
-    softmax_forward_into(input, dim, half_to_float, is_log, out, op);
+    softmax_forward_into(input, dim, half_to_float, mode, out, op);
   } else {
     Tensor tmp = at::empty_like(input, input.options().dtype(want), at::MemoryFormat::Contiguous);
-    softmax_forward_into(input, dim, half_to_float, is_log, tmp, op);
+    softmax_forward_into(input, dim, half_to_float, mode, tmp, op);
     out.copy_(tmp);
   }
   return out;
@@ -313,13 +313,22 @@ static Tensor& softmax_backward_out(const Tensor& grad, const Tensor& output, in
   return grad_input;
 }
 
-Tensor softmax(const Tensor& self, int64_t dim, bool h2f) { return softmax_forward(self, dim, h2f, false, "_softmax"); }
+Tensor softmax(const Tensor& self, int64_t dim, bool h2f) { return softmax_forward(self, dim, h2f, 0, "_softmax"); }
 Tensor& softmax_out(const Tensor& self, int64_t dim, bool h2f, Tensor& out) {
-  return softmax_forward_out(self, dim, h2f, false, out, "_softmax.out");
+  return softmax_forward_out(self, dim, h2f, 0, out, "_softmax.out");
 }
-Tensor log_softmax(const Tensor& self, int64_t dim, bool h2f) { return softmax_forward(self, dim, h2f, true, "_log_softmax"); }
+Tensor log_softmax(const Tensor& self, int64_t dim, bool h2f) { return softmax_forward(self, dim, h2f, 1, "_log_softmax"); }
 Tensor& log_softmax_out(const Tensor& self, int64_t dim, bool h2f, Tensor& out) {
-  return softmax_forward_out(self, dim, h2f, true, out, "_log_softmax.out");
+  return softmax_forward_out(self, dim, h2f, 1, out, "_log_softmax.out");
+}
+// aten::_safe_softmax: softmax whose fully masked (all -inf) rows come out as zeros.  Mirrors
+// _safe_softmax_xpu (src/ATen/native/xpu/SoftMax.cpp:102-110): Half input with dtype Float takes the
+// half_to_float kernel, any other dtype is a conversion first.
+Tensor safe_softmax(const Tensor& self, int64_t dim, std::optional<at::ScalarType> dtype) {
+  if ((self.scalar_type() == at::kHalf || self.scalar_type() == at::kBFloat16) && dtype == at::kFloat)
+    return softmax_forward(self, dim, true, 2, "_safe_softmax");
+  Tensor converted = dtype.has_value() ? self.toType(dtype.value()) : self;
+  return softmax_forward(converted, dim, false, 2, "_safe_softmax");
 }
 Tensor softmax_backward_data(const Tensor& grad, const Tensor& output, int64_t dim, at::ScalarType input_dtype) {
   return softmax_backward(grad, output, dim, input_dtype, false, "_softmax_backward_data");
@@ -464,6 +473,7 @@ TORCH_LIBRARY_IMPL(aten, CUDA, m) {
   m.impl("_fused_rms_norm", TORCH_FN(fused_rms_norm));
   m.impl("_fused_rms_norm_backward", TORCH_FN(fused_rms_norm_backward));
   m.impl("_softmax", TORCH_FN(softmax));
+  m.impl("_safe_softmax", TORCH_FN(safe_softmax));
   m.impl("_softmax.out", TORCH_FN(softmax_out));
   m.impl("_log_softmax", TORCH_FN(log_softmax));
   m.impl("_log_softmax.out", TORCH_FN(log_softmax_out));

@@ -22,6 +22,7 @@ std::atomic<unsigned> g_next_counter_slot{0};
 
 thread_local int tl_last_cuda_error = 0;
 thread_local int tl_forced_path = B2N_PATH_AUTO;
+thread_local bool tl_softmax_safe = false;
 thread_local const char* tl_last_path = "none";
 thread_local unsigned long long tl_launches = 0;
 
@@ -55,6 +56,7 @@ PerDevice& current_device() {
 
 const DeviceInfo& device_info() { return current_device().info; }
 int* device_status_ptr() { return current_device().status_ptr; }
+bool softmax_safe_mode() { return tl_softmax_safe; }
 unsigned* next_tile_counter() {
   unsigned* base = current_device().counters;
   if (base == nullptr) return nullptr;
@@ -255,8 +257,12 @@ int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t in
   if (outer < 0 || N < 0 || inner < 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return B2N_ERR_BAD_ARG;
   if (outer == 0 || N == 0 || inner == 0) return B2N_OK;
   if (!x || !y) return B2N_ERR_BAD_ARG;
-  return launch_softmax_fwd(x, y, outer, N, inner, in_dtype, out_dtype, is_log != 0,
-                            static_cast<cudaStream_t>(stream));
+  if (is_log < 0 || is_log > 2) return B2N_ERR_BAD_ARG;
+  tl_softmax_safe = is_log == 2;
+  const int rc = launch_softmax_fwd(x, y, outer, N, inner, in_dtype, out_dtype, is_log == 1,
+                                    static_cast<cudaStream_t>(stream));
+  tl_softmax_safe = false;
+  return rc;
 }
 
 int b2n_softmax_bwd(const void* dy, const void* y, void* dx, int64_t outer, int64_t N, int64_t inner,

@@ -326,6 +326,7 @@ int check_cuda(cudaError_t e);            // records e for b2n_last_cuda_error; 
 int forced_path();                        // b2n_set_path value of this thread
 void note_path(const char* name);         // records the family used by the last launch
 int* device_status_ptr();                 // device address of the status word of the current device
+bool softmax_safe_mode();                 // this thread's softmax forward is the 'safe' variant (set by the C ABI)
 unsigned* next_tile_counter();            // a zeroed {next tile, CTAs finished} pair for one ring-kernel launch
 int launched();                           // counts one kernel launch; returns check_cuda(cudaGetLastError())
 

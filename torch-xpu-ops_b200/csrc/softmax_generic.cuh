@@ -70,7 +70,8 @@ template <int TPR, typename A> __device__ __forceinline__ MaxSum<A> row_merge(Ma
 // Softmax over the last dim.  Pass 1 streams the row once keeping a running (max, sum); pass 2
 // re-reads it (L1/L2) and writes the result: two reads and one write per element.
 template <typename TI, typename TO, bool LOG, int TPR, int V>
-__global__ void softmax_fwd_generic_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t M, int64_t N) {
+__global__ void softmax_fwd_generic_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t M, int64_t N,
+                                           int safe) {
   using A = acc_t<TI>;
   __shared__ A scratch[64];
   const int tpr = TPR == 32 ? 32 : static_cast<int>(blockDim.x);
@@ -94,13 +95,15 @@ __global__ void softmax_fwd_generic_kernel(const TI* __restrict__ x, TO* __restr
     if (ms.m == -acc_neg_inf<A>()) ms.s = acc_nan<A>();  // +inf in the row: exp(inf - inf)
     const A mx = ms.m;
     const A lg = LOG ? acc_log(ms.s) : A(0);
+    // safe softmax: a row of -inf gives zeros, not NaN (a NaN in the row has made the sum NaN and still wins)
+    const bool zero_row = safe && mx == acc_neg_inf<A>() && !(ms.s != ms.s);
     for (int64_t v = lane; v < nv; v += tpr) {
       const Vec<TI, V> p = ld_vec<TI, V>(xr + v * V);
       Vec<TO, V> o;
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         const A d = to_acc<A>(p.v[e]) - mx;
-        o.v[e] = from_acc<TO>(LOG ? d - lg : acc_exp(d) / ms.s);
+        o.v[e] = from_acc<TO>(zero_row ? A(0) : (LOG ? d - lg : acc_exp(d) / ms.s));
       }
       st_vec<TO, V>(yr + v * V, o);
     }
@@ -157,7 +160,7 @@ __global__ void softmax_bwd_generic_kernel(const TG* __restrict__ dy, const TG* 
 // addresses.  Three passes (max, sum, write).
 template <typename TI, typename TO, bool LOG>
 __global__ void softmax_fwd_spatial_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t outer,
-                                           int64_t N, int64_t inner) {
+                                           int64_t N, int64_t inner, int safe) {
   using A = acc_t<TI>;
   const int64_t total = outer * inner;
   for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -176,9 +179,10 @@ __global__ void softmax_fwd_spatial_kernel(const TI* __restrict__ x, TO* __restr
     for (int64_t j = 0; j < N; ++j) s += acc_exp(to_acc<A>(xp[j * inner]) - mx);
     if (has_nan) s = acc_nan<A>();
     const A lg = LOG ? acc_log(s) : A(0);
+    const bool zero_row = safe && mx == acc_neg_inf<A>() && !has_nan;
     for (int64_t j = 0; j < N; ++j) {
       const A d = to_acc<A>(xp[j * inner]) - mx;
-      yp[j * inner] = from_acc<TO>(LOG ? d - lg : acc_exp(d) / s);
+      yp[j * inner] = from_acc<TO>(zero_row ? A(0) : (LOG ? d - lg : acc_exp(d) / s));
     }
   }
 }

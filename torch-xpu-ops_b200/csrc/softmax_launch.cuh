@@ -41,7 +41,8 @@ int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int6
   if (int e = set_smem_once_sm(kernel, mask)) return e;
   ProfileScope prof(LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring", st);
   return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
-                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter());
+                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(),
+                    softmax_safe_mode() ? 1 : 0);
 }
 
 template <typename T, bool LOG, int GROUP>
@@ -135,7 +136,7 @@ int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_
   ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_twopass" : "softmax_bwd_twopass")
                         : (LOG ? "log_softmax_fwd_twopass" : "softmax_fwd_twopass"), st);
   return launch_pdl(kernel, dim3(grid), dim3(kRingBlock), smem, st, in0, in1, out, M, N, static_cast<int>(stages),
-                    device_status_ptr(), next_tile_counter());
+                    device_status_ptr(), next_tile_counter(), softmax_safe_mode() ? 1 : 0);
 }
 
 template <typename TI, typename TO, bool LOG>
@@ -143,6 +144,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
   const TI* x = static_cast<const TI*>(x_);
   TO* y = static_cast<TO*>(y_);
   const int forced = forced_path();
+  const int safe = softmax_safe_mode() ? 1 : 0;  // rows of -inf give zeros (softmax only)
   if (inner == 1) {
     const int64_t M = outer;
     if constexpr (std::is_same<TI, TO>::value && sizeof(TI) <= 4 && !std::is_same<TI, double>::value) {
@@ -178,20 +180,20 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
     const bool vec = N % V == 0 && is_aligned(x, 16) && is_aligned(y, V * sizeof(TO));
     if (N <= 1024) {
       const int grid = softmax_generic_grid(M, 8);
-      if (vec) softmax_fwd_generic_kernel<TI, TO, LOG, 32, V><<<grid, 256, 0, st>>>(x, y, M, N);
-      else softmax_fwd_generic_kernel<TI, TO, LOG, 32, 1><<<grid, 256, 0, st>>>(x, y, M, N);
+      if (vec) softmax_fwd_generic_kernel<TI, TO, LOG, 32, V><<<grid, 256, 0, st>>>(x, y, M, N, safe);
+      else softmax_fwd_generic_kernel<TI, TO, LOG, 32, 1><<<grid, 256, 0, st>>>(x, y, M, N, safe);
     } else {
       const int grid = softmax_generic_grid(M, 1);
       const int threads = N <= 8192 ? 256 : 1024;
-      if (vec) softmax_fwd_generic_kernel<TI, TO, LOG, 0, V><<<grid, threads, 0, st>>>(x, y, M, N);
-      else softmax_fwd_generic_kernel<TI, TO, LOG, 0, 1><<<grid, threads, 0, st>>>(x, y, M, N);
+      if (vec) softmax_fwd_generic_kernel<TI, TO, LOG, 0, V><<<grid, threads, 0, st>>>(x, y, M, N, safe);
+      else softmax_fwd_generic_kernel<TI, TO, LOG, 0, 1><<<grid, threads, 0, st>>>(x, y, M, N, safe);
     }
     return launched();
   }
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
   const int grid = softmax_generic_grid(outer * inner, 256);
-  softmax_fwd_spatial_kernel<TI, TO, LOG><<<grid, 256, 0, st>>>(x, y, outer, N, inner);
+  softmax_fwd_spatial_kernel<TI, TO, LOG><<<grid, 256, 0, st>>>(x, y, outer, N, inner, safe);
   return launched();
 }
 

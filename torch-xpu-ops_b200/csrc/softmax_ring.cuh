@@ -28,7 +28,7 @@ template <typename T> struct RowExp {
 template <typename T, bool LOG, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S_lag, int RPG,
-                        int* status, unsigned* tile_ctr) {
+                        int* status, unsigned* tile_ctr, int safe) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -115,6 +115,32 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       const float lg = LOG ? logf(sum[0]) : 0.0f;
       const float2 noff = bcast2(-(mx[0] + lg));  // 16-bit log-softmax: x - (max + log sum) in one add
       const float2 inv = bcast2(LOG ? 0.0f : 1.0f / sum[0]);
+      if (safe && mx[0] == ninf) {
+        // safe softmax: a row of -inf gives zeros, not NaN — unless the row holds a NaN, which the
+        // maximum cannot see; the row is read again to find out (rare; the branch is uniform over
+        // the group, so the reduction inside it is legal)
+        float has_nan[1] = {0.0f};
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tg + k * GROUP;
+          if (v < nvec) {
+            float2 f[VH];
+            P::unpack2(lds128(rbase + v * 16), f);
+#pragma unroll
+            for (int e = 0; e < VH; ++e)
+              if (f[e].x != f[e].x || f[e].y != f[e].y) has_nan[0] = 1.0f;
+          }
+        }
+        group_reduce<GROUP, 1>(has_nan, rs->red, grp, tg, red_phase, MaxOp());
+        if (has_nan[0] == 0.0f) {
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) {
+            const int v = tg + k * GROUP;
+            if (v < nvec) sts128(rbase + v * 16, make_uint4(0u, 0u, 0u, 0u));
+          }
+          continue;
+        }
+      }
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
