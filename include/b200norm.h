@@ -170,6 +170,22 @@ int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t in
 int b2n_softmax_bwd(const void* dy, const void* y, void* dx, int64_t outer, int64_t N,
                     int64_t inner, int grad_dtype, int dx_dtype, int is_log, void* stream);
 
+/* ---- masked softmax (last dim) -----------------------------------------------------------------
+ * x, y: [M, N] of dtype; mask: bytes (a bool tensor), non-zero = masked out.  The mask row of
+ * input row r is (r / mask_row_div) % mask_row_mod: (1, M) for a mask of the input's shape, (1, T)
+ * for a [T, T] mask shared by every batch and head of a [B, H, T, T] input, (H*T, B) for a [B, T]
+ * key-padding mask.  Masked elements give 0; a row with nothing left unmasked gives NaN.
+ * Backward: mask of the gradient's shape; dx = y * (dy - sum over unmasked of y*dy), 0 where masked.
+ *
+ * Replaces masked_softmax_kernel / masked_softmax_backward_kernel
+ * (src/ATen/native/xpu/sycl/SoftMaxKernels.cpp:2301-2362, :2364-2407) behind masked_softmax_xpu /
+ * masked_softmax_backward_xpu (src/ATen/native/xpu/SoftMax.cpp:112-126) for the last dim; the
+ * binding composes other dims from masked_fill and the plain softmax entry points. */
+int b2n_masked_softmax_fwd(const void* x, const void* mask, void* y, int64_t M, int64_t N,
+                           int64_t mask_row_div, int64_t mask_row_mod, int dtype, void* stream);
+int b2n_masked_softmax_bwd(const void* dy, const void* y, const void* mask, void* dx, int64_t M,
+                           int64_t N, int dtype, void* stream);
+
 /* ---- nll_loss ---------------------------------------------------------------------------------
  * logp: [M, C] of dtype; target: [M] int64 (target_is_u8 == 0) or uint8; weight: [C] of dtype or
  * NULL.  reduction none: out[M]; mean/sum: out[1].  total_weight[1] of dtype.

@@ -20,6 +20,7 @@ def test_header_declares_the_expected_entry_points():
     names = declared_functions()
     for required in ("b2n_layer_norm_fwd", "b2n_layer_norm_bwd", "b2n_rms_norm_fwd", "b2n_rms_norm_bwd",
                      "b2n_softmax_fwd", "b2n_softmax_bwd", "b2n_nll_loss_fwd", "b2n_nll_loss_bwd", "b2n_cross_entropy_bwd",
+                     "b2n_masked_softmax_fwd", "b2n_masked_softmax_bwd",
                      "b2n_norm_bwd_workspace_bytes", "b2n_strerror", "b2n_abi_version"):
         assert required in names
 

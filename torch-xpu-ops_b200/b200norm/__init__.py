@@ -78,6 +78,8 @@ def load_library() -> ctypes.CDLL:
         "b2n_nll_loss_workspace_bytes": (sz, [i64]),
         "b2n_nll_loss_fwd": (i32, [vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, i64, i32, i32, vp]),
         "b2n_nll_loss_bwd": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i64, i32, i32, vp]),
+        "b2n_masked_softmax_fwd": (i32, [vp, vp, vp, i64, i64, i64, i64, i32, vp]),
+        "b2n_masked_softmax_bwd": (i32, [vp, vp, vp, vp, i64, i64, i32, vp]),
         "b2n_cross_entropy_bwd": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i64, i32, i32, vp]),
     }
     for name, (res, args) in protos.items():

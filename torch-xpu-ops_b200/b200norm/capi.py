@@ -323,6 +323,76 @@ def _log_softmax_backward_data(grad_output, output, dim, input_dtype, out=None):
     return _softmax_bwd(grad_output, output, dim, input_dtype, True, "b2n_softmax_bwd(log)", out)
 
 
+# ---- masked softmax ----------------------------------------------------------------------------------------
+def _masked_layout(input, mask, mask_type):
+    """(row_div, row_mod) of b2n_masked_softmax_fwd for the three layouts masked_softmax_kernel accepts."""
+    if mask.dtype != torch.bool:
+        raise RuntimeError("Mask should be a boolean tensor")
+    if mask_type is None:
+        raise RuntimeError("Mask Type should be defined")
+    if mask_type not in (0, 1, 2):
+        raise RuntimeError("Mask Type should be 0 (src_mask), 1 (src_key_padding_mask), or 2 (default_mask)")
+    rows = input.numel() // max(input.shape[-1], 1) if input.dim() > 0 else 1
+    if mask.shape == input.shape:
+        return 1, max(rows, 1)
+    if (mask_type == 1 and input.dim() == 4 and mask.dim() == 2 and input.shape[0] == mask.shape[0]
+            and input.shape[2] == mask.shape[1] and input.shape[3] == mask.shape[1]):
+        return input.shape[1] * input.shape[2], input.shape[0]
+    if (mask_type == 0 and input.dim() == 4 and mask.dim() == 2 and input.shape[3] == mask.shape[1]
+            and input.shape[2] == mask.shape[0] and mask.shape[0] == mask.shape[1]):
+        return 1, mask.shape[0]
+    raise RuntimeError(f"Mask shape should match input. mask: {list(mask.shape)} input: {list(input.shape)}")
+
+
+def _masked_softmax(input, mask, dim=None, mask_type=None, out=None):
+    """aten::_masked_softmax: softmax with the elements where `mask` is True left out (they give 0)."""
+    _require_cuda(input, mask)
+    lib = load_library()
+    row_div, row_mod = _masked_layout(input, mask, mask_type)
+    x = input.reshape(1) if input.dim() == 0 else input
+    d = x.dim() - 1 if dim is None else dim % x.dim()
+    if d != x.dim() - 1:
+        # other dims: the mask applied up front, then the plain kernels (masked elements come out as exp(-inf) = 0)
+        full = mask if mask.shape == input.shape else (
+            mask.view(mask.shape[0], 1, 1, mask.shape[1]) if mask_type == 1 else mask).expand_as(x)
+        return _softmax(x.masked_fill(full, float("-inf")), d, False, out=out).reshape(input.shape)
+    xc = x.contiguous()
+    m = mask.contiguous()
+    y = out if out is not None else torch.empty_like(xc)
+    n = xc.shape[-1]
+    rows = xc.numel() // n if n > 0 else 0
+    if xc.numel() > 0:
+        with torch.cuda.device(xc.device):
+            _check(lib.b2n_masked_softmax_fwd(_ptr(xc), _ptr(m), _ptr(y), rows, n, row_div, row_mod, _dt(xc.dtype),
+                                              _stream(xc)), "b2n_masked_softmax_fwd")
+    return y.reshape(input.shape)
+
+
+def _masked_softmax_backward(grad_output, output, mask, dim=None, out=None):
+    """aten::_masked_softmax_backward (mask of grad_output's shape)."""
+    _require_cuda(grad_output, output, mask)
+    lib = load_library()
+    if mask.dtype != torch.bool:
+        raise RuntimeError("Mask should be a boolean tensor")
+    if grad_output.shape != mask.shape:
+        raise RuntimeError("Mask shape should match grad shape")
+    g = grad_output.reshape(1) if grad_output.dim() == 0 else grad_output
+    d = g.dim() - 1 if dim is None else dim % g.dim()
+    if d != g.dim() - 1:
+        m = mask.reshape(g.shape)
+        gi = _softmax_backward_data(g.masked_fill(m, 0), output.reshape(g.shape).masked_fill(m, 0), d, g.dtype)
+        return gi.masked_fill(m, 0).reshape(grad_output.shape)
+    gc, yc, mc = g.contiguous(), output.reshape(g.shape).contiguous(), mask.reshape(g.shape).contiguous()
+    dx = out if out is not None else torch.empty_like(gc)
+    n = gc.shape[-1]
+    rows = gc.numel() // n if n > 0 else 0
+    if gc.numel() > 0:
+        with torch.cuda.device(gc.device):
+            _check(lib.b2n_masked_softmax_bwd(_ptr(gc), _ptr(yc), _ptr(mc), _ptr(dx), rows, n, _dt(gc.dtype),
+                                              _stream(gc)), "b2n_masked_softmax_bwd")
+    return dx.reshape(grad_output.shape)
+
+
 # ---- nll_loss --------------------------------------------------------------------------------------------
 def _nll_check(self, target, weight):
     if not 0 < self.dim() <= 2:

@@ -6,6 +6,7 @@
 // are untouched, so autograd formulas and every caller keep working.
 //
 // There is no fallback: a non-zero status from the C ABI becomes a c10::Error.
+#include <limits>
 #include <ATen/ATen.h>
 #include <ATen/AccumulateType.h>
 #include <ATen/ExpandUtils.h>
@@ -345,6 +346,77 @@ Tensor& log_softmax_backward_data_out(const Tensor& grad, const Tensor& output, 
   return softmax_backward_out(grad, output, dim, input_dtype, true, grad_input, "_log_softmax_backward_data.out");
 }
 
+// ---- masked softmax ------------------------------------------------------------------------------
+// Same checks and mask layouts as masked_softmax_kernel / masked_softmax_backward_kernel
+// (src/ATen/native/xpu/sycl/SoftMaxKernels.cpp:2301-2407).
+Tensor masked_softmax(const Tensor& input_, const Tensor& mask_, std::optional<int64_t> dim_,
+                      std::optional<int64_t> mask_type_) {
+  const char* op = "_masked_softmax";
+  TORCH_CHECK(input_.is_cuda() && mask_.is_cuda(), op, ": expected CUDA tensors");
+  TORCH_CHECK(mask_.scalar_type() == at::kBool, "Mask should be a boolean tensor");
+  TORCH_CHECK(mask_type_.has_value(), "Mask Type should be defined");
+  const int64_t mask_type = mask_type_.value();
+  TORCH_CHECK(mask_type == 0 || mask_type == 1 || mask_type == 2,
+              "Mask Type should be 0 (src_mask), 1 (src_key_padding_mask), or 2 (default_mask)");
+  const bool is_BxT = mask_type == 1 && input_.dim() == 4 && mask_.dim() == 2 && input_.size(0) == mask_.size(0) &&
+                      input_.size(2) == mask_.size(1) && input_.size(3) == mask_.size(1);
+  const bool is_TxT = mask_type == 0 && input_.dim() == 4 && mask_.dim() == 2 && input_.size(3) == mask_.size(1) &&
+                      input_.size(2) == mask_.size(0) && mask_.size(0) == mask_.size(1);
+  const bool same = mask_.sizes() == input_.sizes();
+  TORCH_CHECK(same || is_BxT || is_TxT, "Mask shape should match input. mask: ", mask_.sizes(),
+              " input: ", input_.sizes());
+  const c10::cuda::CUDAGuard guard(input_.device());
+  Tensor input = input_.dim() == 0 ? input_.view(1) : input_;
+  const int64_t dim = dim_.has_value() ? at::maybe_wrap_dim(dim_.value(), input.dim()) : input.dim() - 1;
+  if (dim != input.dim() - 1) {
+    // other dims: the mask applied up front, then the plain kernels (masked elements come out as exp(-inf) = 0)
+    Tensor full = same ? (mask_.dim() == 0 ? mask_.view(1) : mask_)
+                       : (is_BxT ? mask_.view({mask_.size(0), 1, 1, mask_.size(1)}) : mask_).expand_as(input);
+    return softmax_forward(input.masked_fill(full, -std::numeric_limits<double>::infinity()), dim, false, 0, op)
+        .view(input_.sizes());
+  }
+  Tensor x = input.contiguous();
+  Tensor mask = mask_.contiguous();
+  Tensor out = at::empty_like(x, x.options(), at::MemoryFormat::Contiguous);
+  if (x.numel() == 0) return out.view(input_.sizes());
+  const int64_t n = x.size(-1), rows = x.numel() / n;
+  int64_t row_div = 1, row_mod = rows;
+  if (!same && is_BxT) { row_div = x.size(1) * x.size(2); row_mod = x.size(0); }
+  if (!same && is_TxT) { row_div = 1; row_mod = mask.size(0); }
+  check_status(b2n_masked_softmax_fwd(x.const_data_ptr(), mask.const_data_ptr(), out.mutable_data_ptr(), rows, n,
+                                      row_div, row_mod, to_b2n_dtype(x.scalar_type(), op), cur_stream()),
+               op);
+  return out.view(input_.sizes());
+}
+
+Tensor masked_softmax_backward(const Tensor& grad_, const Tensor& output_, const Tensor& mask_,
+                               std::optional<int64_t> dim_) {
+  const char* op = "_masked_softmax_backward";
+  TORCH_CHECK(grad_.is_cuda() && output_.is_cuda() && mask_.is_cuda(), op, ": expected CUDA tensors");
+  const c10::cuda::CUDAGuard guard(grad_.device());
+  if (grad_.numel() == 0) return at::empty_like(grad_, grad_.options());
+  Tensor grad = grad_.contiguous(), output = output_.contiguous(), mask = mask_.contiguous();
+  const int64_t dim = dim_.has_value() ? at::maybe_wrap_dim(dim_.value(), output.dim()) : output.dim() - 1;
+  if (grad.dim() == 0) { grad = grad.view(1); mask = mask.view(1); output = output.view(1); }
+  TORCH_CHECK(dim >= 0 && dim < grad.dim(), "dim must be non-negative and less than input dimensions");
+  TORCH_CHECK(grad.sizes() == mask.sizes(), "Mask shape should match grad shape");
+  TORCH_CHECK(mask.scalar_type() == at::kBool, "Mask should be a boolean tensor");
+  TORCH_CHECK(output.scalar_type() == grad.scalar_type() && output.sizes() == grad.sizes(), op,
+              ": grad_output and output must agree in dtype and shape");
+  if (dim != grad.dim() - 1) {
+    Tensor gi = softmax_backward(grad.masked_fill(mask, 0), output.masked_fill(mask, 0), dim, grad.scalar_type(),
+                                 false, op);
+    return gi.masked_fill(mask, 0).view(grad_.sizes());
+  }
+  Tensor gi = at::empty_like(grad, grad.options(), at::MemoryFormat::Contiguous);
+  const int64_t n = grad.size(-1), rows = grad.numel() / n;
+  check_status(b2n_masked_softmax_bwd(grad.const_data_ptr(), output.const_data_ptr(), mask.const_data_ptr(),
+                                      gi.mutable_data_ptr(), rows, n, to_b2n_dtype(grad.scalar_type(), op),
+                                      cur_stream()),
+               op);
+  return gi.view(grad_.sizes());
+}
+
 // ---- nll_loss ------------------------------------------------------------------------------------
 // Shape rules of the upstream meta function for nll_loss_forward.
 static void nll_check(const Tensor& self, const Tensor& target, const Tensor& weight) {
@@ -474,6 +546,8 @@ TORCH_LIBRARY_IMPL(aten, CUDA, m) {
   m.impl("_fused_rms_norm_backward", TORCH_FN(fused_rms_norm_backward));
   m.impl("_softmax", TORCH_FN(softmax));
   m.impl("_safe_softmax", TORCH_FN(safe_softmax));
+  m.impl("_masked_softmax", TORCH_FN(masked_softmax));
+  m.impl("_masked_softmax_backward", TORCH_FN(masked_softmax_backward));
   m.impl("_softmax.out", TORCH_FN(softmax_out));
   m.impl("_log_softmax", TORCH_FN(log_softmax));
   m.impl("_log_softmax.out", TORCH_FN(log_softmax_out));

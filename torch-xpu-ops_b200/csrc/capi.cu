@@ -299,6 +299,23 @@ int b2n_nll_loss_bwd(const void* grad_out, const void* target, const void* weigh
                              dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
 }
 
+int b2n_masked_softmax_fwd(const void* x, const void* mask, void* y, int64_t M, int64_t N, int64_t mask_row_div,
+                           int64_t mask_row_mod, int dtype, void* stream) {
+  if (M < 0 || N < 0 || mask_row_div < 1 || mask_row_mod < 1 || !valid_dtype(dtype)) return B2N_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return B2N_OK;
+  if (!x || !mask || !y) return B2N_ERR_BAD_ARG;
+  return launch_masked_softmax_fwd(x, mask, y, M, N, mask_row_div, mask_row_mod, dtype,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int b2n_masked_softmax_bwd(const void* dy, const void* y, const void* mask, void* dx, int64_t M, int64_t N,
+                           int dtype, void* stream) {
+  if (M < 0 || N < 0 || !valid_dtype(dtype)) return B2N_ERR_BAD_ARG;
+  if (M == 0 || N == 0) return B2N_OK;
+  if (!dy || !y || !mask || !dx) return B2N_ERR_BAD_ARG;
+  return launch_masked_softmax_bwd(dy, y, mask, dx, M, N, dtype, static_cast<cudaStream_t>(stream));
+}
+
 int b2n_cross_entropy_bwd(const void* logp, const void* target, const void* weight, const void* grad_out,
                           const void* total_weight, void* dx, int64_t M, int64_t C, int reduction,
                           int64_t ignore_index, int dtype, int target_is_u8, void* stream) {

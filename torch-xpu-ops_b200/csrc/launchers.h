@@ -33,6 +33,10 @@ int launch_nll_loss_fwd(const void* logp, const void* target, const void* weight
 int launch_nll_loss_bwd(const void* grad_out, const void* target, const void* weight,
                         const void* total_weight, void* grad_input, int64_t M, int64_t C, int reduction,
                         int64_t ignore_index, int dtype, bool target_is_u8, cudaStream_t st);
+int launch_masked_softmax_fwd(const void* x, const void* mask, void* y, int64_t M, int64_t N, int64_t row_div,
+                              int64_t row_mod, int dtype, cudaStream_t st);
+int launch_masked_softmax_bwd(const void* dy, const void* y, const void* mask, void* dx, int64_t M, int64_t N,
+                              int dtype, cudaStream_t st);
 int launch_cross_entropy_bwd(const void* logp, const void* target, const void* weight, const void* grad_out,
                              const void* total_weight, void* dx, int64_t M, int64_t C, int reduction,
                              int64_t ignore_index, int dtype, bool target_is_u8, cudaStream_t st);
