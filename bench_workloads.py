@@ -201,6 +201,63 @@ class Cfg3Softmax(_Simple):
         return 2 * rows * self.T * 2
 
 
+class Cfg3Masked(Cfg3Softmax):
+    """Config 3 with the causal mask applied INSIDE the kernels (aten::_masked_softmax with a [T, T] source mask,
+    aten::_masked_softmax_backward with the mask expanded to the gradient's shape) instead of being written into the
+    scores beforehand.  Not a BASELINE config.  Bytes: forward 2 tensors (the 4 MB mask stays in L2); backward 3
+    tensors + 1 mask byte per element."""
+    name = "cfg3m"
+
+    def describe(self):
+        return ("_masked_softmax (mask_type 0: [2048, 2048] causal source mask) + _masked_softmax_backward (mask of "
+                "the gradient's shape) over the last dim, bf16 [8, 32, 2048, 2048] unmasked scores")
+
+    def bytes_per_rows(self, rows):
+        t = self.T
+        fwd, bwd = 2 * rows * t * 2, 3 * rows * t * 2 + rows * t
+        return {"total": fwd + bwd, "masked_softmax_fwd_ring": fwd, "masked_softmax_bwd_ring": bwd,
+                "masked_softmax_fwd": fwd, "masked_softmax_bwd": bwd}
+
+    def _make(self, rows, dev, gen):
+        t = self.T
+        s = torch.randn((rows, t), generator=gen, device=dev) / math.sqrt(128)
+        g = torch.randn((rows, t), generator=gen, device=dev).to(torch.bfloat16)
+        return s.to(torch.bfloat16), g
+
+    def _masks(self, rows, dev):
+        t = self.T
+        causal = torch.triu(torch.ones(t, t, dtype=torch.bool, device=dev), 1)
+        full = causal.repeat((rows + t - 1) // t, 1)[:rows].contiguous()
+        return causal, full
+
+    def make_cpu_state(self, rows):
+        st = super().make_cpu_state(rows)
+        st["causal"], st["full"] = self._masks(rows, torch.device("cpu"))
+        return st
+
+    def make_device_state(self, rows, dev, seed):
+        st = super().make_device_state(rows, dev, seed)
+        st["causal"], st["full"] = self._masks(rows, dev)
+        # the [T, T] layout of the reference needs a 4-D input: view the rows as [1, rows / T, T, T]
+        st["shape4"] = (1, rows // self.T, self.T, self.T) if rows % self.T == 0 else None
+        return st
+
+    def step(self, capi, st, world):
+        if st["shape4"] is not None:
+            capi._masked_softmax(st["s"].view(st["shape4"]), st["causal"], -1, 0, out=st["p"])
+        else:
+            capi._masked_softmax(st["s"], st["full"], -1, 2, out=st["p"])
+        capi._masked_softmax_backward(st["g"], st["p"], st["full"], -1, out=st["dx"])
+
+    def cpu_step(self, cpu):
+        p = torch._masked_softmax(cpu["s"], cpu["full"], -1, 2)
+        return torch.ops.aten._masked_softmax_backward(cpu["g"], p, cpu["full"], -1)
+
+    def aten_step(self, st, world):
+        p = torch._masked_softmax(st["s"], st["full"], -1, 2)
+        return p, torch.ops.aten._masked_softmax_backward(st["g"], p, st["full"], -1)
+
+
 class Cfg5CrossEntropy(_Simple):
     name, rows, V, cpu_sample_rows = "cfg5", 16384, 128256, 1024
     collective = "all_reduce(fp32[2]: loss sum, weight sum) per step"
@@ -305,5 +362,5 @@ class Cfg5FusedTail(Cfg5CrossEntropy):
         return loss.detach(), x.grad
 
 
-EXTRA = {"cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg5": Cfg5CrossEntropy,
-         "cfg5f": Cfg5FusedTail}
+EXTRA = {"cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,
+         "cfg5": Cfg5CrossEntropy, "cfg5f": Cfg5FusedTail}

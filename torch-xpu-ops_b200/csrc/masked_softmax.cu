@@ -9,11 +9,13 @@
 // Backward (mask of the gradient's shape, :2364-2407): dx = y * (dy - sum_unmasked(y * dy)), zero
 // where masked.
 //
-// One warp per row up to 1024 elements, one CTA per row beyond; 16-byte loads of x with 8- or
-// 4-byte loads of the mask when everything is aligned, scalar accesses otherwise; the row is read
-// twice (second time from L1/L2).
+// Rows the ring takes (16-byte aligned, 16-bit or fp32, N within the ring's reach) run on the softmax
+// ring kernels with the mask applied in registers (softmax_ring.cuh: RowMask).  Everything else runs
+// on the kernels below: one warp per row up to 1024 elements, one CTA per row beyond; 16-byte loads
+// of x with 8- or 4-byte loads of the mask when everything is aligned, scalar accesses otherwise; the
+// row is read twice (second time from L1/L2).
 #include "launchers.h"
-#include "softmax_generic.cuh"
+#include "softmax_launch.cuh"
 
 namespace b2n {
 namespace {
@@ -134,6 +136,26 @@ int masked_fwd_typed(const void* x_, const unsigned char* mask, void* y_, int64_
   T* y = static_cast<T*>(y_);
   constexpr int V = 16 / sizeof(T) > 8 ? 8 : 16 / sizeof(T);  // elements per vector (mask bytes per load)
   const bool vec = N % V == 0 && is_aligned(x, V * sizeof(T)) && is_aligned(y, V * sizeof(T)) && is_aligned(mask, V);
+  const int forced = forced_path();
+  if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
+    if (forced != B2N_PATH_GENERIC && vec && is_aligned(x, 16) && is_aligned(y, 16) && M < (1LL << 31) &&
+        row_div < (1LL << 32) && row_mod < (1LL << 32)) {
+      const DeviceInfo& di = device_info();
+      const RingPlan p = plan_ring(M, N, sizeof(T), 1, kSoftmaxEpt, persistent_ctas(di.sm_count), di.max_smem_optin);
+      if (p.ok) {
+        note_path("ring");
+        const RowMask rm{mask, static_cast<unsigned>(row_div), static_cast<unsigned>(row_mod)};
+        switch (p.group) {
+          case 32: return softmax_fwd_ring_launch<T, false, 32>(p, x, y, M, N, st, rm);
+          case 64: return softmax_fwd_ring_launch<T, false, 64>(p, x, y, M, N, st, rm);
+          case 128: return softmax_fwd_ring_launch<T, false, 128>(p, x, y, M, N, st, rm);
+          case 256: return softmax_fwd_ring_launch<T, false, 256>(p, x, y, M, N, st, rm);
+          default: return softmax_fwd_ring_launch<T, false, 512>(p, x, y, M, N, st, rm);
+        }
+      }
+    }
+  }
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
   ProfileScope prof("masked_softmax_fwd", st);
   if (N <= 1024) {
@@ -158,6 +180,26 @@ int masked_bwd_typed(const void* dy_, const void* y_, const unsigned char* mask,
   constexpr int V = 16 / sizeof(T) > 8 ? 8 : 16 / sizeof(T);
   const bool vec = N % V == 0 && is_aligned(dy, V * sizeof(T)) && is_aligned(y, V * sizeof(T)) &&
                    is_aligned(dx, V * sizeof(T)) && is_aligned(mask, V);
+  const int forced = forced_path();
+  if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
+    if (forced != B2N_PATH_GENERIC && vec && is_aligned(dy, 16) && is_aligned(y, 16) && is_aligned(dx, 16) &&
+        M < (1LL << 31)) {
+      const DeviceInfo& di = device_info();
+      const RingPlan p = plan_ring(M, N, sizeof(T), 2, kSoftmaxEpt, persistent_ctas(di.sm_count), di.max_smem_optin);
+      if (p.ok) {
+        note_path("ring");
+        const RowMask rm{mask, 1u, static_cast<unsigned>(M)};  // a mask of the gradient's shape
+        switch (p.group) {
+          case 32: return softmax_bwd_ring_launch<T, false, 32>(p, dy, y, dx, M, N, st, rm);
+          case 64: return softmax_bwd_ring_launch<T, false, 64>(p, dy, y, dx, M, N, st, rm);
+          case 128: return softmax_bwd_ring_launch<T, false, 128>(p, dy, y, dx, M, N, st, rm);
+          case 256: return softmax_bwd_ring_launch<T, false, 256>(p, dy, y, dx, M, N, st, rm);
+          default: return softmax_bwd_ring_launch<T, false, 512>(p, dy, y, dx, M, N, st, rm);
+        }
+      }
+    }
+  }
+  if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
   ProfileScope prof("masked_softmax_bwd", st);
   if (N <= 1024) {

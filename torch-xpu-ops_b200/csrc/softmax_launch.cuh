@@ -34,27 +34,28 @@ inline int softmax_generic_grid(int64_t rows, int rows_per_block) {
 }
 
 template <typename T, bool LOG, int GROUP>
-int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int64_t N, cudaStream_t st) {
+int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int64_t N, cudaStream_t st,
+                            RowMask rmask = RowMask{nullptr, 1u, 1u}) {
   constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
   auto kernel = softmax_fwd_ring_kernel<T, LOG, GROUP, VPT>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
-  ProfileScope prof(LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring", st);
+  ProfileScope prof(rmask.base ? "masked_softmax_fwd_ring" : (LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring"), st);
   return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
                     p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(),
-                    softmax_safe_mode() ? 1 : 0);
+                    softmax_safe_mode() ? 1 : 0, rmask);
 }
 
 template <typename T, bool LOG, int GROUP>
 int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, int64_t M, int64_t N,
-                            cudaStream_t st) {
+                            cudaStream_t st, RowMask rmask = RowMask{nullptr, 1u, 1u}) {
   constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
   auto kernel = softmax_bwd_ring_kernel<T, LOG, GROUP, VPT>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
-  ProfileScope prof(LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring", st);
+  ProfileScope prof(rmask.base ? "masked_softmax_bwd_ring" : (LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring"), st);
   return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, y, dx, M, static_cast<int>(N),
-                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter());
+                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
 }
 
 // Rows too long for the ring: a row is split over a cluster of C CTAs (C = 1, 2, 4 or 8, one CTA per

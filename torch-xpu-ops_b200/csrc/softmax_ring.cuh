@@ -25,10 +25,33 @@ template <typename T> struct RowExp {
   }
 };
 
+// ---- optional mask (aten::_masked_softmax on the ring) ------------------------------------------
+// mask: one byte per element, non-zero = masked out; the mask row of input row r is
+// (r / row_div) % row_mod (see b2n_masked_softmax_fwd).  A thread fetches the VEC mask bytes of each
+// of its vectors with one read-only global load, issued before the row's shared-memory loads so
+// that both are in flight together; masks shared by many rows stay in L2.
+struct RowMask {
+  const unsigned char* base;  // nullptr: no mask
+  unsigned row_div, row_mod;
+};
+template <int VEC> struct MaskWord;
+template <> struct MaskWord<8> {
+  uint2 w;
+  __device__ __forceinline__ void load(const unsigned char* p) { w = __ldg(reinterpret_cast<const uint2*>(p)); }
+  __device__ __forceinline__ void clear() { w = make_uint2(0u, 0u); }
+  __device__ __forceinline__ bool masked(int e) const { return (((e < 4 ? w.x : w.y) >> (8 * (e & 3))) & 0xffu) != 0u; }
+};
+template <> struct MaskWord<4> {
+  unsigned w;
+  __device__ __forceinline__ void load(const unsigned char* p) { w = __ldg(reinterpret_cast<const unsigned*>(p)); }
+  __device__ __forceinline__ void clear() { w = 0u; }
+  __device__ __forceinline__ bool masked(int e) const { return ((w >> (8 * e)) & 0xffu) != 0u; }
+};
+
 template <typename T, bool LOG, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S_lag, int RPG,
-                        int* status, unsigned* tile_ctr, int safe) {
+                        int* status, unsigned* tile_ctr, int safe, RowMask mask) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -69,6 +92,17 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       if (tile_row0 + lr >= M) break;  // uniform over the group
       const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
+      MaskWord<VEC> mw[VPT];
+      if (mask.base != nullptr) {
+        const unsigned row = static_cast<unsigned>(tile_row0 + lr);
+        const unsigned char* mr = mask.base + static_cast<size_t>((row / mask.row_div) % mask.row_mod) * N;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tg + k * GROUP;
+          if (v < nvec) mw[k].load(mr + v * VEC);
+          else mw[k].clear();
+        }
+      }
       float2 xv[HP];
       float pm[4] = {ninf, ninf, ninf, ninf};
 #pragma unroll
@@ -76,6 +110,13 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
         const int v = tg + k * GROUP;
         if (v < nvec) {
           P::unpack2(lds128(rbase + v * 16), &xv[k * VH]);
+          if (mask.base != nullptr) {  // masked elements take no part: -inf, which comes out as exactly 0
+#pragma unroll
+            for (int e = 0; e < VH; ++e) {
+              if (mw[k].masked(2 * e)) xv[k * VH + e].x = ninf;
+              if (mw[k].masked(2 * e + 1)) xv[k * VH + e].y = ninf;
+            }
+          }
 #pragma unroll
           for (int e = 0; e < VH; ++e) {
             pm[(2 * e) & 3] = fmaxf(pm[(2 * e) & 3], xv[k * VH + e].x);
@@ -171,7 +212,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 template <typename T, bool LOG, int GROUP, int VPT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t M,
-                        int N, int S_lag, int RPG, int* status, unsigned* tile_ctr) {
+                        int N, int S_lag, int RPG, int* status, unsigned* tile_ctr, RowMask mask) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -213,6 +254,17 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
       const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       const uint32_t ybase = dbase + g.slot_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
+      MaskWord<VEC> mw[VPT];
+      if (mask.base != nullptr) {
+        const unsigned row = static_cast<unsigned>(tile_row0 + lr);
+        const unsigned char* mr = mask.base + static_cast<size_t>((row / mask.row_div) % mask.row_mod) * N;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tg + k * GROUP;
+          if (v < nvec) mw[k].load(mr + v * VEC);
+          else mw[k].clear();
+        }
+      }
       float2 dv[HP], yv[HP];
       float2 ps[2] = {bcast2(0.0f), bcast2(0.0f)};
 #pragma unroll
@@ -221,6 +273,13 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
         if (v < nvec) {
           P::unpack2(lds128(dbase + v * 16), &dv[k * VH]);
           P::unpack2(lds128(ybase + v * 16), &yv[k * VH]);
+          if (mask.base != nullptr) {  // masked elements take no part in the row sum
+#pragma unroll
+            for (int e = 0; e < VH; ++e) {
+              if (mw[k].masked(2 * e)) { dv[k * VH + e].x = 0.0f; yv[k * VH + e].x = 0.0f; }
+              if (mw[k].masked(2 * e + 1)) { dv[k * VH + e].y = 0.0f; yv[k * VH + e].y = 0.0f; }
+            }
+          }
 #pragma unroll
           for (int e = 0; e < VH; ++e) {
             const int j = k * VH + e;
@@ -254,6 +313,13 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
               o[e] = fma2(ey, ns, d);   // dy - exp(y)*sum
             } else {
               o[e] = mul2(yy, add2(d, ns));  // y*(dy - sum)
+            }
+          }
+          if (mask.base != nullptr) {  // exactly zero where masked, whatever the row sum is
+#pragma unroll
+            for (int e = 0; e < VH; ++e) {
+              if (mw[k].masked(2 * e)) o[e].x = 0.0f;
+              if (mw[k].masked(2 * e + 1)) o[e].y = 0.0f;
             }
           }
           sts128(dbase + v * 16, P::pack2(o));
