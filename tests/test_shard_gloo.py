@@ -71,6 +71,10 @@ class OracleOps:
     def _log_softmax_backward_data(self, g, y, dim, dt):
         return torch.ops.aten._log_softmax_backward_data(g, y, dim, dt)
 
+    def cross_entropy_backward(self, g, logp, t, w, red, ign, tw):
+        from oracle import aten_oracle as ao
+        return ao.cross_entropy_bwd(g, logp, t, w, red, ign, tw)
+
 
 def _worker(rank, world, port, tmp):
     sys.path.insert(0, str(ROOT))
@@ -106,6 +110,8 @@ def _worker(rank, world, port, tmp):
         assert abs(float(ce.loss) - float(loss)) < 1e-5
         assert torch.allclose(ce.dlogits, lg.grad[s:e], atol=1e-6)
         assert float(ce.sums[1]) == M - 1
+        cef = shard.cross_entropy_step(ops, logits[s:e], t[s:e], -100, fused=True)
+        assert abs(float(cef.loss) - float(loss)) < 1e-5 and torch.allclose(cef.dlogits, lg.grad[s:e], atol=1e-6)
         (Path(tmp) / f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()

@@ -96,11 +96,14 @@ class CrossEntropyStepResult:
     sums: torch.Tensor       # fp32 [2] after the all-reduce: {sum -w*logp, sum w}
 
 
-def cross_entropy_step(ops, logits_shard, target_shard, ignore_index: int = -100, group=None) -> CrossEntropyStepResult:
+def cross_entropy_step(ops, logits_shard, target_shard, ignore_index: int = -100, group=None,
+                       fused: bool = False) -> CrossEntropyStepResult:
     """_log_softmax + nll_loss_forward(mean) + both backward ops on this rank's rows.
 
     The loss is a mean over the GLOBAL weight: the per-rank {loss sum, weight sum} pair is
     all-reduced first, and the backward scatters -1/total_weight with that global total.
+    fused=True replaces the two backward operators by the one-pass ``cross_entropy_backward``
+    (no dense gradient of the log-probabilities in between); the result is the same.
     """
     logp = ops._log_softmax(logits_shard, -1, False)
     # reduction "sum" locally; the division happens after the exchange
@@ -109,6 +112,9 @@ def cross_entropy_step(ops, logits_shard, target_shard, ignore_index: int = -100
     loss = sums[0] / sums[1]
     total_weight = sums[1].to(logp.dtype)
     one = torch.ones((), dtype=logp.dtype, device=logp.device)
-    grad_logp = ops.nll_loss_backward(one, logp, target_shard, None, 1, ignore_index, total_weight)
-    dlogits = ops._log_softmax_backward_data(grad_logp, logp, -1, logits_shard.dtype)
+    if fused:
+        dlogits = ops.cross_entropy_backward(one, logp, target_shard, None, 1, ignore_index, total_weight)
+    else:
+        grad_logp = ops.nll_loss_backward(one, logp, target_shard, None, 1, ignore_index, total_weight)
+        dlogits = ops._log_softmax_backward_data(grad_logp, logp, -1, logits_shard.dtype)
     return CrossEntropyStepResult(loss, logp, dlogits, sums)
