@@ -156,3 +156,71 @@ def test_comparators():
     assert ao.ulp_distance(a, c) == 1
     assert ao.fp32_err(torch.tensor([1.0, 0.0]), torch.tensor([1.0 + 5e-6, 1e-7])) <= 1.0
     assert ao.fp32_err(torch.tensor([1.0]), torch.tensor([1.001])) > 1.0
+
+
+# ---- golden_v2: the operators around the core path -------------------------------------------------
+GOLDEN2 = torch.load(Path(__file__).parent / "golden" / "golden_v2.pt")
+
+
+def _wide(t):
+    return t.double() if t.dtype == torch.float64 else t.float()
+
+
+@pytest.mark.parametrize("name", ["safe_f32", "safe_bf16", "safe_f32_dim0"])
+def test_golden_safe_softmax(name):
+    c = GOLDEN2[name]
+    y = torch.ops.aten._safe_softmax(_wide(c["x"]), c["dim"]).to(c["x"].dtype)
+    assert torch.equal(y, c["y"]) and not bool(torch.isnan(y).any())
+    # the definition: softmax with the all -inf lines replaced by zeros
+    plain = torch.softmax(_wide(c["x"]), c["dim"])
+    dead = (c["x"] == float("-inf")).all(c["dim"], keepdim=True)
+    assert bool(dead.any())
+    assert torch.equal(torch.where(dead, torch.zeros_like(plain), plain).to(c["x"].dtype), c["y"])
+
+
+@pytest.mark.parametrize("name", ["masked_f32", "masked_bf16"])
+def test_golden_masked_softmax(name):
+    c = GOLDEN2[name]
+    dt = c["x"].dtype
+    x = _wide(c["x"])
+    B, H, T, _ = x.shape
+    for tag, mtype in (("full", 2), ("txt", 0), ("bxt", 1)):
+        m = c["mask_" + tag]
+        y = torch._masked_softmax(x, m, -1, mtype).to(dt)
+        assert torch.equal(torch.isnan(y), torch.isnan(c["y_" + tag]))
+        ok = ~torch.isnan(y)
+        assert torch.equal(y[ok], c["y_" + tag][ok])
+        # the definition: softmax of the scores with the masked ones at -inf
+        full = m if tag == "full" else (m.view(B, 1, 1, T) if tag == "bxt" else m).expand(B, H, T, T)
+        ref = torch.softmax(x.masked_fill(full, float("-inf")), -1).to(dt)
+        if dt == torch.float32:  # two CPU kernels: the same values up to the last bits of their row sums
+            assert torch.allclose(ref[ok], c["y_" + tag][ok], rtol=1e-6, atol=1e-8)
+        else:
+            assert ao.ulp_distance(ref[ok], c["y_" + tag][ok]) <= 1
+    dx = torch.ops.aten._masked_softmax_backward(_wide(c["grad"]), _wide(c["y_full"]), c["mask_full"], -1).to(dt)
+    assert torch.equal(dx, c["dx_full"]) and not bool(torch.isnan(dx).any())
+    assert float(dx[c["mask_full"]].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("name", ["ce_f32", "ce_bf16"])
+def test_golden_cross_entropy_backward(name):
+    c = GOLDEN2[name]
+    logp, t = c["logp"], c["target"]
+    for red in (0, 1, 2):
+        for w, tag in ((None, "now"), (c["weight"], "w")):
+            dx = ao.cross_entropy_bwd(c[f"grad_{red}"], logp, t, w, red, c["ignore_index"], c[f"tw_{red}_{tag}"])
+            assert torch.equal(dx, c[f"dx_{red}_{tag}"])
+            # closed form the fused kernel evaluates: s_i * (exp(logp) - onehot)
+            lp = _wide(logp)
+            wt = torch.ones(lp.shape[1]) if w is None else _wide(w)
+            valid = t != c["ignore_index"]
+            tt = torch.where(valid, t, torch.zeros_like(t))
+            s = wt[tt] * _wide(c[f"grad_{red}"]) * valid
+            if red == 1:
+                s = s / _wide(c[f"tw_{red}_{tag}"])
+            onehot = torch.nn.functional.one_hot(tt, lp.shape[1]).to(lp.dtype)
+            closed = (s.reshape(-1, 1) * (lp.exp() - onehot)).to(logp.dtype)
+            if logp.dtype == torch.float32:
+                assert torch.allclose(closed, dx, rtol=1e-5, atol=1e-7)
+            else:
+                assert ao.ulp_distance(closed, dx) <= 1
