@@ -37,23 +37,58 @@ template <typename T, bool LOG, int GROUP>
 int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int64_t N, cudaStream_t st,
                             RowMask rmask = RowMask{nullptr, 1u, 1u}) {
   constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
-  auto kernel = softmax_fwd_ring_kernel<T, LOG, GROUP, VPT>;
+  if (rmask.base != nullptr) {
+    if constexpr (!LOG) {  // only the plain softmax has a masked form
+      auto kernel = softmax_fwd_ring_kernel<T, false, GROUP, VPT, true, false>;
+      static std::atomic<uint64_t> done_m{0};
+      if (int e = set_smem_once_sm(kernel, done_m)) return e;
+      ProfileScope prof("masked_softmax_fwd_ring", st);
+      return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
+                        p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+    } else {
+      return B2N_ERR_BAD_ARG;
+    }
+  }
+  if (softmax_safe_mode()) {
+    if constexpr (!LOG) {
+      auto kernel = softmax_fwd_ring_kernel<T, false, GROUP, VPT, false, true>;
+      static std::atomic<uint64_t> done_s{0};
+      if (int e = set_smem_once_sm(kernel, done_s)) return e;
+      ProfileScope prof("safe_softmax_fwd_ring", st);
+      return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
+                        p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+    } else {
+      return B2N_ERR_BAD_ARG;
+    }
+  }
+  auto kernel = softmax_fwd_ring_kernel<T, LOG, GROUP, VPT, false, false>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
-  ProfileScope prof(rmask.base ? "masked_softmax_fwd_ring" : (LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring"), st);
+  ProfileScope prof(LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring", st);
   return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
-                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(),
-                    softmax_safe_mode() ? 1 : 0, rmask);
+                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
 }
 
 template <typename T, bool LOG, int GROUP>
 int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, int64_t M, int64_t N,
                             cudaStream_t st, RowMask rmask = RowMask{nullptr, 1u, 1u}) {
   constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
-  auto kernel = softmax_bwd_ring_kernel<T, LOG, GROUP, VPT>;
+  if (rmask.base != nullptr) {
+    if constexpr (!LOG) {
+      auto kernel = softmax_bwd_ring_kernel<T, false, GROUP, VPT, true>;
+      static std::atomic<uint64_t> done_m{0};
+      if (int e = set_smem_once_sm(kernel, done_m)) return e;
+      ProfileScope prof("masked_softmax_bwd_ring", st);
+      return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, y, dx, M, static_cast<int>(N),
+                        p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+    } else {
+      return B2N_ERR_BAD_ARG;
+    }
+  }
+  auto kernel = softmax_bwd_ring_kernel<T, LOG, GROUP, VPT, false>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
-  ProfileScope prof(rmask.base ? "masked_softmax_bwd_ring" : (LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring"), st);
+  ProfileScope prof(LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring", st);
   return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, y, dx, M, static_cast<int>(N),
                     p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
 }

@@ -48,10 +48,12 @@ template <> struct MaskWord<4> {
   __device__ __forceinline__ bool masked(int e) const { return ((w >> (8 * e)) & 0xffu) != 0u; }
 };
 
-template <typename T, bool LOG, int GROUP, int VPT>
+// MASKED and SAFE (rows of -inf give zeros) are template arguments so that the plain kernels carry none of their
+// registers or branches.
+template <typename T, bool LOG, int GROUP, int VPT, bool MASKED, bool SAFE>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S_lag, int RPG,
-                        int* status, unsigned* tile_ctr, int safe, RowMask mask) {
+                        int* status, unsigned* tile_ctr, RowMask mask) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -92,8 +94,8 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       if (tile_row0 + lr >= M) break;  // uniform over the group
       const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
-      MaskWord<VEC> mw[VPT];
-      if (mask.base != nullptr) {
+      MaskWord<VEC> mw[MASKED ? VPT : 1];
+      if constexpr (MASKED) {
         const unsigned row = static_cast<unsigned>(tile_row0 + lr);
         const unsigned char* mr = mask.base + static_cast<size_t>((row / mask.row_div) % mask.row_mod) * N;
 #pragma unroll
@@ -110,7 +112,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
         const int v = tg + k * GROUP;
         if (v < nvec) {
           P::unpack2(lds128(rbase + v * 16), &xv[k * VH]);
-          if (mask.base != nullptr) {  // masked elements take no part: -inf, which comes out as exactly 0
+          if constexpr (MASKED) {  // masked elements take no part: -inf, which comes out as exactly 0
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
               if (mw[k].masked(2 * e)) xv[k * VH + e].x = ninf;
@@ -156,7 +158,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       const float lg = LOG ? logf(sum[0]) : 0.0f;
       const float2 noff = bcast2(-(mx[0] + lg));  // 16-bit log-softmax: x - (max + log sum) in one add
       const float2 inv = bcast2(LOG ? 0.0f : 1.0f / sum[0]);
-      if (safe && mx[0] == ninf) {
+      if (SAFE && mx[0] == ninf) {
         // safe softmax: a row of -inf gives zeros, not NaN — unless the row holds a NaN, which the
         // maximum cannot see; the row is read again to find out (rare; the branch is uniform over
         // the group, so the reduction inside it is legal)
@@ -209,7 +211,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 
 // stage = [dy tile | y tile]; dx overwrites the dy tile.
 // softmax: dx = y*(dy - sum(y*dy)); log-softmax: dx = dy - exp(y)*sum(dy).
-template <typename T, bool LOG, int GROUP, int VPT>
+template <typename T, bool LOG, int GROUP, int VPT, bool MASKED>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t M,
                         int N, int S_lag, int RPG, int* status, unsigned* tile_ctr, RowMask mask) {
@@ -254,8 +256,8 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
       const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
       const uint32_t ybase = dbase + g.slot_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
-      MaskWord<VEC> mw[VPT];
-      if (mask.base != nullptr) {
+      MaskWord<VEC> mw[MASKED ? VPT : 1];
+      if constexpr (MASKED) {
         const unsigned row = static_cast<unsigned>(tile_row0 + lr);
         const unsigned char* mr = mask.base + static_cast<size_t>((row / mask.row_div) % mask.row_mod) * N;
 #pragma unroll
@@ -273,7 +275,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
         if (v < nvec) {
           P::unpack2(lds128(dbase + v * 16), &dv[k * VH]);
           P::unpack2(lds128(ybase + v * 16), &yv[k * VH]);
-          if (mask.base != nullptr) {  // masked elements take no part in the row sum
+          if constexpr (MASKED) {  // masked elements take no part in the row sum
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
               if (mw[k].masked(2 * e)) { dv[k * VH + e].x = 0.0f; yv[k * VH + e].x = 0.0f; }
@@ -315,7 +317,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
               o[e] = mul2(yy, add2(d, ns));  // y*(dy - sum)
             }
           }
-          if (mask.base != nullptr) {  // exactly zero where masked, whatever the row sum is
+          if constexpr (MASKED) {  // exactly zero where masked, whatever the row sum is
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
               if (mw[k].masked(2 * e)) o[e].x = 0.0f;
