@@ -154,9 +154,9 @@ int softmax_cluster_launch(const ClusterPlan& p, const T* in0, const T* in1, T* 
 }
 
 // Rows of any length: two passes through the ring per row, the second served from L2.
-template <typename T, bool LOG, bool BWD>
-int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_t N, cudaStream_t st) {
-  auto kernel = softmax_twopass_kernel<T, LOG, BWD>;
+template <typename T, bool LOG, bool BWD, bool SAFE>
+int softmax_twopass_launch_as(const T* in0, const T* in1, T* out, int64_t M, int64_t N, cudaStream_t st) {
+  auto kernel = softmax_twopass_kernel<T, LOG, BWD, SAFE>;
   static std::atomic<uint64_t> mask{0};
   if (int e = set_smem_once_sm(kernel, mask)) return e;
   const DeviceInfo& di = device_info();
@@ -170,9 +170,17 @@ int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_
   const int ctas = persistent_ctas(di.sm_count);
   const int grid = static_cast<int>(M < ctas ? M : ctas);
   ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_twopass" : "softmax_bwd_twopass")
-                        : (LOG ? "log_softmax_fwd_twopass" : "softmax_fwd_twopass"), st);
+                        : (LOG ? "log_softmax_fwd_twopass" : (SAFE ? "safe_softmax_fwd_twopass" : "softmax_fwd_twopass")),
+                    st);
   return launch_pdl(kernel, dim3(grid), dim3(kRingBlock), smem, st, in0, in1, out, M, N, static_cast<int>(stages),
-                    device_status_ptr(), next_tile_counter(), softmax_safe_mode() ? 1 : 0);
+                    device_status_ptr(), next_tile_counter());
+}
+template <typename T, bool LOG, bool BWD>
+int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_t N, cudaStream_t st) {
+  if constexpr (!LOG && !BWD) {  // only the plain forward has a safe form
+    if (softmax_safe_mode()) return softmax_twopass_launch_as<T, false, false, true>(in0, in1, out, M, N, st);
+  }
+  return softmax_twopass_launch_as<T, LOG, BWD, false>(in0, in1, out, M, N, st);
 }
 
 template <typename TI, typename TO, bool LOG>

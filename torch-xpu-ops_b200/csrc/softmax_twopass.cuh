@@ -29,10 +29,10 @@ template <typename T> __device__ __forceinline__ float row_exp2p(float d) {
 }
 
 // BWD == false: in0 = x, out = y.   BWD == true: in0 = dy, in1 = y (forward output), out = dx.
-template <typename T, bool LOG, bool BWD>
+template <typename T, bool LOG, bool BWD, bool SAFE>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* __restrict__ out, int64_t M,
-                       int64_t N, int S, int* status, unsigned* tile_ctr, int safe) {
+                       int64_t N, int S, int* status, unsigned* tile_ctr) {
   using P = Pack16<T>;
   constexpr int VEC = P::VEC, VH = VEC / 2;
   constexpr int NIN2 = BWD ? 2 : 1;                 // tensors staged per chunk in pass 2
@@ -235,7 +235,7 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
     const float lg = (!BWD && LOG) ? logf(r1) : 0.0f;
     const float2 noff = bcast2(-(r0 + lg)), inv = bcast2((!BWD && !LOG) ? 1.0f / r1 : 0.0f);
     // safe softmax: a row of -inf gives zeros, not NaN (a NaN in the row has made the sum NaN and still wins)
-    const bool zero_row = !BWD && safe && r0 == ninf && !(r1 != r1);
+    const bool zero_row = SAFE && !BWD && r0 == ninf && !(r1 != r1);
     const float2 l2e = bcast2(kLog2e), c2 = bcast2(-r0 * kLog2e), ns = bcast2(-r0);
     for (int c = 0; c < nch; ++c) {
       ok = mbar_wait(&rs->full[stage], phase, status);
@@ -280,7 +280,8 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
               }
             }
           }
-          sts128(s0 + v * 16, zero_row ? make_uint4(0u, 0u, 0u, 0u) : P::pack2(o));
+          if constexpr (SAFE) sts128(s0 + v * 16, zero_row ? make_uint4(0u, 0u, 0u, 0u) : P::pack2(o));
+          else sts128(s0 + v * 16, P::pack2(o));
         }
       }
       release();
