@@ -48,13 +48,18 @@ template <typename T, typename WT, bool RMS, int GROUP>
 int norm_fwd_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, float* mean,
                          float* rstd, int64_t M, int64_t N, double eps, cudaStream_t st) {
   constexpr int VPT = kNormFwdEpt / Pack16<T>::VEC;
-  auto kernel = norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT>;
-  static std::atomic<uint64_t> mask{0};
-  if (int e = set_smem_once(kernel, p.smem, mask)) return e;
   ProfileScope prof(RMS ? "rms_norm_fwd_ring" : "layer_norm_fwd_ring", st);
-  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, gamma, beta, y, mean, rstd, M,
-                    static_cast<int>(N), static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg, device_status_ptr(),
-                    next_tile_counter(), ring_tuning().trace_buf, ring_tuning().trace_cap);
+  auto go = [&](auto kernel, std::atomic<uint64_t>& done) -> int {
+    if (int e = set_smem_once(kernel, p.smem, done)) return e;
+    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, gamma, beta, y, mean, rstd, M,
+                      static_cast<int>(N), static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg,
+                      device_status_ptr(), next_tile_counter(), ring_tuning().trace_buf, ring_tuning().trace_cap);
+  };
+  static std::atomic<uint64_t> done[2];
+  // rows that fill every thread's vectors exactly take the instantiation without range checks
+  if (N == static_cast<int64_t>(GROUP) * VPT * Pack16<T>::VEC)
+    return go(norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT, true>, done[0]);
+  return go(norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT, false>, done[1]);
 }
 
 template <typename T, typename WT, bool RMS>
@@ -135,22 +140,25 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
                          const float* rstd, const WT* gamma, T* dx, float* ws, int64_t M, int64_t N,
                          cudaStream_t st) {
   constexpr int VPT = kNormBwdEpt / Pack16<T>::VEC;
-  static std::atomic<uint64_t> mask_w{0}, mask_n{0};
   ProfileScope prof(RMS ? "rms_norm_bwd_ring" : "layer_norm_bwd_ring", st);
+  const bool full = N == static_cast<int64_t>(GROUP) * VPT * Pack16<T>::VEC;
+  const int s_lag = p.stages | (p.lag << 8);
+  const int n = static_cast<int>(N);
+  // fixed tile assignment (no counter) with weight gradients: the partial sums a CTA forms, and with them
+  // dgamma/dbeta, are then the same bits on every run
+  unsigned* ctr = wgrad ? nullptr : next_tile_counter();
+  auto go = [&](auto kernel, std::atomic<uint64_t>& done) -> int {
+    if (int e = set_smem_once(kernel, p.smem, done)) return e;
+    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, M, n, s_lag,
+                      p.rpg, device_status_ptr(), ctr);
+  };
+  static std::atomic<uint64_t> done[4];
   if (wgrad) {
-    auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true>;
-    if (int e = set_smem_once(kernel, p.smem, mask_w)) return e;
-    // fixed tile assignment (no counter): the partial sums a CTA forms, and with them dgamma/dbeta, are then
-    // the same bits on every run
-    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, M,
-                      static_cast<int>(N), p.stages | (p.lag << 8), p.rpg, device_status_ptr(),
-                      static_cast<unsigned*>(nullptr));
-  } else {
-    auto kernel = norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false>;
-    if (int e = set_smem_once(kernel, p.smem, mask_n)) return e;
-    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, M,
-                      static_cast<int>(N), p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter());
+    if (full) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, true>, done[0]);
+    return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, false>, done[1]);
   }
+  if (full) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, true>, done[2]);
+  return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, false>, done[3]);
 }
 
 template <typename T, typename WT, bool RMS>

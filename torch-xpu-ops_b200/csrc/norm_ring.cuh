@@ -34,7 +34,8 @@ __device__ __forceinline__ void load_weights(const WT* __restrict__ w, float fil
 
 constexpr int kTraceTid = 160;  // the consumer thread that writes trace records (lane 0 of warp 5)
 
-template <typename T, typename WT, bool RMS, int GROUP, int VPT>
+// FULL: the row fills every thread's vectors exactly (N == GROUP * VPT * VEC), so no access needs a range check.
+template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool FULL>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta,
                      T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t M,
@@ -114,7 +115,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
-          if (valid[b] && v < nvec) {
+          if (valid[b] && (FULL || v < nvec)) {
             P::unpack2(lds128(rbase[b] + v * 16), &xv[b][k * VH]);
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
@@ -176,7 +177,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
               const int v = tg + k * GROUP;
-              if (valid[b] && v < nvec) {
+              if (valid[b] && (FULL || v < nvec)) {
                 P::unpack2(lds128(rbase[b] + v * 16), &xv[b][k * VH]);
 #pragma unroll
                 for (int e = 0; e < VH; ++e) {
@@ -211,7 +212,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
-          if (v < nvec) {
+          if (FULL || v < nvec) {
             float2 o[VH];
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
@@ -242,7 +243,8 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 //
 // Per row: s1 = sum(gamma*dy), s2 = sum(gamma*dy*xhat), xhat = (x - mean) * rstd,
 // dx = rstd * (gamma*dy - (xhat*s2 + s1)/N)   (RMS: mean = 0, s1 = 0).
-template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD>
+// FULL: the row fills every thread's vectors exactly (N == GROUP * VPT * VEC), so no access needs a range check.
+template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD, bool FULL>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx,
@@ -299,12 +301,15 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     mu = (!RMS && ok) ? __ldg(mean + row0 + b) : 0.0f;
     rsd = ok ? __ldg(rstd + row0 + b) : 0.0f;
   };
-  const bool fixed = tile_ctr == nullptr;  // fixed assignment: this CTA's k-th tile is blockIdx.x + k * gridDim.x
+  // fixed assignment (this CTA's k-th tile is blockIdx.x + k * gridDim.x) exactly when weight gradients are
+  // accumulated: the launcher passes no tile counter then.  A compile-time fact, so that each instantiation
+  // carries only its own way of finding the next tile's statistics.
+  constexpr bool fixed = WGRAD;
   unsigned k_tile = 0;
   for (;; cur.advance(g), ++k_tile) {
     float mu_n = 0.0f, rs_n = 0.0f;
     int id_n = -1;
-    if (fixed) {  // the next tile is known: fetch its statistics a whole tile ahead
+    if constexpr (fixed) {  // the next tile is known: fetch its statistics a whole tile ahead
       const unsigned t = blockIdx.x + (k_tile + 1) * gridDim.x;
       id_n = t < g.ntiles ? static_cast<int>(t) : -1;
       if (id_n >= 0) load_stats(g.first_row(id_n) + grp * RPG, mu_n, rs_n);
@@ -334,7 +339,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
-        if (v < nvec) {
+        if (FULL || v < nvec) {
           float2 dv[VH];
           P::unpack2(lds128(dbase + v * 16), dv);
           P::unpack2(lds128(xbase + v * 16), &xh[k * VH]);
@@ -371,7 +376,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
-        if (v < nvec) {
+        if (FULL || v < nvec) {
           float2 o[VH];
 #pragma unroll
           for (int e = 0; e < VH; ++e) {
@@ -381,7 +386,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
           sts128(dbase + v * 16, P::pack2(o));
         }
       }
-      if (!fixed && r == 0) {  // by now the producer has normally named the next stage's tile
+      if (!fixed && r == 0) {  // (dynamic assignment only) by now the producer has normally named the next stage's tile
         id_n = ring_peek_tile(rs, cur.next_stage(g));
         if (id_n >= 0) load_stats(g.first_row(id_n) + grp * RPG, mu_n, rs_n);
       }
@@ -399,7 +404,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int v = tg + k * GROUP;
-      if (v < nvec) {
+      if (FULL || v < nvec) {
 #pragma unroll
         for (int q = 0; q < VEC / 4; ++q) {
           const int j = (k * VEC + q * 4) / 2;

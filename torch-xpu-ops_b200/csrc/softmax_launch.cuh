@@ -37,60 +37,59 @@ template <typename T, bool LOG, int GROUP>
 int softmax_fwd_ring_launch(const RingPlan& p, const T* x, T* y, int64_t M, int64_t N, cudaStream_t st,
                             RowMask rmask = RowMask{nullptr, 1u, 1u}) {
   constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
+  // rows that fill every thread's vectors exactly take the instantiations without range checks
+  const bool full = N == static_cast<int64_t>(GROUP) * VPT * Pack16<T>::VEC;
+  auto go = [&](auto kernel, std::atomic<uint64_t>& done, const char* name) -> int {
+    if (int e = set_smem_once_sm(kernel, done)) return e;
+    ProfileScope prof(name, st);
+    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
+                      p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+  };
+  static std::atomic<uint64_t> done[6];
   if (rmask.base != nullptr) {
     if constexpr (!LOG) {  // only the plain softmax has a masked form
-      auto kernel = softmax_fwd_ring_kernel<T, false, GROUP, VPT, true, false>;
-      static std::atomic<uint64_t> done_m{0};
-      if (int e = set_smem_once_sm(kernel, done_m)) return e;
-      ProfileScope prof("masked_softmax_fwd_ring", st);
-      return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
-                        p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+      if (full) return go(softmax_fwd_ring_kernel<T, false, GROUP, VPT, true, false, true>, done[0], "masked_softmax_fwd_ring");
+      return go(softmax_fwd_ring_kernel<T, false, GROUP, VPT, true, false, false>, done[1], "masked_softmax_fwd_ring");
     } else {
       return B2N_ERR_BAD_ARG;
     }
   }
   if (softmax_safe_mode()) {
-    if constexpr (!LOG) {
-      auto kernel = softmax_fwd_ring_kernel<T, false, GROUP, VPT, false, true>;
-      static std::atomic<uint64_t> done_s{0};
-      if (int e = set_smem_once_sm(kernel, done_s)) return e;
-      ProfileScope prof("safe_softmax_fwd_ring", st);
-      return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
-                        p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+    if constexpr (!LOG) {  // ... and a safe form (rows of -inf give zeros)
+      if (full) return go(softmax_fwd_ring_kernel<T, false, GROUP, VPT, false, true, true>, done[2], "safe_softmax_fwd_ring");
+      return go(softmax_fwd_ring_kernel<T, false, GROUP, VPT, false, true, false>, done[3], "safe_softmax_fwd_ring");
     } else {
       return B2N_ERR_BAD_ARG;
     }
   }
-  auto kernel = softmax_fwd_ring_kernel<T, LOG, GROUP, VPT, false, false>;
-  static std::atomic<uint64_t> mask{0};
-  if (int e = set_smem_once_sm(kernel, mask)) return e;
-  ProfileScope prof(LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring", st);
-  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, y, M, static_cast<int>(N),
-                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+  const char* name = LOG ? "log_softmax_fwd_ring" : "softmax_fwd_ring";
+  if (full) return go(softmax_fwd_ring_kernel<T, LOG, GROUP, VPT, false, false, true>, done[4], name);
+  return go(softmax_fwd_ring_kernel<T, LOG, GROUP, VPT, false, false, false>, done[5], name);
 }
 
 template <typename T, bool LOG, int GROUP>
 int softmax_bwd_ring_launch(const RingPlan& p, const T* dy, const T* y, T* dx, int64_t M, int64_t N,
                             cudaStream_t st, RowMask rmask = RowMask{nullptr, 1u, 1u}) {
   constexpr int VPT = kSoftmaxEpt / Pack16<T>::VEC;
+  const bool full = N == static_cast<int64_t>(GROUP) * VPT * Pack16<T>::VEC;
+  auto go = [&](auto kernel, std::atomic<uint64_t>& done, const char* name) -> int {
+    if (int e = set_smem_once_sm(kernel, done)) return e;
+    ProfileScope prof(name, st);
+    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, y, dx, M, static_cast<int>(N),
+                      p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+  };
+  static std::atomic<uint64_t> done[4];
   if (rmask.base != nullptr) {
     if constexpr (!LOG) {
-      auto kernel = softmax_bwd_ring_kernel<T, false, GROUP, VPT, true>;
-      static std::atomic<uint64_t> done_m{0};
-      if (int e = set_smem_once_sm(kernel, done_m)) return e;
-      ProfileScope prof("masked_softmax_bwd_ring", st);
-      return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, y, dx, M, static_cast<int>(N),
-                        p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+      if (full) return go(softmax_bwd_ring_kernel<T, false, GROUP, VPT, true, true>, done[0], "masked_softmax_bwd_ring");
+      return go(softmax_bwd_ring_kernel<T, false, GROUP, VPT, true, false>, done[1], "masked_softmax_bwd_ring");
     } else {
       return B2N_ERR_BAD_ARG;
     }
   }
-  auto kernel = softmax_bwd_ring_kernel<T, LOG, GROUP, VPT, false>;
-  static std::atomic<uint64_t> mask{0};
-  if (int e = set_smem_once_sm(kernel, mask)) return e;
-  ProfileScope prof(LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring", st);
-  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, y, dx, M, static_cast<int>(N),
-                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter(), rmask);
+  const char* name = LOG ? "log_softmax_bwd_ring" : "softmax_bwd_ring";
+  if (full) return go(softmax_bwd_ring_kernel<T, LOG, GROUP, VPT, false, true>, done[2], name);
+  return go(softmax_bwd_ring_kernel<T, LOG, GROUP, VPT, false, false>, done[3], name);
 }
 
 // Rows too long for the ring: a row is split over a cluster of C CTAs (C = 1, 2, 4 or 8, one CTA per

@@ -50,7 +50,8 @@ template <> struct MaskWord<4> {
 
 // MASKED and SAFE (rows of -inf give zeros) are template arguments so that the plain kernels carry none of their
 // registers or branches.
-template <typename T, bool LOG, int GROUP, int VPT, bool MASKED, bool SAFE>
+// FULL: the row fills every thread's vectors exactly (N == GROUP * VPT * VEC): no range checks.
+template <typename T, bool LOG, int GROUP, int VPT, bool MASKED, bool SAFE, bool FULL>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int N, int S_lag, int RPG,
                         int* status, unsigned* tile_ctr, RowMask mask) {
@@ -101,7 +102,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
-          if (v < nvec) mw[k].load(mr + v * VEC);
+          if (FULL || v < nvec) mw[k].load(mr + v * VEC);
           else mw[k].clear();
         }
       }
@@ -110,7 +111,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
-        if (v < nvec) {
+        if (FULL || v < nvec) {
           P::unpack2(lds128(rbase + v * 16), &xv[k * VH]);
           if constexpr (MASKED) {  // masked elements take no part: -inf, which comes out as exactly 0
 #pragma unroll
@@ -137,7 +138,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       float2 ps[2] = {bcast2(0.0f), bcast2(0.0f)};
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        if (tg + k * GROUP < nvec) {
+        if (FULL || tg + k * GROUP < nvec) {
 #pragma unroll
           for (int e = 0; e < VH; ++e) {
             const int j = k * VH + e;
@@ -166,7 +167,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
-          if (v < nvec) {
+          if (FULL || v < nvec) {
             float2 f[VH];
             P::unpack2(lds128(rbase + v * 16), f);
 #pragma unroll
@@ -179,7 +180,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 #pragma unroll
           for (int k = 0; k < VPT; ++k) {
             const int v = tg + k * GROUP;
-            if (v < nvec) sts128(rbase + v * 16, make_uint4(0u, 0u, 0u, 0u));
+            if (FULL || v < nvec) sts128(rbase + v * 16, make_uint4(0u, 0u, 0u, 0u));
           }
           continue;
         }
@@ -187,7 +188,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
-        if (v < nvec) {
+        if (FULL || v < nvec) {
           float2 o[VH];
 #pragma unroll
           for (int e = 0; e < VH; ++e) {
@@ -211,7 +212,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
 
 // stage = [dy tile | y tile]; dx overwrites the dy tile.
 // softmax: dx = y*(dy - sum(y*dy)); log-softmax: dx = dy - exp(y)*sum(dy).
-template <typename T, bool LOG, int GROUP, int VPT, bool MASKED>
+template <typename T, bool LOG, int GROUP, int VPT, bool MASKED, bool FULL>
 __global__ void __launch_bounds__(kRingBlock, 1)
 softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t M,
                         int N, int S_lag, int RPG, int* status, unsigned* tile_ctr, RowMask mask) {
@@ -263,7 +264,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
-          if (v < nvec) mw[k].load(mr + v * VEC);
+          if (FULL || v < nvec) mw[k].load(mr + v * VEC);
           else mw[k].clear();
         }
       }
@@ -272,7 +273,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
-        if (v < nvec) {
+        if (FULL || v < nvec) {
           P::unpack2(lds128(dbase + v * 16), &dv[k * VH]);
           P::unpack2(lds128(ybase + v * 16), &yv[k * VH]);
           if constexpr (MASKED) {  // masked elements take no part in the row sum
@@ -299,7 +300,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
-        if (v < nvec) {
+        if (FULL || v < nvec) {
           float2 o[VH];
 #pragma unroll
           for (int e = 0; e < VH; ++e) {
