@@ -75,3 +75,30 @@ def test_product_does_not_import_the_oracle():
         if re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M) or "oracle/" in text:
             offenders.append(str(path))
     assert not offenders, offenders
+
+
+def test_tuning_and_path_setters_validate_their_arguments():
+    # host-side state only: no CUDA call is made
+    lib = b200norm.load_library()
+    for knob in (b200norm.TUNE_ROWS_PER_GROUP, b200norm.TUNE_STAGES, b200norm.TUNE_STORE_LAG,
+                 b200norm.TUNE_CLUSTER_SIZE, b200norm.TUNE_SM_MARGIN):
+        assert lib.b2n_set_tuning(knob, 2) == 0
+        assert lib.b2n_set_tuning(knob, 0) == 0
+        assert lib.b2n_set_tuning(knob, -1) == b200norm.ERR_BAD_ARG
+    assert lib.b2n_set_tuning(99, 1) == b200norm.ERR_BAD_ARG
+    prev = lib.b2n_set_path(b200norm.PATH_GENERIC)
+    assert lib.b2n_set_path(1234) == b200norm.PATH_GENERIC   # an unknown family is ignored: the setting stays
+    assert lib.b2n_set_path(prev) == b200norm.PATH_GENERIC
+
+
+def test_entry_points_reject_bad_arguments_before_touching_the_device():
+    lib = b200norm.load_library()
+    bad = b200norm.ERR_BAD_ARG
+    assert lib.b2n_layer_norm_fwd(None, None, None, None, None, None, -1, 8, 1e-5, 0, 0, None) == bad
+    assert lib.b2n_layer_norm_fwd(None, None, None, None, None, None, 4, 8, 1e-5, 17, 0, None) == bad
+    assert lib.b2n_layer_norm_fwd(None, None, None, None, None, None, 0, 8, 1e-5, 0, 0, None) == 0  # empty batch
+    assert lib.b2n_softmax_fwd(None, None, 2, 4, 1, 0, 0, 3, None) == bad          # mode beyond safe softmax
+    assert lib.b2n_softmax_fwd(None, None, 2, 4, 1, 0, 0, 0, None) == bad          # null pointers
+    assert lib.b2n_masked_softmax_fwd(None, None, None, 2, 4, 0, 1, 0, None) == bad  # row_div < 1
+    assert lib.b2n_cross_entropy_bwd(None, None, None, None, None, None, 3, 5, 7, -100, 0, 0, None) == bad  # reduction
+    assert lib.b2n_cross_entropy_bwd(None, None, None, None, None, None, 0, 5, 1, -100, 0, 0, None) == 0

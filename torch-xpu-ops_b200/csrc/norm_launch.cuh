@@ -55,11 +55,14 @@ int norm_fwd_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const W
                       static_cast<int>(N), static_cast<float>(eps), p.stages | (p.lag << 8), p.rpg,
                       device_status_ptr(), next_tile_counter(), ring_tuning().trace_buf, ring_tuning().trace_cap);
   };
-  static std::atomic<uint64_t> done[2];
+  static std::atomic<uint64_t> done[3];
   // rows that fill every thread's vectors exactly take the instantiation without range checks
-  if (N == static_cast<int64_t>(GROUP) * VPT * Pack16<T>::VEC)
-    return go(norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT, true>, done[0]);
-  return go(norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT, false>, done[1]);
+  // ... and, when the planner chose the usual four rows per group per tile, with that count compiled in
+  if (N == static_cast<int64_t>(GROUP) * VPT * Pack16<T>::VEC) {
+    if (p.rpg == 4) return go(norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, 4>, done[2]);
+    return go(norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, 0>, done[0]);
+  }
+  return go(norm_fwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, 0>, done[1]);
 }
 
 template <typename T, typename WT, bool RMS>
@@ -152,13 +155,15 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
     return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, M, n, s_lag,
                       p.rpg, device_status_ptr(), ctr);
   };
-  static std::atomic<uint64_t> done[4];
+  static std::atomic<uint64_t> done[6];
   if (wgrad) {
-    if (full) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, true>, done[0]);
-    return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, false>, done[1]);
+    if (full && p.rpg == 2) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, true, 2>, done[4]);
+    if (full) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, true, 0>, done[0]);
+    return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, true, false, 0>, done[1]);
   }
-  if (full) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, true>, done[2]);
-  return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, false>, done[3]);
+  if (full && p.rpg == 2) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, true, 2>, done[5]);
+  if (full) return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, true, 0>, done[2]);
+  return go(norm_bwd_ring_kernel<T, WT, RMS, GROUP, VPT, false, false, 0>, done[3]);
 }
 
 template <typename T, typename WT, bool RMS>

@@ -35,13 +35,15 @@ __device__ __forceinline__ void load_weights(const WT* __restrict__ w, float fil
 constexpr int kTraceTid = 160;  // the consumer thread that writes trace records (lane 0 of warp 5)
 
 // FULL: the row fills every thread's vectors exactly (N == GROUP * VPT * VEC), so no access needs a range check.
-template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool FULL>
+// RPGT: rows per group per tile as a compile-time constant (0: taken from the launch argument).
+template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool FULL, int RPGT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta,
                      T* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int64_t M,
-                     int N, float eps, int S_lag, int RPG, int* status, unsigned* tile_ctr,
+                     int N, float eps, int S_lag, int rpg_arg, int* status, unsigned* tile_ctr,
                      unsigned long long* trace_buf, unsigned trace_cap) {
   using P = Pack16<T>;
+  const int RPG = RPGT > 0 ? RPGT : rpg_arg;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   constexpr int RB = 2;  // rows a group works on at once
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -88,6 +90,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
     // A group takes its rows of the tile RB at a time: the partial sums of RB rows go through ONE
     // group reduction (one barrier, RB values), which halves the time the group's warps spend
     // waiting on each other when a single group spans the whole CTA.
+#pragma unroll(RPGT > 0 ? RPGT : 1)
     for (int r = 0; r < RPG; r += RB) {
       const int lr0 = grp * RPG + r;
       const int64_t row_a = tile_row0 + lr0;
@@ -244,13 +247,15 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 // Per row: s1 = sum(gamma*dy), s2 = sum(gamma*dy*xhat), xhat = (x - mean) * rstd,
 // dx = rstd * (gamma*dy - (xhat*s2 + s1)/N)   (RMS: mean = 0, s1 = 0).
 // FULL: the row fills every thread's vectors exactly (N == GROUP * VPT * VEC), so no access needs a range check.
-template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD, bool FULL>
+// RPGT: rows per group per tile as a compile-time constant (0: taken from the launch argument).
+template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD, bool FULL, int RPGT>
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx,
-                     float* __restrict__ ws, int64_t M, int N, int S_lag, int RPG, int* status,
+                     float* __restrict__ ws, int64_t M, int N, int S_lag, int rpg_arg, int* status,
                      unsigned* tile_ctr) {
   using P = Pack16<T>;
+  const int RPG = RPGT > 0 ? RPGT : rpg_arg;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   RingShared* rs = reinterpret_cast<RingShared*>(smem_raw);
@@ -319,6 +324,7 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     const int64_t row_first = g.first_row(i) + grp * RPG;
     if (i != id_c) load_stats(row_first, mu_c, rs_c);  // first tile, or the hint was stale (uniform over a warp)
     const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
+#pragma unroll(RPGT > 0 ? RPGT : 1)
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
       const int64_t row = row_first + r;
