@@ -16,6 +16,7 @@
 // 32 KB of a row per stage; a persistent CTA takes whole rows (handed out dynamically) so the
 // per-row scalars (target, scale) are fetched once per row.  dx may alias logp.
 #include <atomic>
+#include <type_traits>
 
 #include "launchers.h"
 #include "plan.h"
@@ -176,34 +177,40 @@ ce_bwd_ring_kernel(const T* __restrict__ logp, const void* __restrict__ target, 
       const int cv = chunk_vecs(c);
       const uint32_t s0 = stages_u32 + static_cast<uint32_t>(stage) * kStageBytes;
       const int64_t tv_local = tv - static_cast<int64_t>(c) * kCeChunkVecs;  // target vector within this chunk
+      // chunks of the full size (all but a row's last) run the copy of the loop without range checks
+      auto run_chunk = [&](auto full_chunk) {
+        constexpr bool FC = decltype(full_chunk)::value;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        const int v = tid + k * kRingThreads;
-        if (v < cv) {
-          float2 f[VH], o[VH];
-          P::unpack2(lds128(s0 + v * 16), f);
-#pragma unroll
-          for (int e = 0; e < VH; ++e) {
-            float2 ey;
-            if constexpr (sizeof(T) == 4) {
-              ey = make_float2(expf(f[e].x), expf(f[e].y));
-            } else {
-              const float2 tt = mul2(f[e], l2e);
-              ey = make_float2(ex2_approx(tt.x), ex2_approx(tt.y));
-            }
-            o[e] = mul2(ey, s2);
-          }
-          if (v == tv_local) {  // one vector per row: s * (exp(y) - 1) at the target column
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tid + k * kRingThreads;
+          if (FC || v < cv) {
+            float2 f[VH], o[VH];
+            P::unpack2(lds128(s0 + v * 16), f);
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
-              const float yx = f[e].x, yy = f[e].y;
-              if (2 * e == te) o[e].x = s * ((sizeof(T) == 4 ? expf(yx) : ex2_approx(yx * kLog2e)) - 1.0f);
-              if (2 * e + 1 == te) o[e].y = s * ((sizeof(T) == 4 ? expf(yy) : ex2_approx(yy * kLog2e)) - 1.0f);
+              float2 ey;
+              if constexpr (sizeof(T) == 4) {
+                ey = make_float2(expf(f[e].x), expf(f[e].y));
+              } else {
+                const float2 tt = mul2(f[e], l2e);
+                ey = make_float2(ex2_approx(tt.x), ex2_approx(tt.y));
+              }
+              o[e] = mul2(ey, s2);
             }
+            if (v == tv_local) {  // one vector per row: s * (exp(y) - 1) at the target column
+#pragma unroll
+              for (int e = 0; e < VH; ++e) {
+                const float yx = f[e].x, yy = f[e].y;
+                if (2 * e == te) o[e].x = s * ((sizeof(T) == 4 ? expf(yx) : ex2_approx(yx * kLog2e)) - 1.0f);
+                if (2 * e + 1 == te) o[e].y = s * ((sizeof(T) == 4 ? expf(yy) : ex2_approx(yy * kLog2e)) - 1.0f);
+              }
+            }
+            sts128(s0 + v * 16, P::pack2(o));
           }
-          sts128(s0 + v * 16, P::pack2(o));
         }
-      }
+      };
+      if (cv == kCeChunkVecs) run_chunk(std::true_type{});
+      else run_chunk(std::false_type{});
       fence_async_smem();
       __syncwarp();
       if ((tid & 31) == 0) mbar_arrive(&rs->done[stage]);

@@ -69,8 +69,11 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
   ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
-  const int nvec = N / VEC;
-  const float inv_n = 1.0f / static_cast<float>(N);
+  // FULL rows have a compile-time length, and with it compile-time byte offsets
+  const int nvec = FULL ? GROUP * VPT : N / VEC;
+  const float inv_n = 1.0f / static_cast<float>(FULL ? GROUP * VPT * VEC : N);
+  const uint32_t row_bytes = FULL ? static_cast<uint32_t>(GROUP * VPT * 16) : g.row_bytes;
+  const uint32_t stage_bytes = (FULL && RPGT > 0) ? static_cast<uint32_t>(NG * RPGT) * row_bytes : g.stage_bytes;
   constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
   float2 gw[HP], gb[HP];
   load_weights<WT, GROUP, VPT, VEC>(gamma, 1.0f, nvec, tg, gw);
@@ -86,7 +89,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
     if (!ring_consumer_wait(rs, cur, status, i) || i < 0) break;
     const int64_t tile_row0 = g.first_row(i);
     if (tid == kTraceTid) g.trace.put(0, tk, EV_C_WAIT_END, i);
-    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
+    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * stage_bytes;
     // A group takes its rows of the tile RB at a time: the partial sums of RB rows go through ONE
     // group reduction (one barrier, RB values), which halves the time the group's warps spend
     // waiting on each other when a single group spans the whole CTA.
@@ -103,7 +106,7 @@ norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
       for (int b = 0; b < RB; ++b) {
         valid[b] = (r + b < RPG) && (row_a + b < M);
-        rbase[b] = sbase + static_cast<uint32_t>(lr0 + b) * g.row_bytes;
+        rbase[b] = sbase + static_cast<uint32_t>(lr0 + b) * row_bytes;
         // Layer norm works on d = x - shift, shift = the row's first element (a shared-memory
         // broadcast read): a large common offset then cancels exactly instead of being rounded
         // away in the row sums.  RMS norm needs the raw values (shift = 0).
@@ -279,8 +282,12 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
   ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
-  const int nvec = N / VEC;
-  const float inv_n = 1.0f / static_cast<float>(N);
+  // FULL rows have a compile-time length, and with it compile-time byte offsets
+  const int nvec = FULL ? GROUP * VPT : N / VEC;
+  const float inv_n = 1.0f / static_cast<float>(FULL ? GROUP * VPT * VEC : N);
+  const uint32_t row_bytes = FULL ? static_cast<uint32_t>(GROUP * VPT * 16) : g.row_bytes;
+  const uint32_t slot_bytes = (FULL && RPGT > 0) ? static_cast<uint32_t>(NG * RPGT) * row_bytes : g.slot_bytes;
+  const uint32_t stage_bytes = 2u * slot_bytes;
   constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
   float2 gw[HP], dg[HP], db[HP];
   load_weights<WT, GROUP, VPT, VEC>(gamma, 1.0f, nvec, tg, gw);
@@ -323,14 +330,14 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     if (!ring_consumer_wait(rs, cur, status, i) || i < 0) break;
     const int64_t row_first = g.first_row(i) + grp * RPG;
     if (i != id_c) load_stats(row_first, mu_c, rs_c);  // first tile, or the hint was stale (uniform over a warp)
-    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
+    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * stage_bytes;
 #pragma unroll(RPGT > 0 ? RPGT : 1)
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
       const int64_t row = row_first + r;
       if (row >= M) break;  // uniform over the group
-      const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
-      const uint32_t xbase = dbase + g.slot_bytes;
+      const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * row_bytes;
+      const uint32_t xbase = dbase + slot_bytes;
       float mu, rsd;
       if (r < 2) {
         mu = __shfl_sync(0xffffffffu, mu_c, r);

@@ -78,7 +78,8 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
   ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
-  const int nvec = N / VEC;
+  const int nvec = FULL ? GROUP * VPT : N / VEC;  // FULL rows have a compile-time length
+  const uint32_t row_bytes = FULL ? static_cast<uint32_t>(GROUP * VPT * 16) : g.row_bytes;
   int red_phase = 0;
   const float ninf = acc_neg_inf<float>();
   const uint32_t stages_u32 = smem_u32(stages);
@@ -93,7 +94,7 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
       if (tile_row0 + lr >= M) break;  // uniform over the group
-      const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
+      const uint32_t rbase = sbase + static_cast<uint32_t>(lr) * row_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
       MaskWord<VEC> mw[MASKED ? VPT : 1];
       if constexpr (MASKED) {
@@ -240,7 +241,8 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
   ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
-  const int nvec = N / VEC;
+  const int nvec = FULL ? GROUP * VPT : N / VEC;  // FULL rows have a compile-time length
+  const uint32_t row_bytes = FULL ? static_cast<uint32_t>(GROUP * VPT * 16) : g.row_bytes;
   int red_phase = 0;
   const uint32_t stages_u32 = smem_u32(stages);
 
@@ -254,7 +256,7 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
     for (int r = 0; r < RPG; ++r) {
       const int lr = grp * RPG + r;
       if (tile_row0 + lr >= M) break;  // uniform over the group
-      const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * g.row_bytes;
+      const uint32_t dbase = sbase + static_cast<uint32_t>(lr) * row_bytes;
       const uint32_t ybase = dbase + g.slot_bytes;
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
       MaskWord<VEC> mw[MASKED ? VPT : 1];

@@ -13,6 +13,8 @@
 // Same roles as the other ring kernels (ring.cuh): 16 consumer warps, one producer warpgroup that
 // gives its registers to the consumers, every wait an mbarrier wait with a time limit.
 #pragma once
+#include <type_traits>
+
 #include "ring.cuh"
 #include "softmax_generic.cuh"
 #include "softmax_ring.cuh"
@@ -170,46 +172,52 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
       if (!ok) break;
       const int cv = chunk_vecs(c);
       const uint32_t s0 = stages_u32 + static_cast<uint32_t>(stage) * kStageBytes, s1 = s0 + kChunkBytes;
+      // chunks of the full size (all but a row's last) run the copy of the loop without range checks
+      auto run_chunk = [&](auto full_chunk) {
+        constexpr bool FC = decltype(full_chunk)::value;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        const int v = tid + k * kRingThreads;
-        if (v < cv) {
-          float2 f[VH];
-          P::unpack2(lds128(s0 + v * 16), f);
-          if constexpr (!BWD) {
-            float vm = ninf;
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tid + k * kRingThreads;
+          if (FC || v < cv) {
+            float2 f[VH];
+            P::unpack2(lds128(s0 + v * 16), f);
+            if constexpr (!BWD) {
+              float vm = ninf;
 #pragma unroll
-            for (int e = 0; e < VH; ++e) vm = fmaxf(vm, fmaxf(f[e].x, f[e].y));
-            // one rescale per 16-byte vector instead of one per element
-            const float nm = fmaxf(pm, vm);
-            const float scale = (pm == ninf) ? 0.0f : row_exp2p<T>(pm - nm);
-            const float base = (nm == ninf) ? 0.0f : nm;  // all -inf so far: exp(-inf - 0) = 0; NaN stays NaN
-            float2 a = bcast2(0.0f);
-            if constexpr (sizeof(T) == 4) {
+              for (int e = 0; e < VH; ++e) vm = fmaxf(vm, fmaxf(f[e].x, f[e].y));
+              // one rescale per 16-byte vector instead of one per element
+              const float nm = fmaxf(pm, vm);
+              const float scale = (pm == ninf) ? 0.0f : row_exp2p<T>(pm - nm);
+              const float base = (nm == ninf) ? 0.0f : nm;  // all -inf so far: exp(-inf - 0) = 0; NaN stays NaN
+              float2 a = bcast2(0.0f);
+              if constexpr (sizeof(T) == 4) {
 #pragma unroll
-              for (int e = 0; e < VH; ++e) a = add2(a, make_float2(expf(f[e].x - base), expf(f[e].y - base)));
-            } else {
-              // 2^(x*log2e - base*log2e): one packed FMA per pair, then the hardware 2^x
-              const float2 l2e = bcast2(kLog2e), nb = bcast2(-base * kLog2e);
+                for (int e = 0; e < VH; ++e) a = add2(a, make_float2(expf(f[e].x - base), expf(f[e].y - base)));
+              } else {
+                // 2^(x*log2e - base*log2e): one packed FMA per pair, then the hardware 2^x
+                const float2 l2e = bcast2(kLog2e), nb = bcast2(-base * kLog2e);
 #pragma unroll
-              for (int e = 0; e < VH; ++e) {
-                const float2 tt = fma2(f[e], l2e, nb);
-                a = add2(a, make_float2(ex2_approx(tt.x), ex2_approx(tt.y)));
+                for (int e = 0; e < VH; ++e) {
+                  const float2 tt = fma2(f[e], l2e, nb);
+                  a = add2(a, make_float2(ex2_approx(tt.x), ex2_approx(tt.y)));
+                }
               }
+              ps = fmaf(ps, scale, hsum2(a));
+              pm = nm;
+            } else if constexpr (LOG) {
+#pragma unroll
+              for (int e = 0; e < VH; ++e) acc2[e & 1] = add2(acc2[e & 1], f[e]);
+            } else {
+              float2 yv[VH];
+              P::unpack2(lds128(s1 + v * 16), yv);
+#pragma unroll
+              for (int e = 0; e < VH; ++e) acc2[e & 1] = fma2(f[e], yv[e], acc2[e & 1]);
             }
-            ps = fmaf(ps, scale, hsum2(a));
-            pm = nm;
-          } else if constexpr (LOG) {
-#pragma unroll
-            for (int e = 0; e < VH; ++e) acc2[e & 1] = add2(acc2[e & 1], f[e]);
-          } else {
-            float2 yv[VH];
-            P::unpack2(lds128(s1 + v * 16), yv);
-#pragma unroll
-            for (int e = 0; e < VH; ++e) acc2[e & 1] = fma2(f[e], yv[e], acc2[e & 1]);
           }
         }
-      }
+      };
+      if (cv == kTwoPassChunkVecs) run_chunk(std::true_type{});
+      else run_chunk(std::false_type{});
       release();
       next_stage();
     }
@@ -242,48 +250,54 @@ softmax_twopass_kernel(const T* __restrict__ in0, const T* __restrict__ in1, T* 
       if (!ok) break;
       const int cv = chunk_vecs(c);
       const uint32_t s0 = stages_u32 + static_cast<uint32_t>(stage) * kStageBytes, s1 = s0 + kChunkBytes;
+      // chunks of the full size (all but a row's last) run the copy of the loop without range checks
+      auto run_chunk = [&](auto full_chunk) {
+        constexpr bool FC = decltype(full_chunk)::value;
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        const int v = tid + k * kRingThreads;
-        if (v < cv) {
-          float2 f[VH], o[VH];
-          P::unpack2(lds128(s0 + v * 16), f);
-          if constexpr (!BWD) {
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tid + k * kRingThreads;
+          if (FC || v < cv) {
+            float2 f[VH], o[VH];
+            P::unpack2(lds128(s0 + v * 16), f);
+            if constexpr (!BWD) {
 #pragma unroll
-            for (int e = 0; e < VH; ++e) {
-              if constexpr (LOG) {
-                if constexpr (sizeof(T) == 4) o[e] = make_float2((f[e].x - r0) - lg, (f[e].y - r0) - lg);
-                else o[e] = add2(f[e], noff);
-              } else if constexpr (sizeof(T) == 4) {
-                o[e] = make_float2(expf(f[e].x - r0) / r1, expf(f[e].y - r0) / r1);
-              } else {
-                const float2 tt = fma2(f[e], l2e, c2);
-                o[e] = mul2(make_float2(ex2_approx(tt.x), ex2_approx(tt.y)), inv);
-              }
-            }
-          } else {
-            float2 yv[VH];
-            P::unpack2(lds128(s1 + v * 16), yv);
-#pragma unroll
-            for (int e = 0; e < VH; ++e) {
-              if constexpr (LOG) {
-                float2 ey;
-                if constexpr (sizeof(T) == 4) {
-                  ey = make_float2(expf(yv[e].x), expf(yv[e].y));
+              for (int e = 0; e < VH; ++e) {
+                if constexpr (LOG) {
+                  if constexpr (sizeof(T) == 4) o[e] = make_float2((f[e].x - r0) - lg, (f[e].y - r0) - lg);
+                  else o[e] = add2(f[e], noff);
+                } else if constexpr (sizeof(T) == 4) {
+                  o[e] = make_float2(expf(f[e].x - r0) / r1, expf(f[e].y - r0) / r1);
                 } else {
-                  const float2 tt = mul2(yv[e], l2e);
-                  ey = make_float2(ex2_approx(tt.x), ex2_approx(tt.y));
+                  const float2 tt = fma2(f[e], l2e, c2);
+                  o[e] = mul2(make_float2(ex2_approx(tt.x), ex2_approx(tt.y)), inv);
                 }
-                o[e] = fma2(ey, ns, f[e]);           // dy - exp(y) * sum
-              } else {
-                o[e] = mul2(yv[e], add2(f[e], ns));  // y * (dy - sum)
+              }
+            } else {
+              float2 yv[VH];
+              P::unpack2(lds128(s1 + v * 16), yv);
+#pragma unroll
+              for (int e = 0; e < VH; ++e) {
+                if constexpr (LOG) {
+                  float2 ey;
+                  if constexpr (sizeof(T) == 4) {
+                    ey = make_float2(expf(yv[e].x), expf(yv[e].y));
+                  } else {
+                    const float2 tt = mul2(yv[e], l2e);
+                    ey = make_float2(ex2_approx(tt.x), ex2_approx(tt.y));
+                  }
+                  o[e] = fma2(ey, ns, f[e]);           // dy - exp(y) * sum
+                } else {
+                  o[e] = mul2(yv[e], add2(f[e], ns));  // y * (dy - sum)
+                }
               }
             }
+            if constexpr (SAFE) sts128(s0 + v * 16, zero_row ? make_uint4(0u, 0u, 0u, 0u) : P::pack2(o));
+            else sts128(s0 + v * 16, P::pack2(o));
           }
-          if constexpr (SAFE) sts128(s0 + v * 16, zero_row ? make_uint4(0u, 0u, 0u, 0u) : P::pack2(o));
-          else sts128(s0 + v * 16, P::pack2(o));
         }
-      }
+      };
+      if (cv == kTwoPassChunkVecs) run_chunk(std::true_type{});
+      else run_chunk(std::false_type{});
       release();
       next_stage();
     }
