@@ -385,7 +385,9 @@ def main():
     # From four GPUs on, the collective's kernel gets four SMs of its own: measured at N = 8 the step is 132 us with
     # that margin, 163 us without (the all-reduce then waits for a kernel boundary and delays the next kernel's CTAs),
     # 126 us with no collective at all; at N = 2 the all-reduce is too short for the margin to pay.
-    sm_margin = args.sm_margin if args.sm_margin >= 0 else (4 if world >= 4 else 0)
+    # Only the config-4 step has a collective that overlaps kernels; the others keep every SM.
+    overlapped = world >= 4 and args.workload == "cfg4" and COLLECTIVE_MODE == "async"
+    sm_margin = args.sm_margin if args.sm_margin >= 0 else (4 if overlapped else 0)
     capi.set_tuning(b200norm.TUNE_SM_MARGIN, sm_margin)
 
     b200norm.load_library()
