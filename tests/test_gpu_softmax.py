@@ -59,6 +59,8 @@ def test_last_dim_fwd_bwd(M, N, dt, is_log, path):
 @pytest.mark.parametrize("is_log", [False, True])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape,dim", [((6, 5, 3), 0), ((2, 7, 4), 1), ((4, 33, 65), 1), ((128, 16), 0), ((3, 4, 5, 6), 2),
+                                       ((5, 8, 64), 1), ((3, 16, 34), 1), ((2, 64, 130), 1), ((2, 65, 128), 1), ((9, 40, 7), 1),
+                                       ((4, 19, 32, 32), 1),
                                        ((2, 3, 4), -1), ((5,), 0)])
 def test_any_dim(shape, dim, dt, is_log):
     x = ao.randn(shape, 410, dt, 0.0, 2.0)
@@ -277,3 +279,21 @@ def test_safe_softmax_other_dims_and_half_to_float(dt):
         r32 = torch.ops.aten._safe_softmax(x.float(), -1)
         ok = ~torch.isnan(r32)
         assert torch.equal(torch.isnan(y32), torch.isnan(r32)) and torch.allclose(y32[ok], r32[ok], rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("N", [9, 64, 100])
+@pytest.mark.parametrize("is_log", [False, True])
+def test_degenerate_lines_along_an_inner_dim(N, is_log):
+    # the same edge semantics as over the last dim, for lines held in registers (N <= 64) and streamed ones
+    x = ao.randn((3, N, 10), 420)
+    x[0, :, 2] = float("-inf")           # a line of -inf: NaN
+    x[1, 3, 3] = float("inf")            # +inf in a line: NaN
+    x[2, N - 1, 4] = float("nan")        # NaN in a line: NaN
+    x[0, : N // 2, 5] = float("-inf")    # partly masked: zeros / -inf there, finite elsewhere
+    fwd = capi._log_softmax if is_log else capi._softmax
+    y = fwd(x.to(DEV), 1, False).cpu()
+    ref = ao.softmax_fwd(x, 1, is_log)
+    assert torch.equal(torch.isnan(y), torch.isnan(ref))
+    ok = ~torch.isnan(ref) & ~torch.isinf(ref)
+    assert torch.equal(torch.isinf(y), torch.isinf(ref))
+    assert torch.allclose(y[ok], ref[ok], rtol=1e-5, atol=1e-6)

@@ -116,6 +116,21 @@ template <int TPR, typename A, typename Op> __device__ __forceinline__ A row_red
 // (one int per device, passed to the kernels as an argument: see device_status_ptr below)
 __device__ __forceinline__ void record_status(int* status, int code) { atomicCAS(status, 0, code); }
 
+// 2^v by the hardware approximation (relative error ~2^-22: invisible after rounding to 8 or 11 bits of
+// mantissa, which is where the kernels for 16-bit storage use it).
+__device__ __forceinline__ float ex2_approx(float v) {
+  float r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(v));  // no .ftz: subnormal results are kept
+  return r;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+// exp(d) for a result stored as TO: the approximation for 16-bit storage, the precise function otherwise
+template <typename TO> __device__ __forceinline__ float exp_for(float d) {
+  if constexpr (sizeof(TO) <= 2) return ex2_approx(d * kLog2e);
+  else return expf(d);
+}
+template <typename TO> __device__ __forceinline__ double exp_for(double d) { return exp(d); }
+
 // Programmatic dependent launch (sm_90+).  A kernel launched with launch_pdl() below may become
 // resident while the kernel before it in the stream is still running: pdl_wait() holds it until
 // that kernel has completed and its writes are visible, so everything before the call (barrier

@@ -155,9 +155,230 @@ __global__ void softmax_bwd_generic_kernel(const TG* __restrict__ dy, const TG* 
   }
 }
 
+// ---- softmax over a dim that is not the last: shared-memory tiles ----------------------------------
+// The tensor is [outer, N, inner]; a line runs over N with stride `inner`.  Reading lines one element
+// at a time touches memory in 128-byte pieces half a megabyte apart, which DRAM serves at a fifth of
+// its bandwidth.  Here a CTA stages a tile of `tile` adjacent inner positions x all N line elements
+// in shared memory with 16-byte accesses — N contiguous runs of `tile` elements (1 KB where shared
+// memory allows) — one thread per inner position then walks its line in shared memory (consecutive
+// threads, consecutive addresses: no bank conflicts), leaves the result in place, and the tile goes
+// back the same way.  Every element crosses HBM once each way, for any N whose tile fits.
+// Requires inner % VEC == 0 and 16-byte aligned pointers; TI == TO.
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(256)
+softmax_fwd_tile_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t outer, int N, int64_t inner, int tile,
+                        int safe) {
+  using A = acc_t<T>;
+  constexpr int VEC = 16 / sizeof(T);
+  extern __shared__ __align__(16) unsigned char tile_smem[];
+  T* sm = reinterpret_cast<T*>(tile_smem);
+  const int64_t tpo = (inner + tile - 1) / tile, total = outer * tpo;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const int64_t o = t / tpo, i0 = (t % tpo) * tile;
+    const int w = static_cast<int>(inner - i0 < tile ? inner - i0 : tile);  // a multiple of VEC
+    const int vpr = w / VEC;
+    const T* xb = x + o * N * inner + i0;
+    T* yb = y + o * N * inner + i0;
+    for (int j = warp; j < N; j += nwarp)
+      for (int c = lane; c < vpr; c += 32)
+        *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC) =
+            *reinterpret_cast<const uint4*>(xb + static_cast<int64_t>(j) * inner + c * VEC);
+    __syncthreads();
+    for (int c = threadIdx.x; c < w; c += blockDim.x) {
+      // three walks over the line in shared memory (max; sum of exp; result): reads there are cheap, and exp
+      // of a 16-bit result is one hardware instruction
+      A mx = acc_neg_inf<A>();
+      bool has_nan = false;
+      for (int j = 0; j < N; ++j) {
+        const A v = to_acc<A>(sm[static_cast<size_t>(j) * tile + c]);
+        has_nan |= (v != v);
+        mx = acc_max(mx, v);
+      }
+      A s = 0;
+      for (int j = 0; j < N; ++j) s += exp_for<T>(to_acc<A>(sm[static_cast<size_t>(j) * tile + c]) - mx);
+      if (has_nan) s = acc_nan<A>();  // (+inf in the line: exp(inf - inf) has made the sum NaN already)
+      const A lg = LOG ? acc_log(s) : A(0);
+      const A inv = LOG ? A(0) : A(1) / s;
+      const bool zero = safe && mx == acc_neg_inf<A>() && !has_nan;
+      for (int j = 0; j < N; ++j) {
+        const A d = to_acc<A>(sm[static_cast<size_t>(j) * tile + c]) - mx;
+        const A e = LOG ? d - lg : (sizeof(T) <= 2 ? exp_for<T>(d) * inv : exp_for<T>(d) / s);
+        sm[static_cast<size_t>(j) * tile + c] = from_acc<T>(zero ? A(0) : e);
+      }
+    }
+    __syncthreads();
+    for (int j = warp; j < N; j += nwarp)
+      for (int c = lane; c < vpr; c += 32)
+        *reinterpret_cast<uint4*>(yb + static_cast<int64_t>(j) * inner + c * VEC) =
+            *reinterpret_cast<const uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC);
+    __syncthreads();  // the next tile's loads overwrite the staging area
+  }
+}
+
+// dy tile at sm[0 .. N*tile), y tile behind it; dx overwrites the dy tile.
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(256)
+softmax_bwd_tile_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t outer, int N,
+                        int64_t inner, int tile) {
+  using A = acc_t<T>;
+  constexpr int VEC = 16 / sizeof(T);
+  extern __shared__ __align__(16) unsigned char tile_smem[];
+  T* sd = reinterpret_cast<T*>(tile_smem);
+  T* sy = sd + static_cast<size_t>(N) * tile;
+  const int64_t tpo = (inner + tile - 1) / tile, total = outer * tpo;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const int64_t o = t / tpo, i0 = (t % tpo) * tile;
+    const int w = static_cast<int>(inner - i0 < tile ? inner - i0 : tile);
+    const int vpr = w / VEC;
+    const int64_t base = o * N * inner + i0;
+    for (int j = warp; j < N; j += nwarp)
+      for (int c = lane; c < vpr; c += 32) {
+        const int64_t g = base + static_cast<int64_t>(j) * inner + c * VEC;
+        const size_t l = static_cast<size_t>(j) * tile + c * VEC;
+        *reinterpret_cast<uint4*>(sd + l) = *reinterpret_cast<const uint4*>(dy + g);
+        *reinterpret_cast<uint4*>(sy + l) = *reinterpret_cast<const uint4*>(y + g);
+      }
+    __syncthreads();
+    for (int c = threadIdx.x; c < w; c += blockDim.x) {
+      A s = 0;
+      for (int j = 0; j < N; ++j) {
+        const size_t l = static_cast<size_t>(j) * tile + c;
+        const A d = to_acc<A>(sd[l]);
+        s += LOG ? d : d * to_acc<A>(sy[l]);
+      }
+      for (int j = 0; j < N; ++j) {
+        const size_t l = static_cast<size_t>(j) * tile + c;
+        const A d = to_acc<A>(sd[l]), yy = to_acc<A>(sy[l]);
+        sd[l] = from_acc<T>(LOG ? d - exp_for<T>(yy) * s : yy * (d - s));
+      }
+    }
+    __syncthreads();
+    for (int j = warp; j < N; j += nwarp)
+      for (int c = lane; c < vpr; c += 32)
+        *reinterpret_cast<uint4*>(dx + base + static_cast<int64_t>(j) * inner + c * VEC) =
+            *reinterpret_cast<const uint4*>(sd + static_cast<size_t>(j) * tile + c * VEC);
+    __syncthreads();
+  }
+}
+
+
+// ---- softmax over a dim that is not the last, lines short enough for registers ---------------------
+// The tensor is [outer, N, inner]; a line runs over N with stride `inner`.  A thread owns V adjacent
+// inner positions (V = 2 when `inner` and the pointers allow one 4- or 8-byte access for both), keeps
+// its V lines of up to NMAX values in registers and touches every element once: one read, one write
+// (the general kernels below read a line two or three times).  Neighbouring threads own neighbouring
+// inner positions, so every access of a warp is one contiguous run.
+template <typename TI, typename TO, bool LOG, int NMAX, int V>
+__global__ void __launch_bounds__(256) softmax_fwd_spatial_reg_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t outer, int N,
+                                               int64_t inner, int safe) {
+  using A = acc_t<TI>;
+  const int64_t innerv = inner / V, total = outer * innerv;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t o = idx / innerv, in = (idx % innerv) * V;
+    const int64_t base = o * N * inner + in;
+    A v[NMAX][V];
+    A mx[V];
+    bool has_nan[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) { mx[e] = acc_neg_inf<A>(); has_nan[e] = false; }
+#pragma unroll
+    for (int j = 0; j < NMAX; ++j) {
+      if (j < N) {
+        const Vec<TI, V> p = ld_vec<TI, V>(x + base + j * inner);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          v[j][e] = to_acc<A>(p.v[e]);
+          has_nan[e] |= (v[j][e] != v[j][e]);
+          mx[e] = acc_max(mx[e], v[j][e]);
+        }
+      }
+    }
+    A s[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) s[e] = 0;
+#pragma unroll
+    for (int j = 0; j < NMAX; ++j) {
+      if (j < N) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          v[j][e] = v[j][e] - mx[e];
+          const A ex = exp_for<TO>(v[j][e]);
+          s[e] += ex;
+          if (!LOG) v[j][e] = ex;
+        }
+      }
+    }
+    A lg[V], inv[V];
+    bool zero[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      if (has_nan[e] || mx[e] == -acc_neg_inf<A>()) s[e] = acc_nan<A>();  // NaN, or +inf in the line
+      lg[e] = LOG ? acc_log(s[e]) : A(0);
+      inv[e] = LOG ? A(0) : A(1) / s[e];  // 16-bit storage multiplies by it; wider storage divides (exactly rounded)
+      zero[e] = safe && mx[e] == acc_neg_inf<A>() && !has_nan[e];
+    }
+#pragma unroll
+    for (int j = 0; j < NMAX; ++j) {
+      if (j < N) {
+        Vec<TO, V> o2;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const A sm = sizeof(TO) <= 2 ? v[j][e] * inv[e] : v[j][e] / s[e];
+          o2.v[e] = from_acc<TO>(zero[e] ? A(0) : (LOG ? v[j][e] - lg[e] : sm));
+        }
+        st_vec<TO, V>(y + base + j * inner, o2);
+      }
+    }
+  }
+}
+
+template <typename TG, typename TO, bool LOG, int NMAX, int V>
+__global__ void __launch_bounds__(256) softmax_bwd_spatial_reg_kernel(const TG* __restrict__ dy, const TG* __restrict__ y,
+                                               TO* __restrict__ dx, int64_t outer, int N, int64_t inner) {
+  using A = acc_t<TG>;
+  const int64_t innerv = inner / V, total = outer * innerv;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t o = idx / innerv, in = (idx % innerv) * V;
+    const int64_t base = o * N * inner + in;
+    A d[NMAX][V], yy[NMAX][V];
+    A s[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) s[e] = 0;
+#pragma unroll
+    for (int j = 0; j < NMAX; ++j) {
+      if (j < N) {
+        const Vec<TG, V> pd = ld_vec<TG, V>(dy + base + j * inner);
+        const Vec<TG, V> py = ld_vec<TG, V>(y + base + j * inner);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          d[j][e] = to_acc<A>(pd.v[e]);
+          yy[j][e] = to_acc<A>(py.v[e]);
+          s[e] += LOG ? d[j][e] : d[j][e] * yy[j][e];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NMAX; ++j) {
+      if (j < N) {
+        Vec<TO, V> o2;
+#pragma unroll
+        for (int e = 0; e < V; ++e)
+          o2.v[e] = from_acc<TO>(LOG ? d[j][e] - exp_for<TO>(yy[j][e]) * s[e] : yy[j][e] * (d[j][e] - s[e]));
+        st_vec<TO, V>(dx + base + j * inner, o2);
+      }
+    }
+  }
+}
+
+
 // Softmax along a dim that is not the last: the tensor is [outer, N, inner] and one thread walks
 // one (outer, inner) line with stride `inner`, so neighbouring threads touch neighbouring
-// addresses.  Three passes (max, sum, write).
+// addresses.  Two passes: running (max, sum), then write.  Lines of up to 64 values take the register
+// kernels above instead.
 template <typename TI, typename TO, bool LOG>
 __global__ void softmax_fwd_spatial_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t outer,
                                            int64_t N, int64_t inner, int safe) {
@@ -168,16 +389,18 @@ __global__ void softmax_fwd_spatial_kernel(const TI* __restrict__ x, TO* __restr
     const int64_t o = idx / inner, in = idx % inner;
     const TI* xp = x + o * N * inner + in;
     TO* yp = y + o * N * inner + in;
-    A mx = acc_neg_inf<A>();
+    // one pass for both statistics: a running (max, sum of exp(x - max)) pair
+    MaxSum<A> ms;
+    ms.init();
     bool has_nan = false;
     for (int64_t j = 0; j < N; ++j) {
       const A v = to_acc<A>(xp[j * inner]);
       has_nan |= (v != v);
-      mx = acc_max(mx, v);
+      ms.add(v);
     }
-    A s = 0;
-    for (int64_t j = 0; j < N; ++j) s += acc_exp(to_acc<A>(xp[j * inner]) - mx);
-    if (has_nan) s = acc_nan<A>();
+    const A mx = ms.m;
+    A s = ms.s;
+    if (has_nan || mx == -acc_neg_inf<A>()) s = acc_nan<A>();  // NaN, or +inf in the line: exp(inf - inf)
     const A lg = LOG ? acc_log(s) : A(0);
     const bool zero_row = safe && mx == acc_neg_inf<A>() && !has_nan;
     for (int64_t j = 0; j < N; ++j) {

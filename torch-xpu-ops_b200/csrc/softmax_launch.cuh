@@ -182,6 +182,16 @@ int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_
   return softmax_twopass_launch_as<T, LOG, BWD, false>(in0, in1, out, M, N, st);
 }
 
+// Tile width (elements) for the shared-memory tile kernels of the non-last-dim softmax: 1 KB runs when at
+// least three CTAs then fit an SM, halved down to 256-byte runs otherwise; 0 when not even that fits.
+inline int spatial_tile_elems(int64_t N, int esize, int ntensors, int64_t inner, int max_smem) {
+  int tile = 1024 / esize;
+  const int min_tile = 256 / esize;
+  while (tile > min_tile && (N * tile * esize * ntensors > 72 * 1024 || tile / 2 >= inner)) tile /= 2;
+  if (N * tile * esize * ntensors > max_smem) return 0;
+  return tile;
+}
+
 template <typename TI, typename TO, bool LOG>
 int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_t inner, cudaStream_t st) {
   const TI* x = static_cast<const TI*>(x_);
@@ -235,6 +245,43 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
   }
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
+  if constexpr (std::is_same<TI, TO>::value) {
+    constexpr int VEC = 16 / sizeof(TI);
+    const DeviceInfo& di = device_info();
+    const int tile = spatial_tile_elems(N, sizeof(TI), 1, inner, di.max_smem_optin);
+    if (tile > 0 && inner % VEC == 0 && inner >= 64 && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
+      auto kernel = softmax_fwd_tile_kernel<TI, LOG>;
+      static std::atomic<uint64_t> done{0};
+      if (int e = set_smem_once_sm(kernel, done)) return e;
+      const size_t smem = static_cast<size_t>(N) * tile * sizeof(TI);
+      const int64_t tiles = outer * ((inner + tile - 1) / tile);
+      const int64_t cap = static_cast<int64_t>(di.sm_count) * 8;
+      ProfileScope prof(LOG ? "log_softmax_fwd_tile" : "softmax_fwd_tile", st);
+      kernel<<<static_cast<int>(tiles < cap ? tiles : cap), 256, smem, st>>>(x, y, outer, static_cast<int>(N), inner,
+                                                                               tile, safe);
+      return launched();
+    }
+  }
+  if (N <= 64) {
+    // short lines: registers hold them, every element is touched once
+    ProfileScope prof(LOG ? "log_softmax_fwd_spatial" : "softmax_fwd_spatial", st);
+    const bool v2 = inner % 2 == 0 && is_aligned(x, 2 * sizeof(TI)) && is_aligned(y, 2 * sizeof(TO));
+    const int grid = softmax_generic_grid(outer * (v2 ? inner / 2 : inner), 256);
+    const int n = static_cast<int>(N);
+#define B2N_SPATIAL_FWD(NMAX)                                                                                       \
+  do {                                                                                                              \
+    if (v2) softmax_fwd_spatial_reg_kernel<TI, TO, LOG, NMAX, 2><<<grid, 256, 0, st>>>(x, y, outer, n, inner, safe); \
+    else softmax_fwd_spatial_reg_kernel<TI, TO, LOG, NMAX, 1><<<grid, 256, 0, st>>>(x, y, outer, n, inner, safe);    \
+  } while (0)
+    if (N <= 8) B2N_SPATIAL_FWD(8);
+    else if (N <= 16) B2N_SPATIAL_FWD(16);
+    else if (N <= 32) B2N_SPATIAL_FWD(32);
+    else  // one line of 64 values per thread: two would halve the resident warps
+      softmax_fwd_spatial_reg_kernel<TI, TO, LOG, 64, 1><<<softmax_generic_grid(outer * inner, 256), 256, 0, st>>>(
+          x, y, outer, n, inner, safe);
+#undef B2N_SPATIAL_FWD
+    return launched();
+  }
   const int grid = softmax_generic_grid(outer * inner, 256);
   softmax_fwd_spatial_kernel<TI, TO, LOG><<<grid, 256, 0, st>>>(x, y, outer, N, inner, safe);
   return launched();
@@ -296,6 +343,44 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
   }
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
+  if constexpr (std::is_same<TG, TO>::value) {
+    constexpr int VEC = 16 / sizeof(TG);
+    const DeviceInfo& di = device_info();
+    const int tile = spatial_tile_elems(N, sizeof(TG), 2, inner, di.max_smem_optin);
+    if (tile > 0 && inner % VEC == 0 && inner >= 64 && is_aligned(dy, 16) && is_aligned(y, 16) && is_aligned(dx, 16) &&
+        N <= (1 << 20)) {
+      auto kernel = softmax_bwd_tile_kernel<TG, LOG>;
+      static std::atomic<uint64_t> done{0};
+      if (int e = set_smem_once_sm(kernel, done)) return e;
+      const size_t smem = static_cast<size_t>(N) * tile * sizeof(TG) * 2;
+      const int64_t tiles = outer * ((inner + tile - 1) / tile);
+      const int64_t cap = static_cast<int64_t>(di.sm_count) * 8;
+      ProfileScope prof(LOG ? "log_softmax_bwd_tile" : "softmax_bwd_tile", st);
+      kernel<<<static_cast<int>(tiles < cap ? tiles : cap), 256, smem, st>>>(dy, y, dx, outer, static_cast<int>(N), inner,
+                                                                               tile);
+      return launched();
+    }
+  }
+  if (N <= 64) {
+    ProfileScope prof(LOG ? "log_softmax_bwd_spatial" : "softmax_bwd_spatial", st);
+    const bool v2 = inner % 2 == 0 && is_aligned(dy, 2 * sizeof(TG)) && is_aligned(y, 2 * sizeof(TG)) &&
+                    is_aligned(dx, 2 * sizeof(TO));
+    const int grid = softmax_generic_grid(outer * (v2 ? inner / 2 : inner), 256);
+    const int n = static_cast<int>(N);
+#define B2N_SPATIAL_BWD(NMAX)                                                                                    \
+  do {                                                                                                           \
+    if (v2) softmax_bwd_spatial_reg_kernel<TG, TO, LOG, NMAX, 2><<<grid, 256, 0, st>>>(dy, y, dx, outer, n, inner); \
+    else softmax_bwd_spatial_reg_kernel<TG, TO, LOG, NMAX, 1><<<grid, 256, 0, st>>>(dy, y, dx, outer, n, inner);    \
+  } while (0)
+    if (N <= 8) B2N_SPATIAL_BWD(8);
+    else if (N <= 16) B2N_SPATIAL_BWD(16);
+    else if (N <= 32) B2N_SPATIAL_BWD(32);
+    else  // two lines of 64 values of dy and y each would not fit the register file: one line per thread
+      softmax_bwd_spatial_reg_kernel<TG, TO, LOG, 64, 1><<<softmax_generic_grid(outer * inner, 256), 256, 0, st>>>(
+          dy, y, dx, outer, n, inner);
+#undef B2N_SPATIAL_BWD
+    return launched();
+  }
   const int grid = softmax_generic_grid(outer * inner, 256);
   softmax_bwd_spatial_kernel<TG, TO, LOG><<<grid, 256, 0, st>>>(dy, y, dx, outer, N, inner);
   return launched();

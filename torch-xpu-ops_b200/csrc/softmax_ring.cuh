@@ -6,13 +6,6 @@
 
 namespace b2n {
 
-__device__ __forceinline__ float ex2_approx(float v) {
-  float r;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(v));  // no .ftz: subnormal results are kept
-  return r;
-}
-constexpr float kLog2e = 1.4426950408889634f;
-
 // exp(x - mx) for a row maximum mx.  For 16-bit storage the result is rounded to 8 or 11 bits of
 // mantissa anyway, so one FMA plus the hardware 2^x (relative error about 2^-22 plus
 // |x - mx| * 2^-24) is enough; fp32 storage uses expf.
