@@ -155,6 +155,15 @@ __global__ void softmax_bwd_generic_kernel(const TG* __restrict__ dy, const TG* 
   }
 }
 
+// Two adjacent 16-bit values as one 32-bit shared-memory access (the tile kernels walk lines two columns at a time).
+__device__ __forceinline__ float2 ld_pair(const bf16* p) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+__device__ __forceinline__ float2 ld_pair(const f16* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+__device__ __forceinline__ void st_pair(bf16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __float22bfloat162_rn(v); }
+__device__ __forceinline__ void st_pair(f16* p, float2 v) { *reinterpret_cast<__half2*>(p) = __float22half2_rn(v); }
+
 // ---- softmax over a dim that is not the last: shared-memory tiles ----------------------------------
 // The tensor is [outer, N, inner]; a line runs over N with stride `inner`.  Reading lines one element
 // at a time touches memory in 128-byte pieces half a megabyte apart, which DRAM serves at a fifth of
@@ -185,6 +194,41 @@ softmax_fwd_tile_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t oute
         *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC) =
             *reinterpret_cast<const uint4*>(xb + static_cast<int64_t>(j) * inner + c * VEC);
     __syncthreads();
+    if constexpr (sizeof(T) == 2) {
+      // 16-bit storage: a thread walks two adjacent lines with one 32-bit access per step
+      for (int c = 2 * threadIdx.x; c < w; c += 2 * blockDim.x) {
+        T* col = sm + c;
+        float2 mx = make_float2(acc_neg_inf<float>(), acc_neg_inf<float>());
+        bool nan0 = false, nan1 = false;
+        for (int j = 0; j < N; ++j) {
+          const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
+          nan0 |= (v.x != v.x);
+          nan1 |= (v.y != v.y);
+          mx.x = fmaxf(mx.x, v.x);
+          mx.y = fmaxf(mx.y, v.y);
+        }
+        float2 sum = make_float2(0.0f, 0.0f);
+        for (int j = 0; j < N; ++j) {
+          const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
+          sum.x += exp_for<T>(v.x - mx.x);
+          sum.y += exp_for<T>(v.y - mx.y);
+        }
+        if (nan0) sum.x = acc_nan<float>();
+        if (nan1) sum.y = acc_nan<float>();
+        const float2 lg = make_float2(LOG ? logf(sum.x) : 0.0f, LOG ? logf(sum.y) : 0.0f);
+        const float2 inv = make_float2(LOG ? 0.0f : 1.0f / sum.x, LOG ? 0.0f : 1.0f / sum.y);
+        const bool z0 = safe && mx.x == acc_neg_inf<float>() && !nan0, z1 = safe && mx.y == acc_neg_inf<float>() && !nan1;
+        for (int j = 0; j < N; ++j) {
+          const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
+          const float dx0 = v.x - mx.x, dx1 = v.y - mx.y;
+          float2 e = LOG ? make_float2(dx0 - lg.x, dx1 - lg.y)
+                         : make_float2(exp_for<T>(dx0) * inv.x, exp_for<T>(dx1) * inv.y);
+          if (z0) e.x = 0.0f;
+          if (z1) e.y = 0.0f;
+          st_pair(col + static_cast<size_t>(j) * tile, e);
+        }
+      }
+    } else
     for (int c = threadIdx.x; c < w; c += blockDim.x) {
       // three walks over the line in shared memory (max; sum of exp; result): reads there are cheap, and exp
       // of a 16-bit result is one hardware instruction
@@ -241,6 +285,30 @@ softmax_bwd_tile_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
         *reinterpret_cast<uint4*>(sy + l) = *reinterpret_cast<const uint4*>(y + g);
       }
     __syncthreads();
+    if constexpr (sizeof(T) == 2) {
+      for (int c = 2 * threadIdx.x; c < w; c += 2 * blockDim.x) {
+        float2 sum = make_float2(0.0f, 0.0f);
+        for (int j = 0; j < N; ++j) {
+          const size_t l = static_cast<size_t>(j) * tile + c;
+          const float2 d = ld_pair(sd + l);
+          if constexpr (LOG) {
+            sum.x += d.x;
+            sum.y += d.y;
+          } else {
+            const float2 yy = ld_pair(sy + l);
+            sum.x = fmaf(d.x, yy.x, sum.x);
+            sum.y = fmaf(d.y, yy.y, sum.y);
+          }
+        }
+        for (int j = 0; j < N; ++j) {
+          const size_t l = static_cast<size_t>(j) * tile + c;
+          const float2 d = ld_pair(sd + l), yy = ld_pair(sy + l);
+          const float2 o = LOG ? make_float2(d.x - exp_for<T>(yy.x) * sum.x, d.y - exp_for<T>(yy.y) * sum.y)
+                               : make_float2(yy.x * (d.x - sum.x), yy.y * (d.y - sum.y));
+          st_pair(sd + l, o);
+        }
+      }
+    } else
     for (int c = threadIdx.x; c < w; c += blockDim.x) {
       A s = 0;
       for (int j = 0; j < N; ++j) {
