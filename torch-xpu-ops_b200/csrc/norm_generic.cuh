@@ -176,11 +176,15 @@ __global__ void norm_bwd_wgrad_partial_kernel(const T* __restrict__ dy, const T*
 }
 
 // Folds P partial rows [P][2][N] into dgamma (plane 0) and dbeta (plane 1) in a fixed order, so
-// the result does not depend on scheduling.  blockIdx.y selects the plane.
+// the result does not depend on scheduling.  blockIdx.y selects the plane.  A CTA is 32 columns x
+// kFoldLanes row lanes: lane ty sums rows ty, ty + kFoldLanes, ... (a few independent loads each, so
+// the kernel is not a chain of dependent loads), then the lanes' sums are added in lane order.
+constexpr int kFoldLanes = 32;
 template <typename A, typename WT>
-__global__ void norm_bwd_wgrad_fold_kernel(const A* __restrict__ ws, WT* __restrict__ dgamma,
-                                           WT* __restrict__ dbeta, int64_t P, int64_t N) {
-  __shared__ A sm[8][33];
+__global__ void __launch_bounds__(32 * kFoldLanes)
+norm_bwd_wgrad_fold_kernel(const A* __restrict__ ws, WT* __restrict__ dgamma, WT* __restrict__ dbeta, int64_t P,
+                           int64_t N) {
+  __shared__ A sm[kFoldLanes][33];
   pdl_launch_dependents();  // see common.cuh: no-ops unless launched with launch_pdl
   pdl_wait();
   const int tx = threadIdx.x, ty = threadIdx.y;
@@ -190,14 +194,15 @@ __global__ void norm_bwd_wgrad_fold_kernel(const A* __restrict__ ws, WT* __restr
   const int64_t col = static_cast<int64_t>(blockIdx.x) * 32 + tx;
   A s = 0;
   if (col < N) {
-    for (int64_t p = ty; p < P; p += 8) s += ws[(p * 2 + plane) * N + col];
+#pragma unroll 4
+    for (int64_t p = ty; p < P; p += kFoldLanes) s += ws[(p * 2 + plane) * N + col];
   }
   sm[ty][tx] = s;
   __syncthreads();
   if (ty == 0 && col < N) {
     A r = sm[0][tx];
 #pragma unroll
-    for (int k = 1; k < 8; ++k) r += sm[k][tx];
+    for (int k = 1; k < kFoldLanes; ++k) r += sm[k][tx];
     out[col] = from_acc<WT>(r);
   }
 }

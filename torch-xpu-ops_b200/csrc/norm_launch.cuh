@@ -186,7 +186,7 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
       return B2N_ERR_WORKSPACE;
   }
   A* ws = static_cast<A*>(workspace);
-  const dim3 fold_block(32, 8);
+  const dim3 fold_block(32, kFoldLanes);
   const dim3 fold_grid(static_cast<unsigned>((N + 31) / 32), 2);
 
   if constexpr (sizeof(T) <= 4 && !std::is_same<T, double>::value) {
