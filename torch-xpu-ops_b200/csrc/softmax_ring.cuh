@@ -33,7 +33,22 @@ template <> struct MaskWord<8> {
   __device__ __forceinline__ void load(const unsigned char* p) { w = __ldg(reinterpret_cast<const uint2*>(p)); }
   __device__ __forceinline__ void clear() { w = make_uint2(0u, 0u); }
   __device__ __forceinline__ bool masked(int e) const { return (((e < 4 ? w.x : w.y) >> (8 * (e & 3))) & 0xffu) != 0u; }
+  // the eight mask bytes widened to eight 16-bit fields, all ones where masked: what a 16-byte vector of
+  // 16-bit values is combined with directly (three bitwise operations per pair instead of a test per element)
+  __device__ __forceinline__ uint4 halfword_masks() const {
+    const unsigned a = __vcmpne4(w.x, 0u), b = __vcmpne4(w.y, 0u);  // 0xff per non-zero byte
+    return make_uint4(__byte_perm(a, a, 0x1100), __byte_perm(a, a, 0x3322), __byte_perm(b, b, 0x1100),
+                      __byte_perm(b, b, 0x3322));
+  }
 };
+// -inf twice in the 16-bit storage types
+template <typename T> __device__ __forceinline__ constexpr unsigned neg_inf_pair() { return 0u; }
+template <> __device__ __forceinline__ constexpr unsigned neg_inf_pair<bf16>() { return 0xff80ff80u; }
+template <> __device__ __forceinline__ constexpr unsigned neg_inf_pair<f16>() { return 0xfc00fc00u; }
+__device__ __forceinline__ uint4 mask_to(const uint4& v, const uint4& m, unsigned fill) {  // v where m == 0, fill where m == 1
+  return make_uint4((v.x & ~m.x) | (fill & m.x), (v.y & ~m.y) | (fill & m.y), (v.z & ~m.z) | (fill & m.z),
+                    (v.w & ~m.w) | (fill & m.w));
+}
 template <> struct MaskWord<4> {
   unsigned w;
   __device__ __forceinline__ void load(const unsigned char* p) { w = __ldg(reinterpret_cast<const unsigned*>(p)); }
@@ -106,8 +121,12 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (FULL || v < nvec) {
-          P::unpack2(lds128(rbase + v * 16), &xv[k * VH]);
-          if constexpr (MASKED) {  // masked elements take no part: -inf, which comes out as exactly 0
+          if constexpr (MASKED && sizeof(T) == 2) {  // masked elements take no part: -inf, which comes out as exactly 0
+            P::unpack2(mask_to(lds128(rbase + v * 16), mw[k].halfword_masks(), neg_inf_pair<T>()), &xv[k * VH]);
+          } else {
+            P::unpack2(lds128(rbase + v * 16), &xv[k * VH]);
+          }
+          if constexpr (MASKED && sizeof(T) != 2) {
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
               if (mw[k].masked(2 * e)) xv[k * VH + e].x = ninf;
@@ -269,9 +288,15 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
       for (int k = 0; k < VPT; ++k) {
         const int v = tg + k * GROUP;
         if (FULL || v < nvec) {
-          P::unpack2(lds128(dbase + v * 16), &dv[k * VH]);
-          P::unpack2(lds128(ybase + v * 16), &yv[k * VH]);
-          if constexpr (MASKED) {  // masked elements take no part in the row sum
+          if constexpr (MASKED && sizeof(T) == 2) {  // masked elements take no part in the row sum: +0 in both
+            const uint4 hm = mw[k].halfword_masks();
+            P::unpack2(mask_to(lds128(dbase + v * 16), hm, 0u), &dv[k * VH]);
+            P::unpack2(mask_to(lds128(ybase + v * 16), hm, 0u), &yv[k * VH]);
+          } else {
+            P::unpack2(lds128(dbase + v * 16), &dv[k * VH]);
+            P::unpack2(lds128(ybase + v * 16), &yv[k * VH]);
+          }
+          if constexpr (MASKED && sizeof(T) != 2) {
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
               if (mw[k].masked(2 * e)) { dv[k * VH + e].x = 0.0f; yv[k * VH + e].x = 0.0f; }
@@ -313,14 +338,18 @@ softmax_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
               o[e] = mul2(yy, add2(d, ns));  // y*(dy - sum)
             }
           }
-          if constexpr (MASKED) {  // exactly zero where masked, whatever the row sum is
+          if constexpr (MASKED && sizeof(T) == 2) {  // exactly zero where masked, whatever the row sum is
+            sts128(dbase + v * 16, mask_to(P::pack2(o), mw[k].halfword_masks(), 0u));
+          } else {
+            if constexpr (MASKED) {
 #pragma unroll
-            for (int e = 0; e < VH; ++e) {
-              if (mw[k].masked(2 * e)) o[e].x = 0.0f;
-              if (mw[k].masked(2 * e + 1)) o[e].y = 0.0f;
+              for (int e = 0; e < VH; ++e) {
+                if (mw[k].masked(2 * e)) o[e].x = 0.0f;
+                if (mw[k].masked(2 * e + 1)) o[e].y = 0.0f;
+              }
             }
+            sts128(dbase + v * 16, P::pack2(o));
           }
-          sts128(dbase + v * 16, P::pack2(o));
         }
       }
     }
