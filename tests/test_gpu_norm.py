@@ -320,3 +320,32 @@ def test_workspace_too_small_is_rejected():
                                 b200norm.F32, b200norm.F16, None)
     assert rc == b200norm.ERR_UNSUPPORTED_DTYPE
     torch.cuda.synchronize()
+
+
+def test_sm_margin_changes_the_grid_not_the_results():
+    # persistent kernels leave SMs free when asked to (for a collective running beside them): fewer CTAs, same rows
+    M, N = 5000, 2048
+    x = ao.randn((M, N), 360, torch.bfloat16).to(DEV)
+    dy = ao.randn((M, N), 361, torch.bfloat16).to(DEV)
+    g = ao.randn((N,), 362, torch.float32, 1.0, 0.02).to(DEV)
+    b = ao.randn((N,), 363, torch.float32, 0.0, 0.02).to(DEV)
+
+    def run():
+        y, mean, rstd = capi.native_layer_norm(x, [N], g, b, 1e-5)
+        dx, dg, db = capi.native_layer_norm_backward(dy, x, [N], mean, rstd, g, b)
+        p = capi._softmax(x, -1, False)
+        return y, mean, rstd, dx, dg, db, p
+
+    base = run()
+    try:
+        for margin in (1, 8, 140):
+            capi.set_tuning(b200norm.TUNE_SM_MARGIN, margin)
+            got = run()
+            assert capi.last_path() == "ring"
+            for a, r in zip(got[:4] + got[6:], base[:4] + base[6:]):
+                assert torch.equal(a, r)           # per-row results do not depend on which CTA took the row
+            for a, r in zip(got[4:6], base[4:6]):  # the weight gradients are summed over a different set of partial rows
+                assert torch.allclose(a, r, rtol=1e-4, atol=1e-3)
+    finally:
+        capi.set_tuning(b200norm.TUNE_SM_MARGIN, 0)
+    assert capi.device_status() == 0
