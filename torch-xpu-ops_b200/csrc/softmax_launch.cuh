@@ -183,11 +183,11 @@ int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_
 }
 
 // Tile width (elements) for the shared-memory tile kernels of the non-last-dim softmax: 1 KB runs when at
-// least three CTAs then fit an SM, halved down to 256-byte runs otherwise; 0 when not even that fits.
+// least two CTAs then fit an SM, halved down to 256-byte runs otherwise; 0 when not even that fits.
 inline int spatial_tile_elems(int64_t N, int esize, int ntensors, int64_t inner, int max_smem) {
   int tile = 1024 / esize;
   const int min_tile = 256 / esize;
-  while (tile > min_tile && (N * tile * esize * ntensors > 72 * 1024 || tile / 2 >= inner)) tile /= 2;
+  while (tile > min_tile && (N * tile * esize * ntensors > 110 * 1024 || tile / 2 >= inner)) tile /= 2;
   if (N * tile * esize * ntensors > max_smem) return 0;
   return tile;
 }
