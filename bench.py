@@ -8,13 +8,27 @@ default workload is BASELINE config 4: native_layer_norm forward + backward (dx,
 bf16 [65536, 8192] with fp32 gamma/beta, rows sharded evenly over the N ranks (strong scaling), the
 fused fp32 [2, 8192] dgamma|dbeta buffer all-reduced over NCCL each step.  Other workloads
 (--workload cfg1|cfg2|cfg3|cfg5) run the other BASELINE configs the same way; cfg5f is config 5 with the fused
-cross-entropy backward.
+cross-entropy backward, cfg3m config 3 with the mask inside the kernels, ln_long layer norm on rows of 16384.
 
 Prints ONE JSON line (rank 0).  `value` is algorithmic bytes (every tensor of the operators'
 signatures read or written once) of all ranks / device time, inputs resident in HBM; `e2e` is the
 same metric through the ATen dispatcher with pinned HOST buffers, copies inside the timed region.
 `--impl reference` times PyTorch's CPU ATen kernels (the reference path's parity standard, and the
-only implementation of it that runs on this box) on the host cores over a bounded row sample.
+only implementation of it that runs on this box) on the host cores over the same rows.
+
+Timing.  A timed region is EXACTLY --steps steps between two CUDA events on the launching stream, a
+barrier and a device synchronisation on both sides, the maximum over ranks.  A region shorter than
+50 ms is repeated (9 regions, back to back): `ms_per_step` is then the median region and `spread`
+gives the fastest and slowest.  `host_enqueue_us_per_step` is the host time the un-synchronised step
+loop took, `collective_us` one in-stream all-reduce of the step's buffer between its own events.
+
+Steps are enqueued through prepared C-ABI calls (arguments converted once) and, with --graph on
+(the default wherever a workload supports it), replayed from a CUDA graph holding one cycle of the
+workload's rotating buffers — the kernels, their dependent-launch edges and the NCCL all-reduce on
+its side stream — so the host's speed does not enter the device-timed number.
+
+With the default workload on one GPU the line also carries `configs`: a short run of every other
+BASELINE config (and cfg5f) with its own value and per-kernel roofline.
 """
 from __future__ import annotations
 
@@ -58,18 +72,22 @@ class Workload:
 
 
 class Cfg4LayerNorm(Workload):
-    name, rows, N, cpu_sample_rows = "cfg4", 65536, 8192, 4096
+    name, rows, N, cpu_sample_rows = "cfg4", 65536, 8192, 65536
     kernel = "layer_norm_bwd_ring"
+    l2_note = "inputs larger than L2 (no flush needed)"
+    cycle = 2  # steps after which the rotating buffers repeat (the two gradient buffers)
 
     def describe(self):
-        return ("native_layer_norm fwd + native_layer_norm_backward (dx, dgamma, dbeta), bf16 [65536, 8192], "
-                "fp32 gamma/beta, eps 1e-5")
+        return ("native_layer_norm fwd + native_layer_norm_backward (dx, dgamma, dbeta), bf16 "
+                f"[{self.rows}, {self.N}], fp32 gamma/beta, eps 1e-5")
 
     def bytes_per_rows(self, rows):
         n = self.N
         fwd = 2 * rows * n * 2 + 2 * n * 4 + 2 * rows * 4
         bwd = 3 * rows * n * 2 + 2 * rows * 4 + n * 4 + 2 * n * 4
-        return {"total": fwd + bwd, "layer_norm_fwd_ring": fwd, "layer_norm_bwd_ring": bwd}
+        return {"total": fwd + bwd, "layer_norm_fwd_ring": fwd, "layer_norm_bwd_ring": bwd,
+                "layer_norm_fwd_slab": fwd, "layer_norm_bwd_slab": bwd,
+                "layer_norm_fwd_generic": fwd, "layer_norm_bwd_dx_generic": bwd}
 
     def make_device_state(self, rows, dev, seed):
         g = torch.Generator(device=dev).manual_seed(seed)
@@ -93,30 +111,88 @@ class Cfg4LayerNorm(Workload):
         st["ws"] = torch.empty(max(nbytes, 1), device=dev, dtype=torch.uint8)
         return st
 
+    def prepare(self, capi, st):
+        """Prepared C-ABI calls (pointers and sizes converted once) on the CURRENT stream."""
+        st["fwd"] = capi.prepare_layer_norm(st["x"], st["gamma"], st["beta"], 1e-5, st["y"], st["mean"], st["rstd"])
+        st["bwd"] = [capi.prepare_layer_norm_backward(st["dy"], st["x"], st["mean"], st["rstd"], st["gamma"], st["dx"],
+                                                      wg[0], wg[1], st["ws"]) for wg in st["wgrads"]]
+
     def step(self, capi, st, world):
-        n = self.N
         k = st["k"] = st["k"] ^ 1
-        wg = st["wgrads"][k]
         if st["works"][k] is not None:
             st["works"][k].wait()  # stream-level: the buffer's previous all-reduce precedes its reuse
-        capi.native_layer_norm(st["x"], [n], st["gamma"], st["beta"], 1e-5, out=(st["y"], st["mean"], st["rstd"]))
-        capi.native_layer_norm_backward(st["dy"], st["x"], [n], st["mean"], st["rstd"], st["gamma"], st["beta"],
-                                        (True, True, True), out=(st["dx"], wg[0], wg[1]), workspace=st["ws"])
+            st["works"][k] = None
+        st["fwd"]()
+        st["bwd"][k]()
         if world > 1 and COLLECTIVE_MODE != "none":
-            # one all-reduce(SUM) of the fused [dgamma | dbeta] buffer the fold kernel just wrote; asynchronous,
+            # one all-reduce(SUM) of the fused [dgamma | dbeta] buffer the backward just wrote; asynchronous,
             # so it overlaps the next step's forward (nothing reads the reduced gradients inside the step)
             if COLLECTIVE_MODE == "async":
-                st["works"][k] = dist.all_reduce(wg, async_op=True)
+                st["works"][k] = dist.all_reduce(st["wgrads"][k], async_op=True)
             else:
-                dist.all_reduce(wg)
+                dist.all_reduce(st["wgrads"][k])
+
+    def capture_cycle(self, capi, st, world, cs, side):
+        """Enqueue one cycle (two steps) on the capturing stream `cs`; each step's all-reduce goes to `side`
+        and is joined where its buffer is next written, or at the end of the cycle."""
+        pending = [None, None]
+        for k in (1, 0):
+            if pending[k] is not None:
+                cs.wait_event(pending[k])
+            st["fwd"]()
+            st["bwd"][k]()
+            if world > 1 and COLLECTIVE_MODE != "none":
+                if COLLECTIVE_MODE == "async":
+                    ready = torch.cuda.Event()
+                    ready.record(cs)
+                    side.wait_event(ready)
+                    with torch.cuda.stream(side):
+                        dist.all_reduce(st["wgrads"][k])
+                        done = torch.cuda.Event()
+                        done.record(side)
+                    pending[k] = done
+                else:
+                    dist.all_reduce(st["wgrads"][k])
+        for ev in pending:
+            if ev is not None:
+                cs.wait_event(ev)
+
+    def collective_buffer(self, st):
+        return st["wgrads"][0]
 
     def finish(self, st):
-        for w in st["works"]:
+        for i, w in enumerate(st["works"]):
             if w is not None:
                 w.wait()
-        st["works"] = [None, None]
+                st["works"][i] = None
 
-    launches_per_step = 3  # forward ring kernel, backward ring kernel, partial-sum fold
+    launches_per_step = 2  # forward ring kernel, backward ring kernel (the partial sums are folded in its tail)
+
+    def shard_check(self, capi, st, world, rank, rows_of):
+        """After a multi-GPU run: the all-reduced [dgamma | dbeta] against the sum, taken in fp64 on rank 0, of
+        the same operators run block by block over every rank's rows (same seeds).  L1-relative error."""
+        n = self.N
+        self.finish(st)
+        got = st["wgrads"][st["k"]].clone()
+        torch.cuda.synchronize()
+        err = None
+        if rank == 0:
+            dev = got.device
+            total = torch.zeros((2, n), dtype=torch.float64, device=dev)
+            for r in range(world):
+                rows = rows_of(r)
+                blk = st if r == 0 else self.make_device_state(rows, dev, seed=4001 + r)
+                wg = torch.empty((2, n), device=dev, dtype=torch.float32)
+                _, mean, rstd = capi.native_layer_norm(blk["x"], [n], blk["gamma"], blk["beta"], 1e-5)
+                capi.native_layer_norm_backward(blk["dy"], blk["x"], [n], mean, rstd, blk["gamma"], blk["beta"],
+                                                (True, True, True), out=(None, wg[0], wg[1]))
+                total += wg.double()
+                del blk
+            err = {"dgamma_l1_err": float((got[0].double() - total[0]).abs().sum() / total[0].abs().sum()),
+                   "dbeta_l1_err": float((got[1].double() - total[1]).abs().sum() / total[1].abs().sum()),
+                   "what": "all-reduced [dgamma|dbeta] of the last step vs the fp64 sum of every rank's block, "
+                           "recomputed on rank 0"}
+        return err
 
     def cpu_step(self, cpu):
         n = self.N
@@ -127,9 +203,14 @@ class Cfg4LayerNorm(Workload):
     def make_cpu_state(self, rows):
         g = torch.Generator().manual_seed(4001)
         n = self.N
-        return {"x": torch.randn((rows, n), generator=g).to(torch.bfloat16),
-                "dy": torch.randn((rows, n), generator=g).to(torch.bfloat16),
-                "gamma": torch.randn(n, generator=g) * 0.02 + 1.0, "beta": torch.randn(n, generator=g) * 0.02}
+        cpu = {k: torch.empty((rows, n), dtype=torch.bfloat16) for k in ("x", "dy")}
+        blk = 4096
+        for k in ("x", "dy"):  # in row blocks: the fp32 draw of the whole tensor would be 2 GiB at a time
+            for r in range(0, rows, blk):
+                cpu[k][r:r + blk] = torch.randn((min(blk, rows - r), n), generator=g).to(torch.bfloat16)
+        cpu["gamma"] = torch.randn(n, generator=g) * 0.02 + 1.0
+        cpu["beta"] = torch.randn(n, generator=g) * 0.02
+        return cpu
 
     # ---- end to end through the ATen dispatcher, host buffers, chunked so copies overlap kernels ----
     e2e_chunks = 8  # more chunks change nothing: both PCIe directions are busy for the whole step (measured with 32)
@@ -147,6 +228,13 @@ class Cfg4LayerNorm(Workload):
         devb = {k: [torch.empty((crow, n), device=dev, dtype=torch.bfloat16) for _ in range(2)] for k in ("x", "dy")}
         return {"host": host, "dev": devb, "crow": crow, "rows": rows,
                 "streams": [torch.cuda.Stream(dev) for _ in range(3)]}
+
+    def cpu_state_from_e2e(self, e2e):
+        """The pinned host inputs of the end-to-end arm double as the CPU arm's inputs (same seed, same rows)."""
+        g = torch.Generator().manual_seed(4002)
+        n = self.N
+        return {"x": e2e["host"]["x"], "dy": e2e["host"]["dy"], "gamma": torch.randn(n, generator=g) * 0.02 + 1.0,
+                "beta": torch.randn(n, generator=g) * 0.02}
 
     def e2e_step(self, st, e2e, world):
         n, rows, crow = self.N, e2e["rows"], e2e["crow"]
@@ -205,8 +293,9 @@ WORKLOADS = {"cfg4": Cfg4LayerNorm}
 
 
 def _load_more_workloads():
-    from bench_workloads import EXTRA  # noqa: WPS433  (kept in a sibling module to keep this file readable)
+    from bench_workloads import EXTRA, layer_norm_long_rows  # noqa: WPS433  (a sibling module, to keep this file readable)
     WORKLOADS.update(EXTRA)
+    WORKLOADS["ln_long"] = layer_norm_long_rows(Cfg4LayerNorm)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -280,22 +369,29 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def recorded_traffic(kernel: str, units: int):
-    """DRAM bytes per launch from the committed ncu capture (profiles/dram_traffic.json holds bytes per
-    row per kernel, measured on a smaller case of the same row length); None when not captured."""
+def recorded_traffic(kernel: str, units: int, algorithmic_bytes=None):
+    """DRAM bytes per launch from the committed ncu capture (profiles/dram_traffic.json; captured on a smaller
+    case of the same row length and scaled by rows).  DRAM READS scale with the rows and are taken from the
+    capture; DRAM writes of a small capture under-count (part of the output is still dirty in L2 when the kernel
+    ends), so where the file gives the split the write side is the algorithmic figure: every output byte must
+    reach DRAM eventually.  None when the kernel was not captured."""
     p = ROOT / "profiles" / "dram_traffic.json"
     if not p.exists():
         return None
     try:
-        per_row = json.loads(p.read_text()).get(kernel, {}).get("dram_bytes_per_row")
+        rec = json.loads(p.read_text()).get(kernel, {})
+        if "read" in rec and "write_algorithmic" in rec:
+            return round((rec["read"] + rec["write_algorithmic"]) * units)
+        per_row = rec.get("dram_bytes_per_row")
         return None if per_row is None else per_row * units
     except Exception:  # noqa: BLE001
         return None
 
 
-def cpu_measure(wl: Workload, budget_s: float = 12.0):
+def cpu_measure(wl: Workload, cpu=None, budget_s: float = 12.0):
     rows = wl.cpu_sample_rows
-    cpu = wl.make_cpu_state(rows)
+    if cpu is None:
+        cpu = wl.make_cpu_state(rows)
     torch.set_num_threads(os.cpu_count() or 1)
     wl.cpu_step(cpu)  # warm-up
     times = []
@@ -329,14 +425,230 @@ def run_reference(args, wl: Workload, rank: int):
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16->f32 accumulate",
-        "data": "synthetic", "config": {"workload": f"{wl.name}: {wl.describe()}", "rows_per_step": rows},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 storage, f32 accumulate",
+        "data": "synthetic", "config": {"workload": f"{wl.name}: {wl.describe()}", "global_rows": wl.rows,
+                                        "rows_per_step": rows},
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------
+# device timing of one workload
+# --------------------------------------------------------------------------------------------------
+SHORT_REGION_MS = 50.0
+REPEATS = 9
+
+
+class StepRunner:
+    """Runs steps of a workload either call by call (prepared C-ABI calls) or by replaying a CUDA graph that holds
+    one cycle of the workload's rotating buffers."""
+
+    def __init__(self, wl, capi, st, world, dev, want_graph, steps):
+        self.wl, self.capi, self.st, self.world = wl, capi, st, world
+        self.graph = None
+        self.graph_note = "off"
+        self.cycle = getattr(wl, "cycle", 1)
+        self.launches_per_step = wl.launches_per_step
+        if hasattr(wl, "prepare"):
+            wl.prepare(capi, st)
+        if want_graph and hasattr(wl, "capture_cycle"):
+            if steps % self.cycle == 0:
+                self._capture(dev)
+            else:
+                self.graph_note = f"off (--steps {steps} is no whole number of {self.cycle}-step cycles)"
+
+    def _capture(self, dev):
+        wl, st, world = self.wl, self.st, self.world
+        cs, side = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        try:
+            with torch.cuda.stream(cs):
+                wl.prepare(self.capi, st)        # the prepared calls carry the stream they are to run on
+                for _ in range(2):               # warm-up on the capture stream (lazy attribute set-up, NCCL channels)
+                    wl.capture_cycle(self.capi, st, world, cs, side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=cs):
+                wl.capture_cycle(self.capi, st, world, cs, side)
+            self.graph = g
+            self.graph_note = f"on: one graph per {self.cycle} step(s)"
+        except Exception as exc:  # noqa: BLE001
+            torch.cuda.synchronize()
+            self.graph = None
+            self.graph_note = f"off (capture failed: {type(exc).__name__}: {str(exc)[:120]})"
+            if hasattr(wl, "prepare"):
+                wl.prepare(self.capi, st)        # back onto the current stream
+
+    def run(self, steps):
+        if self.graph is not None:
+            for _ in range(max(1, steps // self.cycle)):
+                self.graph.replay()
+            return
+        for _ in range(steps):
+            self.wl.step(self.capi, self.st, self.world)
+
+    def finish(self):
+        if hasattr(self.wl, "finish"):
+            self.wl.finish(self.st)
+
+
+def time_regions(runner: StepRunner, steps: int, world: int, dev, barrier):
+    """-> (list of region times in ms, max over ranks each; host seconds per region; wall-clock span)"""
+    regions, host = [], []
+    t_begin = time.perf_counter()
+    while True:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0 = time.perf_counter()
+        e0.record()
+        runner.run(steps)
+        runner.finish()  # outstanding collectives join the timed stream before the closing event
+        e1.record()
+        host.append(time.perf_counter() - h0)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        regions.append(ms)
+        # every rank takes the same decision: it is made on the all-reduced time of the first region
+        if len(regions) >= (REPEATS if regions[0] < SHORT_REGION_MS else 1):
+            break
+    return regions, host, (t_begin, time.perf_counter())
+
+
+def profile_kernels(runner: StepRunner, capi, steps: int, barrier):
+    """Per-launch CUDA events around every main kernel, call by call (never from the graph: an event pair between
+    two kernels also keeps the second from starting under the first's tail, so these are upper bounds)."""
+    g, runner.graph = runner.graph, None
+    if g is not None and hasattr(runner.wl, "prepare"):
+        runner.wl.prepare(capi, runner.st)
+    capi.profile_begin()
+    runner.run(steps)
+    runner.finish()
+    prof = capi.profile_end()
+    barrier()
+    runner.graph = g
+    return prof
+
+
+def copy_gbs_at_size(nbytes: int, dev, iters: int = 40):
+    """torch copy_ between rotating buffers of `nbytes` each (read + write bytes / time): the copy figure at THIS
+    problem's size, launch latency included, beside the 2 GiB figure the roofline's peak comes from."""
+    nbuf = max(2, min(16, (1 << 30) // max(nbytes, 1)))
+    src = [torch.empty(nbytes, dtype=torch.uint8, device=dev).fill_(i) for i in range(nbuf)]
+    dst = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(nbuf)]
+    for i in range(nbuf):
+        dst[i].copy_(src[i])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        dst[i % nbuf].copy_(src[i % nbuf])
+    e1.record()
+    torch.cuda.synchronize()
+    return 2 * nbytes * iters / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+
+def measure_workload(wl, capi, st, world, rank, dev, steps, warmup, rows, global_rows, scaling, want_graph, barrier):
+    runner = StepRunner(wl, capi, st, world, dev, want_graph, steps)
+    runner.run(-(-max(warmup, 1) // runner.cycle) * runner.cycle)
+    runner.finish()
+    barrier()
+    regions, host, span = time_regions(runner, steps, world, dev, barrier)
+    ms = statistics.median(regions)
+    status = capi.device_status()
+    assert status == 0, f"device status {status}"
+    prof = profile_kernels(runner, capi, min(steps, 50), barrier)
+    peak, peak_kind = measured_peak()
+    bytes_local = wl.bytes_per_rows(rows)
+    kernels = {}
+    for name, (n, total_ms) in prof.items():
+        us = total_ms / n * 1e3
+        entry = {"us_per_launch": round(us, 2), "launches_timed": n}
+        if name in bytes_local:
+            gbs = bytes_local[name] / (us * 1e-6) / 1e9
+            entry.update({"achieved": round(gbs, 1), "frac": round(gbs / peak, 4),
+                          "frac_of_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 4)})
+        kernels[name] = entry
+    top = max(prof, key=lambda k: prof[k][1])
+    total_bytes = wl.bytes_per_rows(global_rows)["total"] if scaling == "strong" else bytes_local["total"] * world
+    out = {
+        "ms_per_step": ms / steps, "value": total_bytes * steps / (ms * 1e-3) / 1e9, "total_bytes": total_bytes,
+        "spread": {"regions": len(regions), "min_ms_per_step": round(min(regions) / steps, 5),
+                   "max_ms_per_step": round(max(regions) / steps, 5)},
+        "host_enqueue_us_per_step": round(statistics.median(host) / steps * 1e6, 2),
+        "graph": runner.graph_note, "kernels": kernels, "top_kernel": top, "peak": peak, "peak_kind": peak_kind,
+        "span": span, "launches": runner.launches_per_step * steps * len(regions), "runner": runner,
+    }
+    return out
+
+
+def roofline_of(res, wl, rows):
+    k = res["kernels"][res["top_kernel"]]
+    return {"bound": "hbm", "kernel": res["top_kernel"], "achieved": k.get("achieved"), "peak": res["peak"], "unit": "GB/s",
+            "frac": k.get("frac"), "peak_kind": res["peak_kind"], "frac_of_nominal_8TBs": k.get("frac_of_nominal_8TBs"),
+            "us_per_launch": k["us_per_launch"], "launches_timed": k["launches_timed"],
+            "traffic": recorded_traffic(res["top_kernel"], rows, wl.bytes_per_rows(rows).get(res["top_kernel"])),
+            "all_kernels": res["kernels"],
+            "note": "per-launch times come from a separate call-by-call pass with an event pair around each launch; "
+                    "the step's ms_per_step is the back-to-back figure"}
+
+
+def collective_time_us(wl, st, world, iters: int = 20):
+    """One in-stream all-reduce of the step's buffer between its own events (median of `iters`)."""
+    if world <= 1 or not hasattr(wl, "collective_buffer"):
+        return None
+    buf = wl.collective_buffer(st).clone()
+    for _ in range(3):
+        dist.all_reduce(buf)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.all_reduce(buf)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return round(statistics.median(times), 2)
+
+
+def run_other_configs(capi, dev, steps_of, barrier):
+    """Short runs of the other BASELINE configs on this GPU: value, step time and per-kernel roofline each."""
+    _load_more_workloads()
+    out = {}
+    for name in ("cfg1", "cfg2", "cfg3", "cfg5", "cfg5f", "ln_long"):
+        if name not in WORKLOADS:
+            continue
+        wl = WORKLOADS[name]()
+        try:
+            st = wl.make_device_state(wl.rows, dev, seed=4001)
+            steps = steps_of(name)
+            res = measure_workload(wl, capi, st, 1, 0, dev, steps, 3, wl.rows, wl.rows, "strong", True, barrier)
+            entry = {"workload": wl.describe(), "value": round(res["value"], 1), "unit": "GB/s", "steps": steps,
+                     "ms_per_step": round(res["ms_per_step"], 5), "spread": res["spread"],
+                     "pct_of_peak_measured": round(100 * res["value"] / res["peak"], 2),
+                     "pct_of_peak_nominal": round(100 * res["value"] / NOMINAL_HBM_GBS, 2),
+                     "graph": res["graph"], "l2": wl.l2_note, "kernels": res["kernels"],
+                     "host_enqueue_us_per_step": res["host_enqueue_us_per_step"]}
+            tensor_bytes = getattr(wl, "tensor_bytes", None)
+            if tensor_bytes is not None and tensor_bytes < (1 << 29):
+                c = copy_gbs_at_size(tensor_bytes, dev)
+                entry["copy_same_size_gbs"] = round(c, 1)
+                entry["pct_of_copy_same_size"] = round(100 * res["value"] / c, 2)
+            out[name] = entry
+            res["runner"] = None
+            del res, st
+        except Exception as exc:  # noqa: BLE001
+            out[name] = {"error": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -349,10 +661,13 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"])
     ap.add_argument("--collective", default="async", choices=["async", "sync", "none"],
                     help="cfg4 gradient all-reduce: overlapped with the next step, in-stream, or (diagnostic) skipped")
+    ap.add_argument("--graph", default="on", choices=["on", "off"],
+                    help="replay the steps from a CUDA graph (where the workload supports it) or enqueue them call by call")
     ap.add_argument("--sm-margin", type=int, default=-1,
                     help="SMs the persistent kernels leave free for a collective kernel running beside them (default: 4 from N=4 on, else 0)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the short runs of the other BASELINE configs")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--rows", type=int, default=0, help="override the workload's global row count (small cases for ncu)")
     args = ap.parse_args()
@@ -382,20 +697,20 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     import b200norm
     from b200norm import capi, shard
-    # From four GPUs on, the collective's kernel gets four SMs of its own: measured at N = 8 the step is 132 us with
-    # that margin, 163 us without (the all-reduce then waits for a kernel boundary and delays the next kernel's CTAs),
-    # 126 us with no collective at all; at N = 2 the all-reduce is too short for the margin to pay.
-    # Only the config-4 step has a collective that overlaps kernels; the others keep every SM.
+    # From four GPUs on, the collective's kernel gets four SMs of its own (a ring CTA fills its SM, so without
+    # them the all-reduce waits for a kernel boundary and then delays the next kernel's CTAs); at N = 2 the
+    # all-reduce is too short for the margin to pay.  Only the config-4 step has a collective that overlaps kernels.
     overlapped = world >= 4 and args.workload == "cfg4" and COLLECTIVE_MODE == "async"
     sm_margin = args.sm_margin if args.sm_margin >= 0 else (4 if overlapped else 0)
     capi.set_tuning(b200norm.TUNE_SM_MARGIN, sm_margin)
 
     b200norm.load_library()
     if args.scaling == "strong":
-        r0, r1 = shard.shard_rows(wl.rows, world, rank)
-        rows = r1 - r0
+        rows_of = lambda r: (lambda a_b: a_b[1] - a_b[0])(shard.shard_rows(wl.rows, world, r))  # noqa: E731
+        rows = rows_of(rank)
         global_rows = wl.rows
     else:
+        rows_of = lambda r: wl.rows  # noqa: E731
         rows = wl.rows
         global_rows = wl.rows * world
     st = wl.make_device_state(rows, dev, seed=4001 + rank)
@@ -407,59 +722,24 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        wl.step(capi, st, world)
-    if hasattr(wl, "finish"):
-        wl.finish(st)
-    barrier()
-    n0 = capi.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_begin = time.perf_counter()
-    e0.record()
-    for _ in range(args.steps):
-        wl.step(capi, st, world)
-    if hasattr(wl, "finish"):
-        wl.finish(st)  # outstanding collectives join the timed stream before the closing event
-    e1.record()
-    barrier()
-    t_end = time.perf_counter()
-    launches = capi.launch_count() - n0
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
-    clocks = sampler.summary(t_begin, t_end)
-    status = capi.device_status()
-    assert status == 0, f"device status {status}"
-
-    # roofline of the dominant kernel: per-launch CUDA events on the launching stream, same steps again
-    prof_steps = min(args.steps, 50)
-    capi.profile_begin()
-    for _ in range(prof_steps):
-        wl.step(capi, st, world)
-    if hasattr(wl, "finish"):
-        wl.finish(st)
-    prof = capi.profile_end()
-    barrier()
-    kernel = max(prof, key=lambda k: prof[k][1])
-    k_launches, k_ms = prof[kernel]
-    per_launch_ms = k_ms / k_launches
-    bytes_local = wl.bytes_per_rows(rows)
-    peak, peak_kind = measured_peak()
-    achieved = bytes_local[kernel] / (per_launch_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": kernel, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "peak_kind": peak_kind,
-                "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
-                "us_per_launch": round(per_launch_ms * 1e3, 2), "launches_timed": k_launches,
-                "traffic": recorded_traffic(kernel, rows),
-                "all_kernels_us": {k: round(v[1] / v[0] * 1e3, 2) for k, v in prof.items()}}
-
-    total_bytes = wl.bytes_per_rows(global_rows)["total"] if args.scaling == "strong" else bytes_local["total"] * world
-    value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+    if world > 1:  # NCCL's communicator and channels exist before anything is timed or captured
+        dist.all_reduce(torch.zeros(1, device=dev))
+        barrier()
+    res = measure_workload(wl, capi, st, world, rank, dev, args.steps, args.warmup, rows, global_rows, args.scaling,
+                           args.graph == "on", barrier)
+    clocks = sampler.summary(*res["span"])
+    roofline = roofline_of(res, wl, rows)
+    coll_us = collective_time_us(wl, st, world)
+    shard_check = None
+    if world > 1 and hasattr(wl, "shard_check") and COLLECTIVE_MODE != "none":
+        shard_check = wl.shard_check(capi, st, world, rank, rows_of)
+        barrier()
+    value, total_bytes, peak = res["value"], res["total_bytes"], res["peak"]
+    res["runner"] = None
 
     # end to end through the ATen dispatcher with host buffers
     e2e = None
+    es = None
     if not args.no_e2e:
         b200norm.enable_aten_overrides()
         es = wl.make_e2e_state(rows, dev)
@@ -483,26 +763,40 @@ def main():
                "ms_per_step": round(ems / args.e2e_steps, 3), "steps": args.e2e_steps,
                "api": "torch.ops.aten.* on CUDA tensors via the dispatcher override; pinned host buffers, "
                       f"{wl.e2e_chunks} row chunks on 3 streams"}
-        del es
     sampler.stop()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        cpu = cpu_measure(wl)
+        cpu_state = wl.cpu_state_from_e2e(es) if (es is not None and hasattr(wl, "cpu_state_from_e2e")
+                                                  and wl.cpu_sample_rows == rows) else None
+        cpu = cpu_measure(wl, cpu_state)
+    del es
+
+    configs = None
+    if world == 1 and args.workload == "cfg4" and args.rows == 0 and not args.no_configs:
+        del st
+        torch.cuda.empty_cache()
+        configs = run_other_configs(capi, dev, lambda name: {"cfg1": 64, "cfg2": 40, "cfg3": 10, "cfg5": 4,
+                                                              "cfg5f": 4, "ln_long": 10}[name], barrier)
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": round(res["ms_per_step"], 5), "higher_is_better": True,
             "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16 storage, f32 accumulate", "data": "synthetic",
             "config": {"workload": f"{wl.name}: {wl.describe()}", "global_rows": global_rows, "rows_per_gpu": rows,
-                       "sm_margin": sm_margin, "parallelism": f"row-sharded dp{world}", "l2": "inputs larger than L2 (no flush needed)",
+                       "sm_margin": sm_margin, "parallelism": f"row-sharded dp{world}", "l2": wl.l2_note,
+                       "graph": res["graph"],
                        "collective": (getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, " + {"async": "overlapped with the next step", "sync": "in stream", "none": "SKIPPED (diagnostic run)"}[COLLECTIVE_MODE]) if world > 1 else "none")},
+            "spread": res["spread"], "host_enqueue_us_per_step": res["host_enqueue_us_per_step"],
+            "collective_us": coll_us, "shard_check": shard_check,
             "pct_of_peak_measured": round(100 * value / world / peak, 2),
             "pct_of_peak_nominal": round(100 * value / world / NOMINAL_HBM_GBS, 2),
-            "rows_per_s": round(global_rows * args.steps / (ms * 1e-3), 1),
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "rows_per_s": round(global_rows / (res["ms_per_step"] * 1e-3), 1),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(res["launches"]), "clocks": clocks,
         }
+        if configs is not None:
+            line["configs"] = configs
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

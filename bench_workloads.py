@@ -37,6 +37,9 @@ class Cfg1LayerNormFwd(_Simple):
     name, rows, N, cpu_sample_rows = "cfg1", 4096, 1024, 4096
     e2e_inputs = ("x",)
     launches_per_step = 1
+    cycle = 16
+    tensor_bytes = 4096 * 1024 * 4
+    l2_note = "tensors (16 MiB) smaller than L2: 16 rotating input/output sets, 0.5 GB, so no launch finds its rows in L2"
 
     def describe(self):
         return "native_layer_norm fwd, fp32 [4096, 1024], eps 1e-5 (launch-bound: 33.6 MB)"
@@ -62,9 +65,17 @@ class Cfg1LayerNormFwd(_Simple):
         st["i"] = 0
         return st
 
+    def prepare(self, capi, st):
+        st["calls"] = [capi.prepare_layer_norm(st["xs"][i], st["gamma"], st["beta"], 1e-5, st["ys"][i], st["mean"], st["rstd"])
+                       for i in range(16)]
+
     def step(self, capi, st, world):
         i = st["i"] = (st["i"] + 1) % 16
-        capi.native_layer_norm(st["xs"][i], [self.N], st["gamma"], st["beta"], 1e-5, out=(st["ys"][i], st["mean"], st["rstd"]))
+        st["calls"][i]()
+
+    def capture_cycle(self, capi, st, world, cs, side):
+        for call in st["calls"]:
+            call()
 
     def cpu_step(self, cpu):
         return torch.ops.aten.native_layer_norm(cpu["x"], [self.N], cpu["gamma"], cpu["beta"], 1e-5)
@@ -83,7 +94,10 @@ class Cfg2RmsNorm(_Simple):
     name, rows, N, cpu_sample_rows = "cfg2", 8192, 4096, 8192
     collective = "all_reduce(fp32[2,N]) per step"
     e2e_inputs = ("x", "dy")
-    launches_per_step = 3
+    launches_per_step = 2
+    cycle = 4
+    tensor_bytes = 8192 * 4096 * 2
+    l2_note = "tensors (64 MiB) smaller than L2: 4 rotating sets of x, dy, y, dx (1 GiB working set)"
 
     def describe(self):
         return "_fused_rms_norm fwd + _fused_rms_norm_backward (dx, dweight), bf16 [8192, 4096], fp32 weight, eps 1e-6"
@@ -114,14 +128,28 @@ class Cfg2RmsNorm(_Simple):
         st["i"] = 0
         return st
 
+    def prepare(self, capi, st):
+        st["calls"] = [(capi.prepare_rms_norm(s["x"], st["weight"], 1e-6, s["y"], st["rstd"]),
+                        capi.prepare_rms_norm_backward(s["dy"], s["x"], st["rstd"], st["weight"], s["dx"], st["wgrad"][0],
+                                                       st["ws"])) for s in st["sets"]]
+
     def step(self, capi, st, world):
         i = st["i"] = (st["i"] + 1) % 4
-        s, n = st["sets"][i], self.N
-        capi._fused_rms_norm(s["x"], [n], st["weight"], 1e-6, out=(s["y"], st["rstd"]))
-        capi._fused_rms_norm_backward(s["dy"], s["x"], [n], st["rstd"], st["weight"], (True, True),
-                                      out=(s["dx"], st["wgrad"][0]), workspace=st["ws"])
+        fwd, bwd = st["calls"][i]
+        fwd()
+        bwd()
         if world > 1:
             dist.all_reduce(st["wgrad"])
+
+    def capture_cycle(self, capi, st, world, cs, side):
+        for fwd, bwd in st["calls"]:
+            fwd()
+            bwd()
+            if world > 1:
+                dist.all_reduce(st["wgrad"])
+
+    def collective_buffer(self, st):
+        return st["wgrad"]
 
     def cpu_step(self, cpu):
         # no CPU kernel exists for _fused_rms_norm(_backward): autograd through the CPU composite
@@ -150,6 +178,7 @@ class Cfg3Softmax(_Simple):
     collective = "none (rows are independent)"
     rows = 8 * 32 * 2048
     e2e_inputs = ("s", "g")
+    l2_note = "inputs (2 GiB per tensor) larger than L2 (no flush needed)"
 
     def describe(self):
         return ("_softmax + _softmax_backward_data over the last dim, bf16 [8, 32, 2048, 2048] causal scores "
@@ -263,6 +292,7 @@ class Cfg5CrossEntropy(_Simple):
     collective = "all_reduce(fp32[2]: loss sum, weight sum) per step"
     e2e_inputs = ("logits", "target")
     launches_per_step = 6
+    l2_note = "inputs (3.9 GiB per tensor) larger than L2 (no flush needed)"
 
     def describe(self):
         return ("_log_softmax + nll_loss_forward(mean) + nll_loss_backward + _log_softmax_backward_data, "
@@ -360,6 +390,18 @@ class Cfg5FusedTail(Cfg5CrossEntropy):
         loss = capi.cross_entropy(x, st["target"])
         loss.backward()
         return loss.detach(), x.grad
+
+
+def layer_norm_long_rows(base):
+    """`base` is bench.Cfg4LayerNorm (handed in, so that this module never imports the script that imports it)."""
+
+    class LayerNormLongRows(base):
+        """Not a BASELINE config: layer norm on rows twice the length one CTA's threads hold (the reference's
+        few-long-rows regime, sycl/Norm.h:620-696), forward + backward with the weight gradients."""
+        name, rows, N, cpu_sample_rows = "ln_long", 16384, 16384, 2048
+        l2_note = "inputs (512 MiB per tensor) larger than L2 (no flush needed)"
+
+    return LayerNormLongRows
 
 
 EXTRA = {"cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,

@@ -86,6 +86,17 @@ const char* b2n_last_path(void);
 /* Reads and clears the device-side status word of the current device (synchronises `stream`).
  * 0, or the b2n_status recorded by a kernel (B2N_ERR_TIMEOUT, B2N_ERR_TARGET_RANGE). */
 int b2n_device_status(void* stream);
+/* The same word for callers that must not block (a dispatcher binding): b2n_status_post enqueues a
+ * copy of the word to a pinned host word behind the work already on `stream`; b2n_status_poll
+ * returns 0 while that copy is still to run, else the value it carried (and, when non-zero, clears
+ * the device word).  Neither synchronises.  The first b2n_status_post on a device allocates the
+ * pinned word and one event (cudaHostAlloc / cudaEventCreate) — the one allocation outside the
+ * caller's hands, made off the kernels' path; call it once before a stream capture begins if
+ * captures are used.  The reference traps on the device instead (SYCL_KERNEL_ASSERT in
+ * src/ATen/native/xpu/sycl/LossNLLKernel.cpp:30-35); a trap is not acceptable on a shared GPU, so
+ * the failure surfaces on the host, one call late. */
+int b2n_status_post(void* stream);
+int b2n_status_poll(void);
 
 /* Number of kernels this thread has launched through the library since it was loaded. */
 unsigned long long b2n_launch_count(void);

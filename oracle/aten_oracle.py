@@ -57,19 +57,21 @@ def ulp_distance(a: torch.Tensor, b: torch.Tensor) -> int:
     return int(d.max())
 
 
-def lowp_mismatch(a: torch.Tensor, ref: torch.Tensor, floor_scale: float = 1e-6):
-    """Gate for bf16/fp16 outputs: an element passes when it is within 1 ulp of the reference OR within the
-    absolute floor floor_scale * max(1, rms(ref)) — the same floor the fp32 gate uses.  The floor only matters
-    for outputs near zero, where one 16-bit ulp is smaller than the fp32 rounding error of the reference itself
-    (a difference of terms of size ~1).  Returns (number of failing elements, worst ulp distance among them)."""
+def lowp_report(a: torch.Tensor, ref: torch.Tensor, floor_scale: float = 1e-6) -> dict:
+    """Gate for bf16/fp16 outputs, with its accounting.  An element passes when it is within 1 ulp of the
+    reference OR within the absolute floor floor_scale * max(1, rms(ref)) — the same floor the fp32 gate uses.
+    An element can need the floor only where one 16-bit ulp of the reference is SMALLER than the floor (a
+    difference below one ulp is at most one ulp apart), i.e. for outputs near zero, where the fp32 rounding of
+    terms of size ~1 already exceeds that ulp.  Returned: 'bad' elements failing both tests and the 'worst' ulp
+    distance among them; 'floor_only' elements more than 1 ulp apart that passed through the floor; 'numel'."""
     assert a.dtype == ref.dtype and a.dtype in (torch.bfloat16, torch.float16), (a.dtype, ref.dtype)
     assert a.shape == ref.shape, (a.shape, ref.shape)
     if a.numel() == 0:
-        return 0, 0
+        return {"bad": 0, "worst": 0, "floor_only": 0, "numel": 0}
     a, ref = a.detach().cpu(), ref.detach().cpu()
     na, nb = torch.isnan(a), torch.isnan(ref)
     if not torch.equal(na, nb):
-        return int((na != nb).sum()), 1 << 30
+        return {"bad": int((na != nb).sum()), "worst": 1 << 30, "floor_only": 0, "numel": a.numel()}
     d = (_ordered_int(a) - _ordered_int(ref)).abs()
     d = torch.where(na, torch.zeros_like(d), d)
     af, rf = a.double(), ref.double()
@@ -80,7 +82,26 @@ def lowp_mismatch(a: torch.Tensor, ref: torch.Tensor, floor_scale: float = 1e-6)
     absdiff = torch.where(af == rf, torch.zeros_like(absdiff), absdiff)  # equal infinities
     bad = (d > 1) & (absdiff > floor)
     n_bad = int(bad.sum())
-    return n_bad, (int(d[bad].max()) if n_bad else 0)
+    return {"bad": n_bad, "worst": int(d[bad].max()) if n_bad else 0,
+            "floor_only": int(((d > 1) & (absdiff <= floor)).sum()), "numel": a.numel()}
+
+
+def lowp_mismatch(a: torch.Tensor, ref: torch.Tensor, floor_scale: float = 1e-6):
+    """(number of failing elements, worst ulp distance among them) of lowp_report."""
+    r = lowp_report(a, ref, floor_scale)
+    return r["bad"], r["worst"]
+
+
+def strict_ulp_failures(a: torch.Tensor, ref64: torch.Tensor) -> int:
+    """Elements of the 16-bit tensor `a` more than 1 ulp from the float64 result rounded once to a's dtype — no
+    floor of any kind.  NaN patterns must coincide (a mismatch counts every element)."""
+    assert a.dtype in (torch.bfloat16, torch.float16) and ref64.dtype == torch.float64
+    a, r = a.detach().cpu(), ref64.detach().cpu().to(a.dtype)
+    na, nb = torch.isnan(a), torch.isnan(r)
+    if not torch.equal(na, nb):
+        return a.numel()
+    d = (_ordered_int(a) - _ordered_int(r)).abs()
+    return int(((d > 1) & ~na).sum())
 
 
 def fp32_err(a: torch.Tensor, b: torch.Tensor) -> float:
@@ -215,3 +236,40 @@ def cross_entropy_bwd(grad_out, logp, target, weight, reduction: int, ignore_ind
     grad = aten.nll_loss_backward(up(grad_out), y, _cpu(target), up(weight), reduction, ignore_index,
                                   up(total_weight))
     return aten._log_softmax_backward_data(grad, y, -1, wide).to(logp.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+# float64 evaluations (for strict_ulp_failures: the op on fp64 upcasts of the same 16-bit inputs)
+# ---------------------------------------------------------------------------------------------------
+def _f64(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    return None if t is None else t.detach().cpu().double()
+
+
+def layer_norm_fwd64(x, normalized_shape, weight, bias, eps):
+    return aten.native_layer_norm(_f64(x), list(normalized_shape), _f64(weight), _f64(bias), eps)
+
+
+def layer_norm_bwd64(dy, x, normalized_shape, mean, rstd, weight, bias):
+    return aten.native_layer_norm_backward(_f64(dy), _f64(x), list(normalized_shape), _f64(mean), _f64(rstd),
+                                           _f64(weight), _f64(bias), [True, True, True])
+
+
+def rms_norm_fwd64(x, normalized_shape, weight, eps):
+    return F.rms_norm(_f64(x), list(normalized_shape), _f64(weight), eps)
+
+
+def rms_norm_bwd64(dy, x, normalized_shape, weight, eps):
+    xf = _f64(x).requires_grad_(True)
+    wf = _f64(weight).requires_grad_(True)
+    y = F.rms_norm(xf, list(normalized_shape), wf, eps)
+    return torch.autograd.grad(y, [xf, wf], _f64(dy))
+
+
+def softmax_fwd64(x, dim, is_log: bool):
+    return (aten._log_softmax if is_log else aten._softmax)(_f64(x), dim, False)
+
+
+def softmax_bwd64(dy, y, dim, is_log: bool):
+    op = aten._log_softmax_backward_data if is_log else aten._softmax_backward_data
+    return op(_f64(dy), _f64(y), dim, torch.float64)
+

@@ -60,3 +60,56 @@ def ring_eligible(n: int, dtype, ept: int) -> bool:
         return False
     vec = 16 // esize
     return n % vec == 0 and n <= 512 * ept
+
+
+def seeded_rows_to_device(seed: int, M: int, N: int, dtype, std: float = 1.0, mean: float = 0.0, block: int = 4096,
+                          post=None) -> torch.Tensor:
+    """An [M, N] tensor drawn on the CPU from torch.Generator().manual_seed(seed) — fp32 normal draws in blocks of
+    `block` rows, scaled, optionally edited by post(block_fp32, first_row), rounded to `dtype` — and copied to the
+    device block by block.  The CPU oracle and the kernels then see bit-identical data without the whole fp32
+    tensor ever existing on the host."""
+    g = torch.Generator(device="cpu").manual_seed(int(seed))
+    out = torch.empty((M, N), dtype=dtype, device=DEV)
+    for r in range(0, M, block):
+        k = min(block, M - r)
+        t = torch.randn((k, N), generator=g, dtype=torch.float32)
+        if std != 1.0:
+            t *= std
+        if mean != 0.0:
+            t += mean
+        if post is not None:
+            t = post(t, r)
+        out[r:r + k] = t.to(dtype)
+    return out
+
+
+def gate_16bit(name: str, got: torch.Tensor, ref_exact: torch.Tensor, ref64: torch.Tensor, cpu_native=None):
+    """The 16-bit gate with its accounting, printed (pytest -s shows it) and asserted:
+    * no element beyond 1 ulp of the fp32-accumulated reference and the absolute floor;
+    * elements that needed the floor: at most 1 in 10 000 (they sit where one 16-bit ulp is below the floor);
+    * against the float64 evaluation rounded once, with NO floor: the kernel's count of elements beyond 1 ulp
+      does not exceed what the parity standard itself (CPU ATen on fp32 upcasts) leaves against float64, plus the
+      same 1 in 10 000 (both evaluate in fp32; neither can be exact where the output is a small difference)."""
+    from oracle import aten_oracle as ao
+    rep = ao.lowp_report(got, ref_exact)
+    strict = ao.strict_ulp_failures(got, ref64)
+    strict_ref = ao.strict_ulp_failures(ref_exact, ref64)
+    print(f"[parity] {name}: {rep['numel']} elements, beyond 1 ulp and floor {rep['bad']}, passed only through the floor "
+          f"{rep['floor_only']}, beyond 1 ulp of fp64 (no floor) {strict} (CPU ATen fp32 itself: {strict_ref})")
+    assert rep["bad"] == 0, f"{name}: {rep['bad']} elements beyond 1 ulp and the floor (worst {rep['worst']} ulp)"
+    allowance = max(1, rep["numel"] // 10000)
+    assert rep["floor_only"] <= allowance, f"{name}: {rep['floor_only']} elements needed the floor"
+    assert strict <= strict_ref + allowance, f"{name}: {strict} elements beyond 1 ulp of fp64 (reference: {strict_ref})"
+
+
+def wgrad_gate(a: torch.Tensor, terms: torch.Tensor, what: str) -> None:
+    """Weight-gradient gate.  a: kernel result [N]; terms: fp64 [M, N] summands.  fp32 results: within 1e-6 of the
+    L1 norm of the terms of the fp64 sum; 16-bit results: 1 ulp of the fp64 sum rounded once, or that same bound."""
+    from oracle import aten_oracle as ao
+    ref = terms.sum(0)
+    l1 = terms.abs().sum(0).clamp_min(1e-30)
+    err = float(((a.detach().cpu().double().reshape(-1) - ref.reshape(-1)).abs() / l1.reshape(-1)).max())
+    if a.dtype in (torch.bfloat16, torch.float16):
+        assert ao.ulp_distance(a.detach().cpu().reshape(-1), ref.reshape(-1).to(a.dtype)) <= 1 or err <= 1e-6, f"{what}: {err:.3e} of L1"
+    else:
+        assert err <= 1e-6, f"{what}: {err:.3e} of L1"

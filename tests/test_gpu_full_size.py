@@ -1,8 +1,13 @@
 """The five workloads at their full sizes.  A CPU oracle over gigabytes would take minutes, so each
-case checks (a) sampled rows bit-for-bit (<= 1 ulp / 1e-5) against the oracle and (b) properties that
+case checks (a) sampled rows (<= 1 ulp / 1e-5) against the oracle and (b) properties that
 hold for every row: softmax rows sum to one and masked entries are exactly zero, log-softmax rows have
 zero log-sum-exp, weight gradients are additive over row blocks (what row sharding relies on), the
-loss equals the mean of the gathered log-probabilities."""
+loss equals the mean of the gathered log-probabilities.
+
+Inputs come from the seeded CPU generator, seed = 1000 * config + tensor index, drawn in row blocks
+(gpu_util.seeded_rows_to_device), so the oracle and the kernels see the same bits.  Each 16-bit comparison
+goes through gpu_util.gate_16bit, which also counts the elements that pass only through the absolute
+floor and compares against the float64 evaluation without any floor."""
 import math
 
 import pytest
@@ -12,7 +17,7 @@ import b200norm
 from b200norm import capi
 from oracle import aten_oracle as ao
 
-from gpu_util import DEV
+from gpu_util import DEV, gate_16bit, seeded_rows_to_device
 
 pytestmark = pytest.mark.gpu
 
@@ -46,19 +51,27 @@ def test_config2_rms_norm_bf16_8192x4096_full_compare():
     assert capi.last_path() == "ring"
     ry, rrstd = ao.rms_norm_fwd(x, [N], w, 1e-6)
     rdx, rdw = ao.rms_norm_bwd(dy, x, [N], w, 1e-6)
-    assert ao.lowp_mismatch(y, ry)[0] == 0 and ao.lowp_mismatch(dx, rdx)[0] == 0
+    gate_16bit("config 2 y", y, ry, ao.rms_norm_fwd64(x, [N], w, 1e-6))
+    dx64, dw64 = ao.rms_norm_bwd64(dy, x, [N], w, 1e-6)
+    gate_16bit("config 2 dx", dx, rdx, dx64)
     terms = dy.double() * x.double() * rrstd.double()
     err = ((dw.cpu().double() - terms.sum(0)).abs() / terms.abs().sum(0)).max()
     assert float(err) <= 1e-6, float(err)
-    assert torch.allclose(dw.cpu(), rdw, rtol=1e-4, atol=1e-3)
+    # ... and against the autograd result of the fp64 composite, on the same L1 scale
+    err64 = ((dw.cpu().double() - dw64).abs() / terms.abs().sum(0)).max()
+    assert float(err64) <= 1e-6, float(err64)
 
 
 def test_config3_causal_softmax_bf16_8x32x2048x2048():
     B, H, T = 8, 32, 2048
-    gen = torch.Generator(device=DEV).manual_seed(3001)
-    s = (torch.randn((B, H, T, T), generator=gen, device=DEV, dtype=torch.float32) / math.sqrt(128)).to(torch.bfloat16)
+    cols = torch.arange(T).view(1, -1)
+
+    def causal(block, first_row):  # strict upper triangle of every [T, T] slice at -inf, before the rounding
+        rows = (torch.arange(first_row, first_row + block.shape[0]) % T).view(-1, 1)
+        return block.masked_fill_(cols > rows, float("-inf"))
+
+    s = seeded_rows_to_device(3001, B * H * T, T, torch.bfloat16, std=1.0 / math.sqrt(128), post=causal).view(B, H, T, T)
     mask = torch.ones(T, T, dtype=torch.bool, device=DEV).triu(1)
-    s.masked_fill_(mask, float("-inf"))
     p = capi._softmax(s, -1, False)
     assert capi.last_path() == "ring"
     flat_s, flat_p = s.view(-1, T), p.view(-1, T)
@@ -67,13 +80,15 @@ def test_config3_causal_softmax_bf16_8x32x2048x2048():
     sums = flat_p.float().sum(-1)
     assert float((sums - 1).abs().max()) <= 4e-3
     idx = sample_rows(flat_s.shape[0])
-    assert ao.lowp_mismatch(flat_p[idx.to(DEV)], ao.softmax_fwd(flat_s[idx.to(DEV)].cpu(), -1, False))[0] == 0
-    g = torch.randn((B, H, T, T), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    xs = flat_s[idx.to(DEV)].cpu()
+    gate_16bit("config 3 softmax", flat_p[idx.to(DEV)], ao.softmax_fwd(xs, -1, False), ao.softmax_fwd64(xs, -1, False))
+    g = seeded_rows_to_device(3002, B * H * T, T, torch.bfloat16).view(B, H, T, T)
     dx = capi._softmax_backward_data(g, p, -1, torch.bfloat16)
     assert capi.last_path() == "ring"
     flat_g, flat_dx = g.view(-1, T), dx.view(-1, T)
-    ref = ao.softmax_bwd(flat_g[idx.to(DEV)].cpu(), flat_p[idx.to(DEV)].cpu(), -1, False, torch.bfloat16)
-    assert ao.lowp_mismatch(flat_dx[idx.to(DEV)], ref)[0] == 0
+    gs, ps = flat_g[idx.to(DEV)].cpu(), flat_p[idx.to(DEV)].cpu()
+    gate_16bit("config 3 softmax backward", flat_dx[idx.to(DEV)], ao.softmax_bwd(gs, ps, -1, False, torch.bfloat16),
+               ao.softmax_bwd64(gs, ps, -1, False))
     # softmax gradients sum to ~0 along the row, and are exactly zero where p is zero
     assert float(dx.masked_select(mask.expand_as(dx)).abs().max()) == 0.0
     assert float(flat_dx.float().sum(-1).abs().max()) <= 5e-2
@@ -82,9 +97,8 @@ def test_config3_causal_softmax_bf16_8x32x2048x2048():
 
 def test_config4_layer_norm_bf16_65536x8192():
     M, N = 65536, 8192
-    gen = torch.Generator(device=DEV).manual_seed(4001)
-    x = torch.randn((M, N), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
-    dy = torch.randn((M, N), generator=gen, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    x = seeded_rows_to_device(4001, M, N, torch.bfloat16)
+    dy = seeded_rows_to_device(4004, M, N, torch.bfloat16)
     g, b = ao.randn((N,), 4002, mean=1.0, std=0.02).to(DEV), ao.randn((N,), 4003, std=0.02).to(DEV)
     y, mean, rstd = capi.native_layer_norm(x, [N], g, b, 1e-5)
     assert capi.last_path() == "ring"
@@ -92,11 +106,13 @@ def test_config4_layer_norm_bf16_65536x8192():
     assert capi.last_path() == "ring"
     idx = sample_rows(M).to(DEV)
     ry, rmean, rrstd = ao.layer_norm_fwd(x[idx].cpu(), [N], g.cpu(), b.cpu(), 1e-5)
-    assert ao.lowp_mismatch(y[idx], ry)[0] == 0
+    y64, mean64, rstd64 = ao.layer_norm_fwd64(x[idx].cpu(), [N], g.cpu(), b.cpu(), 1e-5)
+    gate_16bit("config 4 y", y[idx], ry, y64)
     assert float((mean[idx].cpu() - rmean).abs().max()) <= 1e-6
     assert float(((rstd[idx].cpu() - rrstd) / rrstd).abs().max()) <= 1e-5
     rdx, _, _ = ao.layer_norm_bwd(dy[idx].cpu(), x[idx].cpu(), [N], rmean, rrstd, g.cpu(), b.cpu())
-    assert ao.lowp_mismatch(dx[idx], rdx)[0] == 0
+    dx64, _, _ = ao.layer_norm_bwd64(dy[idx].cpu(), x[idx].cpu(), [N], mean64, rstd64, g.cpu(), b.cpu())
+    gate_16bit("config 4 dx", dx[idx], rdx, dx64)
     # every row: the normalised output before the affine map has zero mean and unit variance
     z = (y[:4096].float() - b) / g
     assert float(z.mean(-1).abs().max()) <= 2e-3 and float((z.var(-1, unbiased=False) - 1).abs().max()) <= 1e-2
@@ -109,27 +125,26 @@ def test_config4_layer_norm_bf16_65536x8192():
     total = sum(parts)
     l1 = (dy[:, :64].double().abs()).sum(0)  # L1 scale of the dbeta terms on a column sample
     assert float(((total[1, :64] - db[:64].double()).abs() / l1).max()) <= 1e-6
-    assert torch.allclose(total[0].float(), dg, rtol=1e-3, atol=0.5)
+    xh64 = (x[:, :64].double() - mean.double().view(-1, 1)) * rstd.double().view(-1, 1)
+    l1g = (dy[:, :64].double() * xh64).abs().sum(0)  # L1 scale of the dgamma terms on the same column sample
+    assert float(((total[0, :64] - dg[:64].double()).abs() / l1g).max()) <= 1e-6
     # ... and dbeta equals an fp64 column sum of dy on a column sample
     ref_db = dy[:, :64].double().sum(0)
     assert float(((db[:64].double() - ref_db).abs() / l1).max()) <= 1e-6
-    xh = (x[:, :64].double() - mean.double()) * rstd.double()
-    terms = dy[:, :64].double() * xh
+    terms = dy[:, :64].double() * xh64
     assert float(((dg[:64].double() - terms.sum(0)).abs() / terms.abs().sum(0)).max()) <= 1e-6
     assert capi.device_status() == 0
 
 
 def test_config5_log_softmax_nll_bf16_16384x128256():
     M, V = 16384, 128256
-    gen = torch.Generator(device=DEV).manual_seed(5001)
-    logits = torch.empty((M, V), device=DEV, dtype=torch.bfloat16)
-    for k in range(0, M, 2048):  # fp32 normal draws in slabs keep the transient under 1.1 GB
-        logits[k:k + 2048] = (torch.randn((2048, V), generator=gen, device=DEV) * 2.0).to(torch.bfloat16)
+    logits = seeded_rows_to_device(5001, M, V, torch.bfloat16, std=2.0, block=1024)
     t = ao.randint(V, (M,), 5002).to(DEV)
     logp = capi._log_softmax(logits, -1, False)
     assert capi.last_path() in ("cluster", "twopass")
     idx = sample_rows(M, 24).to(DEV)
-    assert ao.lowp_mismatch(logp[idx], ao.softmax_fwd(logits[idx].cpu(), -1, True))[0] == 0
+    ls = logits[idx].cpu()
+    gate_16bit("config 5 log-softmax", logp[idx], ao.softmax_fwd(ls, -1, True), ao.softmax_fwd64(ls, -1, True))
     # every row: log-sum-exp of the output is zero up to the bf16 rounding of the entries
     lse = torch.cat([torch.logsumexp(logp[k:k + 1024].float(), -1) for k in range(0, M, 1024)])
     assert float(lse.abs().max()) <= 2e-2
@@ -143,8 +158,9 @@ def test_config5_log_softmax_nll_bf16_16384x128256():
     assert float(grad_logp.gather(1, t.view(-1, 1)).float().mean()) == pytest.approx(-1.0 / M, rel=1e-2)
     dlogits = capi._log_softmax_backward_data(grad_logp, logp, -1, torch.bfloat16)
     assert capi.last_path() in ("cluster", "twopass")
-    ref = ao.softmax_bwd(grad_logp[idx].cpu(), logp[idx].cpu(), -1, True, torch.bfloat16)
-    assert ao.lowp_mismatch(dlogits[idx], ref)[0] == 0
+    gl, lp = grad_logp[idx].cpu(), logp[idx].cpu()
+    gate_16bit("config 5 log-softmax backward", dlogits[idx], ao.softmax_bwd(gl, lp, -1, True, torch.bfloat16),
+               ao.softmax_bwd64(gl, lp, -1, True))
     # rows of the cross-entropy gradient sum to ~0
     rs = torch.cat([dlogits[k:k + 1024].float().sum(-1) for k in range(0, M, 1024)])
     assert float(rs.abs().max()) <= 1e-5

@@ -45,7 +45,10 @@ def check_wgrad(a, terms, what):
     ref = terms.sum(0)
     l1 = terms.abs().sum(0).clamp_min(1e-30)
     if a.dtype in (torch.bfloat16, torch.float16):
-        assert ao.ulp_distance(a.cpu(), ref.to(a.dtype)) <= 1 or torch.allclose(a.cpu().double(), ref, rtol=2e-2, atol=1e-3), what
+        # a 16-bit gradient is the fp32 sum rounded once: 1 ulp of the fp64 sum, or — where the sum cancels to
+        # less than its own rounding error — the same 1e-6 of the terms' L1 norm as the fp32 case
+        err = ((a.cpu().double() - ref).abs() / l1).max()
+        assert ao.ulp_distance(a.cpu(), ref.to(a.dtype)) <= 1 or err <= 1e-6, f"{what}: {float(err):.3e} of L1"
     else:
         err = ((a.cpu().double() - ref).abs() / l1).max()
         assert err <= 1e-6, f"{what}: {float(err):.3e} of L1"
@@ -141,10 +144,11 @@ def test_layer_norm_optional_affine(N, has_w, has_b):
     rdx, rdg, rdb = ao.layer_norm_bwd(dy, x, [N], rmean, rrstd, g, b, mask=(True, g is not None, b is not None))
     check_out(y, ry, "y"); check_out(dx, rdx, "dx")
     assert (dg is None) == (g is None) and (db is None) == (b is None)
+    xh = (x.double() - mean.cpu().double().reshape(-1, 1)) * rstd.cpu().double().reshape(-1, 1)
     if g is not None:
-        assert torch.allclose(dg.cpu(), rdg, rtol=1e-4, atol=1e-5)
+        check_wgrad(dg, dy.double() * xh, "dgamma")
     if b is not None:
-        assert torch.allclose(db.cpu(), rdb, rtol=1e-4, atol=1e-5)
+        check_wgrad(db, dy.double(), "dbeta")
 
 
 @pytest.mark.parametrize("mask", [(True, False, False), (False, True, True), (True, True, False), (False, False, True)])
@@ -158,10 +162,11 @@ def test_layer_norm_backward_masks(mask):
     assert (dx is not None) == mask[0] and (dg is not None) == mask[1] and (db is not None) == mask[2]
     if dx is not None:
         assert ao.lowp_mismatch(dx, rdx)[0] == 0
+    xh = (x.double() - mean.cpu().double().reshape(-1, 1)) * rstd.cpu().double().reshape(-1, 1)
     if dg is not None:
-        assert torch.allclose(dg.cpu(), rdg, rtol=1e-4, atol=1e-4)
+        check_wgrad(dg, dy.double() * xh, "dgamma")
     if db is not None:
-        assert torch.allclose(db.cpu(), rdb, rtol=1e-4, atol=1e-4)
+        check_wgrad(db, dy.double(), "dbeta")
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])

@@ -15,7 +15,10 @@ from gpu_util import DEV, forced_path, guarded_empty, misaligned
 pytestmark = pytest.mark.gpu
 
 ROW_SHAPES = [(1, 1), (3, 5), (7, 128), (33, 130), (129, 1000), (64, 2048), (40, 4096), (9, 8192), (4, 16384),
-              (3, 40000), (2, 128256)]
+              (3, 40000), (2, 128256),
+              # long rows that are NOT a whole number of 16-byte vectors (GPT-2's vocabulary among them): the
+              # two-pass kernels cannot take them, the generic ones must
+              (3, 40001), (2, 50257)]
 DTYPES = [torch.float32, torch.bfloat16, torch.float16]
 PATHS = [b200norm.PATH_AUTO, b200norm.PATH_GENERIC]
 
@@ -180,6 +183,20 @@ def test_ring_is_used_for_aligned_rows_and_refuses_others_when_forced():
     with forced_path(b200norm.PATH_RING):
         with pytest.raises(b200norm.B200NormError):
             capi._softmax(ao.randn((4, 33), 471).to(DEV), -1, False)  # 33 floats: not a multiple of 16 bytes
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_pinned_twopass_refuses_ragged_rows(dt):
+    # a row that is not a multiple of 16 bytes: the vector kernels would drop its tail and misplace every later row
+    x = ao.randn((3, 40001), 470, dt).to(DEV)
+    with forced_path(b200norm.PATH_TWOPASS):
+        with pytest.raises(b200norm.B200NormError):
+            capi._softmax(x, -1, False)
+        with pytest.raises(b200norm.B200NormError):
+            capi._log_softmax_backward_data(x, x, -1, dt)
+    y = capi._softmax(x, -1, False)
+    assert capi.last_path() == "generic"
+    check_out(y, ao.softmax_fwd(x.cpu(), -1, False), "y")
 
 
 @pytest.mark.parametrize("path,name", [(b200norm.PATH_CLUSTER, "cluster"), (b200norm.PATH_TWOPASS, "twopass")])

@@ -98,6 +98,10 @@ def _worker(rank, world, port, tmp):
         res = shard.rms_norm_step(ops, x[s:e], dy[s:e], g, 1e-6)
         _, dw = ao.rms_norm_bwd(dy, x, [N], g, 1e-6)
         assert torch.allclose(res.wgrad[0], dw, rtol=1e-5, atol=1e-5) and float(res.wgrad[1].abs().sum()) == 0.0
+        # a caller's reused buffer may hold anything: the dbeta row still comes back as zeros
+        dirty = torch.full((2, N), 7.0)
+        res = shard.rms_norm_step(ops, x[s:e], dy[s:e], g, 1e-6, wgrad_buf=dirty)
+        assert torch.allclose(res.wgrad[0], dw, rtol=1e-5, atol=1e-5) and float(res.wgrad[1].abs().sum()) == 0.0
 
         V = 29
         logits = ao.randn((M, V), 5, std=2.0)

@@ -63,6 +63,8 @@ def load_library() -> ctypes.CDLL:
         "b2n_set_tuning": (i32, [i32, i32]),
         "b2n_set_trace_buffer": (i32, [vp, sz]),
         "b2n_device_status": (i32, [vp]),
+        "b2n_status_post": (i32, [vp]),
+        "b2n_status_poll": (i32, []),
         "b2n_launch_count": (c.c_ulonglong, []),
         "b2n_profile_begin": (i32, []),
         "b2n_profile_end": (i32, [c.c_char_p, sz]),

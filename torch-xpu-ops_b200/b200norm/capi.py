@@ -123,6 +123,80 @@ def profile_end() -> dict:
     return out
 
 
+def check_status(device=None) -> None:
+    """Raise if a kernel on `device` has recorded a failure (an nll_loss target out of range, a bounded wait that
+    gave up).  Synchronises the current stream; the ATen overrides do the same check without blocking, one call late."""
+    st = device_status(device)
+    if st != OK:
+        raise B200NormError(st, "device status")
+
+
+class Prepared:
+    """One C-ABI call with every argument converted once: calling the object enqueues the kernels again on the
+    stream that was current when it was prepared.  For loops that launch the same operator on the same buffers
+    many times (a training step replayed, a benchmark), where the per-call argument checks of the operator
+    wrappers above would cost more host time than the kernels take on the device."""
+    __slots__ = ("fn", "args", "name", "keep")
+
+    def __init__(self, fn, args, name, keep):
+        self.fn, self.args, self.name, self.keep = fn, args, name, keep  # keep: the tensors whose pointers are baked in
+
+    def __call__(self):
+        rc = self.fn(*self.args)
+        if rc != OK:
+            raise B200NormError(rc, self.name)
+
+
+def prepare_layer_norm(x, gamma, beta, eps, y, mean, rstd) -> Prepared:
+    """native_layer_norm on preallocated contiguous tensors, as a Prepared call."""
+    _require_cuda(x, gamma, beta, y, mean, rstd)
+    lib = load_library()
+    M, N = _norm_dims(x, (x.shape[-1],), gamma, beta)
+    assert x.is_contiguous() and y.is_contiguous() and mean.numel() == M and rstd.numel() == M
+    args = (_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(mean), _ptr(rstd), M, N, float(eps), _dt(x.dtype),
+            _weight_dtype(x, gamma, beta), _stream(x))
+    return Prepared(lib.b2n_layer_norm_fwd, args, "b2n_layer_norm_fwd", (x, gamma, beta, y, mean, rstd))
+
+
+def prepare_layer_norm_backward(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, workspace) -> Prepared:
+    """native_layer_norm_backward on preallocated contiguous tensors, as a Prepared call."""
+    _require_cuda(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, workspace)
+    lib = load_library()
+    M, N = _norm_dims(x, (x.shape[-1],), gamma, None)
+    assert x.is_contiguous() and dy.is_contiguous() and (dx is None or dx.is_contiguous())
+    xdt, wdt = _dt(x.dtype), _weight_dtype(x, gamma, None)
+    nbytes = lib.b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, int(dgamma is not None or dbeta is not None))
+    if nbytes and (workspace is None or workspace.numel() < nbytes):
+        raise ValueError(f"workspace too small: need {nbytes} bytes")
+    args = (_ptr(dy), _ptr(x), _ptr(mean), _ptr(rstd), _ptr(gamma), _ptr(dx), _ptr(dgamma), _ptr(dbeta),
+            _ptr(workspace) if nbytes else None, nbytes, M, N, xdt, wdt, _stream(x))
+    return Prepared(lib.b2n_layer_norm_bwd, args, "b2n_layer_norm_bwd", (dy, x, mean, rstd, gamma, dx, dgamma, dbeta, workspace))
+
+
+def prepare_rms_norm(x, weight, eps, y, rstd) -> Prepared:
+    _require_cuda(x, weight, y, rstd)
+    lib = load_library()
+    M, N = _norm_dims(x, (x.shape[-1],), weight, weight)
+    assert x.is_contiguous() and y.is_contiguous() and rstd.numel() == M
+    args = (_ptr(x), _ptr(weight), _ptr(y), _ptr(rstd), M, N, float(eps), _dt(x.dtype), _weight_dtype(x, weight, None),
+            _stream(x))
+    return Prepared(lib.b2n_rms_norm_fwd, args, "b2n_rms_norm_fwd", (x, weight, y, rstd))
+
+
+def prepare_rms_norm_backward(dy, x, rstd, weight, dx, dweight, workspace) -> Prepared:
+    _require_cuda(dy, x, rstd, weight, dx, dweight, workspace)
+    lib = load_library()
+    M, N = _norm_dims(x, (x.shape[-1],), weight, weight)
+    assert x.is_contiguous() and dy.is_contiguous() and (dx is None or dx.is_contiguous())
+    xdt, wdt = _dt(x.dtype), _weight_dtype(x, weight, None)
+    nbytes = lib.b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, int(dweight is not None))
+    if nbytes and (workspace is None or workspace.numel() < nbytes):
+        raise ValueError(f"workspace too small: need {nbytes} bytes")
+    args = (_ptr(dy), _ptr(x), _ptr(rstd), _ptr(weight), _ptr(dx), _ptr(dweight), _ptr(workspace) if nbytes else None,
+            nbytes, M, N, xdt, wdt, _stream(x))
+    return Prepared(lib.b2n_rms_norm_bwd, args, "b2n_rms_norm_bwd", (dy, x, rstd, weight, dx, dweight, workspace))
+
+
 # ---- layer norm / RMS norm -------------------------------------------------------------------------
 def native_layer_norm(input, normalized_shape, weight=None, bias=None, eps=1e-5, out=None):
     """aten::native_layer_norm -> (Y, mean, rstd); mean/rstd in the accumulate dtype.

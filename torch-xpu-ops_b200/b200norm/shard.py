@@ -77,7 +77,8 @@ def rms_norm_step(ops, x_shard, dy_shard, weight, eps: float, group=None,
     n = x_shard.shape[-1]
     y, rstd = ops._fused_rms_norm(x_shard, [n], weight, eps)
     if wgrad_buf is None:
-        wgrad_buf = torch.zeros(2, n, dtype=torch.float32, device=x_shard.device)
+        wgrad_buf = torch.empty(2, n, dtype=torch.float32, device=x_shard.device)
+    wgrad_buf[1].zero_()  # RMS norm has no dbeta: the row is zeros whatever a reused buffer held before
     if weight.dtype == torch.float32:
         dx, _ = ops._fused_rms_norm_backward(dy_shard, x_shard, [n], rstd, weight, (True, True),
                                              out=(None, wgrad_buf[0]))

@@ -37,13 +37,30 @@ static int to_b2n_dtype(at::ScalarType t, const char* what) {
   }
 }
 
+// What a kernel could not report by trapping — an nll_loss target outside [0, C), a bounded wait that
+// gave up — sits in the library's device status word.  The operators that can set it enqueue a
+// non-blocking copy of the word behind their kernels (note_possible_device_failure); every later
+// operator call on that device looks at the copy once it has arrived and raises.  So the error
+// reaches the caller without any synchronisation on the hot path, one call late — the same way a
+// CUDA launch failure does.  The reference fails in the kernel instead (SYCL_KERNEL_ASSERT,
+// src/ATen/native/xpu/sycl/LossNLLKernel.cpp:30-35).
+static void raise_if_earlier_kernel_failed() {
+  const int st = b2n_status_poll();
+  TORCH_CHECK(st == B2N_OK, "b200norm: an earlier kernel on this device reported: ", b2n_strerror(st),
+              st == B2N_ERR_TARGET_RANGE ? " (nll_loss / cross_entropy: a target is outside [0, n_classes) and is not ignore_index; that row contributed nothing)" : "",
+              st == B2N_ERR_TIMEOUT ? " (the kernel left early: its output is incomplete)" : "");
+}
+
 static void check_status(int st, const char* op) {
   TORCH_CHECK(st == B2N_OK, "b200norm::", op, " failed: ", b2n_strerror(st),
               st == B2N_ERR_CUDA ? " (cudaError " : "", st == B2N_ERR_CUDA ? std::to_string(b2n_last_cuda_error()) : "",
               st == B2N_ERR_CUDA ? ")" : "");
+  raise_if_earlier_kernel_failed();
 }
 
 static void* cur_stream() { return static_cast<void*>(c10::cuda::getCurrentCUDAStream().stream()); }
+
+static void note_possible_device_failure() { b2n_status_post(cur_stream()); }
 
 static at::ScalarType acc_type_of(at::ScalarType t) { return t == at::kDouble ? at::kDouble : at::kFloat; }
 
@@ -450,6 +467,7 @@ static void nll_forward_into(const Tensor& self, const Tensor& target, const Ten
                                 to_b2n_dtype(self.scalar_type(), "nll_loss_forward"),
                                 t.scalar_type() == at::kByte ? 1 : 0, cur_stream()),
                "nll_loss_fwd");
+  note_possible_device_failure();
 }
 
 std::tuple<Tensor, Tensor> nll_loss_forward(const Tensor& self, const Tensor& target,
@@ -507,6 +525,7 @@ static void nll_backward_into(const Tensor& grad_output, const Tensor& self, con
                                 ignore_index, to_b2n_dtype(self.scalar_type(), "nll_loss_backward"),
                                 t.scalar_type() == at::kByte ? 1 : 0, cur_stream()),
                "nll_loss_bwd");
+  note_possible_device_failure();
 }
 
 Tensor nll_loss_backward(const Tensor& grad_output, const Tensor& self, const Tensor& target,

@@ -32,29 +32,43 @@ thread_local std::vector<ProfileRecord> tl_records;
 constexpr size_t kMaxProfileRecords = 1 << 16;
 
 struct PerDevice {
-  std::once_flag once;
+  std::mutex mu;
+  std::atomic<bool> ready{false};
   DeviceInfo info{};
   int* status_ptr = nullptr;
   unsigned* counters = nullptr;
+  // deferred status probe (b2n_status_post / b2n_status_poll): a pinned host word the status is copied
+  // to behind the caller's work, and the event that says the copy has happened
+  int* probe_host = nullptr;
+  cudaEvent_t probe_event = nullptr;
+  cudaStream_t probe_stream = nullptr;
+  bool probe_pending = false;
 };
 PerDevice g_devices[kMaxDevices];
 
+// Per-device set-up: attributes and the device addresses of the library's own words.  Only a
+// complete set-up is remembered; a failed lookup (a sticky error pending, a stream capture under
+// way) is tried again on the next call instead of leaving null pointers behind for good.
 PerDevice& current_device() {
   int dev = 0;
   cudaGetDevice(&dev);
   PerDevice& pd = g_devices[dev % kMaxDevices];
-  std::call_once(pd.once, [&pd, dev]() {
-    cudaDeviceGetAttribute(&pd.info.sm_count, cudaDevAttrMultiProcessorCount, dev);
-    cudaDeviceGetAttribute(&pd.info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_status_word) == cudaSuccess) pd.status_ptr = static_cast<int*>(p);
-    if (cudaGetSymbolAddress(&p, g_tile_counters) == cudaSuccess) pd.counters = static_cast<unsigned*>(p);
-  });
+  if (pd.ready.load(std::memory_order_acquire)) return pd;
+  std::lock_guard<std::mutex> lock(pd.mu);
+  if (pd.ready.load(std::memory_order_relaxed)) return pd;
+  bool ok = cudaDeviceGetAttribute(&pd.info.sm_count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess;
+  ok = ok && cudaDeviceGetAttribute(&pd.info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess;
+  void* p = nullptr;
+  if (ok && cudaGetSymbolAddress(&p, g_status_word) == cudaSuccess) pd.status_ptr = static_cast<int*>(p);
+  if (ok && cudaGetSymbolAddress(&p, g_tile_counters) == cudaSuccess) pd.counters = static_cast<unsigned*>(p);
+  if (ok && pd.status_ptr != nullptr && pd.counters != nullptr) pd.ready.store(true, std::memory_order_release);
+  else cudaGetLastError();  // the failure is reported by the launch that needed the pointers
   return pd;
 }
 }  // namespace
 
 const DeviceInfo& device_info() { return current_device().info; }
+bool device_ready() { return current_device().ready.load(std::memory_order_acquire); }
 int* device_status_ptr() { return current_device().status_ptr; }
 bool softmax_safe_mode() { return tl_softmax_safe; }
 unsigned* next_tile_counter() {
@@ -198,7 +212,51 @@ int b2n_device_status(void* stream) {
   if (check_cuda(cudaStreamSynchronize(st))) return B2N_ERR_CUDA;
   if (v != 0) {
     if (check_cuda(cudaMemsetAsync(p, 0, sizeof(int), st))) return B2N_ERR_CUDA;
+    // A kernel that gave up on a wait may have left its {next tile, finished} pair non-zero; the slot would
+    // be handed to another launch kTileCounterSlots launches later.  Nothing of this library is running on
+    // `st` now, so put every pair back to zero.
+    unsigned* ctrs = current_device().counters;
+    if (v == B2N_ERR_TIMEOUT && ctrs != nullptr &&
+        check_cuda(cudaMemsetAsync(ctrs, 0, 2 * kTileCounterSlots * sizeof(unsigned), st)))
+      return B2N_ERR_CUDA;
     if (check_cuda(cudaStreamSynchronize(st))) return B2N_ERR_CUDA;
+  }
+  return v;
+}
+
+int b2n_status_post(void* stream) {
+  PerDevice& pd = current_device();
+  if (!pd.ready.load(std::memory_order_acquire)) return B2N_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  std::lock_guard<std::mutex> lock(pd.mu);
+  if (pd.probe_host == nullptr) {
+    if (check_cuda(cudaHostAlloc(reinterpret_cast<void**>(&pd.probe_host), sizeof(int), cudaHostAllocDefault))) return B2N_ERR_CUDA;
+    *pd.probe_host = 0;
+    if (check_cuda(cudaEventCreateWithFlags(&pd.probe_event, cudaEventDisableTiming))) return B2N_ERR_CUDA;
+  }
+  if (pd.probe_pending) return B2N_OK;  // one probe in flight is enough: it sees whatever is recorded before it runs ... or the next one does
+  if (check_cuda(cudaMemcpyAsync(pd.probe_host, pd.status_ptr, sizeof(int), cudaMemcpyDeviceToHost, st))) return B2N_ERR_CUDA;
+  if (check_cuda(cudaEventRecord(pd.probe_event, st))) return B2N_ERR_CUDA;
+  pd.probe_stream = st;
+  pd.probe_pending = true;
+  return B2N_OK;
+}
+
+int b2n_status_poll(void) {
+  PerDevice& pd = current_device();
+  if (!pd.ready.load(std::memory_order_acquire)) return B2N_OK;
+  std::lock_guard<std::mutex> lock(pd.mu);
+  if (!pd.probe_pending) return B2N_OK;
+  const cudaError_t q = cudaEventQuery(pd.probe_event);
+  if (q == cudaErrorNotReady) return B2N_OK;
+  pd.probe_pending = false;
+  if (q != cudaSuccess) return check_cuda(q);
+  const int v = *pd.probe_host;
+  if (v != 0) {
+    *pd.probe_host = 0;
+    // clear the device word behind the work already queued on the probe's stream, so the same failure is
+    // reported once
+    cudaMemsetAsync(pd.status_ptr, 0, sizeof(int), pd.probe_stream);
   }
   return v;
 }
@@ -209,6 +267,7 @@ int b2n_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void*
   if (M == 0) return B2N_OK;
   if (!x || !y || !mean || !rstd) return B2N_ERR_BAD_ARG;
   if (gamma == nullptr && beta == nullptr) w_dtype = x_dtype;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_norm_fwd(false, x, gamma, beta, y, mean, rstd, M, N, eps, x_dtype, w_dtype,
                          static_cast<cudaStream_t>(stream));
 }
@@ -219,6 +278,7 @@ int b2n_rms_norm_fwd(const void* x, const void* gamma, void* y, void* rstd, int6
   if (M == 0) return B2N_OK;
   if (!x || !y || !rstd) return B2N_ERR_BAD_ARG;
   if (gamma == nullptr) w_dtype = x_dtype;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_norm_fwd(true, x, gamma, nullptr, y, nullptr, rstd, M, N, eps, x_dtype, w_dtype,
                          static_cast<cudaStream_t>(stream));
 }
@@ -236,6 +296,7 @@ int b2n_layer_norm_bwd(const void* dy, const void* x, const void* mean, const vo
   if (!dy || !x || !mean || !rstd) return B2N_ERR_BAD_ARG;
   if (!dx && !dgamma && !dbeta) return B2N_OK;
   if (gamma == nullptr && dgamma == nullptr && dbeta == nullptr) w_dtype = x_dtype;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_norm_bwd(false, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, workspace, workspace_bytes, M, N,
                          x_dtype, w_dtype, static_cast<cudaStream_t>(stream));
 }
@@ -248,6 +309,7 @@ int b2n_rms_norm_bwd(const void* dy, const void* x, const void* rstd, const void
   if (!dy || !x || !rstd) return B2N_ERR_BAD_ARG;
   if (!dx && !dgamma) return B2N_OK;
   if (gamma == nullptr && dgamma == nullptr) w_dtype = x_dtype;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_norm_bwd(true, dy, x, nullptr, rstd, gamma, dx, dgamma, nullptr, workspace, workspace_bytes, M, N,
                          x_dtype, w_dtype, static_cast<cudaStream_t>(stream));
 }
@@ -258,6 +320,7 @@ int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t in
   if (outer == 0 || N == 0 || inner == 0) return B2N_OK;
   if (!x || !y) return B2N_ERR_BAD_ARG;
   if (is_log < 0 || is_log > 2) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
   tl_softmax_safe = is_log == 2;
   const int rc = launch_softmax_fwd(x, y, outer, N, inner, in_dtype, out_dtype, is_log == 1,
                                     static_cast<cudaStream_t>(stream));
@@ -270,6 +333,7 @@ int b2n_softmax_bwd(const void* dy, const void* y, void* dx, int64_t outer, int6
   if (outer < 0 || N < 0 || inner < 0 || !valid_dtype(grad_dtype) || !valid_dtype(dx_dtype)) return B2N_ERR_BAD_ARG;
   if (outer == 0 || N == 0 || inner == 0) return B2N_OK;
   if (!dy || !y || !dx) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_softmax_bwd(dy, y, dx, outer, N, inner, grad_dtype, dx_dtype, is_log != 0,
                             static_cast<cudaStream_t>(stream));
 }
@@ -283,6 +347,7 @@ int b2n_nll_loss_fwd(const void* logp, const void* target, const void* weight, v
     return B2N_ERR_BAD_ARG;
   if (M > 0 && (!logp || !target)) return B2N_ERR_BAD_ARG;
   if (!out && !(reduction == B2N_REDUCE_NONE && M == 0)) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_nll_loss_fwd(logp, target, weight, out, total_weight, sums_f32, workspace, workspace_bytes, M, C,
                              reduction, ignore_index, dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
 }
@@ -295,6 +360,7 @@ int b2n_nll_loss_bwd(const void* grad_out, const void* target, const void* weigh
   if (M == 0 || C == 0) return B2N_OK;
   if (!grad_out || !target || !grad_input) return B2N_ERR_BAD_ARG;
   if (reduction == B2N_REDUCE_MEAN && !total_weight) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_nll_loss_bwd(grad_out, target, weight, total_weight, grad_input, M, C, reduction, ignore_index,
                              dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
 }
@@ -304,6 +370,7 @@ int b2n_masked_softmax_fwd(const void* x, const void* mask, void* y, int64_t M, 
   if (M < 0 || N < 0 || mask_row_div < 1 || mask_row_mod < 1 || !valid_dtype(dtype)) return B2N_ERR_BAD_ARG;
   if (M == 0 || N == 0) return B2N_OK;
   if (!x || !mask || !y) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_masked_softmax_fwd(x, mask, y, M, N, mask_row_div, mask_row_mod, dtype,
                                    static_cast<cudaStream_t>(stream));
 }
@@ -313,6 +380,7 @@ int b2n_masked_softmax_bwd(const void* dy, const void* y, const void* mask, void
   if (M < 0 || N < 0 || !valid_dtype(dtype)) return B2N_ERR_BAD_ARG;
   if (M == 0 || N == 0) return B2N_OK;
   if (!dy || !y || !mask || !dx) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_masked_softmax_bwd(dy, y, mask, dx, M, N, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -324,6 +392,7 @@ int b2n_cross_entropy_bwd(const void* logp, const void* target, const void* weig
   if (M == 0 || C == 0) return B2N_OK;
   if (!logp || !grad_out || !target || !dx) return B2N_ERR_BAD_ARG;
   if (reduction == B2N_REDUCE_MEAN && !total_weight) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
   return launch_cross_entropy_bwd(logp, target, weight, grad_out, total_weight, dx, M, C, reduction, ignore_index,
                                   dtype, target_is_u8 != 0, static_cast<cudaStream_t>(stream));
 }

@@ -337,6 +337,7 @@ struct DeviceInfo {
   int max_smem_optin;  // bytes of dynamic shared memory a CTA may opt into
 };
 const DeviceInfo& device_info();          // cached per device
+bool device_ready();                      // the current device's attributes, status word and tile counters were found
 int check_cuda(cudaError_t e);            // records e for b2n_last_cuda_error; returns B2N_OK / B2N_ERR_CUDA
 int forced_path();                        // b2n_set_path value of this thread
 void note_path(const char* name);         // records the family used by the last launch

@@ -17,7 +17,7 @@
 //    (different streams, or different host threads) write the same rows and race: serialise them;
 //  * the first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //    that device current) and caches it.  Make that first call before starting any stream capture.
-#include <mutex>
+#include <atomic>
 
 #include "common.cuh"
 #include "launchers.h"
@@ -32,26 +32,22 @@ constexpr size_t kNoAllocScratchBytes = 16u << 20;  // 16 MiB: [148 partial rows
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 constexpr int kMaxDevices = 64;
-struct ScratchAddress {
-  std::once_flag once;
-  void* ptr = nullptr;
-  cudaError_t err = cudaSuccess;
-};
-ScratchAddress g_scratch_address[kMaxDevices];
+// Only a successful lookup is remembered.  A first call that arrives while a stream capture is under way, or
+// with a sticky error pending, fails — and the next call simply looks the address up again.
+std::atomic<void*> g_scratch_address[kMaxDevices];
 
-// Device address of the scratch array on the CURRENT device (looked up once per device).
+// Device address of the scratch array on the CURRENT device (looked up until it succeeds, then cached).
 int scratch_for_current_device(void** out) {
   int dev = 0;
   if (int e = check_cuda(cudaGetDevice(&dev))) return e;
   if (dev < 0 || dev >= kMaxDevices) return B2N_ERR_BAD_ARG;
-  ScratchAddress& sa = g_scratch_address[dev];
-  std::call_once(sa.once, [&sa]() {
-    void* p = nullptr;
-    sa.err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-    if (sa.err == cudaSuccess) sa.ptr = p;
-  });
-  if (sa.err != cudaSuccess || sa.ptr == nullptr) return check_cuda(sa.err == cudaSuccess ? cudaErrorInvalidSymbol : sa.err);
-  *out = sa.ptr;
+  void* p = g_scratch_address[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    const cudaError_t err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (err != cudaSuccess || p == nullptr) return check_cuda(err == cudaSuccess ? cudaErrorInvalidSymbol : err);
+    g_scratch_address[dev].store(p, std::memory_order_release);  // concurrent first calls store the same address
+  }
+  *out = p;
   return B2N_OK;
 }
 
@@ -76,6 +72,7 @@ int b2n_layer_norm_bwd_noalloc(const void* dy, const void* x, const void* mean, 
   const bool want_wgrad = dgamma != nullptr || dbeta != nullptr;
   const size_t need = norm_bwd_workspace_bytes(M, N, x_dtype, w_dtype, want_wgrad ? 1 : 0);
   if (need > kNoAllocScratchBytes) return B2N_ERR_TOO_LARGE;  // the fixed array cannot hold this problem's partial sums
+  if (!device_ready()) return B2N_ERR_CUDA;
   void* scratch = nullptr;
   if (want_wgrad) {
     if (int e = scratch_for_current_device(&scratch)) return e;

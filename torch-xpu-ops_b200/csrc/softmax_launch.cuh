@@ -152,6 +152,11 @@ int softmax_cluster_launch(const ClusterPlan& p, const T* in0, const T* in1, T* 
   return launched();
 }
 
+// The two-pass kernels move whole 16-byte vectors: a row must be a multiple of 16 bytes (rows of
+// any other length — 50257 or 40001 elements, say — go to the generic kernels; a pinned two-pass
+// path then reports B2N_ERR_BAD_ARG like every pinned family that cannot take the shape).
+template <typename T> inline bool twopass_takes(int64_t N) { return N % static_cast<int64_t>(16 / sizeof(T)) == 0; }
+
 // Rows of any length: two passes through the ring per row, the second served from L2.
 template <typename T, bool LOG, bool BWD, bool SAFE>
 int softmax_twopass_launch_as(const T* in0, const T* in1, T* out, int64_t M, int64_t N, cudaStream_t st) {
@@ -220,7 +225,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
             note_path("cluster");
             return softmax_cluster_launch<TI, LOG, false>(cp, x, static_cast<const TI*>(nullptr), y, M, N, st);
           }
-        } else if (forced == B2N_PATH_TWOPASS || (forced == B2N_PATH_AUTO && N * sizeof(TI) >= 32768)) {
+        } else if (twopass_takes<TI>(N) && (forced == B2N_PATH_TWOPASS || (forced == B2N_PATH_AUTO && N * sizeof(TI) >= 32768))) {
           note_path("twopass");
           return softmax_twopass_launch<TI, LOG, false>(x, static_cast<const TI*>(nullptr), y, M, N, st);
         }
@@ -317,7 +322,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
             note_path("cluster");
             return softmax_cluster_launch<TG, LOG, true>(cp, dy, y, dx, M, N, st);
           }
-        } else if (forced == B2N_PATH_TWOPASS || (forced == B2N_PATH_AUTO && N * sizeof(TG) >= 32768)) {
+        } else if (twopass_takes<TG>(N) && (forced == B2N_PATH_TWOPASS || (forced == B2N_PATH_AUTO && N * sizeof(TG) >= 32768))) {
           note_path("twopass");
           return softmax_twopass_launch<TG, LOG, true>(dy, y, dx, M, N, st);
         }
