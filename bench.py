@@ -166,7 +166,7 @@ class Cfg4LayerNorm(Workload):
                 w.wait()
                 st["works"][i] = None
 
-    launches_per_step = 2  # forward ring kernel, backward ring kernel (the partial sums are folded in its tail)
+    launches_per_step = 3  # forward ring kernel, backward ring kernel, partial-sum fold
 
     def shard_check(self, capi, st, world, rank, rows_of):
         """After a multi-GPU run: the all-reduced [dgamma | dbeta] against the sum, taken in fp64 on rank 0, of
@@ -441,6 +441,26 @@ def run_reference(args, wl: Workload, rank: int):
 # --------------------------------------------------------------------------------------------------
 SHORT_REGION_MS = 50.0
 REPEATS = 9
+REGION_PAUSE_S = 0.03
+
+
+def sustained_ms_per_step(runner, steps, world, dev, barrier, regions=REPEATS):
+    """The same steps for `regions` regions' worth back to back, no pause: what the step costs once the power cap
+    has been reached."""
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(regions):
+        runner.run(steps)
+    runner.finish()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    return ms / (regions * steps)
 
 
 class StepRunner:
@@ -500,6 +520,11 @@ def time_regions(runner: StepRunner, steps: int, world: int, dev, barrier):
     regions, host = [], []
     t_begin = time.perf_counter()
     while True:
+        if regions:
+            # Every region is a burst from a rested GPU, like the copy that defines the roofline's peak: under a
+            # second of back-to-back HBM-bound kernels the 1 kW power cap starts to bite (sw_power_cap) and the
+            # same kernels run 3-5 % slower.  What they sustain is reported separately (sustained_ms_per_step).
+            time.sleep(REGION_PAUSE_S)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         h0 = time.perf_counter()
@@ -563,6 +588,8 @@ def measure_workload(wl, capi, st, world, rank, dev, steps, warmup, rows, global
     ms = statistics.median(regions)
     status = capi.device_status()
     assert status == 0, f"device status {status}"
+    sustained = sustained_ms_per_step(runner, steps, world, dev, barrier) if len(regions) > 1 else None
+    time.sleep(REGION_PAUSE_S * 2)
     prof = profile_kernels(runner, capi, min(steps, 50), barrier)
     peak, peak_kind = measured_peak()
     bytes_local = wl.bytes_per_rows(rows)
@@ -580,8 +607,9 @@ def measure_workload(wl, capi, st, world, rank, dev, steps, warmup, rows, global
     out = {
         "ms_per_step": ms / steps, "value": total_bytes * steps / (ms * 1e-3) / 1e9, "total_bytes": total_bytes,
         "spread": {"regions": len(regions), "min_ms_per_step": round(min(regions) / steps, 5),
-                   "max_ms_per_step": round(max(regions) / steps, 5)},
+                   "max_ms_per_step": round(max(regions) / steps, 5), "pause_between_regions_ms": REGION_PAUSE_S * 1e3},
         "host_enqueue_us_per_step": round(statistics.median(host) / steps * 1e6, 2),
+        "sustained_ms_per_step": None if sustained is None else round(sustained, 5),
         "graph": runner.graph_note, "kernels": kernels, "top_kernel": top, "peak": peak, "peak_kind": peak_kind,
         "span": span, "launches": runner.launches_per_step * steps * len(regions), "runner": runner,
     }
@@ -632,6 +660,7 @@ def run_other_configs(capi, dev, steps_of, barrier):
             res = measure_workload(wl, capi, st, 1, 0, dev, steps, 3, wl.rows, wl.rows, "strong", True, barrier)
             entry = {"workload": wl.describe(), "value": round(res["value"], 1), "unit": "GB/s", "steps": steps,
                      "ms_per_step": round(res["ms_per_step"], 5), "spread": res["spread"],
+                     "sustained_ms_per_step": res["sustained_ms_per_step"],
                      "pct_of_peak_measured": round(100 * res["value"] / res["peak"], 2),
                      "pct_of_peak_nominal": round(100 * res["value"] / NOMINAL_HBM_GBS, 2),
                      "graph": res["graph"], "l2": wl.l2_note, "kernels": res["kernels"],
@@ -665,6 +694,7 @@ def main():
                     help="replay the steps from a CUDA graph (where the workload supports it) or enqueue them call by call")
     ap.add_argument("--sm-margin", type=int, default=-1,
                     help="SMs the persistent kernels leave free for a collective kernel running beside them (default: 4 from N=4 on, else 0)")
+    ap.add_argument("--tune", default="", help="(diagnostic) ring-kernel launch parameters, e.g. rpg=2,stages=4,lag=2")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the short runs of the other BASELINE configs")
@@ -703,6 +733,10 @@ def main():
     overlapped = world >= 4 and args.workload == "cfg4" and COLLECTIVE_MODE == "async"
     sm_margin = args.sm_margin if args.sm_margin >= 0 else (4 if overlapped else 0)
     capi.set_tuning(b200norm.TUNE_SM_MARGIN, sm_margin)
+    for item in filter(None, args.tune.split(",")):
+        knob, val = item.split("=")
+        capi.set_tuning({"rpg": b200norm.TUNE_ROWS_PER_GROUP, "stages": b200norm.TUNE_STAGES,
+                         "lag": b200norm.TUNE_STORE_LAG}[knob], int(val))
 
     b200norm.load_library()
     if args.scaling == "strong":
@@ -788,7 +822,8 @@ def main():
                        "sm_margin": sm_margin, "parallelism": f"row-sharded dp{world}", "l2": wl.l2_note,
                        "graph": res["graph"],
                        "collective": (getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, " + {"async": "overlapped with the next step", "sync": "in stream", "none": "SKIPPED (diagnostic run)"}[COLLECTIVE_MODE]) if world > 1 else "none")},
-            "spread": res["spread"], "host_enqueue_us_per_step": res["host_enqueue_us_per_step"],
+            "spread": res["spread"], "sustained_ms_per_step": res["sustained_ms_per_step"],
+            "host_enqueue_us_per_step": res["host_enqueue_us_per_step"],
             "collective_us": coll_us, "shard_check": shard_check,
             "pct_of_peak_measured": round(100 * value / world / peak, 2),
             "pct_of_peak_nominal": round(100 * value / world / NOMINAL_HBM_GBS, 2),

@@ -94,7 +94,7 @@ class Cfg2RmsNorm(_Simple):
     name, rows, N, cpu_sample_rows = "cfg2", 8192, 4096, 8192
     collective = "all_reduce(fp32[2,N]) per step"
     e2e_inputs = ("x", "dy")
-    launches_per_step = 2
+    launches_per_step = 3
     cycle = 4
     tensor_bytes = 8192 * 4096 * 2
     l2_note = "tensors (64 MiB) smaller than L2: 4 rotating sets of x, dy, y, dx (1 GiB working set)"

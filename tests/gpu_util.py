@@ -103,13 +103,21 @@ def gate_16bit(name: str, got: torch.Tensor, ref_exact: torch.Tensor, ref64: tor
 
 
 def wgrad_gate(a: torch.Tensor, terms: torch.Tensor, what: str) -> None:
-    """Weight-gradient gate.  a: kernel result [N]; terms: fp64 [M, N] summands.  fp32 results: within 1e-6 of the
-    L1 norm of the terms of the fp64 sum; 16-bit results: 1 ulp of the fp64 sum rounded once, or that same bound."""
+    """Weight-gradient gate, element by element.  a: kernel result [N]; terms: fp64 [M, N] summands.
+    fp32 results: within 1e-6 of the L1 norm of the element's terms of the fp64 sum.  16-bit results (the fp32 sum
+    rounded once): within 1 ulp of the fp64 sum rounded once, or — where the sum cancels to something smaller than the
+    fp32 rounding of its terms, so that a 16-bit ulp of it means nothing — within that same 1e-6 of L1."""
     from oracle import aten_oracle as ao
-    ref = terms.sum(0)
-    l1 = terms.abs().sum(0).clamp_min(1e-30)
-    err = float(((a.detach().cpu().double().reshape(-1) - ref.reshape(-1)).abs() / l1.reshape(-1)).max())
-    if a.dtype in (torch.bfloat16, torch.float16):
-        assert ao.ulp_distance(a.detach().cpu().reshape(-1), ref.reshape(-1).to(a.dtype)) <= 1 or err <= 1e-6, f"{what}: {err:.3e} of L1"
+    got = a.detach().cpu().reshape(-1)
+    ref = terms.sum(0).reshape(-1)
+    l1 = terms.abs().sum(0).reshape(-1).clamp_min(1e-30)
+    rel = (got.double() - ref).abs() / l1
+    if got.dtype in (torch.bfloat16, torch.float16):
+        r16 = ref.to(got.dtype)
+        assert torch.equal(torch.isnan(got), torch.isnan(r16)), f"{what}: NaN pattern"
+        d = (ao._ordered_int(got) - ao._ordered_int(r16)).abs()
+        bad = (d > 1) & (rel > 1e-6)
+        assert not bool(bad.any()), (f"{what}: {int(bad.sum())} elements beyond 1 ulp and 1e-6 of L1 "
+                                     f"(worst {int(d[bad].max())} ulp, {float(rel[bad].max()):.3e} of L1)")
     else:
-        assert err <= 1e-6, f"{what}: {err:.3e} of L1"
+        assert float(rel.max()) <= 1e-6, f"{what}: {float(rel.max()):.3e} of L1"

@@ -15,7 +15,7 @@ from b200norm import capi
 from oracle import aten_oracle as ao
 from oracle import restate
 
-from gpu_util import DEV, forced_path, guarded_empty, misaligned, ring_eligible
+from gpu_util import DEV, forced_path, guarded_empty, misaligned, ring_eligible, wgrad_gate
 
 pytestmark = pytest.mark.gpu
 
@@ -41,17 +41,8 @@ def check_stat(a, ref, what):
 
 
 def check_wgrad(a, terms, what):
-    """a: kernel result [N]; terms: fp64 [M, N] summands.  Error relative to the L1 norm of the terms."""
-    ref = terms.sum(0)
-    l1 = terms.abs().sum(0).clamp_min(1e-30)
-    if a.dtype in (torch.bfloat16, torch.float16):
-        # a 16-bit gradient is the fp32 sum rounded once: 1 ulp of the fp64 sum, or — where the sum cancels to
-        # less than its own rounding error — the same 1e-6 of the terms' L1 norm as the fp32 case
-        err = ((a.cpu().double() - ref).abs() / l1).max()
-        assert ao.ulp_distance(a.cpu(), ref.to(a.dtype)) <= 1 or err <= 1e-6, f"{what}: {float(err):.3e} of L1"
-    else:
-        err = ((a.cpu().double() - ref).abs() / l1).max()
-        assert err <= 1e-6, f"{what}: {float(err):.3e} of L1"
+    """a: kernel result [N]; terms: fp64 [M, N] summands (see gpu_util.wgrad_gate for the bound)."""
+    wgrad_gate(a, terms, what)
 
 
 @pytest.mark.parametrize("path", PATHS)

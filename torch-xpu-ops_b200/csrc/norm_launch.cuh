@@ -140,8 +140,8 @@ template <typename T> size_t norm_bwd_ws_bytes_typed(int64_t M, int64_t N) {
 
 template <typename T, typename WT, bool RMS, int GROUP>
 int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x, const float* mean,
-                         const float* rstd, const WT* gamma, T* dx, float* ws, WT* dgamma, WT* dbeta, int64_t M,
-                         int64_t N, cudaStream_t st) {
+                         const float* rstd, const WT* gamma, T* dx, float* ws, int64_t M, int64_t N,
+                         cudaStream_t st) {
   constexpr int VPT = kNormBwdEpt / Pack16<T>::VEC;
   ProfileScope prof(RMS ? "rms_norm_bwd_ring" : "layer_norm_bwd_ring", st);
   const bool full = N == static_cast<int64_t>(GROUP) * VPT * Pack16<T>::VEC;
@@ -149,17 +149,11 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
   const int n = static_cast<int>(N);
   // fixed tile assignment (no counter) with weight gradients: the partial sums a CTA forms, and with them
   // dgamma/dbeta, are then the same bits on every run
-  // With weight gradients the same slot serves as the ticket at which the CTAs meet before they fold their
-  // partial sums (see wgrad_fold_in_tail).
-  unsigned* slot = next_tile_counter();
-  int* status = device_status_ptr();
-  if (slot == nullptr || status == nullptr) return B2N_ERR_CUDA;
-  unsigned* ctr = wgrad ? nullptr : slot;
-  unsigned* ticket = wgrad ? slot : nullptr;
+  unsigned* ctr = wgrad ? nullptr : next_tile_counter();
   auto go = [&](auto kernel, std::atomic<uint64_t>& done) -> int {
     if (int e = set_smem_once(kernel, p.smem, done)) return e;
-    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, dgamma, dbeta,
-                      M, n, s_lag, p.rpg, status, ctr, ticket);
+    return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, ws, M, n, s_lag,
+                      p.rpg, device_status_ptr(), ctr);
   };
   static std::atomic<uint64_t> done[6];
   if (wgrad) {
@@ -204,13 +198,15 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
         note_path("ring");
         int e;
         switch (p.group) {
-          case 32: e = norm_bwd_ring_launch<T, WT, RMS, 32>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, dgamma, dbeta, M, N, st); break;
-          case 64: e = norm_bwd_ring_launch<T, WT, RMS, 64>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, dgamma, dbeta, M, N, st); break;
-          case 128: e = norm_bwd_ring_launch<T, WT, RMS, 128>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, dgamma, dbeta, M, N, st); break;
-          case 256: e = norm_bwd_ring_launch<T, WT, RMS, 256>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, dgamma, dbeta, M, N, st); break;
-          default: e = norm_bwd_ring_launch<T, WT, RMS, 512>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, dgamma, dbeta, M, N, st); break;
+          case 32: e = norm_bwd_ring_launch<T, WT, RMS, 32>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          case 64: e = norm_bwd_ring_launch<T, WT, RMS, 64>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          case 128: e = norm_bwd_ring_launch<T, WT, RMS, 128>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          case 256: e = norm_bwd_ring_launch<T, WT, RMS, 256>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
+          default: e = norm_bwd_ring_launch<T, WT, RMS, 512>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
         }
-        return e;  // dgamma / dbeta were folded from the partial sums by the same launch
+        if (e != B2N_OK || !wgrad) return e;
+        return launch_pdl(norm_bwd_wgrad_fold_kernel<float, WT>, fold_grid, fold_block, 0, st,
+                          static_cast<const float*>(ws), dgamma, dbeta, static_cast<int64_t>(p.grid) * p.ng, N);
       }
     }
   }

@@ -34,92 +34,6 @@ __device__ __forceinline__ void load_weights(const WT* __restrict__ w, float fil
 
 constexpr int kTraceTid = 160;  // the consumer thread that writes trace records (lane 0 of warp 5)
 
-// Tail of the backward with weight gradients: the CTAs' partial rows ws[P][2][N] are folded into
-// dgamma / dbeta by the SAME launch, so a step needs no separate fold kernel (one launch and one
-// kernel boundary fewer; at 8192 rows per GPU that boundary is 4 % of the step).
-//
-// Called by the 512 consumer threads of every CTA after they have written their partial rows.
-// The CTAs meet at a ticket in global memory: each announces its rows (release), waits until all
-// gridDim.x have (acquire; the grid never exceeds the SM count and a CTA fills its SM, so all CTAs
-// are resident or will be as soon as whatever holds their SM ends on its own), then folds its own
-// contiguous slice of the 2N output columns.  The wait is bounded like every other wait here: on
-// expiry the CTA records B2N_ERR_TIMEOUT and skips its slice.
-//
-// Summation order is fixed — thread (quad q, lane l) adds rows l, l + 16, ... of its four columns,
-// the 16 lanes are combined by a butterfly — so dgamma / dbeta stay bit-reproducible for a given
-// grid.  ticket: {arrived, left}, both zero before the launch; the last CTA to leave zeroes them.
-// go_flag: a word of the CTA's shared memory.
-template <typename WT, bool RMS>
-__device__ __forceinline__ void wgrad_fold_in_tail(const float* ws, WT* __restrict__ dgamma, WT* __restrict__ dbeta,
-                                                   int P, int N, unsigned* ticket, int* status,
-                                                   volatile int* go_flag) {
-  constexpr int kBar = 15;  // a named barrier no row group uses (groups take 1 .. 512 / GROUP)
-  const int tid = threadIdx.x;
-  __threadfence();  // this thread's partial sums are visible device-wide before the CTA announces them
-  named_bar_sync(kBar, kRingThreads);
-  if (tid == 0) {
-    unsigned seen;
-    asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(seen) : "l"(ticket) : "memory");
-    ++seen;
-    bool ok = true;
-    const unsigned long long t0 = globaltimer_ns();
-    for (uint32_t it = 1; seen < gridDim.x; ++it) {
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ticket) : "memory");
-      if ((it & 0xffu) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
-        record_status(status, B2N_ERR_TIMEOUT);
-        ok = false;
-        break;
-      }
-    }
-    *go_flag = ok ? 1 : 0;
-  }
-  named_bar_sync(kBar, kRingThreads);
-  if (*go_flag) {
-    const int total = (RMS ? 1 : 2) * N;                         // output columns: dgamma, then dbeta
-    const int per_cta = ((total / 4 + gridDim.x - 1) / gridDim.x) * 4;
-    const int c0 = static_cast<int>(blockIdx.x) * per_cta;
-    const int c1 = c0 + per_cta < total ? c0 + per_cta : total;
-    const int lane16 = tid & 15;
-    for (int c = c0 + (tid >> 4) * 4; c - (tid >> 4) * 4 < c1; c += (kRingThreads / 16) * 4) {
-      // (the loop bound is uniform over a warp: both of its quads run the butterfly even when one is past the end)
-      const bool live = c < c1;
-      const int plane = (!RMS && c >= N) ? 1 : 0;
-      const int col = c - plane * N;
-      float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      if (live) {
-        const float* src = ws + static_cast<size_t>(plane) * N + col;
-#pragma unroll 4
-        for (int p = lane16; p < P; p += 16) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(p) * 2 * N));
-          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-        }
-      }
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) {
-        a.x += __shfl_xor_sync(0xffffffffu, a.x, o);
-        a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
-        a.z += __shfl_xor_sync(0xffffffffu, a.z, o);
-        a.w += __shfl_xor_sync(0xffffffffu, a.w, o);
-      }
-      WT* out = plane == 0 ? dgamma : dbeta;
-      if (live && lane16 == 0 && out != nullptr) {
-        out[col] = from_acc<WT>(a.x);
-        out[col + 1] = from_acc<WT>(a.y);
-        out[col + 2] = from_acc<WT>(a.z);
-        out[col + 3] = from_acc<WT>(a.w);
-      }
-    }
-  }
-  named_bar_sync(kBar, kRingThreads);
-  if (tid == 0) {
-    const unsigned left = atomicAdd(ticket + 1, 1u);
-    if (left == gridDim.x - 1) {  // every CTA is past its wait: the pair is free for the slot's next launch
-      ticket[0] = 0;
-      ticket[1] = 0;
-    }
-  }
-}
-
 // FULL: the row fills every thread's vectors exactly (N == GROUP * VPT * VEC), so no access needs a range check.
 // RPGT: rows per group per tile as a compile-time constant (0: taken from the launch argument).
 template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool FULL, int RPGT>
@@ -341,8 +255,8 @@ template <typename T, typename WT, bool RMS, int GROUP, int VPT, bool WGRAD, boo
 __global__ void __launch_bounds__(kRingBlock, 1)
 norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx,
-                     float* ws, WT* __restrict__ dgamma, WT* __restrict__ dbeta, int64_t M, int N, int S_lag,
-                     int rpg_arg, int* status, unsigned* tile_ctr, unsigned* fold_ticket) {
+                     float* __restrict__ ws, int64_t M, int N, int S_lag, int rpg_arg, int* status,
+                     unsigned* tile_ctr) {
   using P = Pack16<T>;
   const int RPG = RPGT > 0 ? RPGT : rpg_arg;
   constexpr int VEC = P::VEC, EPT = VPT * VEC, NG = kRingThreads / GROUP;
@@ -513,7 +427,6 @@ norm_bwd_ring_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
         }
       }
     }
-    wgrad_fold_in_tail<WT, RMS>(ws, dgamma, dbeta, static_cast<int>(gridDim.x) * NG, N, fold_ticket, status, &rs->pad[0]);
   }
 }
 

@@ -226,7 +226,10 @@ template <int NIN> struct RingProducer {
       mbar_wait(&rs->full[cur.s], cur.phase, status);
       cur.advance(g);
     }
-    bulk_wait_all<0>();
+    // The stores must have READ their stage before the CTA's shared memory goes away; that they have been
+    // WRITTEN is the business of the kernel boundary (and of griddepcontrol.wait in a dependent kernel), so the
+    // CTA does not sit out the ~1 us write acknowledgement of its last tile.
+    bulk_wait_read<0>();
     // The last CTA to finish taking tiles zeroes the counter pair for the slot's next launch (every
     // CTA's last fetch completed before it said so: its result is what ended the CTA's loads).
     if (g.ctr != nullptr && !ended) retired = atomicAdd(g.ctr + 1, 1u);  // a wait gave up before the end marker
