@@ -109,16 +109,61 @@ class Cfg4LayerNorm(Workload):
         from b200norm import F32, BF16, load_library
         nbytes = load_library().b2n_norm_bwd_workspace_bytes(rows, n, BF16, F32, 1)
         st["ws"] = torch.empty(max(nbytes, 1), device=dev, dtype=torch.uint8)
+        st["ws2"] = torch.empty(max(nbytes, 1), device=dev, dtype=torch.uint8) if COLLECTIVE_MODE == "fused-side" else None
+        st["side"] = torch.cuda.Stream(dev)
+        st["pending"] = [None, None]
         return st
+
+    def open_exchange(self, st, dev, sm_margin):
+        """(collective) the peer-memory exchange buffers of the fused fold + all-reduce kernel."""
+        from b200norm.peer import WgradExchange
+        ctas = 128 if COLLECTIVE_MODE == "fused" else max(2, 2 * sm_margin)
+        st["exch"] = WgradExchange(self.N, dev, ctas=ctas)
 
     def prepare(self, capi, st):
         """Prepared C-ABI calls (pointers and sizes converted once) on the CURRENT stream."""
         st["fwd"] = capi.prepare_layer_norm(st["x"], st["gamma"], st["beta"], 1e-5, st["y"], st["mean"], st["rstd"])
+        if COLLECTIVE_MODE in ("fused", "fused-side"):
+            wss = [st["ws"], st["ws2"] if st["ws2"] is not None else st["ws"]]
+            st["bwd"], st["exc"] = [], []
+            for k, wg in enumerate(st["wgrads"]):
+                call, rows = capi.prepare_norm_backward_partials(False, st["dy"], st["x"], st["mean"], st["rstd"],
+                                                                 st["gamma"], st["dx"], wss[k])
+                st["bwd"].append(call)
+                if COLLECTIVE_MODE == "fused":
+                    st["exc"].append(st["exch"].prepare(wss[k], rows, wg[0], wg[1]))
+                else:
+                    with torch.cuda.stream(st["side"]):
+                        st["exc"].append(st["exch"].prepare(wss[k], rows, wg[0], wg[1]))
+            return
         st["bwd"] = [capi.prepare_layer_norm_backward(st["dy"], st["x"], st["mean"], st["rstd"], st["gamma"], st["dx"],
                                                       wg[0], wg[1], st["ws"]) for wg in st["wgrads"]]
 
+    def _fused_step(self, st, k, main, side):
+        """Row kernels on `main`; the fused fold + all-reduce behind them on `main` ("fused") or on `side`
+        ("fused-side", joined before buffer k is written again)."""
+        if st["pending"][k] is not None:
+            main.wait_event(st["pending"][k])
+            st["pending"][k] = None
+        st["fwd"]()
+        st["bwd"][k]()
+        if COLLECTIVE_MODE == "fused":
+            st["exc"][k]()
+            return
+        ready = torch.cuda.Event()
+        ready.record(main)
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            st["exc"][k]()
+            done = torch.cuda.Event()
+            done.record(side)
+        st["pending"][k] = done
+
     def step(self, capi, st, world):
         k = st["k"] = st["k"] ^ 1
+        if COLLECTIVE_MODE in ("fused", "fused-side"):
+            self._fused_step(st, k, torch.cuda.current_stream(), st["side"])
+            return
         if st["works"][k] is not None:
             st["works"][k].wait()  # stream-level: the buffer's previous all-reduce precedes its reuse
             st["works"][k] = None
@@ -135,6 +180,15 @@ class Cfg4LayerNorm(Workload):
     def capture_cycle(self, capi, st, world, cs, side):
         """Enqueue one cycle (two steps) on the capturing stream `cs`; each step's all-reduce goes to `side`
         and is joined where its buffer is next written, or at the end of the cycle."""
+        if COLLECTIVE_MODE in ("fused", "fused-side"):
+            # the exchange calls of "fused-side" were prepared on st["side"]; `side` is not used
+            for k in (1, 0):
+                self._fused_step(st, k, cs, st["side"])
+            for k in (0, 1):
+                if st["pending"][k] is not None:
+                    cs.wait_event(st["pending"][k])
+                    st["pending"][k] = None
+            return
         pending = [None, None]
         for k in (1, 0):
             if pending[k] is not None:
@@ -161,6 +215,10 @@ class Cfg4LayerNorm(Workload):
         return st["wgrads"][0]
 
     def finish(self, st):
+        for k in (0, 1):
+            if st["pending"][k] is not None:
+                torch.cuda.current_stream().wait_event(st["pending"][k])
+                st["pending"][k] = None
         for i, w in enumerate(st["works"]):
             if w is not None:
                 w.wait()
@@ -688,8 +746,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg4")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"])
-    ap.add_argument("--collective", default="async", choices=["async", "sync", "none"],
-                    help="cfg4 gradient all-reduce: overlapped with the next step, in-stream, or (diagnostic) skipped")
+    ap.add_argument("--collective", default="async", choices=["async", "sync", "none", "fused", "fused-side"],
+                    help="cfg4 gradient all-reduce: NCCL overlapped with the next step, NCCL in-stream, (diagnostic) skipped, "
+                         "or the library's own fold + all-reduce kernel over peer memory, in-stream / on a second stream")
     ap.add_argument("--graph", default="on", choices=["on", "off"],
                     help="replay the steps from a CUDA graph (where the workload supports it) or enqueue them call by call")
     ap.add_argument("--sm-margin", type=int, default=-1,
@@ -730,7 +789,7 @@ def main():
     # From four GPUs on, the collective's kernel gets four SMs of its own (a ring CTA fills its SM, so without
     # them the all-reduce waits for a kernel boundary and then delays the next kernel's CTAs); at N = 2 the
     # all-reduce is too short for the margin to pay.  Only the config-4 step has a collective that overlaps kernels.
-    overlapped = world >= 4 and args.workload == "cfg4" and COLLECTIVE_MODE == "async"
+    overlapped = world >= 4 and args.workload in ("cfg4", "ln_long") and COLLECTIVE_MODE in ("async", "fused-side")
     sm_margin = args.sm_margin if args.sm_margin >= 0 else (4 if overlapped else 0)
     capi.set_tuning(b200norm.TUNE_SM_MARGIN, sm_margin)
     for item in filter(None, args.tune.split(",")):
@@ -748,6 +807,9 @@ def main():
         rows = wl.rows
         global_rows = wl.rows * world
     st = wl.make_device_state(rows, dev, seed=4001 + rank)
+    if COLLECTIVE_MODE in ("fused", "fused-side"):
+        assert hasattr(wl, "open_exchange"), "--collective fused needs a workload with a weight-gradient exchange"
+        wl.open_exchange(st, dev, sm_margin)
     sampler = ClockSampler(dev)
     sampler.start()
 
@@ -821,7 +883,7 @@ def main():
             "config": {"workload": f"{wl.name}: {wl.describe()}", "global_rows": global_rows, "rows_per_gpu": rows,
                        "sm_margin": sm_margin, "parallelism": f"row-sharded dp{world}", "l2": wl.l2_note,
                        "graph": res["graph"],
-                       "collective": (getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, " + {"async": "overlapped with the next step", "sync": "in stream", "none": "SKIPPED (diagnostic run)"}[COLLECTIVE_MODE]) if world > 1 else "none")},
+                       "collective": (getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, " + {"async": "NCCL, overlapped with the next step", "sync": "NCCL, in stream", "none": "SKIPPED (diagnostic run)", "fused": "own fold + all-reduce kernel over peer memory, in stream", "fused-side": "own fold + all-reduce kernel over peer memory, on a second stream"}[COLLECTIVE_MODE]) if world > 1 else "none")},
             "spread": res["spread"], "sustained_ms_per_step": res["sustained_ms_per_step"],
             "host_enqueue_us_per_step": res["host_enqueue_us_per_step"],
             "collective_us": coll_us, "shard_check": shard_check,

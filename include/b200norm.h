@@ -158,6 +158,59 @@ int b2n_rms_norm_bwd(const void* dy, const void* x, const void* rstd, const void
                      void* dgamma, void* workspace, size_t workspace_bytes, int64_t M, int64_t N,
                      int x_dtype, int w_dtype, void* stream);
 
+/* The backward in two steps, for a row-sharded caller: the row kernels write dx and leave the
+ * weight-gradient partial sums workspace[*partial_rows][2][N] (accumulate type) unfolded;
+ * b2n_norm_wgrad_fold adds the partial rows in index order into dgamma / dbeta (either may be NULL;
+ * RMS norm has no dbeta).  Together they produce exactly what b2n_layer_norm_bwd / b2n_rms_norm_bwd
+ * produce — the one-call entry points run the same two kernels back to back.  Split, the fold (and
+ * the all-reduce of its [dgamma | dbeta] output that follows it on every rank) can be enqueued on a
+ * second stream behind an event, so the next operator's row kernel starts right behind this one's
+ * instead of behind the fold.  rms != 0: RMS norm (mean is ignored).  The workspace must stay
+ * untouched until the fold has run.
+ *
+ * The reference reduces the same way in two stages on one queue: GammaBetaReduceFunctor writes
+ * [num_tile_m, N] partial tiles which `blocks.sum(0)` then adds
+ * (src/ATen/native/xpu/sycl/LayerNormKernels.cpp:701-874, :1196-1407). */
+int b2n_norm_bwd_partials(int rms, const void* dy, const void* x, const void* mean, const void* rstd,
+                          const void* gamma, void* dx, void* workspace, size_t workspace_bytes,
+                          int64_t M, int64_t N, int x_dtype, int w_dtype, int64_t* partial_rows,
+                          void* stream);
+int b2n_norm_wgrad_fold(const void* workspace, int64_t partial_rows, int64_t N, void* dgamma,
+                        void* dbeta, int x_dtype, int w_dtype, void* stream);
+
+/* No counterpart in the reference (it leaves the gradient exchange to c10d's all-reduce,
+ * src/xccl/ProcessGroupXCCL.cpp:1327-1344): b2n_norm_wgrad_fold and the all-reduce(SUM) of its
+ * [dgamma | dbeta] result over the ranks of one node as ONE kernel over peer memory.  Every CTA folds
+ * its slice of the local partial sums into this rank's exchange buffer, raises a flag in every peer's
+ * buffer, waits (bounded: B2N_ERR_TIMEOUT in the device status word) for the peers' flags, reads the
+ * peers' slices with plain peer loads and adds all ranks' slices in rank order — every rank ends
+ * with the same bits.  No multicast, no library collective.
+ *
+ * peer_buffers: host array of `world` device pointers, entry r = rank r's exchange buffer as mapped
+ * into THIS process (entry `rank` = the local one); each buffer has b2n_wgrad_exchange_bytes(n_max)
+ * bytes, zeroed once before first use, 16-byte aligned, mapped so that peer loads and stores from this
+ * device are legal (b2n_wgrad_exchange_alloc / _open below do all of that).  world <= 8, N % 4 == 0, N <= n_max.
+ * ctas: CTAs to use (1..256): ~128 when the kernel has the GPU to itself, as few as the SMs left
+ * free when it runs on a second stream beside persistent kernels.  All ranks must make the same
+ * sequence of calls on a buffer, and one buffer serves one (N, ctas) configuration.  dgamma / dbeta
+ * of w_dtype (dbeta NULL for RMS norm).  The kernel advances its generation counters itself, so a
+ * captured launch can be replayed from a CUDA graph unchanged. */
+size_t b2n_wgrad_exchange_bytes(int64_t n_max);
+/* The exchange buffers.  These four calls DO allocate / map device memory, once, at set-up:
+ * _alloc: cudaMalloc of b2n_wgrad_exchange_bytes(n_max) zeroed bytes on the current device, and its
+ *   64-byte CUDA IPC handle for the other ranks (processes) of the node;
+ * _open: maps a peer's handle into this process — call it with THIS rank's device current: the
+ *   mapping must belong to the context whose kernels use it, and cudaIpcMemLazyEnablePeerAccess then
+ *   switches peer access on for that pair (a handle cannot be opened by the process that exported it);
+ * _close / _free: undo them, after the last kernel that uses the buffers has finished. */
+int b2n_wgrad_exchange_alloc(int64_t n_max, void** local, unsigned char* handle64);
+int b2n_wgrad_exchange_open(const unsigned char* handle64, void** mapped);
+int b2n_wgrad_exchange_close(void* mapped);
+int b2n_wgrad_exchange_free(void* local);
+int b2n_norm_wgrad_fold_allreduce(const void* workspace, int64_t partial_rows, int64_t N,
+                                  void* const* peer_buffers, int64_t n_max, int rank, int world,
+                                  void* dgamma, void* dbeta, int w_dtype, int ctas, void* stream);
+
 /* ---- softmax / log-softmax --------------------------------------------------------------------
  * The tensor is viewed as [outer, N, inner]; the reduction runs over N (inner == 1 for the last
  * dim).  out_dtype == in_dtype, or B2N_F32 with a 16-bit input ("half_to_float").

@@ -56,6 +56,27 @@ def main():
     assert float(((rres.wgrad[0].double() - tw.sum(0)).abs() / tw.abs().sum(0)).max()) <= 1e-6
     assert float(rres.wgrad[1].abs().sum()) == 0.0
 
+    # the library's own fold + all-reduce kernel over peer memory: several generations, against the fp64 sums and
+    # bit-identical on every rank (all ranks add the ranks' slices in the same order)
+    from b200norm.peer import WgradExchange
+    for ctas in (128, 4):
+        ex = WgradExchange(N, dev, ctas=ctas)
+        for it in range(5):
+            xs, dys = x[s:e].contiguous(), (dy[s:e] * float(1 << it)).contiguous()  # powers of two: exact in bf16
+            _, m_, r_ = capi.native_layer_norm(xs, [N], g, b, 1e-5)
+            _, ws, rows = capi.native_layer_norm_backward_partials(dys, xs, [N], m_, r_, g)
+            wg = torch.full((2, N), float("nan"), device=dev)
+            ex.fold_allreduce(ws, rows, wg[0], wg[1])
+            torch.cuda.synchronize()
+            for got, terms, what in ((wg[0], tg * float(1 << it), "dgamma"), (wg[1], tb * float(1 << it), "dbeta")):
+                err = float(((got.double() - terms.sum(0)).abs() / terms.abs().sum(0)).max())
+                assert err <= 1e-6, f"fused exchange, {ctas} CTAs, call {it}, {what}: {err:.2e} of L1"
+            both = [torch.empty_like(wg) for _ in range(world)]
+            dist.all_gather(both, wg)
+            assert all(torch.equal(both[0], o) for o in both[1:]), "ranks disagree bit-wise after the fused exchange"
+        assert capi.device_status() == 0
+        ex.close()
+
     # the whole batch on this GPU alone, straight through the operators (no exchange)
     logp = capi._log_softmax(logits, -1, False)
     _, _, sums = capi.nll_loss_forward(logp, t, None, 2, -100, return_sums=True)

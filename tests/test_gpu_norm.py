@@ -345,3 +345,65 @@ def test_sm_margin_changes_the_grid_not_the_results():
     finally:
         capi.set_tuning(b200norm.TUNE_SM_MARGIN, 0)
     assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("M,N,dt,wdt", [(4096, 8192, torch.bfloat16, torch.float32), (300, 1000, torch.float32, torch.float32),
+                                        (64, 33, torch.float32, torch.float32), (777, 4096, torch.float16, torch.float16)])
+def test_backward_in_two_steps_equals_the_one_call_backward(M, N, dt, wdt, rms):
+    # b2n_norm_bwd_partials + b2n_norm_wgrad_fold are the one-call entry point's own two kernels: same bits
+    x, dy = ao.randn((M, N), 900, dt).to(DEV), ao.randn((M, N), 901, dt).to(DEV)
+    g = ao.randn((N,), 902, wdt, 1.0, 0.02).to(DEV)
+    if rms:
+        _, rstd = capi._fused_rms_norm(x, [N], g, 1e-6)
+        mean = None
+        dx1, dg1 = capi._fused_rms_norm_backward(dy, x, [N], rstd, g)
+        db1 = None
+    else:
+        _, mean, rstd = capi.native_layer_norm(x, [N], g, g, 1e-5)
+        dx1, dg1, db1 = capi.native_layer_norm_backward(dy, x, [N], mean, rstd, g, g)
+    dx2, ws, rows = capi.native_layer_norm_backward_partials(dy, x, [N], mean, rstd, g, rms=rms)
+    assert rows > 0
+    dg2 = torch.empty_like(g)
+    db2 = None if rms else torch.empty_like(g)
+    side = torch.cuda.Stream(DEV)  # the fold on a second stream, behind an event: the use the split exists for
+    ev = torch.cuda.Event()
+    ev.record()
+    side.wait_event(ev)
+    with torch.cuda.stream(side):
+        capi.norm_wgrad_fold(ws, rows, dt, dg2, db2)
+    torch.cuda.synchronize()
+    assert torch.equal(dx1, dx2) and torch.equal(dg1, dg2) and (rms or torch.equal(db1, db2))
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("ctas", [1, 8, 128, 256])
+@pytest.mark.parametrize("rms", [False, True])
+def test_fused_fold_allreduce_on_one_rank_is_the_fold(ctas, rms):
+    # world = 1: the peer-memory kernel reduces to the fold (another fixed summation order: gated like any weight
+    # gradient, not bit-compared); several calls in a row walk through its two buffer generations
+    from b200norm.peer import WgradExchange
+    M, N = 2500, 4096
+    dt = torch.bfloat16
+    ex = WgradExchange(N, DEV, ctas=ctas)
+    for it in range(3):
+        x, dy = ao.randn((M, N), 910 + it, dt), ao.randn((M, N), 920 + it, dt)
+        g = ao.randn((N,), 930, torch.float32, 1.0, 0.02).to(DEV)
+        if rms:
+            _, rstd = capi._fused_rms_norm(x.to(DEV), [N], g, 1e-6)
+            mean = None
+            mu = torch.zeros(M, 1, dtype=torch.float64)
+        else:
+            _, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g, g, 1e-5)
+            mu = mean.cpu().double().reshape(-1, 1)
+        _, ws, rows = capi.native_layer_norm_backward_partials(dy.to(DEV), x.to(DEV), [N], mean, rstd, g, rms=rms)
+        dg = torch.full((N,), float("nan"), device=DEV)
+        db = None if rms else torch.full((N,), float("nan"), device=DEV)
+        ex.fold_allreduce(ws, rows, dg, db)
+        torch.cuda.synchronize()
+        xh = (x.double() - mu) * rstd.cpu().double().reshape(-1, 1)
+        check_wgrad(dg, dy.double() * xh, "dgamma")
+        if not rms:
+            check_wgrad(db, dy.double(), "dbeta")
+    ex.close()
+    assert capi.device_status() == 0

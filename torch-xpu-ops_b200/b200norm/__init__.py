@@ -72,6 +72,14 @@ def load_library() -> ctypes.CDLL:
         "b2n_rms_norm_fwd": (i32, [vp, vp, vp, vp, i64, i64, dbl, i32, i32, vp]),
         "b2n_norm_bwd_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),
         "b2n_layer_norm_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, i32, vp]),
+        "b2n_norm_bwd_partials": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, i32, c.POINTER(i64), vp]),
+        "b2n_norm_wgrad_fold": (i32, [vp, i64, i64, vp, vp, i32, i32, vp]),
+        "b2n_wgrad_exchange_bytes": (sz, [i64]),
+        "b2n_wgrad_exchange_alloc": (i32, [i64, c.POINTER(vp), c.c_char_p]),
+        "b2n_wgrad_exchange_open": (i32, [c.c_char_p, c.POINTER(vp)]),
+        "b2n_wgrad_exchange_close": (i32, [vp]),
+        "b2n_wgrad_exchange_free": (i32, [vp]),
+        "b2n_norm_wgrad_fold_allreduce": (i32, [vp, i64, i64, c.POINTER(vp), i64, i32, i32, vp, vp, i32, i32, vp]),
         "b2n_noalloc_scratch_bytes": (sz, []),
         "b2n_layer_norm_bwd_noalloc": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, vp]),
         "b2n_rms_norm_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, i32, vp]),

@@ -197,6 +197,76 @@ def prepare_rms_norm_backward(dy, x, rstd, weight, dx, dweight, workspace) -> Pr
     return Prepared(lib.b2n_rms_norm_bwd, args, "b2n_rms_norm_bwd", (dy, x, rstd, weight, dx, dweight, workspace))
 
 
+def prepare_norm_backward_partials(rms: bool, dy, x, mean, rstd, gamma, dx, workspace):
+    """The backward's row kernels only (b2n_norm_bwd_partials) as a Prepared call: dx is written, the weight-gradient
+    partial sums stay in `workspace`.  Returns (call, partial_rows): the number of partial rows depends only on the
+    shape and the SM margin in force now, so it is taken from one run of the call made here."""
+    import ctypes
+    _require_cuda(dy, x, mean, rstd, gamma, dx, workspace)
+    lib = load_library()
+    M, N = _norm_dims(x, (x.shape[-1],), gamma, None)
+    assert x.is_contiguous() and dy.is_contiguous() and dx.is_contiguous()
+    xdt, wdt = _dt(x.dtype), _weight_dtype(x, gamma, None)
+    nbytes = lib.b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, 1)
+    if workspace is None or workspace.numel() < nbytes:
+        raise ValueError(f"workspace too small: need {nbytes} bytes")
+    rows = ctypes.c_int64(0)
+    args = (int(bool(rms)), _ptr(dy), _ptr(x), _ptr(mean), _ptr(rstd), _ptr(gamma), _ptr(dx), _ptr(workspace), nbytes,
+            M, N, xdt, wdt, ctypes.byref(rows), _stream(x))
+    call = Prepared(lib.b2n_norm_bwd_partials, args, "b2n_norm_bwd_partials", (dy, x, mean, rstd, gamma, dx, workspace, rows))
+    call()
+    return call, int(rows.value)
+
+
+def prepare_wgrad_fold(workspace, partial_rows: int, x_dtype, dgamma, dbeta) -> Prepared:
+    """b2n_norm_wgrad_fold as a Prepared call on the CURRENT stream (typically a second stream, behind an event
+    recorded after the row kernels)."""
+    _require_cuda(workspace, dgamma, dbeta)
+    lib = load_library()
+    w = dgamma if dgamma is not None else dbeta
+    args = (_ptr(workspace), int(partial_rows), int(w.numel()), _ptr(dgamma), _ptr(dbeta), _dt(x_dtype), _dt(w.dtype),
+            _stream(w))
+    return Prepared(lib.b2n_norm_wgrad_fold, args, "b2n_norm_wgrad_fold", (workspace, dgamma, dbeta))
+
+
+def native_layer_norm_backward_partials(grad_out, input, normalized_shape, mean, rstd, weight=None, workspace=None,
+                                        out=None, rms: bool = False):
+    """The row kernels of native_layer_norm_backward (or, with rms=True, of _fused_rms_norm_backward): returns
+    (dX, workspace, partial_rows); norm_wgrad_fold(workspace, partial_rows, ...) completes dgamma / dbeta."""
+    import ctypes
+    _require_cuda(grad_out, input, mean, rstd, weight)
+    lib = load_library()
+    M, N = _norm_dims(input, normalized_shape, weight, None)
+    x, dy = input.contiguous(), grad_out.contiguous()
+    acc = _acc_dtype(x.dtype)
+    mean_c = None if rms else mean.to(acc).contiguous().view(-1)
+    rstd_c = rstd.to(acc).contiguous().view(-1)
+    g = weight.contiguous() if weight is not None else None
+    dx = out if out is not None else torch.empty_like(x)
+    xdt, wdt = _dt(x.dtype), _weight_dtype(x, weight, None)
+    rows = ctypes.c_int64(0)
+    with torch.cuda.device(x.device):
+        nbytes = lib.b2n_norm_bwd_workspace_bytes(M, N, xdt, wdt, 1)
+        ws = workspace if workspace is not None else torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
+        if ws.numel() < nbytes:
+            raise ValueError(f"workspace too small: {ws.numel()} < {nbytes}")
+        _check(lib.b2n_norm_bwd_partials(int(bool(rms)), _ptr(dy), _ptr(x), _ptr(mean_c), _ptr(rstd_c), _ptr(g), _ptr(dx),
+                                         _ptr(ws), nbytes, M, N, xdt, wdt, ctypes.byref(rows), _stream(x)),
+               "b2n_norm_bwd_partials")
+    return dx, ws, int(rows.value)
+
+
+def norm_wgrad_fold(workspace, partial_rows: int, x_dtype, dgamma=None, dbeta=None):
+    """Folds the partial sums left by native_layer_norm_backward_partials into dgamma / dbeta (current stream)."""
+    w = dgamma if dgamma is not None else dbeta
+    if w is None:
+        return
+    with torch.cuda.device(w.device):
+        _check(load_library().b2n_norm_wgrad_fold(_ptr(workspace), int(partial_rows), int(w.numel()), _ptr(dgamma),
+                                                  _ptr(dbeta), _dt(x_dtype), _dt(w.dtype), _stream(w)),
+               "b2n_norm_wgrad_fold")
+
+
 # ---- layer norm / RMS norm -------------------------------------------------------------------------
 def native_layer_norm(input, normalized_shape, weight=None, bias=None, eps=1e-5, out=None):
     """aten::native_layer_norm -> (Y, mean, rstd); mean/rstd in the accumulate dtype.

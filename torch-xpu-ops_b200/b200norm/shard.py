@@ -50,15 +50,36 @@ class NormStepResult:
     y: torch.Tensor
     dx: torch.Tensor
     wgrad: torch.Tensor  # fp32 [2, N]: row 0 = dgamma, row 1 = dbeta (zeros for RMS norm), summed over ranks
+    ready: Optional["torch.cuda.Event"] = None  # set when the gradient exchange ran on a side stream: wait for it
+                                                # (stream.wait_event) before reading `wgrad`
 
 
 def layer_norm_step(ops, x_shard, dy_shard, gamma, beta, eps: float, group=None,
-                    wgrad_buf: Optional[torch.Tensor] = None) -> NormStepResult:
-    """Forward + backward of native_layer_norm on this rank's rows, then ONE all-reduce of [dgamma|dbeta]."""
+                    wgrad_buf: Optional[torch.Tensor] = None, side_stream=None) -> NormStepResult:
+    """Forward + backward of native_layer_norm on this rank's rows, then ONE all-reduce of [dgamma|dbeta].
+
+    side_stream: a second CUDA stream.  The weight-gradient fold and the all-reduce are then enqueued there,
+    behind an event recorded after the backward's row kernels, so that whatever the caller launches next on its
+    own stream follows those row kernels directly; the result carries `ready`, the event to wait for before
+    `wgrad` is read (and before the workspace behind it is reused)."""
     n = x_shard.shape[-1]
     y, mean, rstd = ops.native_layer_norm(x_shard, [n], gamma, beta, eps)
     if wgrad_buf is None:
         wgrad_buf = torch.empty(2, n, dtype=torch.float32, device=x_shard.device)
+    if side_stream is not None and gamma.dtype == torch.float32:
+        dx, ws, rows = ops.native_layer_norm_backward_partials(dy_shard, x_shard, [n], mean, rstd, gamma)
+        main = torch.cuda.current_stream(x_shard.device)
+        after_rows = torch.cuda.Event()
+        after_rows.record(main)
+        side_stream.wait_event(after_rows)
+        with torch.cuda.stream(side_stream):
+            ops.norm_wgrad_fold(ws, rows, x_shard.dtype, wgrad_buf[0], wgrad_buf[1])
+            all_reduce_sum_(wgrad_buf, group)
+            ready = torch.cuda.Event()
+            ready.record(side_stream)
+        for t in (ws, wgrad_buf, mean, rstd):
+            t.record_stream(side_stream)
+        return NormStepResult(y, dx, wgrad_buf, ready)
     if gamma.dtype == torch.float32:
         # the fold kernel writes dgamma | dbeta straight into the buffer the collective sends
         dx, _, _ = ops.native_layer_norm_backward(dy_shard, x_shard, [n], mean, rstd, gamma, beta,

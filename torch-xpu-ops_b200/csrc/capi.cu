@@ -314,6 +314,28 @@ int b2n_rms_norm_bwd(const void* dy, const void* x, const void* rstd, const void
                          x_dtype, w_dtype, static_cast<cudaStream_t>(stream));
 }
 
+int b2n_norm_bwd_partials(int rms, const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma,
+                          void* dx, void* workspace, size_t workspace_bytes, int64_t M, int64_t N, int x_dtype,
+                          int w_dtype, int64_t* partial_rows, void* stream) {
+  if (M < 0 || N < 0 || !valid_dtype(x_dtype) || !valid_dtype(w_dtype) || partial_rows == nullptr) return B2N_ERR_BAD_ARG;
+  *partial_rows = 0;
+  if (M == 0 || N == 0) return B2N_OK;
+  if (!dy || !x || !rstd || (!rms && !mean)) return B2N_ERR_BAD_ARG;
+  if (!device_ready()) return B2N_ERR_CUDA;
+  return launch_norm_bwd(rms != 0, dy, x, rms ? nullptr : mean, rstd, gamma, dx, nullptr, nullptr, workspace,
+                         workspace_bytes, M, N, x_dtype, w_dtype, static_cast<cudaStream_t>(stream), partial_rows);
+}
+
+int b2n_norm_wgrad_fold(const void* workspace, int64_t partial_rows, int64_t N, void* dgamma, void* dbeta, int x_dtype,
+                        int w_dtype, void* stream) {
+  if (partial_rows < 0 || N < 0 || !valid_dtype(x_dtype) || !valid_dtype(w_dtype)) return B2N_ERR_BAD_ARG;
+  if (N == 0 || (!dgamma && !dbeta)) return B2N_OK;
+  if (!workspace || !is_aligned(workspace, 16)) return B2N_ERR_WORKSPACE;
+  if (!device_ready()) return B2N_ERR_CUDA;
+  return launch_norm_wgrad_fold(workspace, partial_rows, N, dgamma, dbeta, x_dtype, w_dtype,
+                                static_cast<cudaStream_t>(stream));
+}
+
 int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t inner, int in_dtype, int out_dtype,
                     int is_log, void* stream) {
   if (outer < 0 || N < 0 || inner < 0 || !valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return B2N_ERR_BAD_ARG;

@@ -18,7 +18,11 @@ size_t norm_bwd_workspace_bytes(int64_t M, int64_t N, int x_dtype, int w_dtype, 
 int launch_norm_bwd(bool rms, const void* dy, const void* x, const void* mean, const void* rstd,
                     const void* gamma, void* dx, void* dgamma, void* dbeta, void* workspace,
                     size_t workspace_bytes, int64_t M, int64_t N, int x_dtype, int w_dtype,
-                    cudaStream_t st);
+                    cudaStream_t st, int64_t* partials_out = nullptr);
+// partials_out != nullptr: the row kernels leave the weight-gradient partial sums workspace[*partials_out][2][N]
+// unfolded (dgamma / dbeta are not touched); launch_norm_wgrad_fold turns them into dgamma / dbeta.
+int launch_norm_wgrad_fold(const void* workspace, int64_t partial_rows, int64_t N, void* dgamma, void* dbeta,
+                           int x_dtype, int w_dtype, cudaStream_t st);
 
 int launch_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t inner, int in_dtype,
                        int out_dtype, bool is_log, cudaStream_t st);

@@ -43,14 +43,27 @@ size_t norm_bwd_workspace_bytes(int64_t M, int64_t N, int x_dtype, int w_dtype, 
 
 int launch_norm_bwd(bool rms, const void* dy, const void* x, const void* mean, const void* rstd,
                     const void* gamma, void* dx, void* dgamma, void* dbeta, void* ws, size_t ws_bytes,
-                    int64_t M, int64_t N, int x_dtype, int w_dtype, cudaStream_t st) {
+                    int64_t M, int64_t N, int x_dtype, int w_dtype, cudaStream_t st, int64_t* partials_out) {
   switch (combo_of(x_dtype, w_dtype)) {
-    case C_F32: return norm_bwd_f32(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st);
-    case C_F16: return norm_bwd_f16(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st);
-    case C_F16_W32: return norm_bwd_f16_w32(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st);
-    case C_BF16: return norm_bwd_bf16(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st);
-    case C_BF16_W32: return norm_bwd_bf16_w32(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st);
-    case C_F64: return norm_bwd_f64(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st);
+    case C_F32: return norm_bwd_f32(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out);
+    case C_F16: return norm_bwd_f16(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out);
+    case C_F16_W32: return norm_bwd_f16_w32(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out);
+    case C_BF16: return norm_bwd_bf16(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out);
+    case C_BF16_W32: return norm_bwd_bf16_w32(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out);
+    case C_F64: return norm_bwd_f64(rms, dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out);
+    default: return B2N_ERR_UNSUPPORTED_DTYPE;
+  }
+}
+
+int launch_norm_wgrad_fold(const void* ws, int64_t P, int64_t N, void* dgamma, void* dbeta, int x_dtype, int w_dtype,
+                           cudaStream_t st) {
+  switch (combo_of(x_dtype, w_dtype)) {
+    case C_F32: return norm_fold_f32(ws, P, N, dgamma, dbeta, st);
+    case C_F16: return norm_fold_f16(ws, P, N, dgamma, dbeta, st);
+    case C_F16_W32: return norm_fold_f16_w32(ws, P, N, dgamma, dbeta, st);
+    case C_BF16: return norm_fold_bf16(ws, P, N, dgamma, dbeta, st);
+    case C_BF16_W32: return norm_fold_bf16_w32(ws, P, N, dgamma, dbeta, st);
+    case C_F64: return norm_fold_f64(ws, P, N, dgamma, dbeta, st);
     default: return B2N_ERR_UNSUPPORTED_DTYPE;
   }
 }

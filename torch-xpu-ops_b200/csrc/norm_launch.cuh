@@ -169,7 +169,7 @@ int norm_bwd_ring_launch(const RingPlan& p, bool wgrad, const T* dy, const T* x,
 template <typename T, typename WT, bool RMS>
 int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const void* rstd_, const void* gamma_,
                    void* dx_, void* dgamma_, void* dbeta_, void* workspace, size_t workspace_bytes, int64_t M,
-                   int64_t N, cudaStream_t st) {
+                   int64_t N, cudaStream_t st, int64_t* partials_out) {
   using A = acc_t<T>;
   const T* dy = static_cast<const T*>(dy_);
   const T* x = static_cast<const T*>(x_);
@@ -179,7 +179,9 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
   T* dx = static_cast<T*>(dx_);
   WT* dgamma = static_cast<WT*>(dgamma_);
   WT* dbeta = RMS ? nullptr : static_cast<WT*>(dbeta_);
-  const bool wgrad = dgamma != nullptr || dbeta != nullptr;
+  // partials_out: the caller folds the partial sums itself (norm_wgrad_fold_typed), possibly on another stream;
+  // the row kernels then only leave ws[*partials_out][2][N] behind.
+  const bool wgrad = dgamma != nullptr || dbeta != nullptr || partials_out != nullptr;
   const int forced = forced_path();
   if (wgrad) {
     if (workspace == nullptr || !is_aligned(workspace, 16) || workspace_bytes < norm_bwd_ws_bytes_typed<T>(M, N))
@@ -204,7 +206,8 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
           case 256: e = norm_bwd_ring_launch<T, WT, RMS, 256>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
           default: e = norm_bwd_ring_launch<T, WT, RMS, 512>(p, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st); break;
         }
-        if (e != B2N_OK || !wgrad) return e;
+        if (partials_out != nullptr) *partials_out = static_cast<int64_t>(p.grid) * p.ng;
+        if (e != B2N_OK || !wgrad || partials_out != nullptr) return e;
         return launch_pdl(norm_bwd_wgrad_fold_kernel<float, WT>, fold_grid, fold_block, 0, st,
                           static_cast<const float*>(ws), dgamma, dbeta, static_cast<int64_t>(p.grid) * p.ng, N);
       }
@@ -239,10 +242,24 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
       norm_bwd_wgrad_partial_kernel<T, RMS><<<grid, block, 0, st>>>(dy, x, mean, rstd, ws, M, N, rpc);
       if (int e = launched()) return e;
     }
+    if (partials_out != nullptr) {
+      *partials_out = chunks;
+      return B2N_OK;
+    }
     norm_bwd_wgrad_fold_kernel<A, WT><<<fold_grid, fold_block, 0, st>>>(ws, dgamma, dbeta, chunks, N);
     if (int e = launched()) return e;
   }
   return B2N_OK;
+}
+
+// The fold on its own: ws[P][2][N] (accumulate type of T) -> dgamma / dbeta of type WT, fixed order.
+template <typename T, typename WT>
+int norm_wgrad_fold_typed(const void* ws, int64_t P, int64_t N, void* dgamma, void* dbeta, cudaStream_t st) {
+  using A = acc_t<T>;
+  const dim3 fold_block(32, kFoldLanes);
+  const dim3 fold_grid(static_cast<unsigned>((N + 31) / 32), 2);
+  return launch_pdl(norm_bwd_wgrad_fold_kernel<A, WT>, fold_grid, fold_block, 0, st, static_cast<const A*>(ws),
+                    static_cast<WT*>(dgamma), static_cast<WT*>(dbeta), P, N);
 }
 
 // Declares/defines the per-type entry points that norm_dispatch.cu switches over.
@@ -251,7 +268,8 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
                       void* rstd, int64_t M, int64_t N, double eps, cudaStream_t st);                           \
   int norm_bwd_##NAME(bool rms, const void* dy, const void* x, const void* mean, const void* rstd,              \
                       const void* gamma, void* dx, void* dgamma, void* dbeta, void* ws, size_t ws_bytes,        \
-                      int64_t M, int64_t N, cudaStream_t st);                                                   \
+                      int64_t M, int64_t N, cudaStream_t st, int64_t* partials_out);                            \
+  int norm_fold_##NAME(const void* ws, int64_t P, int64_t N, void* dgamma, void* dbeta, cudaStream_t st);       \
   size_t norm_bwd_ws_##NAME(int64_t M, int64_t N);
 
 #define B2N_NORM_TYPED_DEFINE(NAME, T, WT)                                                                      \
@@ -262,9 +280,12 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
   }                                                                                                             \
   int norm_bwd_##NAME(bool rms, const void* dy, const void* x, const void* mean, const void* rstd,              \
                       const void* gamma, void* dx, void* dgamma, void* dbeta, void* ws, size_t ws_bytes,        \
-                      int64_t M, int64_t N, cudaStream_t st) {                                                  \
-    return rms ? norm_bwd_typed<T, WT, true>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st) \
-               : norm_bwd_typed<T, WT, false>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st); \
+                      int64_t M, int64_t N, cudaStream_t st, int64_t* partials_out) {                           \
+    return rms ? norm_bwd_typed<T, WT, true>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out) \
+               : norm_bwd_typed<T, WT, false>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, ws, ws_bytes, M, N, st, partials_out); \
+  }                                                                                                             \
+  int norm_fold_##NAME(const void* ws, int64_t P, int64_t N, void* dgamma, void* dbeta, cudaStream_t st) {      \
+    return norm_wgrad_fold_typed<T, WT>(ws, P, N, dgamma, dbeta, st);                                           \
   }                                                                                                             \
   size_t norm_bwd_ws_##NAME(int64_t M, int64_t N) { return norm_bwd_ws_bytes_typed<T>(M, N); }
 
