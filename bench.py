@@ -109,7 +109,9 @@ class Cfg4LayerNorm(Workload):
         from b200norm import F32, BF16, load_library
         nbytes = load_library().b2n_norm_bwd_workspace_bytes(rows, n, BF16, F32, 1)
         st["ws"] = torch.empty(max(nbytes, 1), device=dev, dtype=torch.uint8)
-        st["ws2"] = torch.empty(max(nbytes, 1), device=dev, dtype=torch.uint8) if COLLECTIVE_MODE == "fused-side" else None
+        # "exchange-side": the backward folds into these, the exchange kernel on the second stream reduces them
+        # over the ranks into st["wgrads"]
+        st["wlocal"] = [torch.empty((2, n), device=dev, dtype=torch.float32) for _ in range(2)] if COLLECTIVE_MODE == "exchange-side" else None
         st["side"] = torch.cuda.Stream(dev)
         st["pending"] = [None, None]
         return st
@@ -117,31 +119,35 @@ class Cfg4LayerNorm(Workload):
     def open_exchange(self, st, dev, sm_margin):
         """(collective) the peer-memory exchange buffers of the fused fold + all-reduce kernel."""
         from b200norm.peer import WgradExchange
-        ctas = 128 if COLLECTIVE_MODE == "fused" else max(2, 2 * sm_margin)
+        ctas = 128 if COLLECTIVE_MODE == "fused" else max(1, sm_margin)
         st["exch"] = WgradExchange(self.N, dev, ctas=ctas)
 
     def prepare(self, capi, st):
         """Prepared C-ABI calls (pointers and sizes converted once) on the CURRENT stream."""
         st["fwd"] = capi.prepare_layer_norm(st["x"], st["gamma"], st["beta"], 1e-5, st["y"], st["mean"], st["rstd"])
-        if COLLECTIVE_MODE in ("fused", "fused-side"):
-            wss = [st["ws"], st["ws2"] if st["ws2"] is not None else st["ws"]]
+        if COLLECTIVE_MODE == "fused":
+            # row kernels, then ONE kernel that folds the partial sums and adds the ranks' results over peer memory
             st["bwd"], st["exc"] = [], []
-            for k, wg in enumerate(st["wgrads"]):
+            for wg in st["wgrads"]:
                 call, rows = capi.prepare_norm_backward_partials(False, st["dy"], st["x"], st["mean"], st["rstd"],
-                                                                 st["gamma"], st["dx"], wss[k])
+                                                                 st["gamma"], st["dx"], st["ws"])
                 st["bwd"].append(call)
-                if COLLECTIVE_MODE == "fused":
-                    st["exc"].append(st["exch"].prepare(wss[k], rows, wg[0], wg[1]))
-                else:
-                    with torch.cuda.stream(st["side"]):
-                        st["exc"].append(st["exch"].prepare(wss[k], rows, wg[0], wg[1]))
+                st["exc"].append(st["exch"].prepare(st["ws"], rows, wg[0], wg[1]))
+            return
+        if COLLECTIVE_MODE == "exchange-side":
+            # the ordinary backward (row kernels + fold) into a local buffer; the same peer-memory kernel, given that
+            # buffer as ONE partial row, adds the ranks' buffers on the second stream
+            st["bwd"] = [capi.prepare_layer_norm_backward(st["dy"], st["x"], st["mean"], st["rstd"], st["gamma"], st["dx"],
+                                                          wl[0], wl[1], st["ws"]) for wl in st["wlocal"]]
+            with torch.cuda.stream(st["side"]):
+                st["exc"] = [st["exch"].prepare(wl, 1, wg[0], wg[1]) for wl, wg in zip(st["wlocal"], st["wgrads"])]
             return
         st["bwd"] = [capi.prepare_layer_norm_backward(st["dy"], st["x"], st["mean"], st["rstd"], st["gamma"], st["dx"],
                                                       wg[0], wg[1], st["ws"]) for wg in st["wgrads"]]
 
     def _fused_step(self, st, k, main, side):
-        """Row kernels on `main`; the fused fold + all-reduce behind them on `main` ("fused") or on `side`
-        ("fused-side", joined before buffer k is written again)."""
+        """Backward on `main`; the peer-memory kernel behind it on `main` ("fused": fold + exchange) or on `side`
+        ("exchange-side": exchange only, joined before buffer k is written again)."""
         if st["pending"][k] is not None:
             main.wait_event(st["pending"][k])
             st["pending"][k] = None
@@ -161,7 +167,7 @@ class Cfg4LayerNorm(Workload):
 
     def step(self, capi, st, world):
         k = st["k"] = st["k"] ^ 1
-        if COLLECTIVE_MODE in ("fused", "fused-side"):
+        if COLLECTIVE_MODE in ("fused", "exchange-side"):
             self._fused_step(st, k, torch.cuda.current_stream(), st["side"])
             return
         if st["works"][k] is not None:
@@ -177,22 +183,26 @@ class Cfg4LayerNorm(Workload):
             else:
                 dist.all_reduce(st["wgrads"][k])
 
-    def capture_cycle(self, capi, st, world, cs, side):
-        """Enqueue one cycle (two steps) on the capturing stream `cs`; each step's all-reduce goes to `side`
-        and is joined where its buffer is next written, or at the end of the cycle."""
-        if COLLECTIVE_MODE in ("fused", "fused-side"):
-            # the exchange calls of "fused-side" were prepared on st["side"]; `side` is not used
-            for k in (1, 0):
-                self._fused_step(st, k, cs, st["side"])
+    def capture_cycle(self, capi, st, world, cs, side, cycles=1):
+        """Enqueue `cycles` cycles (of two steps) on the capturing stream `cs`; each step's all-reduce goes to `side`
+        and is joined where its buffer is next written, or — the last two — at the end.  (A graph is a unit: what is
+        still running on `side` when its last step ends cannot overlap the next replay, so the more steps one graph
+        holds, the smaller the share of that un-overlapped tail.)"""
+        if COLLECTIVE_MODE in ("fused", "exchange-side"):
+            # the exchange calls of "exchange-side" were prepared on st["side"]; `side` is not used
+            for _ in range(cycles):
+                for k in (1, 0):
+                    self._fused_step(st, k, cs, st["side"])
             for k in (0, 1):
                 if st["pending"][k] is not None:
                     cs.wait_event(st["pending"][k])
                     st["pending"][k] = None
             return
         pending = [None, None]
-        for k in (1, 0):
+        for k in [1, 0] * cycles:
             if pending[k] is not None:
                 cs.wait_event(pending[k])
+                pending[k] = None
             st["fwd"]()
             st["bwd"][k]()
             if world > 1 and COLLECTIVE_MODE != "none":
@@ -346,7 +356,7 @@ class Cfg4LayerNorm(Workload):
         return 2 * rows * n * 2, 2 * rows * n * 2 + 2 * n * 4
 
 
-COLLECTIVE_MODE = "async"  # --collective: async (default) | sync | none (diagnostic: no gradient exchange)
+COLLECTIVE_MODE = "async"  # set from --collective in main()
 WORKLOADS = {"cfg4": Cfg4LayerNorm}
 
 
@@ -533,8 +543,14 @@ class StepRunner:
         self.launches_per_step = wl.launches_per_step
         if hasattr(wl, "prepare"):
             wl.prepare(capi, st)
+        self.cycles_per_graph = 1
         if want_graph and hasattr(wl, "capture_cycle"):
             if steps % self.cycle == 0:
+                # one graph holds the whole region's steps when that is at most 64 of them, else the largest
+                # whole number of cycles that divides the region and stays within 64 steps
+                n = steps // self.cycle
+                per = max(d for d in range(1, n + 1) if n % d == 0 and d * self.cycle <= max(64, self.cycle))
+                self.cycles_per_graph = per
                 self._capture(dev)
             else:
                 self.graph_note = f"off (--steps {steps} is no whole number of {self.cycle}-step cycles)"
@@ -550,9 +566,9 @@ class StepRunner:
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=cs):
-                wl.capture_cycle(self.capi, st, world, cs, side)
+                wl.capture_cycle(self.capi, st, world, cs, side, self.cycles_per_graph)
             self.graph = g
-            self.graph_note = f"on: one graph per {self.cycle} step(s)"
+            self.graph_note = f"on: one graph per {self.cycles_per_graph * self.cycle} step(s)"
         except Exception as exc:  # noqa: BLE001
             torch.cuda.synchronize()
             self.graph = None
@@ -562,7 +578,7 @@ class StepRunner:
 
     def run(self, steps):
         if self.graph is not None:
-            for _ in range(max(1, steps // self.cycle)):
+            for _ in range(max(1, steps // (self.cycle * self.cycles_per_graph))):
                 self.graph.replay()
             return
         for _ in range(steps):
@@ -639,7 +655,7 @@ def copy_gbs_at_size(nbytes: int, dev, iters: int = 40):
 
 def measure_workload(wl, capi, st, world, rank, dev, steps, warmup, rows, global_rows, scaling, want_graph, barrier):
     runner = StepRunner(wl, capi, st, world, dev, want_graph, steps)
-    runner.run(-(-max(warmup, 1) // runner.cycle) * runner.cycle)
+    runner.run(-(-max(warmup, 1) // (runner.cycle * runner.cycles_per_graph)) * runner.cycle * runner.cycles_per_graph)
     runner.finish()
     barrier()
     regions, host, span = time_regions(runner, steps, world, dev, barrier)
@@ -746,9 +762,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg4")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"])
-    ap.add_argument("--collective", default="async", choices=["async", "sync", "none", "fused", "fused-side"],
+    ap.add_argument("--collective", default="auto", choices=["auto", "async", "sync", "none", "fused", "exchange-side"],
                     help="cfg4 gradient all-reduce: NCCL overlapped with the next step, NCCL in-stream, (diagnostic) skipped, "
-                         "or the library's own fold + all-reduce kernel over peer memory, in-stream / on a second stream")
+                         "the library's own fold + all-reduce kernel over peer memory in-stream (fused), or its exchange alone "
+                         "on a second stream behind an in-stream fold (exchange-side)")
     ap.add_argument("--graph", default="on", choices=["on", "off"],
                     help="replay the steps from a CUDA graph (where the workload supports it) or enqueue them call by call")
     ap.add_argument("--sm-margin", type=int, default=-1,
@@ -762,7 +779,9 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     global COLLECTIVE_MODE
-    COLLECTIVE_MODE = args.collective
+    # auto: the library's own all-reduce kernel over peer memory on a second stream (2.3 us per step of main-stream
+    # time at two GPUs against 12-14 for NCCL's kernel inside the same graph); NCCL if the buffers cannot be opened
+    COLLECTIVE_MODE = "exchange-side" if args.collective == "auto" else args.collective
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -789,7 +808,9 @@ def main():
     # From four GPUs on, the collective's kernel gets four SMs of its own (a ring CTA fills its SM, so without
     # them the all-reduce waits for a kernel boundary and then delays the next kernel's CTAs); at N = 2 the
     # all-reduce is too short for the margin to pay.  Only the config-4 step has a collective that overlaps kernels.
-    overlapped = world >= 4 and args.workload in ("cfg4", "ln_long") and COLLECTIVE_MODE in ("async", "fused-side")
+    # NCCL's kernel needs SMs of its own beside the persistent kernels from four GPUs on (a ring CTA fills its SM); the
+    # library's one-CTA exchange kernel takes the SM the planner leaves over anyway (no margin)
+    overlapped = world >= 4 and args.workload in ("cfg4", "ln_long") and COLLECTIVE_MODE == "async"
     sm_margin = args.sm_margin if args.sm_margin >= 0 else (4 if overlapped else 0)
     capi.set_tuning(b200norm.TUNE_SM_MARGIN, sm_margin)
     for item in filter(None, args.tune.split(",")):
@@ -807,9 +828,29 @@ def main():
         rows = wl.rows
         global_rows = wl.rows * world
     st = wl.make_device_state(rows, dev, seed=4001 + rank)
-    if COLLECTIVE_MODE in ("fused", "fused-side"):
-        assert hasattr(wl, "open_exchange"), "--collective fused needs a workload with a weight-gradient exchange"
-        wl.open_exchange(st, dev, sm_margin)
+    collective_note = None
+    if COLLECTIVE_MODE in ("fused", "exchange-side"):
+        if not hasattr(wl, "open_exchange") or world == 1:
+            if args.collective != "auto" and world > 1:
+                raise SystemExit(f"--collective {args.collective}: workload {wl.name} has no weight-gradient exchange")
+            COLLECTIVE_MODE = "async"
+        else:
+            ok = torch.ones(1, device=dev)
+            try:
+                wl.open_exchange(st, dev, sm_margin)
+            except Exception as exc:  # noqa: BLE001
+                ok.zero_()
+                collective_note = f"peer-memory exchange unavailable ({type(exc).__name__}: {str(exc)[:100]}): NCCL instead"
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)  # every rank takes the same path
+            if float(ok) == 0.0:
+                if args.collective != "auto":
+                    raise SystemExit(collective_note or "a peer could not open the exchange buffers")
+                COLLECTIVE_MODE = "async"
+                collective_note = collective_note or "peer-memory exchange unavailable on another rank: NCCL instead"
+                if args.sm_margin < 0 and world >= 4:
+                    sm_margin = 4
+                    capi.set_tuning(b200norm.TUNE_SM_MARGIN, sm_margin)
+                st = wl.make_device_state(rows, dev, seed=4001 + rank)
     sampler = ClockSampler(dev)
     sampler.start()
 
@@ -882,8 +923,8 @@ def main():
             "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16 storage, f32 accumulate", "data": "synthetic",
             "config": {"workload": f"{wl.name}: {wl.describe()}", "global_rows": global_rows, "rows_per_gpu": rows,
                        "sm_margin": sm_margin, "parallelism": f"row-sharded dp{world}", "l2": wl.l2_note,
-                       "graph": res["graph"],
-                       "collective": (getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, " + {"async": "NCCL, overlapped with the next step", "sync": "NCCL, in stream", "none": "SKIPPED (diagnostic run)", "fused": "own fold + all-reduce kernel over peer memory, in stream", "fused-side": "own fold + all-reduce kernel over peer memory, on a second stream"}[COLLECTIVE_MODE]) if world > 1 else "none")},
+                       "graph": res["graph"], "collective_note": collective_note,
+                       "collective": (getattr(wl, "collective", "all_reduce(fp32[2,N]) per step, " + {"async": "NCCL, overlapped with the next step", "sync": "NCCL, in stream", "none": "SKIPPED (diagnostic run)", "fused": "own fold + all-reduce kernel over peer memory, in stream", "exchange-side": "fold in stream, own all-reduce kernel over peer memory on a second stream"}[COLLECTIVE_MODE]) if world > 1 else "none")},
             "spread": res["spread"], "sustained_ms_per_step": res["sustained_ms_per_step"],
             "host_enqueue_us_per_step": res["host_enqueue_us_per_step"],
             "collective_us": coll_us, "shard_check": shard_check,

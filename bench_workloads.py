@@ -73,9 +73,10 @@ class Cfg1LayerNormFwd(_Simple):
         i = st["i"] = (st["i"] + 1) % 16
         st["calls"][i]()
 
-    def capture_cycle(self, capi, st, world, cs, side):
-        for call in st["calls"]:
-            call()
+    def capture_cycle(self, capi, st, world, cs, side, cycles=1):
+        for _ in range(cycles):
+            for call in st["calls"]:
+                call()
 
     def cpu_step(self, cpu):
         return torch.ops.aten.native_layer_norm(cpu["x"], [self.N], cpu["gamma"], cpu["beta"], 1e-5)
@@ -141,12 +142,13 @@ class Cfg2RmsNorm(_Simple):
         if world > 1:
             dist.all_reduce(st["wgrad"])
 
-    def capture_cycle(self, capi, st, world, cs, side):
-        for fwd, bwd in st["calls"]:
-            fwd()
-            bwd()
-            if world > 1:
-                dist.all_reduce(st["wgrad"])
+    def capture_cycle(self, capi, st, world, cs, side, cycles=1):
+        for _ in range(cycles):
+            for fwd, bwd in st["calls"]:
+                fwd()
+                bwd()
+                if world > 1:
+                    dist.all_reduce(st["wgrad"])
 
     def collective_buffer(self, st):
         return st["wgrad"]

@@ -74,6 +74,11 @@ inline RingPlan plan_ring(int64_t M, int64_t N, int esize, int nin, int ept, int
   const int64_t ntiles = (M + p.ng * p.rpg - 1) / (p.ng * p.rpg);
   if (ntiles > 0x7fff0000LL) return p;  // tile indices are handed out through a 32-bit counter
   p.grid = static_cast<int>(ntiles < sm_count ? ntiles : sm_count);
+  // No CTA can finish before the one with the most tiles: with w = ceil(ntiles / grid) tiles on the busiest CTA,
+  // ceil(ntiles / w) CTAs do the same work in the same time.  The SMs this leaves out (one of 148 for 8192 rows of
+  // 8192, none for 65536) are free for whatever runs beside the kernel — a collective's kernel on another stream.
+  const int64_t waves = (ntiles + p.grid - 1) / p.grid;
+  p.grid = static_cast<int>((ntiles + waves - 1) / waves);
   p.ok = true;
   return p;
 }
