@@ -407,3 +407,86 @@ def test_fused_fold_allreduce_on_one_rank_is_the_fold(ctas, rms):
             check_wgrad(db, dy.double(), "dbeta")
     ex.close()
     assert capi.device_status() == 0
+
+
+LONG_SHAPES = [(1, 16384), (5, 12288), (37, 16384), (300, 16384), (700, 12288), (9, 32768), (160, 32768), (6, 65536),
+               (40, 65536), (11, 12296), (7, 40000)]
+
+
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("dt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32), (torch.float16, torch.float16)])
+@pytest.mark.parametrize("M,N", LONG_SHAPES)
+def test_long_rows_take_the_slab_kernels(M, N, dt, wdt, rms):
+    # rows beyond one CTA's threads (the reference's few-long-rows regime, sycl/Norm.h:620-696): column slabs over a
+    # thread-block cluster, statistics exchanged through distributed shared memory, weight gradients still fused;
+    # 12296 and 40000 leave a ragged last slab, 300 x 16384 and 700 x 12288 give every cluster several tiles
+    x = ao.randn((M, N), 940 + N % 89, dt)
+    x[0] += 3.0  # a row whose slabs' first elements lie far from the slab means: the exact second pass
+    dy = ao.randn((M, N), 941, dt)
+    g = ao.randn((N,), 942, wdt, 1.0, 0.02)
+    b = ao.randn((N,), 943, wdt, 0.0, 0.02)
+    y_buf, y_chk = guarded_empty((M, N), dt)
+    dx_buf, dx_chk = guarded_empty((M, N), dt)
+    dg_buf, dg_chk = guarded_empty((N,), wdt)
+    if rms:
+        y, rstd = capi._fused_rms_norm(x.to(DEV), [N], g.to(DEV), 1e-6, out=(y_buf, torch.empty(M, device=DEV)))
+        assert capi.last_path() == "slab"
+        dx, dw = capi._fused_rms_norm_backward(dy.to(DEV), x.to(DEV), [N], rstd, g.to(DEV), out=(dx_buf, dg_buf))
+        assert capi.last_path() == "slab"
+        torch.cuda.synchronize()
+        y_chk(); dx_chk(); dg_chk()
+        ry, rrstd = ao.rms_norm_fwd(x, [N], g, 1e-6)
+        check_out(y, ry, "y"); check_stat(rstd, rrstd, "rstd")
+        rdx, _ = ao.rms_norm_bwd(dy, x, [N], g, 1e-6)
+        check_out(dx, rdx, "dx")
+        check_wgrad(dw, dy.double() * x.double() * rstd.cpu().double().reshape(-1, 1), "dweight")
+    else:
+        db_buf, db_chk = guarded_empty((N,), wdt)
+        y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5,
+                                               out=(y_buf, torch.empty(M, device=DEV), torch.empty(M, device=DEV)))
+        assert capi.last_path() == "slab"
+        dx, dg, db = capi.native_layer_norm_backward(dy.to(DEV), x.to(DEV), [N], mean, rstd, g.to(DEV), b.to(DEV),
+                                                     out=(dx_buf, dg_buf, db_buf))
+        assert capi.last_path() == "slab"
+        torch.cuda.synchronize()
+        y_chk(); dx_chk(); dg_chk(); db_chk()
+        ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+        check_out(y, ry, "y"); check_stat(mean, rmean, "mean"); check_stat(rstd, rrstd, "rstd")
+        kmean, krstd = mean.cpu(), rstd.cpu()
+        rdx, _, _ = ao.layer_norm_bwd(dy, x, [N], kmean, krstd, g, b)
+        check_out(dx, rdx, "dx")
+        xh = (x.double() - kmean.double().reshape(-1, 1)) * krstd.double().reshape(-1, 1)
+        check_wgrad(dg, dy.double() * xh, "dgamma")
+        check_wgrad(db, dy.double(), "dbeta")
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("cluster", [2, 4, 8])
+@pytest.mark.parametrize("M,N,dt", [(33, 2048, torch.bfloat16), (130, 1000, torch.float32), (64, 8192, torch.float16)])
+def test_pinned_slab_kernels_on_rows_the_ring_would_take(M, N, dt, cluster):
+    # every cluster size on shapes small enough to compare whole, bit for bit, with the ring kernels' results for
+    # the per-row outputs' gates
+    x, dy = ao.randn((M, N), 950, dt), ao.randn((M, N), 951, dt)
+    g, b = ao.randn((N,), 952, torch.float32, 1.0, 0.02), ao.randn((N,), 953, torch.float32, 0.0, 0.02)
+    if dt == torch.float16:
+        g, b = g.half(), b.half()
+    capi.set_tuning(b200norm.TUNE_CLUSTER_SIZE, cluster)
+    try:
+        with forced_path(b200norm.PATH_CLUSTER):
+            y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5)
+            assert capi.last_path() == "slab"
+            dx, dg, db = capi.native_layer_norm_backward(dy.to(DEV), x.to(DEV), [N], mean, rstd, g.to(DEV), b.to(DEV))
+            assert capi.last_path() == "slab"
+            dxo, _, _ = capi.native_layer_norm_backward(dy.to(DEV), x.to(DEV), [N], mean, rstd, g.to(DEV), b.to(DEV),
+                                                        (True, False, False))
+    finally:
+        capi.set_tuning(b200norm.TUNE_CLUSTER_SIZE, 0)
+    ry, rmean, rrstd = ao.layer_norm_fwd(x, [N], g, b, 1e-5)
+    check_out(y, ry, "y"); check_stat(mean, rmean, "mean"); check_stat(rstd, rrstd, "rstd")
+    rdx, _, _ = ao.layer_norm_bwd(dy, x, [N], mean.cpu(), rstd.cpu(), g, b)
+    check_out(dx, rdx, "dx")
+    assert torch.equal(dx, dxo)  # with and without the weight gradients: the same dx
+    xh = (x.double() - mean.cpu().double().reshape(-1, 1)) * rstd.cpu().double().reshape(-1, 1)
+    check_wgrad(dg, dy.double() * xh, "dgamma")
+    check_wgrad(db, dy.double(), "dbeta")
+    assert capi.device_status() == 0

@@ -7,6 +7,7 @@
 #include "launchers.h"
 #include "norm_generic.cuh"
 #include "norm_ring.cuh"
+#include "norm_slab.cuh"
 #include "plan.h"
 
 namespace b2n {
@@ -41,6 +42,120 @@ bool norm_vectorizable(int64_t N, const void* a, const void* b, const void* c) {
   constexpr int V = 16 / sizeof(T);
   return N % V == 0 && is_aligned(a, 16) && (b == nullptr || is_aligned(b, 16)) &&
          (c == nullptr || is_aligned(c, 16));
+}
+
+// ---- rows longer than the ring takes: column slabs over a thread-block cluster (norm_slab.cuh) --------------
+struct SlabPlan {
+  bool ok = false;
+  int c = 0;          // CTAs per cluster = slabs per row
+  int slab_vecs = 0;  // 16-byte vectors per slab
+  int tr = 0;         // rows per tile
+  int stages = 0;
+  size_t smem = 0;
+};
+// nin: tensors staged per tile (1 forward, 2 backward).  Not ok when the row does not split into at most 8 slabs of
+// at most 512 threads x 16 elements, or fewer than three stages fit (a tile is held from its phase A to its phase B).
+inline SlabPlan plan_slab(int64_t M, int64_t N, int esize, int nin, int max_smem) {
+  SlabPlan p;
+  const int vec = 16 / esize;
+  if (M <= 0 || N <= 0 || N % vec != 0) return p;
+  const int64_t nvec = N / vec;
+  const int64_t cap = static_cast<int64_t>(kNsConsumers) * (kNsEpt / vec);  // vectors one CTA's threads hold
+  const int forced_c = ring_tuning().cluster;
+  for (int c = 2; c <= kNsMaxCluster; c *= 2) {
+    if (forced_c >= 2 && c != forced_c) continue;
+    const int64_t sv = (nvec + c - 1) / c;
+    if (sv > cap) continue;
+    for (int tr = 2; tr >= 1; --tr) {
+      const int64_t stage = static_cast<int64_t>(nin) * tr * sv * 16;
+      int64_t s = (static_cast<int64_t>(max_smem) - kNsHeaderBytes) / stage;
+      if (s > kNsMaxStages) s = kNsMaxStages;
+      const int tuned = ring_tuning().stages;
+      if (tuned >= 3 && tuned < s) s = tuned;
+      if (s < 3 || (tr == 2 && s < 4)) continue;  // two-row tiles only when at least four of them fit
+      p.ok = true;
+      p.c = c;
+      p.slab_vecs = static_cast<int>(sv);
+      p.tr = tr;
+      p.stages = static_cast<int>(s);
+      p.smem = static_cast<size_t>(kNsHeaderBytes + s * stage);
+      return p;
+    }
+  }
+  return p;
+}
+
+constexpr int kSlabNoFit = 1;  // (not a b2n_status) slab_launch: no cluster of this shape fits the device
+
+// Launches `kernel` as clusters of p.c CTAs, as many clusters as the device holds at once (or as there are
+// tiles), with the dependent-launch attribute.  *clusters_out: the number of clusters (= partial rows of the backward).
+template <typename... KArgs, typename... Args>
+int slab_launch(void (*kernel)(KArgs...), const SlabPlan& p, int64_t M, std::atomic<uint64_t>& smem_done, cudaStream_t st,
+                int64_t* clusters_out, Args... args) {
+  if (int e = set_smem_once(kernel, p.smem, smem_done)) return e;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.c;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;  // the occupancy query wants the cluster shape only
+  cfg.blockDim = dim3(kNsThreads);
+  cfg.dynamicSmemBytes = p.smem;
+  cfg.stream = st;
+  const int sms = persistent_ctas(device_info().sm_count);
+  const int by_count = sms / p.c > 0 ? sms / p.c : 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(p.c) * static_cast<unsigned>(by_count));
+  int max_clusters = 0;
+  if (int e = check_cuda(cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg))) return e;
+  if (max_clusters < 1) return kSlabNoFit;  // the device cannot hold even one such cluster: the caller takes another family
+  if (max_clusters > by_count) max_clusters = by_count;
+  const int64_t ntiles = (M + p.tr - 1) / p.tr;
+  int64_t nclusters = ntiles < max_clusters ? ntiles : max_clusters;
+  const int64_t waves = (ntiles + nclusters - 1) / nclusters;  // no cluster finishes before the busiest one
+  nclusters = (ntiles + waves - 1) / waves;
+  if (clusters_out != nullptr) *clusters_out = nclusters;
+  cfg.gridDim = dim3(static_cast<unsigned>(nclusters * p.c));
+  cfg.numAttrs = 2;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return check_cuda(e);
+  return launched();
+}
+
+template <typename T, typename WT, bool RMS>
+int norm_fwd_slab_launch(const SlabPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, float* mean, float* rstd,
+                         int64_t M, int64_t N, double eps, cudaStream_t st) {
+  ProfileScope prof(RMS ? "rms_norm_fwd_slab" : "layer_norm_fwd_slab", st);
+  static std::atomic<uint64_t> done[2];
+  int* status = device_status_ptr();
+  if (p.tr == 2)
+    return slab_launch(norm_fwd_slab_kernel<T, WT, RMS, 2>, p, M, done[0], st, nullptr, x, gamma, beta, y, mean, rstd, M, N,
+                       static_cast<float>(eps), p.slab_vecs, p.stages, status);
+  return slab_launch(norm_fwd_slab_kernel<T, WT, RMS, 1>, p, M, done[1], st, nullptr, x, gamma, beta, y, mean, rstd, M, N,
+                     static_cast<float>(eps), p.slab_vecs, p.stages, status);
+}
+
+template <typename T, typename WT, bool RMS>
+int norm_bwd_slab_launch(const SlabPlan& p, bool wgrad, const T* dy, const T* x, const float* mean, const float* rstd,
+                         const WT* gamma, T* dx, float* ws, int64_t M, int64_t N, cudaStream_t st, int64_t* clusters) {
+  ProfileScope prof(RMS ? "rms_norm_bwd_slab" : "layer_norm_bwd_slab", st);
+  static std::atomic<uint64_t> done[4];
+  int* status = device_status_ptr();
+  if (wgrad) {
+    if (p.tr == 2)
+      return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, true, 2>, p, M, done[0], st, clusters, dy, x, mean, rstd, gamma, dx,
+                         ws, M, N, p.slab_vecs, p.stages, status);
+    return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, true, 1>, p, M, done[1], st, clusters, dy, x, mean, rstd, gamma, dx, ws,
+                       M, N, p.slab_vecs, p.stages, status);
+  }
+  if (p.tr == 2)
+    return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, false, 2>, p, M, done[2], st, clusters, dy, x, mean, rstd, gamma, dx,
+                       ws, M, N, p.slab_vecs, p.stages, status);
+  return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, false, 1>, p, M, done[3], st, clusters, dy, x, mean, rstd, gamma, dx, ws,
+                     M, N, p.slab_vecs, p.stages, status);
 }
 
 // ---- forward ------------------------------------------------------------------------------------
@@ -82,7 +197,7 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
       const DeviceInfo& di = device_info();
       // one tensor per stage: 64 KB tiles (half as many tile hand-overs) still leave three stages in rotation
       const RingPlan p = plan_ring(M, N, sizeof(T), 1, kNormFwdEpt, persistent_ctas(di.sm_count), di.max_smem_optin, 65536);
-      if (p.ok) {
+      if (p.ok && forced != B2N_PATH_CLUSTER) {
         note_path("ring");
         switch (p.group) {
           case 32: return norm_fwd_ring_launch<T, WT, RMS, 32>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
@@ -90,6 +205,17 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
           case 128: return norm_fwd_ring_launch<T, WT, RMS, 128>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
           case 256: return norm_fwd_ring_launch<T, WT, RMS, 256>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
           default: return norm_fwd_ring_launch<T, WT, RMS, 512>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+        }
+      }
+      if (forced == B2N_PATH_AUTO || forced == B2N_PATH_CLUSTER) {
+        // rows beyond the ring (or any row the slabs can take, when that family is pinned): column slabs over a cluster
+        const SlabPlan sp = plan_slab(M, N, sizeof(T), 1, di.max_smem_optin);
+        if (sp.ok) {
+          const int e = norm_fwd_slab_launch<T, WT, RMS>(sp, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+          if (e != kSlabNoFit) {
+            note_path("slab");
+            return e;
+          }
         }
       }
     }
@@ -131,6 +257,9 @@ template <typename T> int64_t wgrad_partial_rows(int64_t M, int64_t N) {
     const DeviceInfo& di = device_info();
     const RingPlan p = plan_norm_bwd<T>(M, N, di, true);
     if (p.ok && static_cast<int64_t>(p.grid) * p.ng > rows) rows = static_cast<int64_t>(p.grid) * p.ng;
+    // the slab kernels write one partial row per cluster: at most one cluster per two SMs
+    const SlabPlan sp = plan_slab(M, N, sizeof(T), 2, di.max_smem_optin);
+    if (sp.ok && di.sm_count / 2 > rows) rows = di.sm_count / 2;
   }
   return rows;
 }
@@ -196,7 +325,21 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
         is_aligned(dx, 16) && N <= (1 << 20)) {
       const DeviceInfo& di = device_info();
       const RingPlan p = plan_norm_bwd<T>(M, N, di);
-      if (p.ok) {
+      if (!(p.ok && forced != B2N_PATH_CLUSTER) && (forced == B2N_PATH_AUTO || forced == B2N_PATH_CLUSTER)) {
+        const SlabPlan sp = plan_slab(M, N, sizeof(T), 2, di.max_smem_optin);
+        if (sp.ok) {
+          int64_t clusters = 0;
+          const int e = norm_bwd_slab_launch<T, WT, RMS>(sp, wgrad, dy, x, mean, rstd, gamma, dx, ws, M, N, st, &clusters);
+          if (e != kSlabNoFit) {
+            note_path("slab");
+            if (partials_out != nullptr) *partials_out = clusters;
+            if (e != B2N_OK || !wgrad || partials_out != nullptr) return e;
+            return launch_pdl(norm_bwd_wgrad_fold_kernel<float, WT>, fold_grid, fold_block, 0, st,
+                              static_cast<const float*>(ws), dgamma, dbeta, clusters, N);
+          }
+        }
+      }
+      if (p.ok && forced != B2N_PATH_CLUSTER) {
         note_path("ring");
         int e;
         switch (p.group) {
