@@ -211,6 +211,33 @@ int b2n_norm_wgrad_fold_allreduce(const void* workspace, int64_t partial_rows, i
                                   void* const* peer_buffers, int64_t n_max, int rank, int world,
                                   void* dgamma, void* dbeta, int w_dtype, int ctas, void* stream);
 
+/* ---- sibling norms -------------------------------------------------------------------------------
+ * GroupNorm forward over a contiguous [N, C, HxW] tensor with G groups (C % G == 0): per (n, g) the
+ * mean and 1/sqrt(var + eps) of the D * HxW elements of the group (D = C / G), then
+ * y = (x - mean) * rstd * gamma[c] + beta[c] per channel c.  gamma, beta: [C] of w_dtype or NULL
+ * (w_dtype == x_dtype, or B2N_F32 with 16-bit x); mean, rstd: [N * G] of stat_dtype (x_dtype, or
+ * B2N_F32 when the weights are fp32).  A group may hold at most 2^31 - 1 elements.
+ *
+ * Replaces at::native::xpu::group_norm_kernel (src/ATen/native/xpu/sycl/GroupNormKernels.h:17-28;
+ * moments GroupNormKernels.cpp:73-136, driver :365-499) behind the GroupNormKernel dispatch stub
+ * (src/ATen/native/xpu/GroupNorm.cpp:20). */
+int b2n_group_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, void* mean,
+                       void* rstd, int64_t N, int64_t C, int64_t HxW, int64_t G, double eps,
+                       int x_dtype, int w_dtype, int stat_dtype, void* stream);
+
+/* BatchNorm statistics of a contiguous [N, C, HxW] tensor, per channel over N and HxW, in fp32:
+ * mean[C] and, mode 0, second[C] = 1 / sqrt(biased var + eps) (batch_norm_stats); mode 1,
+ * second[C] = biased var, and running_mean / running_var ([C] of running_dtype = x_dtype or
+ * B2N_F32; either may be NULL) are blended in place with `momentum`, the variance unbiased by
+ * n / (n - 1) (batch_norm_update_stats).
+ *
+ * Replaces batch_norm_stats_kernel and batch_norm_update_stats_kernel
+ * (src/ATen/native/xpu/sycl/BatchNormKernels.h:19, :52; BatchNormKernels.cpp:992, :3864) behind
+ * batch_norm_stats_xpu / batch_norm_update_stats_xpu (src/ATen/native/xpu/BatchNorm.cpp:20, :76). */
+int b2n_batch_norm_stats(const void* x, float* mean, float* second, void* running_mean,
+                         void* running_var, int64_t N, int64_t C, int64_t HxW, double eps,
+                         double momentum, int mode, int x_dtype, int running_dtype, void* stream);
+
 /* ---- softmax / log-softmax --------------------------------------------------------------------
  * The tensor is viewed as [outer, N, inner]; the reduction runs over N (inner == 1 for the last
  * dim).  out_dtype == in_dtype, or B2N_F32 with a 16-bit input ("half_to_float").

@@ -1,0 +1,144 @@
+"""GroupNorm forward and BatchNorm statistics: CUDA kernels through the C ABI and the dispatcher vs CPU ATen.
+
+Tolerances as for layer norm: fp32 outputs |a-b| <= 1e-5*|b| + 1e-6*max(1, rms(b)); 16-bit outputs within 1 ulp of
+the fp32-accumulated reference (CPU ATen on fp32 upcasts, rounded once) or the same absolute floor; statistics
+relative 1e-5 (+1e-6 absolute).  Shapes: the (N, C, HxW, G) grid the reference's kernel driver distinguishes
+(src/ATen/native/xpu/sycl/GroupNormKernels.cpp:365-499: vectorisable or not, one channel per group, one group) and
+scaled-down versions of test/microbench/group_norm.py's."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import b200norm
+from b200norm import capi
+from oracle import aten_oracle as ao
+
+from gpu_util import DEV
+
+pytestmark = pytest.mark.gpu
+
+# (N, C, spatial, groups)
+GN_SHAPES = [((2, 6, 5), 3), ((1, 4, 1), 2), ((3, 8, 7, 9), 4), ((4, 32, 16, 16), 32), ((2, 32, 8, 8), 1),
+             ((8, 128, 32, 32), 16), ((3, 33, 31), 11), ((2, 64, 4, 8, 8), 8), ((1, 16, 128, 128), 4), ((5, 12, 1000), 3)]
+
+
+def _stat_err(a, ref):
+    a, ref = a.detach().cpu().double().reshape(-1), ref.detach().cpu().double().reshape(-1)
+    return float(((a - ref).abs() / (1e-5 * ref.abs() + 1e-6)).max()) if a.numel() else 0.0
+
+
+@pytest.mark.parametrize("affine", [True, False])
+@pytest.mark.parametrize("dt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                    (torch.bfloat16, torch.float32), (torch.float16, torch.float16)])
+@pytest.mark.parametrize("shape,G", GN_SHAPES)
+def test_group_norm_forward(shape, G, dt, wdt, affine):
+    N, C = shape[0], shape[1]
+    HxW = 1
+    for d in shape[2:]:
+        HxW *= d
+    x = ao.randn(shape, 1100 + C, dt, 0.5, 2.0)
+    g = ao.randn((C,), 1101, wdt, 1.0, 0.2) if affine else None
+    b = ao.randn((C,), 1102, wdt, 0.0, 0.2) if affine else None
+    dev = lambda t: None if t is None else t.to(DEV)
+    y, mean, rstd = capi.native_group_norm(dev(x), dev(g), dev(b), N, C, HxW, G, 1e-5)
+    f32 = lambda t: None if t is None else t.float()
+    ry, rmean, rrstd = torch.ops.aten.native_group_norm(x.float(), f32(g), f32(b), N, C, HxW, G, 1e-5)
+    assert y.shape == x.shape and mean.shape == (N, G) and rstd.shape == (N, G)
+    want_stat = torch.float32 if (affine and wdt == torch.float32) else dt
+    assert mean.dtype == want_stat and rstd.dtype == want_stat
+    if dt == torch.float32:
+        assert ao.fp32_err(y, ry) <= 1.0
+        assert _stat_err(mean, rmean) <= 1.0 and _stat_err(rstd, rrstd) <= 1.0
+    else:
+        assert ao.lowp_mismatch(y, ry.to(dt))[0] == 0
+        if want_stat == torch.float32:
+            assert _stat_err(mean, rmean) <= 1.0 and _stat_err(rstd, rrstd) <= 1.0
+        else:
+            assert ao.ulp_distance(mean.cpu(), rmean.to(dt)) <= 1 and ao.ulp_distance(rstd.cpu(), rrstd.to(dt)) <= 1
+    assert capi.device_status() == 0
+
+
+def test_group_norm_large_offset_and_argument_checks():
+    x = (torch.randn(2, 8, 64) + 3.0e4).to(DEV)  # mean far from the first element's neighbourhood in relative terms
+    y, mean, rstd = capi.native_group_norm(x, None, None, 2, 8, 64, 2, 1e-5)
+    ry, rmean, rrstd = torch.ops.aten.native_group_norm(x.cpu().double(), None, None, 2, 8, 64, 2, 1e-5)
+    assert torch.allclose(y.cpu().double(), ry, atol=2e-2)  # fp32 input at 3e4: one ulp of x is 2e-3 before the 1/std scaling
+    assert _stat_err(mean, rmean) <= 1.0
+    with pytest.raises(RuntimeError):
+        capi.native_group_norm(x, None, None, 2, 8, 64, 3, 1e-5)
+    with pytest.raises(RuntimeError):
+        capi.native_group_norm(x, torch.ones(7, device=DEV), None, 2, 8, 64, 2, 1e-5)
+
+
+def test_group_norm_through_the_dispatcher_with_autograd():
+    b200norm.enable_aten_overrides()
+    x = ao.randn((4, 32, 16, 16), 1110)
+    m = torch.nn.GroupNorm(8, 32)
+    with torch.no_grad():
+        m.weight.copy_(ao.randn((32,), 1111, mean=1.0, std=0.2))
+        m.bias.copy_(ao.randn((32,), 1112, std=0.2))
+    xr = x.clone().requires_grad_(True)
+    yr = m(xr)
+    yr.backward(torch.ones_like(yr) * 0.5)
+    md = torch.nn.GroupNorm(8, 32).to(DEV)
+    md.load_state_dict(m.state_dict())
+    xd = x.to(DEV).requires_grad_(True)
+    capi.native_group_norm(xd.detach(), md.weight.detach(), md.bias.detach(), 4, 32, 256, 8, 1e-5)
+    launches = capi.launch_count()
+    yd = md(xd)
+    assert capi.launch_count() == launches + 1  # the dispatcher reached this library's forward kernel
+    yd.backward(torch.ones_like(yd) * 0.5)    # ... and autograd carries on through the stock backward
+    assert ao.fp32_err(yd, yr) <= 1.0
+    assert torch.allclose(xd.grad.cpu(), xr.grad, rtol=1e-4, atol=1e-5)
+    # channels-last input: made contiguous by the composite, same result
+    yc = md(x.to(DEV).contiguous(memory_format=torch.channels_last))
+    assert ao.fp32_err(yc.contiguous(), yr) <= 1.0
+
+
+BN_SHAPES = [(8, 16), (64, 33), (4, 8, 5), (16, 32, 16, 16), (3, 7, 33, 9), (2, 64, 4, 8, 8), (128, 256), (2, 3, 100000)]
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", BN_SHAPES)
+def test_batch_norm_stats(shape, dt):
+    x = ao.randn(shape, 1200 + shape[1], dt, 1.5, 3.0)
+    mean, invstd = capi.batch_norm_stats(x.to(DEV), 1e-5)
+    dims = [0] + list(range(2, len(shape)))
+    x64 = x.double()
+    rmean = x64.mean(dims)
+    rvar = x64.var(dims, unbiased=False)
+    assert mean.dtype == torch.float32 and mean.shape == (shape[1],)
+    assert _stat_err(mean, rmean) <= 1.0 and _stat_err(invstd, 1.0 / torch.sqrt(rvar + 1e-5)) <= 1.0
+
+    # update_stats: the biased variance out, the running statistics blended with the unbiased one
+    for rdt in (torch.float32, dt):
+        rm0, rv0 = ao.randn((shape[1],), 1201, rdt), ao.randn((shape[1],), 1202, rdt).abs() + 0.5
+        rm, rv = rm0.to(DEV), rv0.to(DEV)
+        m2, v2 = capi.batch_norm_update_stats(x.to(DEV), rm, rv, 0.1)
+        n = x.numel() // shape[1]
+        assert _stat_err(m2, rmean) <= 1.0 and _stat_err(v2, rvar) <= 1.0
+        want_rm = 0.9 * rm0.double() + 0.1 * rmean
+        want_rv = 0.9 * rv0.double() + 0.1 * rvar * n / max(n - 1, 1)
+        tol = 1e-5 if rdt == torch.float32 else 1e-2
+        assert torch.allclose(rm.cpu().double(), want_rm, rtol=tol, atol=tol)
+        assert torch.allclose(rv.cpu().double(), want_rv, rtol=tol, atol=tol)
+    m3, v3 = capi.batch_norm_update_stats(x.to(DEV), None, None, 0.1)
+    assert _stat_err(m3, rmean) <= 1.0 and _stat_err(v3, rvar) <= 1.0
+    assert capi.device_status() == 0
+
+
+def test_batch_norm_ops_through_the_dispatcher():
+    b200norm.enable_aten_overrides()
+    x = ao.randn((8, 24, 10, 10), 1210).to(DEV)
+    launches = capi.launch_count()
+    mean, invstd = torch.batch_norm_stats(x, 1e-5)
+    rm, rv = torch.zeros(24, device=DEV), torch.ones(24, device=DEV)
+    m2, v2 = torch.batch_norm_update_stats(x, rm, rv, 0.1)
+    assert capi.launch_count() == launches + 2
+    xr = x.cpu().double()
+    assert _stat_err(mean, xr.mean((0, 2, 3))) <= 1.0
+    assert _stat_err(invstd, 1 / torch.sqrt(xr.var((0, 2, 3), unbiased=False) + 1e-5)) <= 1.0
+    crm, crv = torch.zeros(24), torch.ones(24)
+    cm, cv = torch.batch_norm_update_stats(x.cpu(), crm, crv, 0.1)
+    assert _stat_err(m2, cm) <= 1.0 and _stat_err(v2, cv) <= 1.0
+    assert torch.allclose(rm.cpu(), crm, rtol=1e-5, atol=1e-6) and torch.allclose(rv.cpu(), crv, rtol=1e-5, atol=1e-6)

@@ -392,6 +392,78 @@ def _fused_rms_norm_backward(grad_out, input, normalized_shape, rstd, weight=Non
     return dx, dgamma
 
 
+# ---- sibling norms: group norm forward, batch norm statistics -------------------------------------------
+def native_group_norm(input, weight, bias, N, C, HxW, group, eps):
+    """aten::native_group_norm -> (Y, mean[N, group], rstd[N, group]); the statistics take the weights' dtype when the
+    input is 16-bit and the weights are float32 (upstream's mixed-type rule), else the input's."""
+    _require_cuda(input, weight, bias)
+    lib = load_library()
+    if input.numel() != N * C * HxW:
+        raise RuntimeError(f"Expected input of {N}*{C}*{HxW} elements, got {list(input.shape)}")
+    if group < 1 or C % group != 0:
+        raise RuntimeError(f"Expected number of channels in input to be divisible by num_groups, but got input of "
+                           f"shape {list(input.shape)} and num_groups={group}")
+    for name, w in (("weight", weight), ("bias", bias)):
+        if w is not None and (w.dim() != 1 or w.numel() != C):
+            raise RuntimeError(f"Expected {name} to be a vector of size equal to the number of channels in input, but got "
+                               f"{name} of shape {list(w.shape)} and input of shape {list(input.shape)}")
+    x = input.contiguous()
+    g = weight.contiguous() if weight is not None else None
+    b = bias.contiguous() if bias is not None else None
+    wdt = _weight_dtype(x, g, b)
+    stat = torch.float32 if (wdt == F32 and (g is not None or b is not None)) else x.dtype
+    y = torch.empty_like(x)
+    mean = torch.empty((N, group), dtype=stat, device=x.device)
+    rstd = torch.empty((N, group), dtype=stat, device=x.device)
+    if x.numel() > 0:
+        with torch.cuda.device(x.device):
+            _check(lib.b2n_group_norm_fwd(_ptr(x), _ptr(g), _ptr(b), _ptr(y), _ptr(mean), _ptr(rstd), N, C, HxW, group,
+                                          float(eps), _dt(x.dtype), wdt, _dt(stat), _stream(x)), "b2n_group_norm_fwd")
+    return y, mean, rstd
+
+
+def _bn_dims(input):
+    if input.dim() < 2:
+        raise RuntimeError("batch norm statistics need an input with at least two dimensions [N, C, ...]")
+    return input.shape[0], input.shape[1], math.prod(input.shape[2:])
+
+
+def batch_norm_stats(input, eps):
+    """aten::batch_norm_stats -> (mean[C], invstd[C]) in float32, over every dimension but the channel."""
+    _require_cuda(input)
+    lib = load_library()
+    N, C, HxW = _bn_dims(input)
+    x = input.contiguous()
+    mean = torch.empty(C, dtype=torch.float32, device=x.device)
+    invstd = torch.empty(C, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.b2n_batch_norm_stats(_ptr(x), _ptr(mean), _ptr(invstd), None, None, N, C, HxW, float(eps), 0.0, 0,
+                                        _dt(x.dtype), F32, _stream(x)), "b2n_batch_norm_stats")
+    return mean, invstd
+
+
+def batch_norm_update_stats(input, running_mean, running_var, momentum):
+    """aten::batch_norm_update_stats -> (mean[C], biased var[C]) in float32; running_mean / running_var (either may be
+    None) are blended in place, the variance unbiased."""
+    _require_cuda(input, running_mean, running_var)
+    lib = load_library()
+    N, C, HxW = _bn_dims(input)
+    x = input.contiguous()
+    r = running_mean if running_mean is not None else running_var
+    if running_mean is not None and running_var is not None and running_mean.dtype != running_var.dtype:
+        raise RuntimeError("running_mean and running_var must have the same dtype")
+    for t in (running_mean, running_var):
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError("running statistics must be contiguous (they are updated in place)")
+    mean = torch.empty(C, dtype=torch.float32, device=x.device)
+    var = torch.empty(C, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(lib.b2n_batch_norm_stats(_ptr(x), _ptr(mean), _ptr(var), _ptr(running_mean), _ptr(running_var), N, C, HxW,
+                                        0.0, float(momentum), 1, _dt(x.dtype), _dt(r.dtype) if r is not None else F32,
+                                        _stream(x)), "b2n_batch_norm_stats")
+    return mean, var
+
+
 # ---- softmax family ----------------------------------------------------------------------------------
 def _softmax_dims(t: torch.Tensor, dim: int):
     if t.dim() == 0:

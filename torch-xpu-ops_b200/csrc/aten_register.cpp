@@ -230,6 +230,107 @@ std::tuple<Tensor, Tensor> fused_rms_norm_backward(const Tensor& grad_out, const
   return std::make_tuple(std::move(dX), std::move(dgamma));
 }
 
+// ---- native_group_norm, batch_norm_stats, batch_norm_update_stats ----------------------------------
+// Host wrapper of upstream's native_group_norm (aten/src/ATen/native/group_norm.cpp) around the kernel the
+// reference registers for its GroupNormKernel stub (src/ATen/native/xpu/GroupNorm.cpp:20): same checks, the
+// statistics in the weights' dtype when the input is 16-bit and the weights are float (mixed type), else the input's.
+std::tuple<Tensor, Tensor, Tensor> native_group_norm(const Tensor& input, const std::optional<Tensor>& weight_opt,
+                                                     const std::optional<Tensor>& bias_opt, int64_t N, int64_t C,
+                                                     int64_t HxW, int64_t group, double eps) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  c10::MaybeOwned<Tensor> bias_mo = at::borrow_from_optional_tensor(bias_opt);
+  const Tensor& weight = *weight_mo;
+  const Tensor& bias = *bias_mo;
+  const char* op = "native_group_norm";
+  TORCH_CHECK(input.is_cuda(), op, ": expected a CUDA tensor");
+  TORCH_CHECK(group > 0, "Expected num groups to be greater than 0, got ", group);
+  TORCH_CHECK(C % group == 0, "Expected number of channels in input to be divisible by num_groups, but got input of shape ",
+              input.sizes(), " and num_groups=", group);
+  TORCH_CHECK(!weight.defined() || (weight.dim() == 1 && weight.numel() == C),
+              "Expected weight to be a vector of size equal to the number of channels in input, but got weight of shape ",
+              weight.sizes(), " and input of shape ", input.sizes());
+  TORCH_CHECK(!bias.defined() || (bias.dim() == 1 && bias.numel() == C),
+              "Expected bias to be a vector of size equal to the number of channels in input, but got bias of shape ",
+              bias.sizes(), " and input of shape ", input.sizes());
+  TORCH_CHECK(input.numel() == N * C * HxW, op, ": input has ", input.numel(), " elements, expected N*C*HxW = ", N * C * HxW);
+  const c10::cuda::CUDAGuard guard(input.device());
+  Tensor X = input.contiguous();
+  auto gamma = weight.expect_contiguous();
+  auto beta = bias.expect_contiguous();
+  const int xdt = to_b2n_dtype(X.scalar_type(), op);
+  const int wdt = weight_dtype(X, weight, bias, op);
+  const bool mixed = wdt == B2N_F32 && xdt != B2N_F32 && (weight.defined() || bias.defined());
+  const auto stat_type = mixed ? at::kFloat : X.scalar_type();
+  Tensor Y = at::empty_like(X, at::MemoryFormat::Contiguous);
+  Tensor mean = at::empty({N, group}, X.options().dtype(stat_type));
+  Tensor rstd = at::empty({N, group}, X.options().dtype(stat_type));
+  if (X.numel() > 0) {
+    check_status(b2n_group_norm_fwd(X.const_data_ptr(), gamma->defined() ? gamma->const_data_ptr() : nullptr,
+                                    beta->defined() ? beta->const_data_ptr() : nullptr, Y.mutable_data_ptr(),
+                                    mean.mutable_data_ptr(), rstd.mutable_data_ptr(), N, C, HxW, group, eps, xdt, wdt,
+                                    to_b2n_dtype(stat_type, op), cur_stream()),
+                 "group_norm_fwd");
+  }
+  return std::make_tuple(std::move(Y), std::move(mean), std::move(rstd));
+}
+
+static void bn_dims(const Tensor& input, const char* op, int64_t& N, int64_t& C, int64_t& HxW) {
+  TORCH_CHECK(input.dim() >= 2, op, ": expected an input with at least two dimensions [N, C, ...]");
+  N = input.size(0);
+  C = input.size(1);
+  HxW = 1;
+  for (int64_t i = 2; i < input.dim(); ++i) HxW *= input.size(i);
+  TORCH_CHECK(C == 0 || (N > 0 && HxW > 0), op, ": expected a non-empty input, got ", input.sizes());
+}
+
+// batch_norm_stats_xpu (src/ATen/native/xpu/BatchNorm.cpp:20): per-channel mean and 1/sqrt(var + eps), float.
+std::tuple<Tensor, Tensor> batch_norm_stats(const Tensor& input, double eps) {
+  const char* op = "batch_norm_stats";
+  TORCH_CHECK(input.is_cuda(), op, ": expected a CUDA tensor");
+  const c10::cuda::CUDAGuard guard(input.device());
+  int64_t N, C, HxW;
+  bn_dims(input, op, N, C, HxW);
+  Tensor X = input.contiguous();
+  Tensor mean = at::empty({C}, X.options().dtype(at::kFloat));
+  Tensor invstd = at::empty({C}, X.options().dtype(at::kFloat));
+  if (C > 0)
+    check_status(b2n_batch_norm_stats(X.const_data_ptr(), mean.mutable_data_ptr<float>(), invstd.mutable_data_ptr<float>(),
+                                      nullptr, nullptr, N, C, HxW, eps, 0.0, 0, to_b2n_dtype(X.scalar_type(), op), B2N_F32,
+                                      cur_stream()),
+                 op);
+  return std::make_tuple(std::move(mean), std::move(invstd));
+}
+
+// batch_norm_update_stats_xpu (BatchNorm.cpp:76): per-channel mean and biased variance, float; the running
+// statistics blended in place with `momentum`.
+std::tuple<Tensor, Tensor> batch_norm_update_stats(const Tensor& input, const std::optional<Tensor>& running_mean_opt,
+                                                   const std::optional<Tensor>& running_var_opt, double momentum) {
+  const char* op = "batch_norm_update_stats";
+  c10::MaybeOwned<Tensor> rm_mo = at::borrow_from_optional_tensor(running_mean_opt);
+  c10::MaybeOwned<Tensor> rv_mo = at::borrow_from_optional_tensor(running_var_opt);
+  const Tensor& rm = *rm_mo;
+  const Tensor& rv = *rv_mo;
+  TORCH_CHECK(input.is_cuda(), op, ": expected a CUDA tensor");
+  const c10::cuda::CUDAGuard guard(input.device());
+  int64_t N, C, HxW;
+  bn_dims(input, op, N, C, HxW);
+  Tensor X = input.contiguous();
+  TORCH_CHECK(!rm.defined() || (rm.is_contiguous() && rm.numel() == C), op, ": running_mean must be a contiguous [C] tensor");
+  TORCH_CHECK(!rv.defined() || (rv.is_contiguous() && rv.numel() == C), op, ": running_var must be a contiguous [C] tensor");
+  TORCH_CHECK(!rm.defined() || !rv.defined() || rm.scalar_type() == rv.scalar_type(), op,
+              ": running_mean and running_var must have the same dtype");
+  const Tensor& r = rm.defined() ? rm : rv;
+  Tensor mean = at::empty({C}, X.options().dtype(at::kFloat));
+  Tensor var = at::empty({C}, X.options().dtype(at::kFloat));
+  if (C > 0)
+    check_status(b2n_batch_norm_stats(X.const_data_ptr(), mean.mutable_data_ptr<float>(), var.mutable_data_ptr<float>(),
+                                      rm.defined() ? rm.mutable_data_ptr() : nullptr, rv.defined() ? rv.mutable_data_ptr() : nullptr,
+                                      N, C, HxW, 0.0, momentum, 1, to_b2n_dtype(X.scalar_type(), op),
+                                      r.defined() ? to_b2n_dtype(r.scalar_type(), op) : B2N_F32, cur_stream()),
+                 op);
+  return std::make_tuple(std::move(mean), std::move(var));
+}
+
 // ---- softmax family ------------------------------------------------------------------------------
 struct SoftmaxDims { int64_t outer, n, inner; };
 static SoftmaxDims softmax_dims(const Tensor& t, int64_t dim) {
@@ -563,6 +664,9 @@ TORCH_LIBRARY_IMPL(aten, CUDA, m) {
   m.impl("native_layer_norm_backward", TORCH_FN(native_layer_norm_backward));
   m.impl("_fused_rms_norm", TORCH_FN(fused_rms_norm));
   m.impl("_fused_rms_norm_backward", TORCH_FN(fused_rms_norm_backward));
+  m.impl("native_group_norm", TORCH_FN(native_group_norm));
+  m.impl("batch_norm_stats", TORCH_FN(batch_norm_stats));
+  m.impl("batch_norm_update_stats", TORCH_FN(batch_norm_update_stats));
   m.impl("_softmax", TORCH_FN(softmax));
   m.impl("_safe_softmax", TORCH_FN(safe_softmax));
   m.impl("_masked_softmax", TORCH_FN(masked_softmax));

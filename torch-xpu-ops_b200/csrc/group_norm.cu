@@ -1,0 +1,323 @@
+// Sibling norms that share the row-statistics machinery: GroupNorm forward and the BatchNorm
+// statistics.
+//
+// GroupNorm over a contiguous [N, C, HxW] tensor is a row-wise normalisation of [N * G, D * HxW]
+// (D = C / G channels per group) followed by a per-CHANNEL affine map, so a row is handled like a
+// layer-norm row — shifted one-pass moments in fp32, the exact second pass when the shift lies far
+// from the mean — and only the weights differ: element j of row (n, g) takes gamma[g * D + j / HxW].
+// One CTA per row at a time, 16-byte accesses when the row is a whole number of aligned vectors; the
+// row is read a second time for the output, from L1/L2 (a group's row is a few KB to a few MB).
+//
+// BatchNorm statistics reduce the other way: per channel c over all n and all spatial positions.  One
+// CTA per channel walks the N runs of HxW contiguous elements (warps over n, lanes along the run);
+// for HxW < 16 (an [N, C] input) 32 adjacent channels share a CTA so that the lanes still read
+// adjacent addresses.  Shifted one-pass sums again, merged exactly.
+//
+// Replaces group_norm_kernel (src/ATen/native/xpu/sycl/GroupNormKernels.h:17-28; moments functors
+// GroupNormKernels.cpp:73-136, driver :365-499), batch_norm_stats_kernel and
+// batch_norm_update_stats_kernel (sycl/BatchNormKernels.h:19, :52; BatchNormKernels.cpp:992, :3864).
+#include "common.cuh"
+#include "launchers.h"
+
+namespace b2n {
+namespace {
+
+// sums of (a, b) over the CTA; every thread gets the totals (fixed order).  scratch: 64 floats.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch) {
+  a = warp_reduce(a, SumOp());
+  b = warp_reduce(b, SumOp());
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) { scratch[w] = a; scratch[32 + w] = b; }
+  __syncthreads();
+  float ra = scratch[0], rb = scratch[32];
+  for (int i = 1; i < nw; ++i) { ra += scratch[i]; rb += scratch[32 + i]; }
+  a = ra;
+  b = rb;
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void row_shifted_sums(const T* __restrict__ row, int64_t L, float shift, float& s, float& q) {
+  s = 0.0f;
+  q = 0.0f;
+  if constexpr (V > 1) {
+    const int64_t nv = L / V;
+    for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+      const Vec<T, V> xv = ld_vec<T, V>(row + v * V);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float d = to_acc<float>(xv.v[e]) - shift;
+        s += d;
+        q = fmaf(d, d, q);
+      }
+    }
+  } else {
+    for (int64_t j = threadIdx.x; j < L; j += blockDim.x) {
+      const float d = to_acc<float>(row[j]) - shift;
+      s += d;
+      q = fmaf(d, d, q);
+    }
+  }
+}
+
+// One CTA per row of [rows = N * G, L = D * HxW].  ST: type of the mean / rstd outputs.
+template <typename T, typename WT, typename ST, int V>
+__global__ void __launch_bounds__(512)
+group_norm_fwd_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta, T* __restrict__ y,
+                      ST* __restrict__ mean, ST* __restrict__ rstd, int64_t rows, int G, int D, int HxW, float eps) {
+  __shared__ float scratch[64];
+  const int64_t L = static_cast<int64_t>(D) * HxW;
+  const float inv_l = 1.0f / static_cast<float>(L);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * L;
+    T* yr = y + row * L;
+    float shift = to_acc<float>(xr[0]);  // the same address for every thread: one broadcast load
+    float s, q;
+    row_shifted_sums<T, V>(xr, L, shift, s, q);
+    block_sum2(s, q, scratch);
+    float mu_d = s * inv_l;
+    float var = fmaf(q, inv_l, -mu_d * mu_d);
+    if (!(mu_d * mu_d <= 8.0f * var)) {  // cancellation (or NaN): once more about the mean just found
+      shift += mu_d;
+      row_shifted_sums<T, V>(xr, L, shift, s, q);
+      block_sum2(s, q, scratch);
+      mu_d = s * inv_l;
+      const float v2 = fmaf(-mu_d, s, q) * inv_l;
+      var = v2 < 0.0f ? 0.0f : v2;  // keeps NaN
+    }
+    const float mu = shift + mu_d;
+    const float rs = 1.0f / sqrtf(var + eps);
+    const int c0 = static_cast<int>(row % G) * D;  // first channel of this row's group
+    if constexpr (V > 1) {
+      const int64_t nv = L / V;
+      const bool one_channel = HxW % V == 0;  // then a vector never straddles two channels
+      for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+        const Vec<T, V> xv = ld_vec<T, V>(xr + v * V);
+        Vec<T, V> o;
+        const int j0 = static_cast<int>(v) * V;
+        int c = c0 + j0 / HxW;
+        float gm = gamma ? to_acc<float>(gamma[c]) : 1.0f, bt = beta ? to_acc<float>(beta[c]) : 0.0f;
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          if (!one_channel && e > 0) {
+            const int ce = c0 + (j0 + e) / HxW;
+            if (ce != c) {
+              c = ce;
+              gm = gamma ? to_acc<float>(gamma[c]) : 1.0f;
+              bt = beta ? to_acc<float>(beta[c]) : 0.0f;
+            }
+          }
+          o.v[e] = from_acc<T>(fmaf((to_acc<float>(xv.v[e]) - mu) * rs, gm, bt));
+        }
+        st_vec<T, V>(yr + v * V, o);
+      }
+    } else {
+      for (int64_t j = threadIdx.x; j < L; j += blockDim.x) {
+        const int c = c0 + static_cast<int>(j / HxW);
+        const float gm = gamma ? to_acc<float>(gamma[c]) : 1.0f, bt = beta ? to_acc<float>(beta[c]) : 0.0f;
+        yr[j] = from_acc<T>(fmaf((to_acc<float>(xr[j]) - mu) * rs, gm, bt));
+      }
+    }
+    if (threadIdx.x == 0) {
+      mean[row] = from_acc<ST>(mu);
+      rstd[row] = from_acc<ST>(rs);
+    }
+    __syncthreads();  // scratch is reused by the next row
+  }
+}
+
+// ---- batch norm statistics ------------------------------------------------------------------------------
+// x: [N, C, HxW].  Channel c's elements: N runs of HxW at (n * C + c) * HxW.  Results in fp32:
+// mean[c]; second[c] = 1 / sqrt(var + eps) (MODE 0, batch_norm_stats) or the biased variance (MODE 1,
+// batch_norm_update_stats, which also folds the batch statistics into running_mean / running_var with `momentum`,
+// the variance unbiased by n / (n - 1)).  RT: type of the running statistics.
+template <typename RT>
+__device__ __forceinline__ void bn_finish(int mode, float mu, float var, float count, float eps, float momentum, int c,
+                                          float* mean, float* second, RT* running_mean, RT* running_var) {
+  mean[c] = mu;
+  if (mode == 0) {
+    second[c] = 1.0f / sqrtf(var + eps);
+  } else {
+    second[c] = var;
+    if (running_mean != nullptr)
+      running_mean[c] = from_acc<RT>((1.0f - momentum) * to_acc<float>(running_mean[c]) + momentum * mu);
+    if (running_var != nullptr) {
+      const float unbiased = var * (count / (count - 1.0f));
+      running_var[c] = from_acc<RT>((1.0f - momentum) * to_acc<float>(running_var[c]) + momentum * unbiased);
+    }
+  }
+}
+
+// HxW >= 16: one CTA per channel, warps over n, lanes along the run.
+template <typename T, typename RT>
+__global__ void __launch_bounds__(512)
+batch_norm_stats_spatial_kernel(const T* __restrict__ x, float* __restrict__ mean, float* __restrict__ second,
+                                RT* __restrict__ running_mean, RT* __restrict__ running_var, int64_t N, int C, int64_t HxW,
+                                float eps, float momentum, int mode) {
+  __shared__ float scratch[64];
+  const int c = blockIdx.x;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const float count = static_cast<float>(N) * static_cast<float>(HxW);
+  float shift = to_acc<float>(x[static_cast<int64_t>(c) * HxW]);
+  float mu_d = 0.0f, var = 0.0f;
+  for (int pass = 0; pass < 2; ++pass) {
+    float s = 0.0f, q = 0.0f;
+    for (int64_t n = w; n < N; n += nw) {
+      const T* run = x + (n * C + c) * HxW;
+      for (int64_t j = l; j < HxW; j += 32) {
+        const float d = to_acc<float>(run[j]) - shift;
+        s += d;
+        q = fmaf(d, d, q);
+      }
+    }
+    block_sum2(s, q, scratch);
+    mu_d = s / count;
+    if (pass == 0) {
+      var = q / count - mu_d * mu_d;
+      if (mu_d * mu_d <= 8.0f * var) break;  // well conditioned: done in one pass
+      shift += mu_d;
+    } else {
+      const float v2 = (q - mu_d * s) / count;
+      var = v2 < 0.0f ? 0.0f : v2;
+    }
+  }
+  if (threadIdx.x == 0) bn_finish<RT>(mode, shift + mu_d, var, count, eps, momentum, c, mean, second, running_mean, running_var);
+}
+
+// HxW < 16: 32 adjacent channels per CTA (lanes along c when HxW == 1), row lanes over (n, position).
+template <typename T, typename RT>
+__global__ void __launch_bounds__(1024)
+batch_norm_stats_flat_kernel(const T* __restrict__ x, float* __restrict__ mean, float* __restrict__ second,
+                             RT* __restrict__ running_mean, RT* __restrict__ running_var, int64_t N, int C, int64_t HxW,
+                             float eps, float momentum, int mode) {
+  __shared__ float ss[32][33], sq[32][33];
+  const int tx = threadIdx.x, ty = threadIdx.y;  // 32 x 32
+  const int c = blockIdx.x * 32 + tx;
+  const int64_t per_c = N * HxW;
+  const float count = static_cast<float>(per_c);
+  float shift = c < C ? to_acc<float>(x[static_cast<int64_t>(c) * HxW]) : 0.0f;
+  float mu_d = 0.0f, var = 0.0f;
+  for (int pass = 0; pass < 2; ++pass) {
+    float s = 0.0f, q = 0.0f;
+    if (c < C) {
+      for (int64_t i = ty; i < per_c; i += 32) {
+        const int64_t n = i / HxW, j = i - n * HxW;
+        const float d = to_acc<float>(x[(n * C + c) * HxW + j]) - shift;
+        s += d;
+        q = fmaf(d, d, q);
+      }
+    }
+    __syncthreads();
+    ss[ty][tx] = s;
+    sq[ty][tx] = q;
+    __syncthreads();
+    s = 0.0f;
+    q = 0.0f;
+    for (int k = 0; k < 32; ++k) { s += ss[k][tx]; q += sq[k][tx]; }
+    mu_d = s / count;
+    bool redo = false;
+    if (pass == 0) {
+      var = q / count - mu_d * mu_d;
+      redo = !(mu_d * mu_d <= 8.0f * var);
+    } else {
+      const float v2 = (q - mu_d * s) / count;
+      var = v2 < 0.0f ? 0.0f : v2;
+    }
+    // the second pass is taken by the whole CTA if any of its channels needs it (the barriers above are CTA-wide)
+    if (pass == 1 || !__syncthreads_or(redo ? 1 : 0)) break;
+    if (redo) shift += mu_d;
+    else { /* channels that were fine repeat the pass about the same shift: same result */ }
+  }
+  if (ty == 0 && c < C) bn_finish<RT>(mode, shift + mu_d, var, count, eps, momentum, c, mean, second, running_mean, running_var);
+}
+
+template <typename T, typename WT, typename ST>
+int group_norm_launch(const void* x, const void* gamma, const void* beta, void* y, void* mean, void* rstd, int64_t N, int64_t C,
+                      int64_t HxW, int64_t G, double eps, cudaStream_t st) {
+  const int64_t rows = N * G, D = C / G, L = D * HxW;
+  constexpr int V = 16 / sizeof(T);
+  const bool vec = L % V == 0 && is_aligned(x, 16) && is_aligned(y, 16);
+  const int threads = L >= 8192 ? 512 : (L >= 2048 ? 256 : 128);
+  const int64_t cap = static_cast<int64_t>(device_info().sm_count) * (2048 / threads);
+  const int grid = static_cast<int>(rows < cap ? rows : cap);
+  ProfileScope prof("group_norm_fwd", st);
+  const T* xp = static_cast<const T*>(x);
+  const WT* g = static_cast<const WT*>(gamma);
+  const WT* b = static_cast<const WT*>(beta);
+  if (vec)
+    group_norm_fwd_kernel<T, WT, ST, V><<<grid, threads, 0, st>>>(xp, g, b, static_cast<T*>(y), static_cast<ST*>(mean),
+                                                                 static_cast<ST*>(rstd), rows, static_cast<int>(G),
+                                                                 static_cast<int>(D), static_cast<int>(HxW), static_cast<float>(eps));
+  else
+    group_norm_fwd_kernel<T, WT, ST, 1><<<grid, threads, 0, st>>>(xp, g, b, static_cast<T*>(y), static_cast<ST*>(mean),
+                                                                 static_cast<ST*>(rstd), rows, static_cast<int>(G),
+                                                                 static_cast<int>(D), static_cast<int>(HxW), static_cast<float>(eps));
+  return launched();
+}
+
+template <typename T, typename RT>
+int batch_norm_stats_launch(const void* x, float* mean, float* second, void* running_mean, void* running_var, int64_t N,
+                            int64_t C, int64_t HxW, double eps, double momentum, int mode, cudaStream_t st) {
+  ProfileScope prof("batch_norm_stats", st);
+  const T* xp = static_cast<const T*>(x);
+  RT* rm = static_cast<RT*>(running_mean);
+  RT* rv = static_cast<RT*>(running_var);
+  if (HxW >= 16) {
+    const int threads = N * HxW >= 16384 ? 512 : 128;
+    batch_norm_stats_spatial_kernel<T, RT><<<static_cast<unsigned>(C), threads, 0, st>>>(
+        xp, mean, second, rm, rv, N, static_cast<int>(C), HxW, static_cast<float>(eps), static_cast<float>(momentum), mode);
+  } else {
+    batch_norm_stats_flat_kernel<T, RT><<<static_cast<unsigned>((C + 31) / 32), dim3(32, 32), 0, st>>>(
+        xp, mean, second, rm, rv, N, static_cast<int>(C), HxW, static_cast<float>(eps), static_cast<float>(momentum), mode);
+  }
+  return launched();
+}
+
+}  // namespace
+}  // namespace b2n
+
+using namespace b2n;
+
+extern "C" {
+
+int b2n_group_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, void* mean, void* rstd, int64_t N,
+                       int64_t C, int64_t HxW, int64_t G, double eps, int x_dtype, int w_dtype, int stat_dtype, void* stream) {
+  if (N < 0 || C < 0 || HxW < 0 || G < 1 || C % G != 0) return B2N_ERR_BAD_ARG;
+  if (N == 0 || C == 0 || HxW == 0) return B2N_OK;
+  if (!x || !y || !mean || !rstd) return B2N_ERR_BAD_ARG;
+  if ((C / G) * HxW > 0x7fffffffLL || C > 0x7fffffffLL) return B2N_ERR_TOO_LARGE;
+  if (!device_ready()) return B2N_ERR_CUDA;
+  if (gamma == nullptr && beta == nullptr) w_dtype = x_dtype;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define B2N_GN(T, WT, ST) return group_norm_launch<T, WT, ST>(x, gamma, beta, y, mean, rstd, N, C, HxW, G, eps, st)
+  if (x_dtype == B2N_F32 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GN(float, float, float);
+  if (x_dtype == B2N_BF16 && w_dtype == B2N_BF16 && stat_dtype == B2N_BF16) B2N_GN(bf16, bf16, bf16);
+  if (x_dtype == B2N_BF16 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GN(bf16, float, float);
+  if (x_dtype == B2N_F16 && w_dtype == B2N_F16 && stat_dtype == B2N_F16) B2N_GN(f16, f16, f16);
+  if (x_dtype == B2N_F16 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GN(f16, float, float);
+#undef B2N_GN
+  return B2N_ERR_UNSUPPORTED_DTYPE;
+}
+
+int b2n_batch_norm_stats(const void* x, float* mean, float* second, void* running_mean, void* running_var, int64_t N,
+                         int64_t C, int64_t HxW, double eps, double momentum, int mode, int x_dtype, int running_dtype,
+                         void* stream) {
+  if (N < 0 || C < 0 || HxW < 0 || mode < 0 || mode > 1) return B2N_ERR_BAD_ARG;
+  if (C == 0) return B2N_OK;
+  if (N == 0 || HxW == 0) return B2N_ERR_BAD_ARG;  // statistics of nothing
+  if (!x || !mean || !second) return B2N_ERR_BAD_ARG;
+  if (C > 0x7fffffffLL) return B2N_ERR_TOO_LARGE;
+  if (!device_ready()) return B2N_ERR_CUDA;
+  if (running_mean == nullptr && running_var == nullptr) running_dtype = B2N_F32;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define B2N_BN(T, RT) return batch_norm_stats_launch<T, RT>(x, mean, second, running_mean, running_var, N, C, HxW, eps, momentum, mode, st)
+  if (x_dtype == B2N_F32 && running_dtype == B2N_F32) B2N_BN(float, float);
+  if (x_dtype == B2N_BF16 && running_dtype == B2N_F32) B2N_BN(bf16, float);
+  if (x_dtype == B2N_BF16 && running_dtype == B2N_BF16) B2N_BN(bf16, bf16);
+  if (x_dtype == B2N_F16 && running_dtype == B2N_F32) B2N_BN(f16, float);
+  if (x_dtype == B2N_F16 && running_dtype == B2N_F16) B2N_BN(f16, f16);
+#undef B2N_BN
+  return B2N_ERR_UNSUPPORTED_DTYPE;
+}
+
+}  // extern "C"

@@ -50,6 +50,7 @@ struct SlabPlan {
   int c = 0;          // CTAs per cluster = slabs per row
   int slab_vecs = 0;  // 16-byte vectors per slab
   int tr = 0;         // rows per tile
+  int depth = 1;      // tiles between a tile's phase A and its phase B (1 or 2)
   int stages = 0;
   size_t smem = 0;
 };
@@ -67,6 +68,7 @@ inline SlabPlan plan_slab(int64_t M, int64_t N, int esize, int nin, int max_smem
     const int64_t sv = (nvec + c - 1) / c;
     if (sv > cap) continue;
     for (int tr = 2; tr >= 1; --tr) {
+      if (ring_tuning().rpg >= 1 && ring_tuning().rpg <= 2 && tr != ring_tuning().rpg) continue;
       const int64_t stage = static_cast<int64_t>(nin) * tr * sv * 16;
       int64_t s = (static_cast<int64_t>(max_smem) - kNsHeaderBytes) / stage;
       if (s > kNsMaxStages) s = kNsMaxStages;
@@ -78,6 +80,8 @@ inline SlabPlan plan_slab(int64_t M, int64_t N, int esize, int nin, int max_smem
       p.slab_vecs = static_cast<int>(sv);
       p.tr = tr;
       p.stages = static_cast<int>(s);
+      p.depth = s >= 5 ? 2 : 1;  // a tile occupies its stage for depth + 1 iterations: deeper only with stages to spare
+      if (ring_tuning().lag >= 1 && ring_tuning().lag <= 2 && ring_tuning().lag + 2 <= s) p.depth = ring_tuning().lag;
       p.smem = static_cast<size_t>(kNsHeaderBytes + s * stage);
       return p;
     }
@@ -129,33 +133,31 @@ template <typename T, typename WT, bool RMS>
 int norm_fwd_slab_launch(const SlabPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, float* mean, float* rstd,
                          int64_t M, int64_t N, double eps, cudaStream_t st) {
   ProfileScope prof(RMS ? "rms_norm_fwd_slab" : "layer_norm_fwd_slab", st);
-  static std::atomic<uint64_t> done[2];
+  static std::atomic<uint64_t> done[4];
   int* status = device_status_ptr();
-  if (p.tr == 2)
-    return slab_launch(norm_fwd_slab_kernel<T, WT, RMS, 2>, p, M, done[0], st, nullptr, x, gamma, beta, y, mean, rstd, M, N,
-                       static_cast<float>(eps), p.slab_vecs, p.stages, status);
-  return slab_launch(norm_fwd_slab_kernel<T, WT, RMS, 1>, p, M, done[1], st, nullptr, x, gamma, beta, y, mean, rstd, M, N,
-                     static_cast<float>(eps), p.slab_vecs, p.stages, status);
+  auto go = [&](auto kernel, std::atomic<uint64_t>& d) {
+    return slab_launch(kernel, p, M, d, st, nullptr, x, gamma, beta, y, mean, rstd, M, N, static_cast<float>(eps), p.slab_vecs,
+                       p.stages, status);
+  };
+  if (p.tr == 2) return p.depth == 2 ? go(norm_fwd_slab_kernel<T, WT, RMS, 2, 2>, done[0]) : go(norm_fwd_slab_kernel<T, WT, RMS, 2, 1>, done[1]);
+  return p.depth == 2 ? go(norm_fwd_slab_kernel<T, WT, RMS, 1, 2>, done[2]) : go(norm_fwd_slab_kernel<T, WT, RMS, 1, 1>, done[3]);
 }
 
 template <typename T, typename WT, bool RMS>
 int norm_bwd_slab_launch(const SlabPlan& p, bool wgrad, const T* dy, const T* x, const float* mean, const float* rstd,
                          const WT* gamma, T* dx, float* ws, int64_t M, int64_t N, cudaStream_t st, int64_t* clusters) {
   ProfileScope prof(RMS ? "rms_norm_bwd_slab" : "layer_norm_bwd_slab", st);
-  static std::atomic<uint64_t> done[4];
+  static std::atomic<uint64_t> done[8];
   int* status = device_status_ptr();
+  auto go = [&](auto kernel, std::atomic<uint64_t>& d) {
+    return slab_launch(kernel, p, M, d, st, clusters, dy, x, mean, rstd, gamma, dx, ws, M, N, p.slab_vecs, p.stages, status);
+  };
   if (wgrad) {
-    if (p.tr == 2)
-      return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, true, 2>, p, M, done[0], st, clusters, dy, x, mean, rstd, gamma, dx,
-                         ws, M, N, p.slab_vecs, p.stages, status);
-    return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, true, 1>, p, M, done[1], st, clusters, dy, x, mean, rstd, gamma, dx, ws,
-                       M, N, p.slab_vecs, p.stages, status);
+    if (p.tr == 2) return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, true, 2, 2>, done[0]) : go(norm_bwd_slab_kernel<T, WT, RMS, true, 2, 1>, done[1]);
+    return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, true, 1, 2>, done[2]) : go(norm_bwd_slab_kernel<T, WT, RMS, true, 1, 1>, done[3]);
   }
-  if (p.tr == 2)
-    return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, false, 2>, p, M, done[2], st, clusters, dy, x, mean, rstd, gamma, dx,
-                       ws, M, N, p.slab_vecs, p.stages, status);
-  return slab_launch(norm_bwd_slab_kernel<T, WT, RMS, false, 1>, p, M, done[3], st, clusters, dy, x, mean, rstd, gamma, dx, ws,
-                     M, N, p.slab_vecs, p.stages, status);
+  if (p.tr == 2) return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, false, 2, 2>, done[4]) : go(norm_bwd_slab_kernel<T, WT, RMS, false, 2, 1>, done[5]);
+  return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, false, 1, 2>, done[6]) : go(norm_bwd_slab_kernel<T, WT, RMS, false, 1, 1>, done[7]);
 }
 
 // ---- forward ------------------------------------------------------------------------------------

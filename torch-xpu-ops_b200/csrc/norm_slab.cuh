@@ -11,15 +11,18 @@
 // deep so that the exchange latency hides behind arithmetic:
 //
 //   iteration i:   phase A of tile i      read the tile's rows from the stage, reduce the slab's partial
-//                                         values over the CTA, one thread pushes them into every peer's
-//                                         header (st.shared::cluster) and arrives on the peer's
-//                                         exchange barrier (mbarrier.arrive.release.cluster);
-//                  phase B of tile i - 1  wait for the C partials of that tile, combine them in rank
+//                                         values over the CTA; one thread sends them to every CTA of the
+//                                         cluster with st.async — a one-way remote store that counts its
+//                                         bytes on the RECEIVER's exchange mbarrier (no fence, no separate
+//                                         arrival, nothing comes back);
+//                  phase B of tile i - D  wait for the C partials of that tile, combine them in rank
 //                                         order (every CTA gets the same bits), read the rows again,
 //                                         write the result in place, hand the stage to the producer.
 //
-// Exchange slots rotate modulo 4: a peer can write the partials of tile t + 4 only after it has seen
-// this CTA's partials of tile t + 2, which this CTA sends after it has finished reading those of tile t.
+// D (1 or 2) is the pipeline depth: how many tiles of arithmetic an exchange has to arrive.  Exchange
+// slots rotate modulo 8: a peer can send the partials of tile t + Q only after it has seen this CTA's
+// partials of tile t + Q - D - 1, which this CTA sends in iteration t + Q - D - 1; this CTA finishes
+// reading those of tile t in iteration t + D; so Q >= 2 D + 2 slots never collide (6 for D = 2).
 // Forward statistics are combined exactly (Chan et al.): slab c contributes its element count, its
 // mean and its centred sum of squares M2; each slab's own moments use the shifted one-pass sums of the
 // ring kernel, with the same exact second pass when the shift is far from the slab's mean.
@@ -39,21 +42,24 @@ constexpr int kNsConsumers = 512;
 constexpr int kNsThreads = kNsConsumers + 32;  // + one producer warp
 constexpr int kNsMaxCluster = 8;
 constexpr int kNsMaxStages = 8;
-constexpr int kNsSlots = 4;
+constexpr int kNsSlots = 8;
 constexpr int kNsHeaderBytes = 2048;
 constexpr int kNsEpt = 16;  // elements per thread, as in the ring kernels
 
 struct NormSlabShared {
   uint64_t full[kNsMaxStages];
   uint64_t done[kNsMaxStages];
-  uint64_t xbar[kNsSlots];                          // C arrivals per use: the partials of one tile are all here
-  float part[kNsSlots][kNsMaxCluster][2][2];        // [slot][source rank][row of the tile][value]
+  uint64_t xbar[kNsSlots];                          // one arrival (the owner's, with the byte count) + C x 16 bytes per use
+  alignas(16) float part[kNsSlots][kNsMaxCluster][2][2];  // [slot][source rank][row of the tile][value]: 16 bytes per source
   float red[kRingRedFloats];                        // CTA-level reduction scratch
 };
 static_assert(sizeof(NormSlabShared) <= kNsHeaderBytes, "slab header too large");
 
-__device__ __forceinline__ void st_remote_f32(uint32_t cluster_addr, float a) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(a) : "memory");
+// 16 bytes into a peer's shared memory, counted on the peer's mbarrier when they land
+__device__ __forceinline__ void st_async_f32x4(uint32_t cluster_addr, float a, float b, float c, float d, uint32_t cluster_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(cluster_addr),
+               "f"(a), "f"(b), "f"(c), "f"(d), "r"(cluster_mbar)
+               : "memory");
 }
 
 struct NormSlabGeom {
@@ -151,19 +157,14 @@ __device__ __forceinline__ void norm_slab_producer(NormSlabShared* sh, unsigned 
   bulk_wait_read<0>();
 }
 
-// One thread of the CTA: the tile's partial values to every CTA of the cluster (its own included), then one
-// arrival on each one's exchange barrier of that slot.  vals[r][k]: row r of the tile, value k.
+// One thread of the CTA: arm this CTA's exchange barrier of the slot for the C x 16 bytes it is about to receive,
+// then send the tile's partial values to every CTA of the cluster (its own included).  vals[r][k]: row r, value k.
 template <int TR>
 __device__ __forceinline__ void norm_slab_push(NormSlabShared* sh, const NormSlabGeom& g, int slot, const float (&vals)[TR][2]) {
-  for (int c = 0; c < g.C; ++c) {
-    const uint32_t base = map_to_rank(smem_u32(&sh->part[slot][g.crank][0][0]), c);
-#pragma unroll
-    for (int r = 0; r < TR; ++r) {
-      st_remote_f32(base + static_cast<uint32_t>(r * 2) * 4u, vals[r][0]);
-      st_remote_f32(base + static_cast<uint32_t>(r * 2 + 1) * 4u, vals[r][1]);
-    }
-    mbar_arrive_remote(map_to_rank(smem_u32(&sh->xbar[slot]), c));
-  }
+  mbar_arrive_expect_tx(&sh->xbar[slot], static_cast<uint32_t>(g.C) * 16u);
+  const float a = vals[0][0], b = vals[0][1], c2 = TR > 1 ? vals[TR - 1][0] : 0.0f, d = TR > 1 ? vals[TR - 1][1] : 0.0f;
+  const uint32_t dst = smem_u32(&sh->part[slot][g.crank][0][0]), bar = smem_u32(&sh->xbar[slot]);
+  for (int c = 0; c < g.C; ++c) st_async_f32x4(map_to_rank(dst, c), a, b, c2, d, map_to_rank(bar, c));
 }
 
 template <typename WT, int VPT, int VEC>
@@ -182,7 +183,7 @@ __device__ __forceinline__ void slab_load_weights(const WT* __restrict__ w, floa
 }
 
 // ---- forward -------------------------------------------------------------------------------------------
-template <typename T, typename WT, bool RMS, int TR>
+template <typename T, typename WT, bool RMS, int TR, int D>
 __global__ void __launch_bounds__(kNsThreads, 1)
 norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta, T* __restrict__ y,
                      float* __restrict__ mean, float* __restrict__ rstd, int64_t M, int64_t N, float eps, int slab_vecs,
@@ -202,7 +203,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->done[s], kNsConsumers / 32);
     }
-    for (int s = 0; s < kNsSlots; ++s) mbar_init(&sh->xbar[s], g.C);
+    for (int s = 0; s < kNsSlots; ++s) mbar_init(&sh->xbar[s], 1);
     mbar_init_fence();
   }
   __syncthreads();
@@ -225,7 +226,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
     if constexpr (!RMS) slab_load_weights<WT, VPT, VEC>(beta, 0.0f, g.v0, g.my_nv, tid, gb);
     int red_phase = 0;
     bool ok = true;
-    for (int64_t i = 0; i <= g.my_tiles && ok; ++i) {
+    for (int64_t i = 0; i < g.my_tiles + D && ok; ++i) {
       if (i < g.my_tiles) {
         // ---- phase A of tile i: this slab's moments of each row --------------------------------------
         const int s = static_cast<int>(i % g.S);
@@ -324,11 +325,11 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         }
         if (tid == 0) norm_slab_push<TR>(sh, g, static_cast<int>(i % kNsSlots), vals);
       }
-      if (i >= 1) {
-        // ---- phase B of tile i - 1: the row's statistics from the C slabs, then the output -------------
-        const int64_t t = i - 1;
+      if (i >= D) {
+        // ---- phase B of tile i - D: the row's statistics from the C slabs, then the output -------------
+        const int64_t t = i - D;
         const int slot = static_cast<int>(t % kNsSlots);
-        if (!mbar_wait_cluster(&sh->xbar[slot], static_cast<uint32_t>((t / kNsSlots) & 1), status)) { ok = false; break; }
+        if (!mbar_wait(&sh->xbar[slot], static_cast<uint32_t>((t / kNsSlots) & 1), status)) { ok = false; break; }
         const int s = static_cast<int>(t % g.S);
         const int64_t row0 = (g.cluster_id + t * g.nclusters) * TR;
         const uint32_t sbase = stages_u32 + static_cast<uint32_t>(s) * stage_bytes;
@@ -383,7 +384,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 
 // ---- backward ------------------------------------------------------------------------------------------
 // stage = [dy rows | x rows]; dx overwrites the dy rows.  ws: partial weight gradients, row `cluster index`.
-template <typename T, typename WT, bool RMS, bool WGRAD, int TR>
+template <typename T, typename WT, bool RMS, bool WGRAD, int TR, int D>
 __global__ void __launch_bounds__(kNsThreads, 1)
 norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx, float* __restrict__ ws,
@@ -403,7 +404,7 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->done[s], kNsConsumers / 32);
     }
-    for (int s = 0; s < kNsSlots; ++s) mbar_init(&sh->xbar[s], g.C);
+    for (int s = 0; s < kNsSlots; ++s) mbar_init(&sh->xbar[s], 1);
     mbar_init_fence();
   }
   __syncthreads();
@@ -426,8 +427,9 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     for (int e = 0; e < HP; ++e) { dg[e] = bcast2(0.0f); db[e] = bcast2(0.0f); }
     int red_phase = 0;
     bool ok = true;
-    // mean / rstd of a tile's rows are fetched one iteration before phase A needs them and kept for phase B
-    float mu_n[TR], rs_n[TR], mu_a[TR], rs_a[TR], mu_b[TR], rs_b[TR];
+    // mean / rstd of a tile's rows are fetched one iteration before phase A needs them and kept until phase B:
+    // hist[0] the tile fetched ahead, hist[1] phase A's, hist[1 + D] phase B's
+    float mu_h[D + 2][TR], rs_h[D + 2][TR];
     auto fetch_stats = [&](int64_t j, float (&mu)[TR], float (&rs)[TR]) {
 #pragma unroll
       for (int r = 0; r < TR; ++r) {
@@ -437,11 +439,21 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
         rs[r] = in ? __ldg(rstd + row) : 0.0f;
       }
     };
-    fetch_stats(0, mu_n, rs_n);
-    for (int64_t i = 0; i <= g.my_tiles && ok; ++i) {
 #pragma unroll
-      for (int r = 0; r < TR; ++r) { mu_b[r] = mu_a[r]; rs_b[r] = rs_a[r]; mu_a[r] = mu_n[r]; rs_a[r] = rs_n[r]; }
-      fetch_stats(i + 1, mu_n, rs_n);
+    for (int h = 0; h < D + 2; ++h)
+#pragma unroll
+      for (int r = 0; r < TR; ++r) { mu_h[h][r] = 0.0f; rs_h[h][r] = 0.0f; }
+    fetch_stats(0, mu_h[0], rs_h[0]);
+    for (int64_t i = 0; i < g.my_tiles + D && ok; ++i) {
+#pragma unroll
+      for (int h = D + 1; h >= 1; --h)
+#pragma unroll
+        for (int r = 0; r < TR; ++r) { mu_h[h][r] = mu_h[h - 1][r]; rs_h[h][r] = rs_h[h - 1][r]; }
+      fetch_stats(i + 1, mu_h[0], rs_h[0]);
+      float (&mu_a)[TR] = mu_h[1];
+      float (&rs_a)[TR] = rs_h[1];
+      float (&mu_b)[TR] = mu_h[1 + D];
+      float (&rs_b)[TR] = rs_h[1 + D];
       if (i < g.my_tiles) {
         // ---- phase A of tile i: this slab's share of the two row sums ---------------------------------
         const int s = static_cast<int>(i % g.S);
@@ -489,11 +501,11 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
           norm_slab_push<TR>(sh, g, static_cast<int>(i % kNsSlots), vals);
         }
       }
-      if (i >= 1) {
-        // ---- phase B of tile i - 1: the row sums from the C slabs, dx, and the weight-gradient terms -----
-        const int64_t t = i - 1;
+      if (i >= D) {
+        // ---- phase B of tile i - D: the row sums from the C slabs, dx, and the weight-gradient terms -----
+        const int64_t t = i - D;
         const int slot = static_cast<int>(t % kNsSlots);
-        if (!mbar_wait_cluster(&sh->xbar[slot], static_cast<uint32_t>((t / kNsSlots) & 1), status)) { ok = false; break; }
+        if (!mbar_wait(&sh->xbar[slot], static_cast<uint32_t>((t / kNsSlots) & 1), status)) { ok = false; break; }
         const int s = static_cast<int>(t % g.S);
         const int64_t row0 = (g.cluster_id + t * g.nclusters) * TR;
         const uint32_t sbase = stages_u32 + static_cast<uint32_t>(s) * stage_bytes;
