@@ -233,3 +233,46 @@ def test_out_of_range_target_surfaces_as_an_error_one_call_late():
     F.nll_loss(logp, ok.to(DEV), ignore_index=10)
     torch.cuda.synchronize()
     torch.softmax(logp, -1)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_cross_entropy_autograd_takes_the_fused_backward(dt, reduction):
+    # F.cross_entropy with class-index targets: same forward operators, but the backward is ONE pass over the
+    # log-probabilities (no dense nll_loss_backward gradient in between) — for every user of the dispatcher
+    M, C = 37, 1000
+    logits = ao.randn((M, C), 695, dt, 0.0, 2.0)
+    t = ao.randint(C, (M,), 696)
+    t[3] = -100
+    w = ao.randn((C,), 697).abs() + 0.1
+    for weight in (None, w):
+        ld = logits.to(DEV).requires_grad_(True)
+        loss = F.cross_entropy(ld, t.to(DEV), None if weight is None else weight.to(DEV).to(dt), reduction=reduction)
+        assert "FusedCrossEntropy" in loss.grad_fn.name()
+        gout = ao.randn(tuple(loss.shape), 698, dt).to(DEV) if reduction == "none" else torch.ones((), device=DEV, dtype=dt)
+        loss.backward(gout)
+        lc = logits.float().requires_grad_(True)
+        rloss = F.cross_entropy(lc, t, weight, reduction=reduction)
+        rloss.backward(gout.cpu().float())
+        if dt == torch.float32:
+            assert ao.fp32_err(loss.detach(), rloss.detach()) <= 2 and ao.fp32_err(ld.grad, lc.grad) <= 4
+        else:
+            assert torch.allclose(loss.detach().float().cpu(), rloss.detach(), rtol=2e-2, atol=1e-2)
+            # bf16: the backward works from the bf16-rounded log-probabilities the forward stored, as the stock path does
+            assert torch.allclose(ld.grad.float().cpu(), lc.grad, rtol=5e-2, atol=2e-3)
+    # what the fused kernel does not cover goes to the composite: label smoothing, probability targets, class dim not last
+    ld = logits.to(DEV).requires_grad_(True)
+    ls = F.cross_entropy(ld, t.to(DEV), label_smoothing=0.1)
+    assert "FusedCrossEntropy" not in ls.grad_fn.name()
+    ls.backward()
+    lc = logits.float().requires_grad_(True)
+    F.cross_entropy(lc, t, label_smoothing=0.1).backward()
+    assert torch.allclose(ld.grad.float().cpu(), lc.grad, rtol=5e-2, atol=2e-3)
+    probs = torch.softmax(ao.randn((M, C), 699), -1)
+    lp = F.cross_entropy(logits.to(DEV).float(), probs.to(DEV))
+    assert torch.allclose(lp.cpu(), F.cross_entropy(logits.float(), probs), rtol=1e-4)
+    x4 = ao.randn((2, 5, 3, 3), 700).to(DEV).requires_grad_(True)
+    l4 = F.cross_entropy(x4, ao.randint(5, (2, 3, 3), 701).to(DEV))
+    assert "FusedCrossEntropy" not in l4.grad_fn.name()
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0

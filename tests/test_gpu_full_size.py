@@ -165,3 +165,29 @@ def test_config5_log_softmax_nll_bf16_16384x128256():
     rs = torch.cat([dlogits[k:k + 1024].float().sum(-1) for k in range(0, M, 1024)])
     assert float(rs.abs().max()) <= 1e-5
     assert capi.device_status() == 0
+
+
+def test_softmax_over_a_middle_dim_beyond_2_to_the_31_elements():
+    # [2, 33000, 33000] bf16 (2.2e9 elements, 4.4 GB per tensor), softmax over dim 1: element offsets need 64 bits
+    # with inner > 1.  Sampled lines against the oracle (first and last line of each outer slice included).
+    O, N, I = 2, 33000, 33000
+    x = torch.empty((O, N, I), dtype=torch.bfloat16, device=DEV)
+    gen = torch.Generator(device=DEV).manual_seed(9001)
+    for o in range(O):
+        for r in range(0, N, 3000):
+            k = min(3000, N - r)
+            x[o, r:r + k] = (torch.randn((k, I), generator=gen, device=DEV) * 2.0).to(torch.bfloat16)
+    y = capi._softmax(x, 1, False)
+    lines = [(0, 0), (0, I - 1), (1, 0), (1, I - 1), (0, 12345), (1, 31999), (1, 7), (0, 16384)]
+    xs = torch.stack([x[o, :, i] for o, i in lines]).cpu()   # [lines, N]
+    ys = torch.stack([y[o, :, i] for o, i in lines])
+    assert ao.lowp_mismatch(ys, ao.softmax_fwd(xs, -1, False))[0] == 0
+    # every line sums to one (checked on a slab of lines per outer slice, and on the very last elements)
+    assert float((y[:, :, :512].float().sum(1) - 1).abs().max()) <= 2e-2
+    assert float((y[:, :, -512:].float().sum(1) - 1).abs().max()) <= 2e-2
+    dy = x  # any tensor of the shape will do as the upstream gradient: reuse the input
+    dx = capi._softmax_backward_data(dy, y, 1, torch.bfloat16)
+    dxs = torch.stack([dx[o, :, i] for o, i in lines])
+    ref = ao.softmax_bwd(xs, ys.cpu(), -1, False, torch.bfloat16)
+    assert ao.lowp_mismatch(dxs, ref)[0] == 0
+    assert capi.device_status() == 0

@@ -2,6 +2,8 @@
 // files so the instantiations compile in parallel.
 #pragma once
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 #include <type_traits>
 
 #include "launchers.h"
@@ -122,6 +124,9 @@ int slab_launch(void (*kernel)(KArgs...), const SlabPlan& p, int64_t M, std::ato
   const int64_t waves = (ntiles + nclusters - 1) / nclusters;  // no cluster finishes before the busiest one
   nclusters = (ntiles + waves - 1) / waves;
   if (clusters_out != nullptr) *clusters_out = nclusters;
+  if (getenv("B2N_DEBUG") != nullptr)
+    fprintf(stderr, "[b200norm] slab launch: C=%d slab_vecs=%d rows/tile=%d depth=%d stages=%d smem=%zu max_clusters=%d clusters=%lld\n",
+            p.c, p.slab_vecs, p.tr, p.depth, p.stages, p.smem, max_clusters, static_cast<long long>(nclusters));
   cfg.gridDim = dim3(static_cast<unsigned>(nclusters * p.c));
   cfg.numAttrs = 2;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
@@ -133,31 +138,38 @@ template <typename T, typename WT, bool RMS>
 int norm_fwd_slab_launch(const SlabPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, float* mean, float* rstd,
                          int64_t M, int64_t N, double eps, cudaStream_t st) {
   ProfileScope prof(RMS ? "rms_norm_fwd_slab" : "layer_norm_fwd_slab", st);
-  static std::atomic<uint64_t> done[4];
+  static std::atomic<uint64_t> done[6];
   int* status = device_status_ptr();
   auto go = [&](auto kernel, std::atomic<uint64_t>& d) {
     return slab_launch(kernel, p, M, d, st, nullptr, x, gamma, beta, y, mean, rstd, M, N, static_cast<float>(eps), p.slab_vecs,
                        p.stages, status);
   };
-  if (p.tr == 2) return p.depth == 2 ? go(norm_fwd_slab_kernel<T, WT, RMS, 2, 2>, done[0]) : go(norm_fwd_slab_kernel<T, WT, RMS, 2, 1>, done[1]);
-  return p.depth == 2 ? go(norm_fwd_slab_kernel<T, WT, RMS, 1, 2>, done[2]) : go(norm_fwd_slab_kernel<T, WT, RMS, 1, 1>, done[3]);
+  // the usual case — whole slabs, two-row tiles — has its own instantiations; anything else takes the general ones
+  const bool full = N == static_cast<int64_t>(p.c) * kNsConsumers * kNsEpt;
+  if (full && p.tr == 2)
+    return p.depth == 2 ? go(norm_fwd_slab_kernel<T, WT, RMS, 2, 2, true>, done[4]) : go(norm_fwd_slab_kernel<T, WT, RMS, 2, 1, true>, done[5]);
+  if (p.tr == 2) return p.depth == 2 ? go(norm_fwd_slab_kernel<T, WT, RMS, 2, 2, false>, done[0]) : go(norm_fwd_slab_kernel<T, WT, RMS, 2, 1, false>, done[1]);
+  return p.depth == 2 ? go(norm_fwd_slab_kernel<T, WT, RMS, 1, 2, false>, done[2]) : go(norm_fwd_slab_kernel<T, WT, RMS, 1, 1, false>, done[3]);
 }
 
 template <typename T, typename WT, bool RMS>
 int norm_bwd_slab_launch(const SlabPlan& p, bool wgrad, const T* dy, const T* x, const float* mean, const float* rstd,
                          const WT* gamma, T* dx, float* ws, int64_t M, int64_t N, cudaStream_t st, int64_t* clusters) {
   ProfileScope prof(RMS ? "rms_norm_bwd_slab" : "layer_norm_bwd_slab", st);
-  static std::atomic<uint64_t> done[8];
+  static std::atomic<uint64_t> done[10];
   int* status = device_status_ptr();
   auto go = [&](auto kernel, std::atomic<uint64_t>& d) {
     return slab_launch(kernel, p, M, d, st, clusters, dy, x, mean, rstd, gamma, dx, ws, M, N, p.slab_vecs, p.stages, status);
   };
+  const bool full = N == static_cast<int64_t>(p.c) * kNsConsumers * kNsEpt;
   if (wgrad) {
-    if (p.tr == 2) return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, true, 2, 2>, done[0]) : go(norm_bwd_slab_kernel<T, WT, RMS, true, 2, 1>, done[1]);
-    return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, true, 1, 2>, done[2]) : go(norm_bwd_slab_kernel<T, WT, RMS, true, 1, 1>, done[3]);
+    if (full && p.tr == 2 && p.depth == 1) return go(norm_bwd_slab_kernel<T, WT, RMS, true, 2, 1, true>, done[8]);
+    if (full && p.tr == 1 && p.depth == 1) return go(norm_bwd_slab_kernel<T, WT, RMS, true, 1, 1, true>, done[9]);
+    if (p.tr == 2) return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, true, 2, 2, false>, done[0]) : go(norm_bwd_slab_kernel<T, WT, RMS, true, 2, 1, false>, done[1]);
+    return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, true, 1, 2, false>, done[2]) : go(norm_bwd_slab_kernel<T, WT, RMS, true, 1, 1, false>, done[3]);
   }
-  if (p.tr == 2) return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, false, 2, 2>, done[4]) : go(norm_bwd_slab_kernel<T, WT, RMS, false, 2, 1>, done[5]);
-  return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, false, 1, 2>, done[6]) : go(norm_bwd_slab_kernel<T, WT, RMS, false, 1, 1>, done[7]);
+  if (p.tr == 2) return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, false, 2, 2, false>, done[4]) : go(norm_bwd_slab_kernel<T, WT, RMS, false, 2, 1, false>, done[5]);
+  return p.depth == 2 ? go(norm_bwd_slab_kernel<T, WT, RMS, false, 1, 2, false>, done[6]) : go(norm_bwd_slab_kernel<T, WT, RMS, false, 1, 1, false>, done[7]);
 }
 
 // ---- forward ------------------------------------------------------------------------------------

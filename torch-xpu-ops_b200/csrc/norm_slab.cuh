@@ -183,7 +183,8 @@ __device__ __forceinline__ void slab_load_weights(const WT* __restrict__ w, floa
 }
 
 // ---- forward -------------------------------------------------------------------------------------------
-template <typename T, typename WT, bool RMS, int TR, int D>
+// FULL: every slab fills every thread's vectors exactly (N == C * 512 * 16): no column range checks.
+template <typename T, typename WT, bool RMS, int TR, int D, bool FULL>
 __global__ void __launch_bounds__(kNsThreads, 1)
 norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta, T* __restrict__ y,
                      float* __restrict__ mean, float* __restrict__ rstd, int64_t M, int64_t N, float eps, int slab_vecs,
@@ -250,7 +251,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
           for (int k = 0; k < VPT; ++k) {
             const int v = tid + k * kNsConsumers;
-            if (valid && v < g.my_nv) {
+            if (valid && (FULL || v < g.my_nv)) {
               float2 xv[VH];
               P::unpack2(lds128(rbase + v * 16), xv);
 #pragma unroll
@@ -298,7 +299,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
               for (int k = 0; k < VPT; ++k) {
                 const int v = tid + k * kNsConsumers;
-                if (valid && v < g.my_nv) {
+                if (valid && (FULL || v < g.my_nv)) {
                   float2 xv[VH];
                   P::unpack2(lds128(rbase + v * 16), xv);
 #pragma unroll
@@ -356,7 +357,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
           for (int k = 0; k < VPT; ++k) {
             const int v = tid + k * kNsConsumers;
-            if (v < g.my_nv) {
+            if (FULL || v < g.my_nv) {
               float2 xv[VH], o[VH];
               P::unpack2(lds128(rbase + v * 16), xv);
 #pragma unroll
@@ -384,7 +385,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 
 // ---- backward ------------------------------------------------------------------------------------------
 // stage = [dy rows | x rows]; dx overwrites the dy rows.  ws: partial weight gradients, row `cluster index`.
-template <typename T, typename WT, bool RMS, bool WGRAD, int TR, int D>
+template <typename T, typename WT, bool RMS, bool WGRAD, int TR, int D, bool FULL>
 __global__ void __launch_bounds__(kNsThreads, 1)
 norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx, float* __restrict__ ws,
@@ -470,7 +471,7 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
 #pragma unroll
           for (int k = 0; k < VPT; ++k) {
             const int v = tid + k * kNsConsumers;
-            if (valid && v < g.my_nv) {
+            if (valid && (FULL || v < g.my_nv)) {
               float2 dv[VH], xh[VH];
               P::unpack2(lds128(dbase + v * 16), dv);
               P::unpack2(lds128(xbase + v * 16), xh);
@@ -524,7 +525,7 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
 #pragma unroll
           for (int k = 0; k < VPT; ++k) {
             const int v = tid + k * kNsConsumers;
-            if (v < g.my_nv) {
+            if (FULL || v < g.my_nv) {
               float2 dv[VH], xh[VH], o[VH];
               P::unpack2(lds128(dbase + v * 16), dv);
               P::unpack2(lds128(xbase + v * 16), xh);

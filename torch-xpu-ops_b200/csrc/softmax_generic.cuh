@@ -169,56 +169,119 @@ __device__ __forceinline__ void st_pair(f16* p, float2 v) { *reinterpret_cast<__
 // at a time touches memory in 128-byte pieces half a megabyte apart, which DRAM serves at a fifth of
 // its bandwidth.  Here a CTA stages a tile of `tile` adjacent inner positions x all N line elements
 // in shared memory with 16-byte accesses — N contiguous runs of `tile` elements (1 KB where shared
-// memory allows) — one thread per inner position then walks its line in shared memory (consecutive
-// threads, consecutive addresses: no bank conflicts), leaves the result in place, and the tile goes
-// back the same way.  Every element crosses HBM once each way, for any N whose tile fits.
+// memory allows), several loads in flight per thread — works on the lines there and sends the tile
+// back the same way: every element crosses HBM once each way, for any N whose tile fits.
+//
+// In shared memory a line is shared by `segs` threads (as many as the CTA's threads allow for the
+// tile's width: a 256-column tile of 16-bit values is 128 column pairs x 2 segments), each walking
+// every segs-th element with a RUNNING (max, sum) — one walk for the statistics instead of two —
+// and consecutive threads touching consecutive addresses (no bank conflicts).  The segments' partial
+// results are combined in segment order through a small scratch array, then each thread writes the
+// results for the elements it walked.
 // Requires inner % VEC == 0 and 16-byte aligned pointers; TI == TO.
+constexpr int kTileThreads = 256;
+
+// running (max, sum of exp(x - max)) with the semantics of the row kernels: -inf entries give 0, a NaN makes
+// the sum NaN (the maximum ignores it), +inf makes exp(inf - inf) = NaN
+template <typename T> struct OnlineMaxSum {
+  float m, s;
+  __device__ __forceinline__ void init() { m = acc_neg_inf<float>(); s = 0.0f; }
+  __device__ __forceinline__ void add(float v) {
+    const float ninf = acc_neg_inf<float>();
+    const float nm = fmaxf(m, v);
+    const float scale = (m == ninf) ? 0.0f : exp_for<T>(m - nm);
+    const float base = (nm == ninf) ? 0.0f : nm;  // all -inf so far: exp(-inf - 0) = 0; NaN stays NaN
+    s = fmaf(s, scale, exp_for<T>(v - base));
+    m = nm;
+  }
+  __device__ __forceinline__ void merge(float om, float os) {
+    const float ninf = acc_neg_inf<float>();
+    const float nm = fmaxf(m, om);
+    // a NaN partial sum must survive a partial maximum of -inf (0 * exp(...) would hide it otherwise)
+    const float a = (m == ninf) ? ((s != s) ? s : 0.0f) : s * exp_for<T>(m - nm);
+    const float b = (om == ninf) ? ((os != os) ? os : 0.0f) : os * exp_for<T>(om - nm);
+    s = a + b;
+    m = nm;
+  }
+};
+
+template <typename T> __device__ __forceinline__ void tile_copy_in(T* sm, const T* gb, int N, int64_t inner, int tile, int vpr) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int total = N * vpr;  // 16-byte vectors of the tile
+#pragma unroll 8
+  for (int i = threadIdx.x; i < total; i += kTileThreads) {
+    const int j = i / vpr, c = i - j * vpr;
+    *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC) =
+        *reinterpret_cast<const uint4*>(gb + static_cast<int64_t>(j) * inner + c * VEC);
+  }
+}
+template <typename T> __device__ __forceinline__ void tile_copy_out(T* gb, const T* sm, int N, int64_t inner, int tile, int vpr) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int total = N * vpr;
+#pragma unroll 8
+  for (int i = threadIdx.x; i < total; i += kTileThreads) {
+    const int j = i / vpr, c = i - j * vpr;
+    *reinterpret_cast<uint4*>(gb + static_cast<int64_t>(j) * inner + c * VEC) =
+        *reinterpret_cast<const uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC);
+  }
+}
+
 template <typename T, bool LOG>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kTileThreads)
 softmax_fwd_tile_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t outer, int N, int64_t inner, int tile,
                         int safe) {
-  using A = acc_t<T>;
   constexpr int VEC = 16 / sizeof(T);
+  constexpr int CPT = sizeof(T) == 2 ? 2 : 1;  // columns a thread handles with one shared-memory access
   extern __shared__ __align__(16) unsigned char tile_smem[];
+  __shared__ float4 part[kTileThreads];  // per (segment, column group): {max0, sum0, max1, sum1}
   T* sm = reinterpret_cast<T*>(tile_smem);
   const int64_t tpo = (inner + tile - 1) / tile, total = outer * tpo;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const float ninf = acc_neg_inf<float>();
   for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
     const int64_t o = t / tpo, i0 = (t % tpo) * tile;
     const int w = static_cast<int>(inner - i0 < tile ? inner - i0 : tile);  // a multiple of VEC
-    const int vpr = w / VEC;
-    const T* xb = x + o * N * inner + i0;
-    T* yb = y + o * N * inner + i0;
-    for (int j = warp; j < N; j += nwarp)
-      for (int c = lane; c < vpr; c += 32)
-        *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC) =
-            *reinterpret_cast<const uint4*>(xb + static_cast<int64_t>(j) * inner + c * VEC);
+    tile_copy_in(sm, x + o * N * inner + i0, N, inner, tile, w / VEC);
     __syncthreads();
-    if constexpr (sizeof(T) == 2) {
-      // 16-bit storage: a thread walks two adjacent lines with one 32-bit access per step
-      for (int c = 2 * threadIdx.x; c < w; c += 2 * blockDim.x) {
-        T* col = sm + c;
-        float2 mx = make_float2(acc_neg_inf<float>(), acc_neg_inf<float>());
-        bool nan0 = false, nan1 = false;
-        for (int j = 0; j < N; ++j) {
+    const int groups = w / CPT;                                  // column groups of the tile (<= kTileThreads)
+    int segs = kTileThreads / groups;
+    if (segs > N) segs = N;
+    if (segs > 32) segs = 32;
+    const bool active = static_cast<int>(threadIdx.x) < groups * segs;
+    const int gidx = threadIdx.x % groups, sg = threadIdx.x / groups;
+    T* col = sm + gidx * CPT;
+    OnlineMaxSum<T> a, b;  // b: the second column of a pair (16-bit storage)
+    a.init();
+    b.init();
+    if (active) {
+#pragma unroll 4
+      for (int j = sg; j < N; j += segs) {
+        if constexpr (CPT == 2) {
           const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
-          nan0 |= (v.x != v.x);
-          nan1 |= (v.y != v.y);
-          mx.x = fmaxf(mx.x, v.x);
-          mx.y = fmaxf(mx.y, v.y);
+          a.add(v.x);
+          b.add(v.y);
+        } else {
+          a.add(to_acc<float>(col[static_cast<size_t>(j) * tile]));
         }
-        float2 sum = make_float2(0.0f, 0.0f);
-        for (int j = 0; j < N; ++j) {
-          const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
-          sum.x += exp_for<T>(v.x - mx.x);
-          sum.y += exp_for<T>(v.y - mx.y);
-        }
-        if (nan0) sum.x = acc_nan<float>();
-        if (nan1) sum.y = acc_nan<float>();
-        const float2 lg = make_float2(LOG ? logf(sum.x) : 0.0f, LOG ? logf(sum.y) : 0.0f);
-        const float2 inv = make_float2(LOG ? 0.0f : 1.0f / sum.x, LOG ? 0.0f : 1.0f / sum.y);
-        const bool z0 = safe && mx.x == acc_neg_inf<float>() && !nan0, z1 = safe && mx.y == acc_neg_inf<float>() && !nan1;
-        for (int j = 0; j < N; ++j) {
+      }
+      part[threadIdx.x] = make_float4(a.m, a.s, b.m, b.s);
+    }
+    __syncthreads();
+    if (active) {
+      const float4 p0 = part[gidx];
+      a.m = p0.x; a.s = p0.y; b.m = p0.z; b.s = p0.w;
+      for (int k = 1; k < segs; ++k) {  // segment order: every thread of the line gets the same bits
+        const float4 pk = part[k * groups + gidx];
+        a.merge(pk.x, pk.y);
+        if (CPT == 2) b.merge(pk.z, pk.w);
+      }
+      // (+inf in the line: exp(inf - inf) has made the sum NaN already; a NaN entry too)
+      const float2 mx = make_float2(a.m, b.m), sum = make_float2(a.s, b.s);
+      const float2 lg = make_float2(LOG ? logf(sum.x) : 0.0f, LOG ? logf(sum.y) : 0.0f);
+      const float2 inv = make_float2(LOG ? 0.0f : 1.0f / sum.x, LOG ? 0.0f : 1.0f / sum.y);
+      const bool z0 = safe && mx.x == ninf && !(sum.x != sum.x), z1 = safe && mx.y == ninf && !(sum.y != sum.y);
+#pragma unroll 4
+      for (int j = sg; j < N; j += segs) {
+        if constexpr (CPT == 2) {
           const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
           const float dx0 = v.x - mx.x, dx1 = v.y - mx.y;
           float2 e = LOG ? make_float2(dx0 - lg.x, dx1 - lg.y)
@@ -226,70 +289,51 @@ softmax_fwd_tile_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t oute
           if (z0) e.x = 0.0f;
           if (z1) e.y = 0.0f;
           st_pair(col + static_cast<size_t>(j) * tile, e);
+        } else {
+          const float d = to_acc<float>(col[static_cast<size_t>(j) * tile]) - mx.x;
+          const float e = LOG ? d - lg.x : exp_for<T>(d) / sum.x;
+          col[static_cast<size_t>(j) * tile] = from_acc<T>(z0 ? 0.0f : e);
         }
-      }
-    } else
-    for (int c = threadIdx.x; c < w; c += blockDim.x) {
-      // three walks over the line in shared memory (max; sum of exp; result): reads there are cheap, and exp
-      // of a 16-bit result is one hardware instruction
-      A mx = acc_neg_inf<A>();
-      bool has_nan = false;
-      for (int j = 0; j < N; ++j) {
-        const A v = to_acc<A>(sm[static_cast<size_t>(j) * tile + c]);
-        has_nan |= (v != v);
-        mx = acc_max(mx, v);
-      }
-      A s = 0;
-      for (int j = 0; j < N; ++j) s += exp_for<T>(to_acc<A>(sm[static_cast<size_t>(j) * tile + c]) - mx);
-      if (has_nan) s = acc_nan<A>();  // (+inf in the line: exp(inf - inf) has made the sum NaN already)
-      const A lg = LOG ? acc_log(s) : A(0);
-      const A inv = LOG ? A(0) : A(1) / s;
-      const bool zero = safe && mx == acc_neg_inf<A>() && !has_nan;
-      for (int j = 0; j < N; ++j) {
-        const A d = to_acc<A>(sm[static_cast<size_t>(j) * tile + c]) - mx;
-        const A e = LOG ? d - lg : (sizeof(T) <= 2 ? exp_for<T>(d) * inv : exp_for<T>(d) / s);
-        sm[static_cast<size_t>(j) * tile + c] = from_acc<T>(zero ? A(0) : e);
       }
     }
     __syncthreads();
-    for (int j = warp; j < N; j += nwarp)
-      for (int c = lane; c < vpr; c += 32)
-        *reinterpret_cast<uint4*>(yb + static_cast<int64_t>(j) * inner + c * VEC) =
-            *reinterpret_cast<const uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC);
+    tile_copy_out(y + o * N * inner + i0, sm, N, inner, tile, w / VEC);
     __syncthreads();  // the next tile's loads overwrite the staging area
   }
 }
 
 // dy tile at sm[0 .. N*tile), y tile behind it; dx overwrites the dy tile.
 template <typename T, bool LOG>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kTileThreads)
 softmax_bwd_tile_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t outer, int N,
                         int64_t inner, int tile) {
-  using A = acc_t<T>;
   constexpr int VEC = 16 / sizeof(T);
+  constexpr int CPT = sizeof(T) == 2 ? 2 : 1;
   extern __shared__ __align__(16) unsigned char tile_smem[];
+  __shared__ float2 part[kTileThreads];
   T* sd = reinterpret_cast<T*>(tile_smem);
   T* sy = sd + static_cast<size_t>(N) * tile;
   const int64_t tpo = (inner + tile - 1) / tile, total = outer * tpo;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
     const int64_t o = t / tpo, i0 = (t % tpo) * tile;
     const int w = static_cast<int>(inner - i0 < tile ? inner - i0 : tile);
-    const int vpr = w / VEC;
     const int64_t base = o * N * inner + i0;
-    for (int j = warp; j < N; j += nwarp)
-      for (int c = lane; c < vpr; c += 32) {
-        const int64_t g = base + static_cast<int64_t>(j) * inner + c * VEC;
-        const size_t l = static_cast<size_t>(j) * tile + c * VEC;
-        *reinterpret_cast<uint4*>(sd + l) = *reinterpret_cast<const uint4*>(dy + g);
-        *reinterpret_cast<uint4*>(sy + l) = *reinterpret_cast<const uint4*>(y + g);
-      }
+    tile_copy_in(sd, dy + base, N, inner, tile, w / VEC);
+    tile_copy_in(sy, y + base, N, inner, tile, w / VEC);
     __syncthreads();
-    if constexpr (sizeof(T) == 2) {
-      for (int c = 2 * threadIdx.x; c < w; c += 2 * blockDim.x) {
-        float2 sum = make_float2(0.0f, 0.0f);
-        for (int j = 0; j < N; ++j) {
-          const size_t l = static_cast<size_t>(j) * tile + c;
+    const int groups = w / CPT;
+    int segs = kTileThreads / groups;
+    if (segs > N) segs = N;
+    if (segs > 32) segs = 32;
+    const bool active = static_cast<int>(threadIdx.x) < groups * segs;
+    const int gidx = threadIdx.x % groups, sg = threadIdx.x / groups;
+    const size_t c = static_cast<size_t>(gidx) * CPT;
+    float2 sum = make_float2(0.0f, 0.0f);
+    if (active) {
+#pragma unroll 4
+      for (int j = sg; j < N; j += segs) {
+        const size_t l = static_cast<size_t>(j) * tile + c;
+        if constexpr (CPT == 2) {
           const float2 d = ld_pair(sd + l);
           if constexpr (LOG) {
             sum.x += d.x;
@@ -299,34 +343,37 @@ softmax_bwd_tile_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
             sum.x = fmaf(d.x, yy.x, sum.x);
             sum.y = fmaf(d.y, yy.y, sum.y);
           }
+        } else {
+          const float d = to_acc<float>(sd[l]);
+          sum.x += LOG ? d : d * to_acc<float>(sy[l]);
         }
-        for (int j = 0; j < N; ++j) {
-          const size_t l = static_cast<size_t>(j) * tile + c;
+      }
+      part[threadIdx.x] = sum;
+    }
+    __syncthreads();
+    if (active) {
+      sum = part[gidx];
+      for (int k = 1; k < segs; ++k) {
+        const float2 pk = part[k * groups + gidx];
+        sum.x += pk.x;
+        sum.y += pk.y;
+      }
+#pragma unroll 4
+      for (int j = sg; j < N; j += segs) {
+        const size_t l = static_cast<size_t>(j) * tile + c;
+        if constexpr (CPT == 2) {
           const float2 d = ld_pair(sd + l), yy = ld_pair(sy + l);
-          const float2 o = LOG ? make_float2(d.x - exp_for<T>(yy.x) * sum.x, d.y - exp_for<T>(yy.y) * sum.y)
+          const float2 r = LOG ? make_float2(d.x - exp_for<T>(yy.x) * sum.x, d.y - exp_for<T>(yy.y) * sum.y)
                                : make_float2(yy.x * (d.x - sum.x), yy.y * (d.y - sum.y));
-          st_pair(sd + l, o);
+          st_pair(sd + l, r);
+        } else {
+          const float d = to_acc<float>(sd[l]), yy = to_acc<float>(sy[l]);
+          sd[l] = from_acc<T>(LOG ? d - exp_for<T>(yy) * sum.x : yy * (d - sum.x));
         }
-      }
-    } else
-    for (int c = threadIdx.x; c < w; c += blockDim.x) {
-      A s = 0;
-      for (int j = 0; j < N; ++j) {
-        const size_t l = static_cast<size_t>(j) * tile + c;
-        const A d = to_acc<A>(sd[l]);
-        s += LOG ? d : d * to_acc<A>(sy[l]);
-      }
-      for (int j = 0; j < N; ++j) {
-        const size_t l = static_cast<size_t>(j) * tile + c;
-        const A d = to_acc<A>(sd[l]), yy = to_acc<A>(sy[l]);
-        sd[l] = from_acc<T>(LOG ? d - exp_for<T>(yy) * s : yy * (d - s));
       }
     }
     __syncthreads();
-    for (int j = warp; j < N; j += nwarp)
-      for (int c = lane; c < vpr; c += 32)
-        *reinterpret_cast<uint4*>(dx + base + static_cast<int64_t>(j) * inner + c * VEC) =
-            *reinterpret_cast<const uint4*>(sd + static_cast<size_t>(j) * tile + c * VEC);
+    tile_copy_out(dx + base, sd, N, inner, tile, w / VEC);
     __syncthreads();
   }
 }

@@ -193,7 +193,7 @@ inline int spatial_tile_elems(int64_t N, int esize, int ntensors, int64_t inner,
   int tile = 1024 / esize;
   const int min_tile = 256 / esize;
   while (tile > min_tile && (N * tile * esize * ntensors > 110 * 1024 || tile / 2 >= inner)) tile /= 2;
-  if (N * tile * esize * ntensors > max_smem) return 0;
+  if (N * tile * esize * ntensors > max_smem - 4096) return 0;  // the kernels keep 4 KB of static scratch
   return tile;
 }
 
@@ -250,7 +250,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
   }
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
-  if constexpr (std::is_same<TI, TO>::value) {
+  if constexpr (std::is_same<TI, TO>::value && !std::is_same<TI, double>::value) {
     constexpr int VEC = 16 / sizeof(TI);
     const DeviceInfo& di = device_info();
     const int tile = spatial_tile_elems(N, sizeof(TI), 1, inner, di.max_smem_optin);
@@ -262,8 +262,8 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
       const int64_t tiles = outer * ((inner + tile - 1) / tile);
       const int64_t cap = static_cast<int64_t>(di.sm_count) * 8;
       ProfileScope prof(LOG ? "log_softmax_fwd_tile" : "softmax_fwd_tile", st);
-      kernel<<<static_cast<int>(tiles < cap ? tiles : cap), 256, smem, st>>>(x, y, outer, static_cast<int>(N), inner,
-                                                                               tile, safe);
+      kernel<<<static_cast<int>(tiles < cap ? tiles : cap), kTileThreads, smem, st>>>(x, y, outer, static_cast<int>(N), inner,
+                                                                                        tile, safe);
       return launched();
     }
   }
@@ -348,7 +348,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
   }
   if (forced == B2N_PATH_RING || forced == B2N_PATH_CLUSTER || forced == B2N_PATH_TWOPASS) return B2N_ERR_BAD_ARG;
   note_path("generic");
-  if constexpr (std::is_same<TG, TO>::value) {
+  if constexpr (std::is_same<TG, TO>::value && !std::is_same<TG, double>::value) {
     constexpr int VEC = 16 / sizeof(TG);
     const DeviceInfo& di = device_info();
     const int tile = spatial_tile_elems(N, sizeof(TG), 2, inner, di.max_smem_optin);
@@ -361,8 +361,8 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
       const int64_t tiles = outer * ((inner + tile - 1) / tile);
       const int64_t cap = static_cast<int64_t>(di.sm_count) * 8;
       ProfileScope prof(LOG ? "log_softmax_bwd_tile" : "softmax_bwd_tile", st);
-      kernel<<<static_cast<int>(tiles < cap ? tiles : cap), 256, smem, st>>>(dy, y, dx, outer, static_cast<int>(N), inner,
-                                                                               tile);
+      kernel<<<static_cast<int>(tiles < cap ? tiles : cap), kTileThreads, smem, st>>>(dy, y, dx, outer, static_cast<int>(N), inner,
+                                                                                        tile);
       return launched();
     }
   }
