@@ -70,8 +70,9 @@ typedef enum b2n_tuning_knob {
   B2N_TUNE_STAGES = 1,         /* upper bound on the ring depth */
   B2N_TUNE_STORE_LAG = 2,      /* bulk stores left in flight before a stage is refilled (1..3) */
   B2N_TUNE_CLUSTER_SIZE = 3,   /* CTAs per row in the cluster kernels (2, 4 or 8) */
-  B2N_TUNE_SM_MARGIN = 4       /* SMs the persistent kernels leave free, e.g. for the kernel of a collective that
+  B2N_TUNE_SM_MARGIN = 4,      /* SMs the persistent kernels leave free, e.g. for the kernel of a collective that
                                   runs beside them on another stream (it cannot share an SM with a ring CTA) */
+  B2N_TUNE_TILE_KB = 5         /* non-last-dim softmax: shared memory (KB) one staged tile may take (0: automatic) */
 } b2n_tuning_knob;
 int b2n_set_tuning(int knob, int value);
 /* Diagnostic: while a buffer is set (this thread), one consumer thread of CTA 0 of the layer-norm /

@@ -246,12 +246,12 @@ def test_cross_entropy_autograd_takes_the_fused_backward(dt, reduction):
     t[3] = -100
     w = ao.randn((C,), 697).abs() + 0.1
     for weight in (None, w):
-        ld = logits.to(DEV).requires_grad_(True)
+        ld = logits.detach().clone().to(DEV).requires_grad_(True)
         loss = F.cross_entropy(ld, t.to(DEV), None if weight is None else weight.to(DEV).to(dt), reduction=reduction)
         assert "FusedCrossEntropy" in loss.grad_fn.name()
         gout = ao.randn(tuple(loss.shape), 698, dt).to(DEV) if reduction == "none" else torch.ones((), device=DEV, dtype=dt)
         loss.backward(gout)
-        lc = logits.float().requires_grad_(True)
+        lc = logits.detach().float().clone().requires_grad_(True)
         rloss = F.cross_entropy(lc, t, weight, reduction=reduction)
         rloss.backward(gout.cpu().float())
         if dt == torch.float32:
@@ -261,11 +261,11 @@ def test_cross_entropy_autograd_takes_the_fused_backward(dt, reduction):
             # bf16: the backward works from the bf16-rounded log-probabilities the forward stored, as the stock path does
             assert torch.allclose(ld.grad.float().cpu(), lc.grad, rtol=5e-2, atol=2e-3)
     # what the fused kernel does not cover goes to the composite: label smoothing, probability targets, class dim not last
-    ld = logits.to(DEV).requires_grad_(True)
+    ld = logits.detach().clone().to(DEV).requires_grad_(True)
     ls = F.cross_entropy(ld, t.to(DEV), label_smoothing=0.1)
     assert "FusedCrossEntropy" not in ls.grad_fn.name()
     ls.backward()
-    lc = logits.float().requires_grad_(True)
+    lc = logits.detach().float().clone().requires_grad_(True)
     F.cross_entropy(lc, t, label_smoothing=0.1).backward()
     assert torch.allclose(ld.grad.float().cpu(), lc.grad, rtol=5e-2, atol=2e-3)
     probs = torch.softmax(ao.randn((M, C), 699), -1)

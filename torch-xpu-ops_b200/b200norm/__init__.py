@@ -27,7 +27,7 @@ ERR_BAD_ARG, ERR_UNSUPPORTED_DTYPE, ERR_WORKSPACE, ERR_CUDA = -1, -2, -3, -4
 ERR_TIMEOUT, ERR_TARGET_RANGE, ERR_TOO_LARGE = -5, -6, -7
 PATH_AUTO, PATH_GENERIC, PATH_RING, PATH_CLUSTER, PATH_TWOPASS = 0, 1, 2, 3, 4
 REDUCE_NONE, REDUCE_MEAN, REDUCE_SUM = 0, 1, 2
-TUNE_ROWS_PER_GROUP, TUNE_STAGES, TUNE_STORE_LAG, TUNE_CLUSTER_SIZE, TUNE_SM_MARGIN = 0, 1, 2, 3, 4
+TUNE_ROWS_PER_GROUP, TUNE_STAGES, TUNE_STORE_LAG, TUNE_CLUSTER_SIZE, TUNE_SM_MARGIN, TUNE_TILE_KB = 0, 1, 2, 3, 4, 5
 
 
 class B200NormError(RuntimeError):

@@ -668,12 +668,14 @@ Tensor& nll_loss_backward_out(const Tensor& grad_output, const Tensor& self, con
 class FusedCrossEntropy : public torch::autograd::Function<FusedCrossEntropy> {
  public:
   static Tensor forward(torch::autograd::AutogradContext* ctx, const Tensor& self, const Tensor& target,
-                        const Tensor& weight, int64_t reduction, int64_t ignore_index) {
+                        const std::optional<Tensor>& weight, int64_t reduction, int64_t ignore_index) {
     at::AutoDispatchBelowADInplaceOrView below_autograd;
     Tensor logp = at::_log_softmax(self, -1, false);
-    std::optional<Tensor> w = weight.defined() ? std::optional<Tensor>(weight) : std::nullopt;
-    auto [loss, total_weight] = at::nll_loss_forward(logp, target, w, reduction, ignore_index);
-    ctx->save_for_backward({logp, target, weight, total_weight});
+    auto [loss, total_weight] = at::nll_loss_forward(logp, target, weight, reduction, ignore_index);
+    // (an absent weight is saved as an empty tensor: the saved list holds defined tensors only)
+    ctx->save_for_backward({logp, target, weight.has_value() && weight->defined() ? *weight : at::empty({0}, logp.options()),
+                            total_weight});
+    ctx->saved_data["has_weight"] = weight.has_value() && weight->defined();
     ctx->saved_data["reduction"] = reduction;
     ctx->saved_data["ignore_index"] = ignore_index;
     return loss;
@@ -692,7 +694,7 @@ class FusedCrossEntropy : public torch::autograd::Function<FusedCrossEntropy> {
     Tensor y = logp.contiguous();
     Tensor g = grads[0].to(y.scalar_type()).contiguous();
     Tensor t = target.contiguous();
-    Tensor w = weight.defined() ? weight.to(y.scalar_type()).contiguous() : Tensor();
+    Tensor w = ctx->saved_data["has_weight"].toBool() ? weight.to(y.scalar_type()).contiguous() : Tensor();
     Tensor tw = total_weight.to(y.scalar_type()).contiguous();
     Tensor dx = at::empty_like(y);
     if (y.numel() > 0) {
@@ -720,7 +722,8 @@ Tensor cross_entropy_loss_autograd(const Tensor& self, const Tensor& target, con
                      (dt == at::kFloat || dt == at::kHalf || dt == at::kBFloat16 || dt == at::kDouble) &&
                      (!weight.defined() || (weight.is_cuda() && weight.dim() == 1 && weight.numel() == self.size(-1)));
   if (!fused) return at::native::cross_entropy_loss_symint(self, target, weight_opt, reduction, std::move(ignore_index), label_smoothing);
-  return FusedCrossEntropy::apply(self, target, weight, reduction, ignore_index.expect_int());
+  return FusedCrossEntropy::apply(self, target, weight.defined() ? std::optional<Tensor>(weight) : std::nullopt, reduction,
+                                  ignore_index.expect_int());
 }
 
 }  // namespace b200norm

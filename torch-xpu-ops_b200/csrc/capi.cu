@@ -162,6 +162,7 @@ int b2n_set_tuning(int knob, int value) {
     case B2N_TUNE_STORE_LAG: t.lag = value; return B2N_OK;
     case B2N_TUNE_CLUSTER_SIZE: t.cluster = value; return B2N_OK;
     case B2N_TUNE_SM_MARGIN: t.sm_margin = value; return B2N_OK;
+    case B2N_TUNE_TILE_KB: t.tile_kb = value; return B2N_OK;
     default: return B2N_ERR_BAD_ARG;
   }
 }

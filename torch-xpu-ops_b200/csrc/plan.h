@@ -23,6 +23,7 @@ struct RingTuning {
   int rpg = 0, stages = 0, lag = 0;
   int cluster = 0;  // CTAs per row in the cluster kernels (1, 2, 4 or 8)
   int sm_margin = 0;  // SMs the persistent kernels leave free (for a collective's kernel running beside them)
+  int tile_kb = 0;    // non-last-dim softmax: shared memory one staged tile may take (0: automatic)
   unsigned long long* trace_buf = nullptr;  // device buffer for the event trace (diagnostic), or null
   unsigned trace_cap = 0;                   // records it can hold
 };

@@ -169,31 +169,23 @@ __device__ __forceinline__ void st_pair(f16* p, float2 v) { *reinterpret_cast<__
 // at a time touches memory in 128-byte pieces half a megabyte apart, which DRAM serves at a fifth of
 // its bandwidth.  Here a CTA stages a tile of `tile` adjacent inner positions x all N line elements
 // in shared memory with 16-byte accesses — N contiguous runs of `tile` elements (1 KB where shared
-// memory allows), several loads in flight per thread — works on the lines there and sends the tile
+// memory allows), four loads in flight per thread — works on the lines there and sends the tile
 // back the same way: every element crosses HBM once each way, for any N whose tile fits.
 //
 // In shared memory a line is shared by `segs` threads (as many as the CTA's threads allow for the
 // tile's width: a 256-column tile of 16-bit values is 128 column pairs x 2 segments), each walking
-// every segs-th element with a RUNNING (max, sum) — one walk for the statistics instead of two —
-// and consecutive threads touching consecutive addresses (no bank conflicts).  The segments' partial
+// every segs-th element, consecutive threads touching consecutive addresses (no bank conflicts).  The segments' partial
 // results are combined in segment order through a small scratch array, then each thread writes the
 // results for the elements it walked.
 // Requires inner % VEC == 0 and 16-byte aligned pointers; TI == TO.
 constexpr int kTileThreads = 256;
+constexpr int kTileScratchBytes = 4096;  // the segments' partial results, in front of the staged tile
 
-// running (max, sum of exp(x - max)) with the semantics of the row kernels: -inf entries give 0, a NaN makes
-// the sum NaN (the maximum ignores it), +inf makes exp(inf - inf) = NaN
+// (max, sum of exp(x - max)) of a segment of a line, with the semantics of the row kernels: -inf entries give 0,
+// a NaN makes the sum NaN (the maximum ignores it), +inf makes exp(inf - inf) = NaN
 template <typename T> struct OnlineMaxSum {
   float m, s;
   __device__ __forceinline__ void init() { m = acc_neg_inf<float>(); s = 0.0f; }
-  __device__ __forceinline__ void add(float v) {
-    const float ninf = acc_neg_inf<float>();
-    const float nm = fmaxf(m, v);
-    const float scale = (m == ninf) ? 0.0f : exp_for<T>(m - nm);
-    const float base = (nm == ninf) ? 0.0f : nm;  // all -inf so far: exp(-inf - 0) = 0; NaN stays NaN
-    s = fmaf(s, scale, exp_for<T>(v - base));
-    m = nm;
-  }
   __device__ __forceinline__ void merge(float om, float os) {
     const float ninf = acc_neg_inf<float>();
     const float nm = fmaxf(m, om);
@@ -205,25 +197,44 @@ template <typename T> struct OnlineMaxSum {
   }
 };
 
+// Tile <-> global copies: a warp takes whole lines (its lanes the line's 16-byte vectors: one contiguous run per
+// access), four lines at a time so that several loads are in flight per thread.
 template <typename T> __device__ __forceinline__ void tile_copy_in(T* sm, const T* gb, int N, int64_t inner, int tile, int vpr) {
   constexpr int VEC = 16 / sizeof(T);
-  const int total = N * vpr;  // 16-byte vectors of the tile
+  if (N >= 32) {
+    // many lines: the tile's vectors as one flat index space over the CTA's threads, eight loads in flight each
+    // (measured better from a few dozen lines on; below that the per-vector division costs more than it gains)
+    const int total = N * vpr;
 #pragma unroll 8
-  for (int i = threadIdx.x; i < total; i += kTileThreads) {
-    const int j = i / vpr, c = i - j * vpr;
-    *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC) =
-        *reinterpret_cast<const uint4*>(gb + static_cast<int64_t>(j) * inner + c * VEC);
+    for (int i = threadIdx.x; i < total; i += kTileThreads) {
+      const int j = i / vpr, c = i - j * vpr;
+      *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC) =
+          *reinterpret_cast<const uint4*>(gb + static_cast<int64_t>(j) * inner + c * VEC);
+    }
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = kTileThreads >> 5;
+  for (int c = lane; c < vpr; c += 32) {
+    int j = warp;
+    for (; j + 3 * nwarp < N; j += 4 * nwarp) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(gb + static_cast<int64_t>(j + u * nwarp) * inner + c * VEC);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j + u * nwarp) * tile + c * VEC) = v[u];
+    }
+    for (; j < N; j += nwarp)
+      *reinterpret_cast<uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC) =
+          *reinterpret_cast<const uint4*>(gb + static_cast<int64_t>(j) * inner + c * VEC);
   }
 }
 template <typename T> __device__ __forceinline__ void tile_copy_out(T* gb, const T* sm, int N, int64_t inner, int tile, int vpr) {
   constexpr int VEC = 16 / sizeof(T);
-  const int total = N * vpr;
-#pragma unroll 8
-  for (int i = threadIdx.x; i < total; i += kTileThreads) {
-    const int j = i / vpr, c = i - j * vpr;
-    *reinterpret_cast<uint4*>(gb + static_cast<int64_t>(j) * inner + c * VEC) =
-        *reinterpret_cast<const uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC);
-  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = kTileThreads >> 5;
+  for (int j = warp; j < N; j += nwarp)
+    for (int c = lane; c < vpr; c += 32)
+      *reinterpret_cast<uint4*>(gb + static_cast<int64_t>(j) * inner + c * VEC) =
+          *reinterpret_cast<const uint4*>(sm + static_cast<size_t>(j) * tile + c * VEC);
 }
 
 template <typename T, bool LOG>
@@ -233,8 +244,8 @@ softmax_fwd_tile_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t oute
   constexpr int VEC = 16 / sizeof(T);
   constexpr int CPT = sizeof(T) == 2 ? 2 : 1;  // columns a thread handles with one shared-memory access
   extern __shared__ __align__(16) unsigned char tile_smem[];
-  __shared__ float4 part[kTileThreads];  // per (segment, column group): {max0, sum0, max1, sum1}
-  T* sm = reinterpret_cast<T*>(tile_smem);
+  float4* part = reinterpret_cast<float4*>(tile_smem);  // per (segment, column group): {max0, sum0, max1, sum1}
+  T* sm = reinterpret_cast<T*>(tile_smem + kTileScratchBytes);
   const int64_t tpo = (inner + tile - 1) / tile, total = outer * tpo;
   const float ninf = acc_neg_inf<float>();
   for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
@@ -253,14 +264,27 @@ softmax_fwd_tile_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t oute
     a.init();
     b.init();
     if (active) {
+      // two short walks (maximum; then sum of exp about it) rather than one with a running pair: a walk's iterations
+      // are then independent but for one fmax or one add, which is what lets several loads be in flight
 #pragma unroll 4
       for (int j = sg; j < N; j += segs) {
         if constexpr (CPT == 2) {
           const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
-          a.add(v.x);
-          b.add(v.y);
+          a.m = fmaxf(a.m, v.x);
+          b.m = fmaxf(b.m, v.y);
         } else {
-          a.add(to_acc<float>(col[static_cast<size_t>(j) * tile]));
+          a.m = fmaxf(a.m, to_acc<float>(col[static_cast<size_t>(j) * tile]));
+        }
+      }
+      const float base0 = (a.m == ninf) ? 0.0f : a.m, base1 = (b.m == ninf) ? 0.0f : b.m;  // all -inf: exp(-inf - 0) = 0
+#pragma unroll 4
+      for (int j = sg; j < N; j += segs) {
+        if constexpr (CPT == 2) {
+          const float2 v = ld_pair(col + static_cast<size_t>(j) * tile);
+          a.s += exp_for<T>(v.x - base0);  // a NaN entry makes the sum NaN (the maximum ignored it)
+          b.s += exp_for<T>(v.y - base1);
+        } else {
+          a.s += exp_for<T>(to_acc<float>(col[static_cast<size_t>(j) * tile]) - base0);
         }
       }
       part[threadIdx.x] = make_float4(a.m, a.s, b.m, b.s);
@@ -302,7 +326,7 @@ softmax_fwd_tile_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t oute
   }
 }
 
-// dy tile at sm[0 .. N*tile), y tile behind it; dx overwrites the dy tile.
+// dy tile first (behind the scratch), y tile behind it; dx overwrites the dy tile.
 template <typename T, bool LOG>
 __global__ void __launch_bounds__(kTileThreads)
 softmax_bwd_tile_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __restrict__ dx, int64_t outer, int N,
@@ -310,8 +334,8 @@ softmax_bwd_tile_kernel(const T* __restrict__ dy, const T* __restrict__ y, T* __
   constexpr int VEC = 16 / sizeof(T);
   constexpr int CPT = sizeof(T) == 2 ? 2 : 1;
   extern __shared__ __align__(16) unsigned char tile_smem[];
-  __shared__ float2 part[kTileThreads];
-  T* sd = reinterpret_cast<T*>(tile_smem);
+  float2* part = reinterpret_cast<float2*>(tile_smem);
+  T* sd = reinterpret_cast<T*>(tile_smem + kTileScratchBytes);
   T* sy = sd + static_cast<size_t>(N) * tile;
   const int64_t tpo = (inner + tile - 1) / tile, total = outer * tpo;
   for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {

@@ -192,8 +192,9 @@ int softmax_twopass_launch(const T* in0, const T* in1, T* out, int64_t M, int64_
 inline int spatial_tile_elems(int64_t N, int esize, int ntensors, int64_t inner, int max_smem) {
   int tile = 1024 / esize;
   const int min_tile = 256 / esize;
-  while (tile > min_tile && (N * tile * esize * ntensors > 110 * 1024 || tile / 2 >= inner)) tile /= 2;
-  if (N * tile * esize * ntensors > max_smem - 4096) return 0;  // the kernels keep 4 KB of static scratch
+  const int64_t budget = (ring_tuning().tile_kb > 0 ? ring_tuning().tile_kb : 110) * 1024;
+  while (tile > min_tile && (N * tile * esize * ntensors > budget || tile / 2 >= inner)) tile /= 2;
+  if (N * tile * esize * ntensors > max_smem - kTileScratchBytes) return 0;  // the kernels keep a scratch area in front of the tile
   return tile;
 }
 
@@ -258,7 +259,7 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
       auto kernel = softmax_fwd_tile_kernel<TI, LOG>;
       static std::atomic<uint64_t> done{0};
       if (int e = set_smem_once_sm(kernel, done)) return e;
-      const size_t smem = static_cast<size_t>(N) * tile * sizeof(TI);
+      const size_t smem = kTileScratchBytes + static_cast<size_t>(N) * tile * sizeof(TI);
       const int64_t tiles = outer * ((inner + tile - 1) / tile);
       const int64_t cap = static_cast<int64_t>(di.sm_count) * 8;
       ProfileScope prof(LOG ? "log_softmax_fwd_tile" : "softmax_fwd_tile", st);
@@ -357,7 +358,7 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
       auto kernel = softmax_bwd_tile_kernel<TG, LOG>;
       static std::atomic<uint64_t> done{0};
       if (int e = set_smem_once_sm(kernel, done)) return e;
-      const size_t smem = static_cast<size_t>(N) * tile * sizeof(TG) * 2;
+      const size_t smem = kTileScratchBytes + static_cast<size_t>(N) * tile * sizeof(TG) * 2;
       const int64_t tiles = outer * ((inner + tile - 1) / tile);
       const int64_t cap = static_cast<int64_t>(di.sm_count) * 8;
       ProfileScope prof(LOG ? "log_softmax_bwd_tile" : "softmax_bwd_tile", st);

@@ -92,24 +92,6 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
   const float ninf = acc_neg_inf<float>();
   const uint32_t stages_u32 = smem_u32(stages);
 
-  // The mask bytes of a row are fetched ONE ROW AHEAD: a global load issued where its value is needed would add
-  // its whole latency to every row.  Within a tile the next row is known; across tiles it is guessed from the tile
-  // id the producer has (normally) already left in the next stage — a hint, checked against the row actually
-  // processed, and a wrong guess simply loads again in place.
-  MaskWord<VEC> mw_next[MASKED ? VPT : 1];
-  int64_t mw_next_row = -1;
-  auto load_mask = [&](int64_t row, MaskWord<VEC> (&m)[MASKED ? VPT : 1]) {
-    if constexpr (MASKED) {
-      const unsigned char* mr = mask.base + static_cast<size_t>((static_cast<unsigned>(row) / mask.row_div) % mask.row_mod) * N;
-#pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        const int v = tg + k * GROUP;
-        if (FULL || v < nvec) m[k].load(mr + v * VEC);
-        else m[k].clear();
-      }
-    }
-  };
-
   RingCursor cur;
   cur.start();
   for (;; cur.advance(g)) {
@@ -124,23 +106,14 @@ softmax_fwd_ring_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, i
       constexpr int HP = EPT / 2, VH = VEC / 2;  // float2 pairs per thread / per 16-byte vector
       MaskWord<VEC> mw[MASKED ? VPT : 1];
       if constexpr (MASKED) {
-        const int64_t row = tile_row0 + lr;
-        if (mw_next_row == row) {
+        const unsigned row = static_cast<unsigned>(tile_row0 + lr);
+        const unsigned char* mr = mask.base + static_cast<size_t>((row / mask.row_div) % mask.row_mod) * N;
 #pragma unroll
-          for (int k = 0; k < VPT; ++k) mw[k] = mw_next[k];
-        } else {
-          load_mask(row, mw);
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tg + k * GROUP;
+          if (FULL || v < nvec) mw[k].load(mr + v * VEC);
+          else mw[k].clear();
         }
-        int64_t nxt = -1;
-        if (r + 1 < RPG) {
-          nxt = row + 1;
-        } else {
-          const int t2 = ring_peek_tile(rs, cur.next_stage(g));
-          if (t2 >= 0) nxt = g.first_row(t2) + grp * RPG;
-        }
-        if (nxt >= M) nxt = -1;
-        if (nxt >= 0) load_mask(nxt, mw_next);
-        mw_next_row = nxt;
       }
       float2 xv[HP];
       float pm[4] = {ninf, ninf, ninf, ninf};
