@@ -52,6 +52,7 @@ struct NormSlabShared {
   uint64_t xbar[kNsSlots];                          // one arrival (the owner's, with the byte count) + C x 16 bytes per use
   alignas(16) float part[kNsSlots][kNsMaxCluster][2][2];  // [slot][source rank][row of the tile][value]: 16 bytes per source
   float red[kRingRedFloats];                        // CTA-level reduction scratch
+  float slab_n[kNsMaxCluster];                      // elements of slab c (forward: weights of the combination)
 };
 static_assert(sizeof(NormSlabShared) <= kNsHeaderBytes, "slab header too large");
 
@@ -72,7 +73,8 @@ struct NormSlabGeom {
   int64_t v0;        // first vector of this CTA's slab
   int S;             // stages
   uint32_t slab_stride;  // bytes between two row-slabs in a stage
-  int64_t ntiles, my_tiles;
+  int64_t ntiles;
+  int my_tiles;      // tiles this cluster processes (the launcher keeps it below 2^31)
 
   template <int TR> __device__ __forceinline__ void init(int64_t M_, int64_t N, int vec, int slab_vecs_, int S_) {
     namespace cg = cooperative_groups;
@@ -90,13 +92,32 @@ struct NormSlabGeom {
     S = S_;
     slab_stride = static_cast<uint32_t>(slab_vecs) * 16u;
     ntiles = (M + TR - 1) / TR;
-    my_tiles = cluster_id < ntiles ? (ntiles - cluster_id + nclusters - 1) / nclusters : 0;
+    my_tiles = cluster_id < ntiles ? static_cast<int>((ntiles - cluster_id + nclusters - 1) / nclusters) : 0;
   }
   // elements of slab c (for the combination of the forward statistics)
   __device__ __forceinline__ float slab_elems(int c, int vec) const {
     const int64_t left = nvec - static_cast<int64_t>(c) * slab_vecs;
     const int64_t nv = left < slab_vecs ? (left > 0 ? left : 0) : slab_vecs;
     return static_cast<float>(nv * vec);
+  }
+};
+
+// Where a tile lives — its stage, the parity of that stage's barriers for this use, its exchange slot and that
+// slot's parity, its first row — carried from tile to tile by additions: no division or 64-bit multiply in the loops.
+struct SlabCursor {
+  int s;
+  uint32_t phase;
+  int slot;
+  uint32_t xphase;
+  int64_t row0;
+  __device__ __forceinline__ void start(const NormSlabGeom& g, int tr) {
+    s = 0; phase = 0; slot = 0; xphase = 0;
+    row0 = g.cluster_id * tr;
+  }
+  __device__ __forceinline__ void advance(const NormSlabGeom& g, int64_t row_step) {
+    if (++s == g.S) { s = 0; phase ^= 1u; }
+    if (++slot == kNsSlots) { slot = 0; xphase ^= 1u; }
+    row0 += row_step;
   }
 };
 
@@ -112,9 +133,7 @@ __device__ __forceinline__ void norm_slab_producer(NormSlabShared* sh, unsigned 
     const int64_t left = g.M - tile * TR;
     return static_cast<int>(left < TR ? left : TR);
   };
-  auto load = [&](int64_t j) {  // this cluster's j-th tile into stage j % S
-    const int s = static_cast<int>(j % g.S);
-    const int64_t tile = g.cluster_id + j * g.nclusters;
+  auto load = [&](int s, int64_t tile) {
     const int rows = rows_of(tile);
     unsigned char* dst = stages + static_cast<size_t>(s) * stage_bytes;
     if (slab_bytes == 0) {  // a slab without columns still takes part in every exchange
@@ -128,14 +147,19 @@ __device__ __forceinline__ void norm_slab_producer(NormSlabShared* sh, unsigned 
       if (NIN == 2) bulk_g2s(dst + static_cast<size_t>(TR + r) * g.slab_stride, in1 + goff, slab_bytes, &sh->full[s]);
     }
   };
-  int64_t issued = 0;
-  for (; issued < g.S && issued < g.my_tiles; ++issued) load(issued);
-  int64_t j = 0;
+  // the load cursor runs S - 1 tiles ahead of the store cursor once the ring is full
+  int issued = 0, ls = 0;
+  int64_t ltile = g.cluster_id;
+  for (; issued < g.S && issued < g.my_tiles; ++issued) {
+    load(ls, ltile);
+    if (++ls == g.S) ls = 0;
+    ltile += g.nclusters;
+  }
+  int j = 0, s = 0;
+  uint32_t parity = 0;
+  int64_t tile = g.cluster_id;
   for (; j < g.my_tiles; ++j) {
-    const int s = static_cast<int>(j % g.S);
-    const uint32_t parity = static_cast<uint32_t>((j / g.S) & 1);
     if (!mbar_wait(&sh->done[s], parity, status)) break;
-    const int64_t tile = g.cluster_id + j * g.nclusters;
     const int rows = rows_of(tile);
     const unsigned char* src = stages + static_cast<size_t>(s) * stage_bytes;
     if (slab_bytes != 0) {
@@ -147,13 +171,19 @@ __device__ __forceinline__ void norm_slab_producer(NormSlabShared* sh, unsigned 
     bulk_commit();
     if (j >= 1 && issued < g.my_tiles) {  // the store of tile j - 1 has read its stage: that is where tile `issued` goes
       bulk_wait_read<1>();
-      load(issued);                       // issued == j - 1 + S here: same stage
+      load(ls, ltile);                    // ls == (j - 1) % S here
+      if (++ls == g.S) ls = 0;
+      ltile += g.nclusters;
       ++issued;
     }
+    if (++s == g.S) { s = 0; parity ^= 1u; }
+    tile += g.nclusters;
   }
   // if a wait gave up, let the loads already issued land before the CTA's shared memory goes away
-  for (int64_t k = j; k < issued; ++k)
-    mbar_wait(&sh->full[static_cast<int>(k % g.S)], static_cast<uint32_t>((k / g.S) & 1), status);
+  for (int k = j; k < issued; ++k) {
+    mbar_wait(&sh->full[s], parity, status);
+    if (++s == g.S) { s = 0; parity ^= 1u; }
+  }
   bulk_wait_read<0>();
 }
 
@@ -227,12 +257,17 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
     if constexpr (!RMS) slab_load_weights<WT, VPT, VEC>(beta, 0.0f, g.v0, g.my_nv, tid, gb);
     int red_phase = 0;
     bool ok = true;
-    for (int64_t i = 0; i < g.my_tiles + D && ok; ++i) {
+    if (tid < g.C) sh->slab_n[tid] = g.slab_elems(tid, VEC);  // read in phase B, behind several barriers
+    const int64_t row_step = g.nclusters * TR;
+    SlabCursor ca, cb;  // phase A's tile and phase B's (D tiles behind)
+    ca.start(g, TR);
+    cb.start(g, TR);
+    for (int i = 0; i < g.my_tiles + D && ok; ++i) {
       if (i < g.my_tiles) {
         // ---- phase A of tile i: this slab's moments of each row --------------------------------------
-        const int s = static_cast<int>(i % g.S);
-        if (!mbar_wait(&sh->full[s], static_cast<uint32_t>((i / g.S) & 1), status)) { ok = false; break; }
-        const int64_t row0 = (g.cluster_id + i * g.nclusters) * TR;
+        const int s = ca.s;
+        if (!mbar_wait(&sh->full[s], ca.phase, status)) { ok = false; break; }
+        const int64_t row0 = ca.row0;
         const uint32_t sbase = stages_u32 + static_cast<uint32_t>(s) * stage_bytes;
         float shift[TR];
         float red1[TR * (RMS ? 1 : 2)];
@@ -324,15 +359,15 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
 #pragma unroll
           for (int r = 0; r < TR; ++r) { vals[r][0] = shift[r] + mu_d[r]; vals[r][1] = m2c[r]; }
         }
-        if (tid == 0) norm_slab_push<TR>(sh, g, static_cast<int>(i % kNsSlots), vals);
+        if (tid == 0) norm_slab_push<TR>(sh, g, ca.slot, vals);
+        ca.advance(g, row_step);
       }
       if (i >= D) {
         // ---- phase B of tile i - D: the row's statistics from the C slabs, then the output -------------
-        const int64_t t = i - D;
-        const int slot = static_cast<int>(t % kNsSlots);
-        if (!mbar_wait(&sh->xbar[slot], static_cast<uint32_t>((t / kNsSlots) & 1), status)) { ok = false; break; }
-        const int s = static_cast<int>(t % g.S);
-        const int64_t row0 = (g.cluster_id + t * g.nclusters) * TR;
+        const int slot = cb.slot;
+        if (!mbar_wait(&sh->xbar[slot], cb.xphase, status)) { ok = false; break; }
+        const int s = cb.s;
+        const int64_t row0 = cb.row0;
         const uint32_t sbase = stages_u32 + static_cast<uint32_t>(s) * stage_bytes;
 #pragma unroll
         for (int r = 0; r < TR; ++r) {
@@ -343,11 +378,11 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
             for (int c = 0; c < g.C; ++c) sum += sh->part[slot][c][r][0];
             rsd = rsqrt_nr(sum * inv_n + eps);
           } else {
-            for (int c = 0; c < g.C; ++c) mu = fmaf(g.slab_elems(c, VEC) * inv_n, sh->part[slot][c][r][0], mu);
+            for (int c = 0; c < g.C; ++c) mu = fmaf(sh->slab_n[c] * inv_n, sh->part[slot][c][r][0], mu);
             float m2 = 0.0f;
             for (int c = 0; c < g.C; ++c) {
               const float d = sh->part[slot][c][r][0] - mu;
-              const float nc = g.slab_elems(c, VEC);
+              const float nc = sh->slab_n[c];
               m2 += nc > 0.0f ? fmaf(nc * d, d, sh->part[slot][c][r][1]) : 0.0f;
             }
             rsd = rsqrt_nr(m2 * inv_n + eps);
@@ -377,6 +412,7 @@ norm_fwd_slab_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, cons
         fence_async_smem();
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(&sh->done[s]);
+        cb.advance(g, row_step);
       }
     }
   }
@@ -431,10 +467,10 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     // mean / rstd of a tile's rows are fetched one iteration before phase A needs them and kept until phase B:
     // hist[0] the tile fetched ahead, hist[1] phase A's, hist[1 + D] phase B's
     float mu_h[D + 2][TR], rs_h[D + 2][TR];
-    auto fetch_stats = [&](int64_t j, float (&mu)[TR], float (&rs)[TR]) {
+    auto fetch_stats = [&](int j, int64_t row0, float (&mu)[TR], float (&rs)[TR]) {
 #pragma unroll
       for (int r = 0; r < TR; ++r) {
-        const int64_t row = (g.cluster_id + j * g.nclusters) * TR + r;
+        const int64_t row = row0 + r;
         const bool in = j < g.my_tiles && row < M;
         mu[r] = (!RMS && in) ? __ldg(mean + row) : 0.0f;
         rs[r] = in ? __ldg(rstd + row) : 0.0f;
@@ -444,22 +480,26 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
     for (int h = 0; h < D + 2; ++h)
 #pragma unroll
       for (int r = 0; r < TR; ++r) { mu_h[h][r] = 0.0f; rs_h[h][r] = 0.0f; }
-    fetch_stats(0, mu_h[0], rs_h[0]);
-    for (int64_t i = 0; i < g.my_tiles + D && ok; ++i) {
+    const int64_t row_step = g.nclusters * TR;
+    SlabCursor ca, cb;
+    ca.start(g, TR);
+    cb.start(g, TR);
+    fetch_stats(0, ca.row0, mu_h[0], rs_h[0]);
+    for (int i = 0; i < g.my_tiles + D && ok; ++i) {
 #pragma unroll
       for (int h = D + 1; h >= 1; --h)
 #pragma unroll
         for (int r = 0; r < TR; ++r) { mu_h[h][r] = mu_h[h - 1][r]; rs_h[h][r] = rs_h[h - 1][r]; }
-      fetch_stats(i + 1, mu_h[0], rs_h[0]);
+      fetch_stats(i + 1, ca.row0 + row_step, mu_h[0], rs_h[0]);  // (ca still points at tile i here)
       float (&mu_a)[TR] = mu_h[1];
       float (&rs_a)[TR] = rs_h[1];
       float (&mu_b)[TR] = mu_h[1 + D];
       float (&rs_b)[TR] = rs_h[1 + D];
       if (i < g.my_tiles) {
         // ---- phase A of tile i: this slab's share of the two row sums ---------------------------------
-        const int s = static_cast<int>(i % g.S);
-        if (!mbar_wait(&sh->full[s], static_cast<uint32_t>((i / g.S) & 1), status)) { ok = false; break; }
-        const int64_t row0 = (g.cluster_id + i * g.nclusters) * TR;
+        const int s = ca.s;
+        if (!mbar_wait(&sh->full[s], ca.phase, status)) { ok = false; break; }
+        const int64_t row0 = ca.row0;
         const uint32_t sbase = stages_u32 + static_cast<uint32_t>(s) * stage_bytes;
         float red1[TR * (RMS ? 1 : 2)];
 #pragma unroll
@@ -499,16 +539,18 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
             vals[r][0] = RMS ? 0.0f : red1[2 * r];
             vals[r][1] = RMS ? red1[r] : red1[2 * r + 1];
           }
-          norm_slab_push<TR>(sh, g, static_cast<int>(i % kNsSlots), vals);
+          norm_slab_push<TR>(sh, g, ca.slot, vals);
         }
       }
+      // (the statistics fetched ahead at the top of the iteration used ca before this advance; past the last
+      // tile the cursor simply runs on, its rows fail the range check)
+      ca.advance(g, row_step);
       if (i >= D) {
         // ---- phase B of tile i - D: the row sums from the C slabs, dx, and the weight-gradient terms -----
-        const int64_t t = i - D;
-        const int slot = static_cast<int>(t % kNsSlots);
-        if (!mbar_wait(&sh->xbar[slot], static_cast<uint32_t>((t / kNsSlots) & 1), status)) { ok = false; break; }
-        const int s = static_cast<int>(t % g.S);
-        const int64_t row0 = (g.cluster_id + t * g.nclusters) * TR;
+        const int slot = cb.slot;
+        if (!mbar_wait(&sh->xbar[slot], cb.xphase, status)) { ok = false; break; }
+        const int s = cb.s;
+        const int64_t row0 = cb.row0;
         const uint32_t sbase = stages_u32 + static_cast<uint32_t>(s) * stage_bytes;
 #pragma unroll
         for (int r = 0; r < TR; ++r) {
@@ -547,6 +589,7 @@ norm_bwd_slab_kernel(const T* __restrict__ dy, const T* __restrict__ x, const fl
         fence_async_smem();
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(&sh->done[s]);
+        cb.advance(g, row_step);
       }
     }
     if (WGRAD) {
