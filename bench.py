@@ -724,7 +724,7 @@ def run_other_configs(capi, dev, steps_of, barrier):
     """Short runs of the other BASELINE configs on this GPU: value, step time and per-kernel roofline each."""
     _load_more_workloads()
     out = {}
-    for name in ("cfg1", "cfg2", "cfg3", "cfg5", "cfg5f", "ln_long"):
+    for name in ("cfg1", "cfg2", "cfg3", "cfg5", "cfg5f", "ln_long", "gn"):
         if name not in WORKLOADS:
             continue
         wl = WORKLOADS[name]()
@@ -914,7 +914,7 @@ def main():
         del st
         torch.cuda.empty_cache()
         configs = run_other_configs(capi, dev, lambda name: {"cfg1": 64, "cfg2": 40, "cfg3": 10, "cfg5": 4,
-                                                              "cfg5f": 4, "ln_long": 10}[name], barrier)
+                                                              "cfg5f": 4, "ln_long": 10, "gn": 10}[name], barrier)
 
     if rank == 0:
         line = {

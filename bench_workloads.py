@@ -394,6 +394,58 @@ class Cfg5FusedTail(Cfg5CrossEntropy):
         return loss.detach(), x.grad
 
 
+class GroupNormFwd(_Simple):
+    """Not a BASELINE config: native_group_norm forward on the reference microbenchmark's large shape
+    (test/microbench/group_norm.py: 16 groups, [1024, 128, 32, 32]), bf16 with bf16 weights.  `rows` are samples."""
+    name, rows, C, HW, G, cpu_sample_rows = "gn", 1024, 128, 32 * 32, 16, 64
+    e2e_inputs = ("x",)
+    launches_per_step = 1
+    l2_note = "input (256 MiB) larger than L2 (no flush needed)"
+
+    def describe(self):
+        return f"native_group_norm fwd, bf16 [{self.rows}, {self.C}, 32, 32], {self.G} groups, bf16 weight/bias, eps 1e-5"
+
+    def bytes_per_rows(self, rows):
+        n = rows * self.C * self.HW
+        fwd = 2 * n * 2 + 2 * self.C * 2 + 2 * rows * self.G * 2
+        return {"total": fwd, "group_norm_fwd": fwd, "group_norm_fwd_ring": fwd}
+
+    def make_cpu_state(self, rows):
+        g = torch.Generator().manual_seed(6001)
+        return {"x": torch.randn((rows, self.C, 32, 32), generator=g).to(torch.bfloat16),
+                "weight": (torch.randn(self.C, generator=g) * 0.02 + 1.0).to(torch.bfloat16),
+                "bias": (torch.randn(self.C, generator=g) * 0.02).to(torch.bfloat16)}
+
+    def make_device_state(self, rows, dev, seed):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        st = {"x": torch.randn((rows, self.C, 32, 32), generator=gen, device=dev).to(torch.bfloat16)}
+        cg = torch.Generator().manual_seed(6002)
+        st["weight"] = (torch.randn(self.C, generator=cg) * 0.02 + 1.0).to(torch.bfloat16).to(dev)
+        st["bias"] = (torch.randn(self.C, generator=cg) * 0.02).to(torch.bfloat16).to(dev)
+        st["y"] = torch.empty_like(st["x"])
+        st["mean"] = torch.empty((rows, self.G), device=dev, dtype=torch.bfloat16)
+        st["rstd"] = torch.empty((rows, self.G), device=dev, dtype=torch.bfloat16)
+        return st
+
+    def step(self, capi, st, world):
+        capi.native_group_norm(st["x"], st["weight"], st["bias"], st["x"].shape[0], self.C, self.HW, self.G, 1e-5,
+                               out=(st["y"], st["mean"], st["rstd"]))
+
+    def cpu_step(self, cpu):
+        return torch.ops.aten.native_group_norm(cpu["x"], cpu["weight"], cpu["bias"], cpu["x"].shape[0], self.C, self.HW,
+                                                self.G, 1e-5)
+
+    def aten_step(self, st, world):
+        return torch.ops.aten.native_group_norm(st["x"], st["weight"], st["bias"], st["x"].shape[0], self.C, self.HW,
+                                                self.G, 1e-5)
+
+    def _nbytes(self, rows, k):
+        return rows * self.C * self.HW * 2
+
+    def _out_bytes(self, rows):
+        return rows * self.C * self.HW * 2 + 2 * rows * self.G * 2
+
+
 def layer_norm_long_rows(base):
     """`base` is bench.Cfg4LayerNorm (handed in, so that this module never imports the script that imports it)."""
 
@@ -406,5 +458,5 @@ def layer_norm_long_rows(base):
     return LayerNormLongRows
 
 
-EXTRA = {"cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,
+EXTRA = {"gn": GroupNormFwd, "cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,
          "cfg5": Cfg5CrossEntropy, "cfg5f": Cfg5FusedTail}

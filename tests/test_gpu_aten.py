@@ -276,3 +276,65 @@ def test_cross_entropy_autograd_takes_the_fused_backward(dt, reduction):
     assert "FusedCrossEntropy" not in l4.grad_fn.name()
     torch.cuda.synchronize()
     assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_softmax_results_matrix_of_the_reference(dtype):
+    # test/xpu/test_nn_xpu.py:14056-14108 (test_softmax_results): non-even sizes, empty tensors and one-element shifts
+    # (sliced, non-contiguous, misaligned views) for softmax and log_softmax with dtype=float over dim 0 AND dim 1,
+    # forward, backward and double backward, against CPU
+    sizes = [(0, 10), (32, 20), (10, 0), (31, 20), (32, 21), (31, 23), (32, 1536), (31, 2048), (33, 2049), (16, 30576)]
+    shifts = [(0, 0), (1, 0), (0, 1), (1, 1)]
+    gen = torch.Generator().manual_seed(720)
+    for fn in (F.softmax, F.log_softmax):
+        for size in sizes:
+            for shift in shifts:
+                base = torch.rand(size, generator=gen).to(dtype)
+                if dtype == torch.float16:
+                    base = base / 100.0
+                gbase = torch.rand(size, generator=gen).to(dtype)
+                inp = base.to(DEV)[shift[0]:, shift[1]:].detach().requires_grad_(True)
+                ref_inp = base[shift[0]:, shift[1]:].clone().detach().requires_grad_(True)
+                for dim in (0, 1):
+                    out = fn(inp, dtype=torch.float, dim=dim)
+                    ref_out = fn(ref_inp, dtype=torch.float, dim=dim)
+                    go = gbase.to(DEV)[shift[0]:, shift[1]:]
+                    ref_go = gbase[shift[0]:, shift[1]:].clone()
+                    (gi,) = torch.autograd.grad(out, inp, grad_outputs=go, create_graph=True)
+                    (ref_gi,) = torch.autograd.grad(ref_out, ref_inp, grad_outputs=ref_go, create_graph=True)
+                    gi.sum().backward()
+                    ref_gi.sum().backward()
+                    # the reference compares with assertEqual's defaults (float32: rtol 1.3e-6, atol 1e-5); the stated
+                    # fp32 tolerance of this build is 1e-5 relative, with that same absolute floor
+                    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-3, atol=1e-4)
+                    torch.testing.assert_close(out.detach().cpu(), ref_out.detach(), **tol)
+                    torch.testing.assert_close(gi.detach().cpu(), ref_gi.detach(), **tol)
+                    torch.testing.assert_close(inp.grad.cpu(), ref_inp.grad, **tol)
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_softmax_backward_with_only_one_unaligned_operand(dtype):
+    # test_nn_xpu.py:17922-17999: 2048 elements (the shared-memory path), 2049 (not a whole number of vectors), and
+    # each operand alone off the 16-byte boundary: the vector kernels must step aside for exactly those
+    gen = torch.Generator().manual_seed(721)
+
+    def unaligned(t):
+        buf = torch.ones(t.numel() + 1, dtype=t.dtype, device=DEV)
+        view = buf[1:]
+        view.copy_(t)
+        assert view.data_ptr() % 16 != 0
+        return view
+
+    for numel in (2048, 2049):
+        out = torch.rand(numel, generator=gen).to(dtype)
+        go = (torch.rand(numel, generator=gen) / numel).to(dtype)
+        expect = torch._softmax_backward_data(go, out, 0, dtype)
+        cases = [(go.to(DEV), out.to(DEV)), (go.to(DEV), unaligned(out)), (unaligned(go), out.to(DEV))]
+        for g, o in cases:
+            got = torch._softmax_backward_data(g, o, 0, dtype)
+            if dtype == torch.float32:
+                assert ao.fp32_err(got, expect) <= 2.0
+            else:
+                assert ao.lowp_mismatch(got, expect)[0] == 0 or torch.allclose(got.float().cpu(), expect.float(), rtol=2e-3, atol=1e-7)

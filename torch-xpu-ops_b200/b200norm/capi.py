@@ -393,9 +393,10 @@ def _fused_rms_norm_backward(grad_out, input, normalized_shape, rstd, weight=Non
 
 
 # ---- sibling norms: group norm forward, batch norm statistics -------------------------------------------
-def native_group_norm(input, weight, bias, N, C, HxW, group, eps):
+def native_group_norm(input, weight, bias, N, C, HxW, group, eps, out=None):
     """aten::native_group_norm -> (Y, mean[N, group], rstd[N, group]); the statistics take the weights' dtype when the
-    input is 16-bit and the weights are float32 (upstream's mixed-type rule), else the input's."""
+    input is 16-bit and the weights are float32 (upstream's mixed-type rule), else the input's.
+    out: optional preallocated (Y, mean, rstd)."""
     _require_cuda(input, weight, bias)
     lib = load_library()
     if input.numel() != N * C * HxW:
@@ -412,9 +413,14 @@ def native_group_norm(input, weight, bias, N, C, HxW, group, eps):
     b = bias.contiguous() if bias is not None else None
     wdt = _weight_dtype(x, g, b)
     stat = torch.float32 if (wdt == F32 and (g is not None or b is not None)) else x.dtype
-    y = torch.empty_like(x)
-    mean = torch.empty((N, group), dtype=stat, device=x.device)
-    rstd = torch.empty((N, group), dtype=stat, device=x.device)
+    if out is not None:
+        y, mean, rstd = out
+        if mean.dtype != stat or rstd.dtype != stat or y.dtype != x.dtype:
+            raise RuntimeError("native_group_norm: out tensors have the wrong dtype")
+    else:
+        y = torch.empty_like(x)
+        mean = torch.empty((N, group), dtype=stat, device=x.device)
+        rstd = torch.empty((N, group), dtype=stat, device=x.device)
     if x.numel() > 0:
         with torch.cuda.device(x.device):
             _check(lib.b2n_group_norm_fwd(_ptr(x), _ptr(g), _ptr(b), _ptr(y), _ptr(mean), _ptr(rstd), N, C, HxW, group,

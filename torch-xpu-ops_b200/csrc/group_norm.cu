@@ -16,8 +16,12 @@
 // Replaces group_norm_kernel (src/ATen/native/xpu/sycl/GroupNormKernels.h:17-28; moments functors
 // GroupNormKernels.cpp:73-136, driver :365-499), batch_norm_stats_kernel and
 // batch_norm_update_stats_kernel (sycl/BatchNormKernels.h:19, :52; BatchNormKernels.cpp:992, :3864).
+#include <atomic>
+
 #include "common.cuh"
+#include "group_norm_ring.cuh"
 #include "launchers.h"
+#include "plan.h"
 
 namespace b2n {
 namespace {
@@ -231,11 +235,54 @@ batch_norm_stats_flat_kernel(const T* __restrict__ x, float* __restrict__ mean, 
   if (ty == 0 && c < C) bn_finish<RT>(mode, shift + mu_d, var, count, eps, momentum, c, mean, second, running_mean, running_var);
 }
 
+template <typename T, typename WT, typename ST, int GROUP>
+int group_norm_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, ST* mean, ST* rstd,
+                           int64_t rows, int64_t L, int64_t G, int64_t D, int64_t HxW, double eps, cudaStream_t st) {
+  constexpr int VPT = 16 / Pack16<T>::VEC;
+  auto kernel = group_norm_fwd_ring_kernel<T, WT, ST, GROUP, VPT>;
+  static std::atomic<uint64_t> done{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError());
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(done.load(std::memory_order_acquire) & bit)) {
+    if (int e = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, device_info().max_smem_optin)))
+      return e;
+    done.fetch_or(bit, std::memory_order_release);
+  }
+  ProfileScope prof("group_norm_fwd_ring", st);
+  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, x, gamma, beta, y, mean, rstd, rows, static_cast<int>(L),
+                    static_cast<int>(G), static_cast<int>(D), static_cast<int>(HxW), static_cast<float>(eps),
+                    p.stages | (p.lag << 8), p.rpg, device_status_ptr(), next_tile_counter());
+}
+
 template <typename T, typename WT, typename ST>
 int group_norm_launch(const void* x, const void* gamma, const void* beta, void* y, void* mean, void* rstd, int64_t N, int64_t C,
                       int64_t HxW, int64_t G, double eps, cudaStream_t st) {
   const int64_t rows = N * G, D = C / G, L = D * HxW;
   constexpr int V = 16 / sizeof(T);
+  if (forced_path() != B2N_PATH_GENERIC && is_aligned(x, 16) && is_aligned(y, 16) && HxW % V == 0 && rows < 0x7fffffffLL) {
+    // a group's row on the shared-memory ring, like a layer-norm row of the same length
+    const DeviceInfo& di = device_info();
+    const RingPlan p = plan_ring(rows, L, sizeof(T), 1, 16, persistent_ctas(di.sm_count), di.max_smem_optin, 65536);
+    if (p.ok) {
+      note_path("ring");
+      const T* xp = static_cast<const T*>(x);
+      const WT* g = static_cast<const WT*>(gamma);
+      const WT* b = static_cast<const WT*>(beta);
+      T* yp = static_cast<T*>(y);
+      ST* mp = static_cast<ST*>(mean);
+      ST* rp = static_cast<ST*>(rstd);
+      switch (p.group) {
+        case 32: return group_norm_ring_launch<T, WT, ST, 32>(p, xp, g, b, yp, mp, rp, rows, L, G, D, HxW, eps, st);
+        case 64: return group_norm_ring_launch<T, WT, ST, 64>(p, xp, g, b, yp, mp, rp, rows, L, G, D, HxW, eps, st);
+        case 128: return group_norm_ring_launch<T, WT, ST, 128>(p, xp, g, b, yp, mp, rp, rows, L, G, D, HxW, eps, st);
+        case 256: return group_norm_ring_launch<T, WT, ST, 256>(p, xp, g, b, yp, mp, rp, rows, L, G, D, HxW, eps, st);
+        default: return group_norm_ring_launch<T, WT, ST, 512>(p, xp, g, b, yp, mp, rp, rows, L, G, D, HxW, eps, st);
+      }
+    }
+  }
+  if (forced_path() == B2N_PATH_RING) return B2N_ERR_BAD_ARG;
+  note_path("generic");
   const bool vec = L % V == 0 && is_aligned(x, 16) && is_aligned(y, 16);
   const int threads = L >= 8192 ? 512 : (L >= 2048 ? 256 : 128);
   const int64_t cap = static_cast<int64_t>(device_info().sm_count) * (2048 / threads);
