@@ -314,3 +314,42 @@ def test_degenerate_lines_along_an_inner_dim(N, is_log):
     ok = ~torch.isnan(ref) & ~torch.isinf(ref)
     assert torch.equal(torch.isinf(y), torch.isinf(ref))
     assert torch.allclose(y[ok], ref[ok], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("is_log", [False, True])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(3, 150, 2048), (2, 300, 512), (1, 19, 200), (5, 64, 64), (2, 2, 4096), (1, 700, 136),
+                                   (4, 33, 1000)])
+def test_middle_dim_tiles(shape, dt, is_log, path):
+    # softmax over dim 1 of [outer, N, inner]: under PATH_AUTO the tensor-map TMA tiles (boxes of N x W elements; 300
+    # and 700 lines take two and three boxes of 256 rows; inner = 200, 136 and 1000 leave a ragged last tile that the
+    # copy fills with zeros on the way in and clips on the way out), under PATH_GENERIC the plain-load tile kernels;
+    # lines of -inf, a NaN and a +inf keep the CPU semantics
+    x = ao.randn(shape, 490 + shape[1], torch.float32, 0.0, 2.0)
+    x[0, :, 3] = float("-inf")
+    x[0, 1, 5] = float("nan")
+    x[-1, 0, 7] = float("inf")
+    x[0, shape[1] // 2:, 9] = float("-inf")
+    x = x.to(dt)
+    dy = ao.randn(shape, 491, dt)
+    fwd = capi._log_softmax if is_log else capi._softmax
+    bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+    with forced_path(path):
+        y_buf, y_chk = guarded_empty(shape, dt)
+        y = fwd(x.to(DEV), 1, False, out=y_buf)
+        dx_buf, dx_chk = guarded_empty(shape, dt)
+        dx = bwd(dy.to(DEV), y, 1, dt, out=dx_buf)
+    torch.cuda.synchronize()
+    y_chk(); dx_chk()
+    ry = ao.softmax_fwd(x, 1, is_log)
+    assert torch.equal(torch.isnan(y.cpu()), torch.isnan(ry))
+    check_out(y, ry, "y")
+    ok = ~torch.isnan(ry).any(dim=1, keepdim=True).expand_as(ry)  # lines that are NaN forward give NaN backward on both sides
+    rdx = ao.softmax_bwd(dy, y.cpu(), 1, is_log, dt)
+    assert torch.equal(torch.isnan(dx.cpu()), torch.isnan(rdx))
+    check_out(torch.where(ok, dx.cpu(), torch.zeros_like(rdx)), torch.where(ok, rdx, torch.zeros_like(rdx)), "dx", tol=2.0)
+    if not is_log:
+        ys = capi._safe_softmax(x.to(DEV), 1)
+        assert float(ys[0, :, 3].abs().max()) == 0.0  # the all -inf line: zeros instead of NaN
+    assert capi.device_status() == 0

@@ -11,6 +11,7 @@
 #include "softmax_ring.cuh"
 #include "softmax_cluster.cuh"
 #include "softmax_twopass.cuh"
+#include "softmax_tma.cuh"
 
 namespace b2n {
 
@@ -198,6 +199,156 @@ inline int spatial_tile_elems(int64_t N, int esize, int ntensors, int64_t inner,
   return tile;
 }
 
+// ---- non-last-dim softmax on tensor-map TMA tiles (softmax_tma.cuh) ----------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// cuTensorMapEncodeTiled, found through the runtime (the library does not link against the driver library)
+inline EncodeTiledFn tensor_map_encoder() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+template <typename T> constexpr CUtensorMapDataType tensor_map_dtype() {
+  if constexpr (std::is_same<T, float>::value) return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  else if constexpr (std::is_same<T, f16>::value) return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  else return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+}
+
+constexpr int kTmaNoFit = 1;  // (not a b2n_status) the shape is not for the TMA tile kernel: the caller takes another one
+
+// [outer, N, inner] of T as a rank-3 tensor map (inner fastest) with boxes of W x NB x 1 elements.
+template <typename T>
+bool encode_spatial_map(CUtensorMap* tm, const T* ptr, int64_t outer, int64_t N, int64_t inner, int W, int NB) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(outer)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(inner) * sizeof(T), static_cast<cuuint64_t>(N) * inner * sizeof(T)};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(W), static_cast<cuuint32_t>(NB), 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  return enc(tm, tensor_map_dtype<T>(), 3, const_cast<T*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The tile geometry of softmax_spatial_tma_kernel for lines of N elements `inner` apart.
+struct TmaTilePlan {
+  bool ok = false;
+  bool reg = false;  // forward with the thread's share of a line in registers
+  int W = 0;         // box width (elements), a multiple of 16 bytes, at most 256 elements
+  int NX = 0;        // boxes per tile along `inner`
+  int NB = 0;        // rows per box
+  int S = 0;         // stages
+  int segs = 0;      // threads per line
+};
+
+// Widest tile first: every thread busy (512 column groups x segments), at least three stages in shared memory
+// (two when nothing narrower than 128-byte runs would give three), not wider than the tensor, and narrower
+// while there are fewer tiles than two per SM.
+inline TmaTilePlan plan_tma_tile(int64_t outer, int64_t N, int64_t inner, int es, int nin, bool bwd, int64_t avail, int sms) {
+  TmaTilePlan p;
+  const int vec = 16 / es, cpt = es == 2 ? 2 : 1, line = 128 / es;  // elements per 16 bytes / per thread / per 128-byte line
+  p.NB = N <= 256 ? static_cast<int>(N) : 256;
+  const int64_t npad = (N + p.NB - 1) / p.NB * p.NB;
+  p.reg = !bwd && N <= 8 * kTmaRegRows;
+  int segs = p.reg ? static_cast<int>((N + kTmaRegRows - 1) / kTmaRegRows) : 1;
+  int64_t wt = static_cast<int64_t>(kTmaConsumers / segs) * cpt;
+  const int64_t row_bytes = npad * es * nin;  // shared memory per column of a tile
+  int64_t fit = avail / 3 / row_bytes;
+  if (fit < line) fit = avail / 2 / row_bytes;  // two stages rather than runs below 128 bytes
+  if (wt > fit) wt = fit;
+  if (wt > inner) wt = inner;
+  while (wt > 2 * line && outer * ((inner + wt - 1) / wt) < 2ll * sms) wt /= 2;
+  // Runs are whole 128-byte lines: every box then starts on a 128-byte boundary of shared memory, which the
+  // bulk-tensor copy requires of its shared-memory address, whatever N is.
+  wt = wt / line * line;
+  // boxes: the fewest that are at most 256 elements wide and whole lines
+  for (; wt >= line; wt -= line) {
+    const int nx = static_cast<int>((wt + 255) / 256);
+    if (wt % (static_cast<int64_t>(nx) * line) == 0) {
+      p.NX = nx;
+      p.W = static_cast<int>(wt / nx);
+      break;
+    }
+  }
+  if (p.W == 0) return p;  // runs below 128 bytes: the plain-load kernels take it
+  const int groups = p.W * p.NX / cpt;
+  if (!p.reg) {
+    segs = kTmaConsumers / groups;
+    if (segs > N) segs = static_cast<int>(N);
+    if (segs > 32) segs = 32;
+  }
+  p.segs = segs;
+  const int64_t s = avail / (row_bytes * p.W * p.NX);
+  if (s < 2) return p;
+  p.S = static_cast<int>(s > kTmaMaxStages ? kTmaMaxStages : s);
+  p.ok = groups * segs <= kTmaConsumers && segs >= 1;
+  return p;
+}
+
+struct TmaLaunchArgs {
+  const CUtensorMap *tm0, *tm1, *tmo;
+  int64_t outer;
+  int N;
+  int64_t inner;
+  const TmaTilePlan* p;
+  int safe;
+  unsigned grid;
+  size_t smem;
+  cudaStream_t st;
+};
+// One function per kernel instantiation: each carries its own "shared-memory limit raised" record.
+template <typename T, bool LOG, bool BWD, bool REG> int tma_tile_go(const TmaLaunchArgs& a) {
+  auto kernel = softmax_spatial_tma_kernel<T, LOG, BWD, REG>;
+  static std::atomic<uint64_t> done{0};
+  if (int e = set_smem_once_sm(kernel, done)) return e;
+  return launch_pdl(kernel, dim3(a.grid), dim3(kTmaThreads), a.smem, a.st, *a.tm0, *a.tm1, *a.tmo, a.outer, a.N, a.inner,
+                    a.p->W, a.p->NX, a.p->NB, a.p->S, a.p->segs, a.safe, device_status_ptr());
+}
+
+// in0 / in1 / out as in softmax_spatial_tma_kernel.  Returns kTmaNoFit when the shape does not suit the kernel
+// (rows or strides the tensor map cannot express, a tile that leaves no room for two stages, no encoder).
+template <typename T, bool LOG, bool BWD>
+int softmax_spatial_tma_launch(const T* in0, const T* in1, T* out, int64_t outer, int64_t N, int64_t inner, int safe,
+                               cudaStream_t st) {
+  constexpr int NIN = BWD ? 2 : 1;
+  constexpr int es = sizeof(T);
+  if (N < 2 || N > 65536 || outer > 0x7fffffffLL || inner > 0x7fffffffLL || (inner * es) % 16 != 0) return kTmaNoFit;
+  if ((N * inner * es) >= (1ll << 40)) return kTmaNoFit;  // the tensor map's stride limit
+  const DeviceInfo& di = device_info();
+  const int64_t avail = static_cast<int64_t>(di.max_smem_optin) - kTmaHeaderBytes;
+  const TmaTilePlan p = plan_tma_tile(outer, N, inner, es, NIN, BWD, avail, di.sm_count);
+  if (!p.ok || (static_cast<int64_t>(p.W) * es) % 128 != 0) return kTmaNoFit;
+  const int64_t npad = (N + p.NB - 1) / p.NB * p.NB;
+  const int WT = p.W * p.NX;
+  CUtensorMap tm0, tm1, tmo;
+  if (!encode_spatial_map(&tm0, in0, outer, N, inner, p.W, p.NB)) return kTmaNoFit;
+  if (!encode_spatial_map(&tm1, BWD ? in1 : in0, outer, N, inner, p.W, p.NB)) return kTmaNoFit;
+  if (!encode_spatial_map(&tmo, out, outer, N, inner, p.W, p.NB)) return kTmaNoFit;
+  const size_t smem = static_cast<size_t>(kTmaHeaderBytes) + static_cast<size_t>(p.S) * npad * WT * es * NIN;
+  const int64_t tiles = outer * ((inner + WT - 1) / WT);
+  const int ctas = persistent_ctas(di.sm_count);
+  int64_t grid = tiles < ctas ? tiles : ctas;
+  const int64_t waves = (tiles + grid - 1) / grid;
+  grid = (tiles + waves - 1) / waves;
+  if (getenv("B2N_DEBUG") != nullptr)
+    fprintf(stderr, "b2n: tma tile W=%d NX=%d NB=%d S=%d segs=%d reg=%d tiles=%lld grid=%lld smem=%zu\n", p.W, p.NX, p.NB, p.S,
+            p.segs, p.reg ? 1 : 0, static_cast<long long>(tiles), static_cast<long long>(grid), smem);
+  ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_tma" : "softmax_bwd_tma") : (LOG ? "log_softmax_fwd_tma" : "softmax_fwd_tma"), st);
+  const TmaLaunchArgs a{&tm0, &tm1, &tmo, outer, static_cast<int>(N), inner, &p, safe, static_cast<unsigned>(grid), smem, st};
+  if constexpr (!BWD) {
+    if (p.reg) return tma_tile_go<T, LOG, false, true>(a);
+  }
+  return tma_tile_go<T, LOG, BWD, false>(a);
+}
+
 template <typename TI, typename TO, bool LOG>
 int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_t inner, cudaStream_t st) {
   const TI* x = static_cast<const TI*>(x_);
@@ -254,6 +405,11 @@ int softmax_fwd_typed(const void* x_, void* y_, int64_t outer, int64_t N, int64_
   if constexpr (std::is_same<TI, TO>::value && !std::is_same<TI, double>::value) {
     constexpr int VEC = 16 / sizeof(TI);
     const DeviceInfo& di = device_info();
+    if (inner % VEC == 0 && inner >= 64 && is_aligned(x, 16) && is_aligned(y, 16) && ring_tuning().tile_kb == 0 &&
+        forced == B2N_PATH_AUTO) {  // (a pinned generic path keeps to the plain-load tile kernels below)
+      const int e = softmax_spatial_tma_launch<TI, LOG, false>(x, static_cast<const TI*>(nullptr), y, outer, N, inner, safe, st);
+      if (e != kTmaNoFit) return e;
+    }
     const int tile = spatial_tile_elems(N, sizeof(TI), 1, inner, di.max_smem_optin);
     if (tile > 0 && inner % VEC == 0 && inner >= 64 && is_aligned(x, 16) && is_aligned(y, 16) && N <= (1 << 20)) {
       auto kernel = softmax_fwd_tile_kernel<TI, LOG>;
@@ -352,6 +508,11 @@ int softmax_bwd_typed(const void* dy_, const void* y_, void* dx_, int64_t outer,
   if constexpr (std::is_same<TG, TO>::value && !std::is_same<TG, double>::value) {
     constexpr int VEC = 16 / sizeof(TG);
     const DeviceInfo& di = device_info();
+    if (inner % VEC == 0 && inner >= 64 && is_aligned(dy, 16) && is_aligned(y, 16) && is_aligned(dx, 16) &&
+        ring_tuning().tile_kb == 0 && forced == B2N_PATH_AUTO) {
+      const int e = softmax_spatial_tma_launch<TG, LOG, true>(dy, y, dx, outer, N, inner, 0, st);
+      if (e != kTmaNoFit) return e;
+    }
     const int tile = spatial_tile_elems(N, sizeof(TG), 2, inner, di.max_smem_optin);
     if (tile > 0 && inner % VEC == 0 && inner >= 64 && is_aligned(dy, 16) && is_aligned(y, 16) && is_aligned(dx, 16) &&
         N <= (1 << 20)) {
