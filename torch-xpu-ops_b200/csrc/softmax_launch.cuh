@@ -289,7 +289,8 @@ inline TmaTilePlan plan_tma_tile(int64_t outer, int64_t N, int64_t inner, int es
   const int64_t s = avail / (row_bytes * p.W * p.NX);
   if (s < 2) return p;
   p.S = static_cast<int>(s > kTmaMaxStages ? kTmaMaxStages : s);
-  p.ok = groups * segs <= kTmaConsumers && segs >= 1;
+  // the kernel's teams: 32 adjacent column groups x segs warps on one named barrier each (ids 1..15)
+  p.ok = groups * segs <= kTmaConsumers && segs >= 1 && groups % 32 == 0 && (segs == 1 || groups / 32 <= 15);
   return p;
 }
 

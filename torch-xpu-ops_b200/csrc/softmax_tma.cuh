@@ -92,7 +92,8 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
   constexpr int CPT = sizeof(T) == 2 ? 2 : 1;  // columns a thread handles with one shared-memory access
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   TmaTileShared* sh = reinterpret_cast<TmaTileShared*>(smem_raw);
-  float4* part = reinterpret_cast<float4*>(smem_raw + 1024);
+  float4* part = reinterpret_cast<float4*>(smem_raw + 1024);  // one slot per consumer thread ...
+  float2* part2 = reinterpret_cast<float2*>(part);            // ... as two halves
   unsigned char* stages = smem_raw + kTmaHeaderBytes;
 
   const int tid = threadIdx.x;
@@ -139,11 +140,10 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
             if (BWD) tma_load_3d(dst + tile_bytes + off, &tm_in1, x0 + bx * W, b * NB, o, &sh->full[s]);
           }
       };
-      int issued = 0, ls = 0;
+      int issued = 0;
       int64_t lt = first;
       for (; issued < S && issued < my_tiles; ++issued) {
-        load(ls, lt);
-        if (++ls == S) ls = 0;
+        load(issued, lt);
         lt += gridDim.x;
       }
       int j = 0, s = 0;
@@ -158,10 +158,12 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
           for (int b = 0; b < nbox; ++b)
             tma_store_3d(&tm_out, x0 + bx * W, b * NB, o, src + static_cast<size_t>(bx) * xbox_bytes + static_cast<size_t>(b) * box_bytes);
         bulk_commit();
-        if (j >= 1 && issued < my_tiles) {  // the store of tile j - 1 has read its stage: the next load goes there
-          bulk_wait_read<1>();
-          load(ls, lt);
-          if (++ls == S) ls = 0;
+        if (issued < my_tiles) {
+          // The stage is free again as soon as the store has READ it (well before it has reached memory), and this
+          // thread has nothing else to do until the consumers finish the next tile: wait for that and refill the
+          // stage at once, so that S - 1 tiles are loaded or on their way while one is worked on.
+          bulk_wait_read<0>();
+          load(s, lt);
           lt += gridDim.x;
           ++issued;
         }
@@ -187,6 +189,10 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
   const int gidx = tid % groups, sg = tid / groups;
   // where this thread's columns start inside a tensor's tile: box gidx / gpb, then column (gidx % gpb) * CPT of it
   const uint32_t col_off = static_cast<uint32_t>(gidx / gpb) * xbox_bytes + static_cast<uint32_t>(gidx % gpb) * CPT * sizeof(T);
+  // The threads that share lines — 32 adjacent column groups x segs segments: segs whole warps — are a TEAM with a
+  // named barrier of its own.  Nothing ever makes all consumers meet, so the teams drift apart and one team's
+  // exp phase (special-function unit) overlaps another's load or store phase (shared-memory pipe), also across tiles.
+  const int team_bar = 1 + (gidx >> 5), team_threads = 32 * segs;  // groups is a multiple of 32; at most 8 teams when segs > 1
   const uint32_t row_pitch = static_cast<uint32_t>(W) * sizeof(T), seg_pitch = row_pitch * segs;
   const int my_rows = sg < N ? (N - sg + segs - 1) / segs : 0;  // rows sg, sg + segs, ... below N
   int s = 0;
@@ -197,69 +203,93 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
     T* col = reinterpret_cast<T*>(t0 + col_off);
     if constexpr (!BWD && REG) {
       // ---- forward, the thread's share of the line in registers: rows sg, sg + segs, ... ----
+      // Rows go in blocks of four: a block past the thread's share is skipped by a branch the whole warp takes
+      // (predicated-off instructions would still take issue slots); 16-bit storage uses packed f32x2 arithmetic.
       float2 v[kTmaRegRows];
       const uint32_t a0 = smem_u32(t0) + col_off + static_cast<uint32_t>(sg) * row_pitch;
       float2 mx = make_float2(ninf, ninf), sum = make_float2(0.0f, 0.0f);
       if (active) {
 #pragma unroll
-        for (int r = 0; r < kTmaRegRows; ++r) {
-          if (r < my_rows) {
-            v[r] = word_to_pair<T>(lds_b32(a0 + r * seg_pitch));
-            mx.x = fmaxf(mx.x, v[r].x);
-            mx.y = fmaxf(mx.y, v[r].y);
+        for (int b4 = 0; b4 < kTmaRegRows; b4 += 4) {
+          if (b4 < my_rows) {
+#pragma unroll
+            for (int r = b4; r < b4 + 4; ++r) {
+              if (r < my_rows) {
+                v[r] = word_to_pair<T>(lds_b32(a0 + r * seg_pitch));
+                mx.x = fmaxf(mx.x, v[r].x);
+                mx.y = fmaxf(mx.y, v[r].y);
+              }
+            }
           }
         }
-        if (segs > 1) part[tid] = make_float4(mx.x, mx.y, 0.0f, 0.0f);
       }
-      if (segs > 1) {  // (segs is the same for every thread)
-        named_bar_sync(1, kTmaConsumers);
-        if (active)
-          for (int q = 0; q < segs; ++q) {
-            const float4 pk = part[q * groups + gidx];
-            mx.x = fmaxf(mx.x, pk.x);
-            mx.y = fmaxf(mx.y, pk.y);
-          }
+      // Two barriers per tile, both the team's own.  A thread's slot holds its maxima in one half and its sums in
+      // the other: the maxima of the next tile are written after this tile's second barrier, which every team
+      // member reaches after reading this tile's maxima, and the sums after the next tile's first barrier.
+      if (active && segs > 1) {  // (whole warps are active or not)
+        part2[2 * tid] = mx;
+        named_bar_sync(team_bar, team_threads);
+        for (int q = 0; q < segs; ++q) {
+          const float2 pk = part2[2 * (q * groups + gidx)];
+          mx.x = fmaxf(mx.x, pk.x);
+          mx.y = fmaxf(mx.y, pk.y);
+        }
       }
       if (active) {
         // the line's maximum is known: ONE exp per element serves both the sum and the output
         const float base0 = (mx.x == ninf) ? 0.0f : mx.x, base1 = (mx.y == ninf) ? 0.0f : mx.y;  // all -inf: exp(-inf - 0) = 0
+        const float2 nbase = make_float2(-base0, -base1), l2e = make_float2(kLog2e, kLog2e);
 #pragma unroll
-        for (int r = 0; r < kTmaRegRows; ++r) {
-          if (r < my_rows) {
-            const float2 e = make_float2(exp_for<T>(v[r].x - base0), CPT == 2 ? exp_for<T>(v[r].y - base1) : 0.0f);
-            sum.x += e.x;  // a NaN entry makes the sum NaN (the maximum ignored it); +inf gives exp(inf - inf) = NaN
-            sum.y += e.y;
-            if (!LOG) v[r] = e;
+        for (int b4 = 0; b4 < kTmaRegRows; b4 += 4) {
+          if (b4 < my_rows) {
+#pragma unroll
+            for (int r = b4; r < b4 + 4; ++r) {
+              if (r < my_rows) {
+                // a NaN entry makes the sum NaN (the maximum ignored it); +inf gives exp(inf - inf) = NaN
+                float2 e;
+                if constexpr (CPT == 2) {
+                  const float2 t = mul2(add2(v[r], nbase), l2e);  // exp_for<T> on both columns
+                  e = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+                  sum = add2(sum, e);
+                } else {
+                  e = make_float2(exp_for<T>(v[r].x - base0), 0.0f);
+                  sum.x += e.x;
+                }
+                if (!LOG) v[r] = e;
+              }
+            }
           }
         }
       }
-      if (segs > 1) {
-        named_bar_sync(1, kTmaConsumers);  // everyone has read the maxima
-        if (active) part[tid] = make_float4(sum.x, sum.y, 0.0f, 0.0f);
-        named_bar_sync(1, kTmaConsumers);
-        if (active) {
-          sum = make_float2(0.0f, 0.0f);
-          for (int q = 0; q < segs; ++q) {  // segment order: every thread of the line gets the same bits
-            const float4 pk = part[q * groups + gidx];
-            sum.x += pk.x;
-            sum.y += pk.y;
-          }
+      if (active && segs > 1) {
+        part2[2 * tid + 1] = sum;
+        named_bar_sync(team_bar, team_threads);
+        sum = make_float2(0.0f, 0.0f);
+        for (int q = 0; q < segs; ++q) {  // segment order: every thread of the line gets the same bits
+          const float2 pk = part2[2 * (q * groups + gidx) + 1];
+          sum.x += pk.x;
+          sum.y += pk.y;
         }
       }
       if (active) {
-        const float2 lg = make_float2(LOG ? logf(sum.x) : 0.0f, LOG ? logf(sum.y) : 0.0f);
+        const float2 nlg = make_float2(LOG ? -logf(sum.x) : 0.0f, LOG ? -logf(sum.y) : 0.0f), nmx = make_float2(-mx.x, -mx.y);
         const float2 inv = make_float2(LOG ? 0.0f : 1.0f / sum.x, LOG ? 0.0f : 1.0f / sum.y);
         const bool z0 = safe && mx.x == ninf && !(sum.x != sum.x), z1 = safe && mx.y == ninf && !(sum.y != sum.y);
 #pragma unroll
-        for (int r = 0; r < kTmaRegRows; ++r) {
-          if (r < my_rows) {
-            float2 e;
-            if constexpr (LOG) e = make_float2((v[r].x - mx.x) - lg.x, (v[r].y - mx.y) - lg.y);  // as the row kernels round it
-            else if constexpr (sizeof(T) == 4) e = make_float2(v[r].x / sum.x, 0.0f);
-            else e = make_float2(v[r].x * inv.x, v[r].y * inv.y);
-            if (z0) e.x = 0.0f;
-            if (z1) e.y = 0.0f;
-            sts_b32(a0 + r * seg_pitch, pair_to_word<T>(e));
+        for (int b4 = 0; b4 < kTmaRegRows; b4 += 4) {
+          if (b4 < my_rows) {
+#pragma unroll
+            for (int r = b4; r < b4 + 4; ++r) {
+              if (r < my_rows) {
+                float2 e;
+                if constexpr (LOG) e = add2(add2(v[r], nmx), nlg);  // (x - max) - log(sum), as the row kernels round it
+                else if constexpr (sizeof(T) == 4) e = make_float2(v[r].x / sum.x, 0.0f);
+                else e = mul2(v[r], inv);
+                if (z0) e.x = 0.0f;
+                if (z1) e.y = 0.0f;
+                sts_b32(a0 + r * seg_pitch, pair_to_word<T>(e));
+              }
+            }
           }
         }
       }
@@ -291,7 +321,9 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
         }
         part[tid] = make_float4(a.m, a.s, b.m, b.s);
       }
-      named_bar_sync(1, kTmaConsumers);
+      if constexpr (!BWD && !REG) {
+      if (active && segs > 1) named_bar_sync(team_bar, team_threads);
+    }
       if (active) {
         const float4 p0 = part[gidx];
         a.m = p0.x; a.s = p0.y; b.m = p0.z; b.s = p0.w;
@@ -321,56 +353,57 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
         }
       }
     } else {
-      const T* ycol = reinterpret_cast<const T*>(t0 + tile_bytes + col_off);
+      // rows sg, sg + segs, ... of the thread's column pair, dy at a0 and y one tile further
+      const uint32_t a0 = smem_u32(t0) + col_off + static_cast<uint32_t>(sg) * row_pitch, y0 = a0 + tile_bytes;
       float2 sum = make_float2(0.0f, 0.0f);
       if (active) {
+        uint32_t o = 0;
 #pragma unroll 4
-        for (int j = sg; j < N; j += segs) {
-          const size_t l = static_cast<size_t>(j) * W;
-          if constexpr (CPT == 2) {
-            const float2 d = ld_pair(col + l);
-            if constexpr (LOG) {
-              sum.x += d.x;
-              sum.y += d.y;
-            } else {
-              const float2 yy = ld_pair(ycol + l);
-              sum.x = fmaf(d.x, yy.x, sum.x);
-              sum.y = fmaf(d.y, yy.y, sum.y);
-            }
+        for (int r = 0; r < my_rows; ++r, o += seg_pitch) {
+          const float2 d = word_to_pair<T>(lds_b32(a0 + o));
+          if constexpr (LOG) {
+            sum.x += d.x;
+            sum.y += d.y;
           } else {
-            const float d = to_acc<float>(col[l]);
-            sum.x += LOG ? d : d * to_acc<float>(ycol[l]);
+            const float2 yy = word_to_pair<T>(lds_b32(y0 + o));
+            if constexpr (CPT == 2) {
+              sum = fma2(d, yy, sum);
+            } else {
+              sum.x = fmaf(d.x, yy.x, sum.x);
+            }
           }
         }
-        part[tid] = make_float4(sum.x, sum.y, 0.0f, 0.0f);
       }
-      named_bar_sync(1, kTmaConsumers);
-      if (active) {
-        const float4 p0 = part[gidx];
-        sum = make_float2(p0.x, p0.y);
-        for (int q = 1; q < segs; ++q) {
-          const float4 pk = part[q * groups + gidx];
+      // One barrier per tile, the team's own: the halves of a thread's slot alternate from tile to tile, and a half
+      // is written again only after the barrier of the tile in between, which every team member reaches after it
+      // has read that half.
+      if (active && segs > 1) {  // (whole warps are active or not)
+        part2[2 * tid + (k & 1)] = sum;
+        named_bar_sync(team_bar, team_threads);
+        sum = make_float2(0.0f, 0.0f);
+        for (int q = 0; q < segs; ++q) {  // segment order: every thread of the line gets the same bits
+          const float2 pk = part2[2 * (q * groups + gidx) + (k & 1)];
           sum.x += pk.x;
           sum.y += pk.y;
         }
+      }
+      if (active) {
+        const float2 nsum = make_float2(-sum.x, -sum.y);
+        uint32_t o = 0;
 #pragma unroll 4
-        for (int j = sg; j < N; j += segs) {
-          const size_t l = static_cast<size_t>(j) * W;
-          if constexpr (CPT == 2) {
-            const float2 d = ld_pair(col + l), yy = ld_pair(ycol + l);
-            const float2 r = LOG ? make_float2(d.x - exp_for<T>(yy.x) * sum.x, d.y - exp_for<T>(yy.y) * sum.y)
-                                 : make_float2(yy.x * (d.x - sum.x), yy.y * (d.y - sum.y));
-            st_pair(col + l, r);
-          } else {
-            const float d = to_acc<float>(col[l]), yy = to_acc<float>(ycol[l]);
-            col[l] = from_acc<T>(LOG ? d - exp_for<T>(yy) * sum.x : yy * (d - sum.x));
-          }
+        for (int r = 0; r < my_rows; ++r, o += seg_pitch) {
+          const float2 d = word_to_pair<T>(lds_b32(a0 + o)), yy = word_to_pair<T>(lds_b32(y0 + o));
+          const float2 res = LOG ? make_float2(d.x - exp_for<T>(yy.x) * sum.x, d.y - exp_for<T>(yy.y) * sum.y)
+                                 : mul2(yy, add2(d, nsum));  // y * (dy - sum)
+          sts_b32(a0 + o, pair_to_word<T>(res));
         }
       }
     }
-    // the partial results of this tile have been read by everyone before the next tile overwrites them: the
-    // barrier at the next tile's hand-over is one full tile of work away, but a thread may race ahead — meet again
-    named_bar_sync(1, kTmaConsumers);
+    // (the three-walk forward keeps all four partial results in one slot: its team meets once more before the next
+    // tile overwrites them)
+    if constexpr (!BWD && !REG) {
+      if (active && segs > 1) named_bar_sync(team_bar, team_threads);
+    }
     fence_async_smem();
     __syncwarp();
     if ((tid & 31) == 0) mbar_arrive(&sh->done[s]);
