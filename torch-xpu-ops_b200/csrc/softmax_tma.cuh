@@ -53,6 +53,16 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, int x, int y
                : "memory");
 }
 
+// 2^v with results below 2^-126 flushed to zero: one special-function instruction, where the variant that keeps
+// subnormal results costs a compare and two conditional multiplies more.  Used for 16-bit storage only, on
+// exp(x - max) <= 1: what is flushed is below 1.2e-38, far under one unit in the last place of anything a 16-bit
+// result can be compared at.
+__device__ __forceinline__ float ex2_ftz(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
 // One 32-bit word of shared memory by its 32-bit shared-space address (address arithmetic stays in 32 bits).
 __device__ __forceinline__ uint32_t lds_b32(uint32_t a) {
   uint32_t v;
@@ -248,8 +258,8 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
                 // a NaN entry makes the sum NaN (the maximum ignored it); +inf gives exp(inf - inf) = NaN
                 float2 e;
                 if constexpr (CPT == 2) {
-                  const float2 t = mul2(add2(v[r], nbase), l2e);  // exp_for<T> on both columns
-                  e = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+                  const float2 t = mul2(add2(v[r], nbase), l2e);  // exp_for<T> on both columns ...
+                  e = make_float2(ex2_ftz(t.x), ex2_ftz(t.y));     // ... but below 2^-126 the result is 0, see ex2_ftz
                   sum = add2(sum, e);
                 } else {
                   e = make_float2(exp_for<T>(v[r].x - base0), 0.0f);
@@ -273,8 +283,9 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
       }
       if (active) {
         const float2 nlg = make_float2(LOG ? -logf(sum.x) : 0.0f, LOG ? -logf(sum.y) : 0.0f), nmx = make_float2(-mx.x, -mx.y);
-        const float2 inv = make_float2(LOG ? 0.0f : 1.0f / sum.x, LOG ? 0.0f : 1.0f / sum.y);
-        const bool z0 = safe && mx.x == ninf && !(sum.x != sum.x), z1 = safe && mx.y == ninf && !(sum.y != sum.y);
+        // safe softmax: a line of -inf (and no NaN) gives zeros — exp(x - max) is 0 there, so a factor of 0 does it
+        const bool z0 = !LOG && safe && mx.x == ninf && !(sum.x != sum.x), z1 = !LOG && safe && mx.y == ninf && !(sum.y != sum.y);
+        const float2 inv = make_float2(LOG || z0 ? 0.0f : 1.0f / sum.x, LOG || z1 ? 0.0f : 1.0f / sum.y);
 #pragma unroll
         for (int b4 = 0; b4 < kTmaRegRows; b4 += 4) {
           if (b4 < my_rows) {
@@ -283,10 +294,8 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
               if (r < my_rows) {
                 float2 e;
                 if constexpr (LOG) e = add2(add2(v[r], nmx), nlg);  // (x - max) - log(sum), as the row kernels round it
-                else if constexpr (sizeof(T) == 4) e = make_float2(v[r].x / sum.x, 0.0f);
+                else if constexpr (sizeof(T) == 4) e = make_float2(z0 ? 0.0f : v[r].x / sum.x, 0.0f);
                 else e = mul2(v[r], inv);
-                if (z0) e.x = 0.0f;
-                if (z1) e.y = 0.0f;
                 sts_b32(a0 + r * seg_pitch, pair_to_word<T>(e));
               }
             }
