@@ -118,9 +118,13 @@ __device__ __forceinline__ void record_status(int* status, int code) { atomicCAS
 
 // 2^v by the hardware approximation (relative error ~2^-22: invisible after rounding to 8 or 11 bits of
 // mantissa, which is where the kernels for 16-bit storage use it).
+// 2^v on the special-function unit, results below 2^-126 flushed to zero: ONE instruction.  (Without .ftz the
+// compiler wraps it in a compare and two conditional multiplies to keep subnormal results — four issue slots per
+// exp, which the softmax kernels spend per element.)  Only kernels with 16-bit storage use it, on arguments <= 0:
+// what is flushed is below 1.2e-38, far under one unit in the last place of anything such a result is compared at.
 __device__ __forceinline__ float ex2_approx(float v) {
   float r;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(v));  // no .ftz: subnormal results are kept
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
   return r;
 }
 constexpr float kLog2e = 1.4426950408889634f;

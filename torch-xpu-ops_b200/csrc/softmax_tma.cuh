@@ -53,16 +53,6 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, int x, int y
                : "memory");
 }
 
-// 2^v with results below 2^-126 flushed to zero: one special-function instruction, where the variant that keeps
-// subnormal results costs a compare and two conditional multiplies more.  Used for 16-bit storage only, on
-// exp(x - max) <= 1: what is flushed is below 1.2e-38, far under one unit in the last place of anything a 16-bit
-// result can be compared at.
-__device__ __forceinline__ float ex2_ftz(float v) {
-  float r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
-  return r;
-}
-
 // One 32-bit word of shared memory by its 32-bit shared-space address (address arithmetic stays in 32 bits).
 __device__ __forceinline__ uint32_t lds_b32(uint32_t a) {
   uint32_t v;
@@ -259,7 +249,7 @@ softmax_spatial_tma_kernel(const __grid_constant__ CUtensorMap tm_in0, const __g
                 float2 e;
                 if constexpr (CPT == 2) {
                   const float2 t = mul2(add2(v[r], nbase), l2e);  // exp_for<T> on both columns ...
-                  e = make_float2(ex2_ftz(t.x), ex2_ftz(t.y));     // ... but below 2^-126 the result is 0, see ex2_ftz
+                  e = make_float2(ex2_approx(t.x), ex2_approx(t.y));
                   sum = add2(sum, e);
                 } else {
                   e = make_float2(exp_for<T>(v[r].x - base0), 0.0f);
