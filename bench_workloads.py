@@ -446,6 +446,64 @@ class GroupNormFwd(_Simple):
         return rows * self.C * self.HW * 2 + 2 * rows * self.G * 2
 
 
+class SpatialSoftmax(_Simple):
+    """Not a BASELINE config: _softmax + _softmax_backward_data over dim 1 of bf16 [16, C, 512, 512] (the reference's
+    spatial kernels, sycl/SoftMaxKernels.cpp:735-950 and :1395-1564; the shape of a segmentation head with C classes).
+    `rows` are samples."""
+    name, rows, C, HW, cpu_sample_rows = "sm_c64", 16, 64, 512 * 512, 1
+    e2e_inputs = ("s", "g")
+    collective = "none (samples are independent)"
+    l2_note = "inputs (512 MiB per tensor) larger than L2 (no flush needed)"
+
+    def describe(self):
+        return f"_softmax + _softmax_backward_data over dim 1, bf16 [{self.rows}, {self.C}, 512, 512]"
+
+    def bytes_per_rows(self, rows):
+        n = rows * self.C * self.HW * 2
+        return {"total": 5 * n, "softmax_fwd_tma": 2 * n, "softmax_bwd_tma": 3 * n}
+
+    def make_cpu_state(self, rows):
+        g = torch.Generator().manual_seed(7001)
+        return {"s": torch.randn((rows, self.C, 512, 512), generator=g).to(torch.bfloat16),
+                "g": torch.randn((rows, self.C, 512, 512), generator=g).to(torch.bfloat16)}
+
+    def make_device_state(self, rows, dev, seed):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        st = {"s": torch.randn((rows, self.C, 512, 512), generator=gen, device=dev).to(torch.bfloat16),
+              "g": torch.randn((rows, self.C, 512, 512), generator=gen, device=dev).to(torch.bfloat16)}
+        st["p"] = torch.empty_like(st["s"])
+        st["dx"] = torch.empty_like(st["s"])
+        return st
+
+    def step(self, capi, st, world):
+        capi._softmax(st["s"], 1, False, out=st["p"])
+        capi._softmax_backward_data(st["g"], st["p"], 1, torch.bfloat16, out=st["dx"])
+
+    def cpu_step(self, cpu):
+        p = torch.ops.aten._softmax(cpu["s"], 1, False)
+        return torch.ops.aten._softmax_backward_data(cpu["g"], p, 1, torch.bfloat16)
+
+    def aten_step(self, st, world):
+        p = torch.ops.aten._softmax(st["s"], 1, False)
+        return p, torch.ops.aten._softmax_backward_data(st["g"], p, 1, torch.bfloat16)
+
+    def _nbytes(self, rows, k):
+        return rows * self.C * self.HW * 2
+
+    def _out_bytes(self, rows):
+        return 2 * rows * self.C * self.HW * 2
+
+
+class SpatialSoftmax19(SpatialSoftmax):
+    name, C = "sm_c19", 19
+    l2_note = "inputs (152 MiB per tensor) larger than L2 (no flush needed)"
+
+
+class SpatialSoftmax150(SpatialSoftmax):
+    name, C = "sm_c150", 150
+    l2_note = "inputs (1200 MiB per tensor) larger than L2 (no flush needed)"
+
+
 def layer_norm_long_rows(base):
     """`base` is bench.Cfg4LayerNorm (handed in, so that this module never imports the script that imports it)."""
 
@@ -458,5 +516,5 @@ def layer_norm_long_rows(base):
     return LayerNormLongRows
 
 
-EXTRA = {"gn": GroupNormFwd, "cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,
+EXTRA = {"sm_c19": SpatialSoftmax19, "sm_c64": SpatialSoftmax, "sm_c150": SpatialSoftmax150, "gn": GroupNormFwd, "cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,
          "cfg5": Cfg5CrossEntropy, "cfg5f": Cfg5FusedTail}
