@@ -253,6 +253,17 @@ int b2n_batch_norm_stats(const void* x, float* mean, float* second, void* runnin
 int b2n_softmax_fwd(const void* x, void* y, int64_t outer, int64_t N, int64_t inner, int in_dtype,
                     int out_dtype, int is_log, void* stream);
 
+/* Host-only query, no device needed: the shared-memory tile geometry the library uses for softmax over a dim
+ * that is NOT the last ([outer, N, inner], inner > 1) on tensor-map TMA tiles, for a GPU with `sm_count` SMs and
+ * `max_smem_bytes` of opt-in shared memory per CTA.  out[8] = {fits (0: another kernel family takes the shape),
+ * box width W in elements, boxes per tile, rows per box, stages, threads per line, forward-in-registers flag,
+ * dynamic shared memory in bytes}.  Invariants a caller (and the tests) can rely on when fits == 1:
+ * W * elem_size is a multiple of 128 bytes and W <= 256; (W * boxes / columns-per-thread) * threads-per-line <= 512;
+ * at least two stages; the shared memory fits.  The reference has no counterpart: its spatial kernels
+ * (sycl/SoftMaxKernels.cpp:735-950) pick their work-group shape inside the launcher. */
+int b2n_softmax_tile_plan(int64_t outer, int64_t N, int64_t inner, int elem_size, int backward, int sm_count,
+                          int64_t max_smem_bytes, int* out);
+
 /* dy: grad_dtype; y (forward output): grad_dtype; dx: dx_dtype (== grad_dtype, or a 16-bit type
  * with grad_dtype == B2N_F32 for the half_to_float backward).
  * softmax: dx = y*(dy - sum(y*dy)); log-softmax: dx = dy - exp(y)*sum(dy).

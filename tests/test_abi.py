@@ -102,3 +102,44 @@ def test_entry_points_reject_bad_arguments_before_touching_the_device():
     assert lib.b2n_masked_softmax_fwd(None, None, None, 2, 4, 0, 1, 0, None) == bad  # row_div < 1
     assert lib.b2n_cross_entropy_bwd(None, None, None, None, None, None, 3, 5, 7, -100, 0, 0, None) == bad  # reduction
     assert lib.b2n_cross_entropy_bwd(None, None, None, None, None, None, 0, 5, 1, -100, 0, 0, None) == 0
+
+
+def test_spatial_softmax_tile_plans_keep_their_invariants():
+    # The geometry of the tensor-map TMA tile kernels, computed on the host: a box row that is not a whole number
+    # of 128-byte lines would put a bulk-tensor copy on a misaligned shared-memory address, and a team of threads
+    # that is not whole warps would leave a named barrier short of arrivals -- neither may ever be planned.
+    lib = b200norm.load_library()
+    out = (ctypes.c_int * 8)()
+    header, consumers, reg_rows = 1024 + 512 * 16, 512, 32
+    seen_fit = seen_reg = seen_multibox = seen_nofit = 0
+    for esize in (2, 4):
+        cpt = 2 if esize == 2 else 1
+        for backward in (0, 1):
+            for n in (2, 3, 19, 31, 32, 33, 64, 100, 150, 255, 256, 257, 300, 700, 1000, 4096, 33000, 65536):
+                for inner in (8, 64, 72, 136, 200, 512, 1000, 4096, 262144):
+                    for outer in (1, 3, 16, 4096):
+                        if (inner * esize) % 16:
+                            continue
+                        for smem in (232448, 101376):
+                            rc = lib.b2n_softmax_tile_plan(outer, n, inner, esize, backward, 148, smem, out)
+                            assert rc == 0
+                            fits, w, nx, nb, stages, segs, reg, smem_used = list(out)
+                            if not fits:
+                                seen_nofit += 1
+                                continue
+                            seen_fit += 1
+                            seen_reg += reg
+                            seen_multibox += nx > 1
+                            assert (w * esize) % 128 == 0 and 0 < w <= 256 and nx >= 1
+                            assert nb == min(n, 256)
+                            groups = w * nx // cpt
+                            assert groups % 32 == 0 and groups * segs <= consumers and segs >= 1
+                            assert segs == 1 or groups // 32 <= 15          # named barriers 1..15
+                            assert 2 <= stages <= 4 and header < smem_used <= smem
+                            npad = -(-n // nb) * nb
+                            assert smem_used == header + stages * npad * w * nx * esize * (2 if backward else 1)
+                            if reg:
+                                assert not backward and -(-n // segs) <= reg_rows
+    assert seen_fit > 200 and seen_reg > 50 and seen_multibox > 20 and seen_nofit > 50
+    assert lib.b2n_softmax_tile_plan(1, 4, 64, 3, 0, 148, 232448, out) != 0        # element size
+    assert lib.b2n_softmax_tile_plan(1, 4, 64, 2, 0, 148, 232448, None) != 0       # no result array

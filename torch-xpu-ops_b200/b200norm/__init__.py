@@ -87,6 +87,7 @@ def load_library() -> ctypes.CDLL:
         "b2n_batch_norm_stats": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, dbl, dbl, i32, i32, i32, vp]),
         "b2n_softmax_fwd": (i32, [vp, vp, i64, i64, i64, i32, i32, i32, vp]),
         "b2n_softmax_bwd": (i32, [vp, vp, vp, i64, i64, i64, i32, i32, i32, vp]),
+        "b2n_softmax_tile_plan": (i32, [i64, i64, i64, i32, i32, i32, i64, vp]),
         "b2n_nll_loss_workspace_bytes": (sz, [i64]),
         "b2n_nll_loss_fwd": (i32, [vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, i64, i32, i32, vp]),
         "b2n_nll_loss_bwd": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i64, i32, i32, vp]),
