@@ -191,3 +191,30 @@ def test_softmax_over_a_middle_dim_beyond_2_to_the_31_elements():
     ref = ao.softmax_bwd(xs, ys.cpu(), -1, False, torch.bfloat16)
     assert ao.lowp_mismatch(dxs, ref)[0] == 0
     assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("C", [19, 64, 150])
+def test_softmax_over_dim_1_of_16xCx512x512_bf16(C):
+    # the shapes of the bench's sm_c19 / sm_c64 / sm_c150 lines (tensor-map TMA tiles): sampled lines against the
+    # oracle, and for EVERY line: the softmax sums to one, the backward sums to zero (sum_j y_j (dy_j - s) = 0)
+    O, HW = 16, 512 * 512
+    x = seeded_rows_to_device(11000 + C, O * C, HW, torch.bfloat16, std=2.0, block=64).view(O, C, HW)
+    dy = seeded_rows_to_device(12000 + C, O * C, HW, torch.bfloat16, block=64).view(O, C, HW)
+    y = capi._softmax(x, 1, False)
+    assert capi.last_path() == "tma"
+    dx = capi._softmax_backward_data(dy, y, 1, torch.bfloat16)
+    assert capi.last_path() == "tma"
+    g = torch.Generator().manual_seed(C)
+    lines = [(0, 0), (O - 1, HW - 1)] + [(int(torch.randint(0, O, (1,), generator=g)), int(torch.randint(0, HW, (1,), generator=g)))
+                                        for _ in range(62)]
+    xs = torch.stack([x[o, :, i] for o, i in lines]).cpu()
+    ys = torch.stack([y[o, :, i] for o, i in lines])
+    gate_16bit(f"dim-1 softmax C={C} y", ys, ao.softmax_fwd(xs, -1, False), ao.softmax_fwd64(xs, -1, False))
+    dys = torch.stack([dy[o, :, i] for o, i in lines]).cpu()
+    dxs = torch.stack([dx[o, :, i] for o, i in lines])
+    gate_16bit(f"dim-1 softmax C={C} dx", dxs, ao.softmax_bwd(dys, ys.cpu(), -1, False, torch.bfloat16),
+               ao.softmax_bwd64(dys, ys.cpu(), -1, False))
+    assert float((y.float().sum(1) - 1).abs().max()) <= C * 2e-3          # bf16 rounding of C terms
+    scale = float((y.float() * dy.float().abs()).sum(1).max())
+    assert float(dx.float().sum(1).abs().max()) <= 8e-3 * max(1.0, scale)
+    assert capi.device_status() == 0

@@ -3,6 +3,8 @@ test_gpu_norm.py: fp32 1e-5 relative with an absolute floor, 16-bit within 1 ulp
 fp32-accumulated reference)."""
 import math
 
+import ctypes
+
 import pytest
 import torch
 
@@ -352,4 +354,51 @@ def test_middle_dim_tiles(shape, dt, is_log, path):
     if not is_log:
         ys = capi._safe_softmax(x.to(DEV), 1)
         assert float(ys[0, :, 3].abs().max()) == 0.0  # the all -inf line: zeros instead of NaN
+    assert capi.device_status() == 0
+
+
+def _random_middle_dim_shapes(count, seed):
+    g = torch.Generator().manual_seed(seed)
+    shapes = []
+    for _ in range(count):
+        outer = int(torch.randint(1, 6, (1,), generator=g))
+        n = int(torch.randint(2, 600, (1,), generator=g))
+        inner = 8 * int(torch.randint(8, 400, (1,), generator=g))
+        shapes.append((outer, n, inner))
+    return shapes
+
+
+@pytest.mark.parametrize("shape", _random_middle_dim_shapes(24, 77))
+def test_middle_dim_random_shapes_take_the_tma_tiles(shape):
+    # seeded random [outer, N, inner] with inner a whole number of 16-byte vectors: whatever tile geometry the planner
+    # picks (boxes of 128..512 bytes, one to four per tile, one or several boxes of rows, ragged last tiles), forward and
+    # backward agree with the oracle in bf16, and log-softmax in fp32; the path is reported
+    outer, n, inner = shape
+    x = ao.randn(shape, 7000 + n, torch.float32, 0.0, 3.0)
+    dy = ao.randn(shape, 7001 + inner, torch.float32)
+    for dt, is_log in ((torch.bfloat16, False), (torch.float32, True), (torch.float16, True)):
+        xt, dyt = x.to(dt), dy.to(dt)
+        fwd = capi._log_softmax if is_log else capi._softmax
+        bwd = capi._log_softmax_backward_data if is_log else capi._softmax_backward_data
+        y_buf, y_chk = guarded_empty(shape, dt)
+        y = fwd(xt.to(DEV), 1, False, out=y_buf)
+        used = capi.last_path()
+        dx_buf, dx_chk = guarded_empty(shape, dt)
+        dx = bwd(dyt.to(DEV), y, 1, dt, out=dx_buf)
+        torch.cuda.synchronize()
+        y_chk(); dx_chk()
+        plan = (ctypes.c_int * 8)()
+        assert b200norm.load_library().b2n_softmax_tile_plan(outer, n, inner, xt.element_size(), 0, 148, 232448, plan) == 0
+        assert (used == "tma") == bool(plan[0]), (used, list(plan))
+        check_out(y, ao.softmax_fwd(xt, 1, is_log), f"y {dt} {shape}")
+        rdx = ao.softmax_bwd(dyt, y.cpu(), 1, is_log, dt)
+        if dt == torch.float32:
+            # dx = dy - exp(y) * sum(dy): where the two cancel, the error is that of the line's SUM, taken here in
+            # another order than on the CPU.  Its a-priori bound for pairwise summation in fp32 is log2(n) * 2^-24 of
+            # the L1 norm of the terms (5.5e-7 for n <= 600); the element-wise 1e-5 stays for everything else.
+            l1 = dyt.abs().sum(1, keepdim=True)
+            tol = 1e-5 * rdx.abs() + 5.5e-7 * l1 + 1e-6
+            assert bool(((dx.cpu() - rdx).abs() <= tol).all()), f"dx {dt} {shape}"
+        else:
+            check_out(dx, rdx, f"dx {dt} {shape}")
     assert capi.device_status() == 0

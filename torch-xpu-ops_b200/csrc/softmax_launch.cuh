@@ -343,6 +343,7 @@ int softmax_spatial_tma_launch(const T* in0, const T* in1, T* out, int64_t outer
     fprintf(stderr, "b2n: tma tile W=%d NX=%d NB=%d S=%d segs=%d reg=%d tiles=%lld grid=%lld smem=%zu\n", p.W, p.NX, p.NB, p.S,
             p.segs, p.reg ? 1 : 0, static_cast<long long>(tiles), static_cast<long long>(grid), smem);
   ProfileScope prof(BWD ? (LOG ? "log_softmax_bwd_tma" : "softmax_bwd_tma") : (LOG ? "log_softmax_fwd_tma" : "softmax_fwd_tma"), st);
+  note_path("tma");
   const TmaLaunchArgs a{&tm0, &tm1, &tmo, outer, static_cast<int>(N), inner, &p, safe, static_cast<unsigned>(grid), smem, st};
   if constexpr (!BWD) {
     if (p.reg) return tma_tile_go<T, LOG, false, true>(a);
