@@ -9,7 +9,7 @@ bf16 [65536, 8192] with fp32 gamma/beta, rows sharded evenly over the N ranks (s
 fused fp32 [2, 8192] dgamma|dbeta buffer all-reduced over NCCL each step.  Other workloads
 (--workload cfg1|cfg2|cfg3|cfg5) run the other BASELINE configs the same way; cfg5f is config 5 with the fused
 cross-entropy backward, cfg3m config 3 with the mask inside the kernels, ln_long layer norm on rows of 16384,
-gn a GroupNorm forward, sm_c19|sm_c64|sm_c150 softmax over dim 1 of bf16 [16, C, 512, 512].
+gn a GroupNorm forward, bn batch_norm_stats, sm_c19|sm_c64|sm_c150 softmax over dim 1 of bf16 [16, C, 512, 512].
 
 Prints ONE JSON line (rank 0).  `value` is algorithmic bytes (every tensor of the operators'
 signatures read or written once) of all ranks / device time, inputs resident in HBM; `e2e` is the
@@ -725,7 +725,7 @@ def run_other_configs(capi, dev, steps_of, barrier):
     """Short runs of the other BASELINE configs on this GPU: value, step time and per-kernel roofline each."""
     _load_more_workloads()
     out = {}
-    for name in ("cfg1", "cfg2", "cfg3", "cfg5", "cfg5f", "ln_long", "gn", "sm_c19", "sm_c64", "sm_c150"):
+    for name in ("cfg1", "cfg2", "cfg3", "cfg5", "cfg5f", "ln_long", "gn", "bn", "sm_c19", "sm_c64", "sm_c150"):
         if name not in WORKLOADS:
             continue
         wl = WORKLOADS[name]()
@@ -915,7 +915,7 @@ def main():
         del st
         torch.cuda.empty_cache()
         configs = run_other_configs(capi, dev, lambda name: {"cfg1": 64, "cfg2": 40, "cfg3": 10, "cfg5": 4,
-                                                              "cfg5f": 4, "ln_long": 10, "gn": 10, "sm_c19": 20, "sm_c64": 10,
+                                                              "cfg5f": 4, "ln_long": 10, "gn": 10, "bn": 10, "sm_c19": 20, "sm_c64": 10,
                                                               "sm_c150": 6}[name], barrier)
 
     if rank == 0:

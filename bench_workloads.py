@@ -446,6 +446,48 @@ class GroupNormFwd(_Simple):
         return rows * self.C * self.HW * 2 + 2 * rows * self.G * 2
 
 
+class BatchNormStats(_Simple):
+    """Not a BASELINE config: batch_norm_stats (per-channel mean and 1/sqrt(var + eps)) on the first shape of the
+    reference microbenchmark (test/microbench/batch_norm_2d.py: [256, 256, 56, 56]), bf16.  `rows` are samples.
+    A read-only kernel: the roofline compares it with the measured COPY bandwidth, which counts a read and a write."""
+    name, rows, C, HW, cpu_sample_rows = "bn", 256, 256, 56 * 56, 32
+    e2e_inputs = ("x",)
+    launches_per_step = 1
+    l2_note = "input (392 MiB) larger than L2 (no flush needed)"
+
+    def describe(self):
+        return f"batch_norm_stats, bf16 [{self.rows}, {self.C}, 56, 56], eps 1e-5"
+
+    def bytes_per_rows(self, rows):
+        t = rows * self.C * self.HW * 2 + 2 * self.C * 4
+        return {"total": t, "batch_norm_stats": t}
+
+    def make_cpu_state(self, rows):
+        g = torch.Generator().manual_seed(8001)
+        return {"x": torch.randn((rows, self.C, 56, 56), generator=g).to(torch.bfloat16)}
+
+    def make_device_state(self, rows, dev, seed):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        return {"x": (torch.randn((rows, self.C, 56, 56), generator=gen, device=dev) * 1.5 + 0.5).to(torch.bfloat16)}
+
+    def step(self, capi, st, world):
+        st["out"] = capi.batch_norm_stats(st["x"], 1e-5)
+
+    def cpu_step(self, cpu):
+        x = cpu["x"].float()
+        var, mean = torch.var_mean(x, (0, 2, 3), unbiased=False)
+        return mean, torch.rsqrt(var + 1e-5)
+
+    def aten_step(self, st, world):
+        return torch.batch_norm_stats(st["x"], 1e-5)
+
+    def _nbytes(self, rows, k):
+        return rows * self.C * self.HW * 2
+
+    def _out_bytes(self, rows):
+        return 2 * self.C * 4
+
+
 class SpatialSoftmax(_Simple):
     """Not a BASELINE config: _softmax + _softmax_backward_data over dim 1 of bf16 [16, C, 512, 512] (the reference's
     spatial kernels, sycl/SoftMaxKernels.cpp:735-950 and :1395-1564; the shape of a segmentation head with C classes).
@@ -516,5 +558,5 @@ def layer_norm_long_rows(base):
     return LayerNormLongRows
 
 
-EXTRA = {"sm_c19": SpatialSoftmax19, "sm_c64": SpatialSoftmax, "sm_c150": SpatialSoftmax150, "gn": GroupNormFwd, "cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,
+EXTRA = {"bn": BatchNormStats, "sm_c19": SpatialSoftmax19, "sm_c64": SpatialSoftmax, "sm_c150": SpatialSoftmax150, "gn": GroupNormFwd, "cfg1": Cfg1LayerNormFwd, "cfg2": Cfg2RmsNorm, "cfg3": Cfg3Softmax, "cfg3m": Cfg3Masked,
          "cfg5": Cfg5CrossEntropy, "cfg5f": Cfg5FusedTail}

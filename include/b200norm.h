@@ -239,6 +239,19 @@ int b2n_batch_norm_stats(const void* x, float* mean, float* second, void* runnin
                          void* running_var, int64_t N, int64_t C, int64_t HxW, double eps,
                          double momentum, int mode, int x_dtype, int running_dtype, void* stream);
 
+/* The same with a caller-allocated scratch area, which lets several CTAs share a channel (few channels, or
+ * channels with much data, would otherwise leave most of the GPU idle: one CTA per channel).  The size comes
+ * from b2n_batch_norm_stats_workspace_bytes (0: no scratch is useful for the shape); contents are ignored on
+ * entry; `workspace` 16-byte aligned.  With workspace == NULL, or too small, this is b2n_batch_norm_stats.
+ * Results do not depend on the order in which the CTAs finish (partial sums are added in a fixed order).
+ * The reference reduces a channel inside one work-group or with its own two-stage scheme
+ * (sycl/BatchNormKernels.cpp:992 ff.); the scratch is this build's equivalent of its staging buffers. */
+size_t b2n_batch_norm_stats_workspace_bytes(int64_t N, int64_t C, int64_t HxW, int x_dtype);
+int b2n_batch_norm_stats_ws(const void* x, float* mean, float* second, void* running_mean,
+                            void* running_var, int64_t N, int64_t C, int64_t HxW, double eps,
+                            double momentum, int mode, int x_dtype, int running_dtype, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
 /* ---- softmax / log-softmax --------------------------------------------------------------------
  * The tensor is viewed as [outer, N, inner]; the reduction runs over N (inner == 1 for the last
  * dim).  out_dtype == in_dtype, or B2N_F32 with a 16-bit input ("half_to_float").

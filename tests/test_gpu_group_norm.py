@@ -95,7 +95,10 @@ def test_group_norm_through_the_dispatcher_with_autograd():
     assert ao.fp32_err(yc.contiguous(), yr) <= 1.0
 
 
-BN_SHAPES = [(8, 16), (64, 33), (4, 8, 5), (16, 32, 16, 16), (3, 7, 33, 9), (2, 64, 4, 8, 8), (128, 256), (2, 3, 100000)]
+# the last four take several CTAs per channel (few channels with much data each): the reference microbenchmark's
+# (4, 8, 640, 1024) and (24, 512, 28, 28), and two with ragged splits
+BN_SHAPES = [(8, 16), (64, 33), (4, 8, 5), (16, 32, 16, 16), (3, 7, 33, 9), (2, 64, 4, 8, 8), (128, 256), (2, 3, 100000),
+             (4, 8, 640, 1024), (24, 512, 28, 28), (7, 5, 3000, 8), (129, 2, 72, 56)]
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
@@ -142,3 +145,33 @@ def test_batch_norm_ops_through_the_dispatcher():
     cm, cv = torch.batch_norm_update_stats(x.cpu(), crm, crv, 0.1)
     assert _stat_err(m2, cm) <= 1.0 and _stat_err(v2, cv) <= 1.0
     assert torch.allclose(rm.cpu(), crm, rtol=1e-5, atol=1e-6) and torch.allclose(rv.cpu(), crv, rtol=1e-5, atol=1e-6)
+
+
+def test_batch_norm_stats_split_over_several_ctas_is_reproducible_and_survives_a_large_offset():
+    # [6, 4, 200, 1000] bf16: four channels, so every channel is shared by dozens of CTAs whose partial sums are added
+    # in a fixed order — two runs give the same bits, and the one-CTA-per-channel path (no scratch) agrees to fp32
+    # rounding.  Then a mean 300 standard deviations away from zero: the sums about a few sampled elements stay
+    # well conditioned; and a channel whose sampled elements are outliers takes the second pass about its mean.
+    lib = b200norm.load_library()
+    x = ao.randn((6, 4, 200, 1000), 1300, torch.bfloat16, 0.5, 2.0)
+    N, C, HxW = 6, 4, 200 * 1000
+    assert lib.b2n_batch_norm_stats_workspace_bytes(N, C, HxW, b200norm.BF16) > 0
+    xd = x.to(DEV)
+    m1, i1 = capi.batch_norm_stats(xd, 1e-5)
+    m2, i2 = capi.batch_norm_stats(xd, 1e-5)
+    assert torch.equal(m1, m2) and torch.equal(i1, i2)
+    m0, i0 = torch.empty_like(m1), torch.empty_like(i1)
+    rc = lib.b2n_batch_norm_stats(xd.data_ptr(), m0.data_ptr(), i0.data_ptr(), None, None, N, C, HxW, 1e-5, 0.0, 0,
+                                  b200norm.BF16, b200norm.F32, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    x64 = x.double()
+    rmean, rvar = x64.mean((0, 2, 3)), x64.var((0, 2, 3), unbiased=False)
+    for m, i in ((m1, i1), (m0, i0)):
+        assert _stat_err(m, rmean) <= 1.0 and _stat_err(i, 1.0 / torch.sqrt(rvar + 1e-5)) <= 1.0
+    y = ao.randn((6, 4, 200, 1000), 1301, torch.float32, 300.0, 1.0)
+    y[:, 1, 0, 0] = -5000.0  # channel 1: the sampled elements are outliers, the first pass cancels, the second repairs it
+    m, i = capi.batch_norm_stats(y.to(DEV), 1e-5)
+    y64 = y.double()
+    assert _stat_err(m, y64.mean((0, 2, 3))) <= 1.0
+    assert _stat_err(i, 1.0 / torch.sqrt(y64.var((0, 2, 3), unbiased=False) + 1e-5)) <= 2.0
+    assert capi.device_status() == 0

@@ -443,9 +443,19 @@ def batch_norm_stats(input, eps):
     mean = torch.empty(C, dtype=torch.float32, device=x.device)
     invstd = torch.empty(C, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _check(lib.b2n_batch_norm_stats(_ptr(x), _ptr(mean), _ptr(invstd), None, None, N, C, HxW, float(eps), 0.0, 0,
-                                        _dt(x.dtype), F32, _stream(x)), "b2n_batch_norm_stats")
+        ws, nbytes = _bn_workspace(lib, x, N, C, HxW)
+        _check(lib.b2n_batch_norm_stats_ws(_ptr(x), _ptr(mean), _ptr(invstd), None, None, N, C, HxW, float(eps), 0.0, 0,
+                                           _dt(x.dtype), F32, _ptr(ws) if ws is not None else None, nbytes, _stream(x)),
+               "b2n_batch_norm_stats_ws")
     return mean, invstd
+
+
+def _bn_workspace(lib, x, N, C, HxW):
+    """The scratch b2n_batch_norm_stats_ws asks for (None, 0 when the shape needs none)."""
+    nbytes = int(lib.b2n_batch_norm_stats_workspace_bytes(N, C, HxW, _dt(x.dtype)))
+    if nbytes == 0:
+        return None, 0
+    return torch.empty(nbytes, dtype=torch.uint8, device=x.device), nbytes
 
 
 def batch_norm_update_stats(input, running_mean, running_var, momentum):
@@ -464,9 +474,11 @@ def batch_norm_update_stats(input, running_mean, running_var, momentum):
     mean = torch.empty(C, dtype=torch.float32, device=x.device)
     var = torch.empty(C, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _check(lib.b2n_batch_norm_stats(_ptr(x), _ptr(mean), _ptr(var), _ptr(running_mean), _ptr(running_var), N, C, HxW,
-                                        0.0, float(momentum), 1, _dt(x.dtype), _dt(r.dtype) if r is not None else F32,
-                                        _stream(x)), "b2n_batch_norm_stats")
+        ws, nbytes = _bn_workspace(lib, x, N, C, HxW)
+        _check(lib.b2n_batch_norm_stats_ws(_ptr(x), _ptr(mean), _ptr(var), _ptr(running_mean), _ptr(running_var), N, C, HxW,
+                                           0.0, float(momentum), 1, _dt(x.dtype), _dt(r.dtype) if r is not None else F32,
+                                           _ptr(ws) if ws is not None else None, nbytes, _stream(x)),
+               "b2n_batch_norm_stats_ws")
     return mean, var
 
 

@@ -295,11 +295,15 @@ std::tuple<Tensor, Tensor> batch_norm_stats(const Tensor& input, double eps) {
   Tensor X = input.contiguous();
   Tensor mean = at::empty({C}, X.options().dtype(at::kFloat));
   Tensor invstd = at::empty({C}, X.options().dtype(at::kFloat));
-  if (C > 0)
-    check_status(b2n_batch_norm_stats(X.const_data_ptr(), mean.mutable_data_ptr<float>(), invstd.mutable_data_ptr<float>(),
-                                      nullptr, nullptr, N, C, HxW, eps, 0.0, 0, to_b2n_dtype(X.scalar_type(), op), B2N_F32,
-                                      cur_stream()),
+  if (C > 0) {
+    const int xdt = to_b2n_dtype(X.scalar_type(), op);
+    const size_t ws_bytes = b2n_batch_norm_stats_workspace_bytes(N, C, HxW, xdt);  // several CTAs per channel need scratch
+    Tensor ws = ws_bytes ? at::empty({static_cast<int64_t>(ws_bytes)}, X.options().dtype(at::kByte)) : Tensor();
+    check_status(b2n_batch_norm_stats_ws(X.const_data_ptr(), mean.mutable_data_ptr<float>(), invstd.mutable_data_ptr<float>(),
+                                         nullptr, nullptr, N, C, HxW, eps, 0.0, 0, xdt, B2N_F32,
+                                         ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, cur_stream()),
                  op);
+  }
   return std::make_tuple(std::move(mean), std::move(invstd));
 }
 
@@ -324,12 +328,17 @@ std::tuple<Tensor, Tensor> batch_norm_update_stats(const Tensor& input, const st
   const Tensor& r = rm.defined() ? rm : rv;
   Tensor mean = at::empty({C}, X.options().dtype(at::kFloat));
   Tensor var = at::empty({C}, X.options().dtype(at::kFloat));
-  if (C > 0)
-    check_status(b2n_batch_norm_stats(X.const_data_ptr(), mean.mutable_data_ptr<float>(), var.mutable_data_ptr<float>(),
-                                      rm.defined() ? rm.mutable_data_ptr() : nullptr, rv.defined() ? rv.mutable_data_ptr() : nullptr,
-                                      N, C, HxW, 0.0, momentum, 1, to_b2n_dtype(X.scalar_type(), op),
-                                      r.defined() ? to_b2n_dtype(r.scalar_type(), op) : B2N_F32, cur_stream()),
+  if (C > 0) {
+    const int xdt = to_b2n_dtype(X.scalar_type(), op);
+    const size_t ws_bytes = b2n_batch_norm_stats_workspace_bytes(N, C, HxW, xdt);
+    Tensor ws = ws_bytes ? at::empty({static_cast<int64_t>(ws_bytes)}, X.options().dtype(at::kByte)) : Tensor();
+    check_status(b2n_batch_norm_stats_ws(X.const_data_ptr(), mean.mutable_data_ptr<float>(), var.mutable_data_ptr<float>(),
+                                         rm.defined() ? rm.mutable_data_ptr() : nullptr,
+                                         rv.defined() ? rv.mutable_data_ptr() : nullptr, N, C, HxW, 0.0, momentum, 1, xdt,
+                                         r.defined() ? to_b2n_dtype(r.scalar_type(), op) : B2N_F32,
+                                         ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes, cur_stream()),
                  op);
+  }
   return std::make_tuple(std::move(mean), std::move(var));
 }
 

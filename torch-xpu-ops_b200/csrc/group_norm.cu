@@ -235,6 +235,195 @@ batch_norm_stats_flat_kernel(const T* __restrict__ x, float* __restrict__ mean, 
   if (ty == 0 && c < C) bn_finish<RT>(mode, shift + mu_d, var, count, eps, momentum, c, mean, second, running_mean, running_var);
 }
 
+// ---- vector path: HxW a whole number of 16-byte vectors, x 16-byte aligned ---------------------------------
+// Sums of d = x - sh and d^2 over vectors [begin, end) of one channel (xc: the channel's first element; vector idx
+// is vector idx % HV of sample idx / HV).  16-byte loads, four in flight per thread — addresses first, then the
+// loads back to back, then the arithmetic (packed f32x2); a thread's position advances by additions.
+template <typename T>
+__device__ __forceinline__ void bn_channel_sums(const T* __restrict__ xc, int64_t sample_stride, int64_t HV, int64_t begin,
+                                                int64_t end, float sh, float& s_out, float& q_out) {
+  using P = Pack16<T>;
+  constexpr int V = P::VEC, VH = V / 2;
+  const float2 nsh = make_float2(-sh, -sh);
+  float2 s2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, q2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+  auto add_vec = [&](const uint4& w) {
+    float2 xv[VH];
+    P::unpack2(w, xv);
+#pragma unroll
+    for (int e = 0; e < VH; ++e) {
+      const float2 d = add2(xv[e], nsh);
+      s2[e & 1] = add2(s2[e & 1], d);
+      q2[e & 1] = fma2(d, d, q2[e & 1]);
+    }
+  };
+  // one stride of the CTA as (samples, vectors): j + step_j < 2 * HV, so one wrap suffices
+  const int64_t stride = blockDim.x, step_n = stride / HV, step_j = stride % HV;
+  auto advance = [&](int64_t& n, int64_t& j) {
+    n += step_n;
+    j += step_j;
+    if (j >= HV) { j -= HV; ++n; }
+  };
+  int64_t idx = begin + threadIdx.x;
+  int64_t n = idx / HV, j = idx - n * HV;
+  for (; idx + 3 * stride < end; idx += 4 * stride) {
+    const uint4* p[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      p[u] = reinterpret_cast<const uint4*>(xc + n * sample_stride + j * V);
+      advance(n, j);
+    }
+    uint4 w[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) w[u] = __ldg(p[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) add_vec(w[u]);
+  }
+  if (idx < end) {
+    // the last one to three strides, still loaded together: a stride past the end reads this thread's first vector
+    // of the group again (a valid address) and is left out of the sums
+    const uint4* p0 = reinterpret_cast<const uint4*>(xc + n * sample_stride + j * V);
+    const uint4* p[3];
+    bool have[3];
+#pragma unroll
+    for (int u = 0; u < 3; ++u) {
+      have[u] = idx + u * stride < end;
+      p[u] = have[u] ? reinterpret_cast<const uint4*>(xc + n * sample_stride + j * V) : p0;
+      advance(n, j);
+    }
+    uint4 w[3];
+#pragma unroll
+    for (int u = 0; u < 3; ++u) w[u] = __ldg(p[u]);
+#pragma unroll
+    for (int u = 0; u < 3; ++u)
+      if (have[u]) add_vec(w[u]);
+  }
+  s_out = (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
+  q_out = (q2[0].x + q2[0].y) + (q2[1].x + q2[1].y);
+}
+
+// The value the sums of a channel are taken about: the mean of the first element of up to eight samples.  Any
+// value near the channel's mean will do (the result does not depend on it beyond rounding); ONE element is within
+// 2.8 standard deviations of the mean only 99.5 % of the time, and every miss costs a second pass over the channel.
+// Every CTA that touches a channel computes the same value.
+template <typename T>
+__device__ __forceinline__ float bn_channel_shift(const T* __restrict__ xc, int64_t sample_stride, int64_t N) {
+  const int k = N < 8 ? static_cast<int>(N) : 8;
+  float a = 0.0f;
+  for (int n = 0; n < k; ++n) a += to_acc<float>(xc[n * sample_stride]);
+  return a / static_cast<float>(k);
+}
+
+// Mean and variance of a channel from its sums about `shift`; when |mean - shift| is large against the spread
+// (or the sums are NaN) the subtraction cancels and the whole CTA sums the channel once more about the mean found.
+template <typename T, typename RT>
+__device__ __forceinline__ void bn_channel_finish(const T* __restrict__ xc, int64_t sample_stride, int64_t HV, int64_t TV,
+                                                  float shift, float s, float q, float count, int mode, float eps, float momentum,
+                                                  int c, float* mean, float* second, RT* running_mean, RT* running_var,
+                                                  float* scratch) {
+  float mu_d = s / count;
+  float var = q / count - mu_d * mu_d;
+  if (!(mu_d * mu_d <= 8.0f * var)) {  // (uniform over the CTA: every thread holds the same s and q)
+    shift += mu_d;
+    bn_channel_sums<T>(xc, sample_stride, HV, 0, TV, shift, s, q);
+    block_sum2(s, q, scratch);
+    mu_d = s / count;
+    const float v2 = (q - mu_d * s) / count;
+    var = v2 < 0.0f ? 0.0f : v2;  // keeps NaN
+  }
+  if (threadIdx.x == 0) bn_finish<RT>(mode, shift + mu_d, var, count, eps, momentum, c, mean, second, running_mean, running_var);
+}
+
+// One CTA per channel (no scratch memory needed): fine when there are at least a few hundred channels.
+template <typename T, typename RT>
+__global__ void __launch_bounds__(512, 2)
+batch_norm_stats_channel_kernel(const T* __restrict__ x, float* __restrict__ mean, float* __restrict__ second,
+                                RT* __restrict__ running_mean, RT* __restrict__ running_var, int64_t N, int C, int64_t HxW,
+                                float eps, float momentum, int mode) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float scratch[64];
+  const int c = blockIdx.x;
+  const int64_t HV = HxW / V, TV = N * HV, sample_stride = static_cast<int64_t>(C) * HxW;
+  const T* xc = x + static_cast<int64_t>(c) * HxW;
+  const float shift = bn_channel_shift<T>(xc, sample_stride, N);
+  float s, q;
+  bn_channel_sums<T>(xc, sample_stride, HV, 0, TV, shift, s, q);
+  block_sum2(s, q, scratch);
+  bn_channel_finish<T, RT>(xc, sample_stride, HV, TV, shift, s, q, static_cast<float>(N) * static_cast<float>(HxW), mode, eps,
+                           momentum, c, mean, second, running_mean, running_var, scratch);
+}
+
+// Two kernels with scratch memory, for any number of channels.  The C * TV vectors of the tensor's channels, laid
+// end to end, are cut into gridDim.x equal ranges of G vectors — ONE balanced wave of CTAs, whatever C is.  A range
+// covers parts of one or more channels; for each, the CTA sums about the channel's shift value (bn_channel_shift: every
+// CTA that touches a channel computes the same one, so the sums simply add) and leaves {sum d, sum d^2} in
+// partial[c][slot], slot = this CTA's index among the CTAs that touch channel c.
+template <typename T>
+__global__ void __launch_bounds__(512, 2)
+batch_norm_stats_range_kernel(const T* __restrict__ x, int64_t N, int C, int64_t HxW, int64_t G, int max_slots,
+                              float2* __restrict__ partial) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float scratch[64];
+  const int64_t HV = HxW / V, TV = N * HV, sample_stride = static_cast<int64_t>(C) * HxW;
+  const int64_t total = static_cast<int64_t>(C) * TV;
+  int64_t g0 = static_cast<int64_t>(blockIdx.x) * G;
+  const int64_t g1 = g0 + G < total ? g0 + G : total;
+  int64_t c = g0 / TV;
+  while (g0 < g1) {
+    const int64_t cbase = c * TV, cend = cbase + TV;
+    const int64_t seg_end = g1 < cend ? g1 : cend;
+    const T* xc = x + c * HxW;
+    const float shift = bn_channel_shift<T>(xc, sample_stride, N);
+    float s, q;
+    bn_channel_sums<T>(xc, sample_stride, HV, g0 - cbase, seg_end - cbase, shift, s, q);
+    block_sum2(s, q, scratch);
+    if (threadIdx.x == 0) partial[c * max_slots + (static_cast<int64_t>(blockIdx.x) - cbase / G)] = make_float2(s, q);
+    g0 = seg_end;
+    ++c;
+  }
+}
+// One CTA per channel: add the channel's partial sums in slot order (the same bits on every run) and finish.
+template <typename T, typename RT>
+__global__ void __launch_bounds__(512, 2)
+batch_norm_stats_finish_kernel(const T* __restrict__ x, float* __restrict__ mean, float* __restrict__ second,
+                               RT* __restrict__ running_mean, RT* __restrict__ running_var, int64_t N, int C, int64_t HxW,
+                               float eps, float momentum, int mode, int64_t G, int max_slots, const float2* __restrict__ partial) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float scratch[64];
+  const int c = blockIdx.x;
+  const int64_t HV = HxW / V, TV = N * HV, sample_stride = static_cast<int64_t>(C) * HxW;
+  const int64_t cbase = static_cast<int64_t>(c) * TV;
+  const int nslots = static_cast<int>((cbase + TV - 1) / G - cbase / G) + 1;  // CTAs of the range kernel that touched channel c
+  float s = 0.0f, q = 0.0f;
+  for (int k = 0; k < nslots; ++k) {
+    const float2 pk = partial[static_cast<int64_t>(c) * max_slots + k];
+    s += pk.x;
+    q += pk.y;
+  }
+  const T* xc = x + static_cast<int64_t>(c) * HxW;
+  bn_channel_finish<T, RT>(xc, sample_stride, HV, TV, bn_channel_shift<T>(xc, sample_stride, N), s, q, static_cast<float>(N) * static_cast<float>(HxW),
+                           mode, eps, momentum, c, mean, second, running_mean, running_var, scratch);
+}
+
+// The range kernel's grid: two CTAs per SM, each with at least 4096 vectors; 0: the tensor is too small to be worth it.
+struct BnStatsPlan {
+  int grid = 0;
+  int64_t G = 0;
+  int max_slots = 0;
+  size_t bytes = 0;
+};
+inline BnStatsPlan bn_stats_plan(int64_t N, int64_t C, int64_t HxW, int vec, int sm_count) {
+  BnStatsPlan p;
+  const int64_t tv = N * (HxW / vec), total = C * tv;
+  int64_t grid = 2ll * sm_count;
+  if (grid > total / 4096) grid = total / 4096;
+  if (grid < 2 || tv < 1) return p;
+  p.G = (total + grid - 1) / grid;
+  p.grid = static_cast<int>((total + p.G - 1) / p.G);
+  p.max_slots = static_cast<int>((tv + p.G - 1) / p.G) + 1;
+  p.bytes = static_cast<size_t>(C) * p.max_slots * sizeof(float2);
+  return p;
+}
+
 template <typename T, typename WT, typename ST, int GROUP>
 int group_norm_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, ST* mean, ST* rstd,
                            int64_t rows, int64_t L, int64_t G, int64_t D, int64_t HxW, double eps, cudaStream_t st) {
@@ -304,11 +493,30 @@ int group_norm_launch(const void* x, const void* gamma, const void* beta, void* 
 
 template <typename T, typename RT>
 int batch_norm_stats_launch(const void* x, float* mean, float* second, void* running_mean, void* running_var, int64_t N,
-                            int64_t C, int64_t HxW, double eps, double momentum, int mode, cudaStream_t st) {
+                            int64_t C, int64_t HxW, double eps, double momentum, int mode, void* workspace,
+                            size_t workspace_bytes, cudaStream_t st) {
   ProfileScope prof("batch_norm_stats", st);
   const T* xp = static_cast<const T*>(x);
   RT* rm = static_cast<RT*>(running_mean);
   RT* rv = static_cast<RT*>(running_var);
+  constexpr int V = 16 / sizeof(T);
+  if (HxW % V == 0 && is_aligned(x, 16) && C <= 0x7fffffffLL) {
+    const BnStatsPlan p = bn_stats_plan(N, C, HxW, V, device_info().sm_count);
+    // with fewer CTAs than one per channel would give, or without scratch, one CTA per channel
+    if (p.grid > 0 && workspace != nullptr && workspace_bytes >= p.bytes && is_aligned(workspace, 8)) {
+      float2* partial = static_cast<float2*>(workspace);
+      batch_norm_stats_range_kernel<T><<<static_cast<unsigned>(p.grid), 512, 0, st>>>(xp, N, static_cast<int>(C), HxW, p.G,
+                                                                                    p.max_slots, partial);
+      if (int e = launched()) return e;
+      batch_norm_stats_finish_kernel<T, RT><<<static_cast<unsigned>(C), 512, 0, st>>>(
+          xp, mean, second, rm, rv, N, static_cast<int>(C), HxW, static_cast<float>(eps), static_cast<float>(momentum), mode,
+          p.G, p.max_slots, partial);
+      return launched();
+    }
+    batch_norm_stats_channel_kernel<T, RT><<<static_cast<unsigned>(C), 512, 0, st>>>(
+        xp, mean, second, rm, rv, N, static_cast<int>(C), HxW, static_cast<float>(eps), static_cast<float>(momentum), mode);
+    return launched();
+  }
   if (HxW >= 16) {
     const int threads = N * HxW >= 16384 ? 512 : 128;
     batch_norm_stats_spatial_kernel<T, RT><<<static_cast<unsigned>(C), threads, 0, st>>>(
@@ -346,9 +554,24 @@ int b2n_group_norm_fwd(const void* x, const void* gamma, const void* beta, void*
   return B2N_ERR_UNSUPPORTED_DTYPE;
 }
 
+size_t b2n_batch_norm_stats_workspace_bytes(int64_t N, int64_t C, int64_t HxW, int x_dtype) {
+  const int es = x_dtype == B2N_F32 ? 4 : (x_dtype == B2N_BF16 || x_dtype == B2N_F16) ? 2 : 0;
+  if (es == 0 || N < 1 || C < 1 || HxW < 1 || C > 0x7fffffffLL) return 0;
+  const int vec = 16 / es;
+  if (HxW % vec != 0 || !device_ready()) return 0;
+  return bn_stats_plan(N, C, HxW, vec, device_info().sm_count).bytes;
+}
+
 int b2n_batch_norm_stats(const void* x, float* mean, float* second, void* running_mean, void* running_var, int64_t N,
                          int64_t C, int64_t HxW, double eps, double momentum, int mode, int x_dtype, int running_dtype,
                          void* stream) {
+  return b2n_batch_norm_stats_ws(x, mean, second, running_mean, running_var, N, C, HxW, eps, momentum, mode, x_dtype,
+                                 running_dtype, nullptr, 0, stream);
+}
+
+int b2n_batch_norm_stats_ws(const void* x, float* mean, float* second, void* running_mean, void* running_var, int64_t N,
+                            int64_t C, int64_t HxW, double eps, double momentum, int mode, int x_dtype, int running_dtype,
+                            void* workspace, size_t workspace_bytes, void* stream) {
   if (N < 0 || C < 0 || HxW < 0 || mode < 0 || mode > 1) return B2N_ERR_BAD_ARG;
   if (C == 0) return B2N_OK;
   if (N == 0 || HxW == 0) return B2N_ERR_BAD_ARG;  // statistics of nothing
@@ -357,7 +580,9 @@ int b2n_batch_norm_stats(const void* x, float* mean, float* second, void* runnin
   if (!device_ready()) return B2N_ERR_CUDA;
   if (running_mean == nullptr && running_var == nullptr) running_dtype = B2N_F32;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define B2N_BN(T, RT) return batch_norm_stats_launch<T, RT>(x, mean, second, running_mean, running_var, N, C, HxW, eps, momentum, mode, st)
+#define B2N_BN(T, RT) \
+  return batch_norm_stats_launch<T, RT>(x, mean, second, running_mean, running_var, N, C, HxW, eps, momentum, mode, workspace, \
+                                        workspace_bytes, st)
   if (x_dtype == B2N_F32 && running_dtype == B2N_F32) B2N_BN(float, float);
   if (x_dtype == B2N_BF16 && running_dtype == B2N_F32) B2N_BN(bf16, float);
   if (x_dtype == B2N_BF16 && running_dtype == B2N_BF16) B2N_BN(bf16, bf16);
