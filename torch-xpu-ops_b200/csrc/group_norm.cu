@@ -424,11 +424,15 @@ inline BnStatsPlan bn_stats_plan(int64_t N, int64_t C, int64_t HxW, int vec, int
   return p;
 }
 
-template <typename T, typename WT, typename ST, int GROUP>
+template <typename T, typename WT, typename ST, int GROUP, bool FULL = false>
 int group_norm_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, ST* mean, ST* rstd,
                            int64_t rows, int64_t L, int64_t G, int64_t D, int64_t HxW, double eps, cudaStream_t st) {
   constexpr int VPT = 16 / Pack16<T>::VEC;
-  auto kernel = group_norm_fwd_ring_kernel<T, WT, ST, GROUP, VPT>;
+  if constexpr (!FULL) {
+    if (L == static_cast<int64_t>(GROUP) * 16)  // the row fills every thread's vectors: the instantiation without range checks
+      return group_norm_ring_launch<T, WT, ST, GROUP, true>(p, x, gamma, beta, y, mean, rstd, rows, L, G, D, HxW, eps, st);
+  }
+  auto kernel = group_norm_fwd_ring_kernel<T, WT, ST, GROUP, VPT, FULL>;
   static std::atomic<uint64_t> done{0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError());

@@ -9,7 +9,9 @@
 
 namespace b2n {
 
-template <typename T, typename WT, typename ST, int GROUP, int VPT>
+// FULL: a row fills every thread's vectors exactly (N == GROUP * VPT * VEC): no column range checks, row length and
+// byte offsets compile-time — as in the layer-norm ring kernels.
+template <typename T, typename WT, typename ST, int GROUP, int VPT, bool FULL>
 __global__ void __launch_bounds__(kRingBlock, 1)
 group_norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, const WT* __restrict__ beta, T* __restrict__ y,
                            ST* __restrict__ mean, ST* __restrict__ rstd, int64_t M, int N, int G, int D, int HxW, float eps,
@@ -38,14 +40,15 @@ group_norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma
   ring_consumer_regs();
 
   const int grp = tid / GROUP, tg = tid % GROUP;
-  const int nvec = N / VEC;
+  const int nvec = FULL ? GROUP * VPT : N / VEC;
+  const uint32_t row_bytes = FULL ? static_cast<uint32_t>(GROUP * VPT * 16) : g.row_bytes;
   const float inv_n = 1.0f / static_cast<float>(N);
   constexpr int HP = EPT / 2, VH = VEC / 2;
   int chan[VPT];  // channel, within the group, of each of this thread's vectors
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = tg + k * GROUP;
-    chan[k] = v < nvec ? (v * VEC) / HxW : 0;
+    chan[k] = (FULL || v < nvec) ? (v * VEC) / HxW : 0;
   }
   int red_phase = 0;
   const uint32_t stages_u32 = smem_u32(stages);
@@ -70,7 +73,7 @@ group_norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma
 #pragma unroll
       for (int b = 0; b < RB; ++b) {
         valid[b] = (r + b < RPG) && (row_a + b < M);
-        rbase[b] = sbase + static_cast<uint32_t>(lr0 + b) * g.row_bytes;
+        rbase[b] = sbase + static_cast<uint32_t>(lr0 + b) * row_bytes;
         // (the launcher takes this kernel only for fewer than 2^31 rows: a 32-bit remainder)
         const int c0 = valid[b] ? static_cast<int>(static_cast<unsigned>(row_a + b) % static_cast<unsigned>(G)) * D : 0;
 #pragma unroll
@@ -89,7 +92,7 @@ group_norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
-          if (valid[b] && v < nvec) {
+          if (valid[b] && (FULL || v < nvec)) {
             P::unpack2(lds128(rbase[b] + v * 16), &xv[b][k * VH]);
 #pragma unroll
             for (int e = 0; e < VH; ++e) {
@@ -126,7 +129,7 @@ group_norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma
 #pragma unroll
           for (int k = 0; k < VPT; ++k) {
             const int v = tg + k * GROUP;
-            if (valid[b] && v < nvec) {
+            if (valid[b] && (FULL || v < nvec)) {
               P::unpack2(lds128(rbase[b] + v * 16), &xv[b][k * VH]);
 #pragma unroll
               for (int e = 0; e < VH; ++e) {
@@ -158,7 +161,7 @@ group_norm_fwd_ring_kernel(const T* __restrict__ x, const WT* __restrict__ gamma
 #pragma unroll
         for (int k = 0; k < VPT; ++k) {
           const int v = tg + k * GROUP;
-          if (v < nvec) {
+          if (FULL || v < nvec) {
             const float2 gm = bcast2(gam[b][k]), bt = bcast2(bet[b][k]);
             float2 o[VH];
 #pragma unroll
