@@ -224,3 +224,67 @@ def test_golden_cross_entropy_backward(name):
                 assert torch.allclose(closed, dx, rtol=1e-5, atol=1e-7)
             else:
                 assert ao.ulp_distance(closed, dx) <= 1
+
+
+# ---- golden_v3: group norm, batch norm statistics, softmax over a middle dim, layer norm on long rows -------------
+GOLDEN3 = torch.load(Path(__file__).parent / "golden" / "golden_v3.pt")
+
+
+@pytest.mark.parametrize("name", ["smd1_bf16", "smd1_f32", "smd1_f16"])
+def test_golden_softmax_over_dim_1(name):
+    # the oracle the GPU tests use reproduces the fixture bit for bit, and the fixture has the properties of the op
+    c = GOLDEN3[name]
+    x, dt = c["x"], c["x"].dtype
+    for is_log, key in ((False, "softmax"), (True, "log_softmax")):
+        y = ao.softmax_fwd(x, 1, is_log)
+        assert torch.equal(torch.isnan(y), torch.isnan(c[key]))
+        ok = ~torch.isnan(y)
+        assert torch.equal(y[ok], c[key][ok])
+        dx = ao.softmax_bwd(c["dy"], c[key], 1, is_log, dt)
+        okb = ~torch.isnan(dx)
+        assert torch.equal(torch.isnan(dx), torch.isnan(c[key + "_bwd"])) and torch.equal(dx[okb], c[key + "_bwd"][okb])
+    live = ~torch.isnan(c["softmax"]).any(1)
+    assert bool(live.any()) and not bool(live.all())          # the all -inf line is there, and it is the only dead one
+    sums = _wide(c["softmax"]).sum(1)[live]
+    assert float((sums - 1).abs().max()) <= (1e-5 if dt == torch.float32 else 3e-2)
+
+
+def test_golden_layer_norm_long_rows():
+    c = GOLDEN3["ln_long_bf16_w32"]
+    n = c["x"].shape[-1]
+    assert n > 8192                                             # longer than one CTA's threads hold
+    y, mean, rstd = ao.layer_norm_fwd(c["x"], [n], c["gamma"], c["beta"], c["eps"])
+    assert torch.equal(y, c["y"]) and torch.equal(mean.reshape(-1), c["mean"].reshape(-1))
+    dx, dg, db = ao.layer_norm_bwd(c["dy"], c["x"], [n], c["mean"], c["rstd"], c["gamma"], c["beta"])
+    assert torch.equal(dx, c["dx"]) and torch.equal(dg, c["dgamma"]) and torch.equal(db, c["dbeta"])
+    # known answer: normalised rows have zero mean and unit variance before the affine map
+    xh = (_wide(c["x"]) - c["mean"].reshape(-1, 1)) * c["rstd"].reshape(-1, 1)
+    assert float(xh.mean(1).abs().max()) <= 1e-5 and float((xh.var(1, unbiased=False) - 1).abs().max()) <= 1e-4
+
+
+@pytest.mark.parametrize("name", ["gn_f32", "gn_bf16", "gn_f32_odd"])
+def test_golden_group_norm(name):
+    c = GOLDEN3[name]
+    x, dt = c["x"], c["x"].dtype
+    N, C = x.shape[0], x.shape[1]
+    hw = x.numel() // (N * C)
+    y, mean, rstd = torch.ops.aten.native_group_norm(_wide(x), _wide(c["weight"]), _wide(c["bias"]), N, C, hw, c["G"], c["eps"])
+    assert torch.equal(y.to(dt), c["y"]) and torch.equal(mean.float(), c["mean"]) and torch.equal(rstd.float(), c["rstd"])
+    # the definition: a layer norm of each (sample, group) row with per-channel weights
+    rows = _wide(x).reshape(N, c["G"], -1)
+    ref = (rows - rows.mean(2, keepdim=True)) / torch.sqrt(rows.var(2, unbiased=False, keepdim=True) + c["eps"])
+    ref = ref.reshape(N, C, hw) * _wide(c["weight"]).view(1, C, 1) + _wide(c["bias"]).view(1, C, 1)
+    assert torch.allclose(ref.reshape(x.shape), _wide(c["y"]), rtol=2e-2 if dt != torch.float32 else 1e-4, atol=2e-2 if dt != torch.float32 else 1e-5)
+
+
+@pytest.mark.parametrize("name", ["bn_f32", "bn_bf16", "bn_f32_small"])
+def test_golden_batch_norm_statistics(name):
+    c = GOLDEN3[name]
+    x = c["x"]
+    cm, cinv = None, None
+    crm, crv = c["running_mean"].clone(), c["running_var"].clone()
+    m, v = torch.batch_norm_update_stats(_wide(x), crm, crv, c["momentum"])     # CPU ATen against the float64 fixture
+    assert torch.allclose(m, c["mean"], rtol=1e-5, atol=1e-6) and torch.allclose(v, c["var"], rtol=1e-4, atol=1e-6)
+    assert torch.allclose(crm, c["running_mean_out"], rtol=1e-5, atol=1e-6)
+    assert torch.allclose(crv, c["running_var_out"], rtol=1e-4, atol=1e-6)
+    assert torch.allclose(c["invstd"], 1.0 / torch.sqrt(c["var"] + c["eps"]), rtol=1e-5)
