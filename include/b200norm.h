@@ -226,6 +226,18 @@ int b2n_group_norm_fwd(const void* x, const void* gamma, const void* beta, void*
                        void* rstd, int64_t N, int64_t C, int64_t HxW, int64_t G, double eps,
                        int x_dtype, int w_dtype, int stat_dtype, void* stream);
 
+/* GroupNorm backward from the forward's saved statistics (mean, rstd: [N * G] of stat_dtype):
+ * dx [N, C, HxW] of x_dtype, dgamma / dbeta [C] of w_dtype; any of the three may be NULL (not wanted).  gamma may be
+ * NULL (ones).  With xhat = (x - mean) * rstd and g = dy * gamma[c]:
+ * dx = rstd * (g - (xhat * sum(g * xhat) + sum(g)) / (D * HxW)) per (n, group) row;
+ * dgamma[c] = sum over n, HxW of dy * xhat; dbeta[c] = sum dy.  An element of the N = 0 / HxW = 0 corner writes nothing.
+ *
+ * Replaces at::native::xpu::group_norm_backward_kernel (src/ATen/native/xpu/sycl/GroupNormKernels.h:30-42) behind the
+ * GroupNormBackwardKernel dispatch stub (src/ATen/native/xpu/GroupNorm.cpp:23). */
+int b2n_group_norm_bwd(const void* dy, const void* x, const void* mean, const void* rstd,
+                       const void* gamma, void* dx, void* dgamma, void* dbeta, int64_t N, int64_t C,
+                       int64_t HxW, int64_t G, int x_dtype, int w_dtype, int stat_dtype, void* stream);
+
 /* BatchNorm statistics of a contiguous [N, C, HxW] tensor, per channel over N and HxW, in fp32:
  * mean[C] and, mode 0, second[C] = 1 / sqrt(biased var + eps) (batch_norm_stats); mode 1,
  * second[C] = biased var, and running_mean / running_var ([C] of running_dtype = x_dtype or

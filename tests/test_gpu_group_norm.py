@@ -1,4 +1,4 @@
-"""GroupNorm forward and BatchNorm statistics: CUDA kernels through the C ABI and the dispatcher vs CPU ATen.
+"""GroupNorm forward and backward, BatchNorm statistics: CUDA kernels through the C ABI and the dispatcher vs CPU ATen.
 
 Tolerances as for layer norm: fp32 outputs |a-b| <= 1e-5*|b| + 1e-6*max(1, rms(b)); 16-bit outputs within 1 ulp of
 the fp32-accumulated reference (CPU ATen on fp32 upcasts, rounded once) or the same absolute floor; statistics
@@ -13,7 +13,7 @@ import b200norm
 from b200norm import capi
 from oracle import aten_oracle as ao
 
-from gpu_util import DEV
+from gpu_util import DEV, wgrad_gate
 
 pytestmark = pytest.mark.gpu
 
@@ -58,6 +58,48 @@ def test_group_norm_forward(shape, G, dt, wdt, affine):
     assert capi.device_status() == 0
 
 
+@pytest.mark.parametrize("affine", [True, False])
+@pytest.mark.parametrize("dt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                    (torch.bfloat16, torch.float32), (torch.float16, torch.float16)])
+@pytest.mark.parametrize("shape,G", GN_SHAPES)
+def test_group_norm_backward(shape, G, dt, wdt, affine):
+    # dX against CPU ATen on fp32 upcasts (rounded once); dgamma / dbeta element by element against an fp64 sum of
+    # their terms (1e-6 of the L1 norm; 16-bit: one ulp of that sum); the statistics are the forward's own
+    N, C = shape[0], shape[1]
+    HxW = 1
+    for d in shape[2:]:
+        HxW *= d
+    x = ao.randn(shape, 1400 + C, dt, 0.5, 2.0)
+    dy = ao.randn(shape, 1401 + C, dt)
+    g = ao.randn((C,), 1402, wdt, 1.0, 0.2) if affine else None
+    dev = lambda t: None if t is None else t.to(DEV)
+    _, mean, rstd = capi.native_group_norm(dev(x), dev(g), None, N, C, HxW, G, 1e-5)
+    dx, dg, db = capi.native_group_norm_backward(dev(dy), dev(x), mean, rstd, dev(g), N, C, HxW, G, (True, True, True))
+    f32 = lambda t: None if t is None else t.float()
+    m32, r32 = mean.float().cpu(), rstd.float().cpu()
+    rdx, _, _ = torch.ops.aten.native_group_norm_backward(dy.float(), x.float(), m32, r32, f32(g), N, C, HxW, G,
+                                                          [True, affine, affine])
+    assert dx.shape == x.shape and dx.dtype == dt
+    if dt == torch.float32:
+        assert ao.fp32_err(dx, rdx) <= 1.0
+    else:
+        assert ao.lowp_mismatch(dx, rdx.to(dt))[0] == 0
+    if affine:
+        assert dg.shape == (C,) and db.shape == (C,) and dg.dtype == wdt and db.dtype == wdt
+        D = C // G
+        x64 = x.double().reshape(N, C, HxW)
+        xh = (x64 - m32.double().repeat_interleave(D, 1).view(N, C, 1)) * r32.double().repeat_interleave(D, 1).view(N, C, 1)
+        d64 = dy.double().reshape(N, C, HxW)
+        wgrad_gate(dg, (d64 * xh).permute(0, 2, 1).reshape(-1, C), "dgamma")
+        wgrad_gate(db, d64.permute(0, 2, 1).reshape(-1, C), "dbeta")
+    else:
+        assert dg is None and db is None
+    # masked-off outputs are not computed
+    only_dx = capi.native_group_norm_backward(dev(dy), dev(x), mean, rstd, dev(g), N, C, HxW, G, (True, False, False))
+    assert only_dx[1] is None and only_dx[2] is None and torch.equal(only_dx[0], dx)
+    assert capi.device_status() == 0
+
+
 def test_group_norm_large_offset_and_argument_checks():
     x = (torch.randn(2, 8, 64) + 3.0e4).to(DEV)  # mean far from the first element's neighbourhood in relative terms
     y, mean, rstd = capi.native_group_norm(x, None, None, 2, 8, 64, 2, 1e-5)
@@ -87,9 +129,17 @@ def test_group_norm_through_the_dispatcher_with_autograd():
     launches = capi.launch_count()
     yd = md(xd)
     assert capi.launch_count() == launches + 1  # the dispatcher reached this library's forward kernel
-    yd.backward(torch.ones_like(yd) * 0.5)    # ... and autograd carries on through the stock backward
+    yd.backward(torch.ones_like(yd) * 0.5)
+    # ... and autograd's native_group_norm_backward reached this library's kernels too (it runs on the autograd engine's
+    # own thread, whose launch counter this thread cannot see: the gradients are bit-identical to a direct call)
+    _, mean, rstd = capi.native_group_norm(xd.detach(), md.weight.detach(), md.bias.detach(), 4, 32, 256, 8, 1e-5)
+    ddx, ddg, ddb = capi.native_group_norm_backward(torch.full_like(yd, 0.5), xd.detach(), mean, rstd, md.weight.detach(), 4, 32,
+                                                    256, 8)
+    assert torch.equal(xd.grad, ddx) and torch.equal(md.weight.grad, ddg) and torch.equal(md.bias.grad, ddb)
     assert ao.fp32_err(yd, yr) <= 1.0
-    assert torch.allclose(xd.grad.cpu(), xr.grad, rtol=1e-4, atol=1e-5)
+    assert ao.fp32_err(xd.grad, xr.grad) <= 1.0
+    assert torch.allclose(md.weight.grad.cpu(), m.weight.grad, rtol=1e-5, atol=1e-4)
+    assert torch.allclose(md.bias.grad.cpu(), m.bias.grad, rtol=1e-5, atol=1e-4)
     # channels-last input: made contiguous by the composite, same result
     yc = md(x.to(DEV).contiguous(memory_format=torch.channels_last))
     assert ao.fp32_err(yc.contiguous(), yr) <= 1.0
@@ -137,7 +187,7 @@ def test_batch_norm_ops_through_the_dispatcher():
     mean, invstd = torch.batch_norm_stats(x, 1e-5)
     rm, rv = torch.zeros(24, device=DEV), torch.ones(24, device=DEV)
     m2, v2 = torch.batch_norm_update_stats(x, rm, rv, 0.1)
-    assert capi.launch_count() == launches + 2
+    assert capi.launch_count() == launches + 2, capi.launch_count() - launches
     xr = x.cpu().double()
     assert _stat_err(mean, xr.mean((0, 2, 3))) <= 1.0
     assert _stat_err(invstd, 1 / torch.sqrt(xr.var((0, 2, 3), unbiased=False) + 1e-5)) <= 1.0

@@ -428,6 +428,43 @@ def native_group_norm(input, weight, bias, N, C, HxW, group, eps, out=None):
     return y, mean, rstd
 
 
+def native_group_norm_backward(grad_out, input, mean, rstd, weight, N, C, HxW, group, output_mask=(True, True, True)):
+    """aten::native_group_norm_backward -> (dX?, dgamma?, dbeta?); masked-off outputs are None, and so are dgamma /
+    dbeta when there is no weight (upstream sizes them after it).  mean / rstd: the forward's saved statistics."""
+    _require_cuda(grad_out, input, mean, rstd, weight)
+    lib = load_library()
+    if input.numel() != N * C * HxW or grad_out.numel() != input.numel():
+        raise RuntimeError(f"Expected input and grad_out of {N}*{C}*{HxW} elements, got {list(input.shape)} and "
+                           f"{list(grad_out.shape)}")
+    if group < 1 or C % group != 0:
+        raise RuntimeError(f"Expected number of channels in input to be divisible by num_groups, but got input of "
+                           f"shape {list(input.shape)} and num_groups={group}")
+    if mean.numel() != N * group or rstd.numel() != N * group or mean.dtype != rstd.dtype:
+        raise RuntimeError("native_group_norm_backward: mean and rstd must be [N, group] tensors of one dtype")
+    if weight is not None and (weight.dim() != 1 or weight.numel() != C):
+        raise RuntimeError(f"Expected weight to be a vector of size equal to the number of channels in input, but got "
+                           f"weight of shape {list(weight.shape)} and input of shape {list(input.shape)}")
+    x = input.contiguous()
+    dy = grad_out.to(x.dtype).contiguous()
+    g = weight.contiguous() if weight is not None else None
+    wdt = _weight_dtype(x, g, None)
+    m, r = mean.contiguous(), rstd.contiguous()
+    dx = torch.empty_like(x) if output_mask[0] else None
+    dgamma = torch.empty_like(g) if (output_mask[1] and g is not None) else None
+    dbeta = torch.empty_like(g) if (output_mask[2] and g is not None) else None
+    if C > 0 and (x.numel() > 0 or dgamma is not None or dbeta is not None):
+        if x.numel() == 0:  # sums over nothing
+            for t in (dgamma, dbeta):
+                if t is not None:
+                    t.zero_()
+        else:
+            with torch.cuda.device(x.device):
+                _check(lib.b2n_group_norm_bwd(_ptr(dy), _ptr(x), _ptr(m), _ptr(r), _ptr(g), _ptr(dx), _ptr(dgamma), _ptr(dbeta),
+                                              N, C, HxW, group, _dt(x.dtype), wdt, _dt(m.dtype), _stream(x)),
+                       "b2n_group_norm_bwd")
+    return dx, dgamma, dbeta
+
+
 def _bn_dims(input):
     if input.dim() < 2:
         raise RuntimeError("batch norm statistics need an input with at least two dimensions [N, C, ...]")

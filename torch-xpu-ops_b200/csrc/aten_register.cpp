@@ -276,6 +276,52 @@ std::tuple<Tensor, Tensor, Tensor> native_group_norm(const Tensor& input, const 
   return std::make_tuple(std::move(Y), std::move(mean), std::move(rstd));
 }
 
+// Host wrapper of upstream's native_group_norm_backward (aten/src/ATen/native/group_norm.cpp) around the kernel the
+// reference registers for its GroupNormBackwardKernel stub (src/ATen/native/xpu/GroupNorm.cpp:23): dX like X, dgamma /
+// dbeta like the weight (undefined without one, or when masked off).
+std::tuple<Tensor, Tensor, Tensor> native_group_norm_backward(const Tensor& grad_out, const Tensor& input, const Tensor& mean,
+                                                              const Tensor& rstd, const std::optional<Tensor>& weight_opt,
+                                                              int64_t N, int64_t C, int64_t HxW, int64_t group,
+                                                              std::array<bool, 3> mask) {
+  c10::MaybeOwned<Tensor> weight_mo = at::borrow_from_optional_tensor(weight_opt);
+  const Tensor& weight = *weight_mo;
+  const char* op = "native_group_norm_backward";
+  TORCH_CHECK(input.is_cuda() && grad_out.is_cuda(), op, ": expected CUDA tensors");
+  TORCH_CHECK(group > 0 && C % group == 0, "Expected number of channels in input to be divisible by num_groups, but got input of shape ",
+              input.sizes(), " and num_groups=", group);
+  TORCH_CHECK(input.numel() == N * C * HxW && grad_out.numel() == input.numel(), op, ": input and grad_out must have N*C*HxW = ",
+              N * C * HxW, " elements");
+  TORCH_CHECK(mean.numel() == N * group && rstd.numel() == N * group && mean.scalar_type() == rstd.scalar_type(), op,
+              ": mean and rstd must be [N, group] tensors of one dtype");
+  TORCH_CHECK(!weight.defined() || (weight.dim() == 1 && weight.numel() == C),
+              "Expected weight to be a vector of size equal to the number of channels in input, but got weight of shape ",
+              weight.sizes(), " and input of shape ", input.sizes());
+  const c10::cuda::CUDAGuard guard(input.device());
+  Tensor X = input.contiguous();
+  Tensor dY = grad_out.to(X.scalar_type()).contiguous();
+  Tensor M = mean.contiguous(), R = rstd.contiguous();
+  auto gamma = weight.expect_contiguous();
+  const int xdt = to_b2n_dtype(X.scalar_type(), op);
+  const int wdt = weight_dtype(X, weight, Tensor(), op);
+  Tensor dX, dgamma, dbeta;
+  if (mask[0]) dX = at::empty_like(X, at::MemoryFormat::Contiguous);
+  if (mask[1] && weight.defined()) dgamma = at::empty_like(*gamma, at::MemoryFormat::Contiguous);
+  if (mask[2] && weight.defined()) dbeta = at::empty_like(*gamma, at::MemoryFormat::Contiguous);
+  if (X.numel() == 0) {
+    if (dgamma.defined()) dgamma.zero_();
+    if (dbeta.defined()) dbeta.zero_();
+  } else if (dX.defined() || dgamma.defined() || dbeta.defined()) {
+    check_status(b2n_group_norm_bwd(dY.const_data_ptr(), X.const_data_ptr(), M.const_data_ptr(), R.const_data_ptr(),
+                                    gamma->defined() ? gamma->const_data_ptr() : nullptr,
+                                    dX.defined() ? dX.mutable_data_ptr() : nullptr,
+                                    dgamma.defined() ? dgamma.mutable_data_ptr() : nullptr,
+                                    dbeta.defined() ? dbeta.mutable_data_ptr() : nullptr, N, C, HxW, group, xdt, wdt,
+                                    to_b2n_dtype(M.scalar_type(), op), cur_stream()),
+                 "group_norm_bwd");
+  }
+  return std::make_tuple(std::move(dX), std::move(dgamma), std::move(dbeta));
+}
+
 static void bn_dims(const Tensor& input, const char* op, int64_t& N, int64_t& C, int64_t& HxW) {
   TORCH_CHECK(input.dim() >= 2, op, ": expected an input with at least two dimensions [N, C, ...]");
   N = input.size(0);
@@ -748,6 +794,7 @@ TORCH_LIBRARY_IMPL(aten, CUDA, m) {
   m.impl("_fused_rms_norm", TORCH_FN(fused_rms_norm));
   m.impl("_fused_rms_norm_backward", TORCH_FN(fused_rms_norm_backward));
   m.impl("native_group_norm", TORCH_FN(native_group_norm));
+  m.impl("native_group_norm_backward", TORCH_FN(native_group_norm_backward));
   m.impl("batch_norm_stats", TORCH_FN(batch_norm_stats));
   m.impl("batch_norm_update_stats", TORCH_FN(batch_norm_update_stats));
   m.impl("_softmax", TORCH_FN(softmax));

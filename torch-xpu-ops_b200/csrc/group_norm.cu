@@ -130,6 +130,111 @@ group_norm_fwd_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, con
   }
 }
 
+// ---- group norm backward ------------------------------------------------------------------------------------
+// Row (n, g) of [N * G, L = D * HxW] with xhat = (x - mean) * rstd and g_j = dy_j * gamma[c(j)]:
+//   dx_j = rstd * (g_j - (xhat_j * s2 + s1) / L),  s1 = sum g,  s2 = sum g * xhat          (one CTA per row, two walks,
+//   the second served by L1/L2);
+//   dgamma[c] = sum over n and the channel's HxW elements of dy * xhat,  dbeta[c] = sum dy   (one CTA per channel).
+// The formulas of the reference's backward (GroupNormKernels.cpp, ComputeInternalGradients / GroupNormBackward /
+// GammaBetaBackward), evaluated in fp32 from the saved statistics.
+template <typename T, typename WT, typename ST, int V>
+__global__ void __launch_bounds__(512)
+group_norm_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x, const ST* __restrict__ mean,
+                         const ST* __restrict__ rstd, const WT* __restrict__ gamma, T* __restrict__ dx, int64_t rows, int G,
+                         int D, int HxW) {
+  __shared__ float scratch[64];
+  const int64_t L = static_cast<int64_t>(D) * HxW;
+  const float inv_l = 1.0f / static_cast<float>(L);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * L;
+    const T* gr = dy + row * L;
+    T* dr = dx + row * L;
+    const float mu = to_acc<float>(mean[row]), rs = to_acc<float>(rstd[row]);
+    const int c0 = static_cast<int>(row % G) * D;
+    // V > 1 is taken only when HxW % V == 0: a vector then lies in one channel
+    auto walk = [&](auto&& body) {
+      if constexpr (V > 1) {
+        const int64_t nv = L / V;
+        for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+          const Vec<T, V> xv = ld_vec<T, V>(xr + v * V), gv = ld_vec<T, V>(gr + v * V);
+          const float gm = gamma ? to_acc<float>(gamma[c0 + static_cast<int>((v * V) / HxW)]) : 1.0f;
+          Vec<T, V> o;
+#pragma unroll
+          for (int e = 0; e < V; ++e) o.v[e] = body(to_acc<float>(xv.v[e]), to_acc<float>(gv.v[e]) * gm);
+          if (body.stores) st_vec<T, V>(dr + v * V, o);
+        }
+      } else {
+        for (int64_t j = threadIdx.x; j < L; j += blockDim.x) {
+          const float gm = gamma ? to_acc<float>(gamma[c0 + static_cast<int>(j / HxW)]) : 1.0f;
+          const T o = body(to_acc<float>(xr[j]), to_acc<float>(gr[j]) * gm);
+          if (body.stores) dr[j] = o;
+        }
+      }
+    };
+    float s1 = 0.0f, s2 = 0.0f;
+    struct Sums {
+      float &s1, &s2, mu, rs;
+      bool stores;
+      __device__ T operator()(float xv, float g) const {
+        s1 += g;
+        s2 = fmaf(g, (xv - mu) * rs, s2);
+        return T();
+      }
+    } sums{s1, s2, mu, rs, false};
+    walk(sums);
+    block_sum2(s1, s2, scratch);
+    struct Out {
+      float a, b, mu, rs;
+      bool stores;
+      __device__ T operator()(float xv, float g) const { return from_acc<T>(rs * (g - fmaf((xv - mu) * rs, a, b))); }
+    } out{s2 * inv_l, s1 * inv_l, mu, rs, true};
+    walk(out);
+    __syncthreads();  // scratch is reused by the next row
+  }
+}
+
+template <typename T, typename WT, typename ST, int V>
+__global__ void __launch_bounds__(512)
+group_norm_bwd_wgrad_kernel(const T* __restrict__ dy, const T* __restrict__ x, const ST* __restrict__ mean,
+                            const ST* __restrict__ rstd, WT* __restrict__ dgamma, WT* __restrict__ dbeta, int64_t N, int C,
+                            int G, int HxW) {
+  __shared__ float scratch[64];
+  const int c = blockIdx.x, D = C / G, g = c / D;
+  float sg = 0.0f, sb = 0.0f;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  // warps over samples, lanes along the run: each sample's statistics are read once per warp
+  for (int64_t n = w; n < N; n += nw) {
+    const float mu = to_acc<float>(mean[n * G + g]), rs = to_acc<float>(rstd[n * G + g]);
+    const T* xr = x + (n * C + c) * static_cast<int64_t>(HxW);
+    const T* gr = dy + (n * C + c) * static_cast<int64_t>(HxW);
+    float a = 0.0f, b = 0.0f;  // sum dy * (x - mu), sum dy of this run
+    if constexpr (V > 1) {
+      for (int v = l; v < HxW / V; v += 32) {
+        const Vec<T, V> xv = ld_vec<T, V>(xr + v * V), gv = ld_vec<T, V>(gr + v * V);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float d = to_acc<float>(gv.v[e]);
+          a = fmaf(d, to_acc<float>(xv.v[e]) - mu, a);
+          b += d;
+        }
+      }
+    } else {
+      for (int j = l; j < HxW; j += 32) {
+        const float d = to_acc<float>(gr[j]);
+        a = fmaf(d, to_acc<float>(xr[j]) - mu, a);
+        b += d;
+      }
+    }
+    sg = fmaf(a, rs, sg);
+    sb += b;
+  }
+  block_sum2(sg, sb, scratch);
+  if (threadIdx.x == 0) {
+    if (dgamma) dgamma[c] = from_acc<WT>(sg);
+    if (dbeta) dbeta[c] = from_acc<WT>(sb);
+  }
+}
+
 // ---- batch norm statistics ------------------------------------------------------------------------------
 // x: [N, C, HxW].  Channel c's elements: N runs of HxW at (n * C + c) * HxW.  Results in fp32:
 // mean[c]; second[c] = 1 / sqrt(var + eps) (MODE 0, batch_norm_stats) or the biased variance (MODE 1,
@@ -495,6 +600,45 @@ int group_norm_launch(const void* x, const void* gamma, const void* beta, void* 
   return launched();
 }
 
+template <typename T, typename WT, typename ST>
+int group_norm_bwd_launch(const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma, void* dx,
+                          void* dgamma, void* dbeta, int64_t N, int64_t C, int64_t HxW, int64_t G, cudaStream_t st) {
+  const int64_t rows = N * G, D = C / G, L = D * HxW;
+  constexpr int V = 16 / sizeof(T);
+  const bool vec = HxW % V == 0 && is_aligned(x, 16) && is_aligned(dy, 16) && (dx == nullptr || is_aligned(dx, 16));
+  const T* gp = static_cast<const T*>(dy);
+  const T* xp = static_cast<const T*>(x);
+  const ST* mp = static_cast<const ST*>(mean);
+  const ST* rp = static_cast<const ST*>(rstd);
+  ProfileScope prof("group_norm_bwd", st);
+  if (dx != nullptr) {
+    const int threads = L >= 8192 ? 512 : (L >= 2048 ? 256 : 128);
+    const int64_t cap = static_cast<int64_t>(device_info().sm_count) * (2048 / threads);
+    const int grid = static_cast<int>(rows < cap ? rows : cap);
+    const WT* wp = static_cast<const WT*>(gamma);
+    if (vec)
+      group_norm_bwd_dx_kernel<T, WT, ST, V><<<grid, threads, 0, st>>>(gp, xp, mp, rp, wp, static_cast<T*>(dx), rows,
+                                                                       static_cast<int>(G), static_cast<int>(D), static_cast<int>(HxW));
+    else
+      group_norm_bwd_dx_kernel<T, WT, ST, 1><<<grid, threads, 0, st>>>(gp, xp, mp, rp, wp, static_cast<T*>(dx), rows,
+                                                                       static_cast<int>(G), static_cast<int>(D), static_cast<int>(HxW));
+    if (int e = launched()) return e;
+  }
+  if (dgamma != nullptr || dbeta != nullptr) {
+    const int threads = N * HxW >= 16384 ? 512 : 128;
+    if (vec)
+      group_norm_bwd_wgrad_kernel<T, WT, ST, V><<<static_cast<unsigned>(C), threads, 0, st>>>(
+          gp, xp, mp, rp, static_cast<WT*>(dgamma), static_cast<WT*>(dbeta), N, static_cast<int>(C), static_cast<int>(G),
+          static_cast<int>(HxW));
+    else
+      group_norm_bwd_wgrad_kernel<T, WT, ST, 1><<<static_cast<unsigned>(C), threads, 0, st>>>(
+          gp, xp, mp, rp, static_cast<WT*>(dgamma), static_cast<WT*>(dbeta), N, static_cast<int>(C), static_cast<int>(G),
+          static_cast<int>(HxW));
+    if (int e = launched()) return e;
+  }
+  return B2N_OK;
+}
+
 template <typename T, typename RT>
 int batch_norm_stats_launch(const void* x, float* mean, float* second, void* running_mean, void* running_var, int64_t N,
                             int64_t C, int64_t HxW, double eps, double momentum, int mode, void* workspace,
@@ -555,6 +699,26 @@ int b2n_group_norm_fwd(const void* x, const void* gamma, const void* beta, void*
   if (x_dtype == B2N_F16 && w_dtype == B2N_F16 && stat_dtype == B2N_F16) B2N_GN(f16, f16, f16);
   if (x_dtype == B2N_F16 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GN(f16, float, float);
 #undef B2N_GN
+  return B2N_ERR_UNSUPPORTED_DTYPE;
+}
+
+int b2n_group_norm_bwd(const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma, void* dx,
+                       void* dgamma, void* dbeta, int64_t N, int64_t C, int64_t HxW, int64_t G, int x_dtype, int w_dtype,
+                       int stat_dtype, void* stream) {
+  if (N < 0 || C < 0 || HxW < 0 || G < 1 || C % G != 0) return B2N_ERR_BAD_ARG;
+  if (C == 0) return B2N_OK;
+  if (!dy || !x || !mean || !rstd) return (N == 0 || HxW == 0) && !dx ? B2N_OK : B2N_ERR_BAD_ARG;
+  if ((C / G) * HxW > 0x7fffffffLL || C > 0x7fffffffLL || HxW > 0x7fffffffLL) return B2N_ERR_TOO_LARGE;
+  if (!device_ready()) return B2N_ERR_CUDA;
+  if (gamma == nullptr && dgamma == nullptr && dbeta == nullptr) w_dtype = x_dtype;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define B2N_GNB(T, WT, ST) return group_norm_bwd_launch<T, WT, ST>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, N, C, HxW, G, st)
+  if (x_dtype == B2N_F32 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GNB(float, float, float);
+  if (x_dtype == B2N_BF16 && w_dtype == B2N_BF16 && stat_dtype == B2N_BF16) B2N_GNB(bf16, bf16, bf16);
+  if (x_dtype == B2N_BF16 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GNB(bf16, float, float);
+  if (x_dtype == B2N_F16 && w_dtype == B2N_F16 && stat_dtype == B2N_F16) B2N_GNB(f16, f16, f16);
+  if (x_dtype == B2N_F16 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GNB(f16, float, float);
+#undef B2N_GNB
   return B2N_ERR_UNSUPPORTED_DTYPE;
 }
 
