@@ -13,7 +13,7 @@ import b200norm
 from b200norm import capi
 from oracle import aten_oracle as ao
 
-from gpu_util import DEV, wgrad_gate
+from gpu_util import DEV, forced_path, wgrad_gate
 
 pytestmark = pytest.mark.gpu
 
@@ -75,6 +75,8 @@ def test_group_norm_backward(shape, G, dt, wdt, affine):
     dev = lambda t: None if t is None else t.to(DEV)
     _, mean, rstd = capi.native_group_norm(dev(x), dev(g), None, N, C, HxW, G, 1e-5)
     dx, dg, db = capi.native_group_norm_backward(dev(dy), dev(x), mean, rstd, dev(g), N, C, HxW, G, (True, True, True))
+    vec = 16 // x.element_size()
+    assert capi.last_path() == ("ring" if HxW % vec == 0 and (C // G) * HxW <= 8192 else "generic")
     f32 = lambda t: None if t is None else t.float()
     m32, r32 = mean.float().cpu(), rstd.float().cpu()
     rdx, _, _ = torch.ops.aten.native_group_norm_backward(dy.float(), x.float(), m32, r32, f32(g), N, C, HxW, G,
@@ -97,6 +99,14 @@ def test_group_norm_backward(shape, G, dt, wdt, affine):
     # masked-off outputs are not computed
     only_dx = capi.native_group_norm_backward(dev(dy), dev(x), mean, rstd, dev(g), N, C, HxW, G, (True, False, False))
     assert only_dx[1] is None and only_dx[2] is None and torch.equal(only_dx[0], dx)
+    # the plain kernels (what shapes the ring cannot take run) pass the same gate on every shape
+    with forced_path(b200norm.PATH_GENERIC):
+        gdx = capi.native_group_norm_backward(dev(dy), dev(x), mean, rstd, dev(g), N, C, HxW, G, (True, False, False))[0]
+        assert capi.last_path() == "generic"
+    if dt == torch.float32:
+        assert ao.fp32_err(gdx, rdx) <= 1.0
+    else:
+        assert ao.lowp_mismatch(gdx, rdx.to(dt))[0] == 0
     assert capi.device_status() == 0
 
 

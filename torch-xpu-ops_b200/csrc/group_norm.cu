@@ -209,15 +209,27 @@ group_norm_bwd_wgrad_kernel(const T* __restrict__ dy, const T* __restrict__ x, c
     const T* gr = dy + (n * C + c) * static_cast<int64_t>(HxW);
     float a = 0.0f, b = 0.0f;  // sum dy * (x - mu), sum dy of this run
     if constexpr (V > 1) {
-      for (int v = l; v < HxW / V; v += 32) {
-        const Vec<T, V> xv = ld_vec<T, V>(xr + v * V), gv = ld_vec<T, V>(gr + v * V);
+      const int nv = HxW / V;
+      auto add_pair = [&](const Vec<T, V>& xv, const Vec<T, V>& gv) {
 #pragma unroll
         for (int e = 0; e < V; ++e) {
           const float d = to_acc<float>(gv.v[e]);
           a = fmaf(d, to_acc<float>(xv.v[e]) - mu, a);
           b += d;
         }
+      };
+      int v = l;
+      for (; v + 96 < nv; v += 128) {  // four vector pairs in flight per lane
+        Vec<T, V> xv[4], gv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          xv[u] = ld_vec<T, V>(xr + (v + 32 * u) * V);
+          gv[u] = ld_vec<T, V>(gr + (v + 32 * u) * V);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) add_pair(xv[u], gv[u]);
       }
+      for (; v < nv; v += 32) add_pair(ld_vec<T, V>(xr + v * V), ld_vec<T, V>(gr + v * V));
     } else {
       for (int j = l; j < HxW; j += 32) {
         const float d = to_acc<float>(gr[j]);
@@ -600,6 +612,29 @@ int group_norm_launch(const void* x, const void* gamma, const void* beta, void* 
   return launched();
 }
 
+template <typename T, typename WT, typename ST, int GROUP, bool FULL = false>
+int group_norm_bwd_ring_launch(const RingPlan& p, const T* dy, const T* x, const ST* mean, const ST* rstd, const WT* gamma, T* dx,
+                               int64_t rows, int64_t L, int64_t G, int64_t D, int64_t HxW, cudaStream_t st) {
+  constexpr int VPT = 16 / Pack16<T>::VEC;
+  if constexpr (!FULL) {
+    if (L == static_cast<int64_t>(GROUP) * 16)
+      return group_norm_bwd_ring_launch<T, WT, ST, GROUP, true>(p, dy, x, mean, rstd, gamma, dx, rows, L, G, D, HxW, st);
+  }
+  auto kernel = group_norm_bwd_ring_kernel<T, WT, ST, GROUP, VPT, FULL>;
+  static std::atomic<uint64_t> done{0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError());
+  const uint64_t bit = 1ull << (dev & 63);
+  if (!(done.load(std::memory_order_acquire) & bit)) {
+    if (int e = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, device_info().max_smem_optin)))
+      return e;
+    done.fetch_or(bit, std::memory_order_release);
+  }
+  return launch_pdl(kernel, dim3(p.grid), dim3(kRingBlock), p.smem, st, dy, x, mean, rstd, gamma, dx, rows, static_cast<int>(L),
+                    static_cast<int>(G), static_cast<int>(D), static_cast<int>(HxW), p.stages | (p.lag << 8), p.rpg,
+                    device_status_ptr(), next_tile_counter());
+}
+
 template <typename T, typename WT, typename ST>
 int group_norm_bwd_launch(const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma, void* dx,
                           void* dgamma, void* dbeta, int64_t N, int64_t C, int64_t HxW, int64_t G, cudaStream_t st) {
@@ -611,7 +646,30 @@ int group_norm_bwd_launch(const void* dy, const void* x, const void* mean, const
   const ST* mp = static_cast<const ST*>(mean);
   const ST* rp = static_cast<const ST*>(rstd);
   ProfileScope prof("group_norm_bwd", st);
-  if (dx != nullptr) {
+  bool dx_done = dx == nullptr;
+  if (!dx_done && forced_path() != B2N_PATH_GENERIC && vec && rows < 0x7fffffffLL) {
+    // dX on the shared-memory ring, like a layer-norm backward row of the same length
+    const DeviceInfo& di = device_info();
+    const RingPlan p = plan_ring(rows, L, sizeof(T), 2, 16, persistent_ctas(di.sm_count), di.max_smem_optin);
+    if (p.ok) {
+      note_path("ring");
+      const WT* wp = static_cast<const WT*>(gamma);
+      T* dp = static_cast<T*>(dx);
+      int e;
+      switch (p.group) {
+        case 32: e = group_norm_bwd_ring_launch<T, WT, ST, 32>(p, gp, xp, mp, rp, wp, dp, rows, L, G, D, HxW, st); break;
+        case 64: e = group_norm_bwd_ring_launch<T, WT, ST, 64>(p, gp, xp, mp, rp, wp, dp, rows, L, G, D, HxW, st); break;
+        case 128: e = group_norm_bwd_ring_launch<T, WT, ST, 128>(p, gp, xp, mp, rp, wp, dp, rows, L, G, D, HxW, st); break;
+        case 256: e = group_norm_bwd_ring_launch<T, WT, ST, 256>(p, gp, xp, mp, rp, wp, dp, rows, L, G, D, HxW, st); break;
+        default: e = group_norm_bwd_ring_launch<T, WT, ST, 512>(p, gp, xp, mp, rp, wp, dp, rows, L, G, D, HxW, st); break;
+      }
+      if (e) return e;
+      dx_done = true;
+    }
+  }
+  if (!dx_done && forced_path() == B2N_PATH_RING) return B2N_ERR_BAD_ARG;
+  if (!dx_done) {
+    note_path("generic");
     const int threads = L >= 8192 ? 512 : (L >= 2048 ? 256 : 128);
     const int64_t cap = static_cast<int64_t>(device_info().sm_count) * (2048 / threads);
     const int grid = static_cast<int>(rows < cap ? rows : cap);
