@@ -237,6 +237,14 @@ int b2n_group_norm_fwd(const void* x, const void* gamma, const void* beta, void*
 int b2n_group_norm_bwd(const void* dy, const void* x, const void* mean, const void* rstd,
                        const void* gamma, void* dx, void* dgamma, void* dbeta, int64_t N, int64_t C,
                        int64_t HxW, int64_t G, int x_dtype, int w_dtype, int stat_dtype, void* stream);
+/* The same with a caller-allocated scratch area (size from b2n_group_norm_bwd_workspace_bytes, 0: none is useful;
+ * contents ignored on entry; 16-byte aligned): the weight gradients are then summed by every SM whatever C is, parts
+ * added in a fixed order, instead of by one CTA per channel. */
+size_t b2n_group_norm_bwd_workspace_bytes(int64_t N, int64_t C, int64_t HxW, int x_dtype);
+int b2n_group_norm_bwd_ws(const void* dy, const void* x, const void* mean, const void* rstd,
+                          const void* gamma, void* dx, void* dgamma, void* dbeta, int64_t N, int64_t C,
+                          int64_t HxW, int64_t G, int x_dtype, int w_dtype, int stat_dtype, void* workspace,
+                          size_t workspace_bytes, void* stream);
 
 /* BatchNorm statistics of a contiguous [N, C, HxW] tensor, per channel over N and HxW, in fp32:
  * mean[C] and, mode 0, second[C] = 1 / sqrt(biased var + eps) (batch_norm_stats); mode 1,

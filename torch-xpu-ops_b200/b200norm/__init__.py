@@ -85,6 +85,8 @@ def load_library() -> ctypes.CDLL:
         "b2n_rms_norm_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, sz, i64, i64, i32, i32, vp]),
         "b2n_group_norm_fwd": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, dbl, i32, i32, i32, vp]),
         "b2n_group_norm_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, i32, vp]),
+        "b2n_group_norm_bwd_workspace_bytes": (sz, [i64, i64, i64, i32]),
+        "b2n_group_norm_bwd_ws": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, i32, vp, sz, vp]),
         "b2n_batch_norm_stats": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, dbl, dbl, i32, i32, i32, vp]),
         "b2n_batch_norm_stats_workspace_bytes": (sz, [i64, i64, i64, i32]),
         "b2n_batch_norm_stats_ws": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, dbl, dbl, i32, i32, i32, vp, sz, vp]),

@@ -459,9 +459,13 @@ def native_group_norm_backward(grad_out, input, mean, rstd, weight, N, C, HxW, g
                     t.zero_()
         else:
             with torch.cuda.device(x.device):
-                _check(lib.b2n_group_norm_bwd(_ptr(dy), _ptr(x), _ptr(m), _ptr(r), _ptr(g), _ptr(dx), _ptr(dgamma), _ptr(dbeta),
-                                              N, C, HxW, group, _dt(x.dtype), wdt, _dt(m.dtype), _stream(x)),
-                       "b2n_group_norm_bwd")
+                nbytes = int(lib.b2n_group_norm_bwd_workspace_bytes(N, C, HxW, _dt(x.dtype))) if (dgamma is not None or
+                                                                                                 dbeta is not None) else 0
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
+                _check(lib.b2n_group_norm_bwd_ws(_ptr(dy), _ptr(x), _ptr(m), _ptr(r), _ptr(g), _ptr(dx), _ptr(dgamma),
+                                                 _ptr(dbeta), N, C, HxW, group, _dt(x.dtype), wdt, _dt(m.dtype),
+                                                 _ptr(ws) if ws is not None else None, nbytes, _stream(x)),
+                       "b2n_group_norm_bwd_ws")
     return dx, dgamma, dbeta
 
 

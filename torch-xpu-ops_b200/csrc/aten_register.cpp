@@ -311,12 +311,15 @@ std::tuple<Tensor, Tensor, Tensor> native_group_norm_backward(const Tensor& grad
     if (dgamma.defined()) dgamma.zero_();
     if (dbeta.defined()) dbeta.zero_();
   } else if (dX.defined() || dgamma.defined() || dbeta.defined()) {
-    check_status(b2n_group_norm_bwd(dY.const_data_ptr(), X.const_data_ptr(), M.const_data_ptr(), R.const_data_ptr(),
-                                    gamma->defined() ? gamma->const_data_ptr() : nullptr,
-                                    dX.defined() ? dX.mutable_data_ptr() : nullptr,
-                                    dgamma.defined() ? dgamma.mutable_data_ptr() : nullptr,
-                                    dbeta.defined() ? dbeta.mutable_data_ptr() : nullptr, N, C, HxW, group, xdt, wdt,
-                                    to_b2n_dtype(M.scalar_type(), op), cur_stream()),
+    const size_t ws_bytes = (dgamma.defined() || dbeta.defined()) ? b2n_group_norm_bwd_workspace_bytes(N, C, HxW, xdt) : 0;
+    Tensor ws = ws_bytes ? at::empty({static_cast<int64_t>(ws_bytes)}, X.options().dtype(at::kByte)) : Tensor();
+    check_status(b2n_group_norm_bwd_ws(dY.const_data_ptr(), X.const_data_ptr(), M.const_data_ptr(), R.const_data_ptr(),
+                                       gamma->defined() ? gamma->const_data_ptr() : nullptr,
+                                       dX.defined() ? dX.mutable_data_ptr() : nullptr,
+                                       dgamma.defined() ? dgamma.mutable_data_ptr() : nullptr,
+                                       dbeta.defined() ? dbeta.mutable_data_ptr() : nullptr, N, C, HxW, group, xdt, wdt,
+                                       to_b2n_dtype(M.scalar_type(), op), ws_bytes ? ws.mutable_data_ptr() : nullptr, ws_bytes,
+                                       cur_stream()),
                  "group_norm_bwd");
   }
   return std::make_tuple(std::move(dX), std::move(dgamma), std::move(dbeta));

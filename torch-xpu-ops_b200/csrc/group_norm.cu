@@ -541,6 +541,102 @@ inline BnStatsPlan bn_stats_plan(int64_t N, int64_t C, int64_t HxW, int vec, int
   return p;
 }
 
+// ---- group norm weight gradients over every SM (scratch memory) --------------------------------------------------
+// The same cut as the BatchNorm statistics: the C * N * HxW / V vectors of all channels, laid end to end, in
+// gridDim.x equal ranges.  For its part of a channel a CTA accumulates
+//   sum over vectors of rstd[n, g] * sum_e dy_e * (x_e - mean[n, g])   and   sum dy
+// (linear in the vectors, so parts simply add), statistics looked up per vector (a run's vectors share them: L1),
+// and leaves the pair in partial[c][slot]; a second kernel adds a channel's parts in slot order.
+template <typename T, typename ST>
+__global__ void __launch_bounds__(512, 2)
+group_norm_wgrad_range_kernel(const T* __restrict__ dy, const T* __restrict__ x, const ST* __restrict__ mean,
+                              const ST* __restrict__ rstd, int64_t N, int C, int G, int64_t HxW, int64_t Gv, int max_slots,
+                              float2* __restrict__ partial) {
+  using P = Pack16<T>;
+  constexpr int V = P::VEC, VH = V / 2;
+  __shared__ float scratch[64];
+  const int64_t HV = HxW / V, TV = N * HV, sample_stride = static_cast<int64_t>(C) * HxW;
+  const int64_t total = static_cast<int64_t>(C) * TV;
+  const int D = C / G;
+  int64_t g0 = static_cast<int64_t>(blockIdx.x) * Gv;
+  const int64_t g1 = g0 + Gv < total ? g0 + Gv : total;
+  int64_t c = g0 / TV;
+  const int64_t stride = blockDim.x, step_n = stride / HV, step_j = stride % HV;
+  while (g0 < g1) {
+    const int64_t cbase = c * TV, cend = cbase + TV;
+    const int64_t seg_end = g1 < cend ? g1 : cend;
+    const int64_t coff = c * HxW;
+    const int grp = static_cast<int>(c) / D;
+    float sg = 0.0f, sb = 0.0f;
+    auto add_vec = [&](const uint4& wx, const uint4& wd, int64_t n) {
+      const float mu = to_acc<float>(mean[n * G + grp]), rs = to_acc<float>(rstd[n * G + grp]);
+      float2 xv[VH], dv[VH];
+      P::unpack2(wx, xv);
+      P::unpack2(wd, dv);
+      const float2 nmu = make_float2(-mu, -mu);
+      float2 a = make_float2(0.0f, 0.0f), b = make_float2(0.0f, 0.0f);
+#pragma unroll
+      for (int e = 0; e < VH; ++e) {
+        a = fma2(dv[e], add2(xv[e], nmu), a);
+        b = add2(b, dv[e]);
+      }
+      sg = fmaf(a.x + a.y, rs, sg);
+      sb += b.x + b.y;
+    };
+    auto advance = [&](int64_t& n, int64_t& j) {
+      n += step_n;
+      j += step_j;
+      if (j >= HV) { j -= HV; ++n; }
+    };
+    const int64_t end = seg_end - cbase;
+    int64_t idx = g0 - cbase + threadIdx.x;
+    int64_t n = idx / HV, j = idx - n * HV;
+    for (; idx + 3 * stride < end; idx += 4 * stride) {  // four vector pairs in flight per thread
+      int64_t off[4], ns[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        off[u] = coff + n * sample_stride + j * V;
+        ns[u] = n;
+        advance(n, j);
+      }
+      uint4 wx[4], wd[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        wx[u] = __ldg(reinterpret_cast<const uint4*>(x + off[u]));
+        wd[u] = __ldg(reinterpret_cast<const uint4*>(dy + off[u]));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) add_vec(wx[u], wd[u], ns[u]);
+    }
+    for (; idx < end; idx += stride) {
+      const int64_t off = coff + n * sample_stride + j * V;
+      add_vec(__ldg(reinterpret_cast<const uint4*>(x + off)), __ldg(reinterpret_cast<const uint4*>(dy + off)), n);
+      advance(n, j);
+    }
+    block_sum2(sg, sb, scratch);
+    if (threadIdx.x == 0) partial[c * max_slots + (static_cast<int64_t>(blockIdx.x) - cbase / Gv)] = make_float2(sg, sb);
+    g0 = seg_end;
+    ++c;
+  }
+}
+// One thread per channel: the channel's parts in slot order (the same bits on every run).
+template <typename WT>
+__global__ void group_norm_wgrad_finish_kernel(const float2* __restrict__ partial, WT* __restrict__ dgamma, WT* __restrict__ dbeta,
+                                               int C, int64_t TV, int64_t Gv, int max_slots) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int64_t cbase = static_cast<int64_t>(c) * TV;
+  const int nslots = static_cast<int>((cbase + TV - 1) / Gv - cbase / Gv) + 1;
+  float sg = 0.0f, sb = 0.0f;
+  for (int k = 0; k < nslots; ++k) {
+    const float2 pk = partial[static_cast<int64_t>(c) * max_slots + k];
+    sg += pk.x;
+    sb += pk.y;
+  }
+  if (dgamma) dgamma[c] = from_acc<WT>(sg);
+  if (dbeta) dbeta[c] = from_acc<WT>(sb);
+}
+
 template <typename T, typename WT, typename ST, int GROUP, bool FULL = false>
 int group_norm_ring_launch(const RingPlan& p, const T* x, const WT* gamma, const WT* beta, T* y, ST* mean, ST* rstd,
                            int64_t rows, int64_t L, int64_t G, int64_t D, int64_t HxW, double eps, cudaStream_t st) {
@@ -637,7 +733,8 @@ int group_norm_bwd_ring_launch(const RingPlan& p, const T* dy, const T* x, const
 
 template <typename T, typename WT, typename ST>
 int group_norm_bwd_launch(const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma, void* dx,
-                          void* dgamma, void* dbeta, int64_t N, int64_t C, int64_t HxW, int64_t G, cudaStream_t st) {
+                          void* dgamma, void* dbeta, int64_t N, int64_t C, int64_t HxW, int64_t G, void* workspace,
+                          size_t workspace_bytes, cudaStream_t st) {
   const int64_t rows = N * G, D = C / G, L = D * HxW;
   constexpr int V = 16 / sizeof(T);
   const bool vec = HxW % V == 0 && is_aligned(x, 16) && is_aligned(dy, 16) && (dx == nullptr || is_aligned(dx, 16));
@@ -681,6 +778,19 @@ int group_norm_bwd_launch(const void* dy, const void* x, const void* mean, const
       group_norm_bwd_dx_kernel<T, WT, ST, 1><<<grid, threads, 0, st>>>(gp, xp, mp, rp, wp, static_cast<T*>(dx), rows,
                                                                        static_cast<int>(G), static_cast<int>(D), static_cast<int>(HxW));
     if (int e = launched()) return e;
+  }
+  if ((dgamma != nullptr || dbeta != nullptr) && vec && forced_path() != B2N_PATH_GENERIC) {
+    // with scratch memory: one balanced wave of CTAs over all channels, then a fixed-order finish
+    const BnStatsPlan p = bn_stats_plan(N, C, HxW, V, device_info().sm_count);
+    if (p.grid > 0 && workspace != nullptr && workspace_bytes >= p.bytes && is_aligned(workspace, 8)) {
+      float2* partial = static_cast<float2*>(workspace);
+      group_norm_wgrad_range_kernel<T, ST><<<static_cast<unsigned>(p.grid), 512, 0, st>>>(
+          gp, xp, mp, rp, N, static_cast<int>(C), static_cast<int>(G), HxW, p.G, p.max_slots, partial);
+      if (int e = launched()) return e;
+      group_norm_wgrad_finish_kernel<WT><<<static_cast<unsigned>((C + 255) / 256), 256, 0, st>>>(
+          partial, static_cast<WT*>(dgamma), static_cast<WT*>(dbeta), static_cast<int>(C), N * (HxW / V), p.G, p.max_slots);
+      return launched();
+    }
   }
   if (dgamma != nullptr || dbeta != nullptr) {
     const int threads = N * HxW >= 16384 ? 512 : 128;
@@ -760,9 +870,20 @@ int b2n_group_norm_fwd(const void* x, const void* gamma, const void* beta, void*
   return B2N_ERR_UNSUPPORTED_DTYPE;
 }
 
+size_t b2n_group_norm_bwd_workspace_bytes(int64_t N, int64_t C, int64_t HxW, int x_dtype) {
+  return b2n_batch_norm_stats_workspace_bytes(N, C, HxW, x_dtype);  // the same cut of the same layout
+}
+
 int b2n_group_norm_bwd(const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma, void* dx,
                        void* dgamma, void* dbeta, int64_t N, int64_t C, int64_t HxW, int64_t G, int x_dtype, int w_dtype,
                        int stat_dtype, void* stream) {
+  return b2n_group_norm_bwd_ws(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, N, C, HxW, G, x_dtype, w_dtype, stat_dtype, nullptr, 0,
+                               stream);
+}
+
+int b2n_group_norm_bwd_ws(const void* dy, const void* x, const void* mean, const void* rstd, const void* gamma, void* dx,
+                          void* dgamma, void* dbeta, int64_t N, int64_t C, int64_t HxW, int64_t G, int x_dtype, int w_dtype,
+                          int stat_dtype, void* workspace, size_t workspace_bytes, void* stream) {
   if (N < 0 || C < 0 || HxW < 0 || G < 1 || C % G != 0) return B2N_ERR_BAD_ARG;
   if (C == 0) return B2N_OK;
   if (!dy || !x || !mean || !rstd) return (N == 0 || HxW == 0) && !dx ? B2N_OK : B2N_ERR_BAD_ARG;
@@ -770,7 +891,8 @@ int b2n_group_norm_bwd(const void* dy, const void* x, const void* mean, const vo
   if (!device_ready()) return B2N_ERR_CUDA;
   if (gamma == nullptr && dgamma == nullptr && dbeta == nullptr) w_dtype = x_dtype;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define B2N_GNB(T, WT, ST) return group_norm_bwd_launch<T, WT, ST>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, N, C, HxW, G, st)
+#define B2N_GNB(T, WT, ST) \
+  return group_norm_bwd_launch<T, WT, ST>(dy, x, mean, rstd, gamma, dx, dgamma, dbeta, N, C, HxW, G, workspace, workspace_bytes, st)
   if (x_dtype == B2N_F32 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GNB(float, float, float);
   if (x_dtype == B2N_BF16 && w_dtype == B2N_BF16 && stat_dtype == B2N_BF16) B2N_GNB(bf16, bf16, bf16);
   if (x_dtype == B2N_BF16 && w_dtype == B2N_F32 && stat_dtype == B2N_F32) B2N_GNB(bf16, float, float);
