@@ -480,6 +480,7 @@ batch_norm_stats_range_kernel(const T* __restrict__ x, int64_t N, int C, int64_t
                               float2* __restrict__ partial) {
   constexpr int V = 16 / sizeof(T);
   __shared__ float scratch[64];
+  pdl_launch_dependents();  // the finish kernel may take its place on the SMs; it waits for this grid to complete
   const int64_t HV = HxW / V, TV = N * HV, sample_stride = static_cast<int64_t>(C) * HxW;
   const int64_t total = static_cast<int64_t>(C) * TV;
   int64_t g0 = static_cast<int64_t>(blockIdx.x) * G;
@@ -510,6 +511,7 @@ batch_norm_stats_finish_kernel(const T* __restrict__ x, float* __restrict__ mean
   const int64_t HV = HxW / V, TV = N * HV, sample_stride = static_cast<int64_t>(C) * HxW;
   const int64_t cbase = static_cast<int64_t>(c) * TV;
   const int nslots = static_cast<int>((cbase + TV - 1) / G - cbase / G) + 1;  // CTAs of the range kernel that touched channel c
+  pdl_wait();  // launched as a programmatic dependent of the range kernel: its partial sums are complete from here on
   float s = 0.0f, q = 0.0f;
   for (int k = 0; k < nslots; ++k) {
     const float2 pk = partial[static_cast<int64_t>(c) * max_slots + k];
@@ -558,6 +560,7 @@ group_norm_wgrad_range_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   const int64_t HV = HxW / V, TV = N * HV, sample_stride = static_cast<int64_t>(C) * HxW;
   const int64_t total = static_cast<int64_t>(C) * TV;
   const int D = C / G;
+  pdl_launch_dependents();
   int64_t g0 = static_cast<int64_t>(blockIdx.x) * Gv;
   const int64_t g1 = g0 + Gv < total ? g0 + Gv : total;
   int64_t c = g0 / TV;
@@ -624,6 +627,7 @@ template <typename WT>
 __global__ void group_norm_wgrad_finish_kernel(const float2* __restrict__ partial, WT* __restrict__ dgamma, WT* __restrict__ dbeta,
                                                int C, int64_t TV, int64_t Gv, int max_slots) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();  // a programmatic dependent of the range kernel
   if (c >= C) return;
   const int64_t cbase = static_cast<int64_t>(c) * TV;
   const int nslots = static_cast<int>((cbase + TV - 1) / Gv - cbase / Gv) + 1;
@@ -787,9 +791,9 @@ int group_norm_bwd_launch(const void* dy, const void* x, const void* mean, const
       group_norm_wgrad_range_kernel<T, ST><<<static_cast<unsigned>(p.grid), 512, 0, st>>>(
           gp, xp, mp, rp, N, static_cast<int>(C), static_cast<int>(G), HxW, p.G, p.max_slots, partial);
       if (int e = launched()) return e;
-      group_norm_wgrad_finish_kernel<WT><<<static_cast<unsigned>((C + 255) / 256), 256, 0, st>>>(
-          partial, static_cast<WT*>(dgamma), static_cast<WT*>(dbeta), static_cast<int>(C), N * (HxW / V), p.G, p.max_slots);
-      return launched();
+      return launch_pdl(group_norm_wgrad_finish_kernel<WT>, dim3(static_cast<unsigned>((C + 255) / 256)), dim3(256), 0, st,
+                        static_cast<const float2*>(partial), static_cast<WT*>(dgamma), static_cast<WT*>(dbeta), static_cast<int>(C),
+                        N * (HxW / V), p.G, p.max_slots);
     }
   }
   if (dgamma != nullptr || dbeta != nullptr) {
@@ -824,10 +828,9 @@ int batch_norm_stats_launch(const void* x, float* mean, float* second, void* run
       batch_norm_stats_range_kernel<T><<<static_cast<unsigned>(p.grid), 512, 0, st>>>(xp, N, static_cast<int>(C), HxW, p.G,
                                                                                     p.max_slots, partial);
       if (int e = launched()) return e;
-      batch_norm_stats_finish_kernel<T, RT><<<static_cast<unsigned>(C), 512, 0, st>>>(
-          xp, mean, second, rm, rv, N, static_cast<int>(C), HxW, static_cast<float>(eps), static_cast<float>(momentum), mode,
-          p.G, p.max_slots, partial);
-      return launched();
+      return launch_pdl(batch_norm_stats_finish_kernel<T, RT>, dim3(static_cast<unsigned>(C)), dim3(512), 0, st, xp, mean, second,
+                        rm, rv, N, static_cast<int>(C), HxW, static_cast<float>(eps), static_cast<float>(momentum), mode, p.G,
+                        p.max_slots, static_cast<const float2*>(partial));
     }
     batch_norm_stats_channel_kernel<T, RT><<<static_cast<unsigned>(C), 512, 0, st>>>(
         xp, mean, second, rm, rv, N, static_cast<int>(C), HxW, static_cast<float>(eps), static_cast<float>(momentum), mode);
