@@ -249,9 +249,9 @@ struct TmaTilePlan {
   int segs = 0;      // threads per line
 };
 
-// Widest tile first: every thread busy (512 column groups x segments), at least three stages in shared memory
-// (two when nothing narrower than 128-byte runs would give three), not wider than the tensor, and narrower
-// while there are fewer tiles than two per SM.
+// Widest tile first: every thread busy (512 column groups x segments), two stages (backward) or three (forward, two
+// when nothing narrower than 128-byte runs would give three) in shared memory, not wider than the tensor, and
+// narrower while there are fewer tiles than two per SM.
 inline TmaTilePlan plan_tma_tile(int64_t outer, int64_t N, int64_t inner, int es, int nin, bool bwd, int64_t avail, int sms) {
   TmaTilePlan p;
   const int vec = 16 / es, cpt = es == 2 ? 2 : 1, line = 128 / es;  // elements per 16 bytes / per thread / per 128-byte line
@@ -259,10 +259,29 @@ inline TmaTilePlan plan_tma_tile(int64_t outer, int64_t N, int64_t inner, int es
   const int64_t npad = (N + p.NB - 1) / p.NB * p.NB;
   p.reg = !bwd && N <= 8 * kTmaRegRows;
   int segs = p.reg ? static_cast<int>((N + kTmaRegRows - 1) / kTmaRegRows) : 1;
+  if (p.reg) {
+    // Column groups come in whole warps (32), so several segment counts can give the same tile width; among those,
+    // take the one that leaves the fewest threads and row slots (blocks of four) idle — the forward in registers is
+    // bound by instruction issue.  Never a narrower tile for it: measured, width and long segments matter more
+    // (N = 200: 7 segments x 64 groups = 448 threads -> 8 x 64 = 512, +6 %; N = 150 narrowed from 96 to 64 groups: -16 %).
+    const int smin = segs, grp0 = kTmaConsumers / smin / 32 * 32;
+    double best = -1.0;
+    for (int sg = smin; sg <= 16 && kTmaConsumers / sg / 32 * 32 == grp0 && grp0 > 0; ++sg) {
+      const int rows = static_cast<int>((N + sg - 1) / sg), slots = (rows + 3) / 4 * 4;
+      const double util = (static_cast<double>(N) / (sg * slots)) * (static_cast<double>(grp0) * sg / kTmaConsumers);
+      if (util > best + 1e-9) {
+        best = util;
+        segs = sg;
+      }
+    }
+  }
   int64_t wt = static_cast<int64_t>(kTmaConsumers / segs) * cpt;
   const int64_t row_bytes = npad * es * nin;  // shared memory per column of a tile
-  int64_t fit = avail / 3 / row_bytes;
-  if (fit < line) fit = avail / 2 / row_bytes;  // two stages rather than runs below 128 bytes
+  // Width first, stages second: the backward (two input tiles per stage) is sized for TWO stages — runs twice as wide
+  // measured 4 to 18 % faster than a third stage of narrow ones (128-byte runs half a megabyte apart are what DRAM
+  // likes least).  The forward keeps three stages where they leave at least one line per run.
+  int64_t fit = avail / (bwd ? 2 : 3) / row_bytes;
+  if (fit < line) fit = avail / 2 / row_bytes;
   if (wt > fit) wt = fit;
   if (wt > inner) wt = inner;
   while (wt > 2 * line && outer * ((inner + wt - 1) / wt) < 2ll * sms) wt /= 2;
