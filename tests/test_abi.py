@@ -131,7 +131,7 @@ def test_spatial_softmax_tile_plans_keep_their_invariants():
                             seen_reg += reg
                             seen_multibox += nx > 1
                             assert (w * esize) % 128 == 0 and 0 < w <= 256 and nx >= 1
-                            assert nb == min(n, 256)
+                            assert nb == -(-n // -(-n // 256)) and nb <= 256   # boxes of equal height
                             groups = w * nx // cpt
                             assert groups % 32 == 0 and groups * segs <= consumers and segs >= 1
                             assert segs == 1 or groups // 32 <= 15          # named barriers 1..15

@@ -255,9 +255,10 @@ struct TmaTilePlan {
 inline TmaTilePlan plan_tma_tile(int64_t outer, int64_t N, int64_t inner, int es, int nin, bool bwd, int64_t avail, int sms) {
   TmaTilePlan p;
   const int vec = 16 / es, cpt = es == 2 ? 2 : 1, line = 128 / es;  // elements per 16 bytes / per thread / per 128-byte line
-  p.NB = N <= 256 ? static_cast<int>(N) : 256;
+  const int64_t nboxes = (N + 255) / 256;                 // boxes of at most 256 rows ...
+  p.NB = static_cast<int>((N + nboxes - 1) / nboxes);     // ... of equal height: at most nboxes - 1 padding rows in all
   const int64_t npad = (N + p.NB - 1) / p.NB * p.NB;
-  p.reg = !bwd && N <= 8 * kTmaRegRows;
+  p.reg = !bwd && N <= 16 * kTmaRegRows;  // up to 16 threads per line (one warp of column groups left): 128-byte runs
   int segs = p.reg ? static_cast<int>((N + kTmaRegRows - 1) / kTmaRegRows) : 1;
   if (p.reg) {
     // Column groups come in whole warps (32), so several segment counts can give the same tile width; among those,

@@ -3,7 +3,7 @@
 // The tensor is [outer, N, inner]; a line runs over N with stride `inner`.  A tile is all N line elements
 // x W adjacent inner positions: N runs of W elements, `inner` elements apart.  That is exactly what a
 // tiled bulk-tensor copy moves with ONE instruction: the tensor is described to the TMA unit as a
-// rank-3 tensor (inner, N, outer), a tile is a box of W x NB x 1 elements (NB = N, or 256 rows at a time
+// rank-3 tensor (inner, N, outer), a tile is a box of W x NB x 1 elements (NB = N, or equal boxes of at most 256 rows
 // for longer lines), and `cp.async.bulk.tensor.3d` brings the box into shared memory — densely packed,
 // row pitch W — while completing a transaction count on an mbarrier; the mirror instruction sends the
 // result back.  Coordinates past the tensor's edge are filled with zeros on the way in and dropped on
@@ -12,7 +12,7 @@
 //
 // A tile is NX boxes wide (W <= 256 elements each) so that short lines still make tiles of tens of KB, and a
 // line is shared by `segs` threads.  In the forward, when a thread's share of a line is at most 32 elements
-// (lines up to 256 long), the thread keeps it in REGISTERS: one shared-memory read and ONE exp per element
+// (lines up to 512 long), the thread keeps it in REGISTERS: one shared-memory read and ONE exp per element
 // (exp(x - max) serves the sum and the output) — with two exps per element the kernel is bound by the
 // special-function unit, not by HBM.
 //
