@@ -7,8 +7,9 @@
 // for longer lines), and `cp.async.bulk.tensor.3d` brings the box into shared memory — densely packed,
 // row pitch W — while completing a transaction count on an mbarrier; the mirror instruction sends the
 // result back.  Coordinates past the tensor's edge are filled with zeros on the way in and dropped on
-// the way out, so edge tiles need no special case.  Every tile starts at x = k * W with W * sizeof(T) a
-// multiple of 16 bytes, as the bulk-tensor copy requires.
+// the way out, so edge tiles need no special case.  Every box starts at x = k * W with W * sizeof(T) a
+// whole number of 128-byte lines: the copy's start is then 16-byte aligned in global memory, as it must be, and
+// every box lands on a 128-byte boundary of shared memory, whatever N is.
 //
 // A tile is NX boxes wide (W <= 256 elements each) so that short lines still make tiles of tens of KB, and a
 // line is shared by `segs` threads.  In the forward, when a thread's share of a line is at most 32 elements
@@ -17,11 +18,12 @@
 // special-function unit, not by HBM.
 //
 // Persistent CTAs, one per SM: a producer thread keeps S tiles in flight (loads of the next tiles and
-// the store of the previous one overlap the arithmetic); 512 consumer threads work on the tile in shared
-// memory as the tile kernels of softmax_generic.cuh do — a line shared by `segs` threads, each walking
-// every segs-th element, consecutive threads on consecutive addresses, partial results combined in
-// segment order — and leave the result in place.  Every element crosses HBM once each way.
-// No cluster multicast; every wait bounded.
+// the store of the previous one overlap the arithmetic; a stage is refilled as soon as its store has READ it);
+// 512 consumer threads work on the tile in shared memory — a line shared by `segs` threads, each taking every
+// segs-th element, consecutive threads on consecutive addresses, partial results combined in segment order —
+// and leave the result in place.  The threads that share lines (32 adjacent column groups x segs warps) form a
+// team with a named barrier of its own; the teams never meet, so their phases overlap.  Every element crosses
+// HBM once each way.  No cluster multicast; every wait bounded.
 #pragma once
 #include <cuda.h>
 
