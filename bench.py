@@ -87,7 +87,7 @@ class Cfg4LayerNorm(Workload):
         fwd = 2 * rows * n * 2 + 2 * n * 4 + 2 * rows * 4
         bwd = 3 * rows * n * 2 + 2 * rows * 4 + n * 4 + 2 * n * 4
         return {"total": fwd + bwd, "layer_norm_fwd_ring": fwd, "layer_norm_bwd_ring": bwd,
-                "layer_norm_fwd_slab": fwd, "layer_norm_bwd_slab": bwd,
+                "layer_norm_fwd_slab": fwd, "layer_norm_bwd_slab": bwd, "layer_norm_fwd_ring2w": fwd,
                 "layer_norm_fwd_generic": fwd, "layer_norm_bwd_dx_generic": bwd}
 
     def make_device_state(self, rows, dev, seed):

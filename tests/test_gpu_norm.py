@@ -416,7 +416,7 @@ LONG_SHAPES = [(1, 16384), (5, 12288), (37, 16384), (300, 16384), (700, 12288), 
 @pytest.mark.parametrize("rms", [False, True])
 @pytest.mark.parametrize("dt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32), (torch.float16, torch.float16)])
 @pytest.mark.parametrize("M,N", LONG_SHAPES)
-def test_long_rows_take_the_slab_kernels(M, N, dt, wdt, rms):
+def test_long_rows_take_the_two_walk_ring_and_the_slab_kernels(M, N, dt, wdt, rms):
     # rows beyond one CTA's threads (the reference's few-long-rows regime, sycl/Norm.h:620-696): column slabs over a
     # thread-block cluster, statistics exchanged through distributed shared memory, weight gradients still fused;
     # 12296 and 40000 leave a ragged last slab, 300 x 16384 and 700 x 12288 give every cluster several tiles
@@ -428,9 +428,11 @@ def test_long_rows_take_the_slab_kernels(M, N, dt, wdt, rms):
     y_buf, y_chk = guarded_empty((M, N), dt)
     dx_buf, dx_chk = guarded_empty((M, N), dt)
     dg_buf, dg_chk = guarded_empty((N,), wdt)
+    # forward: rows up to 16384 stay inside one CTA (weights in registers, the row walked twice in shared memory)
+    fwd_path = "ring2w" if N <= 16384 else "slab"
     if rms:
         y, rstd = capi._fused_rms_norm(x.to(DEV), [N], g.to(DEV), 1e-6, out=(y_buf, torch.empty(M, device=DEV)))
-        assert capi.last_path() == "slab"
+        assert capi.last_path() == fwd_path
         dx, dw = capi._fused_rms_norm_backward(dy.to(DEV), x.to(DEV), [N], rstd, g.to(DEV), out=(dx_buf, dg_buf))
         assert capi.last_path() == "slab"
         torch.cuda.synchronize()
@@ -444,7 +446,7 @@ def test_long_rows_take_the_slab_kernels(M, N, dt, wdt, rms):
         db_buf, db_chk = guarded_empty((N,), wdt)
         y, mean, rstd = capi.native_layer_norm(x.to(DEV), [N], g.to(DEV), b.to(DEV), 1e-5,
                                                out=(y_buf, torch.empty(M, device=DEV), torch.empty(M, device=DEV)))
-        assert capi.last_path() == "slab"
+        assert capi.last_path() == fwd_path
         dx, dg, db = capi.native_layer_norm_backward(dy.to(DEV), x.to(DEV), [N], mean, rstd, g.to(DEV), b.to(DEV),
                                                      out=(dx_buf, dg_buf, db_buf))
         assert capi.last_path() == "slab"

@@ -9,6 +9,7 @@
 #include "launchers.h"
 #include "norm_generic.cuh"
 #include "norm_ring.cuh"
+#include "norm_ring2w.cuh"
 #include "norm_slab.cuh"
 #include "plan.h"
 
@@ -222,6 +223,23 @@ int norm_fwd_typed(const void* x_, const void* gamma_, const void* beta_, void* 
           case 128: return norm_fwd_ring_launch<T, WT, RMS, 128>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
           case 256: return norm_fwd_ring_launch<T, WT, RMS, 256>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
           default: return norm_fwd_ring_launch<T, WT, RMS, 512>(p, x, gamma, beta, y, mean, rstd, M, N, eps, st);
+        }
+      }
+      if (forced != B2N_PATH_CLUSTER && !p.ok && N > 8192 && N <= 16384) {
+        // rows of up to twice what a ring CTA's registers hold: weights in registers, the row walked twice in shared memory
+        const RingPlan p2 = plan_ring(M, N, sizeof(T), 1, kNorm2wEpt, persistent_ctas(di.sm_count), di.max_smem_optin, 65536);
+        if (p2.ok && p2.group == kRingThreads && p2.stages >= 3) {
+          note_path("ring2w");
+          ProfileScope prof(RMS ? "rms_norm_fwd_ring2w" : "layer_norm_fwd_ring2w", st);
+          auto go = [&](auto kernel, std::atomic<uint64_t>& done) -> int {
+            if (int e = set_smem_once(kernel, p2.smem, done)) return e;
+            return launch_pdl(kernel, dim3(p2.grid), dim3(kRingBlock), p2.smem, st, x, gamma, beta, y, mean, rstd, M,
+                              static_cast<int>(N), static_cast<float>(eps), p2.stages | (p2.lag << 8), p2.rpg,
+                              device_status_ptr(), next_tile_counter());
+          };
+          static std::atomic<uint64_t> done2w[2];
+          if (N == static_cast<int64_t>(kRingThreads) * kNorm2wEpt) return go(norm_fwd_ring2w_kernel<T, WT, RMS, true>, done2w[0]);
+          return go(norm_fwd_ring2w_kernel<T, WT, RMS, false>, done2w[1]);
         }
       }
       if (forced == B2N_PATH_AUTO || forced == B2N_PATH_CLUSTER) {
