@@ -434,7 +434,9 @@ def test_long_rows_take_the_two_walk_ring_and_the_slab_kernels(M, N, dt, wdt, rm
         y, rstd = capi._fused_rms_norm(x.to(DEV), [N], g.to(DEV), 1e-6, out=(y_buf, torch.empty(M, device=DEV)))
         assert capi.last_path() == fwd_path
         dx, dw = capi._fused_rms_norm_backward(dy.to(DEV), x.to(DEV), [N], rstd, g.to(DEV), out=(dx_buf, dg_buf))
-        assert capi.last_path() == "slab"
+        # RMS backward: 16-bit rows up to 16384 stay inside one CTA too (gamma and dgamma in registers); fp32 rows
+        # of that length leave fewer than three stages in shared memory and take the slabs
+        assert capi.last_path() == ("ring2w" if N <= 16384 and dt != torch.float32 else "slab")
         torch.cuda.synchronize()
         y_chk(); dx_chk(); dg_chk()
         ry, rrstd = ao.rms_norm_fwd(x, [N], g, 1e-6)

@@ -281,6 +281,14 @@ template <typename T> RingPlan plan_norm_bwd(int64_t M, int64_t N, const DeviceI
   return plan_ring(M, N, sizeof(T), 2, kNormBwdEpt, full ? di.sm_count : persistent_ctas(di.sm_count),
                    di.max_smem_optin);
 }
+// The two-walk RMS backward: rows of 8192 < N <= 16384 whose two input rows leave three stages in shared memory.
+template <typename T> RingPlan plan_norm_bwd_2w(int64_t M, int64_t N, const DeviceInfo& di, bool full = false) {
+  RingPlan p;
+  if (N <= 8192 || N > 16384) return p;
+  p = plan_ring(M, N, sizeof(T), 2, kNorm2wEpt, full ? di.sm_count : persistent_ctas(di.sm_count), di.max_smem_optin);
+  if (p.ok && (p.group != kRingThreads || p.stages < 3)) p.ok = false;
+  return p;
+}
 // Number of partial rows ([2][N] accumulate-type values each) the weight-gradient reduction writes.
 inline int64_t wgrad_generic_chunks(int64_t M) {
   int64_t c = (M + 63) / 64;
@@ -295,6 +303,9 @@ template <typename T> int64_t wgrad_partial_rows(int64_t M, int64_t N) {
     // the slab kernels write one partial row per cluster: at most one cluster per two SMs
     const SlabPlan sp = plan_slab(M, N, sizeof(T), 2, di.max_smem_optin);
     if (sp.ok && di.sm_count / 2 > rows) rows = di.sm_count / 2;
+    // the two-walk RMS backward (rows of 8192 < N <= 16384) writes one per CTA
+    const RingPlan p2 = plan_norm_bwd_2w<T>(M, N, di, true);
+    if (p2.ok && p2.grid > rows) rows = p2.grid;
   }
   return rows;
 }
@@ -360,6 +371,34 @@ int norm_bwd_typed(const void* dy_, const void* x_, const void* mean_, const voi
         is_aligned(dx, 16) && N <= (1 << 20)) {
       const DeviceInfo& di = device_info();
       const RingPlan p = plan_norm_bwd<T>(M, N, di);
+      if constexpr (RMS) {
+        if (!p.ok && forced == B2N_PATH_AUTO) {
+          // rows of up to twice what a ring CTA's registers hold, RMS norm: gamma and dgamma in registers, two walks
+          const RingPlan p2 = plan_norm_bwd_2w<T>(M, N, di);
+          if (p2.ok) {
+            note_path("ring2w");
+            int e;
+            {
+              ProfileScope prof("rms_norm_bwd_ring2w", st);
+              auto go = [&](auto kernel, std::atomic<uint64_t>& done) -> int {
+                if (int e2 = set_smem_once(kernel, p2.smem, done)) return e2;
+                return launch_pdl(kernel, dim3(p2.grid), dim3(kRingBlock), p2.smem, st, dy, x, rstd, gamma, dx, ws, M,
+                                  static_cast<int>(N), p2.stages | (p2.lag << 8), p2.rpg, device_status_ptr());
+              };
+              static std::atomic<uint64_t> done2w[4];
+              const bool full = N == static_cast<int64_t>(kRingThreads) * kNorm2wEpt;
+              if (wgrad) e = full ? go(rms_norm_bwd_ring2w_kernel<T, WT, true, true>, done2w[0])
+                                  : go(rms_norm_bwd_ring2w_kernel<T, WT, true, false>, done2w[1]);
+              else e = full ? go(rms_norm_bwd_ring2w_kernel<T, WT, false, true>, done2w[2])
+                            : go(rms_norm_bwd_ring2w_kernel<T, WT, false, false>, done2w[3]);
+            }
+            if (partials_out != nullptr) *partials_out = p2.grid;
+            if (e != B2N_OK || !wgrad || partials_out != nullptr) return e;
+            return launch_pdl(norm_bwd_wgrad_fold_kernel<float, WT>, fold_grid, fold_block, 0, st,
+                              static_cast<const float*>(ws), dgamma, dbeta, static_cast<int64_t>(p2.grid), N);
+          }
+        }
+      }
       if (!(p.ok && forced != B2N_PATH_CLUSTER) && (forced == B2N_PATH_AUTO || forced == B2N_PATH_CLUSTER)) {
         const SlabPlan sp = plan_slab(M, N, sizeof(T), 2, di.max_smem_optin);
         if (sp.ok) {

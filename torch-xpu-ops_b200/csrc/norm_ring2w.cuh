@@ -178,4 +178,152 @@ norm_fwd_ring2w_kernel(const T* __restrict__ x, const WT* __restrict__ gamma, co
   }
 }
 
+// RMS norm backward for the same rows, one CTA per row, stage = [dy row | x row], dx overwrites dy:
+//   g = dy * gamma,  xhat = x * rstd,  s2 = sum(g * xhat),  dx = rstd * (g - xhat * s2 / N),  dgamma += dy * xhat.
+// gamma and the dgamma accumulators of the thread's 32 columns live in registers (64 of them) — which is why this
+// exists for RMS norm only: layer norm adds 32 dbeta accumulators, and 96 registers of persistent state do not fit
+// (its rows of this length stay with the slab kernels).  The row is walked twice in shared memory: for s2, then
+// for dx and dgamma.  Tiles are assigned to CTAs in the fixed pattern (no counter), so a CTA's partial weight
+// gradient — row blockIdx.x of ws[P][2][N] — is the same bits on every run; rstd of the next tile's rows is
+// fetched a tile ahead.
+template <typename T, typename WT, bool WGRAD, bool FULL>
+__global__ void __launch_bounds__(kRingBlock, 1)
+rms_norm_bwd_ring2w_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ rstd,
+                           const WT* __restrict__ gamma, T* __restrict__ dx, float* __restrict__ ws, int64_t M, int N,
+                           int S_lag, int RPG, int* status) {
+  using P = Pack16<T>;
+  constexpr int GROUP = kRingThreads;
+  constexpr int VEC = P::VEC, VPT = kNorm2wEpt / VEC, HP = kNorm2wEpt / 2, VH = VEC / 2;
+  constexpr int RB = 2;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  RingShared* rs = reinterpret_cast<RingShared*>(smem_raw);
+  unsigned char* stages = smem_raw + kRingHeaderBytes;
+
+  RingGeom g;
+  g.init(M, N, sizeof(T), RPG, S_lag, 2, nullptr);  // no tile counter: the fixed assignment
+  ring_init(rs, g.S, kRingThreads / 32);
+  const int tid = threadIdx.x;
+  if (tid >= kRingThreads) {
+    ring_producer_regs();
+    if (tid == kRingThreads) {
+      RingProducer<2> prod(rs, stages, g, status);
+      prod.in[0] = reinterpret_cast<const unsigned char*>(dy);
+      prod.in[1] = reinterpret_cast<const unsigned char*>(x);
+      prod.out = reinterpret_cast<unsigned char*>(dx);
+      prod.run();
+    }
+    return;
+  }
+  ring_consumer_regs();
+
+  const int nvec = FULL ? GROUP * VPT : N / VEC;
+  const uint32_t row_bytes = FULL ? static_cast<uint32_t>(GROUP * VPT * 16) : g.row_bytes;
+  const float inv_n = 1.0f / static_cast<float>(N);
+  float2 gw[HP], dg[HP];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = tid + k * GROUP;
+#pragma unroll
+    for (int e = 0; e < VEC; e += 2) {
+      const bool ok = (FULL || v < nvec) && gamma != nullptr;
+      const int col = v * VEC + e;
+      gw[(k * VEC + e) / 2] = ok ? make_float2(to_acc<float>(gamma[col]), to_acc<float>(gamma[col + 1])) : bcast2(1.0f);
+      dg[(k * VEC + e) / 2] = bcast2(0.0f);
+    }
+  }
+  int red_phase = 0;
+  const uint32_t stages_u32 = smem_u32(stages);
+  auto load_rstd = [&](unsigned tile, float (&out)[RB]) {
+#pragma unroll
+    for (int b = 0; b < RB; ++b) {
+      const int64_t row = tile < g.ntiles ? g.first_row(static_cast<int>(tile)) + b : M;
+      out[b] = (b < RPG && row < M) ? __ldg(rstd + row) : 0.0f;
+    }
+  };
+  float rs_c[RB], rs_n[RB];
+  load_rstd(blockIdx.x, rs_c);
+
+  RingCursor cur;
+  cur.start();
+  unsigned k_tile = 0;
+  for (;; cur.advance(g), ++k_tile) {
+    load_rstd(blockIdx.x + (k_tile + 1) * gridDim.x, rs_n);  // the next tile's, used a whole tile from now
+    int i;
+    if (!ring_consumer_wait(rs, cur, status, i) || i < 0) break;
+    const int64_t tile_row0 = g.first_row(i);
+    const uint32_t sbase = stages_u32 + static_cast<uint32_t>(cur.s) * g.stage_bytes;
+    for (int r = 0; r < RPG; r += RB) {
+      const int64_t row_a = tile_row0 + r;
+      if (row_a >= M) break;  // uniform over the CTA
+      bool valid[RB];
+      uint32_t dbase[RB];
+      float rsd[RB];
+      float red[RB];
+#pragma unroll
+      for (int b = 0; b < RB; ++b) {
+        valid[b] = (r + b < RPG) && (row_a + b < M);
+        dbase[b] = sbase + static_cast<uint32_t>(r + b) * row_bytes;
+        rsd[b] = r == 0 ? rs_c[b] : (valid[b] ? __ldg(rstd + row_a + b) : 0.0f);  // (tiles of more than two rows: in place)
+        // ---- walk 1: s2 = sum (dy * gamma) * (x * rstd) ----
+        const float2 rs2 = bcast2(rsd[b]);
+        float2 p2[2] = {bcast2(0.0f), bcast2(0.0f)};
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tid + k * GROUP;
+          if (valid[b] && (FULL || v < nvec)) {
+            float2 dv[VH], xv[VH];
+            P::unpack2(lds128(dbase[b] + v * 16), dv);
+            P::unpack2(lds128(dbase[b] + g.slot_bytes + v * 16), xv);
+#pragma unroll
+            for (int e = 0; e < VH; ++e) p2[e & 1] = fma2(mul2(dv[e], gw[k * VH + e]), mul2(xv[e], rs2), p2[e & 1]);
+          }
+        }
+        red[b] = hsum2(add2(p2[0], p2[1]));
+      }
+      group_reduce<GROUP, RB>(red, rs->red, 0, tid, red_phase, SumOp());
+      // ---- walk 2: dx = rstd * g - xhat * (s2 / N) * rstd, dgamma += dy * xhat ----
+#pragma unroll
+      for (int b = 0; b < RB; ++b) {
+        if (!valid[b]) continue;
+        const float2 rs2 = bcast2(rsd[b]), nar = bcast2(-(red[b] * inv_n * rsd[b]));
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const int v = tid + k * GROUP;
+          if (FULL || v < nvec) {
+            float2 dv[VH], xv[VH], o[VH];
+            P::unpack2(lds128(dbase[b] + v * 16), dv);
+            P::unpack2(lds128(dbase[b] + g.slot_bytes + v * 16), xv);
+#pragma unroll
+            for (int e = 0; e < VH; ++e) {
+              const int j = k * VH + e;
+              const float2 xh = mul2(xv[e], rs2);
+              o[e] = fma2(mul2(dv[e], gw[j]), rs2, mul2(xh, nar));
+              if (WGRAD) dg[j] = fma2(dv[e], xh, dg[j]);
+            }
+            sts128(dbase[b] + v * 16, P::pack2(o));
+          }
+        }
+      }
+    }
+    ring_consumer_release(rs, cur);
+#pragma unroll
+    for (int b = 0; b < RB; ++b) rs_c[b] = rs_n[b];
+  }
+
+  if (WGRAD) {
+    float* wg = ws + static_cast<int64_t>(blockIdx.x) * 2 * N;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int v = tid + k * GROUP;
+      if (FULL || v < nvec) {
+#pragma unroll
+        for (int q = 0; q < VEC / 4; ++q) {
+          const int j = (k * VEC + q * 4) / 2;
+          *reinterpret_cast<float4*>(wg + v * VEC + q * 4) = make_float4(dg[j].x, dg[j].y, dg[j + 1].x, dg[j + 1].y);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace b2n
