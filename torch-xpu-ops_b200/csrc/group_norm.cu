@@ -373,43 +373,51 @@ __device__ __forceinline__ void bn_channel_sums(const T* __restrict__ xc, int64_
       q2[e & 1] = fma2(d, d, q2[e & 1]);
     }
   };
-  // one stride of the CTA as (samples, vectors): j + step_j < 2 * HV, so one wrap suffices
-  const int64_t stride = blockDim.x, step_n = stride / HV, step_j = stride % HV;
-  auto advance = [&](int64_t& n, int64_t& j) {
-    n += step_n;
-    j += step_j;
-    if (j >= HV) { j -= HV; ++n; }
-  };
+  // One stride of the CTA as (samples, vectors): j + step_j < 2 * HV, so one wrap suffices.  The thread carries a
+  // POINTER and its vector index inside the run: a stride adds a constant to the pointer, a wrap into the next
+  // sample's run another constant — no 64-bit multiply per vector.
+  const int64_t stride = blockDim.x;
+  const int64_t step_n = stride / HV;
+  const int hv = static_cast<int>(HV), step_j = static_cast<int>(stride % HV);  // (a run has fewer than 2^31 vectors)
+  const int64_t d_stride = step_n * sample_stride + static_cast<int64_t>(step_j) * V;  // elements
+  const int64_t d_wrap = sample_stride - HV * V;
   int64_t idx = begin + threadIdx.x;
-  int64_t n = idx / HV, j = idx - n * HV;
+  const int64_t n0 = idx / HV;
+  int j = static_cast<int>(idx - n0 * HV);
+  const T* p = xc + n0 * sample_stride + static_cast<int64_t>(j) * V;
+  auto advance = [&]() {
+    j += step_j;
+    p += d_stride;
+    if (j >= hv) { j -= hv; p += d_wrap; }
+  };
   for (; idx + 3 * stride < end; idx += 4 * stride) {
-    const uint4* p[4];
+    const uint4* q[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      p[u] = reinterpret_cast<const uint4*>(xc + n * sample_stride + j * V);
-      advance(n, j);
+      q[u] = reinterpret_cast<const uint4*>(p);
+      advance();
     }
     uint4 w[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) w[u] = __ldg(p[u]);
+    for (int u = 0; u < 4; ++u) w[u] = __ldg(q[u]);
 #pragma unroll
     for (int u = 0; u < 4; ++u) add_vec(w[u]);
   }
   if (idx < end) {
     // the last one to three strides, still loaded together: a stride past the end reads this thread's first vector
     // of the group again (a valid address) and is left out of the sums
-    const uint4* p0 = reinterpret_cast<const uint4*>(xc + n * sample_stride + j * V);
-    const uint4* p[3];
+    const uint4* q0 = reinterpret_cast<const uint4*>(p);
+    const uint4* q[3];
     bool have[3];
 #pragma unroll
     for (int u = 0; u < 3; ++u) {
       have[u] = idx + u * stride < end;
-      p[u] = have[u] ? reinterpret_cast<const uint4*>(xc + n * sample_stride + j * V) : p0;
-      advance(n, j);
+      q[u] = have[u] ? reinterpret_cast<const uint4*>(p) : q0;
+      advance();
     }
     uint4 w[3];
 #pragma unroll
-    for (int u = 0; u < 3; ++u) w[u] = __ldg(p[u]);
+    for (int u = 0; u < 3; ++u) w[u] = __ldg(q[u]);
 #pragma unroll
     for (int u = 0; u < 3; ++u)
       if (have[u]) add_vec(w[u]);
@@ -564,7 +572,9 @@ group_norm_wgrad_range_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   int64_t g0 = static_cast<int64_t>(blockIdx.x) * Gv;
   const int64_t g1 = g0 + Gv < total ? g0 + Gv : total;
   int64_t c = g0 / TV;
-  const int64_t stride = blockDim.x, step_n = stride / HV, step_j = stride % HV;
+  const int64_t stride = blockDim.x, step_n = stride / HV;
+  const int hv = static_cast<int>(HV), step_j32 = static_cast<int>(stride % HV);  // (a run has fewer than 2^31 vectors)
+  const int64_t d_stride = step_n * sample_stride + static_cast<int64_t>(step_j32) * V, d_wrap = sample_stride - HV * V;
   while (g0 < g1) {
     const int64_t cbase = c * TV, cend = cbase + TV;
     const int64_t seg_end = g1 < cend ? g1 : cend;
@@ -586,35 +596,39 @@ group_norm_wgrad_range_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       sg = fmaf(a.x + a.y, rs, sg);
       sb += b.x + b.y;
     };
-    auto advance = [&](int64_t& n, int64_t& j) {
-      n += step_n;
-      j += step_j;
-      if (j >= HV) { j -= HV; ++n; }
-    };
+    // the thread carries its element offset, its sample and its vector index inside the run: a stride adds constants,
+    // a wrap into the next sample's run another one — no 64-bit multiply per vector
     const int64_t end = seg_end - cbase;
     int64_t idx = g0 - cbase + threadIdx.x;
-    int64_t n = idx / HV, j = idx - n * HV;
+    int64_t n = idx / HV;
+    int j = static_cast<int>(idx - n * HV);
+    int64_t off = coff + n * sample_stride + static_cast<int64_t>(j) * V;
+    auto advance = [&]() {
+      n += step_n;
+      j += step_j32;
+      off += d_stride;
+      if (j >= hv) { j -= hv; ++n; off += d_wrap; }
+    };
     for (; idx + 3 * stride < end; idx += 4 * stride) {  // four vector pairs in flight per thread
-      int64_t off[4], ns[4];
+      int64_t offs[4], ns[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        off[u] = coff + n * sample_stride + j * V;
+        offs[u] = off;
         ns[u] = n;
-        advance(n, j);
+        advance();
       }
       uint4 wx[4], wd[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        wx[u] = __ldg(reinterpret_cast<const uint4*>(x + off[u]));
-        wd[u] = __ldg(reinterpret_cast<const uint4*>(dy + off[u]));
+        wx[u] = __ldg(reinterpret_cast<const uint4*>(x + offs[u]));
+        wd[u] = __ldg(reinterpret_cast<const uint4*>(dy + offs[u]));
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) add_vec(wx[u], wd[u], ns[u]);
     }
     for (; idx < end; idx += stride) {
-      const int64_t off = coff + n * sample_stride + j * V;
       add_vec(__ldg(reinterpret_cast<const uint4*>(x + off)), __ldg(reinterpret_cast<const uint4*>(dy + off)), n);
-      advance(n, j);
+      advance();
     }
     block_sum2(sg, sb, scratch);
     if (threadIdx.x == 0) partial[c * max_slots + (static_cast<int64_t>(blockIdx.x) - cbase / Gv)] = make_float2(sg, sb);
